@@ -1,0 +1,100 @@
+// Embedding gather, fused residual-add + RMSNorm, SiLU-mul.
+//
+// Formulas (reference: zhangjianbang-nb/qwen25vl-lite):
+//   embedding   x[n,:] = E[token[n],:]                          src/qwen25vl_lite/text.py:213
+//   RMSNorm     h = x * rsqrt(mean(x^2) + eps) * w              src/qwen25vl_lite/layers.py:27-31
+//   SwiGLU act  f = silu(g) * u, silu(z) = z / (1 + exp(-z))    src/qwen25vl_lite/text.py:66
+// The residual stream x is float in both dtypes; the norm fuses the pending residual update
+// (x += delta) so that a block's output is read once.
+#include "common.cuh"
+
+template <typename T>
+__global__ void embed_gather_kernel(const T* __restrict__ table, const int* __restrict__ ids,
+                                    float* __restrict__ x, int hidden, int vocab) {
+  const int row = blockIdx.x;
+  int id = ids[row];
+  id = id < 0 ? 0 : (id >= vocab ? vocab - 1 : id);  // the host validates ids; never read outside
+  const T* src = table + (size_t)id * hidden;
+  float* dst = x + (size_t)row * hidden;
+  for (int c = threadIdx.x; c < hidden; c += blockDim.x) dst[c] = to_f32(src[c]);
+}
+
+// x[row] += delta[row] (if delta), then out[r] = rmsnorm(x[row]) * w.
+// rows == nullptr: row = r, x is updated in place.  rows != nullptr: row = rows[r], x is left
+// untouched (used for the final norm, which only the wanted positions need).
+template <typename T, bool EXACT>
+__global__ void add_rmsnorm_kernel(float* __restrict__ x, const T* __restrict__ delta,
+                                   const float* __restrict__ w, float eps, T* __restrict__ out,
+                                   const int* __restrict__ rows, int hidden) {
+  extern __shared__ float row_cache[];  // hidden floats + 32 scratch
+  float* scratch = row_cache + hidden;
+  const int r = blockIdx.x;
+  const int row = rows ? rows[r] : r;
+  float* xr = x + (size_t)row * hidden;
+  const T* dr = delta ? delta + (size_t)row * hidden : nullptr;
+  float ss = 0.f;
+  for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
+    float v = xr[c];
+    if (dr) {
+      v += to_f32(dr[c]);
+      if (!rows) xr[c] = v;
+    }
+    row_cache[c] = v;
+    ss += v * v;
+  }
+  const float total = block_sum(ss, scratch);
+  const float inv = EXACT ? 1.0f / sqrtf(total / (float)hidden + eps) : rsqrtf(total / (float)hidden + eps);
+  T* o = out + (size_t)r * hidden;
+  for (int c = threadIdx.x; c < hidden; c += blockDim.x) o[c] = from_f32<T>(row_cache[c] * inv * w[c]);
+}
+
+// gu is [n, 2*inter]: gate in the first half of a row, up in the second.
+template <typename T>
+__global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, int n, int inter) {
+  const size_t total = (size_t)n * inter;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+    const size_t row = i / inter, c = i % inter;
+    const float g = to_f32(gu[row * 2 * inter + c]);
+    const float u = to_f32(gu[row * 2 * inter + inter + c]);
+    out[i] = from_f32<T>(g / (1.0f + expf(-g)) * u);
+  }
+}
+
+template <typename T>
+static int embed_gather(const void* table, const int* ids, float* x, int n, int hidden, int vocab, void* stream) {
+  if (n <= 0) return 0;
+  embed_gather_kernel<T><<<n, 256, 0, (cudaStream_t)stream>>>((const T*)table, ids, x, hidden, vocab);
+  return launch_status();
+}
+
+template <typename T, bool EXACT>
+static int add_rmsnorm(float* x, const void* delta, const float* w, float eps, void* out, const int* rows,
+                       int n_out, int hidden, void* stream) {
+  if (n_out <= 0) return 0;
+  const size_t smem = (size_t)(hidden + 32) * sizeof(float);
+  if (smem > 200 * 1024) return (int)cudaErrorInvalidValue;
+  if (smem > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(add_rmsnorm_kernel<T, EXACT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+  }
+  const int threads = hidden >= 1024 ? 256 : 128;
+  add_rmsnorm_kernel<T, EXACT><<<n_out, threads, smem, (cudaStream_t)stream>>>(x, (const T*)delta, w, eps, (T*)out, rows, hidden);
+  return launch_status();
+}
+
+template <typename T>
+static int silu_mul(const void* gu, void* out, int n, int inter, void* stream) {
+  if (n <= 0) return 0;
+  const size_t total = (size_t)n * inter;
+  size_t blocks = (total + 255) / 256;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  silu_mul_kernel<T><<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>((const T*)gu, (T*)out, n, inter);
+  return launch_status();
+}
+
+Q25_EXPORT int q25_embed_gather_f32(const void* t, const int* ids, float* x, int n, int h, int v, void* s) { return embed_gather<float>(t, ids, x, n, h, v, s); }
+Q25_EXPORT int q25_embed_gather_bf16(const void* t, const int* ids, float* x, int n, int h, int v, void* s) { return embed_gather<bf16>(t, ids, x, n, h, v, s); }
+Q25_EXPORT int q25_add_rmsnorm_f32(float* x, const void* d, const float* w, float eps, void* o, const int* rows, int n, int h, void* s) { return add_rmsnorm<float, true>(x, d, w, eps, o, rows, n, h, s); }
+Q25_EXPORT int q25_add_rmsnorm_bf16(float* x, const void* d, const float* w, float eps, void* o, const int* rows, int n, int h, void* s) { return add_rmsnorm<bf16, false>(x, d, w, eps, o, rows, n, h, s); }
+Q25_EXPORT int q25_silu_mul_f32(const void* gu, void* o, int n, int inter, void* s) { return silu_mul<float>(gu, o, n, inter, s); }
+Q25_EXPORT int q25_silu_mul_bf16(const void* gu, void* o, int n, int inter, void* s) { return silu_mul<bf16>(gu, o, n, inter, s); }

@@ -1,0 +1,105 @@
+// Token selection on the device: argmax, temperature sampling, penalties.
+//
+// Reference (zhangjianbang-nb/qwen25vl-lite):
+//   greedy       temperature <= 0 -> argmax (first maximum)      src/qwen25vl_lite/sampling.py:69-70
+//   temperature  scores = float(logits) / T, softmax, one draw   src/qwen25vl_lite/sampling.py:72,103-106
+//   keying       one random stream per (seed, index of the token being drawn)
+//                                                                src/qwen25vl_lite/engine.py:823-829
+//   penalties    seen tokens: positive logits / r, negative * r; minus presence; minus
+//                frequency * count                               src/qwen25vl_lite/sampling.py:44-64
+//
+// The draw is Gumbel-max: argmax_i(score_i + g_i) with g_i = -log(-log(u_i)) is a sample of
+// softmax(score).  u_i comes from a counter-based generator, so a row needs no scan and no
+// state: key = mix(seed * GOLDEN + token_index), u_i = (top 23 bits of mix(key + i * ODD) + 0.5)
+// / 2^23, mix = the splitmix64 finaliser.  This is not torch.multinomial's stream; the plain
+// implementation of the test-suite restates it.
+#include "common.cuh"
+
+__device__ __forceinline__ unsigned long long mix64(unsigned long long x) {
+  x ^= x >> 30;
+  x *= 0xBF58476D1CE4E5B9ull;
+  x ^= x >> 27;
+  x *= 0x94D049BB133111EBull;
+  x ^= x >> 31;
+  return x;
+}
+
+__device__ __forceinline__ float gumbel(unsigned long long key, int i) {
+  const unsigned long long bits = mix64(key + (unsigned long long)i * 0xD1342543DE82EF95ull) >> 41;
+  const float u = ((float)bits + 0.5f) * (1.0f / 8388608.0f);  // exact: 24-bit odd numerator
+  return -logf(-logf(u));
+}
+
+// One block per row.  temperature[row] <= 0: plain argmax.  Ties go to the lowest index.
+__global__ void sample_rows_kernel(const float* __restrict__ logits, size_t ld, int vocab,
+                                   const float* __restrict__ temperature,
+                                   const unsigned long long* __restrict__ seed,
+                                   const int* __restrict__ token_index, int* __restrict__ out) {
+  __shared__ float best_v[32];
+  __shared__ int best_i[32];
+  const int row = blockIdx.x;
+  const float* lg = logits + (size_t)row * ld;
+  const float t = temperature ? temperature[row] : 0.f;
+  const bool draw = t > 0.f;
+  unsigned long long key = 0;
+  if (draw) key = mix64(seed[row] * 0x9E3779B97F4A7C15ull + (unsigned long long)(long long)token_index[row]);
+  float bv = -INFINITY;
+  int bi = 0x7fffffff;
+  for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
+    float v = lg[i];
+    if (draw) v = v / t + gumbel(key, i);
+    if (v > bv || (v == bv && i < bi) || bi == 0x7fffffff) { bv = v; bi = i; }
+  }
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+    const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+    if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+  }
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  if (lane == 0) { best_v[warp] = bv; best_i[warp] = bi; }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const int nwarps = (blockDim.x + 31) >> 5;
+    for (int w = 1; w < nwarps; ++w)
+      if (best_v[w] > bv || (best_v[w] == bv && best_i[w] < bi)) { bv = best_v[w]; bi = best_i[w]; }
+    out[row] = bi == 0x7fffffff ? 0 : bi;
+  }
+}
+
+// In place on logits[row]: ids/counts of row r are [offsets[r], offsets[r+1]).
+__global__ void apply_penalties_kernel(float* __restrict__ logits, size_t ld, int vocab, const int* __restrict__ ids,
+                                       const int* __restrict__ counts, const int* __restrict__ offsets,
+                                       const float* __restrict__ repetition, const float* __restrict__ presence,
+                                       const float* __restrict__ frequency) {
+  const int row = blockIdx.x;
+  float* lg = logits + (size_t)row * ld;
+  const float r = repetition[row], pr = presence[row], fr = frequency[row];
+  for (int e = offsets[row] + threadIdx.x; e < offsets[row + 1]; e += blockDim.x) {
+    const int id = ids[e];
+    if (id < 0 || id >= vocab) continue;
+    float v = lg[id];
+    if (r != 1.0f) v = v > 0.f ? v / r : v * r;
+    v -= pr;
+    v -= fr * (float)counts[e];
+    lg[id] = v;
+  }
+}
+
+Q25_EXPORT int q25_sample_rows(const float* logits, long long ld, int rows, int vocab, const float* temperature,
+                               const unsigned long long* seed, const int* token_index, int* out, void* stream) {
+  if (rows <= 0) return 0;
+  if (vocab <= 0) return (int)cudaErrorInvalidValue;
+  const int threads = vocab >= 8192 ? 1024 : 256;
+  sample_rows_kernel<<<rows, threads, 0, (cudaStream_t)stream>>>(logits, (size_t)ld, vocab, temperature, seed,
+                                                                 token_index, out);
+  return launch_status();
+}
+
+Q25_EXPORT int q25_apply_penalties(float* logits, long long ld, int rows, int vocab, const int* ids, const int* counts,
+                                   const int* offsets, const float* repetition, const float* presence,
+                                   const float* frequency, void* stream) {
+  if (rows <= 0) return 0;
+  apply_penalties_kernel<<<rows, 256, 0, (cudaStream_t)stream>>>(logits, (size_t)ld, vocab, ids, counts, offsets,
+                                                                 repetition, presence, frequency);
+  return launch_status();
+}

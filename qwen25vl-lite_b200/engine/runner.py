@@ -1,0 +1,250 @@
+"""The step function: one batch of (request, its next tokens) through the model, from the
+cache that earlier steps left, returning logits at the wanted places.
+
+The reference runs prompt portions one request at a time and decoded tokens as a separate
+batch (``ModelRunner.run_prefill_chunk`` / ``run_decode``, src/qwen25vl_lite/engine.py:
+318-335, 430-472) and rebuilds its index tensors from Python lists every step
+(engine.py:296,314,322,439-452).  Here a step is one flat batch: portions of prompts of any
+length beside single decoded tokens, described by a handful of int32 arrays that are packed
+on the host and copied to the device in one transfer.
+
+Per step, for S entries holding N tokens in all (everything int32):
+
+    token_ids[N]          positions[axes, N]      token_seq[N]   entry of each token
+    cu_q[S + 1]           first token of each entry
+    q_start_pos[S]        tokens of the request already in the cache
+    slot_ids[S]           per-request state slot
+    logit_rows[M]         flat indices of the tokens whose logits are wanted
+    per cache group:      kv_slot[N] (page * page_size + offset), block_table[S, W]
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Dict, List, Optional, Sequence
+
+import numpy as np
+import torch
+
+from ..cache.manager import CacheManager, RequestCache
+from ..models.decoder import DecoderModel, StopRuntime
+
+
+@dataclass
+class Request:
+    """A live request as the step function sees it."""
+
+    request_id: object
+    cache: RequestCache
+
+    @property
+    def num_computed(self) -> int:
+        return self.cache.num_tokens
+
+
+@dataclass
+class StepEntry:
+    request: Request
+    tokens: Sequence[int]
+    want: Sequence[int] = ()                     # indices into ``tokens``
+    positions: Optional[np.ndarray] = None       # [axes, len(tokens)]; None = plain text
+
+
+@dataclass
+class KVStep:
+    """A cache group's side of one step, as a mixer's kernels need it."""
+
+    k_pages: torch.Tensor = None
+    v_pages: torch.Tensor = None
+    kv_slot: torch.Tensor = None
+    block_table: torch.Tensor = None
+    page_size: int = 0
+
+
+@dataclass
+class StepContext:
+    dtype: torch.dtype
+    device: torch.device
+    n_tokens: int
+    n_seqs: int
+    token_ids: torch.Tensor
+    positions: torch.Tensor
+    token_seq: torch.Tensor
+    cu_q: torch.Tensor
+    q_start_pos: torch.Tensor
+    slot_ids: torch.Tensor
+    logit_rows: Optional[torch.Tensor]
+    max_q_len: int
+    max_kv_len: int
+    group_kv_slot: List[torch.Tensor]
+    group_block_table: List[torch.Tensor]
+    cache: CacheManager
+    # host copies, for parts written with torch operators (toy parts in tests)
+    host_q_lens: List[int] = field(default_factory=list)
+    host_q_start: List[int] = field(default_factory=list)
+    host_slots: List[int] = field(default_factory=list)
+
+    def kv(self, stop: StopRuntime) -> KVStep:
+        group, k_pages, v_pages = self.cache.stop_pages(stop.index)
+        return KVStep(k_pages, v_pages, self.group_kv_slot[group.index], self.group_block_table[group.index],
+                      group.page_size)
+
+
+class ModelRunner:
+    """Owns the model, the cache and the staging buffers; ``step`` is the step function."""
+
+    def __init__(self, model: DecoderModel, num_pages: int, page_size: int, max_requests: int,
+                 max_step_tokens: int = 8192):
+        if model.dtype is None:
+            raise ValueError("the model has no weights loaded")
+        self.model = model
+        self.device = model.device
+        self.dtype = model.dtype
+        self.cache = CacheManager(model.stop_needs(), num_pages, page_size, max_requests)
+        self.cache.allocate_device(self.device, self.dtype)
+        for stop in model.stops:
+            stop.state = self.cache.states.get(stop.index)
+        self.axes = model.position.axes
+        self.vocab_size = model.head.vocab_size
+        self._staging: Optional[torch.Tensor] = None
+        self._staging_free = torch.cuda.Event() if self.device.type == "cuda" else None
+        self._reserve(max_step_tokens * (3 + self.axes + len(self.cache.groups)) + 4096)
+        self.live: Dict[object, Request] = {}
+        self.steps = 0
+
+    # ---- requests ----------------------------------------------------------------------
+    def open_request(self, request_id) -> Request:
+        if request_id in self.live:
+            raise ValueError(f"request {request_id!r} is already live")
+        req = Request(request_id, self.cache.open())
+        self.live[request_id] = req
+        return req
+
+    def close_request(self, req: Request) -> None:
+        self.cache.close(req.cache)
+        self.live.pop(req.request_id, None)
+
+    # ---- the step ----------------------------------------------------------------------
+    def _reserve(self, n_ints: int) -> None:
+        if self._staging is not None and self._staging.numel() >= n_ints:
+            return
+        n_ints = max(n_ints, 1 << 16)
+        pin = self.device.type == "cuda"
+        self._staging = torch.empty(n_ints, dtype=torch.int32, pin_memory=pin)
+        self._staging_np = self._staging.numpy()
+        self._device_ints = torch.empty(n_ints, dtype=torch.int32, device=self.device)
+
+    def step(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
+        """Runs the tokens the entries bring, as one batch.  Returns float32 logits
+        [number of wanted places, vocab] on the device, in the order of the entries and of
+        each entry's ``want`` (None when nothing is wanted).  On return the tokens are in
+        the cache and every request's count has advanced."""
+        if not entries:
+            return None
+        ps = self.cache.page_size
+        groups = self.cache.groups
+        q_lens = [len(e.tokens) for e in entries]
+        if min(q_lens) <= 0:
+            raise ValueError("a step entry brings no tokens")
+        if len({id(e.request) for e in entries}) != len(entries):
+            raise ValueError("a request appears twice in one step")
+        S, N = len(entries), int(sum(q_lens))
+        starts = [e.request.cache.num_tokens for e in entries]
+        for e, n, s in zip(entries, q_lens, starts):
+            self.cache.ensure(e.request.cache, s + n)       # no-op when the caller already did
+        widths = [max(max(len(e.request.cache.tables[g.index]) for e in entries), 1) for g in groups]
+        M = sum(len(e.want) for e in entries)
+
+        # ---- pack ----
+        total = N * (2 + self.axes + len(groups)) + (S + 1) + 2 * S + M + S * sum(widths) + 4 * (7 + 2 * len(groups))
+        self._reserve(total)
+        if self._staging_free is not None:
+            self._staging_free.synchronize()               # the last copy out of the staging buffer is done
+        buf = self._staging_np
+        off = 0
+
+        def take(n):
+            nonlocal off
+            view = buf[off:off + n]
+            span = (off, n)
+            off += (n + 3) & ~3                           # every array starts on a 16-byte boundary
+            return view, span
+
+        tok, tok_s = take(N)
+        pos, pos_s = take(self.axes * N)
+        pos = pos.reshape(self.axes, N)
+        tseq, tseq_s = take(N)
+        cu, cu_s = take(S + 1)
+        qs, qs_s = take(S)
+        sl, sl_s = take(S)
+        rows, rows_s = take(M)
+        g_slot, g_slot_s, g_tab, g_tab_s = [], [], [], []
+        for g, w in zip(groups, widths):
+            a, a_s = take(N)
+            b, b_s = take(S * w)
+            g_slot.append(a); g_slot_s.append(a_s); g_tab.append(b.reshape(S, w)); g_tab_s.append(b_s)
+
+        at = 0
+        r = 0
+        cu[0] = 0
+        last_position = []
+        for i, (e, n, s) in enumerate(zip(entries, q_lens, starts)):
+            ids = np.asarray(e.tokens, dtype=np.int64)
+            if ids.min() < 0 or ids.max() >= self.vocab_size:
+                raise ValueError(f"request {e.request.request_id!r}: token id outside [0, {self.vocab_size})")
+            tok[at:at + n] = ids
+            if e.positions is None:
+                pos[:, at:at + n] = self.model.position.default_positions(s, n, e.request.cache.position_offset)
+            else:
+                p = np.asarray(e.positions)
+                if p.shape != (self.axes, n):
+                    raise ValueError(f"positions must be [{self.axes}, {n}], got {p.shape}")
+                pos[:, at:at + n] = p
+            last_position.append(int(pos[:, at:at + n].max()))
+            tseq[at:at + n] = i
+            cu[i + 1] = at + n
+            qs[i] = s
+            sl[i] = e.request.cache.slot
+            for w_ in e.want:
+                if not 0 <= int(w_) < n:
+                    raise ValueError(f"wanted place {w_} is outside the {n} tokens of the entry")
+                rows[r] = at + int(w_)
+                r += 1
+            logical = np.arange(s, s + n)
+            for g, gs, gt in zip(groups, g_slot, g_tab):
+                table = np.asarray(e.request.cache.tables[g.index], dtype=np.int64)
+                gs[at:at + n] = table[logical // ps] * ps + logical % ps
+                gt[i, :len(table)] = np.maximum(table, 0)
+                gt[i, len(table):] = 0
+            at += n
+
+        dev = self._device_ints
+        dev[:off].copy_(self._staging[:off], non_blocking=True)
+        if self._staging_free is not None:
+            self._staging_free.record()
+
+        def d(span, shape=None):
+            t = dev[span[0]:span[0] + span[1]]
+            return t if shape is None else t.view(shape)
+
+        ctx = StepContext(
+            dtype=self.dtype, device=self.device, n_tokens=N, n_seqs=S,
+            token_ids=d(tok_s), positions=d(pos_s, (self.axes, N)), token_seq=d(tseq_s), cu_q=d(cu_s),
+            q_start_pos=d(qs_s), slot_ids=d(sl_s), logit_rows=d(rows_s) if M else None,
+            max_q_len=max(q_lens), max_kv_len=max(s + n for s, n in zip(starts, q_lens)),
+            group_kv_slot=[d(s_) for s_ in g_slot_s],
+            group_block_table=[d(s_, (S, w)) for s_, w in zip(g_tab_s, widths)],
+            cache=self.cache, host_q_lens=q_lens, host_q_start=starts,
+            host_slots=[e.request.cache.slot for e in entries],
+        )
+        logits = self.model.forward(ctx)
+
+        for e, n, p_max in zip(entries, q_lens, last_position):
+            # plain text that follows resumes one past the largest position seen so far
+            # (the reference's rope_delta = max(pos) + 1 - length, src/qwen25vl_lite/rope.py:235)
+            c = e.request.cache
+            c.max_position = max(c.max_position, p_max)
+            self.cache.advance(c, n)
+            c.position_offset = c.max_position + 1 - c.num_tokens
+        self.steps += 1
+        return logits

@@ -1,0 +1,370 @@
+"""Continuous batching above the step function: admit, cut prompts into portions under a
+token budget, decode, finish, free; and what happens when pages run out.
+
+After the reference's ``LLMEngine`` (src/qwen25vl_lite/engine.py:489-937), with these
+decisions of its own:
+
+* one step is one batch.  Every running request has ``pending`` tokens not yet in the
+  cache (a whole prompt, the rest of one, or the one token it generated last); the step
+  feeds ``min(pending, budget)`` of them and samples when the portion reaches the end.
+  Decoded tokens are taken first (one each), prompts share what is left of
+  ``max_num_batched_tokens``, continuing prompts before new admissions, all first come
+  first served.  (The reference's budget counts prompt tokens only and each portion is a
+  forward pass of its own, engine.py:631-698, 748-778.)
+* a request whose prompt completes in a step samples its first token from that step and
+  decodes from the next one on (the reference also decodes it in the same iteration,
+  engine.py:780-805).
+* pages run out: a waiting request is only admitted when its first portion fits, and
+  never by evicting another.  When a *running* request cannot get the pages for its next
+  tokens, the newest running request (lowest priority first) is preempted: its pages and
+  state slot are given back and it returns to the front of the waiting queue with
+  ``prompt + generated`` as the tokens to recompute, positions and sampling keys
+  unchanged, so it continues exactly where it stopped.  (The reference's recompute
+  re-runs the prompt only and loses the generated tokens' keys, engine.py:713-718.)
+  If the request that lacks pages is the only one running, nothing can be freed:
+  ``RuntimeError("pool too small ...")``.
+* finishing: EOS unless ``ignore_eos``, ``stop_token_ids``, ``max_tokens``,
+  ``prompt + output >= max_model_len`` (engine.py:831-872).
+"""
+
+from __future__ import annotations
+
+import time
+from collections import deque
+from dataclasses import dataclass, field
+from typing import Deque, Dict, List, Optional, Sequence as Seq
+
+import numpy as np
+
+from ..cache.page_pool import OutOfPages
+from ..config.engine_config import EngineConfig
+from ..sampling.params import SamplingParams
+from ..sampling.sampler import new_seed
+from .runner import Request, StepEntry
+
+
+@dataclass
+class RequestOutput:
+    """What the caller gets back for a finished request (engine.py:96-112)."""
+
+    seq_id: int
+    prompt_token_ids: List[int]
+    output_token_ids: List[int]
+    finish_reason: str
+    metrics: Dict[str, float] = field(default_factory=dict)
+
+    @property
+    def num_prompt_tokens(self) -> int:
+        return len(self.prompt_token_ids)
+
+    @property
+    def num_output_tokens(self) -> int:
+        return len(self.output_token_ids)
+
+
+@dataclass
+class Sequence:
+    seq_id: int
+    prompt_token_ids: List[int]
+    params: SamplingParams
+    seed: int
+    prompt_positions: Optional[np.ndarray] = None      # [axes, len(prompt)] or None (plain text)
+    rope_delta: int = 0
+    priority: int = 0
+    output_token_ids: List[int] = field(default_factory=list)
+    request: Optional[Request] = None                  # live handle of the step function
+    status: str = "waiting"                            # waiting | running | finished
+    arrival: float = field(default_factory=time.time)
+    first_token_at: Optional[float] = None
+    preemptions: int = 0
+
+    @property
+    def num_tokens(self) -> int:
+        return len(self.prompt_token_ids) + len(self.output_token_ids)
+
+    @property
+    def num_computed(self) -> int:
+        return self.request.num_computed if self.request is not None else 0
+
+    @property
+    def pending(self) -> int:
+        return self.num_tokens - self.num_computed
+
+    def tokens(self, start: int, end: int) -> List[int]:
+        p = len(self.prompt_token_ids)
+        if end <= p:
+            return self.prompt_token_ids[start:end]
+        return (self.prompt_token_ids[start:] if start < p else []) + self.output_token_ids[max(start - p, 0):end - p]
+
+    def positions(self, start: int, end: int) -> Optional[np.ndarray]:
+        """Explicit positions of tokens [start, end) when the prompt came with positions."""
+        if self.prompt_positions is None:
+            return None
+        p = len(self.prompt_token_ids)
+        cols = []
+        if start < p:
+            cols.append(self.prompt_positions[:, start:min(end, p)])
+        if end > p:
+            run = np.arange(max(start, p), end, dtype=np.int64) + self.rope_delta
+            cols.append(np.broadcast_to(run, (self.prompt_positions.shape[0], run.shape[0])))
+        return np.concatenate(cols, axis=1)
+
+
+@dataclass
+class EngineStats:
+    steps: int = 0
+    prefill_tokens: int = 0
+    decode_tokens: int = 0
+    generated_tokens: int = 0
+    preemptions: int = 0
+    finished: int = 0
+    _window: Deque = field(default_factory=lambda: deque(maxlen=64), repr=False)
+
+    def record_step(self, seconds: float, decoded: int) -> None:
+        if decoded:
+            self._window.append((seconds, decoded))
+
+    @property
+    def decode_tokens_per_s(self) -> float:
+        t = sum(s for s, _ in self._window)
+        return sum(n for _, n in self._window) / t if t > 0 else 0.0
+
+
+class LLMEngine:
+    """``add_request`` / ``step`` / ``run_until_complete`` as in the reference.  ``runner``
+    must offer ``cache``, ``open_request``, ``close_request`` and ``step(entries)``;
+    ``sampler`` must offer ``sample(logits, params, seeds, token_indices, previous)``."""
+
+    def __init__(self, runner, sampler, engine_cfg: EngineConfig, eos_token_id: Optional[int] = None):
+        self.runner = runner
+        self.sampler = sampler
+        self.ecfg = engine_cfg
+        self.eos_token_id = eos_token_id
+        self.waiting: Deque[Sequence] = deque()
+        self.running: List[Sequence] = []
+        self.finished: List[RequestOutput] = []
+        self.stats_ = EngineStats()
+        self._next_id = 0
+
+    # ---- requests ----------------------------------------------------------------------
+    def add_request(self, prompt_token_ids: Seq[int], sampling_params: Optional[SamplingParams] = None, *,
+                    positions=None, image_spans=None, priority: int = 0) -> int:
+        """Registers a request and returns its id.  ``positions`` ([axes, len(prompt)]) or
+        ``image_spans`` ([(start, t, h, w)], merged grid units) describe a prompt with image
+        runs; without them the prompt is plain text."""
+        params = sampling_params or SamplingParams()
+        params.validate()
+        if params.stop:
+            raise ValueError("string stop sequences need a tokenizer; the engine accepts only stop_token_ids")
+        ids = [int(t) for t in prompt_token_ids]
+        if not ids:
+            raise ValueError("prompt is empty")
+        if len(ids) > self.ecfg.max_model_len:
+            raise ValueError(f"prompt of {len(ids)} tokens exceeds max_model_len {self.ecfg.max_model_len}")
+        rope_delta = 0
+        if image_spans is not None and positions is None:
+            from ..parts.position import prompt_positions
+            positions, rope_delta = prompt_positions(len(ids), image_spans)
+        if positions is not None:
+            positions = np.asarray(positions, dtype=np.int64)
+            if positions.ndim != 2 or positions.shape[1] != len(ids):
+                raise ValueError(f"positions must be [axes, {len(ids)}], got {positions.shape}")
+            rope_delta = int(positions.max()) + 1 - len(ids)
+        seq = Sequence(self._next_id, ids, params, params.seed if params.seed is not None else new_seed(),
+                       positions, rope_delta, priority)
+        probe_pages = -(-len(ids) // self.ecfg.block_size)
+        if all(g.window is None for g in self.runner.cache.groups) and probe_pages > self.runner.cache.num_pages:
+            raise ValueError(f"prompt of {len(ids)} tokens needs {probe_pages} pages, the pool has "
+                             f"{self.runner.cache.num_pages}")
+        self._next_id += 1
+        self.waiting.append(seq)
+        return seq.seq_id
+
+    def abort(self, seq_id: int) -> bool:
+        for seq in list(self.running) + list(self.waiting):
+            if seq.seq_id == seq_id:
+                self._release(seq)
+                if seq in self.running:
+                    self.running.remove(seq)
+                else:
+                    self.waiting.remove(seq)
+                seq.status = "finished"
+                return True
+        return False
+
+    def has_work(self) -> bool:
+        return bool(self.waiting or self.running)
+
+    # ---- scheduling --------------------------------------------------------------------
+    def _release(self, seq: Sequence) -> None:
+        if seq.request is not None:
+            self.runner.close_request(seq.request)
+            seq.request = None
+
+    def _preempt(self, victim: Sequence, scheduled: Dict[int, int]) -> None:
+        self.running.remove(victim)
+        scheduled.pop(victim.seq_id, None)
+        self._release(victim)
+        victim.status = "waiting"
+        victim.preemptions += 1
+        self.stats_.preemptions += 1
+        self.waiting.appendleft(victim)
+
+    def _portion(self, seq: Sequence, budget: int) -> int:
+        if seq.pending <= budget:
+            return seq.pending
+        return budget if self.ecfg.enable_chunked_prefill else 0
+
+    def schedule(self) -> Dict[int, int]:
+        """Decides this step: ``{seq_id: number of tokens to feed}``; admits and preempts
+        as a side effect.  Every chosen portion has its pages."""
+        budget = self.ecfg.max_num_batched_tokens
+        scheduled: Dict[int, int] = {}
+        cache = self.runner.cache
+        for want_decode in (True, False):
+            for seq in list(self.running):
+                if seq not in self.running or seq.seq_id in scheduled or (seq.pending == 1) != want_decode:
+                    continue
+                n = self._portion(seq, budget)
+                if n <= 0:
+                    continue
+                while True:
+                    try:
+                        cache.ensure(seq.request.cache, seq.num_computed + n)
+                        break
+                    except OutOfPages:
+                        victim = min(self.running, key=lambda s: (s.priority, -s.arrival, -s.seq_id))
+                        if len(self.running) == 1:
+                            raise RuntimeError(
+                                f"pool too small: request {seq.seq_id} needs pages for {seq.num_computed + n} tokens "
+                                f"and nothing else is running that could give pages back") from None
+                        budget += scheduled.get(victim.seq_id, 0)
+                        self._preempt(victim, scheduled)
+                        if victim is seq:
+                            n = 0
+                            break
+                if n > 0:
+                    scheduled[seq.seq_id] = n
+                    budget -= n
+        while self.waiting and budget > 0 and len(self.running) < self.ecfg.max_num_seqs and cache.free_slots > 0:
+            seq = self.waiting[0]
+            n = self._portion(seq, budget)
+            if n <= 0:
+                break
+            request = self.runner.open_request(seq.seq_id)
+            if not cache.can_hold(request.cache, n):
+                self.runner.close_request(request)
+                if not self.running:
+                    raise RuntimeError(f"pool too small: the first {n} tokens of request {seq.seq_id} do not fit "
+                                       f"an empty pool")
+                break
+            cache.ensure(request.cache, n)
+            seq.request = request
+            seq.status = "running"
+            self.waiting.popleft()
+            self.running.append(seq)
+            scheduled[seq.seq_id] = n
+            budget -= n
+        return scheduled
+
+    # ---- stepping ----------------------------------------------------------------------
+    def step(self) -> List[RequestOutput]:
+        """One scheduling iteration and one batch; returns the requests that finished."""
+        t0 = time.perf_counter()
+        scheduled = self.schedule()
+        by_id = {s.seq_id: s for s in self.running}
+        entries, samplers = [], []
+        decoded = 0
+        for seq_id, n in scheduled.items():
+            seq = by_id[seq_id]
+            start = seq.num_computed
+            reaches_end = start + n == seq.num_tokens
+            entries.append(StepEntry(seq.request, seq.tokens(start, start + n), [n - 1] if reaches_end else [],
+                                     seq.positions(start, start + n)))
+            if reaches_end:
+                samplers.append(seq)
+            if n == 1 and seq.output_token_ids:
+                decoded += 1
+                self.stats_.decode_tokens += 1
+            else:
+                self.stats_.prefill_tokens += n
+        done: List[RequestOutput] = []
+        if entries:
+            logits = self.runner.step(entries)
+            if samplers:
+                tokens = self.sampler.sample(
+                    logits, [s.params for s in samplers], [s.seed for s in samplers],
+                    [len(s.output_token_ids) for s in samplers], [s.output_token_ids for s in samplers])
+                for seq, token in zip(samplers, tokens):
+                    self._accept(seq, int(token), done)
+        self.stats_.steps += 1
+        self.stats_.record_step(time.perf_counter() - t0, decoded)
+        self.finished.extend(done)
+        return done
+
+    def _accept(self, seq: Sequence, token: int, done: List[RequestOutput]) -> None:
+        seq.output_token_ids.append(token)
+        self.stats_.generated_tokens += 1
+        if seq.first_token_at is None:
+            seq.first_token_at = time.time()
+        p = seq.params
+        reason = None
+        if self.eos_token_id is not None and token == self.eos_token_id and not p.ignore_eos:
+            reason = "stop"
+        elif token in set(p.stop_token_ids or ()):
+            reason = "stop"
+        elif len(seq.output_token_ids) >= p.max_tokens:
+            reason = "length"
+        elif seq.num_tokens >= self.ecfg.max_model_len:
+            reason = "length"
+        if reason is None:
+            return
+        seq.status = "finished"
+        self._release(seq)
+        self.running.remove(seq)
+        self.stats_.finished += 1
+        done.append(RequestOutput(
+            seq.seq_id, list(seq.prompt_token_ids), list(seq.output_token_ids), reason,
+            {"prompt_tokens": float(len(seq.prompt_token_ids)),
+             "completion_tokens": float(len(seq.output_token_ids)),
+             "ttft_s": max(0.0, seq.first_token_at - seq.arrival),
+             "elapsed_s": time.time() - seq.arrival,
+             "preemptions": float(seq.preemptions)}))
+
+    # ---- driver ------------------------------------------------------------------------
+    def run_until_complete(self, max_steps: int = 1_000_000, max_stall: int = 64) -> List[RequestOutput]:
+        """Steps until every request has finished.  ``max_stall`` steps in a row without
+        progress raise instead of spinning (engine.py:878-905)."""
+        steps = stall = 0
+        last = self._progress()
+        while self.has_work() and steps < max_steps:
+            self.step()
+            steps += 1
+            now = self._progress()
+            if now == last:
+                stall += 1
+                if stall >= max_stall:
+                    raise RuntimeError(f"scheduler made no progress for {max_stall} steps "
+                                       f"(waiting={len(self.waiting)} running={len(self.running)})")
+            else:
+                stall, last = 0, now
+        if self.has_work():
+            raise RuntimeError(f"engine did not finish within {max_steps} steps")
+        return self.finished
+
+    def _progress(self):
+        return (len(self.waiting), len(self.running), len(self.finished), self.stats_.preemptions,
+                sum(s.num_computed + len(s.output_token_ids) for s in self.running))
+
+    def stats(self) -> Dict[str, float]:
+        st = self.stats_
+        cache = self.runner.cache
+        return {
+            "steps": float(st.steps), "prefill_tokens": float(st.prefill_tokens),
+            "decode_tokens": float(st.decode_tokens), "generated_tokens": float(st.generated_tokens),
+            "preemptions": float(st.preemptions), "finished": float(st.finished),
+            "waiting": float(len(self.waiting)), "running": float(len(self.running)),
+            "kv_blocks_used": float(max(cache.pages_in_use(), default=0)),
+            "kv_blocks_total": float(cache.num_pages),
+            "decode_tokens_per_s": st.decode_tokens_per_s,
+        }

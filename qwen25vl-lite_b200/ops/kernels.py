@@ -1,0 +1,190 @@
+"""Python face of the CUDA kernels: each function checks its tensors and launches one kernel
+on torch's current stream through ctypes.
+
+There is no fallback: on a machine without the built library, or when a launch fails, the
+call raises.  Tensors are torch CUDA tensors used as typed device buffers; nothing here
+calls a torch operator on the data.
+"""
+
+from __future__ import annotations
+
+import ctypes
+from typing import Dict, Optional
+
+import torch
+
+from .build import build_library
+
+_P = ctypes.c_void_p
+_I = ctypes.c_int
+_F = ctypes.c_float
+_LL = ctypes.c_longlong
+
+_SIGNATURES = {
+    "q25_embed_gather": [_P, _P, _P, _I, _I, _I, _P],
+    "q25_add_rmsnorm": [_P, _P, _P, _F, _P, _P, _I, _I, _P],
+    "q25_silu_mul": [_P, _P, _I, _I, _P],
+    "q25_rope_store": [_P, _P, _I, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P],
+    "q25_paged_attention_generic": [_P, _I, _P, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _P],
+}
+_UNTYPED = {
+    "q25_gemm_f32": [_P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P],
+    "q25_sample_rows": [_P, _LL, _I, _I, _P, _P, _P, _P, _P],
+    "q25_apply_penalties": [_P, _LL, _I, _I, _P, _P, _P, _P, _P, _P, _P],
+}
+
+_SUFFIX = {torch.float32: "_f32", torch.bfloat16: "_bf16"}
+_libs: Dict[str, ctypes.CDLL] = {}
+_fns: Dict[str, object] = {}
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+def load_library(name: str = "core") -> ctypes.CDLL:
+    """Builds (first use) and loads a kernel library; raises if that is not possible."""
+    lib = _libs.get(name)
+    if lib is None:
+        path = build_library(name)
+        try:
+            lib = ctypes.CDLL(path)
+        except OSError as exc:  # pragma: no cover - depends on the machine
+            raise KernelError(f"cannot load the CUDA kernel library {path}: {exc}") from exc
+        _libs[name] = lib
+    return lib
+
+
+def _fn(symbol: str, argtypes, library: str = "core"):
+    f = _fns.get(symbol)
+    if f is None:
+        lib = load_library(library)
+        try:
+            f = getattr(lib, symbol)
+        except AttributeError as exc:
+            raise KernelError(f"the kernel library has no symbol {symbol}") from exc
+        f.argtypes = argtypes
+        f.restype = _I
+        _fns[symbol] = f
+    return f
+
+
+def _typed(base: str, dtype: torch.dtype):
+    try:
+        return _fn(base + _SUFFIX[dtype], _SIGNATURES[base])
+    except KeyError:
+        raise KernelError(f"{base}: unsupported dtype {dtype}") from None
+
+
+def _check(code: int, what: str) -> None:
+    if code != 0:
+        raise KernelError(f"CUDA kernel {what} could not be launched: cudaError {code} "
+                          f"({torch.cuda.get_device_name() if torch.cuda.is_available() else 'no device'})")
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _ptr(t: Optional[torch.Tensor]) -> int:
+    return 0 if t is None else t.data_ptr()
+
+
+def _dev(t: torch.Tensor, dtype: torch.dtype, what: str) -> torch.Tensor:
+    if not t.is_cuda or t.dtype != dtype or not t.is_contiguous():
+        raise KernelError(f"{what}: needs a contiguous CUDA tensor of {dtype}, got {t.dtype} on {t.device}, "
+                          f"contiguous={t.is_contiguous()}")
+    return t
+
+
+# ---------------------------------------------------------------------------------------------
+
+
+def embed_gather(table: torch.Tensor, ids: torch.Tensor, x_out: torch.Tensor) -> None:
+    """x_out[n, :] (float32) = table[ids[n], :]."""
+    n, hidden = x_out.shape
+    _dev(ids, torch.int32, "embed_gather ids"); _dev(x_out, torch.float32, "embed_gather out")
+    _check(_typed("q25_embed_gather", table.dtype)(table.data_ptr(), ids.data_ptr(), x_out.data_ptr(), n, hidden,
+                                                   table.shape[0], _stream()), "embed_gather")
+
+
+def add_rmsnorm(x: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Tensor, eps: float,
+                out: torch.Tensor, rows: Optional[torch.Tensor] = None) -> None:
+    """x += delta (when given); out = rmsnorm(x) * weight.  With ``rows`` only those rows are
+    normalised into out[0..len(rows)) and x is left as it is."""
+    hidden = x.shape[-1]
+    n_out = out.shape[0]
+    _dev(x, torch.float32, "add_rmsnorm x"); _dev(weight, torch.float32, "add_rmsnorm weight")
+    if delta is not None:
+        _dev(delta, out.dtype, "add_rmsnorm delta")
+    if rows is not None:
+        _dev(rows, torch.int32, "add_rmsnorm rows")
+    _check(_typed("q25_add_rmsnorm", out.dtype)(x.data_ptr(), _ptr(delta), weight.data_ptr(), float(eps),
+                                                out.data_ptr(), _ptr(rows), n_out, hidden, _stream()), "add_rmsnorm")
+
+
+def silu_mul(gate_up: torch.Tensor, out: torch.Tensor) -> None:
+    n, inter = out.shape
+    _dev(gate_up, out.dtype, "silu_mul input")
+    _check(_typed("q25_silu_mul", out.dtype)(gate_up.data_ptr(), out.data_ptr(), n, inter, _stream()), "silu_mul")
+
+
+def rope_store(qkv: torch.Tensor, positions: Optional[torch.Tensor], inv_freq: Optional[torch.Tensor],
+               axis: Optional[torch.Tensor], k_pages: Optional[torch.Tensor], v_pages: Optional[torch.Tensor],
+               kv_slot: Optional[torch.Tensor], nq: int, nkv: int, head_dim: int, page_size: int) -> None:
+    """Rotates q (in place) and k by the position encoding and writes k, v into the pages at
+    ``kv_slot``.  positions None: no rotation; pages None: nothing stored."""
+    n = qkv.shape[0]
+    rotate = positions is not None
+    store = k_pages is not None
+    _check(_typed("q25_rope_store", qkv.dtype)(
+        qkv.data_ptr(), _ptr(positions), n, _ptr(inv_freq), _ptr(axis), _ptr(k_pages), _ptr(v_pages), _ptr(kv_slot),
+        nq, nkv, head_dim, page_size, int(rotate), int(store), _stream()), "rope_store")
+
+
+def paged_attention_generic(qkv: torch.Tensor, out: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor,
+                            block_table: torch.Tensor, token_seq: torch.Tensor, cu_q: torch.Tensor,
+                            q_start_pos: torch.Tensor, nq: int, nkv: int, head_dim: int, page_size: int,
+                            window: int, scale: float) -> None:
+    n = qkv.shape[0]
+    if head_dim % 16 or head_dim > 256:
+        raise KernelError(f"attention: head size {head_dim} is not a multiple of 16 up to 256")
+    _check(_typed("q25_paged_attention_generic", qkv.dtype)(
+        qkv.data_ptr(), qkv.stride(0), out.data_ptr(), k_pages.data_ptr(), v_pages.data_ptr(), block_table.data_ptr(),
+        block_table.shape[1], token_seq.data_ptr(), cu_q.data_ptr(), q_start_pos.data_ptr(), n, nq, nkv, head_dim,
+        page_size, int(window or 0), float(scale), _stream()), "paged_attention_generic")
+
+
+def gemm_f32(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor) -> None:
+    """out[M,N] = a[M,K] . w[N,K]^T + bias, plain float32 FMA."""
+    m, k = a.shape
+    n = w.shape[0]
+    if w.shape[1] != k or out.shape[0] != m or out.shape[1] != n:
+        raise KernelError(f"gemm_f32: shapes {tuple(a.shape)} x {tuple(w.shape)}^T -> {tuple(out.shape)} do not agree")
+    for t, what in ((a, "a"), (w, "w"), (out, "out")):
+        if t.dtype != torch.float32 or not t.is_cuda or t.stride(1) != 1:
+            raise KernelError(f"gemm_f32 {what}: needs a float32 CUDA matrix with unit inner stride")
+    _check(_fn("q25_gemm_f32", _UNTYPED["q25_gemm_f32"])(
+        a.data_ptr(), w.data_ptr(), _ptr(bias), out.data_ptr(), m, n, k, a.stride(0), w.stride(0), out.stride(0),
+        _stream()), "gemm_f32")
+
+
+def sample_rows(logits: torch.Tensor, temperature: Optional[torch.Tensor], seed: Optional[torch.Tensor],
+                token_index: Optional[torch.Tensor], out: torch.Tensor) -> None:
+    """out[r] = argmax(logits[r]) where temperature[r] <= 0 (or temperature is None), else a
+    draw from softmax(logits[r] / temperature[r]) keyed by (seed[r], token_index[r])."""
+    rows, vocab = logits.shape
+    _dev(out, torch.int32, "sample_rows out")
+    if logits.dtype != torch.float32 or logits.stride(1) != 1:
+        raise KernelError("sample_rows: logits must be float32 rows")
+    _check(_fn("q25_sample_rows", _UNTYPED["q25_sample_rows"])(
+        logits.data_ptr(), logits.stride(0), rows, vocab, _ptr(temperature), _ptr(seed), _ptr(token_index),
+        out.data_ptr(), _stream()), "sample_rows")
+
+
+def apply_penalties(logits: torch.Tensor, ids: torch.Tensor, counts: torch.Tensor, offsets: torch.Tensor,
+                    repetition: torch.Tensor, presence: torch.Tensor, frequency: torch.Tensor) -> None:
+    rows, vocab = logits.shape
+    _check(_fn("q25_apply_penalties", _UNTYPED["q25_apply_penalties"])(
+        logits.data_ptr(), logits.stride(0), rows, vocab, ids.data_ptr(), counts.data_ptr(), offsets.data_ptr(),
+        repetition.data_ptr(), presence.data_ptr(), frequency.data_ptr(), _stream()), "apply_penalties")

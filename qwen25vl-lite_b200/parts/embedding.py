@@ -1,0 +1,51 @@
+"""Token embedding and output head (reference src/qwen25vl_lite/text.py:213;
+src/qwen25vl_lite/model.py:84-86,200-202): a row gather without scaling, and
+``logits = h . W^T`` without bias, where W is the embedding table again when the head is
+tied and the checkpoint stores no head of its own (model.py:381-388,416-418)."""
+
+from __future__ import annotations
+
+import torch
+
+from ..ops import kernels
+from ..ops.linear import Linear
+from .base import Part, TensorSpec, register_embedding, register_head
+
+
+@register_embedding("token_embedding")
+class TokenEmbedding(Part):
+    def __init__(self, vocab_size: int, hidden_size: int):
+        self.vocab_size, self.hidden_size = int(vocab_size), int(hidden_size)
+        self.weight = None
+
+    def tensor_specs(self):
+        return (TensorSpec("weight", (self.vocab_size, self.hidden_size)),)
+
+    def load(self, tensors, device, dtype):
+        self.weight = tensors["weight"].to(device=device, dtype=dtype).contiguous()
+
+    def forward(self, ctx):
+        x = torch.empty((ctx.n_tokens, self.hidden_size), dtype=torch.float32, device=self.weight.device)
+        kernels.embed_gather(self.weight, ctx.token_ids, x)
+        return x
+
+
+@register_head("linear_head")
+class LinearHead(Part):
+    def __init__(self, vocab_size: int, hidden_size: int, tied: bool):
+        self.vocab_size, self.hidden_size, self.tied = int(vocab_size), int(hidden_size), bool(tied)
+        self.proj = None
+
+    def tensor_specs(self):
+        return (TensorSpec("weight", (self.vocab_size, self.hidden_size), optional=self.tied),)
+
+    def load(self, tensors, device, dtype, tied_weight=None):
+        if "weight" in tensors:      # an explicit head wins over the tie
+            self.proj = Linear(tensors["weight"].to(device=device, dtype=dtype).contiguous())
+        elif self.tied and tied_weight is not None:
+            self.proj = Linear(tied_weight)
+        else:
+            raise ValueError("output head has no weight and is not tied")
+
+    def forward(self, ctx, h):
+        return self.proj(h, out_dtype=torch.float32)
