@@ -13,7 +13,6 @@ are held in float32, which keeps a 32-bit tensor 32-bit and widens a bfloat16 on
 
 from __future__ import annotations
 
-import warnings
 from typing import Dict, List, Tuple
 
 import torch
@@ -86,9 +85,7 @@ def load_model(model_dir: str, dtype: str = "float32", device: str = "cuda:0"):
 
     def get_tensor(name: str) -> torch.Tensor:
         f, raw_name = where[name]
-        with warnings.catch_warnings():
-            warnings.simplefilter("ignore")      # the mapping is read-only; tensors are only copied from
-            return f.tensor(raw_name)
+        return f.tensor(raw_name)
 
     model.load(get_tensor, set(where), device, TORCH_DTYPES[dtype])
     return cfg, model

@@ -13,6 +13,7 @@ import json
 import mmap
 import os
 import struct
+import warnings
 from typing import Dict, Iterable, List, Tuple
 
 import torch
@@ -69,7 +70,9 @@ class SafetensorsFile:
             return torch.empty(tuple(meta["shape"]), dtype=dtype)
         if (hi - lo) != count * torch.empty((), dtype=dtype).element_size():
             raise ValueError(f"{self.path}: tensor {name!r} has {hi - lo} bytes for shape {meta['shape']}")
-        flat = torch.frombuffer(self._map, dtype=dtype, count=count, offset=self._base + lo)
+        with warnings.catch_warnings():
+            warnings.simplefilter("ignore")   # the mapping is read-only; the views are only read from
+            flat = torch.frombuffer(self._map, dtype=dtype, count=count, offset=self._base + lo)
         return flat.reshape(tuple(meta["shape"]))
 
 

@@ -1,0 +1,149 @@
+"""A toy mixer with state of its own, and a toy architecture around it, are registered from
+here, built, loaded and stepped without a change to the engine's files.  The toy model also
+runs one layer twice and lets one stop read another stop's cache."""
+
+import json
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from plain import decoder as plain
+from qwen25vl_lite.config import LayerSpec, ModelSpec, PartSpec, ScheduleEntry, register_architecture
+from qwen25vl_lite.engine.runner import ModelRunner, StepEntry
+from qwen25vl_lite.parts import MIXERS, Mixer, StateNeed, TensorSpec, register_mixer
+from qwen25vl_lite.weights import load_model, write_random_model
+
+pytestmark = pytest.mark.gpu
+
+HIDDEN, HEADS, KV, D, INTER, VOCAB, EPS, DECAY = 48, 3, 1, 16, 80, 97, 1e-5, 0.9
+
+
+if "toy_decaying_sum" not in MIXERS:
+    @register_mixer("toy_decaying_sum")
+    class DecayingSum(Mixer):
+        """s_t = decay * s_(t-1) + h_t;  out_t = W s_t.  The state s is the request's
+        fixed-size state; it is read at the start of a portion and written at its end."""
+
+        def __init__(self, hidden_size, decay, position=None):
+            self.hidden_size, self.decay = hidden_size, decay
+
+        def tensor_specs(self):
+            return (TensorSpec("mix.weight", (self.hidden_size, self.hidden_size)),)
+
+        def state_need(self):
+            return StateNeed((self.hidden_size,), "float32")
+
+        def load(self, tensors, device, dtype):
+            self.w = tensors["mix.weight"].to(device=device, dtype=torch.float32)
+
+        def forward(self, ctx, h, stop):
+            out = torch.empty_like(h)
+            at = 0
+            for n, slot in zip(ctx.host_q_lens, ctx.host_slots):
+                s = stop.state[slot]
+                for t in range(n):
+                    s = self.decay * s + h[at + t].float()
+                    out[at + t] = (self.w @ s).to(h.dtype)
+                stop.state[slot] = s
+                at += n
+            return out
+
+
+def toy_spec(cfg):
+    norms = lambda: (PartSpec("rmsnorm", dict(dim=HIDDEN, eps=EPS), "norm_a."), PartSpec("rmsnorm", dict(dim=HIDDEN, eps=EPS), "norm_b."))
+    ffn = PartSpec("swiglu", dict(hidden_size=HIDDEN, intermediate_size=INTER), "ffn.")
+    layers = (
+        LayerSpec("prenorm_residual", PartSpec("toy_decaying_sum", dict(hidden_size=HIDDEN, decay=DECAY), "toy."), ffn, norms(), "blocks.0."),
+        LayerSpec("prenorm_residual", PartSpec("gqa_attention", dict(hidden_size=HIDDEN, num_heads=HEADS, num_kv_heads=KV, head_dim=D), "attn."),
+                  ffn, norms(), "blocks.1."),
+    )
+    return ModelSpec(
+        embedding=PartSpec("token_embedding", dict(vocab_size=VOCAB, hidden_size=HIDDEN), "embed."),
+        layers=layers,
+        schedule=(ScheduleEntry(0), ScheduleEntry(1), ScheduleEntry(0), ScheduleEntry(1, cache_of=1)),
+        final_norm=PartSpec("rmsnorm", dict(dim=HIDDEN, eps=EPS), "final_norm."),
+        head=PartSpec("linear_head", dict(vocab_size=VOCAB, hidden_size=HIDDEN, tied=True), "head."),
+        position=PartSpec("mrope", dict(head_dim=D, theta=10000.0, sections=(2, 3, 3))),
+    )
+
+
+register_architecture("ToyRecurrentForTest", lambda raw: dict(raw), toy_spec, replace=True)
+
+
+def oracle(w, ids):
+    """The toy model from the plain parts, whole sequence, float64."""
+    n = len(ids)
+    cfg = {"num_attention_heads": HEADS, "num_key_value_heads": KV, "hidden_size": HEADS * D}
+    cos, sin = plain.mrope_cos_sin(plain.text_positions(n), D, 10000.0, (2, 3, 3), np.float64)
+    x = w["embed.weight"][np.asarray(ids)]
+
+    def ffn(x, p):
+        return plain.swiglu_mlp(plain.rms_norm(x, w[p + "norm_b.weight"], EPS), w, p + "ffn.")
+
+    def toy(x):
+        h = plain.rms_norm(x, w["blocks.0.norm_a.weight"], EPS)
+        s, out = np.zeros(HIDDEN), np.zeros_like(h)
+        for t in range(n):
+            s = DECAY * s + h[t]
+            out[t] = w["blocks.0.toy.mix.weight"] @ s
+        x = x + out
+        return x + ffn(x, "blocks.0.")
+
+    def qkv(h):
+        p = "blocks.1.attn."
+        q = (h @ w[p + "q_proj.weight"].T + w[p + "q_proj.bias"]).reshape(n, HEADS, D)
+        k = (h @ w[p + "k_proj.weight"].T + w[p + "k_proj.bias"]).reshape(n, KV, D)
+        v = (h @ w[p + "v_proj.weight"].T + w[p + "v_proj.bias"]).reshape(n, KV, D)
+        return plain.apply_mrope(q, cos, sin), plain.apply_mrope(k, cos, sin), v
+
+    def attn(x, kv=None):
+        q, k, v = qkv(plain.rms_norm(x, w["blocks.1.norm_a.weight"], EPS))
+        if kv is not None:
+            k, v = kv                                  # this stop reads the other stop's keys and values
+        x = x + plain.causal_attention(q, k, v).reshape(n, HEADS * D) @ w["blocks.1.attn.o_proj.weight"].T
+        return x + ffn(x, "blocks.1."), (k, v)
+
+    x = toy(x)
+    x, kv = attn(x)
+    x = toy(x)
+    x, _ = attn(x, kv)
+    return plain.rms_norm(x, w["final_norm.weight"], EPS) @ w["embed.weight"].T
+
+
+def test_toy_architecture_builds_loads_and_steps(tmp_path):
+    folder = write_random_model(str(tmp_path / "toy"), {"architectures": ["ToyRecurrentForTest"]}, seed=4, prefix="")
+    _, model = load_model(folder, "float32", "cuda:0")
+    needs = model.stop_needs()
+    assert [n.state is not None for n in needs] == [True, False, True, False]
+    assert needs[3].cache_of == 1 and needs[0].cache is None
+    runner = ModelRunner(model, 16, 8, 2)
+    assert len(runner.cache.groups) == 1 and runner.cache.groups[0].stops == [1]      # stop 3 keeps no pages
+    assert sorted(runner.cache.states) == [0, 2]                                     # one state per stop, not per layer
+    w = {k: v.astype(np.float64) for k, v in plain.read_safetensors(os.path.join(folder, "model.safetensors")).items()}
+    rng = np.random.default_rng(0)
+    ids_a, ids_b = rng.integers(0, VOCAB, size=29).tolist(), rng.integers(0, VOCAB, size=18).tolist()
+    want_a, want_b = oracle(w, ids_a), oracle(w, ids_b)
+
+    ra = runner.open_request("a")
+    whole = runner.step([StepEntry(ra, ids_a, list(range(29)))]).cpu().numpy()
+    assert np.abs(whole - want_a).max() < 1e-4
+    runner.close_request(ra)
+
+    # the same slots again, in portions, two requests side by side: the state was zeroed at
+    # admission, is carried across portions, and the cut does not change the result
+    ra, rb = runner.open_request("a2"), runner.open_request("b")
+    got_a, got_b = [], []
+    cuts_a, cuts_b = [0, 5, 7, 20, 29], [0, 9, 10, 18, 18]
+    for i in range(4):
+        entries, na, nb = [], cuts_a[i + 1] - cuts_a[i], cuts_b[i + 1] - cuts_b[i]
+        entries.append(StepEntry(ra, ids_a[cuts_a[i]:cuts_a[i + 1]], list(range(na))))
+        if nb:
+            entries.append(StepEntry(rb, ids_b[cuts_b[i]:cuts_b[i + 1]], list(range(nb))))
+        out = runner.step(entries).cpu().numpy()
+        got_a.append(out[:na])
+        got_b.append(out[na:])
+    assert np.abs(np.concatenate(got_a) - want_a).max() < 1e-4
+    assert np.abs(np.concatenate(got_b) - want_b).max() < 1e-4
+    assert np.abs(np.concatenate(got_a) - whole).max() < 1e-5

@@ -1,0 +1,262 @@
+"""Each CUDA kernel alone against a plain float64 computation of the same operation, at sizes
+other than the engine's (odd widths, head sizes in steps of 16, odd head counts)."""
+
+import numpy as np
+import pytest
+import torch
+
+from plain import decoder as plain
+
+pytestmark = pytest.mark.gpu
+
+DTYPES = [torch.float32, torch.bfloat16]
+
+
+def tol(dtype):
+    return 2e-5 if dtype == torch.float32 else 2e-2
+
+
+def dev(a, dtype=None):
+    t = torch.as_tensor(np.asarray(a)).cuda()
+    return t if dtype is None else t.to(dtype)
+
+
+def f64(t):
+    return t.detach().to("cpu", torch.float64).numpy()
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_embed_gather(dtype):
+    from qwen25vl_lite.ops import kernels
+    rng = np.random.default_rng(0)
+    table = dev(rng.standard_normal((1000, 72)), dtype)
+    ids = rng.integers(0, 1000, size=37)
+    out = torch.empty((37, 72), dtype=torch.float32, device="cuda")
+    kernels.embed_gather(table, dev(ids.astype(np.int32)), out)
+    assert np.array_equal(f64(out), f64(table)[ids])
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("hidden", [200, 2048 + 16])
+def test_add_rmsnorm(dtype, hidden):
+    from qwen25vl_lite.ops import kernels
+    rng = np.random.default_rng(1)
+    x0 = rng.standard_normal((9, hidden)) * 3
+    delta = dev(rng.standard_normal((9, hidden)), dtype)
+    w = dev(1 + 0.1 * rng.standard_normal(hidden), torch.float32)
+    x = dev(x0, torch.float32)
+    out = torch.empty((9, hidden), dtype=dtype, device="cuda")
+    kernels.add_rmsnorm(x, delta, w, 1e-5, out)
+    xs = f64(dev(x0, torch.float32)) + f64(delta)
+    assert np.abs(f64(x) - xs).max() < 1e-6                  # the residual stream took the update
+    ref = plain.rms_norm(xs, f64(w), 1e-5)
+    assert np.abs(f64(out) - ref).max() < tol(dtype) * 4
+    # rows: only some rows, x untouched, update still applied to the normalised value
+    rows = np.asarray([7, 0, 3], dtype=np.int32)
+    x2 = dev(x0, torch.float32)
+    out2 = torch.empty((3, hidden), dtype=dtype, device="cuda")
+    kernels.add_rmsnorm(x2, delta, w, 1e-5, out2, dev(rows))
+    assert np.array_equal(f64(x2), f64(dev(x0, torch.float32)))
+    assert np.abs(f64(out2) - ref[rows]).max() < tol(dtype) * 4
+    # no update
+    out3 = torch.empty((9, hidden), dtype=dtype, device="cuda")
+    kernels.add_rmsnorm(x2, None, w, 1e-5, out3)
+    assert np.abs(f64(out3) - plain.rms_norm(f64(x2), f64(w), 1e-5)).max() < tol(dtype) * 4
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_silu_mul(dtype):
+    from qwen25vl_lite.ops import kernels
+    gu = dev(np.random.default_rng(2).standard_normal((13, 2 * 136)) * 2, dtype)
+    out = torch.empty((13, 136), dtype=dtype, device="cuda")
+    kernels.silu_mul(gu, out)
+    g, u = f64(gu)[:, :136], f64(gu)[:, 136:]
+    assert np.abs(f64(out) - plain.silu(g) * u).max() < tol(dtype) * 4
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("nq,nkv,d,section", [(5, 5, 48, (8, 8, 8)), (16, 2, 128, (16, 24, 24)), (3, 1, 16, (2, 3, 3))])
+def test_rope_store(dtype, nq, nkv, d, section):
+    from qwen25vl_lite.ops import kernels
+    from qwen25vl_lite.parts.position import MRope
+    rng = np.random.default_rng(3)
+    n, page_size, pages = 21, 8, 7
+    qkv0 = dev(rng.standard_normal((n, (nq + 2 * nkv) * d)), dtype)
+    pos = rng.integers(0, 3000, size=(3, n))
+    rope = MRope(d, 50000.0, section)
+    rope.load({}, "cuda", dtype)
+    slots = rng.permutation(pages * page_size)[:n].astype(np.int32)
+    k_pages = torch.zeros((pages, nkv, page_size, d), dtype=dtype, device="cuda")
+    v_pages = torch.zeros_like(k_pages)
+    qkv = qkv0.clone()
+    kernels.rope_store(qkv, dev(pos.astype(np.int32)), rope.inv_freq, rope.axis, k_pages, v_pages, dev(slots),
+                       nq, nkv, d, page_size)
+    cos, sin = plain.mrope_cos_sin(pos, d, 50000.0, section, np.float64)
+    x = f64(qkv0).reshape(n, nq + 2 * nkv, d)
+    q_ref = plain.apply_mrope(x[:, :nq], cos, sin)
+    k_ref = plain.apply_mrope(x[:, nq:nq + nkv], cos, sin)
+    # float32 angles at positions up to 3000 carry up to ~2e-4 rad of rounding
+    t = 2e-3 if dtype == torch.float32 else 4e-2
+    assert np.abs(f64(qkv).reshape(n, -1, d)[:, :nq] - q_ref).max() < t
+    kp, vp = f64(k_pages), f64(v_pages)
+    for i, s in enumerate(slots):
+        assert np.abs(kp[s // page_size, :, s % page_size] - k_ref[i]).max() < t
+        assert np.array_equal(vp[s // page_size, :, s % page_size], x[i, nq + nkv:])
+    # slot -1 stores nothing; no positions = no rotation
+    k2 = torch.zeros_like(k_pages)
+    qkv = qkv0.clone()
+    kernels.rope_store(qkv, None, None, None, k2, torch.zeros_like(k2), dev(np.full(n, -1, np.int32)), nq, nkv, d, page_size)
+    assert float(k2.abs().max()) == 0 and torch.equal(qkv, qkv0)
+
+
+def paged_case(rng, lens, q_lens, nq, nkv, d, page_size, dtype, n_pages=None):
+    """Random requests laid out in shuffled pages.  Returns tensors for the kernel and the
+    dense per-request q, k, v for the oracle."""
+    total_pages = sum(-(-L // page_size) for L in lens)
+    n_pages = n_pages or total_pages + 3
+    order = rng.permutation(n_pages)
+    k_pages = torch.zeros((n_pages, nkv, page_size, d), dtype=dtype, device="cuda")
+    v_pages = torch.zeros_like(k_pages)
+    width = max(-(-L // page_size) for L in lens)
+    table = np.zeros((len(lens), width), dtype=np.int32)
+    dense, qs, token_seq, cu, start = [], [], [], [0], []
+    at = 0
+    for s, (L, ql) in enumerate(zip(lens, q_lens)):
+        k = torch.as_tensor(rng.standard_normal((L, nkv, d))).to(dtype)
+        v = torch.as_tensor(rng.standard_normal((L, nkv, d))).to(dtype)
+        q = torch.as_tensor(rng.standard_normal((ql, nq, d))).to(dtype)
+        npg = -(-L // page_size)
+        table[s, :npg] = order[at:at + npg]
+        at += npg
+        for j in range(L):
+            pg = table[s, j // page_size]
+            k_pages[pg, :, j % page_size] = k[j].cuda()
+            v_pages[pg, :, j % page_size] = v[j].cuda()
+        dense.append((q, k, v))
+        qs.append(q)
+        token_seq += [s] * ql
+        cu.append(cu[-1] + ql)
+        start.append(L - ql)
+    n = cu[-1]
+    qkv = torch.zeros((n, (nq + 2 * nkv) * d), dtype=dtype, device="cuda")
+    qkv[:, :nq * d] = torch.cat(qs).reshape(n, nq * d).cuda()
+    return dict(qkv=qkv, k_pages=k_pages, v_pages=v_pages, table=dev(table), token_seq=dev(np.asarray(token_seq, np.int32)),
+                cu=dev(np.asarray(cu, np.int32)), start=dev(np.asarray(start, np.int32)), dense=dense)
+
+
+def attention_oracle(dense, window):
+    outs = []
+    for q, k, v in dense:
+        L, ql = k.shape[0], q.shape[0]
+        qf = np.zeros((L, q.shape[1], q.shape[2]))
+        qf[L - ql:] = f64(q)
+        outs.append(plain.causal_attention(qf, f64(k), f64(v), window)[L - ql:])
+    return np.concatenate(outs).reshape(sum(o.shape[0] for o in outs), -1)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("nq,nkv,d,page_size,window", [
+    (4, 2, 16, 4, None), (6, 1, 32, 8, None), (5, 5, 48, 16, 24), (16, 2, 128, 16, None), (3, 3, 256, 16, 40),
+    (8, 2, 64, 16, 33), (7, 7, 80, 32, None)])
+def test_paged_attention_generic(dtype, nq, nkv, d, page_size, window):
+    from qwen25vl_lite.ops import kernels
+    rng = np.random.default_rng(5)
+    lens, q_lens = [1, 37, 130, 64, 200], [1, 37, 2, 1, 45]     # a first token, a whole prompt, portions, a decode
+    c = paged_case(rng, lens, q_lens, nq, nkv, d, page_size, dtype)
+    out = torch.empty((c["qkv"].shape[0], nq * d), dtype=dtype, device="cuda")
+    kernels.paged_attention_generic(c["qkv"], out, c["k_pages"], c["v_pages"], c["table"], c["token_seq"], c["cu"],
+                                    c["start"], nq, nkv, d, page_size, window or 0, d ** -0.5)
+    ref = attention_oracle(c["dense"], window)
+    assert np.abs(f64(out) - ref).max() < tol(dtype) * 2
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_attention_finds_a_far_key_and_the_window_edge(dtype):
+    """One key among hundreds gets a score that dominates the softmax: the output must be
+    that key's value.  The key sits on the first slot of a page, on the last one, and just
+    inside / just outside the window."""
+    from qwen25vl_lite.ops import kernels
+    nq, nkv, d, ps, L = 2, 1, 32, 16, 300
+    for key, window, visible in [(0, None, True), (143, None, True), (144, None, True), (299, None, True),
+                                 (300 - 50, 50, True), (300 - 51, 50, False)]:
+        rng = np.random.default_rng(key)
+        c = paged_case(rng, [L], [1], nq, nkv, d, ps, dtype)
+        q, k, v = c["dense"][0]
+        k = k.clone()
+        k[key] = (q[0, 0] * 6).to(dtype)            # q . k ~ 6 |q|^2: e^(6*32/sqrt(32)) beats 299 others
+        pg = int(c["table"][0, key // ps])
+        c["k_pages"][pg, :, key % ps] = k[key].cuda()
+        out = torch.empty((1, nq * d), dtype=dtype, device="cuda")
+        kernels.paged_attention_generic(c["qkv"], out, c["k_pages"], c["v_pages"], c["table"], c["token_seq"], c["cu"],
+                                        c["start"], nq, nkv, d, ps, window or 0, d ** -0.5)
+        hit = np.abs(f64(out)[0, :d] - f64(v)[key, 0]).max() < 5e-2
+        assert hit == visible, f"key {key} window {window}: found={hit}"
+        ref = attention_oracle([(q, k, v)], window)
+        assert np.abs(f64(out) - ref).max() < tol(dtype) * 2
+
+
+@pytest.mark.parametrize("m,n,k", [(1, 100, 70), (37, 130, 257), (200, 64, 16), (16, 300, 2048)])
+def test_gemm_f32(m, n, k):
+    from qwen25vl_lite.ops import kernels
+    rng = np.random.default_rng(6)
+    a, w, b = dev(rng.standard_normal((m, k)), torch.float32), dev(rng.standard_normal((n, k)), torch.float32), \
+        dev(rng.standard_normal(n), torch.float32)
+    out = torch.empty((m, n), dtype=torch.float32, device="cuda")
+    kernels.gemm_f32(a, w, b, out)
+    ref = f64(a) @ f64(w).T + f64(b)
+    assert np.abs(f64(out) - ref).max() < 1e-5 * np.sqrt(k) * 4
+    # a row's result does not depend on the batch it is in: bit for bit
+    out1 = torch.empty((1, n), dtype=torch.float32, device="cuda")
+    kernels.gemm_f32(a[m // 2:m // 2 + 1].contiguous(), w, b, out1)
+    assert torch.equal(out1[0], out[m // 2])
+    out_nb = torch.empty((m, n), dtype=torch.float32, device="cuda")
+    kernels.gemm_f32(a, w, None, out_nb)
+    assert np.abs(f64(out_nb) - f64(a) @ f64(w).T).max() < 1e-5 * np.sqrt(k) * 4
+
+
+def test_sample_rows_greedy_and_temperature():
+    from qwen25vl_lite.ops import kernels
+    rng = np.random.default_rng(7)
+    logits = rng.standard_normal((6, 1031)).astype(np.float32)
+    logits[1, 500] = logits[1, 77] = 9.0                     # a tie: the lower index wins
+    lg = dev(logits)
+    out = torch.empty(6, dtype=torch.int32, device="cuda")
+    kernels.sample_rows(lg, None, None, None, out)
+    assert out.tolist() == [int(np.argmax(r)) for r in logits] and out[1].item() == 77
+    temps = np.asarray([0.0, 0.8, 1.3, 0.0, 0.05, 2.0], dtype=np.float32)
+    seeds = np.asarray([1, 2, 2**63 + 5, 4, 5, 6], dtype=np.uint64)
+    index = np.asarray([0, 3, 1, 2, 9, 100], dtype=np.int32)
+    kernels.sample_rows(lg, dev(temps), dev(seeds.view(np.int64)), dev(index), out)
+    want = [plain.sample(logits[r], float(temps[r]), int(seeds[r]), int(index[r])) for r in range(6)]
+    assert out.tolist() == want
+    # the draws follow softmax(logits / T)
+    small = np.tile(np.asarray([[2.0, 1.0, 0.0, -1.0]], dtype=np.float32), (4000, 1))
+    o = torch.empty(4000, dtype=torch.int32, device="cuda")
+    kernels.sample_rows(dev(small), dev(np.full(4000, 1.0, np.float32)), dev(np.full(4000, 7, np.int64)),
+                        dev(np.arange(4000, dtype=np.int32)), o)
+    freq = np.bincount(o.cpu().numpy(), minlength=4) / 4000
+    p = np.exp(small[0]) / np.exp(small[0]).sum()
+    assert np.abs(freq - p).max() < 0.03
+
+
+def test_penalties_and_filters():
+    from qwen25vl_lite.sampling import Sampler, SamplingParams, filter_scores
+    rng = np.random.default_rng(8)
+    logits = rng.standard_normal((3, 300)).astype(np.float32)
+    prev = [[5, 5, 9], [], [1, 2, 3, 3, 3]]
+    params = [SamplingParams(repetition_penalty=1.5, presence_penalty=0.2, frequency_penalty=0.1),
+              SamplingParams(), SamplingParams(temperature=0.7, seed=3, frequency_penalty=0.5)]
+    got = Sampler("cuda").sample(dev(logits), params, [0, 0, 3], [3, 0, 5], prev)
+    want = []
+    for r, p in enumerate(params):
+        lg = plain.apply_penalties(logits[r], prev[r], p.repetition_penalty, p.presence_penalty, p.frequency_penalty)
+        want.append(plain.sample(lg, p.temperature, 3, [3, 0, 5][r]))
+    assert got == want
+    for kw in (dict(top_k=5), dict(top_p=0.6), dict(min_p=0.1), dict(top_k=20, min_p=0.05, top_p=0.8)):
+        full = {**dict(top_k=-1, min_p=0.0, top_p=1.0), **kw}
+        s = filter_scores(dev(logits[0] / 0.7), full["top_k"], full["min_p"], full["top_p"]).cpu().numpy()
+        ref = plain.filter_scores(logits[0] / np.float32(0.7), **full)
+        assert np.array_equal(np.isinf(s), np.isinf(ref)), kw
+        p = SamplingParams(temperature=0.7, seed=11, **kw)
+        tok = Sampler("cuda").sample(dev(logits[:1]), [p], [11], [2], [[]])[0]
+        assert tok == plain.sample(logits[0], 0.7, 11, 2, full["top_k"], full["min_p"], full["top_p"])

@@ -1,0 +1,149 @@
+"""Replay on the GPU against the plain implementation: every way of cutting and batching,
+in 32-bit and in bfloat16, on the tiny configurations."""
+
+import numpy as np
+import pytest
+
+import replay_util as ru
+from tiny_models import TINY
+
+pytestmark = pytest.mark.gpu
+
+# float32: the logits of the tiny models are O(0.1-1); the engine's float32 path agrees with the
+# float64 oracle to a few 1e-6.  bfloat16: weights, activations and the cache are rounded to 8
+# bits of mantissa, errors of a few 1e-2 on logits of that size are rounding, not faults.
+TOL = {"float32": 1e-4, "bfloat16": 6e-2}
+LENGTHS = {"A": (5, 11, 17, 70), "B": (1, 9, 23, 40, 97), "C": (3, 31, 64, 130)}
+
+
+def _requests(name, seed=0):
+    vocab = TINY[name][0]["text_config"]["vocab_size"]
+    rng = np.random.default_rng(seed)
+    return {f"r{i}": rng.integers(0, vocab, size=n).tolist() for i, n in enumerate(LENGTHS[name])}
+
+
+def _bf16_dir(tmp_path_factory, name):
+    from tiny_models import make_model_dir
+
+    return make_model_dir(tmp_path_factory.mktemp("bf16"), name, "bfloat16")
+
+
+def _check(got, want, tol, what):
+    for rid, ref in want.items():
+        err = np.abs(got[rid] - ref).max()
+        assert err < tol, f"{what}: request {rid} differs from the plain decoder by {err:.3e}"
+
+
+@pytest.fixture(scope="module")
+def cases(model_dirs, tmp_path_factory):
+    """(name, dtype) -> (model folder, requests, oracle).  The bfloat16 oracle reads the
+    bfloat16-rounded weights, so only the engine's own rounding is measured."""
+    out = {}
+    for name in TINY:
+        reqs = _requests(name)
+        out[name, "float32"] = (model_dirs[name], reqs, ru.oracle(model_dirs[name], reqs))
+        d = _bf16_dir(tmp_path_factory, name)
+        out[name, "bfloat16"] = (d, reqs, ru.oracle(d, reqs))
+    return out
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", list(TINY))
+def test_whole(cases, name, dtype):
+    folder, reqs, want = cases[name, dtype]
+    steps = ru.whole(reqs)
+    got, runner = ru.run_in_process(folder, dtype, steps, ru.max_live_tokens(steps), TINY[name][2])
+    _check(got, want, TOL[dtype], "whole")
+    runner.cache.check([])
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", list(TINY))
+def test_last_32_one_by_one(cases, name, dtype):
+    folder, reqs, want = cases[name, dtype]
+    steps = ru.prefill_then_decode(reqs, 32)
+    got, runner = ru.run_in_process(folder, dtype, steps, ru.max_live_tokens(steps), TINY[name][2])
+    _check(got, want, TOL[dtype], "decode")
+    runner.cache.check([])
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", list(TINY))
+def test_portions_of_changing_size(cases, name, dtype):
+    folder, reqs, want = cases[name, dtype]
+    steps = ru.portions(reqs, (7, 2, 13, 3, 2, 21, 5))
+    got, runner = ru.run_in_process(folder, dtype, steps, ru.max_live_tokens(steps), TINY[name][2])
+    _check(got, want, TOL[dtype], "portions")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", list(TINY))
+def test_mixed_with_page_reuse(cases, name, dtype):
+    folder, _, _ = cases[name, dtype]
+    vocab = TINY[name][0]["text_config"]["vocab_size"]
+    rng = np.random.default_rng(11)
+    reqs = {f"m{i}": rng.integers(0, vocab, size=int(n)).tolist() for i, n in enumerate(rng.integers(20, 120, size=9))}
+    want = ru.oracle(folder, reqs)
+    steps = ru.mixed(reqs, seed=3)
+    assert max(len(s["entries"]) for s in steps) >= 3
+    budget = ru.max_live_tokens(steps)
+    got, runner = ru.run_in_process(folder, dtype, steps, budget, TINY[name][2])
+    _check(got, want, TOL[dtype], "mixed")
+    # so few pages that they were used again: more pages were handed out than the pool has
+    assert sum(-(-len(v) // 64) * 64 for v in reqs.values()) > budget
+    runner.cache.check([])
+
+
+def test_float32_cut_independence(cases):
+    """The 32-bit path sums in an order that depends only on a token's own position, so
+    whole and cut replays agree far below the tolerance (bit for bit in the matrix
+    products; attention and norms within a few ulp)."""
+    folder, reqs, _ = cases["B", "float32"]
+    a, _ = ru.run_in_process(folder, "float32", ru.whole(reqs), 512, 8)
+    b, _ = ru.run_in_process(folder, "float32", ru.portions(reqs, (3, 2, 9)), 512, 8)
+    for rid in reqs:
+        assert np.abs(a[rid] - b[rid]).max() < 2e-6
+
+
+def test_image_positions_through_replay(cases):
+    """tiny-B's prompt with a 12-token image run (t1 x h3 x w4): explicit positions in the
+    prompt portions, then plain tokens that resume at max + 1 through the stored offset."""
+    from plain import decoder as plain
+
+    folder, _, _ = cases["B", "float32"]
+    rng = np.random.default_rng(4)
+    ids = rng.integers(0, 512, size=46).tolist()
+    pos40, delta = plain.prompt_positions(40, [(9, 1, 3, 4)])
+    pos = np.concatenate([pos40] + [plain.decode_positions(n, delta) for n in range(40, 46)], axis=1)
+    want = ru.oracle(folder, {"img": ids}, {"img": pos})
+    steps, at = [], 0
+    for n in (7, 7, 7, 7, 7, 5):                       # the prompt in portions of 7, positions given
+        steps.append({"step": len(steps), "end": [], "entries": [
+            {"id": "img", "tokens": ids[at:at + n], "want": list(range(n)), "positions": pos40[:, at:at + n].tolist()}]})
+        at += n
+    for i in range(40, 46):                            # then decoded tokens without positions
+        steps.append({"step": len(steps), "end": [], "entries": [{"id": "img", "tokens": [ids[i]], "want": [0]}]})
+    got, _ = ru.run_in_process(folder, "float32", steps, 64, 8)
+    _check(got, want, 1e-4, "image positions")
+
+
+def test_trace_run_program(cases, tmp_path):
+    """The program itself: protocol lines, files, exit code."""
+    folder, reqs, want = cases["A", "float32"]
+    steps = ru.mixed(reqs, seed=5, max_live=3)
+    got = ru.run_program(folder, "float32", steps, ru.max_live_tokens(steps), str(tmp_path / "out"))
+    _check(got, want, 1e-4, "program")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_long_decoding_and_first_tokens(cases, dtype):
+    """Two tokens in one step, then 254 tokens one by one; the logits of the first
+    positions (sequences of length 1, 2, 3) are checked like all others."""
+    folder, _, _ = cases["B", dtype]
+    ids = np.random.default_rng(8).integers(0, 512, size=256).tolist()
+    want = ru.oracle(folder, {"long": ids})
+    steps = ru.prefill_then_decode({"long": ids}, tail=254)
+    assert len(steps) == 255 and len(steps[0]["entries"][0]["tokens"]) == 2
+    got, _ = ru.run_in_process(folder, dtype, steps, 256, 8)
+    _check(got, want, TOL[dtype], "long decoding")
+    assert np.abs(got["long"][:3] - want["long"][:3]).max() < TOL[dtype]

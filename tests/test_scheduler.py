@@ -1,0 +1,231 @@
+"""The scheduler's decisions, on the host: a fake step function records what it is fed and
+"generates" a token that depends on every token it has seen, so a lost or repeated token
+changes the output."""
+
+from typing import List
+
+import pytest
+
+from qwen25vl_lite.cache import CacheManager, StopNeeds
+from qwen25vl_lite.config import EngineConfig
+from qwen25vl_lite.engine.runner import Request
+from qwen25vl_lite.engine.scheduler import LLMEngine
+from qwen25vl_lite.parts import KVCacheNeed
+from qwen25vl_lite.sampling import SamplingParams
+
+VOCAB = 1000
+
+
+def next_token(history: List[int]) -> int:
+    return (sum((i + 1) * t for i, t in enumerate(history)) * 31 + len(history)) % VOCAB
+
+
+class FakeRunner:
+    """The step function's face without a model: checks that every request's tokens arrive
+    in order, each exactly once, with the pages they need already held."""
+
+    def __init__(self, num_pages, page_size, max_requests, window=None):
+        self.cache = CacheManager([StopNeeds(KVCacheNeed(1, 16, window))], num_pages, page_size, max_requests)
+        self.history = {}
+        self.batches = []
+
+    def open_request(self, rid):
+        self.history[rid] = []
+        return Request(rid, self.cache.open())
+
+    def close_request(self, req):
+        self.cache.close(req.cache)
+        del self.history[req.request_id]
+
+    def step(self, entries):
+        self.batches.append([(e.request.request_id, len(e.tokens), len(e.want)) for e in entries])
+        rows = []
+        for e in entries:
+            h = self.history[e.request.request_id]
+            assert len(h) == e.request.cache.num_tokens
+            assert self.cache.pages_missing(e.request.cache, len(h) + len(e.tokens)) == [0]
+            for i, t in enumerate(e.tokens):
+                h.append(int(t))
+                if i in e.want:
+                    rows.append(list(h))
+            self.cache.advance(e.request.cache, len(e.tokens))
+        self.cache.check([r for r in self._live()])
+        return rows
+
+    def _live(self):
+        return [r for r in self._requests]
+
+    _requests: list = []
+
+
+class FakeSampler:
+    def sample(self, rows, params, seeds, token_indices, previous):
+        return [next_token(h) for h in rows]
+
+
+def make_engine(num_pages=64, page_size=4, window=None, eos=None, **cfg):
+    ecfg = EngineConfig(num_blocks=num_pages, block_size=page_size, **cfg)
+    runner = FakeRunner(num_pages, page_size, ecfg.max_num_seqs, window)
+    engine = LLMEngine(runner, FakeSampler(), ecfg, eos_token_id=eos)
+    runner._requests = _LiveView(engine)
+    return engine, runner
+
+
+class _LiveView:
+    def __init__(self, engine):
+        self.engine = engine
+
+    def __iter__(self):
+        return iter(s.request.cache for s in self.engine.running if s.request is not None)
+
+
+def expected(prompt, n):
+    h = list(prompt)
+    out = []
+    for _ in range(n):
+        out.append(next_token(h))
+        h.append(out[-1])
+    return out
+
+
+def test_one_request_generates_the_chain():
+    engine, runner = make_engine()
+    prompt = [5, 9, 2, 7, 7, 1]
+    engine.add_request(prompt, SamplingParams(max_tokens=8))
+    outs = engine.run_until_complete()
+    assert outs[0].output_token_ids == expected(prompt, 8) and outs[0].finish_reason == "length"
+    assert runner.batches[0] == [(0, 6, 1)] and all(b == [(0, 1, 1)] for b in runner.batches[1:])
+    assert len(runner.batches) == 8                       # first token from the prompt step, then 7 decodes
+    assert runner.cache.pages_in_use() == [0] and runner.cache.free_slots == 8
+    assert outs[0].metrics["prompt_tokens"] == 6 and outs[0].metrics["completion_tokens"] == 8
+
+
+def test_prompts_are_cut_under_the_token_budget_and_decodes_go_first():
+    engine, runner = make_engine(max_num_batched_tokens=16)
+    a = engine.add_request(list(range(1, 11)), SamplingParams(max_tokens=30))
+    engine.step()                                          # a's prompt (10 tokens)
+    b = engine.add_request(list(range(100, 164)), SamplingParams(max_tokens=4))
+    engine.step()
+    assert runner.batches[-1] == [(a, 1, 1), (b, 15, 0)]   # one decoded token, the rest of the budget to b's prompt
+    engine.step(); engine.step(); engine.step()
+    assert [x for batch in runner.batches[2:5] for x in batch if x[0] == b] == [(b, 15, 0), (b, 15, 0), (b, 15, 0)]
+    engine.step()
+    assert runner.batches[-1] == [(a, 1, 1), (b, 4, 1)]    # the portion that reaches the end samples
+    outs = {o.seq_id: o for o in engine.run_until_complete()}
+    assert outs[a].output_token_ids == expected(range(1, 11), 30)
+    assert outs[b].output_token_ids == expected(range(100, 164), 4)
+    assert max(sum(n for _, n, _ in batch) for batch in runner.batches) <= 16
+
+
+def test_without_chunked_prefill_a_prompt_runs_whole_or_not_at_all():
+    engine, runner = make_engine(max_num_batched_tokens=32, enable_chunked_prefill=False)
+    engine.add_request(list(range(20)), SamplingParams(max_tokens=2))
+    engine.add_request(list(range(20)), SamplingParams(max_tokens=2))
+    engine.step()
+    assert runner.batches[0] == [(0, 20, 1)]               # the second prompt does not fit beside the first
+    engine.run_until_complete()
+    engine.add_request(list(range(40)), SamplingParams(max_tokens=2))
+    with pytest.raises(RuntimeError, match="no progress"):
+        engine.run_until_complete(max_stall=8)
+
+
+def test_admission_is_limited_by_slots_and_first_come_first_served():
+    engine, runner = make_engine(max_num_seqs=2)
+    ids = [engine.add_request([i + 1] * 5, SamplingParams(max_tokens=3)) for i in range(5)]
+    engine.step()
+    assert [x[0] for x in runner.batches[0]] == ids[:2] and len(engine.waiting) == 3
+    outs = engine.run_until_complete()
+    assert sorted(o.seq_id for o in outs) == ids
+    assert [o.seq_id for o in outs] == ids                  # same lengths: they finish in arrival order
+    for o in outs:
+        assert o.output_token_ids == expected(o.prompt_token_ids, 3)
+
+
+def test_finish_reasons():
+    prompt = [3, 1, 4, 1, 5]
+    chain = expected(prompt, 10)
+    engine, _ = make_engine(eos=chain[2])
+    engine.add_request(prompt, SamplingParams(max_tokens=10))
+    engine.add_request(prompt, SamplingParams(max_tokens=10, ignore_eos=True))
+    engine.add_request(prompt, SamplingParams(max_tokens=10, ignore_eos=True, stop_token_ids=[chain[4]]))
+    outs = {o.seq_id: o for o in engine.run_until_complete()}
+    assert outs[0].output_token_ids == chain[:3] and outs[0].finish_reason == "stop"
+    assert outs[1].output_token_ids == chain and outs[1].finish_reason == "length"
+    assert outs[2].output_token_ids == chain[:5] and outs[2].finish_reason == "stop"
+    engine, _ = make_engine(max_model_len=8)
+    engine.add_request(prompt, SamplingParams(max_tokens=10))
+    out = engine.run_until_complete()[0]
+    assert len(out.output_token_ids) == 3 and out.finish_reason == "length"     # 5 + 3 = max_model_len
+
+
+def test_bad_requests_are_refused():
+    engine, _ = make_engine(max_model_len=16, num_pages=3)
+    with pytest.raises(ValueError, match="empty"):
+        engine.add_request([], SamplingParams())
+    with pytest.raises(ValueError, match="max_model_len"):
+        engine.add_request([1] * 17, SamplingParams())
+    with pytest.raises(ValueError, match="stop"):
+        engine.add_request([1], SamplingParams(stop=["x"]))
+    with pytest.raises(ValueError, match="temperature"):
+        engine.add_request([1], SamplingParams(temperature=-1))
+    with pytest.raises(ValueError, match="pages"):
+        engine.add_request([1] * 13, SamplingParams())      # 4 pages of 4, the pool has 3
+
+
+def test_pages_run_out_newest_is_preempted_and_continues_exactly():
+    prompts = [[i + 1, i + 2, i + 3] * 4 for i in range(4)]           # 12 tokens each
+    reference, _ = make_engine(num_pages=256)
+    for p in prompts:
+        reference.add_request(p, SamplingParams(max_tokens=12))
+    want = {o.seq_id: o.output_token_ids for o in reference.run_until_complete()}
+    assert reference.stats()["preemptions"] == 0
+
+    engine, runner = make_engine(num_pages=14)                        # 4 x 12 tokens fit (12 pages), growth does not
+    for p in prompts:
+        engine.add_request(p, SamplingParams(max_tokens=12))
+    outs = engine.run_until_complete()
+    assert {o.seq_id: o.output_token_ids for o in outs} == want       # nothing lost, nothing repeated
+    assert engine.stats()["preemptions"] > 0
+    assert max(o.metrics["preemptions"] for o in outs if o.seq_id == 0) == 0     # the oldest is never the victim
+    assert runner.cache.pages_in_use() == [0] and runner.cache.free_slots == 8
+    recomputed = [b for b in runner.batches for (rid, n, w) in b if n > 12]
+    assert recomputed                                                 # prompt + generated came back as one portion
+
+
+def test_a_waiting_request_never_evicts_a_running_one():
+    engine, runner = make_engine(num_pages=8)
+    engine.add_request([1] * 20, SamplingParams(max_tokens=4))        # 5 pages, then 6
+    engine.step()
+    engine.add_request([2] * 20, SamplingParams(max_tokens=4))        # does not fit beside it
+    engine.step()
+    assert len(engine.running) == 1 and len(engine.waiting) == 1 and engine.stats()["preemptions"] == 0
+    outs = engine.run_until_complete()
+    assert len(outs) == 2 and engine.stats()["preemptions"] == 0
+
+
+def test_pool_too_small_for_the_only_running_request():
+    engine, _ = make_engine(num_pages=4)
+    engine.add_request([1] * 15, SamplingParams(max_tokens=8))        # 15 tokens fit 4 pages, the 17th does not
+    with pytest.raises(RuntimeError, match="pool too small"):
+        engine.run_until_complete()
+
+
+def test_window_group_lets_a_long_request_run_in_few_pages():
+    engine, runner = make_engine(num_pages=6, window=8, max_num_batched_tokens=8)
+    prompt = list(range(1, 41))
+    engine.add_request(prompt, SamplingParams(max_tokens=20))         # 60 tokens = 15 pages without a window
+    out = engine.run_until_complete()[0]
+    assert out.output_token_ids == expected(prompt, 20)
+    assert engine.stats()["preemptions"] == 0 and runner.cache.pages_in_use() == [0]
+
+
+def test_abort_and_stats():
+    engine, runner = make_engine()
+    a = engine.add_request([1, 2, 3], SamplingParams(max_tokens=50))
+    b = engine.add_request([4, 5, 6], SamplingParams(max_tokens=3))
+    engine.step()
+    assert engine.abort(a) and not engine.abort(99)
+    outs = engine.run_until_complete()
+    assert [o.seq_id for o in outs] == [b]
+    st = engine.stats()
+    assert st["finished"] == 1 and st["running"] == 0 and st["kv_blocks_used"] == 0 and st["generated_tokens"] == 4
