@@ -76,7 +76,17 @@ def _typed(base: str, dtype: torch.dtype):
         raise KernelError(f"{base}: unsupported dtype {dtype}") from None
 
 
+_launches = 0
+
+
+def launch_count() -> int:
+    """How many kernels of this engine have been launched by this process."""
+    return _launches
+
+
 def _check(code: int, what: str) -> None:
+    global _launches
+    _launches += 1
     if code != 0:
         raise KernelError(f"CUDA kernel {what} could not be launched: cudaError {code} "
                           f"({torch.cuda.get_device_name() if torch.cuda.is_available() else 'no device'})")
