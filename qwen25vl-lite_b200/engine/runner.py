@@ -79,6 +79,10 @@ class StepContext:
     group_kv_slot: List[torch.Tensor]
     group_block_table: List[torch.Tensor]
     cache: CacheManager
+    # work lists of the tensor-core attention kernels: entries that bring one token, and per
+    # query-group size G the (entry, 64-row tile) pairs of the other entries
+    decode_items: Optional[torch.Tensor] = None
+    prefill_tiles: Dict[int, Optional[torch.Tensor]] = field(default_factory=dict)
     # host copies, for parts written with torch operators (toy parts in tests)
     host_q_lens: List[int] = field(default_factory=list)
     host_q_start: List[int] = field(default_factory=list)
@@ -105,6 +109,9 @@ class ModelRunner:
         for stop in model.stops:
             stop.state = self.cache.states.get(stop.index)
         self.axes = model.position.axes
+        # query heads per kv head of every attention mixer, for the attention work lists
+        blocks = getattr(model, "blocks", [])
+        self.group_sizes = sorted({int(b.mixer.rows_per_token) for b in blocks if hasattr(b.mixer, "rows_per_token")})
         self.vocab_size = model.head.vocab_size
         self._staging: Optional[torch.Tensor] = None
         self._staging_free = torch.cuda.Event() if self.device.type == "cuda" else None
@@ -156,7 +163,17 @@ class ModelRunner:
         M = sum(len(e.want) for e in entries)
 
         # ---- pack ----
-        total = N * (2 + self.axes + len(groups)) + (S + 1) + 2 * S + M + S * sum(widths) + 4 * (7 + 2 * len(groups))
+        decode_list = [i for i, n in enumerate(q_lens) if n == 1]
+        tile_lists = {}
+        for G in self.group_sizes:
+            pairs = []
+            for i, n in enumerate(q_lens):
+                if n > 1 or G > 16:
+                    pairs += [(i, t) for t in range(-(-n * G // 64))]
+            tile_lists[G] = pairs
+        n_work = len(decode_list) + sum(2 * len(v) + 4 for v in tile_lists.values())
+        total = (N * (2 + self.axes + len(groups)) + (S + 1) + 2 * S + M + S * sum(widths) + n_work
+                 + 4 * (8 + 2 * len(groups)))
         self._reserve(total)
         if self._staging_free is not None:
             self._staging_free.synchronize()               # the last copy out of the staging buffer is done
@@ -183,6 +200,14 @@ class ModelRunner:
             a, a_s = take(N)
             b, b_s = take(S * w)
             g_slot.append(a); g_slot_s.append(a_s); g_tab.append(b.reshape(S, w)); g_tab_s.append(b_s)
+
+        dec, dec_s = take(len(decode_list))
+        dec[:] = decode_list
+        tile_s = {}
+        for G, pairs in tile_lists.items():
+            view, tile_s[G] = take(2 * len(pairs))
+            if pairs:
+                view[:] = np.asarray(pairs, dtype=np.int32).reshape(-1)
 
         at = 0
         r = 0
@@ -234,7 +259,10 @@ class ModelRunner:
             max_q_len=max(q_lens), max_kv_len=max(s + n for s, n in zip(starts, q_lens)),
             group_kv_slot=[d(s_) for s_ in g_slot_s],
             group_block_table=[d(s_, (S, w)) for s_, w in zip(g_tab_s, widths)],
-            cache=self.cache, host_q_lens=q_lens, host_q_start=starts,
+            cache=self.cache,
+            decode_items=d(dec_s) if decode_list else None,
+            prefill_tiles={G: (d(sp, (sp[1] // 2, 2)) if sp[1] else None) for G, sp in tile_s.items()},
+            host_q_lens=q_lens, host_q_start=starts,
             host_slots=[e.request.cache.slot for e in entries],
         )
         logits = self.model.forward(ctx)

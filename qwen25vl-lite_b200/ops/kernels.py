@@ -28,6 +28,8 @@ _SIGNATURES = {
     "q25_paged_attention_generic": [_P, _I, _P, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _P],
 }
 _UNTYPED = {
+    "q25_attention_decode_bf16": [_P, _I, _P, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _I, _P, _P],
+    "q25_attention_prefill_bf16": [_P, _I, _P, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _P],
     "q25_gemm_f32": [_P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P],
     "q25_sample_rows": [_P, _LL, _I, _I, _P, _P, _P, _P, _P],
     "q25_apply_penalties": [_P, _LL, _I, _I, _P, _P, _P, _P, _P, _P, _P],
@@ -163,6 +165,45 @@ def paged_attention_generic(qkv: torch.Tensor, out: torch.Tensor, k_pages: torch
         qkv.data_ptr(), qkv.stride(0), out.data_ptr(), k_pages.data_ptr(), v_pages.data_ptr(), block_table.data_ptr(),
         block_table.shape[1], token_seq.data_ptr(), cu_q.data_ptr(), q_start_pos.data_ptr(), n, nq, nkv, head_dim,
         page_size, int(window or 0), float(scale), _stream()), "paged_attention_generic")
+
+
+def attention_mma_supports(dtype: torch.dtype, head_dim: int, page_size: int) -> bool:
+    """Sizes the tensor-core attention kernels take; everything else goes to the general kernel."""
+    return (dtype == torch.bfloat16 and head_dim % 16 == 0 and 16 <= head_dim <= 128
+            and page_size > 0 and page_size & (page_size - 1) == 0)
+
+
+def attention_decode(qkv: torch.Tensor, out: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor,
+                     block_table: torch.Tensor, cu_q: torch.Tensor, q_start_pos: torch.Tensor, items: torch.Tensor,
+                     nq: int, nkv: int, head_dim: int, page_size: int, window: int, scale: float, n_splits: int,
+                     scratch: Optional[torch.Tensor]) -> None:
+    """Tensor-core attention for the entries listed in ``items`` (int32 entry indices), each
+    of which brings exactly one token.  With ``n_splits`` > 1 the keys of an entry are cut
+    into that many ranges whose partial results go through ``scratch`` (float32, at least
+    ``len(items) * nq * n_splits * (head_dim + 2)`` elements)."""
+    n_items = items.shape[0]
+    if nq // nkv > 16:
+        raise KernelError("attention_decode: more than 16 query heads per kv head; use attention_prefill")
+    if n_splits > 1:
+        need = n_items * nq * n_splits * (head_dim + 2)
+        if scratch is None or scratch.dtype != torch.float32 or scratch.numel() < need:
+            raise KernelError(f"attention_decode: {n_splits} splits need {need} float32 of scratch memory")
+    _check(_fn("q25_attention_decode_bf16", _UNTYPED["q25_attention_decode_bf16"])(
+        qkv.data_ptr(), qkv.stride(0), out.data_ptr(), k_pages.data_ptr(), v_pages.data_ptr(), block_table.data_ptr(),
+        block_table.shape[1], cu_q.data_ptr(), q_start_pos.data_ptr(), items.data_ptr(), n_items, nq, nkv, head_dim,
+        page_size, int(window or 0), float(scale), int(n_splits), _ptr(scratch), _stream()), "attention_decode")
+
+
+def attention_prefill(qkv: torch.Tensor, out: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor,
+                      block_table: torch.Tensor, cu_q: torch.Tensor, q_start_pos: torch.Tensor, tiles: torch.Tensor,
+                      nq: int, nkv: int, head_dim: int, page_size: int, window: int, scale: float) -> None:
+    """Tensor-core attention for runs of tokens.  ``tiles`` is int32 [n, 2]: (entry, row
+    tile), a row tile being 64 consecutive rows of the entry's (token, head of the kv group)
+    pairs, token-major."""
+    _check(_fn("q25_attention_prefill_bf16", _UNTYPED["q25_attention_prefill_bf16"])(
+        qkv.data_ptr(), qkv.stride(0), out.data_ptr(), k_pages.data_ptr(), v_pages.data_ptr(), block_table.data_ptr(),
+        block_table.shape[1], cu_q.data_ptr(), q_start_pos.data_ptr(), tiles.data_ptr(), tiles.shape[0], nq, nkv,
+        head_dim, page_size, int(window or 0), float(scale), _stream()), "attention_prefill")
 
 
 def gemm_f32(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor) -> None:

@@ -33,6 +33,7 @@ class GQAAttention(Mixer):
         self.qkv_bias, self.out_bias = bool(qkv_bias), bool(out_bias)
         self.window = None if not window else int(window)
         self.scale = float(head_dim) ** -0.5
+        self.rows_per_token = num_heads // num_kv_heads      # query heads that share one kv head
         self.qkv_proj = None
         self.o_proj = None
 

@@ -260,3 +260,64 @@ def test_penalties_and_filters():
         p = SamplingParams(temperature=0.7, seed=11, **kw)
         tok = Sampler("cuda").sample(dev(logits[:1]), [p], [11], [2], [[]])[0]
         assert tok == plain.sample(logits[0], 0.7, 11, 2, full["top_k"], full["min_p"], full["top_p"])
+
+
+def run_mma_attention(c, lens, q_lens, nq, nkv, d, page_size, window, splits):
+    """The tensor-core kernels as the engine calls them: one-token entries through the decode
+    kernel, runs through the prefill kernel."""
+    from qwen25vl_lite.ops import kernels
+    G = nq // nkv
+    out = torch.zeros((c["qkv"].shape[0], nq * d), dtype=torch.bfloat16, device="cuda")
+    dec = [i for i, n in enumerate(q_lens) if n == 1 and G <= 16]
+    tiles = [(i, t) for i, n in enumerate(q_lens) if i not in dec for t in range(-(-n * G // 64))]
+    if dec:
+        scratch = torch.full((len(dec) * nq * splits * (d + 2) + 7,), float("nan"), device="cuda") if splits > 1 else None
+        kernels.attention_decode(c["qkv"], out, c["k_pages"], c["v_pages"], c["table"], c["cu"], c["start"],
+                                 dev(np.asarray(dec, np.int32)), nq, nkv, d, page_size, window or 0, d ** -0.5, splits, scratch)
+    if tiles:
+        kernels.attention_prefill(c["qkv"], out, c["k_pages"], c["v_pages"], c["table"], c["cu"], c["start"],
+                                  dev(np.asarray(tiles, np.int32)), nq, nkv, d, page_size, window or 0, d ** -0.5)
+    return out
+
+
+@pytest.mark.parametrize("splits", [1, 3, 16])
+@pytest.mark.parametrize("nq,nkv,d,page_size,window", [
+    (4, 2, 16, 4, None), (6, 1, 32, 8, None), (5, 5, 48, 16, 24), (16, 2, 128, 16, None), (8, 2, 64, 16, 33),
+    (7, 7, 80, 32, None), (12, 4, 96, 16, 100), (4, 1, 112, 8, None), (32, 1, 64, 16, None)])
+def test_attention_tensor_core_kernels(nq, nkv, d, page_size, window, splits):
+    rng = np.random.default_rng(9)
+    lens, q_lens = [1, 37, 130, 64, 200, 333, 31], [1, 37, 2, 1, 45, 1, 1]
+    c = paged_case(rng, lens, q_lens, nq, nkv, d, page_size, torch.bfloat16)
+    out = run_mma_attention(c, lens, q_lens, nq, nkv, d, page_size, window, splits)
+    ref = attention_oracle(c["dense"], window)
+    assert np.abs(f64(out) - ref).max() < 3e-2
+
+
+@pytest.mark.parametrize("q_len", [1, 5])
+def test_tensor_core_attention_finds_a_far_key_and_the_window_edge(q_len):
+    """As for the general kernel: one dominant key on page edges, at both ends, and just inside /
+    outside the window; through the decode kernel (one token, several splits) and the prefill
+    kernel (a run of 5 whose last query is the one that matches)."""
+    nq, nkv, d, ps, L = 8, 2, 128, 16, 700
+    for key, window, visible in [(0, None, True), (15, None, True), (16, None, True), (351, None, True),
+                                 (699, None, True), (700 - 60, 60, True), (700 - 61, 60, False)]:
+        rng = np.random.default_rng(key)
+        c = paged_case(rng, [L], [q_len], nq, nkv, d, ps, torch.bfloat16)
+        q, k, v = c["dense"][0]
+        k = k.clone()
+        k[key, 0] = (q[-1, 0] * 3).to(torch.bfloat16)      # the last query's head 0 matches this key
+        pg = int(c["table"][0, key // ps])
+        c["k_pages"][pg, 0, key % ps] = k[key, 0].cuda()
+        out = run_mma_attention(c, [L], [q_len], nq, nkv, d, ps, window, splits=5)
+        hit = np.abs(f64(out)[-1, :d] - f64(v)[key, 0]).max() < 6e-2
+        assert hit == visible, f"key {key} window {window}: found={hit}"
+        ref = attention_oracle([(q, k, v)], window)
+        assert np.abs(f64(out) - ref).max() < 3e-2
+
+
+def test_decode_splits_heuristic():
+    from qwen25vl_lite.ops.attention import decode_splits
+    assert decode_splits(1, 2, 100) == 1                  # short context: nothing to split
+    assert decode_splits(1, 2, 2048) == 8                 # 2048 keys / 256 per split
+    assert decode_splits(64, 2, 4096) == 2                # 128 (entry, head) pairs already fill the GPU
+    assert decode_splits(8, 2, 100000) == 18
