@@ -223,10 +223,13 @@ def run_ours(args):
     clocks.start()
     value, ms_per_step, launches, ctx = decode_device(8, args.steps, args.warmup)
     clock_record = clocks.stop()
-    e2e_value = decode_e2e(8, args.steps, args.warmup)
-    small = max(8, args.steps // 4)
-    b1, _, _, _ = decode_device(1, small, args.warmup)
-    b64, _, _, _ = decode_device(64, small, args.warmup)
+    if args.headline_only:          # for profiler runs: the headline loop and the prefill alone
+        e2e_value = b1 = b64 = None
+    else:
+        e2e_value = decode_e2e(8, args.steps, args.warmup)
+        small = max(8, args.steps // 4)
+        b1, _, _, _ = decode_device(1, small, args.warmup)
+        b64, _, _, _ = decode_device(64, small, args.warmup)
 
     step_bytes = weight_bytes(t, layers) + 8 * ctx * kv_bytes_per_token(t, layers)
     achieved = step_bytes / (ms_per_step / 1e3) / 1e9
@@ -261,6 +264,7 @@ def main(argv=None):
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--layers", type=int, default=None, help="fewer layers than the model has (named in config)")
+    ap.add_argument("--headline-only", action="store_true", help="skip e2e and the batch 1 / 64 points")
     args = ap.parse_args(argv)
     if args.gpus != 1:
         print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not measured")

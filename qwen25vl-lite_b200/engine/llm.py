@@ -35,7 +35,7 @@ class LLM:
         else:
             raise ValueError("LLM needs a model folder or a random_config")
         self.runner = ModelRunner(self.model, self.ecfg.num_blocks, self.ecfg.block_size, self.ecfg.max_num_seqs,
-                                  max_step_tokens=self.ecfg.max_num_batched_tokens)
+                                  max_step_tokens=self.ecfg.max_num_batched_tokens, cuda_graphs=self.ecfg.cuda_graph)
         self.sampler = Sampler(self.ecfg.device)
         self.engine = LLMEngine(self.runner, self.sampler, self.ecfg, getattr(self.config, "eos_token_id", None))
 

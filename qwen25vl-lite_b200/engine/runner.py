@@ -94,11 +94,15 @@ class StepContext:
                       group.page_size)
 
 
+GRAPH_WIDTH_STEP = 16      # block-table widths of captured steps are rounded up to this many pages
+MAX_GRAPHS = 32
+
+
 class ModelRunner:
     """Owns the model, the cache and the staging buffers; ``step`` is the step function."""
 
     def __init__(self, model: DecoderModel, num_pages: int, page_size: int, max_requests: int,
-                 max_step_tokens: int = 8192):
+                 max_step_tokens: int = 8192, cuda_graphs: bool = True):
         if model.dtype is None:
             raise ValueError("the model has no weights loaded")
         self.model = model
@@ -118,6 +122,14 @@ class ModelRunner:
         self._reserve(max_step_tokens * (3 + self.axes + len(self.cache.groups)) + 4096)
         self.live: Dict[object, Request] = {}
         self.steps = 0
+        # Steps that bring one token per request are launch-bound (hundreds of small kernels), so
+        # they are captured once per (batch size, block-table width) and replayed.  Only when every
+        # mixer says its forward can be captured (no host-side loop over the batch).
+        mixers = [b.mixer for b in getattr(model, "blocks", [])]
+        self.cuda_graphs = bool(cuda_graphs and self.device.type == "cuda" and mixers
+                                and all(getattr(m, "graph_safe", False) for m in mixers))
+        self._graphs: Dict[tuple, tuple] = {}
+        self.graph_replays = 0
 
     # ---- requests ----------------------------------------------------------------------
     def open_request(self, request_id) -> Request:
@@ -141,6 +153,28 @@ class ModelRunner:
         self._staging_np = self._staging.numpy()
         self._device_ints = torch.empty(n_ints, dtype=torch.int32, device=self.device)
 
+    def _replay(self, key, ctx: StepContext, layout) -> torch.Tensor:
+        """Runs a one-token-per-request step from its captured graph.  The step's int arrays sit
+        at the same device addresses for the same key (same counts, same packing order), so a
+        replay only needs the new values, which ``step`` has already copied.  The first step
+        of a key runs once uncaptured (library warm-up; writing the same keys and values
+        twice changes nothing), then is captured and replayed."""
+        hit = self._graphs.get(key)
+        if hit is not None and hit[2] != layout:
+            hit = None                                  # the staging buffer was re-allocated since
+        if hit is None:
+            if len(self._graphs) >= MAX_GRAPHS:
+                self._graphs.pop(next(iter(self._graphs)))
+            self.model.forward(ctx)
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                logits = self.model.forward(ctx)
+            hit = (graph, logits, layout)
+            self._graphs[key] = hit
+        hit[0].replay()
+        self.graph_replays += 1
+        return hit[1]
+
     def step(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
         """Runs the tokens the entries bring, as one batch.  Returns float32 logits
         [number of wanted places, vocab] on the device, in the order of the entries and of
@@ -160,6 +194,10 @@ class ModelRunner:
         for e, n, s in zip(entries, q_lens, starts):
             self.cache.ensure(e.request.cache, s + n)       # no-op when the caller already did
         widths = [max(max(len(e.request.cache.tables[g.index]) for e in entries), 1) for g in groups]
+        graph_key = None
+        if self.cuda_graphs and max(q_lens) == 1 and all(list(e.want) == [0] for e in entries):
+            widths = [-(-w // GRAPH_WIDTH_STEP) * GRAPH_WIDTH_STEP for w in widths]
+            graph_key = (len(entries), tuple(widths))
         M = sum(len(e.want) for e in entries)
 
         # ---- pack ----
@@ -256,7 +294,8 @@ class ModelRunner:
             dtype=self.dtype, device=self.device, n_tokens=N, n_seqs=S,
             token_ids=d(tok_s), positions=d(pos_s, (self.axes, N)), token_seq=d(tseq_s), cu_q=d(cu_s),
             q_start_pos=d(qs_s), slot_ids=d(sl_s), logit_rows=d(rows_s) if M else None,
-            max_q_len=max(q_lens), max_kv_len=max(s + n for s, n in zip(starts, q_lens)),
+            max_q_len=max(q_lens),
+            max_kv_len=(max(widths) * ps if graph_key else max(s + n for s, n in zip(starts, q_lens))),
             group_kv_slot=[d(s_) for s_ in g_slot_s],
             group_block_table=[d(s_, (S, w)) for s_, w in zip(g_tab_s, widths)],
             cache=self.cache,
@@ -265,7 +304,10 @@ class ModelRunner:
             host_q_lens=q_lens, host_q_start=starts,
             host_slots=[e.request.cache.slot for e in entries],
         )
-        logits = self.model.forward(ctx)
+        if graph_key is None:
+            logits = self.model.forward(ctx)
+        else:
+            logits = self._replay(graph_key, ctx, (dev.data_ptr(), off))
 
         for e, n, p_max in zip(entries, q_lens, last_position):
             # plain text that follows resumes one past the largest position seen so far

@@ -34,6 +34,7 @@ class GQAAttention(Mixer):
         self.window = None if not window else int(window)
         self.scale = float(head_dim) ** -0.5
         self.rows_per_token = num_heads // num_kv_heads      # query heads that share one kv head
+        self.graph_safe = True                               # forward is a fixed sequence of launches
         self.qkv_proj = None
         self.o_proj = None
 
