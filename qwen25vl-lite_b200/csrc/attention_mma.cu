@@ -332,20 +332,24 @@ __global__ void attention_combine_kernel(AttnArgs a, int n_items) {
   const int item = w / a.nq, head = w - item * a.nq;
   const int token = a.cu_q[a.items[item]];
   const size_t base = ((size_t)item * a.nq + head) * a.n_splits;
-  float M = -INFINITY;
-  for (int i = 0; i < a.n_splits; ++i) M = fmaxf(M, a.part_ml[(base + i) * 2]);
-  float lsum = 0.f;
-  for (int i = 0; i < a.n_splits; ++i) {
-    const float mi = a.part_ml[(base + i) * 2];
-    lsum += mi == -INFINITY ? 0.f : a.part_ml[(base + i) * 2 + 1] * exp2f(mi - M);
-  }
-  for (int c = lane; c < D; c += 32) {
+  // lanes over the splits for the maximum and the sum (n_splits <= 64), then over the channels
+  float m0 = lane < a.n_splits ? a.part_ml[(base + lane) * 2] : -INFINITY;
+  float m1 = lane + 32 < a.n_splits ? a.part_ml[(base + lane + 32) * 2] : -INFINITY;
+  const float M = warp_max(fmaxf(m0, m1));
+  const float w0 = m0 == -INFINITY ? 0.f : exp2f(m0 - M), w1 = m1 == -INFINITY ? 0.f : exp2f(m1 - M);
+  float lpart = 0.f;
+  if (lane < a.n_splits) lpart += a.part_ml[(base + lane) * 2 + 1] * w0;
+  if (lane + 32 < a.n_splits) lpart += a.part_ml[(base + lane + 32) * 2 + 1] * w1;
+  const float inv = 1.0f / warp_sum(lpart);
+  for (int c0 = 0; c0 < D; c0 += 32) {      // every lane takes part in the shuffles, also past D
+    const int c = c0 + lane;
     float acc = 0.f;
+#pragma unroll 4
     for (int i = 0; i < a.n_splits; ++i) {
-      const float mi = a.part_ml[(base + i) * 2];
-      if (mi != -INFINITY) acc += a.part_o[(base + i) * D + c] * exp2f(mi - M);
+      const float wi = __shfl_sync(0xffffffffu, i < 32 ? w0 : w1, i & 31);
+      if (c < D) acc = fmaf(a.part_o[(base + i) * D + c], wi, acc);
     }
-    a.out[(size_t)token * a.nq * D + (size_t)head * D + c] = __float2bfloat16_rn(acc / lsum);
+    if (c < D) a.out[(size_t)token * a.nq * D + (size_t)head * D + c] = __float2bfloat16_rn(acc * inv);
   }
 }
 

@@ -48,14 +48,18 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ x, const T* __restrict__ 
   for (int c = threadIdx.x; c < hidden; c += blockDim.x) o[c] = from_f32<T>(row_cache[c] * inv * w[c]);
 }
 
-// gu is [n, 2*inter]: gate in the first half of a row, up in the second.
+// gu is [n, 2*inter].  paired == 0: gate in the first half of a row, up in the second.
+// paired == 1: groups of 16 columns hold 8 gate features followed by their 8 up features (the
+// layout the skinny GEMM's SwiGLU epilogue wants of the weight rows).
 template <typename T>
-__global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, int n, int inter) {
+__global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, int n, int inter, int paired) {
   const size_t total = (size_t)n * inter;
   for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
     const size_t row = i / inter, c = i % inter;
-    const float g = to_f32(gu[row * 2 * inter + c]);
-    const float u = to_f32(gu[row * 2 * inter + inter + c]);
+    const size_t gc = paired ? (c >> 3) * 16 + (c & 7) : c;
+    const size_t uc = paired ? gc + 8 : inter + c;
+    const float g = to_f32(gu[row * 2 * inter + gc]);
+    const float u = to_f32(gu[row * 2 * inter + uc]);
     out[i] = from_f32<T>(g / (1.0f + expf(-g)) * u);
   }
 }
@@ -83,12 +87,12 @@ static int add_rmsnorm(float* x, const void* delta, const float* w, float eps, v
 }
 
 template <typename T>
-static int silu_mul(const void* gu, void* out, int n, int inter, void* stream) {
+static int silu_mul(const void* gu, void* out, int n, int inter, int paired, void* stream) {
   if (n <= 0) return 0;
   const size_t total = (size_t)n * inter;
   size_t blocks = (total + 255) / 256;
   if (blocks > 148 * 16) blocks = 148 * 16;
-  silu_mul_kernel<T><<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>((const T*)gu, (T*)out, n, inter);
+  silu_mul_kernel<T><<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>((const T*)gu, (T*)out, n, inter, paired);
   return launch_status();
 }
 
@@ -96,5 +100,5 @@ Q25_EXPORT int q25_embed_gather_f32(const void* t, const int* ids, float* x, int
 Q25_EXPORT int q25_embed_gather_bf16(const void* t, const int* ids, float* x, int n, int h, int v, void* s) { return embed_gather<bf16>(t, ids, x, n, h, v, s); }
 Q25_EXPORT int q25_add_rmsnorm_f32(float* x, const void* d, const float* w, float eps, void* o, const int* rows, int n, int h, void* s) { return add_rmsnorm<float, true>(x, d, w, eps, o, rows, n, h, s); }
 Q25_EXPORT int q25_add_rmsnorm_bf16(float* x, const void* d, const float* w, float eps, void* o, const int* rows, int n, int h, void* s) { return add_rmsnorm<bf16, false>(x, d, w, eps, o, rows, n, h, s); }
-Q25_EXPORT int q25_silu_mul_f32(const void* gu, void* o, int n, int inter, void* s) { return silu_mul<float>(gu, o, n, inter, s); }
-Q25_EXPORT int q25_silu_mul_bf16(const void* gu, void* o, int n, int inter, void* s) { return silu_mul<bf16>(gu, o, n, inter, s); }
+Q25_EXPORT int q25_silu_mul_f32(const void* gu, void* o, int n, int inter, int paired, void* s) { return silu_mul<float>(gu, o, n, inter, paired, s); }
+Q25_EXPORT int q25_silu_mul_bf16(const void* gu, void* o, int n, int inter, int paired, void* s) { return silu_mul<bf16>(gu, o, n, inter, paired, s); }

@@ -30,30 +30,24 @@ __device__ __forceinline__ float gumbel(unsigned long long key, int i) {
   return -logf(-logf(u));
 }
 
-// One block per row.  temperature[row] <= 0: plain argmax.  Ties go to the lowest index.
-__global__ void sample_rows_kernel(const float* __restrict__ logits, size_t ld, int vocab,
-                                   const float* __restrict__ temperature,
-                                   const unsigned long long* __restrict__ seed,
-                                   const int* __restrict__ token_index, int* __restrict__ out) {
+// Value of candidate i of a row: the logit itself (greedy) or logit / T + Gumbel noise.
+__device__ __forceinline__ float candidate(const float* lg, int i, bool draw, float t, unsigned long long key) {
+  const float v = lg[i];
+  return draw ? v / t + gumbel(key, i) : v;
+}
+
+__device__ __forceinline__ void better(float& bv, int& bi, float v, int i) {
+  if (v > bv || (v == bv && i < bi) || bi == 0x7fffffff) { bv = v; bi = i; }
+}
+
+// Best (value, index) of the block's candidates; ties go to the lowest index.  Valid in thread 0.
+__device__ __forceinline__ void block_best(float& bv, int& bi) {
   __shared__ float best_v[32];
   __shared__ int best_i[32];
-  const int row = blockIdx.x;
-  const float* lg = logits + (size_t)row * ld;
-  const float t = temperature ? temperature[row] : 0.f;
-  const bool draw = t > 0.f;
-  unsigned long long key = 0;
-  if (draw) key = mix64(seed[row] * 0x9E3779B97F4A7C15ull + (unsigned long long)(long long)token_index[row]);
-  float bv = -INFINITY;
-  int bi = 0x7fffffff;
-  for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
-    float v = lg[i];
-    if (draw) v = v / t + gumbel(key, i);
-    if (v > bv || (v == bv && i < bi) || bi == 0x7fffffff) { bv = v; bi = i; }
-  }
   for (int o = 16; o > 0; o >>= 1) {
     const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
     const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
-    if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+    if (oi != 0x7fffffff) better(bv, bi, ov, oi);
   }
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   if (lane == 0) { best_v[warp] = bv; best_i[warp] = bi; }
@@ -61,9 +55,50 @@ __global__ void sample_rows_kernel(const float* __restrict__ logits, size_t ld, 
   if (threadIdx.x == 0) {
     const int nwarps = (blockDim.x + 31) >> 5;
     for (int w = 1; w < nwarps; ++w)
-      if (best_v[w] > bv || (best_v[w] == bv && best_i[w] < bi)) { bv = best_v[w]; bi = best_i[w]; }
-    out[row] = bi == 0x7fffffff ? 0 : bi;
+      if (best_i[w] != 0x7fffffff) better(bv, bi, best_v[w], best_i[w]);
   }
+}
+
+// grid (chunks, rows): each block scans one chunk of a row's vocabulary.  With one chunk the
+// winner is final; with more, partial winners go to `partial` and sample_final_kernel picks.
+// temperature[row] <= 0: plain argmax.
+__global__ void sample_rows_kernel(const float* __restrict__ logits, size_t ld, int vocab, int chunk,
+                                   const float* __restrict__ temperature,
+                                   const unsigned long long* __restrict__ seed,
+                                   const int* __restrict__ token_index, int* __restrict__ out,
+                                   float* __restrict__ partial_v, int* __restrict__ partial_i) {
+  const int row = blockIdx.y;
+  const float* lg = logits + (size_t)row * ld;
+  const float t = temperature ? temperature[row] : 0.f;
+  const bool draw = t > 0.f;
+  unsigned long long key = 0;
+  if (draw) key = mix64(seed[row] * 0x9E3779B97F4A7C15ull + (unsigned long long)(long long)token_index[row]);
+  const int begin = blockIdx.x * chunk, end = min(vocab, begin + chunk);
+  float bv = -INFINITY;
+  int bi = 0x7fffffff;
+  for (int i = begin + threadIdx.x; i < end; i += blockDim.x) better(bv, bi, candidate(lg, i, draw, t, key), i);
+  block_best(bv, bi);
+  if (threadIdx.x == 0) {
+    if (gridDim.x == 1) {
+      out[row] = bi == 0x7fffffff ? 0 : bi;
+    } else {
+      partial_v[(size_t)row * gridDim.x + blockIdx.x] = bv;
+      partial_i[(size_t)row * gridDim.x + blockIdx.x] = bi;
+    }
+  }
+}
+
+__global__ void sample_final_kernel(const float* __restrict__ partial_v, const int* __restrict__ partial_i, int chunks,
+                                    int* __restrict__ out) {
+  const int row = blockIdx.x;
+  float bv = -INFINITY;
+  int bi = 0x7fffffff;
+  for (int c = threadIdx.x; c < chunks; c += blockDim.x) {
+    const int i = partial_i[(size_t)row * chunks + c];
+    if (i != 0x7fffffff) better(bv, bi, partial_v[(size_t)row * chunks + c], i);
+  }
+  block_best(bv, bi);
+  if (threadIdx.x == 0) out[row] = bi == 0x7fffffff ? 0 : bi;
 }
 
 // In place on logits[row]: ids/counts of row r are [offsets[r], offsets[r+1]).
@@ -85,13 +120,30 @@ __global__ void apply_penalties_kernel(float* __restrict__ logits, size_t ld, in
   }
 }
 
+// Chunks a row is cut into: enough blocks to fill the GPU when there are few rows.
+Q25_EXPORT int q25_sample_chunks(int rows, int vocab) {
+  if (vocab < 16384) return 1;
+  int want = (2 * 148 + rows - 1) / rows;
+  int most = (vocab + 4095) / 4096;
+  int c = want < most ? want : most;
+  return c < 1 ? 1 : c;
+}
+
+// scratch: 2 * rows * chunks 4-byte words when q25_sample_chunks(rows, vocab) > 1, else unused.
 Q25_EXPORT int q25_sample_rows(const float* logits, long long ld, int rows, int vocab, const float* temperature,
-                               const unsigned long long* seed, const int* token_index, int* out, void* stream) {
+                               const unsigned long long* seed, const int* token_index, int* out, void* scratch,
+                               void* stream) {
   if (rows <= 0) return 0;
   if (vocab <= 0) return (int)cudaErrorInvalidValue;
-  const int threads = vocab >= 8192 ? 1024 : 256;
-  sample_rows_kernel<<<rows, threads, 0, (cudaStream_t)stream>>>(logits, (size_t)ld, vocab, temperature, seed,
-                                                                 token_index, out);
+  const int chunks = q25_sample_chunks(rows, vocab);
+  if (chunks > 1 && !scratch) return (int)cudaErrorInvalidValue;
+  const int chunk = (vocab + chunks - 1) / chunks;
+  const int threads = chunk >= 4096 ? 512 : 256;
+  float* pv = (float*)scratch;
+  int* pi = (int*)scratch + (size_t)rows * chunks;
+  sample_rows_kernel<<<dim3(chunks, rows), threads, 0, (cudaStream_t)stream>>>(logits, (size_t)ld, vocab, chunk, temperature,
+                                                                            seed, token_index, out, pv, pi);
+  if (chunks > 1) sample_final_kernel<<<rows, 64, 0, (cudaStream_t)stream>>>(pv, pi, chunks, out);
   return launch_status();
 }
 

@@ -28,6 +28,7 @@ import torch
 
 from ..cache.manager import CacheManager, RequestCache
 from ..models.decoder import DecoderModel, StopRuntime
+from ..ops import kernels
 
 
 @dataclass
@@ -167,11 +168,13 @@ class ModelRunner:
                 self._graphs.pop(next(iter(self._graphs)))
             self.model.forward(ctx)
             graph = torch.cuda.CUDAGraph()
+            before = kernels.launch_count()
             with torch.cuda.graph(graph):
                 logits = self.model.forward(ctx)
-            hit = (graph, logits, layout)
+            hit = (graph, logits, layout, kernels.launch_count() - before)
             self._graphs[key] = hit
         hit[0].replay()
+        kernels.count_replayed(hit[3])
         self.graph_replays += 1
         return hit[1]
 

@@ -23,7 +23,7 @@ _LL = ctypes.c_longlong
 _SIGNATURES = {
     "q25_embed_gather": [_P, _P, _P, _I, _I, _I, _P],
     "q25_add_rmsnorm": [_P, _P, _P, _F, _P, _P, _I, _I, _P],
-    "q25_silu_mul": [_P, _P, _I, _I, _P],
+    "q25_silu_mul": [_P, _P, _I, _I, _I, _P],
     "q25_rope_store": [_P, _P, _I, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P],
     "q25_paged_attention_generic": [_P, _I, _P, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _P],
 }
@@ -31,7 +31,8 @@ _UNTYPED = {
     "q25_attention_decode_bf16": [_P, _I, _P, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _I, _P, _P],
     "q25_attention_prefill_bf16": [_P, _I, _P, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _P],
     "q25_gemm_f32": [_P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P],
-    "q25_sample_rows": [_P, _LL, _I, _I, _P, _P, _P, _P, _P],
+    "q25_gemm_skinny_bf16": [_P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _P],
+    "q25_sample_rows": [_P, _LL, _I, _I, _P, _P, _P, _P, _P, _P],
     "q25_apply_penalties": [_P, _LL, _I, _I, _P, _P, _P, _P, _P, _P, _P],
 }
 
@@ -86,6 +87,12 @@ def launch_count() -> int:
     return _launches
 
 
+def count_replayed(n: int) -> None:
+    """Launches that ran from a captured graph (they do not pass through ``_check``)."""
+    global _launches
+    _launches += n
+
+
 def _check(code: int, what: str) -> None:
     global _launches
     _launches += 1
@@ -135,10 +142,15 @@ def add_rmsnorm(x: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Te
                                                 out.data_ptr(), _ptr(rows), n_out, hidden, _stream()), "add_rmsnorm")
 
 
-def silu_mul(gate_up: torch.Tensor, out: torch.Tensor) -> None:
+def silu_mul(gate_up: torch.Tensor, out: torch.Tensor, paired: bool = False) -> None:
+    """out = silu(gate) * up.  ``gate_up`` rows hold gate then up (halves), or with ``paired``
+    groups of 8 gate features followed by their 8 up features."""
     n, inter = out.shape
     _dev(gate_up, out.dtype, "silu_mul input")
-    _check(_typed("q25_silu_mul", out.dtype)(gate_up.data_ptr(), out.data_ptr(), n, inter, _stream()), "silu_mul")
+    if paired and inter % 8:
+        raise KernelError(f"silu_mul: the paired layout needs a width that is a multiple of 8, got {inter}")
+    _check(_typed("q25_silu_mul", out.dtype)(gate_up.data_ptr(), out.data_ptr(), n, inter, int(paired), _stream()),
+           "silu_mul")
 
 
 def rope_store(qkv: torch.Tensor, positions: Optional[torch.Tensor], inv_freq: Optional[torch.Tensor],
@@ -220,6 +232,32 @@ def gemm_f32(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out
         _stream()), "gemm_f32")
 
 
+SKINNY_STORE, SKINNY_BIAS, SKINNY_F32, SKINNY_SWIGLU = 0, 1, 2, 3
+SKINNY_MAX_ROWS = 64
+
+
+def gemm_skinny_supports(x: torch.Tensor, w: torch.Tensor) -> bool:
+    return (x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and 1 <= x.shape[0] <= SKINNY_MAX_ROWS
+            and w.shape[1] % 32 == 0 and x.stride(1) == 1 and x.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0)
+
+
+def gemm_skinny(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor, epilogue: int) -> None:
+    """out = x . w^T for at most 64 rows of x, streaming the weights once (bfloat16).
+    ``epilogue``: SKINNY_STORE, SKINNY_BIAS (float32 bias), SKINNY_F32 (float32 out) or
+    SKINNY_SWIGLU (w rows are groups of 8 gate + 8 up features; out has half as many columns)."""
+    m, k = x.shape
+    n = w.shape[0]
+    if not gemm_skinny_supports(x, w) or w.shape[1] != k or not w.is_contiguous():
+        raise KernelError(f"gemm_skinny: unsupported operands {tuple(x.shape)} {x.dtype} x {tuple(w.shape)} {w.dtype}")
+    cols = n // 2 if epilogue == SKINNY_SWIGLU else n
+    want = torch.float32 if epilogue == SKINNY_F32 else torch.bfloat16
+    if out.shape != (m, cols) or out.dtype != want or out.stride(1) != 1:
+        raise KernelError(f"gemm_skinny: output must be [{m}, {cols}] {want}")
+    _check(_fn("q25_gemm_skinny_bf16", _UNTYPED["q25_gemm_skinny_bf16"])(
+        w.data_ptr(), x.data_ptr(), x.stride(0), _ptr(bias), out.data_ptr(), out.stride(0), m, n, k, int(epilogue),
+        _stream()), "gemm_skinny")
+
+
 def sample_rows(logits: torch.Tensor, temperature: Optional[torch.Tensor], seed: Optional[torch.Tensor],
                 token_index: Optional[torch.Tensor], out: torch.Tensor) -> None:
     """out[r] = argmax(logits[r]) where temperature[r] <= 0 (or temperature is None), else a
@@ -228,9 +266,12 @@ def sample_rows(logits: torch.Tensor, temperature: Optional[torch.Tensor], seed:
     _dev(out, torch.int32, "sample_rows out")
     if logits.dtype != torch.float32 or logits.stride(1) != 1:
         raise KernelError("sample_rows: logits must be float32 rows")
+    # a large vocabulary is scanned by several blocks per row; their partial winners need scratch
+    chunks = _fn("q25_sample_chunks", [_I, _I])(rows, vocab)
+    scratch = torch.empty(2 * rows * chunks, dtype=torch.int32, device=logits.device) if chunks > 1 else None
     _check(_fn("q25_sample_rows", _UNTYPED["q25_sample_rows"])(
         logits.data_ptr(), logits.stride(0), rows, vocab, _ptr(temperature), _ptr(seed), _ptr(token_index),
-        out.data_ptr(), _stream()), "sample_rows")
+        out.data_ptr(), _ptr(scratch), _stream()), "sample_rows")
 
 
 def apply_penalties(logits: torch.Tensor, ids: torch.Tensor, counts: torch.Tensor, offsets: torch.Tensor,

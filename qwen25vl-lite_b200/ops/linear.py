@@ -2,9 +2,11 @@
 
 * float32: the engine's own FMA kernel (``csrc/gemm_f32.cu``), whose per-element summation
   order is fixed, so results do not depend on the batch.  No library, no TF32.
-* bfloat16: the library product (cuBLAS through ``torch.mm`` / ``torch.addmm``) with float32
-  accumulation.  The reference's engine uses the same library for every projection
-  (``nn.Linear``, src/qwen25vl_lite/text.py:61-63,80-83; src/qwen25vl_lite/model.py:84).
+* bfloat16, at most 64 rows (decode steps): the engine's weight-streaming kernel
+  (``csrc/gemm_skinny.cu``, mma.sync with the weights on the 16-row side).
+* bfloat16, more rows: the library product (cuBLAS through ``torch.mm`` / ``torch.addmm``)
+  with float32 accumulation.  The reference's engine uses the same library for every
+  projection (``nn.Linear``, src/qwen25vl_lite/text.py:61-63,80-83; src/qwen25vl_lite/model.py:84).
 """
 
 from __future__ import annotations
@@ -34,6 +36,15 @@ class Linear:
             out = torch.empty((x.shape[0], self.out_features), dtype=torch.float32, device=x.device)
             kernels.gemm_f32(x, w, self.bias, out)
             return out
+        if kernels.gemm_skinny_supports(x, w):
+            f32 = out_dtype == torch.float32
+            out = torch.empty((x.shape[0], self.out_features), dtype=torch.float32 if f32 else w.dtype, device=x.device)
+            if f32 and self.bias is None:
+                kernels.gemm_skinny(x, w, None, out, kernels.SKINNY_F32)
+                return out
+            if not f32:
+                kernels.gemm_skinny(x, w, self.bias, out, kernels.SKINNY_BIAS if self.bias is not None else kernels.SKINNY_STORE)
+                return out
         if out_dtype is not None and out_dtype != w.dtype:
             y = torch.mm(x, w.t(), out_dtype=out_dtype)
             if self.bias is not None:

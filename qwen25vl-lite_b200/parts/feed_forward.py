@@ -24,12 +24,23 @@ class SwiGLU(FeedForward):
                 TensorSpec("down_proj.weight", (h, i)))
 
     def load(self, tensors, device, dtype):
-        gu = torch.cat([tensors["gate_proj.weight"], tensors["up_proj.weight"]], dim=0)
-        self.gate_up_proj = Linear(gu.to(device=device, dtype=dtype).contiguous())
+        gate, up = tensors["gate_proj.weight"].to(device), tensors["up_proj.weight"].to(device)
+        self.paired = self.intermediate_size % 8 == 0
+        if self.paired:
+            # rows in groups of 16: 8 gate features, then their 8 up features, so that the
+            # weight-streaming kernel can form silu(gate) * up in its epilogue
+            h = self.hidden_size
+            gu = torch.stack([gate.reshape(-1, 8, h), up.reshape(-1, 8, h)], dim=1).reshape(2 * self.intermediate_size, h)
+        else:
+            gu = torch.cat([gate, up], dim=0)
+        self.gate_up_proj = Linear(gu.to(dtype=dtype).contiguous())
         self.down_proj = Linear(tensors["down_proj.weight"].to(device=device, dtype=dtype).contiguous())
 
     def forward(self, ctx, h):
-        gu = self.gate_up_proj(h)
         act = torch.empty((h.shape[0], self.intermediate_size), dtype=h.dtype, device=h.device)
-        kernels.silu_mul(gu, act)
+        w = self.gate_up_proj.weight
+        if self.paired and kernels.gemm_skinny_supports(h, w):
+            kernels.gemm_skinny(h, w, None, act, kernels.SKINNY_SWIGLU)
+        else:
+            kernels.silu_mul(self.gate_up_proj(h), act, self.paired)
         return self.down_proj(act)
