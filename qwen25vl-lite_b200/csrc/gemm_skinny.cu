@@ -1,30 +1,68 @@
-// y[M,N] = x[M,K] . W[N,K]^T for a handful of rows (decode steps: M = live requests <= 64), bf16.
+// y[M,N] = x[M,K] . W[N,K]^T for a handful of rows (decode steps: M = live requests <= 16), bf16.
 //
-// With so few rows the product is a stream of the weights: every byte of W is read once and
-// used for M multiply-adds, so the kernel is built around keeping HBM busy, not the tensor cores.
-// The weights take the 16-row side of mma.sync m16n8k16 (the roles of the operands are swapped:
-// W is "A", x^T is "B"), which gives 8 batch columns per instruction and M/8 instructions per
-// weight fragment.  Each thread loads 16 contiguous bytes of a weight row straight from global
-// memory (no shared-memory staging) and feeds them to two MMAs; because a dot product does not
-// care about the order of its terms, the 8 values are assigned to the MMA's k slots in the order
-// they lie in memory, and x is read with the same assignment.  x is small and stays in L1/L2.
+// With so few rows the product is a stream of the weights: every byte of W is read once and used
+// for M multiply-adds, so the kernel is built around keeping HBM busy, not the tensor cores.
 //
-// A CTA has WARPS_N x WARPS_K warps: WARPS_N groups of 16 output features, each summed over K by
-// WARPS_K warps that take contiguous K ranges and add up through shared memory in a fixed order.
-// Epilogues: plain store, + float bias, float output (logits), and SwiGLU (rows come as 8 gate
-// rows followed by their 8 up rows, so silu(gate) * up is formed in registers; reference formula
-// src/qwen25vl_lite/text.py:66).
+//   * A CTA owns 16 output features (16 rows of W) and walks K in chunks of 1024.  A producer warp
+//     brings each chunk into shared memory with one bulk asynchronous copy per row
+//     (cp.async.bulk, 2 KB contiguous in global memory each) that signals an mbarrier; a ring of
+//     stages keeps several chunks in flight while the four consumer warps work.
+//   * The weights take the 16-row side of mma.sync m16n8k16 (the operands are swapped: W is "A",
+//     x^T is "B"), 8 batch columns per instruction.  A thread reads 16 contiguous bytes of a row
+//     from shared memory and feeds them to two MMAs; a dot product does not care about the order
+//     of its terms, so the 8 values take the MMA's k slots in memory order and x is read with the
+//     same assignment (16 bytes per thread from global memory; x is small and stays in L1).
+//   * The four consumer warps take alternate 32-wide k blocks of every chunk and add up through
+//     shared memory in warp order at the end, so the result does not depend on timing.
+//   * Epilogues: plain store, + float bias, float output (logits), and SwiGLU: the 16 rows come as
+//     8 gate features followed by their 8 up features, so silu(gate) * up is formed in registers
+//     (reference formula src/qwen25vl_lite/text.py:66).
+//
+// Every wait on an mbarrier is bounded: after WAIT_LIMIT polls the kernel records an error code in
+// *err, stops waiting anywhere, and runs to its end (its output is then invalid).
 #include "common.cuh"
 
 enum { EPI_STORE = 0, EPI_BIAS = 1, EPI_F32 = 2, EPI_SWIGLU = 3 };
 
-__device__ __forceinline__ uint4 ldg_stream(const void* p) {
+#define GS_KC 1024                       // K elements per chunk
+#define GS_ROWS 16
+#define GS_PITCH (GS_KC * 2 + 64)        // bytes; pitch mod 128 = 64 keeps 16-byte shared loads conflict-free
+#define GS_STAGE (GS_ROWS * GS_PITCH)
+#define GS_CONSUMERS 4
+#define GS_THREADS ((GS_CONSUMERS + 1) * 32)
+#define WAIT_LIMIT (1 << 22)
+
+__device__ __forceinline__ unsigned s32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(unsigned long long* bar, int count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(s32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(unsigned long long* bar, unsigned bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(s32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(unsigned long long* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(s32(bar)) : "memory");
+}
+// Polls until the phase with the given parity has completed, at most WAIT_LIMIT times.
+__device__ __forceinline__ bool mbar_wait(unsigned long long* bar, unsigned parity) {
+  for (int i = 0; i < WAIT_LIMIT; ++i) {
+    unsigned done;
+    asm volatile(
+        "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
+        : "=r"(done) : "r"(s32(bar)), "r"(parity) : "memory");
+    if (done) return true;
+  }
+  return false;
+}
+__device__ __forceinline__ void bulk_copy(void* dst, const void* src, unsigned bytes, unsigned long long* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n"
+               ::"r"(s32(dst)), "l"(src), "r"(bytes), "r"(s32(bar)) : "memory");
+}
+__device__ __forceinline__ uint4 lds128(const void* p) {
   uint4 v;
-  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];\n"
-               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+  asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];\n" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(s32(p)));
   return v;
 }
-
 __device__ __forceinline__ void mma16816(float (&c)[4], unsigned a0, unsigned a1, unsigned a2, unsigned a3,
                                          unsigned b0, unsigned b1) {
   asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
@@ -32,75 +70,96 @@ __device__ __forceinline__ void mma16816(float (&c)[4], unsigned a0, unsigned a1
                : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-template <int MT, int WARPS_N, int WARPS_K, int EPI>
-__global__ void __launch_bounds__(WARPS_N * WARPS_K * 32)
+template <int MT, int EPI>
+__global__ void __launch_bounds__(GS_THREADS)
 gemm_skinny_kernel(const bf16* __restrict__ W, const bf16* __restrict__ X, int ldx, const float* __restrict__ bias,
-                   void* __restrict__ out, int ldo, int M, int N, int K) {
-  constexpr int UNROLL = 4;                        // 32-wide K blocks whose weight loads are in flight together
-  __shared__ float red[WARPS_K > 1 ? (WARPS_K - 1) * WARPS_N * 16 * MT * 8 : 1];
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
-  const int wn = warp % WARPS_N, wk = warp / WARPS_N;
-  const int row0 = (blockIdx.x * WARPS_N + wn) * 16;
-  const int kblocks = K / 32;
-  const int per = (kblocks + WARPS_K - 1) / WARPS_K;
-  const int kb_begin = wk * per, kb_end = min(kblocks, kb_begin + per);
+                   void* __restrict__ out, int ldo, int M, int N, int K, int n_stages, int* __restrict__ err) {
+  extern __shared__ __align__(128) unsigned char smem[];
+  unsigned char* stages = smem;
+  float* red = reinterpret_cast<float*>(smem + (size_t)n_stages * GS_STAGE);            // [3 warps][32 lanes][MT * 4]
+  unsigned long long* full = reinterpret_cast<unsigned long long*>(red + 3 * 32 * MT * 4);
+  unsigned long long* empty = full + n_stages;
 
-  const bf16* w0 = W + (size_t)min(row0 + g, N - 1) * K + 8 * t;
-  const bf16* w1 = W + (size_t)min(row0 + g + 8, N - 1) * K + 8 * t;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+  const int row0 = blockIdx.x * GS_ROWS;
+  const int n_chunks = (K + GS_KC - 1) / GS_KC;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < n_stages; ++s) {
+      mbar_init(full + s, 1);
+      mbar_init(empty + s, GS_CONSUMERS);
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+  }
+  __syncthreads();
+
+  if (warp == GS_CONSUMERS) {
+    // ---- producer: one bulk copy per row and chunk ----
+    const bf16* src = W + (size_t)min(row0 + (lane & 15), N - 1) * K;
+    bool ok = true;
+    for (int c = 0; c < n_chunks; ++c) {
+      const int s = c % n_stages;
+      if (c >= n_stages && ok) {
+        ok = mbar_wait(empty + s, ((c / n_stages) - 1) & 1);
+        if (!ok && lane == 0) atomicExch(err, 1);
+      }
+      const unsigned bytes = (unsigned)min(GS_KC, K - c * GS_KC) * 2;
+      if (lane == 0) mbar_expect_tx(full + s, bytes * GS_ROWS);
+      __syncwarp();
+      if (lane < GS_ROWS) bulk_copy(stages + (size_t)s * GS_STAGE + lane * GS_PITCH, src + (size_t)c * GS_KC, bytes, full + s);
+    }
+    return;
+  }
+
+  // ---- consumers ----
   const bf16* xr[MT];
 #pragma unroll
   for (int mt = 0; mt < MT; ++mt) xr[mt] = X + (size_t)min(mt * 8 + g, M - 1) * ldx + 8 * t;
-
   float acc[MT][4];
 #pragma unroll
   for (int mt = 0; mt < MT; ++mt) acc[mt][0] = acc[mt][1] = acc[mt][2] = acc[mt][3] = 0.f;
 
-  int kb = kb_begin;
-  for (; kb + UNROLL <= kb_end; kb += UNROLL) {
-    uint4 a0[UNROLL], a1[UNROLL];
-#pragma unroll
-    for (int u = 0; u < UNROLL; ++u) {
-      a0[u] = ldg_stream(w0 + (size_t)(kb + u) * 32);
-      a1[u] = ldg_stream(w1 + (size_t)(kb + u) * 32);
+  bool ok = true;
+  for (int c = 0; c < n_chunks; ++c) {
+    const int s = c % n_stages;
+    if (ok) {
+      ok = mbar_wait(full + s, (c / n_stages) & 1);
+      if (!ok && lane == 0) atomicExch(err, 2);
     }
-#pragma unroll
-    for (int u = 0; u < UNROLL; ++u) {
+    const unsigned char* st = stages + (size_t)s * GS_STAGE;
+    const int kblocks = min(GS_KC, K - c * GS_KC) / 32;
+#pragma unroll 2
+    for (int kb = warp; kb < kblocks; kb += GS_CONSUMERS) {
+      const uint4 a0 = lds128(st + g * GS_PITCH + kb * 64 + t * 16);
+      const uint4 a1 = lds128(st + (g + 8) * GS_PITCH + kb * 64 + t * 16);
 #pragma unroll
       for (int mt = 0; mt < MT; ++mt) {
-        const uint4 b = *reinterpret_cast<const uint4*>(xr[mt] + (size_t)(kb + u) * 32);
-        mma16816(acc[mt], a0[u].x, a1[u].x, a0[u].y, a1[u].y, b.x, b.y);
-        mma16816(acc[mt], a0[u].z, a1[u].z, a0[u].w, a1[u].w, b.z, b.w);
+        const uint4 b = *reinterpret_cast<const uint4*>(xr[mt] + (size_t)c * GS_KC + kb * 32);
+        mma16816(acc[mt], a0.x, a1.x, a0.y, a1.y, b.x, b.y);
+        mma16816(acc[mt], a0.z, a1.z, a0.w, a1.w, b.z, b.w);
       }
     }
-  }
-  for (; kb < kb_end; ++kb) {
-    const uint4 a0 = ldg_stream(w0 + (size_t)kb * 32), a1 = ldg_stream(w1 + (size_t)kb * 32);
-#pragma unroll
-    for (int mt = 0; mt < MT; ++mt) {
-      const uint4 b = *reinterpret_cast<const uint4*>(xr[mt] + (size_t)kb * 32);
-      mma16816(acc[mt], a0.x, a1.x, a0.y, a1.y, b.x, b.y);
-      mma16816(acc[mt], a0.z, a1.z, a0.w, a1.w, b.z, b.w);
-    }
+    __syncwarp();
+    if (lane == 0) mbar_arrive(empty + s);
   }
 
-  if constexpr (WARPS_K > 1) {   // sum over the K ranges, in warp order
-    if (wk > 0) {
-      float* dst = red + (((size_t)(wk - 1) * WARPS_N + wn) * 32 + lane) * MT * 4;
+  // ---- sum the four warps in warp order (named barrier: every consumer thread gets here) ----
+  if (warp > 0) {
+    float* dst = red + ((size_t)(warp - 1) * 32 + lane) * MT * 4;
 #pragma unroll
-      for (int mt = 0; mt < MT; ++mt)
+    for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
-        for (int e = 0; e < 4; ++e) dst[mt * 4 + e] = acc[mt][e];
-    }
-    __syncthreads();
-    if (wk > 0) return;
+      for (int e = 0; e < 4; ++e) dst[mt * 4 + e] = acc[mt][e];
+  }
+  asm volatile("bar.sync 1, %0;\n" ::"n"(GS_CONSUMERS * 32) : "memory");
+  if (warp > 0) return;
 #pragma unroll
-    for (int k2 = 1; k2 < WARPS_K; ++k2) {
-      const float* src = red + (((size_t)(k2 - 1) * WARPS_N + wn) * 32 + lane) * MT * 4;
+  for (int w = 0; w < GS_CONSUMERS - 1; ++w) {
+    const float* src = red + ((size_t)w * 32 + lane) * MT * 4;
 #pragma unroll
-      for (int mt = 0; mt < MT; ++mt)
+    for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
-        for (int e = 0; e < 4; ++e) acc[mt][e] += src[mt * 4 + e];
-    }
+      for (int e = 0; e < 4; ++e) acc[mt][e] += src[mt * 4 + e];
   }
 
   // accumulator (mt, e): output feature row0 + g + 8 * (e / 2), batch column mt * 8 + 2 t + (e & 1)
@@ -111,7 +170,7 @@ gemm_skinny_kernel(const bf16* __restrict__ W, const bf16* __restrict__ X, int l
       const int m = mt * 8 + 2 * t + e;
       if (m >= M) continue;
       if constexpr (EPI == EPI_SWIGLU) {
-        // rows g of this 16-row group are gate features, rows g + 8 the matching up features
+        // rows g of the group are gate features, rows g + 8 the matching up features
         const int f = (row0 >> 1) + g;
         if (row0 + g + 8 < N) {
           const float gate = acc[mt][e], up = acc[mt][e + 2];
@@ -132,43 +191,39 @@ gemm_skinny_kernel(const bf16* __restrict__ W, const bf16* __restrict__ X, int l
   }
 }
 
-template <int MT, int WARPS_N, int WARPS_K>
-static int launch_epi(int epi, const bf16* W, const bf16* X, int ldx, const float* bias, void* out, int ldo, int M, int N,
-                      int K, cudaStream_t s) {
-  const dim3 grid((N + WARPS_N * 16 - 1) / (WARPS_N * 16)), block(WARPS_N * WARPS_K * 32);
-  switch (epi) {
-    case EPI_STORE: gemm_skinny_kernel<MT, WARPS_N, WARPS_K, EPI_STORE><<<grid, block, 0, s>>>(W, X, ldx, bias, out, ldo, M, N, K); break;
-    case EPI_BIAS: gemm_skinny_kernel<MT, WARPS_N, WARPS_K, EPI_BIAS><<<grid, block, 0, s>>>(W, X, ldx, bias, out, ldo, M, N, K); break;
-    case EPI_F32: gemm_skinny_kernel<MT, WARPS_N, WARPS_K, EPI_F32><<<grid, block, 0, s>>>(W, X, ldx, bias, out, ldo, M, N, K); break;
-    case EPI_SWIGLU: gemm_skinny_kernel<MT, WARPS_N, WARPS_K, EPI_SWIGLU><<<grid, block, 0, s>>>(W, X, ldx, bias, out, ldo, M, N, K); break;
-    default: return (int)cudaErrorInvalidValue;
-  }
+template <int MT, int EPI>
+static int launch(const bf16* W, const bf16* X, int ldx, const float* bias, void* out, int ldo, int M, int N, int K, int* err,
+                  cudaStream_t s) {
+  const int n_chunks = (K + GS_KC - 1) / GS_KC;
+  const int n_stages = n_chunks < 6 ? n_chunks : 6;
+  const size_t smem = (size_t)n_stages * GS_STAGE + 3 * 32 * MT * 4 * sizeof(float) + 2 * n_stages * sizeof(unsigned long long);
+  cudaError_t e = cudaFuncSetAttribute(gemm_skinny_kernel<MT, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, 216 * 1024);
+  if (e != cudaSuccess) return (int)e;
+  gemm_skinny_kernel<MT, EPI><<<(N + GS_ROWS - 1) / GS_ROWS, GS_THREADS, smem, s>>>(W, X, ldx, bias, out, ldo, M, N, K, n_stages, err);
   return launch_status();
 }
 
 template <int MT>
-static int launch_shape(int epi, const bf16* W, const bf16* X, int ldx, const float* bias, void* out, int ldo, int M, int N,
-                        int K, cudaStream_t s) {
-  // Wide outputs: 4 feature groups per CTA, each warp sums all of K.  Narrow outputs would leave
-  // SMs idle that way, so a CTA takes one group of 16 features and its warps split K.
-  const long long wide_ctas = (N + 63) / 64;
-  if (wide_ctas >= 2 * 148) return launch_epi<MT, 4, 1>(epi, W, X, ldx, bias, out, ldo, M, N, K, s);
-  if (K >= 8192) return launch_epi<MT, 1, 8>(epi, W, X, ldx, bias, out, ldo, M, N, K, s);
-  return launch_epi<MT, 1, 4>(epi, W, X, ldx, bias, out, ldo, M, N, K, s);
+static int launch_epi(int epi, const bf16* W, const bf16* X, int ldx, const float* bias, void* out, int ldo, int M, int N,
+                      int K, int* err, cudaStream_t s) {
+  switch (epi) {
+    case EPI_STORE: return launch<MT, EPI_STORE>(W, X, ldx, bias, out, ldo, M, N, K, err, s);
+    case EPI_BIAS: return launch<MT, EPI_BIAS>(W, X, ldx, bias, out, ldo, M, N, K, err, s);
+    case EPI_F32: return launch<MT, EPI_F32>(W, X, ldx, bias, out, ldo, M, N, K, err, s);
+    case EPI_SWIGLU: return launch<MT, EPI_SWIGLU>(W, X, ldx, bias, out, ldo, M, N, K, err, s);
+    default: return (int)cudaErrorInvalidValue;
+  }
 }
 
 // epi: 0 store bf16, 1 + bias then store bf16, 2 store float, 3 SwiGLU pairs (N counts gate and up
-// rows together, the output has N / 2 columns).  Needs K % 32 == 0, 1 <= M <= 64, 16-byte aligned rows.
+// rows together, the output has N / 2 columns).  Needs K % 32 == 0, 1 <= M <= 16, 16-byte aligned
+// rows of W and x.  err: one int in device memory that receives a nonzero code if a wait gave up.
 Q25_EXPORT int q25_gemm_skinny_bf16(const void* W, const void* X, int ldx, const float* bias, void* out, int ldo, int M,
-                                    int N, int K, int epi, void* stream) {
+                                    int N, int K, int epi, int* err, void* stream) {
   if (M <= 0 || N <= 0) return 0;
-  if (M > 64 || K <= 0 || K % 32 || ldx % 8 || (epi == EPI_SWIGLU && N % 16) || (epi == EPI_BIAS && !bias))
+  if (M > 16 || K <= 0 || K % 32 || ldx % 8 || (epi == EPI_SWIGLU && N % 16) || (epi == EPI_BIAS && !bias) || !err)
     return (int)cudaErrorInvalidValue;
   cudaStream_t s = (cudaStream_t)stream;
-  const bf16* w = (const bf16*)W;
-  const bf16* x = (const bf16*)X;
-  if (M <= 8) return launch_shape<1>(epi, w, x, ldx, bias, out, ldo, M, N, K, s);
-  if (M <= 16) return launch_shape<2>(epi, w, x, ldx, bias, out, ldo, M, N, K, s);
-  if (M <= 32) return launch_shape<4>(epi, w, x, ldx, bias, out, ldo, M, N, K, s);
-  return launch_shape<8>(epi, w, x, ldx, bias, out, ldo, M, N, K, s);
+  if (M <= 8) return launch_epi<1>(epi, (const bf16*)W, (const bf16*)X, ldx, bias, out, ldo, M, N, K, err, s);
+  return launch_epi<2>(epi, (const bf16*)W, (const bf16*)X, ldx, bias, out, ldo, M, N, K, err, s);
 }

@@ -131,6 +131,9 @@ class ModelRunner:
                                 and all(getattr(m, "graph_safe", False) for m in mixers))
         self._graphs: Dict[tuple, tuple] = {}
         self.graph_replays = 0
+        # kernels with bounded waits report a wait that gave up here; read back after every step
+        # and looked at before the next one
+        self._error_host = torch.zeros(1, dtype=torch.int32, pin_memory=self.device.type == "cuda")
 
     # ---- requests ----------------------------------------------------------------------
     def open_request(self, request_id) -> Request:
@@ -185,6 +188,9 @@ class ModelRunner:
         the cache and every request's count has advanced."""
         if not entries:
             return None
+        if int(self._error_host[0]) != 0:
+            raise kernels.KernelError(f"a kernel of the previous step gave up waiting (code {int(self._error_host[0])}); "
+                                      "its results are invalid")
         ps = self.cache.page_size
         groups = self.cache.groups
         q_lens = [len(e.tokens) for e in entries]
@@ -312,6 +318,8 @@ class ModelRunner:
         else:
             logits = self._replay(graph_key, ctx, (dev.data_ptr(), off))
 
+        if self.device.type == "cuda":
+            self._error_host.copy_(kernels.error_flag(self.device), non_blocking=True)
         for e, n, p_max in zip(entries, q_lens, last_position):
             # plain text that follows resumes one past the largest position seen so far
             # (the reference's rope_delta = max(pos) + 1 - length, src/qwen25vl_lite/rope.py:235)

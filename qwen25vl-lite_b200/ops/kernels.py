@@ -31,7 +31,7 @@ _UNTYPED = {
     "q25_attention_decode_bf16": [_P, _I, _P, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _I, _P, _P],
     "q25_attention_prefill_bf16": [_P, _I, _P, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _P],
     "q25_gemm_f32": [_P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P],
-    "q25_gemm_skinny_bf16": [_P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _P],
+    "q25_gemm_skinny_bf16": [_P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _P, _P],
     "q25_sample_rows": [_P, _LL, _I, _I, _P, _P, _P, _P, _P, _P],
     "q25_apply_penalties": [_P, _LL, _I, _I, _P, _P, _P, _P, _P, _P, _P],
 }
@@ -233,7 +233,17 @@ def gemm_f32(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out
 
 
 SKINNY_STORE, SKINNY_BIAS, SKINNY_F32, SKINNY_SWIGLU = 0, 1, 2, 3
-SKINNY_MAX_ROWS = 64
+SKINNY_MAX_ROWS = 16
+_error_flags: Dict[torch.device, torch.Tensor] = {}
+
+
+def error_flag(device) -> torch.Tensor:
+    """One int32 per device that kernels with bounded waits set when a wait gave up."""
+    device = torch.device(device)
+    flag = _error_flags.get(device)
+    if flag is None:
+        flag = _error_flags[device] = torch.zeros(1, dtype=torch.int32, device=device)
+    return flag
 
 
 def gemm_skinny_supports(x: torch.Tensor, w: torch.Tensor) -> bool:
@@ -242,7 +252,7 @@ def gemm_skinny_supports(x: torch.Tensor, w: torch.Tensor) -> bool:
 
 
 def gemm_skinny(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor, epilogue: int) -> None:
-    """out = x . w^T for at most 64 rows of x, streaming the weights once (bfloat16).
+    """out = x . w^T for at most 16 rows of x, streaming the weights once (bfloat16).
     ``epilogue``: SKINNY_STORE, SKINNY_BIAS (float32 bias), SKINNY_F32 (float32 out) or
     SKINNY_SWIGLU (w rows are groups of 8 gate + 8 up features; out has half as many columns)."""
     m, k = x.shape
@@ -255,7 +265,7 @@ def gemm_skinny(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], 
         raise KernelError(f"gemm_skinny: output must be [{m}, {cols}] {want}")
     _check(_fn("q25_gemm_skinny_bf16", _UNTYPED["q25_gemm_skinny_bf16"])(
         w.data_ptr(), x.data_ptr(), x.stride(0), _ptr(bias), out.data_ptr(), out.stride(0), m, n, k, int(epilogue),
-        _stream()), "gemm_skinny")
+        error_flag(x.device).data_ptr(), _stream()), "gemm_skinny")
 
 
 def sample_rows(logits: torch.Tensor, temperature: Optional[torch.Tensor], seed: Optional[torch.Tensor],

@@ -323,12 +323,12 @@ def test_decode_splits_heuristic():
     assert decode_splits(8, 2, 100000) == 18
 
 
-@pytest.mark.parametrize("m", [1, 5, 8, 13, 16, 29, 64])
+@pytest.mark.parametrize("m", [1, 5, 8, 13, 16])
 @pytest.mark.parametrize("n,k", [(100, 64), (2560, 2048), (4752, 256), (2048, 11008), (48, 8192)])
 def test_gemm_skinny(m, n, k):
     """The weight-streaming product against float64 on the same bfloat16 operands, all epilogues,
-    wide and narrow outputs (one group of 16 features per CTA with K split over its warps),
-    row counts that do not fill the 8-wide MMA columns, N that is no multiple of 16."""
+    one and many K chunks (so that the ring of stages wraps), row counts that do not fill the
+    8-wide MMA columns, N that is no multiple of 16."""
     from qwen25vl_lite.ops import kernels
     rng = np.random.default_rng(m * 1000 + n)
     x = dev(rng.standard_normal((m, k)), torch.bfloat16)
@@ -355,17 +355,19 @@ def test_gemm_skinny(m, n, k):
         act2 = torch.empty_like(act)
         kernels.silu_mul(gu, act2, paired=True)
         pairs = f64(gu).reshape(m, n // 16, 2, 8)
-        assert np.abs(f64(act2) - (plain.silu(pairs[:, :, 0]) * pairs[:, :, 1]).reshape(m, n // 2)).max() < 2e-2 * scale
+        want2 = (plain.silu(pairs[:, :, 0]) * pairs[:, :, 1]).reshape(m, n // 2)
+        assert np.abs(f64(act2) - want2).max() / max(1.0, np.abs(want2).max()) < 1e-2
+    assert int(kernels.error_flag("cuda:0")[0]) == 0
 
 
 def test_gemm_skinny_refuses_what_it_cannot_do():
     from qwen25vl_lite.ops import kernels
-    x = torch.zeros((65, 64), dtype=torch.bfloat16, device="cuda")
+    x = torch.zeros((17, 64), dtype=torch.bfloat16, device="cuda")
     w = torch.zeros((32, 64), dtype=torch.bfloat16, device="cuda")
     assert not kernels.gemm_skinny_supports(x, w)
     assert not kernels.gemm_skinny_supports(x[:4, :48], w[:, :48])          # K no multiple of 32
     with pytest.raises(kernels.KernelError):
-        kernels.gemm_skinny(x, w, None, torch.empty((65, 32), dtype=torch.bfloat16, device="cuda"), kernels.SKINNY_STORE)
+        kernels.gemm_skinny(x, w, None, torch.empty((17, 32), dtype=torch.bfloat16, device="cuda"), kernels.SKINNY_STORE)
 
 
 def test_sample_rows_large_vocabulary():
