@@ -3,17 +3,19 @@
 // With so few rows the product is a stream of the weights: every byte of W is read once and used
 // for M multiply-adds, so the kernel is built around keeping HBM busy, not the tensor cores.
 //
-//   * A CTA owns 16 output features (16 rows of W) and walks K in chunks of 1024.  A producer warp
-//     brings each chunk into shared memory with one bulk asynchronous copy per row
-//     (cp.async.bulk, 2 KB contiguous in global memory each) that signals an mbarrier; a ring of
-//     stages keeps several chunks in flight while the four consumer warps work.
+//   * One persistent CTA per SM takes groups of 16 output features (16 rows of W) in turn and walks
+//     K in chunks of 1024.  A producer warp brings each chunk into shared memory with one bulk
+//     asynchronous copy per row (cp.async.bulk, 2 KB contiguous in global memory each) that signals
+//     an mbarrier; a ring of stages keeps several chunks in flight, across group borders too,
+//     while the eight consumer warps work.  x is copied once and stays in shared memory when it
+//     fits; otherwise its part of each chunk travels with the chunk.
 //   * The weights take the 16-row side of mma.sync m16n8k16 (the operands are swapped: W is "A",
 //     x^T is "B"), 8 batch columns per instruction.  A thread reads 16 contiguous bytes of a row
 //     from shared memory and feeds them to two MMAs; a dot product does not care about the order
 //     of its terms, so the 8 values take the MMA's k slots in memory order and x is read with the
-//     same assignment (16 bytes per thread from global memory; x is small and stays in L1).
-//   * The four consumer warps take alternate 32-wide k blocks of every chunk and add up through
-//     shared memory in warp order at the end, so the result does not depend on timing.
+//     same assignment.
+//   * The consumer warps take alternate 32-wide k blocks of every chunk and add up through shared
+//     memory in warp order at the end of a group, so the result does not depend on timing.
 //   * Epilogues: plain store, + float bias, float output (logits), and SwiGLU: the 16 rows come as
 //     8 gate features followed by their 8 up features, so silu(gate) * up is formed in registers
 //     (reference formula src/qwen25vl_lite/text.py:66).
@@ -27,9 +29,9 @@ enum { EPI_STORE = 0, EPI_BIAS = 1, EPI_F32 = 2, EPI_SWIGLU = 3 };
 #define GS_KC 1024                       // K elements per chunk
 #define GS_ROWS 16
 #define GS_PITCH (GS_KC * 2 + 64)        // bytes; pitch mod 128 = 64 keeps 16-byte shared loads conflict-free
-#define GS_STAGE (GS_ROWS * GS_PITCH)
-#define GS_CONSUMERS 4
+#define GS_CONSUMERS 8
 #define GS_THREADS ((GS_CONSUMERS + 1) * 32)
+#define GS_SMEM_BUDGET (220 * 1024)
 #define WAIT_LIMIT (1 << 22)
 
 __device__ __forceinline__ unsigned s32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
@@ -70,121 +72,182 @@ __device__ __forceinline__ void mma16816(float (&c)[4], unsigned a0, unsigned a1
                : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
+// Shared memory of a CTA:  x (when it stays resident: M rows of K values, pitch xp)  |  the ring of
+// stages, each 16 weight rows of one chunk (and, when x is not resident, the M rows of x for that
+// chunk)  |  two buffers for the cross-warp sum  |  mbarriers: full[S], empty[S], x.
+struct SkinnyLayout {
+  int xp;            // pitch of a resident x row in bytes (0: x travels with the chunks)
+  int stage_bytes;
+  int n_stages;
+  size_t stages_off, red_off, bar_off, total;
+};
+
+static SkinnyLayout skinny_layout(int M, int K, int MT) {
+  SkinnyLayout L;
+  const int n_chunks = (K + GS_KC - 1) / GS_KC;
+  const size_t red = (size_t)2 * (GS_CONSUMERS - 1) * 32 * MT * 4 * sizeof(float);
+  const size_t bars = 64 * sizeof(unsigned long long);
+  const int xrow = K * 2 + ((K * 2) % 128 == 0 ? 64 : 0);
+  const size_t resident = (size_t)M * xrow;
+  const bool fits = resident + 3 * (size_t)GS_ROWS * GS_PITCH + red + bars <= GS_SMEM_BUDGET;
+  L.xp = fits ? xrow : 0;
+  const size_t xbytes = fits ? (resident + 127) / 128 * 128 : 0;
+  L.stage_bytes = (GS_ROWS + (fits ? 0 : M)) * GS_PITCH;
+  int s = (int)((GS_SMEM_BUDGET - xbytes - red - bars) / L.stage_bytes);
+  // more stages than the chunks of four row groups would never fill
+  L.n_stages = s > 4 * n_chunks ? 4 * n_chunks : (s > 24 ? 24 : s);
+  L.stages_off = xbytes;
+  L.red_off = L.stages_off + (size_t)L.n_stages * L.stage_bytes;
+  L.bar_off = L.red_off + red;
+  L.total = L.bar_off + bars;
+  return L;
+}
+
 template <int MT, int EPI>
 __global__ void __launch_bounds__(GS_THREADS)
 gemm_skinny_kernel(const bf16* __restrict__ W, const bf16* __restrict__ X, int ldx, const float* __restrict__ bias,
-                   void* __restrict__ out, int ldo, int M, int N, int K, int n_stages, int* __restrict__ err) {
+                   void* __restrict__ out, int ldo, int M, int N, int K, SkinnyLayout L, int* __restrict__ err) {
   extern __shared__ __align__(128) unsigned char smem[];
-  unsigned char* stages = smem;
-  float* red = reinterpret_cast<float*>(smem + (size_t)n_stages * GS_STAGE);            // [3 warps][32 lanes][MT * 4]
-  unsigned long long* full = reinterpret_cast<unsigned long long*>(red + 3 * 32 * MT * 4);
-  unsigned long long* empty = full + n_stages;
+  unsigned char* xs = smem;
+  unsigned char* stages = smem + L.stages_off;
+  float* red = reinterpret_cast<float*>(smem + L.red_off);
+  unsigned long long* full = reinterpret_cast<unsigned long long*>(smem + L.bar_off);
+  unsigned long long* empty = full + L.n_stages;
+  unsigned long long* xbar = empty + L.n_stages;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
-  const int row0 = blockIdx.x * GS_ROWS;
   const int n_chunks = (K + GS_KC - 1) / GS_KC;
+  const int groups = (N + GS_ROWS - 1) / GS_ROWS;
+  const bool resident = L.xp != 0;
+  const int S = L.n_stages;
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < n_stages; ++s) {
+    for (int s = 0; s < S; ++s) {
       mbar_init(full + s, 1);
       mbar_init(empty + s, GS_CONSUMERS);
     }
+    mbar_init(xbar, 1);
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
   }
   __syncthreads();
 
   if (warp == GS_CONSUMERS) {
-    // ---- producer: one bulk copy per row and chunk ----
-    const bf16* src = W + (size_t)min(row0 + (lane & 15), N - 1) * K;
-    bool ok = true;
-    for (int c = 0; c < n_chunks; ++c) {
-      const int s = c % n_stages;
-      if (c >= n_stages && ok) {
-        ok = mbar_wait(empty + s, ((c / n_stages) - 1) & 1);
-        if (!ok && lane == 0) atomicExch(err, 1);
-      }
-      const unsigned bytes = (unsigned)min(GS_KC, K - c * GS_KC) * 2;
-      if (lane == 0) mbar_expect_tx(full + s, bytes * GS_ROWS);
+    // ---- producer: one bulk copy per row and chunk, running ahead through the ring ----
+    if (resident) {
+      if (lane == 0) mbar_expect_tx(xbar, (unsigned)M * K * 2);
       __syncwarp();
-      if (lane < GS_ROWS) bulk_copy(stages + (size_t)s * GS_STAGE + lane * GS_PITCH, src + (size_t)c * GS_KC, bytes, full + s);
+      if (lane < M) bulk_copy(xs + (size_t)lane * L.xp, X + (size_t)lane * ldx, (unsigned)K * 2, xbar);
+    }
+    bool ok = true;
+    int it = 0;
+    for (int grp = blockIdx.x; grp < groups; grp += gridDim.x) {
+      const bf16* src = W + (size_t)min(grp * GS_ROWS + (lane & 15), N - 1) * K;
+      for (int c = 0; c < n_chunks; ++c, ++it) {
+        const int s = it % S;
+        if (it >= S && ok) {
+          ok = mbar_wait(empty + s, ((it / S) - 1) & 1);
+          if (!ok && lane == 0) atomicExch(err, 1);
+        }
+        const unsigned bytes = (unsigned)min(GS_KC, K - c * GS_KC) * 2;
+        unsigned char* st = stages + (size_t)s * L.stage_bytes;
+        if (lane == 0) mbar_expect_tx(full + s, bytes * (GS_ROWS + (resident ? 0 : M)));
+        __syncwarp();
+        if (lane < GS_ROWS) bulk_copy(st + lane * GS_PITCH, src + (size_t)c * GS_KC, bytes, full + s);
+        if (!resident && lane < M)
+          bulk_copy(st + (GS_ROWS + lane) * GS_PITCH, X + (size_t)lane * ldx + (size_t)c * GS_KC, bytes, full + s);
+      }
     }
     return;
   }
 
   // ---- consumers ----
-  const bf16* xr[MT];
-#pragma unroll
-  for (int mt = 0; mt < MT; ++mt) xr[mt] = X + (size_t)min(mt * 8 + g, M - 1) * ldx + 8 * t;
-  float acc[MT][4];
-#pragma unroll
-  for (int mt = 0; mt < MT; ++mt) acc[mt][0] = acc[mt][1] = acc[mt][2] = acc[mt][3] = 0.f;
-
   bool ok = true;
-  for (int c = 0; c < n_chunks; ++c) {
-    const int s = c % n_stages;
-    if (ok) {
-      ok = mbar_wait(full + s, (c / n_stages) & 1);
-      if (!ok && lane == 0) atomicExch(err, 2);
-    }
-    const unsigned char* st = stages + (size_t)s * GS_STAGE;
-    const int kblocks = min(GS_KC, K - c * GS_KC) / 32;
-#pragma unroll 2
-    for (int kb = warp; kb < kblocks; kb += GS_CONSUMERS) {
-      const uint4 a0 = lds128(st + g * GS_PITCH + kb * 64 + t * 16);
-      const uint4 a1 = lds128(st + (g + 8) * GS_PITCH + kb * 64 + t * 16);
+  if (resident) {
+    ok = mbar_wait(xbar, 0);
+    if (!ok && lane == 0) atomicExch(err, 3);
+  }
+  // rows of x this thread reads for each 8-column tile (rows past M repeat the last one; their
+  // columns are never stored)
+  int xrow[MT];
 #pragma unroll
-      for (int mt = 0; mt < MT; ++mt) {
-        const uint4 b = *reinterpret_cast<const uint4*>(xr[mt] + (size_t)c * GS_KC + kb * 32);
-        mma16816(acc[mt], a0.x, a1.x, a0.y, a1.y, b.x, b.y);
-        mma16816(acc[mt], a0.z, a1.z, a0.w, a1.w, b.z, b.w);
+  for (int mt = 0; mt < MT; ++mt) xrow[mt] = min(mt * 8 + g, M - 1);
+
+  int it = 0, round = 0;
+  for (int grp = blockIdx.x; grp < groups; grp += gridDim.x, ++round) {
+    float acc[MT][4];
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt) acc[mt][0] = acc[mt][1] = acc[mt][2] = acc[mt][3] = 0.f;
+    for (int c = 0; c < n_chunks; ++c, ++it) {
+      const int s = it % S;
+      if (ok) {
+        ok = mbar_wait(full + s, (it / S) & 1);
+        if (!ok && lane == 0) atomicExch(err, 2);
       }
-    }
-    __syncwarp();
-    if (lane == 0) mbar_arrive(empty + s);
-  }
-
-  // ---- sum the four warps in warp order (named barrier: every consumer thread gets here) ----
-  if (warp > 0) {
-    float* dst = red + ((size_t)(warp - 1) * 32 + lane) * MT * 4;
+      const unsigned char* st = stages + (size_t)s * L.stage_bytes;
+      const unsigned char* xb = resident ? xs + (size_t)c * GS_KC * 2 : st + GS_ROWS * GS_PITCH;
+      const int xpitch = resident ? L.xp : GS_PITCH;
+      const int kblocks = min(GS_KC, K - c * GS_KC) / 32;
+#pragma unroll 2
+      for (int kb = warp; kb < kblocks; kb += GS_CONSUMERS) {
+        const uint4 a0 = lds128(st + g * GS_PITCH + kb * 64 + t * 16);
+        const uint4 a1 = lds128(st + (g + 8) * GS_PITCH + kb * 64 + t * 16);
 #pragma unroll
-    for (int mt = 0; mt < MT; ++mt)
-#pragma unroll
-      for (int e = 0; e < 4; ++e) dst[mt * 4 + e] = acc[mt][e];
-  }
-  asm volatile("bar.sync 1, %0;\n" ::"n"(GS_CONSUMERS * 32) : "memory");
-  if (warp > 0) return;
-#pragma unroll
-  for (int w = 0; w < GS_CONSUMERS - 1; ++w) {
-    const float* src = red + ((size_t)w * 32 + lane) * MT * 4;
-#pragma unroll
-    for (int mt = 0; mt < MT; ++mt)
-#pragma unroll
-      for (int e = 0; e < 4; ++e) acc[mt][e] += src[mt * 4 + e];
-  }
-
-  // accumulator (mt, e): output feature row0 + g + 8 * (e / 2), batch column mt * 8 + 2 t + (e & 1)
-#pragma unroll
-  for (int mt = 0; mt < MT; ++mt) {
-#pragma unroll
-    for (int e = 0; e < 2; ++e) {
-      const int m = mt * 8 + 2 * t + e;
-      if (m >= M) continue;
-      if constexpr (EPI == EPI_SWIGLU) {
-        // rows g of the group are gate features, rows g + 8 the matching up features
-        const int f = (row0 >> 1) + g;
-        if (row0 + g + 8 < N) {
-          const float gate = acc[mt][e], up = acc[mt][e + 2];
-          reinterpret_cast<bf16*>(out)[(size_t)m * ldo + f] = __float2bfloat16_rn(gate / (1.0f + __expf(-gate)) * up);
+        for (int mt = 0; mt < MT; ++mt) {
+          const uint4 b = lds128(xb + (size_t)xrow[mt] * xpitch + kb * 64 + t * 16);
+          mma16816(acc[mt], a0.x, a1.x, a0.y, a1.y, b.x, b.y);
+          mma16816(acc[mt], a0.z, a1.z, a0.w, a1.w, b.z, b.w);
         }
-      } else {
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(empty + s);
+    }
+
+    // sum the warps in warp order; the buffer alternates between rounds, so warp 0 may still read
+    // one while the others already fill the next (named barrier: every consumer thread gets here)
+    float* buf = red + (size_t)(round & 1) * (GS_CONSUMERS - 1) * 32 * MT * 4;
+    if (warp > 0) {
+      float* dst = buf + ((size_t)(warp - 1) * 32 + lane) * MT * 4;
 #pragma unroll
-        for (int h = 0; h < 2; ++h) {
-          const int n = row0 + g + 8 * h;
-          if (n >= N) continue;
-          float v = acc[mt][e + 2 * h];
-          if constexpr (EPI == EPI_BIAS) v += bias[n];
-          if constexpr (EPI == EPI_F32) reinterpret_cast<float*>(out)[(size_t)m * ldo + n] = v;
-          else reinterpret_cast<bf16*>(out)[(size_t)m * ldo + n] = __float2bfloat16_rn(v);
+      for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) dst[mt * 4 + e] = acc[mt][e];
+    }
+    asm volatile("bar.sync 1, %0;\n" ::"n"(GS_CONSUMERS * 32) : "memory");
+    if (warp > 0) continue;
+#pragma unroll
+    for (int w = 0; w < GS_CONSUMERS - 1; ++w) {
+      const float* src = buf + ((size_t)w * 32 + lane) * MT * 4;
+#pragma unroll
+      for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) acc[mt][e] += src[mt * 4 + e];
+    }
+
+    // accumulator (mt, e): output feature row0 + g + 8 * (e / 2), batch column mt * 8 + 2 t + (e & 1)
+    const int row0 = grp * GS_ROWS;
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt) {
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        const int m = mt * 8 + 2 * t + e;
+        if (m >= M) continue;
+        if constexpr (EPI == EPI_SWIGLU) {
+          // rows g of the group are gate features, rows g + 8 the matching up features
+          const int f = (row0 >> 1) + g;
+          if (row0 + g + 8 < N) {
+            const float gate = acc[mt][e], up = acc[mt][e + 2];
+            reinterpret_cast<bf16*>(out)[(size_t)m * ldo + f] = __float2bfloat16_rn(gate / (1.0f + __expf(-gate)) * up);
+          }
+        } else {
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            const int n = row0 + g + 8 * h;
+            if (n >= N) continue;
+            float v = acc[mt][e + 2 * h];
+            if constexpr (EPI == EPI_BIAS) v += bias[n];
+            if constexpr (EPI == EPI_F32) reinterpret_cast<float*>(out)[(size_t)m * ldo + n] = v;
+            else reinterpret_cast<bf16*>(out)[(size_t)m * ldo + n] = __float2bfloat16_rn(v);
+          }
         }
       }
     }
@@ -194,12 +257,13 @@ gemm_skinny_kernel(const bf16* __restrict__ W, const bf16* __restrict__ X, int l
 template <int MT, int EPI>
 static int launch(const bf16* W, const bf16* X, int ldx, const float* bias, void* out, int ldo, int M, int N, int K, int* err,
                   cudaStream_t s) {
-  const int n_chunks = (K + GS_KC - 1) / GS_KC;
-  const int n_stages = n_chunks < 6 ? n_chunks : 6;
-  const size_t smem = (size_t)n_stages * GS_STAGE + 3 * 32 * MT * 4 * sizeof(float) + 2 * n_stages * sizeof(unsigned long long);
-  cudaError_t e = cudaFuncSetAttribute(gemm_skinny_kernel<MT, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, 216 * 1024);
+  const SkinnyLayout L = skinny_layout(M, K, MT);
+  if (L.n_stages < 2 && (K + GS_KC - 1) / GS_KC > 1) return (int)cudaErrorInvalidValue;
+  cudaError_t e = cudaFuncSetAttribute(gemm_skinny_kernel<MT, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, GS_SMEM_BUDGET);
   if (e != cudaSuccess) return (int)e;
-  gemm_skinny_kernel<MT, EPI><<<(N + GS_ROWS - 1) / GS_ROWS, GS_THREADS, smem, s>>>(W, X, ldx, bias, out, ldo, M, N, K, n_stages, err);
+  const int groups = (N + GS_ROWS - 1) / GS_ROWS;
+  const int grid = groups < 148 ? groups : 148;          // one persistent CTA per SM
+  gemm_skinny_kernel<MT, EPI><<<grid, GS_THREADS, L.total, s>>>(W, X, ldx, bias, out, ldo, M, N, K, L, err);
   return launch_status();
 }
 
