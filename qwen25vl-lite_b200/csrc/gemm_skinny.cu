@@ -14,8 +14,9 @@
 //     from shared memory and feeds them to two MMAs; a dot product does not care about the order
 //     of its terms, so the 8 values take the MMA's k slots in memory order and x is read with the
 //     same assignment.
-//   * The consumer warps take alternate 32-wide k blocks of every chunk and add up through shared
-//     memory in warp order at the end of a group, so the result does not depend on timing.
+//   * The eight MMA warps take alternate 32-wide k blocks of every chunk; at the end of a group
+//     they leave their partial sums in shared memory for an epilogue warp, which adds them in warp
+//     order (so the result does not depend on timing) and stores, while the MMA warps go on.
 //   * Epilogues: plain store, + float bias, float output (logits), and SwiGLU: the 16 rows come as
 //     8 gate features followed by their 8 up features, so silu(gate) * up is formed in registers
 //     (reference formula src/qwen25vl_lite/text.py:66).
@@ -30,7 +31,8 @@ enum { EPI_STORE = 0, EPI_BIAS = 1, EPI_F32 = 2, EPI_SWIGLU = 3 };
 #define GS_ROWS 16
 #define GS_PITCH (GS_KC * 2 + 64)        // bytes; pitch mod 128 = 64 keeps 16-byte shared loads conflict-free
 #define GS_CONSUMERS 8
-#define GS_THREADS ((GS_CONSUMERS + 1) * 32)
+#define GS_RED_BUFS 4                    // buffers of partial sums between the MMA warps and the epilogue warp
+#define GS_THREADS ((GS_CONSUMERS + 2) * 32)
 #define GS_SMEM_BUDGET (220 * 1024)
 #define WAIT_LIMIT (1 << 22)
 
@@ -74,7 +76,7 @@ __device__ __forceinline__ void mma16816(float (&c)[4], unsigned a0, unsigned a1
 
 // Shared memory of a CTA:  x (when it stays resident: M rows of K values, pitch xp)  |  the ring of
 // stages, each 16 weight rows of one chunk (and, when x is not resident, the M rows of x for that
-// chunk)  |  two buffers for the cross-warp sum  |  mbarriers: full[S], empty[S], x.
+// chunk)  |  buffers of per-warp partial sums  |  mbarriers: full[S], empty[S], x, red_full[], red_empty[].
 struct SkinnyLayout {
   int xp;            // pitch of a resident x row in bytes (0: x travels with the chunks)
   int stage_bytes;
@@ -85,7 +87,7 @@ struct SkinnyLayout {
 static SkinnyLayout skinny_layout(int M, int K, int MT) {
   SkinnyLayout L;
   const int n_chunks = (K + GS_KC - 1) / GS_KC;
-  const size_t red = (size_t)2 * (GS_CONSUMERS - 1) * 32 * MT * 4 * sizeof(float);
+  const size_t red = (size_t)GS_RED_BUFS * GS_CONSUMERS * 32 * MT * 4 * sizeof(float);
   const size_t bars = 64 * sizeof(unsigned long long);
   const int xrow = K * 2 + ((K * 2) % 128 == 0 ? 64 : 0);
   const size_t resident = (size_t)M * xrow;
@@ -103,6 +105,67 @@ static SkinnyLayout skinny_layout(int M, int K, int MT) {
   return L;
 }
 
+// The epilogue warp: adds the MMA warps' partial sums in warp order and stores the 16 features of
+// the group for every batch row.
+template <int MT, int EPI>
+__device__ __forceinline__ void skinny_epilogue(const float* red, unsigned long long* red_full, unsigned long long* red_empty,
+                                                const float* __restrict__ bias, void* __restrict__ out, int ldo, int M,
+                                                int N, int groups, int* err) {
+  const int lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+  bool ok = true;
+  int round = 0;
+  for (int grp = blockIdx.x; grp < groups; grp += gridDim.x, ++round) {
+    const int b = round % GS_RED_BUFS;
+    if (ok) {
+      ok = mbar_wait(red_full + b, (round / GS_RED_BUFS) & 1);
+      if (!ok && lane == 0) atomicExch(err, 5);
+    }
+    float acc[MT][4];
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt) acc[mt][0] = acc[mt][1] = acc[mt][2] = acc[mt][3] = 0.f;
+#pragma unroll
+    for (int w = 0; w < GS_CONSUMERS; ++w) {
+      const float* src = red + (((size_t)b * GS_CONSUMERS + w) * 32 + lane) * MT * 4;
+#pragma unroll
+      for (int mt = 0; mt < MT; ++mt) {
+        const float4 v = *reinterpret_cast<const float4*>(src + mt * 4);
+        acc[mt][0] += v.x; acc[mt][1] += v.y; acc[mt][2] += v.z; acc[mt][3] += v.w;
+      }
+    }
+    __syncwarp();
+    if (lane == 0) mbar_arrive(red_empty + b);
+
+    // accumulator (mt, e): output feature row0 + g + 8 * (e / 2), batch column mt * 8 + 2 t + (e & 1)
+    const int row0 = grp * GS_ROWS;
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt) {
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        const int m = mt * 8 + 2 * t + e;
+        if (m >= M) continue;
+        if constexpr (EPI == EPI_SWIGLU) {
+          // rows g of the group are gate features, rows g + 8 the matching up features
+          const int f = (row0 >> 1) + g;
+          if (row0 + g + 8 < N) {
+            const float gate = acc[mt][e], up = acc[mt][e + 2];
+            reinterpret_cast<bf16*>(out)[(size_t)m * ldo + f] = __float2bfloat16_rn(gate / (1.0f + __expf(-gate)) * up);
+          }
+        } else {
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            const int n = row0 + g + 8 * h;
+            if (n >= N) continue;
+            float v = acc[mt][e + 2 * h];
+            if constexpr (EPI == EPI_BIAS) v += bias[n];
+            if constexpr (EPI == EPI_F32) reinterpret_cast<float*>(out)[(size_t)m * ldo + n] = v;
+            else reinterpret_cast<bf16*>(out)[(size_t)m * ldo + n] = __float2bfloat16_rn(v);
+          }
+        }
+      }
+    }
+  }
+}
+
 template <int MT, int EPI>
 __global__ void __launch_bounds__(GS_THREADS)
 gemm_skinny_kernel(const bf16* __restrict__ W, const bf16* __restrict__ X, int ldx, const float* __restrict__ bias,
@@ -114,6 +177,8 @@ gemm_skinny_kernel(const bf16* __restrict__ W, const bf16* __restrict__ X, int l
   unsigned long long* full = reinterpret_cast<unsigned long long*>(smem + L.bar_off);
   unsigned long long* empty = full + L.n_stages;
   unsigned long long* xbar = empty + L.n_stages;
+  unsigned long long* red_full = xbar + 1;
+  unsigned long long* red_empty = red_full + GS_RED_BUFS;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
   const int n_chunks = (K + GS_KC - 1) / GS_KC;
@@ -127,6 +192,10 @@ gemm_skinny_kernel(const bf16* __restrict__ W, const bf16* __restrict__ X, int l
       mbar_init(empty + s, GS_CONSUMERS);
     }
     mbar_init(xbar, 1);
+    for (int b = 0; b < GS_RED_BUFS; ++b) {
+      mbar_init(red_full + b, GS_CONSUMERS);
+      mbar_init(red_empty + b, 1);
+    }
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
   }
   __syncthreads();
@@ -160,7 +229,12 @@ gemm_skinny_kernel(const bf16* __restrict__ W, const bf16* __restrict__ X, int l
     return;
   }
 
-  // ---- consumers ----
+  if (warp == GS_CONSUMERS + 1) {
+    skinny_epilogue<MT, EPI>(red, red_full, red_empty, bias, out, ldo, M, N, groups, err);
+    return;
+  }
+
+  // ---- consumers (MMA warps) ----
   bool ok = true;
   if (resident) {
     ok = mbar_wait(xbar, 0);
@@ -202,55 +276,18 @@ gemm_skinny_kernel(const bf16* __restrict__ W, const bf16* __restrict__ X, int l
       if (lane == 0) mbar_arrive(empty + s);
     }
 
-    // sum the warps in warp order; the buffer alternates between rounds, so warp 0 may still read
-    // one while the others already fill the next (named barrier: every consumer thread gets here)
-    float* buf = red + (size_t)(round & 1) * (GS_CONSUMERS - 1) * 32 * MT * 4;
-    if (warp > 0) {
-      float* dst = buf + ((size_t)(warp - 1) * 32 + lane) * MT * 4;
-#pragma unroll
-      for (int mt = 0; mt < MT; ++mt)
-#pragma unroll
-        for (int e = 0; e < 4; ++e) dst[mt * 4 + e] = acc[mt][e];
+    // hand the partial sums to the epilogue warp
+    const int b = round % GS_RED_BUFS;
+    if (round >= GS_RED_BUFS && ok) {
+      ok = mbar_wait(red_empty + b, ((round / GS_RED_BUFS) - 1) & 1);
+      if (!ok && lane == 0) atomicExch(err, 4);
     }
-    asm volatile("bar.sync 1, %0;\n" ::"n"(GS_CONSUMERS * 32) : "memory");
-    if (warp > 0) continue;
+    float* dst = red + (((size_t)b * GS_CONSUMERS + warp) * 32 + lane) * MT * 4;
 #pragma unroll
-    for (int w = 0; w < GS_CONSUMERS - 1; ++w) {
-      const float* src = buf + ((size_t)w * 32 + lane) * MT * 4;
-#pragma unroll
-      for (int mt = 0; mt < MT; ++mt)
-#pragma unroll
-        for (int e = 0; e < 4; ++e) acc[mt][e] += src[mt * 4 + e];
-    }
-
-    // accumulator (mt, e): output feature row0 + g + 8 * (e / 2), batch column mt * 8 + 2 t + (e & 1)
-    const int row0 = grp * GS_ROWS;
-#pragma unroll
-    for (int mt = 0; mt < MT; ++mt) {
-#pragma unroll
-      for (int e = 0; e < 2; ++e) {
-        const int m = mt * 8 + 2 * t + e;
-        if (m >= M) continue;
-        if constexpr (EPI == EPI_SWIGLU) {
-          // rows g of the group are gate features, rows g + 8 the matching up features
-          const int f = (row0 >> 1) + g;
-          if (row0 + g + 8 < N) {
-            const float gate = acc[mt][e], up = acc[mt][e + 2];
-            reinterpret_cast<bf16*>(out)[(size_t)m * ldo + f] = __float2bfloat16_rn(gate / (1.0f + __expf(-gate)) * up);
-          }
-        } else {
-#pragma unroll
-          for (int h = 0; h < 2; ++h) {
-            const int n = row0 + g + 8 * h;
-            if (n >= N) continue;
-            float v = acc[mt][e + 2 * h];
-            if constexpr (EPI == EPI_BIAS) v += bias[n];
-            if constexpr (EPI == EPI_F32) reinterpret_cast<float*>(out)[(size_t)m * ldo + n] = v;
-            else reinterpret_cast<bf16*>(out)[(size_t)m * ldo + n] = __float2bfloat16_rn(v);
-          }
-        }
-      }
-    }
+    for (int mt = 0; mt < MT; ++mt)
+      *reinterpret_cast<float4*>(dst + mt * 4) = make_float4(acc[mt][0], acc[mt][1], acc[mt][2], acc[mt][3]);
+    __syncwarp();
+    if (lane == 0) mbar_arrive(red_full + b);
   }
 }
 
