@@ -522,3 +522,53 @@ Q25_EXPORT int q25_attention_prefill_bf16(const void* qkv, int qkv_stride, void*
   cudaStream_t s = (cudaStream_t)stream;
   DISPATCH_D(launch_prefill, a, n_tiles, s)
 }
+
+// ------------------------------------------------------------------------------------------------
+// The same decode attention for callers that cannot allocate: see attention_noalloc.h.
+// ------------------------------------------------------------------------------------------------
+#include <stdio.h>
+
+#include "attention_noalloc.h"
+
+// Scratch for the split partials.  In host code this name is only a stand-in for the symbol, not a
+// device address: the address each device gave it is looked up once below and passed to the kernel.
+static __device__ __align__(256) float q25_noalloc_scratch[Q25_NOALLOC_SCRATCH_FLOATS];
+
+#define Q25_NOALLOC_MAX_DEVICES 64
+static float* q25_noalloc_address[Q25_NOALLOC_MAX_DEVICES];
+static thread_local char q25_noalloc_message[256] = "";
+
+Q25_EXPORT const char* q25_attention_decode_noalloc_error(void) { return q25_noalloc_message; }
+
+Q25_EXPORT int q25_attention_decode_bf16_noalloc(const void* qkv, int qkv_stride, void* out, const void* kp,
+                                                 const void* vp, const int* bt, int tw, const int* cu_q,
+                                                 const int* q_start, const int* items, int n_items, int nq, int nkv,
+                                                 int d, int page_size, int window, float scale, int n_splits,
+                                                 void* stream) {
+  q25_noalloc_message[0] = 0;
+  if (n_items <= 0) return 0;
+  const long long need = q25_attention_decode_scratch_floats(n_items, nq, d, n_splits);
+  if (need > (long long)Q25_NOALLOC_SCRATCH_FLOATS) {
+    snprintf(q25_noalloc_message, sizeof(q25_noalloc_message),
+             "attention_decode_noalloc: %d entries x %d heads x %d splits need %lld floats of scratch, the built-in "
+             "array holds %d; use fewer splits or the entry point that takes a scratch buffer",
+             n_items, nq, n_splits, need, Q25_NOALLOC_SCRATCH_FLOATS);
+    return Q25_NOALLOC_TOO_LARGE;
+  }
+  int device = -1;
+  cudaError_t e = cudaGetDevice(&device);
+  if (e == cudaSuccess && (device < 0 || device >= Q25_NOALLOC_MAX_DEVICES)) e = cudaErrorInvalidDevice;
+  if (e == cudaSuccess && !q25_noalloc_address[device]) {   // set-up: first call on this device
+    void* address = nullptr;
+    e = cudaGetSymbolAddress(&address, q25_noalloc_scratch);
+    if (e == cudaSuccess) q25_noalloc_address[device] = static_cast<float*>(address);
+  }
+  if (e != cudaSuccess) {
+    snprintf(q25_noalloc_message, sizeof(q25_noalloc_message), "attention_decode_noalloc: set-up failed: %s",
+             cudaGetErrorString(e));
+    return (int)e;
+  }
+  return q25_attention_decode_bf16(qkv, qkv_stride, out, kp, vp, bt, tw, cu_q, q_start, items, n_items, nq, nkv, d,
+                                   page_size, window, scale, n_splits, n_splits > 1 ? q25_noalloc_address[device] : nullptr,
+                                   stream);
+}
