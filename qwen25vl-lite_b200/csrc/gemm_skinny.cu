@@ -25,7 +25,7 @@
 // *err, stops waiting anywhere, and runs to its end (its output is then invalid).
 #include "common.cuh"
 
-enum { EPI_STORE = 0, EPI_BIAS = 1, EPI_F32 = 2, EPI_SWIGLU = 3 };
+enum { EPI_STORE = 0, EPI_BIAS = 1, EPI_F32 = 2, EPI_SWIGLU = 3, EPI_RESIDUAL = 4 };
 
 #define GS_KC 1024                       // K elements per chunk
 #define GS_ROWS 16
@@ -158,6 +158,7 @@ __device__ __forceinline__ void skinny_epilogue(const float* red, unsigned long 
             float v = acc[mt][e + 2 * h];
             if constexpr (EPI == EPI_BIAS) v += bias[n];
             if constexpr (EPI == EPI_F32) reinterpret_cast<float*>(out)[(size_t)m * ldo + n] = v;
+            else if constexpr (EPI == EPI_RESIDUAL) reinterpret_cast<float*>(out)[(size_t)m * ldo + n] += v;
             else reinterpret_cast<bf16*>(out)[(size_t)m * ldo + n] = __float2bfloat16_rn(v);
           }
         }
@@ -166,10 +167,15 @@ __device__ __forceinline__ void skinny_epilogue(const float* red, unsigned long 
   }
 }
 
-template <int MT, int EPI>
+// NORM: X is the float residual stream; the rows are RMS-normalised (x * rsqrt(mean(x^2) + eps) *
+// norm_w, reference src/qwen25vl_lite/layers.py:27-31) into shared memory by the MMA warps while
+// the first weight chunks are already on their way, so the norm costs no launch and no time.
+template <int MT, int EPI, bool NORM>
 __global__ void __launch_bounds__(GS_THREADS)
-gemm_skinny_kernel(const bf16* __restrict__ W, const bf16* __restrict__ X, int ldx, const float* __restrict__ bias,
-                   void* __restrict__ out, int ldo, int M, int N, int K, SkinnyLayout L, int* __restrict__ err) {
+gemm_skinny_kernel(const bf16* __restrict__ W, const void* __restrict__ Xv, int ldx, const float* __restrict__ norm_w,
+                   float eps, const float* __restrict__ bias, void* __restrict__ out, int ldo, int M, int N, int K,
+                   SkinnyLayout L, int* __restrict__ err) {
+  const bf16* X = reinterpret_cast<const bf16*>(Xv);
   extern __shared__ __align__(128) unsigned char smem[];
   unsigned char* xs = smem;
   unsigned char* stages = smem + L.stages_off;
@@ -202,7 +208,7 @@ gemm_skinny_kernel(const bf16* __restrict__ W, const bf16* __restrict__ X, int l
 
   if (warp == GS_CONSUMERS) {
     // ---- producer: one bulk copy per row and chunk, running ahead through the ring ----
-    if (resident) {
+    if (resident && !NORM) {
       if (lane == 0) mbar_expect_tx(xbar, (unsigned)M * K * 2);
       __syncwarp();
       if (lane < M) bulk_copy(xs + (size_t)lane * L.xp, X + (size_t)lane * ldx, (unsigned)K * 2, xbar);
@@ -236,7 +242,29 @@ gemm_skinny_kernel(const bf16* __restrict__ W, const bf16* __restrict__ X, int l
 
   // ---- consumers (MMA warps) ----
   bool ok = true;
-  if (resident) {
+  if constexpr (NORM) {
+    const float* Xf = reinterpret_cast<const float*>(Xv);
+    for (int m = warp; m < M; m += GS_CONSUMERS) {
+      const float* xr = Xf + (size_t)m * ldx;
+      float ss = 0.f;
+      for (int k = lane * 4; k < K; k += 128) {
+        const float4 v = *reinterpret_cast<const float4*>(xr + k);
+        ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+      }
+      const float inv = rsqrtf(warp_sum(ss) / (float)K + eps);
+      for (int k = lane * 4; k < K; k += 128) {
+        const float4 v = *reinterpret_cast<const float4*>(xr + k);
+        const float4 w = *reinterpret_cast<const float4*>(norm_w + k);
+        __nv_bfloat162 lo = __floats2bfloat162_rn(v.x * inv * w.x, v.y * inv * w.y);
+        __nv_bfloat162 hi = __floats2bfloat162_rn(v.z * inv * w.z, v.w * inv * w.w);
+        uint2 packed;
+        packed.x = *reinterpret_cast<unsigned*>(&lo);
+        packed.y = *reinterpret_cast<unsigned*>(&hi);
+        *reinterpret_cast<uint2*>(xs + (size_t)m * L.xp + (size_t)k * 2) = packed;
+      }
+    }
+    asm volatile("bar.sync 1, %0;\n" ::"n"(GS_CONSUMERS * 32) : "memory");
+  } else if (resident) {
     ok = mbar_wait(xbar, 0);
     if (!ok && lane == 0) atomicExch(err, 3);
   }
@@ -291,40 +319,63 @@ gemm_skinny_kernel(const bf16* __restrict__ W, const bf16* __restrict__ X, int l
   }
 }
 
-template <int MT, int EPI>
-static int launch(const bf16* W, const bf16* X, int ldx, const float* bias, void* out, int ldo, int M, int N, int K, int* err,
-                  cudaStream_t s) {
+template <int MT, int EPI, bool NORM>
+static int launch(const bf16* W, const void* X, int ldx, const float* norm_w, float eps, const float* bias, void* out,
+                  int ldo, int M, int N, int K, int* err, cudaStream_t s) {
   const SkinnyLayout L = skinny_layout(M, K, MT);
   if (L.n_stages < 2 && (K + GS_KC - 1) / GS_KC > 1) return (int)cudaErrorInvalidValue;
-  cudaError_t e = cudaFuncSetAttribute(gemm_skinny_kernel<MT, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, GS_SMEM_BUDGET);
+  if (NORM && L.xp == 0) return (int)cudaErrorInvalidValue;      // the normalised rows must stay resident
+  cudaError_t e = cudaFuncSetAttribute(gemm_skinny_kernel<MT, EPI, NORM>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       GS_SMEM_BUDGET);
   if (e != cudaSuccess) return (int)e;
   const int groups = (N + GS_ROWS - 1) / GS_ROWS;
   const int grid = groups < 148 ? groups : 148;          // one persistent CTA per SM
-  gemm_skinny_kernel<MT, EPI><<<grid, GS_THREADS, L.total, s>>>(W, X, ldx, bias, out, ldo, M, N, K, L, err);
+  gemm_skinny_kernel<MT, EPI, NORM><<<grid, GS_THREADS, L.total, s>>>(W, X, ldx, norm_w, eps, bias, out, ldo, M, N, K, L, err);
   return launch_status();
 }
 
-template <int MT>
-static int launch_epi(int epi, const bf16* W, const bf16* X, int ldx, const float* bias, void* out, int ldo, int M, int N,
-                      int K, int* err, cudaStream_t s) {
+template <int MT, bool NORM>
+static int launch_epi(int epi, const bf16* W, const void* X, int ldx, const float* norm_w, float eps, const float* bias,
+                      void* out, int ldo, int M, int N, int K, int* err, cudaStream_t s) {
   switch (epi) {
-    case EPI_STORE: return launch<MT, EPI_STORE>(W, X, ldx, bias, out, ldo, M, N, K, err, s);
-    case EPI_BIAS: return launch<MT, EPI_BIAS>(W, X, ldx, bias, out, ldo, M, N, K, err, s);
-    case EPI_F32: return launch<MT, EPI_F32>(W, X, ldx, bias, out, ldo, M, N, K, err, s);
-    case EPI_SWIGLU: return launch<MT, EPI_SWIGLU>(W, X, ldx, bias, out, ldo, M, N, K, err, s);
+    case EPI_STORE: return launch<MT, EPI_STORE, NORM>(W, X, ldx, norm_w, eps, bias, out, ldo, M, N, K, err, s);
+    case EPI_BIAS: return launch<MT, EPI_BIAS, NORM>(W, X, ldx, norm_w, eps, bias, out, ldo, M, N, K, err, s);
+    case EPI_F32: return launch<MT, EPI_F32, NORM>(W, X, ldx, norm_w, eps, bias, out, ldo, M, N, K, err, s);
+    case EPI_SWIGLU: return launch<MT, EPI_SWIGLU, NORM>(W, X, ldx, norm_w, eps, bias, out, ldo, M, N, K, err, s);
+    case EPI_RESIDUAL: return launch<MT, EPI_RESIDUAL, NORM>(W, X, ldx, norm_w, eps, bias, out, ldo, M, N, K, err, s);
     default: return (int)cudaErrorInvalidValue;
   }
 }
 
+// Whether x of M rows and K columns stays resident in shared memory (what the norm-fused variant needs).
+Q25_EXPORT int q25_gemm_skinny_resident(int M, int K) {
+  if (M <= 0 || M > 16 || K <= 0 || K % 32) return 0;
+  return skinny_layout(M, K, M <= 8 ? 1 : 2).xp != 0;
+}
+
 // epi: 0 store bf16, 1 + bias then store bf16, 2 store float, 3 SwiGLU pairs (N counts gate and up
-// rows together, the output has N / 2 columns).  Needs K % 32 == 0, 1 <= M <= 16, 16-byte aligned
-// rows of W and x.  err: one int in device memory that receives a nonzero code if a wait gave up.
+// rows together, the output has N / 2 columns), 4 add into a float matrix (out[m][n] += y[m][n], the
+// residual stream).  Needs K % 32 == 0, 1 <= M <= 16, 16-byte aligned rows of W and x.
+// err: one int in device memory that receives a nonzero code if a wait gave up.
 Q25_EXPORT int q25_gemm_skinny_bf16(const void* W, const void* X, int ldx, const float* bias, void* out, int ldo, int M,
                                     int N, int K, int epi, int* err, void* stream) {
   if (M <= 0 || N <= 0) return 0;
   if (M > 16 || K <= 0 || K % 32 || ldx % 8 || (epi == EPI_SWIGLU && N % 16) || (epi == EPI_BIAS && !bias) || !err)
     return (int)cudaErrorInvalidValue;
   cudaStream_t s = (cudaStream_t)stream;
-  if (M <= 8) return launch_epi<1>(epi, (const bf16*)W, (const bf16*)X, ldx, bias, out, ldo, M, N, K, err, s);
-  return launch_epi<2>(epi, (const bf16*)W, (const bf16*)X, ldx, bias, out, ldo, M, N, K, err, s);
+  if (M <= 8) return launch_epi<1, false>(epi, (const bf16*)W, X, ldx, nullptr, 0.f, bias, out, ldo, M, N, K, err, s);
+  return launch_epi<2, false>(epi, (const bf16*)W, X, ldx, nullptr, 0.f, bias, out, ldo, M, N, K, err, s);
+}
+
+// The same product on rmsnorm(X) * norm_w, X being float rows (the residual stream); the
+// normalisation happens inside the kernel.  Needs q25_gemm_skinny_resident(M, K).
+Q25_EXPORT int q25_gemm_skinny_norm_bf16(const void* W, const float* X, int ldx, const float* norm_w, float eps,
+                                         const float* bias, void* out, int ldo, int M, int N, int K, int epi, int* err,
+                                         void* stream) {
+  if (M <= 0 || N <= 0) return 0;
+  if (M > 16 || K <= 0 || K % 32 || ldx % 4 || !norm_w || (epi == EPI_SWIGLU && N % 16) || (epi == EPI_BIAS && !bias) || !err)
+    return (int)cudaErrorInvalidValue;
+  cudaStream_t s = (cudaStream_t)stream;
+  if (M <= 8) return launch_epi<1, true>(epi, (const bf16*)W, X, ldx, norm_w, eps, bias, out, ldo, M, N, K, err, s);
+  return launch_epi<2, true>(epi, (const bf16*)W, X, ldx, norm_w, eps, bias, out, ldo, M, N, K, err, s);
 }

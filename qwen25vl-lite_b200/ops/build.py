@@ -122,6 +122,9 @@ def build_library(name: str, verbose: bool = True) -> str:
         if res.returncode != 0:
             raise BuildError(f"linking {name} failed:\n{res.stdout}\n{res.stderr}")
         os.replace(tmp, target)
+        for old in os.listdir(os.path.dirname(out_dir)):      # builds of earlier sources are of no use
+            if old.startswith(name + "-") and old != os.path.basename(out_dir):
+                shutil.rmtree(os.path.join(os.path.dirname(out_dir), old), ignore_errors=True)
     finally:
         stop.set()
     if verbose:

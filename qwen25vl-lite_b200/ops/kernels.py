@@ -232,7 +232,7 @@ def gemm_f32(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out
         _stream()), "gemm_f32")
 
 
-SKINNY_STORE, SKINNY_BIAS, SKINNY_F32, SKINNY_SWIGLU = 0, 1, 2, 3
+SKINNY_STORE, SKINNY_BIAS, SKINNY_F32, SKINNY_SWIGLU, SKINNY_RESIDUAL = 0, 1, 2, 3, 4
 SKINNY_MAX_ROWS = 16
 _error_flags: Dict[torch.device, torch.Tensor] = {}
 
@@ -253,19 +253,46 @@ def gemm_skinny_supports(x: torch.Tensor, w: torch.Tensor) -> bool:
 
 def gemm_skinny(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor, epilogue: int) -> None:
     """out = x . w^T for at most 16 rows of x, streaming the weights once (bfloat16).
-    ``epilogue``: SKINNY_STORE, SKINNY_BIAS (float32 bias), SKINNY_F32 (float32 out) or
-    SKINNY_SWIGLU (w rows are groups of 8 gate + 8 up features; out has half as many columns)."""
+    ``epilogue``: SKINNY_STORE, SKINNY_BIAS (float32 bias), SKINNY_F32 (float32 out),
+    SKINNY_SWIGLU (w rows are groups of 8 gate + 8 up features; out has half as many columns)
+    or SKINNY_RESIDUAL (out is float32 and the product is added into it)."""
     m, k = x.shape
     n = w.shape[0]
     if not gemm_skinny_supports(x, w) or w.shape[1] != k or not w.is_contiguous():
         raise KernelError(f"gemm_skinny: unsupported operands {tuple(x.shape)} {x.dtype} x {tuple(w.shape)} {w.dtype}")
-    cols = n // 2 if epilogue == SKINNY_SWIGLU else n
-    want = torch.float32 if epilogue == SKINNY_F32 else torch.bfloat16
-    if out.shape != (m, cols) or out.dtype != want or out.stride(1) != 1:
-        raise KernelError(f"gemm_skinny: output must be [{m}, {cols}] {want}")
+    _skinny_out(out, m, n, epilogue, "gemm_skinny")
     _check(_fn("q25_gemm_skinny_bf16", _UNTYPED["q25_gemm_skinny_bf16"])(
         w.data_ptr(), x.data_ptr(), x.stride(0), _ptr(bias), out.data_ptr(), out.stride(0), m, n, k, int(epilogue),
         error_flag(x.device).data_ptr(), _stream()), "gemm_skinny")
+
+
+def _skinny_out(out: torch.Tensor, m: int, n: int, epilogue: int, what: str) -> None:
+    cols = n // 2 if epilogue == SKINNY_SWIGLU else n
+    want = torch.float32 if epilogue in (SKINNY_F32, SKINNY_RESIDUAL) else torch.bfloat16
+    if out.shape != (m, cols) or out.dtype != want or out.stride(1) != 1:
+        raise KernelError(f"{what}: output must be [{m}, {cols}] {want}")
+
+
+def gemm_skinny_norm_supports(x: torch.Tensor, w: torch.Tensor) -> bool:
+    """Whether ``gemm_skinny_norm`` takes the float32 rows ``x`` (the residual stream) and ``w``."""
+    return (x.dtype == torch.float32 and w.dtype == torch.bfloat16 and x.dim() == 2 and x.stride(1) == 1
+            and x.stride(0) % 4 == 0 and x.data_ptr() % 16 == 0 and w.is_contiguous()
+            and bool(_fn("q25_gemm_skinny_resident", [_I, _I])(x.shape[0], w.shape[1])))
+
+
+def gemm_skinny_norm(x: torch.Tensor, norm_weight: torch.Tensor, eps: float, w: torch.Tensor,
+                     bias: Optional[torch.Tensor], out: torch.Tensor, epilogue: int) -> None:
+    """out = (rmsnorm(x) * norm_weight) . w^T with the normalisation done inside the kernel;
+    x is float32 [M <= 16, K], everything else as for ``gemm_skinny``."""
+    m, k = x.shape
+    n = w.shape[0]
+    if not gemm_skinny_norm_supports(x, w) or w.shape[1] != k:
+        raise KernelError(f"gemm_skinny_norm: unsupported operands {tuple(x.shape)} {x.dtype} x {tuple(w.shape)} {w.dtype}")
+    _dev(norm_weight, torch.float32, "gemm_skinny_norm norm weight")
+    _skinny_out(out, m, n, epilogue, "gemm_skinny_norm")
+    _check(_fn("q25_gemm_skinny_norm_bf16", [_P, _P, _I, _P, _F, _P, _P, _I, _I, _I, _I, _I, _P, _P])(
+        w.data_ptr(), x.data_ptr(), x.stride(0), norm_weight.data_ptr(), float(eps), _ptr(bias), out.data_ptr(),
+        out.stride(0), m, n, k, int(epilogue), error_flag(x.device).data_ptr(), _stream()), "gemm_skinny_norm")
 
 
 def sample_rows(logits: torch.Tensor, temperature: Optional[torch.Tensor], seed: Optional[torch.Tensor],

@@ -2,8 +2,10 @@
 
 * float32: the engine's own FMA kernel (``csrc/gemm_f32.cu``), whose per-element summation
   order is fixed, so results do not depend on the batch.  No library, no TF32.
-* bfloat16, at most 64 rows (decode steps): the engine's weight-streaming kernel
-  (``csrc/gemm_skinny.cu``, mma.sync with the weights on the 16-row side).
+* bfloat16, at most 16 rows (decode steps): the engine's weight-streaming kernel
+  (``csrc/gemm_skinny.cu``).  It can normalise its input on the fly (a ``DeferredNorm``)
+  and add its result into the float32 residual stream, which removes the norm kernels and
+  the separate residual additions from a decode step.
 * bfloat16, more rows: the library product (cuBLAS through ``torch.mm`` / ``torch.addmm``)
   with float32 accumulation.  The reference's engine uses the same library for every
   projection (``nn.Linear``, src/qwen25vl_lite/text.py:61-63,80-83; src/qwen25vl_lite/model.py:84).
@@ -18,6 +20,21 @@ import torch
 from . import kernels
 
 
+class DeferredNorm:
+    """``rmsnorm(x) * weight`` that has not been computed yet: a product that can normalise
+    inside its kernel takes it as it is, anything else calls ``materialize``."""
+
+    def __init__(self, x: torch.Tensor, weight: torch.Tensor, eps: float, dtype: torch.dtype):
+        self.x, self.weight, self.eps, self.dtype = x, weight, eps, dtype
+        self.shape = x.shape
+        self.device = x.device
+
+    def materialize(self) -> torch.Tensor:
+        out = torch.empty(self.x.shape, dtype=self.dtype, device=self.x.device)
+        kernels.add_rmsnorm(self.x, None, self.weight, self.eps, out)
+        return out
+
+
 class Linear:
     """A weight [N, K] (and optional float32 bias [N]) held on the device for ``y = x W^T + b``."""
 
@@ -28,23 +45,24 @@ class Linear:
         # the library path adds the bias in the activation dtype
         self._bias_lib = None if bias is None or weight.dtype == torch.float32 else bias.to(weight.dtype)
 
-    def __call__(self, x: torch.Tensor, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+    def __call__(self, x, out_dtype: Optional[torch.dtype] = None, residual: Optional[torch.Tensor] = None):
+        """``x``: activations [M, K] or a ``DeferredNorm``.  With ``residual`` (float32 [M, N])
+        the product is added into it and None is returned when the kernel at hand can do
+        that; otherwise the product is returned and the caller adds it later."""
         w = self.weight
         if x.shape[-1] != self.in_features:
             raise ValueError(f"linear: input width {x.shape[-1]} does not match weight {tuple(w.shape)}")
+        deferred = isinstance(x, DeferredNorm)
+        if w.dtype == torch.bfloat16 and x.shape[0] <= kernels.SKINNY_MAX_ROWS:
+            y = self._skinny(x, deferred, out_dtype, residual)
+            if y is not NotImplemented:
+                return y
+        if deferred:
+            x = x.materialize()
         if w.dtype == torch.float32:
             out = torch.empty((x.shape[0], self.out_features), dtype=torch.float32, device=x.device)
             kernels.gemm_f32(x, w, self.bias, out)
             return out
-        if kernels.gemm_skinny_supports(x, w):
-            f32 = out_dtype == torch.float32
-            out = torch.empty((x.shape[0], self.out_features), dtype=torch.float32 if f32 else w.dtype, device=x.device)
-            if f32 and self.bias is None:
-                kernels.gemm_skinny(x, w, None, out, kernels.SKINNY_F32)
-                return out
-            if not f32:
-                kernels.gemm_skinny(x, w, self.bias, out, kernels.SKINNY_BIAS if self.bias is not None else kernels.SKINNY_STORE)
-                return out
         if out_dtype is not None and out_dtype != w.dtype:
             y = torch.mm(x, w.t(), out_dtype=out_dtype)
             if self.bias is not None:
@@ -53,3 +71,28 @@ class Linear:
         if self._bias_lib is not None:
             return torch.addmm(self._bias_lib, x, w.t())
         return torch.mm(x, w.t())
+
+    def _skinny(self, x, deferred: bool, out_dtype, residual):
+        """The weight-streaming kernel with the epilogue the call asks for, or NotImplemented."""
+        w = self.weight
+        if deferred:
+            if not kernels.gemm_skinny_norm_supports(x.x, w):
+                return NotImplemented
+        elif not kernels.gemm_skinny_supports(x, w):
+            return NotImplemented
+        m = x.shape[0]
+        if residual is not None and self.bias is None:
+            epilogue, out, result = kernels.SKINNY_RESIDUAL, residual, None
+        elif out_dtype == torch.float32:
+            if self.bias is not None:
+                return NotImplemented
+            out = torch.empty((m, self.out_features), dtype=torch.float32, device=x.device)
+            epilogue, result = kernels.SKINNY_F32, out
+        else:
+            out = torch.empty((m, self.out_features), dtype=w.dtype, device=x.device)
+            epilogue, result = (kernels.SKINNY_BIAS if self.bias is not None else kernels.SKINNY_STORE), out
+        if deferred:
+            kernels.gemm_skinny_norm(x.x, x.weight, x.eps, w, self.bias, out, epilogue)
+        else:
+            kernels.gemm_skinny(x, w, self.bias, out, epilogue)
+        return result

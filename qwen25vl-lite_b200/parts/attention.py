@@ -62,11 +62,15 @@ class GQAAttention(Mixer):
         ob = tensors["o_proj.bias"].to(device=device, dtype=torch.float32).contiguous() if self.out_bias else None
         self.o_proj = Linear(tensors["o_proj.weight"].to(device=device, dtype=dtype).contiguous(), ob)
 
-    def forward(self, ctx, h, stop):
+    accepts_deferred_norm = True     # forward takes a DeferredNorm as its input
+    accepts_residual = True          # forward can add its result into the residual stream itself
+
+    def forward(self, ctx, h, stop, residual=None):
+        """Returns the update of the residual stream, or None after adding it into ``residual``."""
         qkv = self.qkv_proj(h)
         kv = ctx.kv(stop)
         self.position.rotate_and_store(ctx, qkv, self.num_heads, self.num_kv_heads, self.head_dim,
                                        kv if stop.owns_cache else None)
         out = attention_ops.paged_attention(ctx, qkv, kv, self.num_heads, self.num_kv_heads, self.head_dim,
                                             self.window, self.scale)
-        return self.o_proj(out)
+        return self.o_proj(out, residual=residual)

@@ -63,7 +63,7 @@ class Norm(Part):
     activation dtype.  With ``rows`` (int32 indices) only those rows are produced and x is
     left untouched."""
 
-    def forward(self, ctx, x, delta, rows=None):
+    def forward(self, ctx, x, delta, rows=None, defer=False):
         raise NotImplementedError
 
 
@@ -89,7 +89,11 @@ class PositionEncoding(Part):
 class Mixer(Part):
     """The token-mixing part of a layer.
 
-    ``forward(ctx, h, stop) -> [N, H]`` in the activation dtype.  ``stop`` is the runtime
+    ``forward(ctx, h, stop) -> [N, H]`` in the activation dtype.  Two optional capabilities a
+    mixer (or feed-forward) may declare as class attributes: ``accepts_residual`` -- forward
+    takes ``residual=`` (the float32 stream) and may add its result into it, returning None;
+    ``accepts_deferred_norm`` -- ``h`` may be an ``ops.linear.DeferredNorm`` to be normalised
+    inside the part's first product.  ``stop`` is the runtime
     record of the schedule stop being run (``engine.runner.StopRuntime``): ``stop.kv`` gives
     the pages of this stop (or of the stop whose cache it reads) with ``stop.owns_cache``
     telling whether to write this step's keys and values; ``stop.state`` is the fixed-size

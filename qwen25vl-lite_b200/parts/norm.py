@@ -9,6 +9,7 @@ from __future__ import annotations
 import torch
 
 from ..ops import kernels
+from ..ops.linear import DeferredNorm
 from .base import Norm, TensorSpec, register_norm
 
 
@@ -25,7 +26,13 @@ class RMSNorm(Norm):
     def load(self, tensors, device, dtype):
         self.weight = tensors["weight"].to(device=device, dtype=torch.float32).contiguous()
 
-    def forward(self, ctx, x, delta, rows=None):
+    def forward(self, ctx, x, delta, rows=None, defer=False):
+        """``defer``: the caller's consumer can normalise inside its own kernel; when nothing
+        has to be added first and the step is small enough for that kernel, no kernel is
+        launched here and a ``DeferredNorm`` is returned instead of the activation."""
+        if (defer and delta is None and rows is None and ctx.dtype == torch.bfloat16
+                and x.shape[0] <= kernels.SKINNY_MAX_ROWS):
+            return DeferredNorm(x, self.weight, self.eps, ctx.dtype)
         n_out = x.shape[0] if rows is None else rows.shape[0]
         out = torch.empty((n_out, self.dim), dtype=ctx.dtype, device=x.device)
         kernels.add_rmsnorm(x, delta, self.weight, self.eps, out, rows)

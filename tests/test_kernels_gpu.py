@@ -400,3 +400,47 @@ def test_sample_rows_large_vocabulary():
         u = ((x >> np.uint64(41)).astype(np.float64) + 0.5) / 8388608.0
         g = -np.log(-np.log(u.astype(np.float32), dtype=np.float32), dtype=np.float32)
         assert got[r] == int(np.argmax(logits[r] / temps[r] + g))
+
+
+@pytest.mark.parametrize("m", [1, 7, 8, 16])
+@pytest.mark.parametrize("n,k", [(2560, 2048), (96, 64), (4752, 256), (1024, 3584)])
+def test_gemm_skinny_with_norm_inside_and_residual_epilogue(m, n, k):
+    """The product that normalises its float32 input inside the kernel, and the epilogue that
+    adds into the float32 residual stream."""
+    from qwen25vl_lite.ops import kernels
+    rng = np.random.default_rng(m * 77 + k)
+    x = dev(rng.standard_normal((m, k)) * 3, torch.float32)
+    nw = dev(1 + 0.1 * rng.standard_normal(k), torch.float32)
+    w = dev(rng.standard_normal((n, k)) * 0.05, torch.bfloat16)
+    bias = dev(rng.standard_normal(n), torch.float32)
+    assert kernels.gemm_skinny_norm_supports(x, w)
+    h = plain.rms_norm(f64(x), f64(nw), 1e-5)
+    ref = h @ f64(w).T
+    scale = max(1.0, np.abs(ref).max())
+    out = torch.empty((m, n), dtype=torch.bfloat16, device="cuda")
+    kernels.gemm_skinny_norm(x, nw, 1e-5, w, bias, out, kernels.SKINNY_BIAS)
+    assert np.abs(f64(out) - (ref + f64(bias))).max() / scale < 1.5e-2       # h is rounded to bfloat16 inside
+    if n % 16 == 0:
+        act = torch.empty((m, n // 2), dtype=torch.bfloat16, device="cuda")
+        kernels.gemm_skinny_norm(x, nw, 1e-5, w, None, act, kernels.SKINNY_SWIGLU)
+        pairs = ref.reshape(m, n // 16, 2, 8)
+        want = (plain.silu(pairs[:, :, 0]) * pairs[:, :, 1]).reshape(m, n // 2)
+        assert np.abs(f64(act) - want).max() / max(1.0, np.abs(want).max()) < 2e-2
+    # residual epilogue: stream += a . w^T, in float32
+    a = dev(rng.standard_normal((m, k)), torch.bfloat16)
+    stream0 = rng.standard_normal((m, n)) * 5
+    stream = dev(stream0, torch.float32)
+    kernels.gemm_skinny(a, w, None, stream, kernels.SKINNY_RESIDUAL)
+    want = f64(dev(stream0, torch.float32)) + f64(a) @ f64(w).T
+    assert np.abs(f64(stream) - want).max() / max(1.0, np.abs(want).max()) < 1e-5
+    assert int(kernels.error_flag("cuda:0")[0]) == 0
+
+
+def test_gemm_skinny_norm_needs_resident_rows():
+    from qwen25vl_lite.ops import kernels
+    x = torch.zeros((16, 11008), dtype=torch.float32, device="cuda")      # 16 rows of 11008 do not fit beside the ring
+    w = torch.zeros((32, 11008), dtype=torch.bfloat16, device="cuda")
+    assert not kernels.gemm_skinny_norm_supports(x, w)
+    with pytest.raises(kernels.KernelError):
+        kernels.gemm_skinny_norm(x, torch.ones(11008, device="cuda"), 1e-6, w, None,
+                                 torch.empty((16, 32), dtype=torch.bfloat16, device="cuda"), kernels.SKINNY_STORE)
