@@ -19,7 +19,11 @@
 //            edge are skipped.
 // Head sizes: multiples of 16 up to 128.  Page sizes: powers of two.  Other sizes take the general
 // kernel.
+#include <cooperative_groups.h>
+
 #include "common.cuh"
+
+namespace cg = cooperative_groups;
 
 #define ATTN_THREADS 128
 #define DEC_BN 32
@@ -438,6 +442,237 @@ __global__ void __launch_bounds__(ATTN_THREADS) attention_prefill_kernel(AttnArg
 }
 
 // ------------------------------------------------------------------------------------------------
+// decode, fused: position encoding of q and k, the write of the new key and value into the pages,
+// the attention and the merge of the splits in one kernel.  The splits of an (entry, kv head) pair
+// form a thread-block cluster (at most 8 CTAs); they leave their partial results in their own
+// shared memory and the first CTA of the cluster reads them through distributed shared memory.
+// The CTA whose range holds the token's own key rotates that key, patches it (and the value) into
+// the tile in shared memory and stores both to the pages for later steps, so no kernel has to
+// run before this one.  Rotation as in rope_cache.cu (reference src/qwen25vl_lite/rope.py:48-96).
+// ------------------------------------------------------------------------------------------------
+struct RopeArgs {
+  const int* positions;   // [axes, n_tokens]
+  int n_tokens;
+  const float* inv_freq;  // [D/2]
+  const int* axis;        // [D/2]
+  const int* kv_slot;     // [n_tokens]: page * page_size + offset of each token's key
+  bf16* kpages_w;
+  bf16* vpages_w;
+};
+
+__device__ __forceinline__ unsigned rotate_pair_lo(unsigned x1, unsigned x2, float c0, float s0, float c1, float s1) {
+  const __nv_bfloat162 a = *reinterpret_cast<__nv_bfloat162*>(&x1), b = *reinterpret_cast<__nv_bfloat162*>(&x2);
+  return pack_bf16(__low2float(a) * c0 - __low2float(b) * s0, __high2float(a) * c1 - __high2float(b) * s1);
+}
+__device__ __forceinline__ unsigned rotate_pair_hi(unsigned x1, unsigned x2, float c0, float s0, float c1, float s1) {
+  const __nv_bfloat162 a = *reinterpret_cast<__nv_bfloat162*>(&x1), b = *reinterpret_cast<__nv_bfloat162*>(&x2);
+  return pack_bf16(__low2float(b) * c0 + __low2float(a) * s0, __high2float(b) * c1 + __high2float(a) * s1);
+}
+
+template <int D>
+__global__ void __launch_bounds__(ATTN_THREADS) attention_decode_fused_kernel(AttnArgs a, RopeArgs r) {
+  static_assert(D % 32 == 0, "the rotation pairs channel j with j + D/2 inside one thread");
+  extern __shared__ __align__(16) unsigned char smem[];
+  constexpr int P = Tile<D>::PITCH;
+  constexpr int TILE = DEC_BN * P;
+  constexpr int HALF = D / 2;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+  const int item = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z;
+  const int seq = a.items[item];
+  const int G = a.nq / a.nkv;
+  const int token = a.cu_q[seq];
+  const int p = a.q_start_pos[seq];
+  const int lo = a.window > 0 ? max(0, p - a.window + 1) : 0;
+  const int first_tile_key = lo & ~(DEC_BN - 1);
+  const int n_tiles = (p - first_tile_key) / DEC_BN + 1;
+  const int per_split = (n_tiles + a.n_splits - 1) / a.n_splits;
+  const int t_begin = split * per_split, t_end = min(n_tiles, t_begin + per_split);
+  const int* table = a.block_table + (size_t)seq * a.table_width;
+
+  // start the first tile's copies before the position-encoding arithmetic
+  unsigned char* wbuf = smem + (size_t)warp * 4 * TILE;
+  int tile = t_begin + warp;
+  if (tile < t_end) load_kv_tile<D, DEC_BN>(wbuf, wbuf + TILE, a, table, kvh, first_tile_key + tile * DEC_BN, p, lane, 32);
+  cp_async_commit();
+
+  // q of the group's heads, rotated in registers: channels j and j + D/2 sit in k-steps ks and
+  // ks + D/32 of the same thread
+  unsigned qf[D / 16][4];
+  const bf16* qbase = a.qkv + (size_t)token * a.qkv_stride + (size_t)kvh * G * D;
+  load_q<D>(qf, [&](int row) { return row < G ? qbase + (size_t)row * D : (const bf16*)nullptr; });
+  const float pos0 = (float)r.positions[token], pos1 = (float)r.positions[(size_t)r.n_tokens + token],
+              pos2 = (float)r.positions[(size_t)2 * r.n_tokens + token];
+  auto angle = [&](int j) {
+    const int ax = r.axis[j];
+    return (ax == 0 ? pos0 : (ax == 1 ? pos1 : pos2)) * r.inv_freq[j];
+  };
+#pragma unroll
+  for (int ks = 0; ks < D / 32; ++ks) {
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {       // registers 0,1 (columns 2t, 2t+1) and 2,3 (columns 2t+8, 2t+9)
+      const int j = ks * 16 + 2 * t + 8 * half;
+      float s0, c0, s1, c1;
+      sincosf(angle(j), &s0, &c0);
+      sincosf(angle(j + 1), &s1, &c1);
+#pragma unroll
+      for (int row = 0; row < 2; ++row) {         // rows g and g + 8
+        const unsigned x1 = qf[ks][2 * half + row], x2 = qf[ks + D / 32][2 * half + row];
+        qf[ks][2 * half + row] = rotate_pair_lo(x1, x2, c0, s0, c1, s1);
+        qf[ks + D / 32][2 * half + row] = rotate_pair_hi(x1, x2, c0, s0, c1, s1);
+      }
+    }
+  }
+
+  float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+  float o[D / 8][4];
+#pragma unroll
+  for (int nb = 0; nb < D / 8; ++nb) o[nb][0] = o[nb][1] = o[nb][2] = o[nb][3] = 0.f;
+
+  int stage = 0;
+  for (; tile < t_end; tile += 4) {
+    const int next = tile + 4;
+    if (next < t_end) {
+      unsigned char* nb = wbuf + (size_t)(stage ^ 1) * 2 * TILE;
+      load_kv_tile<D, DEC_BN>(nb, nb + TILE, a, table, kvh, first_tile_key + next * DEC_BN, p, lane, 32);
+    }
+    cp_async_commit();
+    cp_async_wait<1>();
+    __syncwarp();
+    const int key0 = first_tile_key + tile * DEC_BN;
+    unsigned char* cb = wbuf + (size_t)stage * 2 * TILE;
+    if (tile == n_tiles - 1) {
+      // the token's own key and value: rotate k, patch both into the tile, store both to the pages
+      const bf16* kv_new = a.qkv + (size_t)token * a.qkv_stride + (size_t)(a.nq + kvh) * D;
+      const bf16* v_new = kv_new + (size_t)a.nkv * D;
+      const int slot = r.kv_slot[token];
+      const size_t page_off = slot >= 0 ? ((((size_t)(slot >> a.page_shift) * a.nkv + kvh) << a.page_shift)
+                                           + (slot & ((1 << a.page_shift) - 1))) * D : 0;
+      bf16* krow = reinterpret_cast<bf16*>(cb + (p - key0) * P);
+      bf16* vrow = reinterpret_cast<bf16*>(cb + TILE + (p - key0) * P);
+      for (int j = lane; j < HALF; j += 32) {
+        float sn, cs;
+        sincosf(angle(j), &sn, &cs);
+        const float x1 = __bfloat162float(kv_new[j]), x2 = __bfloat162float(kv_new[j + HALF]);
+        const bf16 y1 = __float2bfloat16_rn(x1 * cs - x2 * sn), y2 = __float2bfloat16_rn(x2 * cs + x1 * sn);
+        krow[j] = y1;
+        krow[j + HALF] = y2;
+        if (slot >= 0) {
+          r.kpages_w[page_off + j] = y1;
+          r.kpages_w[page_off + j + HALF] = y2;
+        }
+      }
+      for (int c = lane; c < D; c += 32) {
+        const bf16 v = v_new[c];
+        vrow[c] = v;
+        if (slot >= 0) r.vpages_w[page_off + c] = v;
+      }
+      __syncwarp();
+    }
+    const bool need_mask = key0 < lo || key0 + DEC_BN - 1 > p;
+    attend_tile<D, DEC_BN>(qf, cb, cb + TILE, key0, lo, p, lo, p, need_mask, a.scale_log2, m, l, o);
+    __syncwarp();
+    stage ^= 1;
+  }
+  cp_async_wait<0>();
+  l[0] = quad_sum(l[0]);
+  l[1] = quad_sum(l[1]);
+
+  // merge the 4 warps of the CTA (as in attention_decode_kernel), keep the result in shared memory
+  __syncthreads();
+  float* ml = reinterpret_cast<float*>(smem);                 // [4 warps][16 rows][2]
+  float* slab = ml + 4 * 16 * 2;                              // [4 warps][16 rows][D]
+  float* cta_ml = slab + 4 * 16 * D;                          // [16 rows][2]: this CTA's merged maximum and sum
+  float* cta_o = cta_ml + 16 * 2;                             // [16 rows][D]
+  if (t == 0) {
+    ml[(warp * 16 + g) * 2] = m[0];
+    ml[(warp * 16 + g) * 2 + 1] = l[0];
+    ml[(warp * 16 + g + 8) * 2] = m[1];
+    ml[(warp * 16 + g + 8) * 2 + 1] = l[1];
+  }
+  __syncthreads();
+  float f[2];
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    const int row = g + 8 * h;
+    float mm = -INFINITY;
+    for (int w = 0; w < 4; ++w) mm = fmaxf(mm, ml[(w * 16 + row) * 2]);
+    f[h] = (m[h] == -INFINITY) ? 0.f : exp2f(m[h] - mm);
+  }
+#pragma unroll
+  for (int nb = 0; nb < D / 8; ++nb) {
+    float* r0 = slab + ((size_t)warp * 16 + g) * D + nb * 8 + 2 * t;
+    float* r1 = slab + ((size_t)warp * 16 + g + 8) * D + nb * 8 + 2 * t;
+    r0[0] = o[nb][0] * f[0];
+    r0[1] = o[nb][1] * f[0];
+    r1[0] = o[nb][2] * f[1];
+    r1[1] = o[nb][3] * f[1];
+  }
+  __syncthreads();
+  for (int idx = threadIdx.x; idx < G * D; idx += ATTN_THREADS) {
+    const int row = idx / D, c = idx - row * D;
+    float mm = -INFINITY;
+    for (int w = 0; w < 4; ++w) mm = fmaxf(mm, ml[(w * 16 + row) * 2]);
+    float lsum = 0.f, acc = 0.f;
+    for (int w = 0; w < 4; ++w) {
+      const float mw = ml[(w * 16 + row) * 2];
+      lsum += mw == -INFINITY ? 0.f : ml[(w * 16 + row) * 2 + 1] * exp2f(mw - mm);
+      acc += slab[((size_t)w * 16 + row) * D + c];
+    }
+    cta_o[row * D + c] = acc;
+    if (c == 0) {
+      cta_ml[row * 2] = mm;
+      cta_ml[row * 2 + 1] = lsum;
+    }
+  }
+
+  // merge the splits: the first CTA of the cluster reads the others' results
+  cg::cluster_group cluster = cg::this_cluster();
+  cluster.sync();
+  if (cluster.block_rank() == 0) {
+    const int n = (int)cluster.num_blocks();
+    for (int idx = threadIdx.x; idx < G * D; idx += ATTN_THREADS) {
+      const int row = idx / D, c = idx - row * D;
+      float M = -INFINITY;
+      for (int k = 0; k < n; ++k) M = fmaxf(M, cluster.map_shared_rank(cta_ml, k)[row * 2]);
+      float lsum = 0.f, acc = 0.f;
+      for (int k = 0; k < n; ++k) {
+        const float* rml = cluster.map_shared_rank(cta_ml, k);
+        const float mk = rml[row * 2];
+        if (mk == -INFINITY) continue;
+        const float wgt = exp2f(mk - M);
+        lsum += rml[row * 2 + 1] * wgt;
+        acc += cluster.map_shared_rank(cta_o, k)[row * D + c] * wgt;
+      }
+      a.out[(size_t)token * a.nq * D + (size_t)(kvh * G + row) * D + c] = __float2bfloat16_rn(acc / lsum);
+    }
+  }
+  cluster.sync();   // nobody's shared memory goes away while the first CTA still reads it
+}
+
+template <int D>
+static int launch_decode_fused(const AttnArgs& a, const RopeArgs& r, int n_items, cudaStream_t s) {
+  constexpr size_t kv = (size_t)4 * 4 * DEC_BN * Tile<D>::PITCH;
+  constexpr size_t merge = (size_t)(4 * 16 * 2 + 4 * 16 * D + 16 * 2 + 16 * D) * sizeof(float);
+  constexpr size_t smem = kv > merge ? kv : merge;
+  cudaError_t e = cudaFuncSetAttribute(attention_decode_fused_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (e != cudaSuccess) return (int)e;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(n_items, a.nkv, a.n_splits);
+  cfg.blockDim = dim3(ATTN_THREADS);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = s;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 1;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = a.n_splits;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  e = cudaLaunchKernelEx(&cfg, attention_decode_fused_kernel<D>, a, r);
+  return e != cudaSuccess ? (int)e : launch_status();
+}
+
+// ------------------------------------------------------------------------------------------------
 template <int D>
 static int launch_decode(const AttnArgs& a, int n_items, cudaStream_t s) {
   constexpr size_t kv = (size_t)4 * 4 * DEC_BN * Tile<D>::PITCH;                       // 4 warps x 2 stages x (K,V)
@@ -521,6 +756,35 @@ Q25_EXPORT int q25_attention_prefill_bf16(const void* qkv, int qkv_stride, void*
   if (e) return e;
   cudaStream_t s = (cudaStream_t)stream;
   DISPATCH_D(launch_prefill, a, n_tiles, s)
+}
+
+// Fused decode step of attention: rotates q and the new k by the 3-axis rotary encoding, stores the new
+// k and v at kv_slot, attends, merges the n_splits <= 8 key ranges inside a cluster.  qkv holds the
+// un-rotated projections and is not modified.  Head sizes 32, 64, 96, 128; groups of at most 16.
+Q25_EXPORT int q25_attention_decode_fused_bf16(const void* qkv, int qkv_stride, void* out, void* kp, void* vp,
+                                               const int* bt, int tw, const int* cu_q, const int* q_start,
+                                               const int* items, int n_items, int nq, int nkv, int d, int page_size,
+                                               int window, float scale, int n_splits, const int* positions,
+                                               int n_tokens, const float* inv_freq, const int* axis,
+                                               const int* kv_slot, void* stream) {
+  if (n_items <= 0) return 0;
+  AttnArgs a;
+  int e = fill_args(a, qkv, qkv_stride, out, kp, vp, bt, tw, cu_q, q_start, items, nq, nkv, page_size, window, scale);
+  if (e) return e;
+  if (nq / nkv > 16 || n_splits < 1 || n_splits > 8 || !positions || !inv_freq || !axis || !kv_slot)
+    return (int)cudaErrorInvalidValue;
+  a.n_splits = n_splits;
+  RopeArgs r;
+  r.positions = positions; r.n_tokens = n_tokens; r.inv_freq = inv_freq; r.axis = axis; r.kv_slot = kv_slot;
+  r.kpages_w = (bf16*)kp; r.vpages_w = (bf16*)vp;
+  cudaStream_t s = (cudaStream_t)stream;
+  switch (d) {
+    case 32: return launch_decode_fused<32>(a, r, n_items, s);
+    case 64: return launch_decode_fused<64>(a, r, n_items, s);
+    case 96: return launch_decode_fused<96>(a, r, n_items, s);
+    case 128: return launch_decode_fused<128>(a, r, n_items, s);
+    default: return (int)cudaErrorInvalidValue;
+  }
 }
 
 // ------------------------------------------------------------------------------------------------

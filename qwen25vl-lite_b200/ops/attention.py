@@ -1,9 +1,16 @@
-"""Choice of the attention kernel for a step.
+"""Choice of the attention kernels for a step.
 
 bfloat16 with a head size and page size the tensor-core kernels take (``csrc/attention_mma.cu``):
-entries that bring one token go to the split-KV decode kernel, runs of tokens to the
-prefill kernel.  Everything else (float32, other sizes) goes to the general kernel
-(``csrc/attention_generic.cu``).
+
+* a step in which every entry brings one token, with a rotary position encoding that can hand
+  out its tables: one fused kernel rotates q and the new k, writes the new k and v into the
+  pages, attends, and merges its key ranges inside a thread-block cluster;
+* otherwise the position encoding runs first (``rotate_and_store``), then entries that bring one
+  token go to the split-KV decode kernel (partials through scratch memory and a combine
+  kernel) and runs of tokens to the prefill kernel.
+
+Everything else (float32, other sizes) goes to the general kernel
+(``csrc/attention_generic.cu``) after ``rotate_and_store``.
 """
 
 from __future__ import annotations
@@ -16,12 +23,12 @@ SM_COUNT = 148
 _scratch = {}
 
 
-def decode_splits(n_items: int, nkv: int, max_kv_len: int) -> int:
+def decode_splits(n_items: int, nkv: int, max_kv_len: int, most: int = 64) -> int:
     """Into how many key ranges a decode entry is cut: enough CTAs for two per SM, but at
     least 256 keys (two 32-key tiles per warp) in each."""
     by_work = max(1, -(-max_kv_len // 256))
     by_sms = max(1, (2 * SM_COUNT) // max(1, n_items * nkv))
-    return int(min(by_work, by_sms, 64))
+    return int(min(by_work, by_sms, most))
 
 
 def _scratch_floats(n: int, device) -> torch.Tensor:
@@ -33,9 +40,31 @@ def _scratch_floats(n: int, device) -> torch.Tensor:
     return buf
 
 
+def attend(ctx, qkv, kv, position, nq: int, nkv: int, head_dim: int, window, scale: float, store: bool) -> torch.Tensor:
+    """Position-encodes q and k, writes this step's k and v into the pages (``store``), and
+    attends.  qkv: [N, (nq + 2 nkv) * D] as projected; kv: the stop's pages, slots and block
+    table for this step.  Returns [N, nq * D]."""
+    window = int(window or 0)
+    group = nq // nkv
+    tables = getattr(position, "rope_tables", None)
+    if (store and tables is not None and ctx.decode_items is not None and ctx.decode_items.shape[0] == ctx.n_seqs
+            and ctx.prefill_tiles.get(group, 0) is None
+            and kernels.attention_fused_supports(qkv.dtype, head_dim, kv.page_size, group)):
+        inv_freq, axis = tables()
+        out = torch.empty((qkv.shape[0], nq * head_dim), dtype=qkv.dtype, device=qkv.device)
+        visible = min(ctx.max_kv_len, window) if window else ctx.max_kv_len
+        splits = decode_splits(ctx.n_seqs, nkv, visible, most=8)
+        kernels.attention_decode_fused(qkv, out, kv.k_pages, kv.v_pages, kv.block_table, ctx.cu_q, ctx.q_start_pos,
+                                       ctx.decode_items, nq, nkv, head_dim, kv.page_size, window, scale, splits,
+                                       ctx.positions, inv_freq, axis, kv.kv_slot)
+        return out
+    position.rotate_and_store(ctx, qkv, nq, nkv, head_dim, kv if store else None)
+    return paged_attention(ctx, qkv, kv, nq, nkv, head_dim, window, scale)
+
+
 def paged_attention(ctx, qkv, kv, nq: int, nkv: int, head_dim: int, window, scale: float) -> torch.Tensor:
-    """qkv: [N, (nq + 2 nkv) * D] with q already position-encoded; kv: the stop's pages and
-    block table for this step.  Returns [N, nq * D]."""
+    """qkv: [N, (nq + 2 nkv) * D] with q already position-encoded and this step's keys and
+    values already in the pages.  Returns [N, nq * D]."""
     out = torch.empty((qkv.shape[0], nq * head_dim), dtype=qkv.dtype, device=qkv.device)
     window = int(window or 0)
     group = nq // nkv

@@ -206,6 +206,32 @@ def attention_decode(qkv: torch.Tensor, out: torch.Tensor, k_pages: torch.Tensor
         page_size, int(window or 0), float(scale), int(n_splits), _ptr(scratch), _stream()), "attention_decode")
 
 
+def attention_fused_supports(dtype: torch.dtype, head_dim: int, page_size: int, group: int) -> bool:
+    return attention_mma_supports(dtype, head_dim, page_size) and head_dim % 32 == 0 and group <= 16
+
+
+def attention_decode_fused(qkv: torch.Tensor, out: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor,
+                           block_table: torch.Tensor, cu_q: torch.Tensor, q_start_pos: torch.Tensor, items: torch.Tensor,
+                           nq: int, nkv: int, head_dim: int, page_size: int, window: int, scale: float, n_splits: int,
+                           positions: torch.Tensor, inv_freq: torch.Tensor, axis: torch.Tensor,
+                           kv_slot: torch.Tensor) -> None:
+    """One kernel for a step of one-token entries: 3-axis rotary encoding of q and the new k
+    (``positions`` int32 [3, N], ``inv_freq`` float32 [D/2], ``axis`` int32 [D/2]), the write of
+    the new k and v at ``kv_slot``, attention, and the merge of ``n_splits`` <= 8 key ranges
+    inside a thread-block cluster.  ``qkv`` is read as projected and left unchanged."""
+    if not attention_fused_supports(qkv.dtype, head_dim, page_size, nq // nkv) or not 1 <= n_splits <= 8:
+        raise KernelError(f"attention_decode_fused: unsupported head size {head_dim}, page size {page_size}, "
+                          f"group {nq // nkv} or splits {n_splits}")
+    if positions.dtype != torch.int32 or positions.dim() != 2 or positions.shape[0] != 3:
+        raise KernelError("attention_decode_fused: positions must be int32 [3, N]")
+    _check(_fn("q25_attention_decode_fused_bf16",
+               [_P, _I, _P, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _I, _P, _I, _P, _P, _P, _P])(
+        qkv.data_ptr(), qkv.stride(0), out.data_ptr(), k_pages.data_ptr(), v_pages.data_ptr(), block_table.data_ptr(),
+        block_table.shape[1], cu_q.data_ptr(), q_start_pos.data_ptr(), items.data_ptr(), items.shape[0], nq, nkv,
+        head_dim, page_size, int(window or 0), float(scale), int(n_splits), positions.data_ptr(), positions.shape[1],
+        inv_freq.data_ptr(), axis.data_ptr(), kv_slot.data_ptr(), _stream()), "attention_decode_fused")
+
+
 def attention_prefill(qkv: torch.Tensor, out: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor,
                       block_table: torch.Tensor, cu_q: torch.Tensor, q_start_pos: torch.Tensor, tiles: torch.Tensor,
                       nq: int, nkv: int, head_dim: int, page_size: int, window: int, scale: float) -> None:

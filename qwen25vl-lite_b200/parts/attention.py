@@ -68,9 +68,6 @@ class GQAAttention(Mixer):
     def forward(self, ctx, h, stop, residual=None):
         """Returns the update of the residual stream, or None after adding it into ``residual``."""
         qkv = self.qkv_proj(h)
-        kv = ctx.kv(stop)
-        self.position.rotate_and_store(ctx, qkv, self.num_heads, self.num_kv_heads, self.head_dim,
-                                       kv if stop.owns_cache else None)
-        out = attention_ops.paged_attention(ctx, qkv, kv, self.num_heads, self.num_kv_heads, self.head_dim,
-                                            self.window, self.scale)
+        out = attention_ops.attend(ctx, qkv, ctx.kv(stop), self.position, self.num_heads, self.num_kv_heads,
+                                   self.head_dim, self.window, self.scale, stop.owns_cache)
         return self.o_proj(out, residual=residual)

@@ -75,6 +75,8 @@ class PositionEncoding(Part):
     starting at index ``start`` of a request whose per-request offset is ``offset``
     -> int array [axes, count].
     ``rotate_and_store(ctx, qkv, ...)``: encode q and k in place and write k, v to the pages.
+    Optional ``rope_tables() -> (inv_freq, axis)``: a 3-axis rotary encoding that lets the fused
+    decode attention kernel do the rotation itself.
     """
 
     axes = 1

@@ -74,6 +74,10 @@ class MRope(PositionEncoding):
         run = np.arange(start + offset, start + offset + count, dtype=np.int64)
         return np.broadcast_to(run, (self.axes, count))
 
+    def rope_tables(self):
+        """(inv_freq float32 [D/2], axis int32 [D/2]) for kernels that rotate by themselves."""
+        return self.inv_freq, self.axis
+
     def rotate_and_store(self, ctx, qkv, nq, nkv, head_dim, kv):
         """kv: the pages and slots of the stop's cache group, or None to store nothing."""
         if head_dim != self.head_dim:

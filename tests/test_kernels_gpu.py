@@ -403,7 +403,7 @@ def test_sample_rows_large_vocabulary():
 
 
 @pytest.mark.parametrize("m", [1, 7, 8, 16])
-@pytest.mark.parametrize("n,k", [(2560, 2048), (96, 64), (4752, 256), (1024, 3584)])
+@pytest.mark.parametrize("n,k", [(2560, 2048), (96, 64), (4752, 256), (1024, 3072)])
 def test_gemm_skinny_with_norm_inside_and_residual_epilogue(m, n, k):
     """The product that normalises its float32 input inside the kernel, and the epilogue that
     adds into the float32 residual stream."""
@@ -444,3 +444,56 @@ def test_gemm_skinny_norm_needs_resident_rows():
     with pytest.raises(kernels.KernelError):
         kernels.gemm_skinny_norm(x, torch.ones(11008, device="cuda"), 1e-6, w, None,
                                  torch.empty((16, 32), dtype=torch.bfloat16, device="cuda"), kernels.SKINNY_STORE)
+
+
+@pytest.mark.parametrize("splits", [1, 2, 5, 8])
+@pytest.mark.parametrize("nq,nkv,d,section,page_size,window", [
+    (16, 2, 128, (16, 24, 24), 16, None), (6, 1, 32, (4, 6, 6), 8, None), (8, 2, 64, (8, 12, 12), 16, 70),
+    (12, 4, 96, (16, 16, 16), 4, None), (3, 3, 64, (10, 11, 11), 32, 33)])
+def test_attention_decode_fused(nq, nkv, d, section, page_size, window, splits):
+    """The one-kernel decode step of attention: rotary encoding of q and the new k inside the
+    kernel, the new k and v written to their page slot, cluster merge of the splits."""
+    from qwen25vl_lite.ops import kernels
+    from qwen25vl_lite.parts.position import MRope
+    rng = np.random.default_rng(12)
+    lens = [1, 33, 130, 64, 290, 31, 600]
+    c = paged_case(rng, lens, [1] * len(lens), nq, nkv, d, page_size, torch.bfloat16)
+    n = len(lens)
+    theta = 10000.0
+    rope = MRope(d, theta, section)
+    rope.load({}, "cuda", torch.bfloat16)
+    positions = rng.integers(0, 2000, size=(3, n))
+    cos, sin = plain.mrope_cos_sin(positions, d, theta, section, np.float64)
+    k_raw = torch.as_tensor(rng.standard_normal((n, nkv, d))).to(torch.bfloat16)
+    v_raw = torch.as_tensor(rng.standard_normal((n, nkv, d))).to(torch.bfloat16)
+    qkv = c["qkv"].clone()
+    qkv[:, nq * d:(nq + nkv) * d] = k_raw.reshape(n, -1).cuda()
+    qkv[:, (nq + nkv) * d:] = v_raw.reshape(n, -1).cuda()
+    q_raw = f64(qkv[:, :nq * d]).reshape(n, nq, d)
+    q_rot = plain.apply_mrope(q_raw, cos, sin)
+    k_rot = plain.apply_mrope(f64(k_raw), cos, sin)
+    table = c["table"].cpu().numpy()
+    slots, dense = [], []
+    for i, L in enumerate(lens):
+        page = int(table[i, (L - 1) // page_size])
+        slots.append(page * page_size + (L - 1) % page_size)
+        c["k_pages"][page, :, (L - 1) % page_size] = 0          # the new token's slot is still empty
+        c["v_pages"][page, :, (L - 1) % page_size] = 0
+        _, k, v = c["dense"][i]
+        k, v = k.clone(), v.clone()
+        k[L - 1] = torch.as_tensor(k_rot[i]).to(torch.bfloat16)
+        v[L - 1] = v_raw[i]
+        dense.append((torch.as_tensor(q_rot[i:i + 1]).to(torch.bfloat16), k, v))
+    out = torch.zeros((n, nq * d), dtype=torch.bfloat16, device="cuda")
+    qkv_before = qkv.clone()
+    kernels.attention_decode_fused(qkv, out, c["k_pages"], c["v_pages"], c["table"], c["cu"], c["start"],
+                                   dev(np.arange(n, dtype=np.int32)), nq, nkv, d, page_size, window or 0, d ** -0.5,
+                                   splits, dev(positions.astype(np.int32)), rope.inv_freq, rope.axis,
+                                   dev(np.asarray(slots, np.int32)))
+    assert torch.equal(qkv, qkv_before)                          # the projections are left as they were
+    ref = attention_oracle(dense, window)
+    assert np.abs(f64(out) - ref).max() < 4e-2
+    kp, vp = f64(c["k_pages"]), f64(c["v_pages"])
+    for i, s in enumerate(slots):                                # the new key and value are in the pages now
+        assert np.abs(kp[s // page_size, :, s % page_size] - k_rot[i]).max() < 4e-2
+        assert np.array_equal(vp[s // page_size, :, s % page_size], f64(v_raw[i]))
