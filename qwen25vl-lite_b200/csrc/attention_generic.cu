@@ -24,6 +24,8 @@ __global__ void paged_attention_generic_kernel(
     const T* __restrict__ vpages, const int* __restrict__ block_table, int table_width,
     const int* __restrict__ token_seq, const int* __restrict__ cu_q, const int* __restrict__ q_start_pos,
     int n_tokens, int nq, int nkv, int d, int page_size, int window, float scale) {
+  pdl_trigger();
+  pdl_wait();
   extern __shared__ __align__(16) unsigned char att_smem[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   // per warp: q (d floats), probabilities (32 floats), V row offsets (32 x size_t)
@@ -105,7 +107,7 @@ static int paged_attention_generic(const void* qkv, int qkv_stride, void* out, c
   const long long items = (long long)n_tokens * nq;
   const unsigned blocks = (unsigned)((items + ATT_WARPS - 1) / ATT_WARPS);
   const size_t smem = ATT_WARPS * ((size_t)(d + 32) * sizeof(float) + 32 * sizeof(size_t));
-  paged_attention_generic_kernel<T><<<blocks, ATT_WARPS * 32, smem, (cudaStream_t)stream>>>(
+  launch(paged_attention_generic_kernel<T>, dim3(blocks), dim3(ATT_WARPS * 32), smem, (cudaStream_t)stream, 
       (const T*)qkv, qkv_stride, (T*)out, (const T*)kpages, (const T*)vpages, block_table, table_width, token_seq,
       cu_q, q_start_pos, n_tokens, nq, nkv, d, page_size, window, scale);
   return launch_status();

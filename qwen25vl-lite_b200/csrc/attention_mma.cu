@@ -19,11 +19,7 @@
 //            edge are skipped.
 // Head sizes: multiples of 16 up to 128.  Page sizes: powers of two.  Other sizes take the general
 // kernel.
-#include <cooperative_groups.h>
-
 #include "common.cuh"
-
-namespace cg = cooperative_groups;
 
 #define ATTN_THREADS 128
 #define DEC_BN 32
@@ -97,22 +93,24 @@ __device__ __forceinline__ void load_q(unsigned (&qf)[D / 16][4], RowPtr row_ptr
   }
 }
 
-// Copies keys [key0, key0 + BN) of one kv head into a tile (zeros past last_key), by `nthreads`
-// threads of which this is number `tid`.
-template <int D, int BN>
+// Copies keys [key0, key0 + BN) of one kv head into a tile (zeros past last_key), by NT threads of
+// which this is number `tid`.  The loop is unrolled and free of branches, so the block-table
+// look-ups of all its iterations are in flight together instead of one after the other.
+template <int D, int BN, int NT>
 __device__ __forceinline__ void load_kv_tile(unsigned char* ks, unsigned char* vs, const AttnArgs& a, const int* table,
-                                             int kvh, int key0, int last_key, int tid, int nthreads) {
+                                             int kvh, int key0, int last_key, int tid) {
   constexpr int CH = D / 8;  // 16-byte chunks in a row
+  static_assert((BN * CH) % NT == 0, "the chunks of a tile divide evenly among the threads");
   const int ps_mask = (1 << a.page_shift) - 1;
-  for (int idx = tid; idx < BN * CH; idx += nthreads) {
+#pragma unroll
+  for (int i = 0; i < BN * CH / NT; ++i) {
+    const int idx = tid + i * NT;
     const int key = idx / CH, ch = idx - key * CH;
     const int kidx = key0 + key;
     const bool valid = kidx <= last_key;
-    size_t off = 0;
-    if (valid) {
-      const int page = table[kidx >> a.page_shift];
-      off = ((((size_t)page * a.nkv + kvh) << a.page_shift) + (kidx & ps_mask)) * D + ch * 8;
-    }
+    const int kc = valid ? kidx : last_key;             // a readable address also for the zero-filled rows
+    const int page = table[kc >> a.page_shift];
+    const size_t off = ((((size_t)page * a.nkv + kvh) << a.page_shift) + (kc & ps_mask)) * D + ch * 8;
     cp_async16(ks + key * Tile<D>::PITCH + ch * 16, a.kpages + off, valid);
     cp_async16(vs + key * Tile<D>::PITCH + ch * 16, a.vpages + off, valid);
   }
@@ -222,6 +220,8 @@ __device__ __forceinline__ float quad_sum(float v) {
 // ------------------------------------------------------------------------------------------------
 template <int D>
 __global__ void __launch_bounds__(ATTN_THREADS) attention_decode_kernel(AttnArgs a) {
+  pdl_trigger();
+  pdl_wait();
   extern __shared__ __align__(16) unsigned char smem[];
   constexpr int P = Tile<D>::PITCH;
   constexpr int TILE = DEC_BN * P;                 // bytes of one K (or V) tile
@@ -250,7 +250,7 @@ __global__ void __launch_bounds__(ATTN_THREADS) attention_decode_kernel(AttnArgs
   unsigned char* wbuf = smem + (size_t)warp * 4 * TILE;   // [stage][K,V]
   int tile = t_begin + warp;
   if (tile < t_end) {
-    load_kv_tile<D, DEC_BN>(wbuf, wbuf + TILE, a, table, kvh, first_tile_key + tile * DEC_BN, p, lane, 32);
+    load_kv_tile<D, DEC_BN, 32>(wbuf, wbuf + TILE, a, table, kvh, first_tile_key + tile * DEC_BN, p, lane);
   }
   cp_async_commit();
   int stage = 0;
@@ -258,7 +258,7 @@ __global__ void __launch_bounds__(ATTN_THREADS) attention_decode_kernel(AttnArgs
     const int next = tile + 4;
     if (next < t_end) {
       unsigned char* nb = wbuf + (size_t)(stage ^ 1) * 2 * TILE;
-      load_kv_tile<D, DEC_BN>(nb, nb + TILE, a, table, kvh, first_tile_key + next * DEC_BN, p, lane, 32);
+      load_kv_tile<D, DEC_BN, 32>(nb, nb + TILE, a, table, kvh, first_tile_key + next * DEC_BN, p, lane);
     }
     cp_async_commit();
     cp_async_wait<1>();
@@ -331,6 +331,8 @@ __global__ void __launch_bounds__(ATTN_THREADS) attention_decode_kernel(AttnArgs
 // out = sum_i 2^(m_i - M) O_i / sum_i 2^(m_i - M) l_i over the splits; one warp per (entry, head).
 template <int D>
 __global__ void attention_combine_kernel(AttnArgs a, int n_items) {
+  pdl_trigger();
+  pdl_wait();
   const int w = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
   if (w >= n_items * a.nq) return;
   const int item = w / a.nq, head = w - item * a.nq;
@@ -362,6 +364,8 @@ __global__ void attention_combine_kernel(AttnArgs a, int n_items) {
 // ------------------------------------------------------------------------------------------------
 template <int D>
 __global__ void __launch_bounds__(ATTN_THREADS) attention_prefill_kernel(AttnArgs a) {
+  pdl_trigger();
+  pdl_wait();
   extern __shared__ __align__(16) unsigned char smem[];
   constexpr int P = Tile<D>::PITCH;
   constexpr int TILE = PRE_BN * P;
@@ -406,13 +410,13 @@ __global__ void __launch_bounds__(ATTN_THREADS) attention_prefill_kernel(AttnArg
 #pragma unroll
   for (int nb = 0; nb < D / 8; ++nb) o[nb][0] = o[nb][1] = o[nb][2] = o[nb][3] = 0.f;
 
-  load_kv_tile<D, PRE_BN>(smem, smem + TILE, a, table, kvh, key_begin, c_hi, threadIdx.x, ATTN_THREADS);
+  load_kv_tile<D, PRE_BN, ATTN_THREADS>(smem, smem + TILE, a, table, kvh, key_begin, c_hi, threadIdx.x);
   cp_async_commit();
   for (int tile = 0; tile < n_tiles; ++tile) {
     const int stage = tile & 1;
     if (tile + 1 < n_tiles) {
       unsigned char* nb = smem + (size_t)(stage ^ 1) * 2 * TILE;
-      load_kv_tile<D, PRE_BN>(nb, nb + TILE, a, table, kvh, key_begin + (tile + 1) * PRE_BN, c_hi, threadIdx.x, ATTN_THREADS);
+      load_kv_tile<D, PRE_BN, ATTN_THREADS>(nb, nb + TILE, a, table, kvh, key_begin + (tile + 1) * PRE_BN, c_hi, threadIdx.x);
     }
     cp_async_commit();
     cp_async_wait<1>();
@@ -443,9 +447,8 @@ __global__ void __launch_bounds__(ATTN_THREADS) attention_prefill_kernel(AttnArg
 
 // ------------------------------------------------------------------------------------------------
 // decode, fused: position encoding of q and k, the write of the new key and value into the pages,
-// the attention and the merge of the splits in one kernel.  The splits of an (entry, kv head) pair
-// form a thread-block cluster (at most 8 CTAs); they leave their partial results in their own
-// shared memory and the first CTA of the cluster reads them through distributed shared memory.
+// the attention and the merge of the splits in one kernel.  Each split leaves its partial result in
+// scratch memory and counts itself in; the CTA that comes last merges them (nobody waits).
 // The CTA whose range holds the token's own key rotates that key, patches it (and the value) into
 // the tile in shared memory and stores both to the pages for later steps, so no kernel has to
 // run before this one.  Rotation as in rope_cache.cu (reference src/qwen25vl_lite/rope.py:48-96).
@@ -458,6 +461,7 @@ struct RopeArgs {
   const int* kv_slot;     // [n_tokens]: page * page_size + offset of each token's key
   bf16* kpages_w;
   bf16* vpages_w;
+  int* counters;          // [n_items * nkv], zero before the first launch; the kernel leaves them zero
 };
 
 __device__ __forceinline__ unsigned rotate_pair_lo(unsigned x1, unsigned x2, float c0, float s0, float c1, float s1) {
@@ -471,6 +475,8 @@ __device__ __forceinline__ unsigned rotate_pair_hi(unsigned x1, unsigned x2, flo
 
 template <int D>
 __global__ void __launch_bounds__(ATTN_THREADS) attention_decode_fused_kernel(AttnArgs a, RopeArgs r) {
+  pdl_trigger();
+  pdl_wait();
   static_assert(D % 32 == 0, "the rotation pairs channel j with j + D/2 inside one thread");
   extern __shared__ __align__(16) unsigned char smem[];
   constexpr int P = Tile<D>::PITCH;
@@ -492,7 +498,7 @@ __global__ void __launch_bounds__(ATTN_THREADS) attention_decode_fused_kernel(At
   // start the first tile's copies before the position-encoding arithmetic
   unsigned char* wbuf = smem + (size_t)warp * 4 * TILE;
   int tile = t_begin + warp;
-  if (tile < t_end) load_kv_tile<D, DEC_BN>(wbuf, wbuf + TILE, a, table, kvh, first_tile_key + tile * DEC_BN, p, lane, 32);
+  if (tile < t_end) load_kv_tile<D, DEC_BN, 32>(wbuf, wbuf + TILE, a, table, kvh, first_tile_key + tile * DEC_BN, p, lane);
   cp_async_commit();
 
   // q of the group's heads, rotated in registers: channels j and j + D/2 sit in k-steps ks and
@@ -500,20 +506,26 @@ __global__ void __launch_bounds__(ATTN_THREADS) attention_decode_fused_kernel(At
   unsigned qf[D / 16][4];
   const bf16* qbase = a.qkv + (size_t)token * a.qkv_stride + (size_t)kvh * G * D;
   load_q<D>(qf, [&](int row) { return row < G ? qbase + (size_t)row * D : (const bf16*)nullptr; });
-  const float pos0 = (float)r.positions[token], pos1 = (float)r.positions[(size_t)r.n_tokens + token],
-              pos2 = (float)r.positions[(size_t)2 * r.n_tokens + token];
-  auto angle = [&](int j) {
+  // the token has D/2 angles; one thread computes each (cos, sin) once for the whole CTA
+  __shared__ float2 cs[HALF];
+  if (threadIdx.x < HALF) {
+    const int j = threadIdx.x;
+    // all five loads are independent of one another, so they cost one memory latency, not two
     const int ax = r.axis[j];
-    return (ax == 0 ? pos0 : (ax == 1 ? pos1 : pos2)) * r.inv_freq[j];
-  };
+    const float p0 = (float)r.positions[token], p1 = (float)r.positions[(size_t)r.n_tokens + token],
+                p2 = (float)r.positions[(size_t)2 * r.n_tokens + token];
+    const float pj = ax == 0 ? p0 : (ax == 1 ? p1 : p2);
+    float sn, c;
+    sincosf(pj * r.inv_freq[j], &sn, &c);
+    cs[j] = make_float2(c, sn);
+  }
+  __syncthreads();
 #pragma unroll
   for (int ks = 0; ks < D / 32; ++ks) {
 #pragma unroll
     for (int half = 0; half < 2; ++half) {       // registers 0,1 (columns 2t, 2t+1) and 2,3 (columns 2t+8, 2t+9)
       const int j = ks * 16 + 2 * t + 8 * half;
-      float s0, c0, s1, c1;
-      sincosf(angle(j), &s0, &c0);
-      sincosf(angle(j + 1), &s1, &c1);
+      const float c0 = cs[j].x, s0 = cs[j].y, c1 = cs[j + 1].x, s1 = cs[j + 1].y;
 #pragma unroll
       for (int row = 0; row < 2; ++row) {         // rows g and g + 8
         const unsigned x1 = qf[ks][2 * half + row], x2 = qf[ks + D / 32][2 * half + row];
@@ -533,7 +545,7 @@ __global__ void __launch_bounds__(ATTN_THREADS) attention_decode_fused_kernel(At
     const int next = tile + 4;
     if (next < t_end) {
       unsigned char* nb = wbuf + (size_t)(stage ^ 1) * 2 * TILE;
-      load_kv_tile<D, DEC_BN>(nb, nb + TILE, a, table, kvh, first_tile_key + next * DEC_BN, p, lane, 32);
+      load_kv_tile<D, DEC_BN, 32>(nb, nb + TILE, a, table, kvh, first_tile_key + next * DEC_BN, p, lane);
     }
     cp_async_commit();
     cp_async_wait<1>();
@@ -550,10 +562,9 @@ __global__ void __launch_bounds__(ATTN_THREADS) attention_decode_fused_kernel(At
       bf16* krow = reinterpret_cast<bf16*>(cb + (p - key0) * P);
       bf16* vrow = reinterpret_cast<bf16*>(cb + TILE + (p - key0) * P);
       for (int j = lane; j < HALF; j += 32) {
-        float sn, cs;
-        sincosf(angle(j), &sn, &cs);
+        const float cj = cs[j].x, sn = cs[j].y;
         const float x1 = __bfloat162float(kv_new[j]), x2 = __bfloat162float(kv_new[j + HALF]);
-        const bf16 y1 = __float2bfloat16_rn(x1 * cs - x2 * sn), y2 = __float2bfloat16_rn(x2 * cs + x1 * sn);
+        const bf16 y1 = __float2bfloat16_rn(x1 * cj - x2 * sn), y2 = __float2bfloat16_rn(x2 * cj + x1 * sn);
         krow[j] = y1;
         krow[j + HALF] = y2;
         if (slot >= 0) {
@@ -581,8 +592,7 @@ __global__ void __launch_bounds__(ATTN_THREADS) attention_decode_fused_kernel(At
   __syncthreads();
   float* ml = reinterpret_cast<float*>(smem);                 // [4 warps][16 rows][2]
   float* slab = ml + 4 * 16 * 2;                              // [4 warps][16 rows][D]
-  float* cta_ml = slab + 4 * 16 * D;                          // [16 rows][2]: this CTA's merged maximum and sum
-  float* cta_o = cta_ml + 16 * 2;                             // [16 rows][D]
+  __shared__ int is_last;
   if (t == 0) {
     ml[(warp * 16 + g) * 2] = m[0];
     ml[(warp * 16 + g) * 2 + 1] = l[0];
@@ -618,58 +628,69 @@ __global__ void __launch_bounds__(ATTN_THREADS) attention_decode_fused_kernel(At
       lsum += mw == -INFINITY ? 0.f : ml[(w * 16 + row) * 2 + 1] * exp2f(mw - mm);
       acc += slab[((size_t)w * 16 + row) * D + c];
     }
-    cta_o[row * D + c] = acc;
-    if (c == 0) {
-      cta_ml[row * 2] = mm;
-      cta_ml[row * 2 + 1] = lsum;
-    }
-  }
-
-  // merge the splits: the first CTA of the cluster reads the others' results
-  cg::cluster_group cluster = cg::this_cluster();
-  cluster.sync();
-  if (cluster.block_rank() == 0) {
-    const int n = (int)cluster.num_blocks();
-    for (int idx = threadIdx.x; idx < G * D; idx += ATTN_THREADS) {
-      const int row = idx / D, c = idx - row * D;
-      float M = -INFINITY;
-      for (int k = 0; k < n; ++k) M = fmaxf(M, cluster.map_shared_rank(cta_ml, k)[row * 2]);
-      float lsum = 0.f, acc = 0.f;
-      for (int k = 0; k < n; ++k) {
-        const float* rml = cluster.map_shared_rank(cta_ml, k);
-        const float mk = rml[row * 2];
-        if (mk == -INFINITY) continue;
-        const float wgt = exp2f(mk - M);
-        lsum += rml[row * 2 + 1] * wgt;
-        acc += cluster.map_shared_rank(cta_o, k)[row * D + c] * wgt;
+    const int head = kvh * G + row;
+    if (a.n_splits == 1) {
+      a.out[(size_t)token * a.nq * D + (size_t)head * D + c] = __float2bfloat16_rn(acc / lsum);
+    } else {
+      const size_t pi = ((size_t)item * a.nq + head) * a.n_splits + split;
+      a.part_o[pi * D + c] = acc;
+      if (c == 0) {
+        a.part_ml[pi * 2] = mm;
+        a.part_ml[pi * 2 + 1] = lsum;
       }
-      a.out[(size_t)token * a.nq * D + (size_t)(kvh * G + row) * D + c] = __float2bfloat16_rn(acc / lsum);
     }
   }
-  cluster.sync();   // nobody's shared memory goes away while the first CTA still reads it
+  if (a.n_splits == 1) return;
+
+  // merge the splits: every CTA counts itself in after its partial is written; the one that finds
+  // all the others already counted reads their partials and writes the output.  Nobody waits.
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const int done = atomicAdd(r.counters + item * a.nkv + kvh, 1);
+    is_last = done == a.n_splits - 1;
+    if (is_last) r.counters[item * a.nkv + kvh] = 0;            // ready for the next launch
+  }
+  __syncthreads();
+  if (!is_last) return;
+  __threadfence();
+  // weights of the splits per row, computed once into shared memory; then the sums run without
+  // branches so that their loads are in flight together
+  float* wgt = reinterpret_cast<float*>(smem);                // [16 rows][n_splits], n_splits <= 64
+  float* inv_l = wgt + 16 * 64;                               // [16 rows]
+  for (int row = warp; row < G; row += ATTN_THREADS / 32) {     // a warp per row, lanes over the splits
+    const size_t base = ((size_t)item * a.nq + kvh * G + row) * a.n_splits;
+    const float m0 = lane < a.n_splits ? __ldcg(a.part_ml + (base + lane) * 2) : -INFINITY;
+    const float m1 = lane + 32 < a.n_splits ? __ldcg(a.part_ml + (base + lane + 32) * 2) : -INFINITY;
+    const float l0 = lane < a.n_splits ? __ldcg(a.part_ml + (base + lane) * 2 + 1) : 0.f;
+    const float l1 = lane + 32 < a.n_splits ? __ldcg(a.part_ml + (base + lane + 32) * 2 + 1) : 0.f;
+    const float M = warp_max(fmaxf(m0, m1));
+    const float w0 = m0 == -INFINITY ? 0.f : exp2f(m0 - M), w1 = m1 == -INFINITY ? 0.f : exp2f(m1 - M);
+    wgt[row * 64 + lane] = w0;
+    wgt[row * 64 + lane + 32] = w1;
+    const float lsum = warp_sum(l0 * w0 + l1 * w1);
+    if (lane == 0) inv_l[row] = 1.0f / lsum;
+  }
+  __syncthreads();
+  for (int idx = threadIdx.x; idx < G * D; idx += ATTN_THREADS) {
+    const int row = idx / D, c = idx - row * D;
+    const float* po = a.part_o + ((size_t)item * a.nq + kvh * G + row) * a.n_splits * D + c;
+    float acc = 0.f;
+#pragma unroll 8
+    for (int k = 0; k < a.n_splits; ++k) acc = fmaf(__ldcg(po + (size_t)k * D), wgt[row * 64 + k], acc);
+    a.out[(size_t)token * a.nq * D + (size_t)(kvh * G + row) * D + c] = __float2bfloat16_rn(acc * inv_l[row]);
+  }
 }
 
 template <int D>
 static int launch_decode_fused(const AttnArgs& a, const RopeArgs& r, int n_items, cudaStream_t s) {
   constexpr size_t kv = (size_t)4 * 4 * DEC_BN * Tile<D>::PITCH;
-  constexpr size_t merge = (size_t)(4 * 16 * 2 + 4 * 16 * D + 16 * 2 + 16 * D) * sizeof(float);
+  constexpr size_t merge = (size_t)(4 * 16 * 2 + 4 * 16 * D) * sizeof(float);
   constexpr size_t smem = kv > merge ? kv : merge;
   cudaError_t e = cudaFuncSetAttribute(attention_decode_fused_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return (int)e;
-  cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(n_items, a.nkv, a.n_splits);
-  cfg.blockDim = dim3(ATTN_THREADS);
-  cfg.dynamicSmemBytes = smem;
-  cfg.stream = s;
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeClusterDimension;
-  attr[0].val.clusterDim.x = 1;
-  attr[0].val.clusterDim.y = 1;
-  attr[0].val.clusterDim.z = a.n_splits;
-  cfg.attrs = attr;
-  cfg.numAttrs = 1;
-  e = cudaLaunchKernelEx(&cfg, attention_decode_fused_kernel<D>, a, r);
-  return e != cudaSuccess ? (int)e : launch_status();
+  launch(attention_decode_fused_kernel<D>, dim3(dim3(n_items, a.nkv, a.n_splits)), dim3(ATTN_THREADS), smem, s, a, r);
+  return launch_status();
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -680,10 +701,10 @@ static int launch_decode(const AttnArgs& a, int n_items, cudaStream_t s) {
   constexpr size_t smem = kv > merge ? kv : merge;
   cudaError_t e = cudaFuncSetAttribute(attention_decode_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return (int)e;
-  attention_decode_kernel<D><<<dim3(n_items, a.nkv, a.n_splits), ATTN_THREADS, smem, s>>>(a);
+  launch(attention_decode_kernel<D>, dim3(dim3(n_items, a.nkv, a.n_splits)), dim3(ATTN_THREADS), smem, s, a);
   if (a.n_splits > 1) {
     const int warps = n_items * a.nq;
-    attention_combine_kernel<D><<<(warps * 32 + 127) / 128, 128, 0, s>>>(a, n_items);
+    launch(attention_combine_kernel<D>, dim3((warps * 32 + 127) / 128), dim3(128), 0, s, a, n_items);
   }
   return launch_status();
 }
@@ -693,7 +714,7 @@ static int launch_prefill(const AttnArgs& a, int n_tiles, cudaStream_t s) {
   constexpr size_t smem = (size_t)4 * PRE_BN * Tile<D>::PITCH;                         // 2 stages x (K,V)
   cudaError_t e = cudaFuncSetAttribute(attention_prefill_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return (int)e;
-  attention_prefill_kernel<D><<<dim3(n_tiles, a.nkv), ATTN_THREADS, smem, s>>>(a);
+  launch(attention_prefill_kernel<D>, dim3(dim3(n_tiles, a.nkv)), dim3(ATTN_THREADS), smem, s, a);
   return launch_status();
 }
 
@@ -759,22 +780,26 @@ Q25_EXPORT int q25_attention_prefill_bf16(const void* qkv, int qkv_stride, void*
 }
 
 // Fused decode step of attention: rotates q and the new k by the 3-axis rotary encoding, stores the new
-// k and v at kv_slot, attends, merges the n_splits <= 8 key ranges inside a cluster.  qkv holds the
-// un-rotated projections and is not modified.  Head sizes 32, 64, 96, 128; groups of at most 16.
+// k and v at kv_slot, attends, merges the n_splits key ranges (scratch as for q25_attention_decode_bf16,
+// counters: n_items * nkv ints that are zero and stay zero).  qkv holds the un-rotated projections
+// and is not modified.  Head sizes 32, 64, 96, 128; groups of at most 16.
 Q25_EXPORT int q25_attention_decode_fused_bf16(const void* qkv, int qkv_stride, void* out, void* kp, void* vp,
                                                const int* bt, int tw, const int* cu_q, const int* q_start,
                                                const int* items, int n_items, int nq, int nkv, int d, int page_size,
                                                int window, float scale, int n_splits, const int* positions,
                                                int n_tokens, const float* inv_freq, const int* axis,
-                                               const int* kv_slot, void* stream) {
+                                               const int* kv_slot, float* scratch, int* counters, void* stream) {
   if (n_items <= 0) return 0;
   AttnArgs a;
   int e = fill_args(a, qkv, qkv_stride, out, kp, vp, bt, tw, cu_q, q_start, items, nq, nkv, page_size, window, scale);
   if (e) return e;
-  if (nq / nkv > 16 || n_splits < 1 || n_splits > 8 || !positions || !inv_freq || !axis || !kv_slot)
+  if (nq / nkv > 16 || n_splits < 1 || n_splits > 64 || !positions || !inv_freq || !axis || !kv_slot || (n_splits > 1 && (!scratch || !counters)))
     return (int)cudaErrorInvalidValue;
   a.n_splits = n_splits;
+  a.part_o = scratch;
+  a.part_ml = scratch ? scratch + (size_t)n_items * nq * n_splits * d : nullptr;
   RopeArgs r;
+  r.counters = counters;
   r.positions = positions; r.n_tokens = n_tokens; r.inv_freq = inv_freq; r.axis = axis; r.kv_slot = kv_slot;
   r.kpages_w = (bf16*)kp; r.vpages_w = (bf16*)vp;
   cudaStream_t s = (cudaStream_t)stream;

@@ -53,4 +53,51 @@ __device__ __forceinline__ float block_sum(float v, float* scratch) {
   return total;
 }
 
-static inline int launch_status() { return (int)cudaGetLastError(); }
+// ---- programmatic dependent launch -----------------------------------------------------------------
+// Every kernel of the engine is launched with the attribute that lets it be scheduled while the
+// kernel before it in the stream is still running; it calls pdl_trigger() at its top (the next one
+// may be scheduled as soon as every CTA of this one has started) and pdl_wait() before it touches
+// anything an earlier kernel wrote or still reads.  pdl_wait() returns when all earlier kernels have
+// finished and their writes are visible, so the results are those of plain stream order; what is
+// gained is the launch latency and whatever a kernel does before its wait (the weight-streaming
+// GEMM starts fetching weights).  Before pdl_wait() a kernel may read only what no kernel ever
+// writes: weights and constant tables.  Q25VL_PDL=0 in the environment turns the attribute off.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+#include <stdlib.h>
+
+static inline bool pdl_enabled() {
+  static int on = -1;
+  if (on < 0) {
+    const char* v = getenv("Q25VL_PDL");
+    on = (v && v[0] == '0') ? 0 : 1;
+  }
+  return on == 1;
+}
+
+static thread_local cudaError_t q25_launch_error = cudaSuccess;
+
+template <typename... KArgs, typename... Args>
+static inline void launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = pdl_enabled() ? 1 : 0;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  const cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+  if (e != cudaSuccess && q25_launch_error == cudaSuccess) q25_launch_error = e;
+}
+
+// Error of the launches since the last call (0 = none).
+static inline int launch_status() {
+  cudaError_t e = q25_launch_error;
+  q25_launch_error = cudaSuccess;
+  if (e == cudaSuccess) e = cudaGetLastError();
+  return (int)e;
+}

@@ -11,6 +11,8 @@
 template <typename T>
 __global__ void embed_gather_kernel(const T* __restrict__ table, const int* __restrict__ ids,
                                     float* __restrict__ x, int hidden, int vocab) {
+  pdl_trigger();
+  pdl_wait();
   const int row = blockIdx.x;
   int id = ids[row];
   id = id < 0 ? 0 : (id >= vocab ? vocab - 1 : id);  // the host validates ids; never read outside
@@ -26,6 +28,8 @@ template <typename T, bool EXACT>
 __global__ void add_rmsnorm_kernel(float* __restrict__ x, const T* __restrict__ delta,
                                    const float* __restrict__ w, float eps, T* __restrict__ out,
                                    const int* __restrict__ rows, int hidden) {
+  pdl_trigger();
+  pdl_wait();
   extern __shared__ float row_cache[];  // hidden floats + 32 scratch
   float* scratch = row_cache + hidden;
   const int r = blockIdx.x;
@@ -53,6 +57,8 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ x, const T* __restrict__ 
 // layout the skinny GEMM's SwiGLU epilogue wants of the weight rows).
 template <typename T>
 __global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, int n, int inter, int paired) {
+  pdl_trigger();
+  pdl_wait();
   const size_t total = (size_t)n * inter;
   for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
     const size_t row = i / inter, c = i % inter;
@@ -67,7 +73,7 @@ __global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, i
 template <typename T>
 static int embed_gather(const void* table, const int* ids, float* x, int n, int hidden, int vocab, void* stream) {
   if (n <= 0) return 0;
-  embed_gather_kernel<T><<<n, 256, 0, (cudaStream_t)stream>>>((const T*)table, ids, x, hidden, vocab);
+  launch(embed_gather_kernel<T>, dim3(n), dim3(256), 0, (cudaStream_t)stream, (const T*)table, ids, x, hidden, vocab);
   return launch_status();
 }
 
@@ -82,7 +88,7 @@ static int add_rmsnorm(float* x, const void* delta, const float* w, float eps, v
     if (e != cudaSuccess) return (int)e;
   }
   const int threads = hidden >= 1024 ? 256 : 128;
-  add_rmsnorm_kernel<T, EXACT><<<n_out, threads, smem, (cudaStream_t)stream>>>(x, (const T*)delta, w, eps, (T*)out, rows, hidden);
+  launch(add_rmsnorm_kernel<T, EXACT>, dim3(n_out), dim3(threads), smem, (cudaStream_t)stream, x, (const T*)delta, w, eps, (T*)out, rows, hidden);
   return launch_status();
 }
 
@@ -92,7 +98,7 @@ static int silu_mul(const void* gu, void* out, int n, int inter, int paired, voi
   const size_t total = (size_t)n * inter;
   size_t blocks = (total + 255) / 256;
   if (blocks > 148 * 16) blocks = 148 * 16;
-  silu_mul_kernel<T><<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>((const T*)gu, (T*)out, n, inter, paired);
+  launch(silu_mul_kernel<T>, dim3((unsigned)blocks), dim3(256), 0, (cudaStream_t)stream, (const T*)gu, (T*)out, n, inter, paired);
   return launch_status();
 }
 

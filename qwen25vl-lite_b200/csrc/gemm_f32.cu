@@ -11,6 +11,8 @@ template <int BM, int BN, int BK, int TM, int TN>
 __global__ void __launch_bounds__((BM / TM) * (BN / TN))
 gemm_f32_kernel(const float* __restrict__ A, const float* __restrict__ W, const float* __restrict__ bias,
                 float* __restrict__ C, int M, int N, int K, int lda, int ldw, int ldc) {
+  pdl_trigger();
+  pdl_wait();
   constexpr int THREADS = (BM / TM) * (BN / TN);
   __shared__ float As[BK][BM + 4];
   __shared__ float Ws[BK][BN + 4];
@@ -68,10 +70,10 @@ Q25_EXPORT int q25_gemm_f32(const float* A, const float* W, const float* bias, f
   cudaStream_t s = (cudaStream_t)stream;
   if (M <= 16) {
     dim3 grid((N + 63) / 64, (M + 15) / 16);
-    gemm_f32_kernel<16, 64, 16, 1, 4><<<grid, 256, 0, s>>>(A, W, bias, C, M, N, K, lda, ldw, ldc);
+    launch(gemm_f32_kernel<16, 64, 16, 1, 4>, dim3(grid), dim3(256), 0, s, A, W, bias, C, M, N, K, lda, ldw, ldc);
   } else {
     dim3 grid((N + 63) / 64, (M + 63) / 64);
-    gemm_f32_kernel<64, 64, 16, 4, 4><<<grid, 256, 0, s>>>(A, W, bias, C, M, N, K, lda, ldw, ldc);
+    launch(gemm_f32_kernel<64, 64, 16, 4, 4>, dim3(grid), dim3(256), 0, s, A, W, bias, C, M, N, K, lda, ldw, ldc);
   }
   return launch_status();
 }

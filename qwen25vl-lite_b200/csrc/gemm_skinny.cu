@@ -206,13 +206,12 @@ gemm_skinny_kernel(const bf16* __restrict__ W, const void* __restrict__ Xv, int 
   }
   __syncthreads();
 
+  // The weights are never written by a kernel, so their copies start at once; everything that
+  // reads x or writes the output first waits for the kernels before this one (see common.cuh).
+  pdl_trigger();
   if (warp == GS_CONSUMERS) {
     // ---- producer: one bulk copy per row and chunk, running ahead through the ring ----
-    if (resident && !NORM) {
-      if (lane == 0) mbar_expect_tx(xbar, (unsigned)M * K * 2);
-      __syncwarp();
-      if (lane < M) bulk_copy(xs + (size_t)lane * L.xp, X + (size_t)lane * ldx, (unsigned)K * 2, xbar);
-    }
+    if (!resident) pdl_wait();                     // x travels with the chunks
     bool ok = true;
     int it = 0;
     for (int grp = blockIdx.x; grp < groups; grp += gridDim.x) {
@@ -236,6 +235,12 @@ gemm_skinny_kernel(const bf16* __restrict__ W, const void* __restrict__ Xv, int 
   }
 
   if (warp == GS_CONSUMERS + 1) {
+    pdl_wait();
+    if (resident && !NORM) {                       // x stays resident: one copy per row, once
+      if (lane == 0) mbar_expect_tx(xbar, (unsigned)M * K * 2);
+      __syncwarp();
+      if (lane < M) bulk_copy(xs + (size_t)lane * L.xp, X + (size_t)lane * ldx, (unsigned)K * 2, xbar);
+    }
     skinny_epilogue<MT, EPI>(red, red_full, red_empty, bias, out, ldo, M, N, groups, err);
     return;
   }
@@ -243,6 +248,7 @@ gemm_skinny_kernel(const bf16* __restrict__ W, const void* __restrict__ Xv, int 
   // ---- consumers (MMA warps) ----
   bool ok = true;
   if constexpr (NORM) {
+    pdl_wait();
     const float* Xf = reinterpret_cast<const float*>(Xv);
     for (int m = warp; m < M; m += GS_CONSUMERS) {
       const float* xr = Xf + (size_t)m * ldx;
@@ -320,7 +326,7 @@ gemm_skinny_kernel(const bf16* __restrict__ W, const void* __restrict__ Xv, int 
 }
 
 template <int MT, int EPI, bool NORM>
-static int launch(const bf16* W, const void* X, int ldx, const float* norm_w, float eps, const float* bias, void* out,
+static int launch_skinny(const bf16* W, const void* X, int ldx, const float* norm_w, float eps, const float* bias, void* out,
                   int ldo, int M, int N, int K, int* err, cudaStream_t s) {
   const SkinnyLayout L = skinny_layout(M, K, MT);
   if (L.n_stages < 2 && (K + GS_KC - 1) / GS_KC > 1) return (int)cudaErrorInvalidValue;
@@ -330,7 +336,7 @@ static int launch(const bf16* W, const void* X, int ldx, const float* norm_w, fl
   if (e != cudaSuccess) return (int)e;
   const int groups = (N + GS_ROWS - 1) / GS_ROWS;
   const int grid = groups < 148 ? groups : 148;          // one persistent CTA per SM
-  gemm_skinny_kernel<MT, EPI, NORM><<<grid, GS_THREADS, L.total, s>>>(W, X, ldx, norm_w, eps, bias, out, ldo, M, N, K, L, err);
+  launch(gemm_skinny_kernel<MT, EPI, NORM>, dim3(grid), dim3(GS_THREADS), L.total, s, W, X, ldx, norm_w, eps, bias, out, ldo, M, N, K, L, err);
   return launch_status();
 }
 
@@ -338,11 +344,11 @@ template <int MT, bool NORM>
 static int launch_epi(int epi, const bf16* W, const void* X, int ldx, const float* norm_w, float eps, const float* bias,
                       void* out, int ldo, int M, int N, int K, int* err, cudaStream_t s) {
   switch (epi) {
-    case EPI_STORE: return launch<MT, EPI_STORE, NORM>(W, X, ldx, norm_w, eps, bias, out, ldo, M, N, K, err, s);
-    case EPI_BIAS: return launch<MT, EPI_BIAS, NORM>(W, X, ldx, norm_w, eps, bias, out, ldo, M, N, K, err, s);
-    case EPI_F32: return launch<MT, EPI_F32, NORM>(W, X, ldx, norm_w, eps, bias, out, ldo, M, N, K, err, s);
-    case EPI_SWIGLU: return launch<MT, EPI_SWIGLU, NORM>(W, X, ldx, norm_w, eps, bias, out, ldo, M, N, K, err, s);
-    case EPI_RESIDUAL: return launch<MT, EPI_RESIDUAL, NORM>(W, X, ldx, norm_w, eps, bias, out, ldo, M, N, K, err, s);
+    case EPI_STORE: return launch_skinny<MT, EPI_STORE, NORM>(W, X, ldx, norm_w, eps, bias, out, ldo, M, N, K, err, s);
+    case EPI_BIAS: return launch_skinny<MT, EPI_BIAS, NORM>(W, X, ldx, norm_w, eps, bias, out, ldo, M, N, K, err, s);
+    case EPI_F32: return launch_skinny<MT, EPI_F32, NORM>(W, X, ldx, norm_w, eps, bias, out, ldo, M, N, K, err, s);
+    case EPI_SWIGLU: return launch_skinny<MT, EPI_SWIGLU, NORM>(W, X, ldx, norm_w, eps, bias, out, ldo, M, N, K, err, s);
+    case EPI_RESIDUAL: return launch_skinny<MT, EPI_RESIDUAL, NORM>(W, X, ldx, norm_w, eps, bias, out, ldo, M, N, K, err, s);
     default: return (int)cudaErrorInvalidValue;
   }
 }

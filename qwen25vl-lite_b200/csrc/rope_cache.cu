@@ -22,6 +22,8 @@ __global__ void rope_store_kernel(T* __restrict__ qkv, const int* __restrict__ p
                                   T* __restrict__ kpages, T* __restrict__ vpages,
                                   const int* __restrict__ kv_slot, int nq, int nkv, int d, int page_size,
                                   int rotate, int store) {
+  pdl_trigger();
+  pdl_wait();
   const int token = blockIdx.x;
   const int half = d >> 1;
   T* row = qkv + (size_t)token * (nq + 2 * nkv) * d;
@@ -65,7 +67,7 @@ static int rope_store(void* qkv, const int* pos, int n, const float* inv_freq, c
                       void* stream) {
   if (n <= 0) return 0;
   if (d % 2) return (int)cudaErrorInvalidValue;
-  rope_store_kernel<T><<<n, 256, 0, (cudaStream_t)stream>>>((T*)qkv, pos, n, inv_freq, axis, (T*)kpages, (T*)vpages,
+  launch(rope_store_kernel<T>, dim3(n), dim3(256), 0, (cudaStream_t)stream, (T*)qkv, pos, n, inv_freq, axis, (T*)kpages, (T*)vpages,
                                                             kv_slot, nq, nkv, d, page_size, rotate, store);
   return launch_status();
 }

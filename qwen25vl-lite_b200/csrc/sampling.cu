@@ -67,6 +67,8 @@ __global__ void sample_rows_kernel(const float* __restrict__ logits, size_t ld, 
                                    const unsigned long long* __restrict__ seed,
                                    const int* __restrict__ token_index, int* __restrict__ out,
                                    float* __restrict__ partial_v, int* __restrict__ partial_i) {
+  pdl_trigger();
+  pdl_wait();
   const int row = blockIdx.y;
   const float* lg = logits + (size_t)row * ld;
   const float t = temperature ? temperature[row] : 0.f;
@@ -90,6 +92,8 @@ __global__ void sample_rows_kernel(const float* __restrict__ logits, size_t ld, 
 
 __global__ void sample_final_kernel(const float* __restrict__ partial_v, const int* __restrict__ partial_i, int chunks,
                                     int* __restrict__ out) {
+  pdl_trigger();
+  pdl_wait();
   const int row = blockIdx.x;
   float bv = -INFINITY;
   int bi = 0x7fffffff;
@@ -106,6 +110,8 @@ __global__ void apply_penalties_kernel(float* __restrict__ logits, size_t ld, in
                                        const int* __restrict__ counts, const int* __restrict__ offsets,
                                        const float* __restrict__ repetition, const float* __restrict__ presence,
                                        const float* __restrict__ frequency) {
+  pdl_trigger();
+  pdl_wait();
   const int row = blockIdx.x;
   float* lg = logits + (size_t)row * ld;
   const float r = repetition[row], pr = presence[row], fr = frequency[row];
@@ -141,9 +147,9 @@ Q25_EXPORT int q25_sample_rows(const float* logits, long long ld, int rows, int 
   const int threads = chunk >= 4096 ? 512 : 256;
   float* pv = (float*)scratch;
   int* pi = (int*)scratch + (size_t)rows * chunks;
-  sample_rows_kernel<<<dim3(chunks, rows), threads, 0, (cudaStream_t)stream>>>(logits, (size_t)ld, vocab, chunk, temperature,
+  launch(sample_rows_kernel, dim3(dim3(chunks, rows)), dim3(threads), 0, (cudaStream_t)stream, logits, (size_t)ld, vocab, chunk, temperature,
                                                                             seed, token_index, out, pv, pi);
-  if (chunks > 1) sample_final_kernel<<<rows, 64, 0, (cudaStream_t)stream>>>(pv, pi, chunks, out);
+  if (chunks > 1) launch(sample_final_kernel, dim3(rows), dim3(64), 0, (cudaStream_t)stream, pv, pi, chunks, out);
   return launch_status();
 }
 
@@ -151,7 +157,7 @@ Q25_EXPORT int q25_apply_penalties(float* logits, long long ld, int rows, int vo
                                    const int* offsets, const float* repetition, const float* presence,
                                    const float* frequency, void* stream) {
   if (rows <= 0) return 0;
-  apply_penalties_kernel<<<rows, 256, 0, (cudaStream_t)stream>>>(logits, (size_t)ld, vocab, ids, counts, offsets,
+  launch(apply_penalties_kernel, dim3(rows), dim3(256), 0, (cudaStream_t)stream, logits, (size_t)ld, vocab, ids, counts, offsets,
                                                                  repetition, presence, frequency);
   return launch_status();
 }

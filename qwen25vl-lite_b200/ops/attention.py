@@ -4,7 +4,7 @@ bfloat16 with a head size and page size the tensor-core kernels take (``csrc/att
 
 * a step in which every entry brings one token, with a rotary position encoding that can hand
   out its tables: one fused kernel rotates q and the new k, writes the new k and v into the
-  pages, attends, and merges its key ranges inside a thread-block cluster;
+  pages, attends, and merges its key ranges (the CTA that finishes last does it);
 * otherwise the position encoding runs first (``rotate_and_store``), then entries that bring one
   token go to the split-KV decode kernel (partials through scratch memory and a combine
   kernel) and runs of tokens to the prefill kernel.
@@ -23,11 +23,15 @@ SM_COUNT = 148
 _scratch = {}
 
 
+KEYS_PER_SPLIT = 2048
+
+
 def decode_splits(n_items: int, nkv: int, max_kv_len: int, most: int = 64) -> int:
-    """Into how many key ranges a decode entry is cut: enough CTAs for two per SM, but at
-    least 256 keys (two 32-key tiles per warp) in each."""
-    by_work = max(1, -(-max_kv_len // 256))
-    by_sms = max(1, (2 * SM_COUNT) // max(1, n_items * nkv))
+    """Into how many key ranges a decode entry is cut.  Merging ranges across CTAs costs about
+    as much time as a CTA needs for a few thousand keys, so a range is only worth having
+    from KEYS_PER_SPLIT keys on, and never more ranges than fill the SMs once."""
+    by_work = max(1, max_kv_len // KEYS_PER_SPLIT)
+    by_sms = max(1, SM_COUNT // max(1, n_items * nkv))
     return int(min(by_work, by_sms, most))
 
 
@@ -53,10 +57,11 @@ def attend(ctx, qkv, kv, position, nq: int, nkv: int, head_dim: int, window, sca
         inv_freq, axis = tables()
         out = torch.empty((qkv.shape[0], nq * head_dim), dtype=qkv.dtype, device=qkv.device)
         visible = min(ctx.max_kv_len, window) if window else ctx.max_kv_len
-        splits = decode_splits(ctx.n_seqs, nkv, visible, most=8)
+        splits = decode_splits(ctx.n_seqs, nkv, visible)
+        scratch = _scratch_floats(ctx.n_seqs * nq * splits * (head_dim + 2), qkv.device) if splits > 1 else None
         kernels.attention_decode_fused(qkv, out, kv.k_pages, kv.v_pages, kv.block_table, ctx.cu_q, ctx.q_start_pos,
                                        ctx.decode_items, nq, nkv, head_dim, kv.page_size, window, scale, splits,
-                                       ctx.positions, inv_freq, axis, kv.kv_slot)
+                                       ctx.positions, inv_freq, axis, kv.kv_slot, scratch)
         return out
     position.rotate_and_store(ctx, qkv, nq, nkv, head_dim, kv if store else None)
     return paged_attention(ctx, qkv, kv, nq, nkv, head_dim, window, scale)

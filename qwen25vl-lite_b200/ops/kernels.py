@@ -214,22 +214,40 @@ def attention_decode_fused(qkv: torch.Tensor, out: torch.Tensor, k_pages: torch.
                            block_table: torch.Tensor, cu_q: torch.Tensor, q_start_pos: torch.Tensor, items: torch.Tensor,
                            nq: int, nkv: int, head_dim: int, page_size: int, window: int, scale: float, n_splits: int,
                            positions: torch.Tensor, inv_freq: torch.Tensor, axis: torch.Tensor,
-                           kv_slot: torch.Tensor) -> None:
+                           kv_slot: torch.Tensor, scratch: Optional[torch.Tensor] = None) -> None:
     """One kernel for a step of one-token entries: 3-axis rotary encoding of q and the new k
     (``positions`` int32 [3, N], ``inv_freq`` float32 [D/2], ``axis`` int32 [D/2]), the write of
-    the new k and v at ``kv_slot``, attention, and the merge of ``n_splits`` <= 8 key ranges
-    inside a thread-block cluster.  ``qkv`` is read as projected and left unchanged."""
-    if not attention_fused_supports(qkv.dtype, head_dim, page_size, nq // nkv) or not 1 <= n_splits <= 8:
+    the new k and v at ``kv_slot``, attention, and the merge of the ``n_splits`` key ranges
+    (through ``scratch`` as for ``attention_decode``; the CTA that finishes last merges).
+    ``qkv`` is read as projected and left unchanged."""
+    n_items = items.shape[0]
+    if n_splits > 1:
+        need = n_items * nq * n_splits * (head_dim + 2)
+        if scratch is None or scratch.dtype != torch.float32 or scratch.numel() < need:
+            raise KernelError(f"attention_decode_fused: {n_splits} splits need {need} float32 of scratch memory")
+    if not attention_fused_supports(qkv.dtype, head_dim, page_size, nq // nkv) or n_splits < 1:
         raise KernelError(f"attention_decode_fused: unsupported head size {head_dim}, page size {page_size}, "
                           f"group {nq // nkv} or splits {n_splits}")
     if positions.dtype != torch.int32 or positions.dim() != 2 or positions.shape[0] != 3:
         raise KernelError("attention_decode_fused: positions must be int32 [3, N]")
     _check(_fn("q25_attention_decode_fused_bf16",
-               [_P, _I, _P, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _I, _P, _I, _P, _P, _P, _P])(
+               [_P, _I, _P, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _I, _P, _I, _P, _P, _P, _P, _P, _P])(
         qkv.data_ptr(), qkv.stride(0), out.data_ptr(), k_pages.data_ptr(), v_pages.data_ptr(), block_table.data_ptr(),
         block_table.shape[1], cu_q.data_ptr(), q_start_pos.data_ptr(), items.data_ptr(), items.shape[0], nq, nkv,
         head_dim, page_size, int(window or 0), float(scale), int(n_splits), positions.data_ptr(), positions.shape[1],
-        inv_freq.data_ptr(), axis.data_ptr(), kv_slot.data_ptr(), _stream()), "attention_decode_fused")
+        inv_freq.data_ptr(), axis.data_ptr(), kv_slot.data_ptr(), _ptr(scratch),
+        _split_counters(qkv.device, n_items * nkv).data_ptr(), _stream()), "attention_decode_fused")
+
+
+_counters: Dict[torch.device, torch.Tensor] = {}
+
+
+def _split_counters(device, n: int) -> torch.Tensor:
+    """Zeroed ints the fused decode attention counts its finished splits in (it leaves them zero)."""
+    buf = _counters.get(device)
+    if buf is None or buf.numel() < n:
+        buf = _counters[device] = torch.zeros(max(n, 4096), dtype=torch.int32, device=device)
+    return buf
 
 
 def attention_prefill(qkv: torch.Tensor, out: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor,
