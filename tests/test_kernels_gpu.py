@@ -318,10 +318,10 @@ def test_tensor_core_attention_finds_a_far_key_and_the_window_edge(q_len):
 def test_decode_splits_heuristic():
     from qwen25vl_lite.ops.attention import decode_splits
     assert decode_splits(1, 2, 100) == 1                  # short context: nothing to split
-    assert decode_splits(1, 2, 2048) == 1                 # a cross-CTA merge costs more than 2048 keys
-    assert decode_splits(1, 2, 32768) == 16
+    assert decode_splits(1, 2, 2048) == 8                 # 2048 keys / 256 per split
+    assert decode_splits(8, 2, 4096) == 9                 # 144 CTAs: one per SM, no second wave
     assert decode_splits(64, 2, 8192) == 1                # 128 (entry, head) pairs already fill the GPU
-    assert decode_splits(8, 2, 100000) == 9               # never more CTAs than SMs
+    assert decode_splits(1, 1, 100000) == 64
 
 
 @pytest.mark.parametrize("m", [1, 5, 8, 13, 16])
