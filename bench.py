@@ -120,7 +120,82 @@ def kv_bytes_per_token(t, layers):
 
 
 def run_reference(args):
-    print(json.dumps({"impl": "reference", "unavailable": "reference arm not wired yet"}))
+    """The unmodified reference (installed under baseline/_ref) on the same metric: 3B sizes,
+    random bfloat16 weights, batch 8, 2,048-token prompts, through its own public API and stock
+    settings (LLMEngine.add_request / step; no opt-in kernels, no CUDA graphs).  None of this
+    repository's models, kernels or engine is imported on this path."""
+    ref = os.path.join(ROOT, "baseline", "_ref")
+    if not os.path.isdir(os.path.join(ref, "qwen25vl_lite")):
+        print(json.dumps({"impl": "reference", "unavailable": "baseline/_ref is not installed (see DESIGN.md)"}))
+        return 0
+    sys.path.insert(0, ref)
+    try:
+        import numpy as np
+        import torch
+
+        import qwen25vl_lite as reference
+        if os.path.realpath(os.path.dirname(reference.__file__)) != os.path.realpath(os.path.join(ref, "qwen25vl_lite")):
+            raise RuntimeError("the reference package did not come first on sys.path")
+        from qwen25vl_lite import EngineConfig, LLMEngine, ModelRunner, Qwen25VLConfig, SamplingParams
+        from qwen25vl_lite.model import Qwen25VLLite
+
+        t = dict(CONFIG_3B["text_config"])
+        layers = args.layers or FULL_LAYERS
+        t["num_hidden_layers"] = layers
+        t["mrope_section"] = t.pop("rope_scaling")["mrope_section"]
+        # the vision tower is built by the reference's model class but never run here; keep it tiny
+        raw = {"text_config": t, "tie_word_embeddings": True,
+               "vision_config": {"depth": 1, "hidden_size": 64, "intermediate_size": 64, "num_heads": 2,
+                                 "out_hidden_size": t["hidden_size"], "fullatt_block_indexes": [0]}}
+        cfg = Qwen25VLConfig.from_dict(raw)
+        torch.manual_seed(0)
+        with torch.device("cuda:0"):
+            model = Qwen25VLLite(cfg)
+        with torch.no_grad():
+            for name, p in model.named_parameters():
+                p.normal_(0.0, 0.02)
+                if name.endswith("norm.weight") or "layernorm" in name:
+                    p.add_(1.0)
+        model = model.to(torch.bfloat16).eval()
+        ecfg = EngineConfig(num_blocks=8 * CONTEXT_LEN // PAGE + 64, block_size=PAGE, max_num_seqs=8,
+                            max_num_batched_tokens=8192, max_model_len=CONTEXT_LEN, enable_prefix_cache=False,
+                            device="cuda:0", dtype=torch.bfloat16)
+        engine = LLMEngine(ModelRunner(model, ecfg, device="cuda:0"), ecfg)
+        rng = np.random.default_rng(0)
+        params = SamplingParams(temperature=0.0, max_tokens=args.warmup + args.steps + 8, ignore_eos=True)
+        for _ in range(8):
+            engine.add_request(rng.integers(0, 150000, size=PROMPT_LEN).tolist(), params)
+        with torch.no_grad():
+            while engine.waiting or any(s.num_computed_tokens < len(s.prompt_token_ids) for s in engine.running):
+                engine.step()
+            for _ in range(args.warmup):
+                engine.step()
+            clocks = ClockSampler()
+            clocks.start()
+            torch.cuda.synchronize()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            for _ in range(args.steps):
+                engine.step()
+            b.record()
+            torch.cuda.synchronize()
+            ms = a.elapsed_time(b)
+            clock_record = clocks.stop()
+        value = 8 * args.steps / (ms / 1e3)
+        d = t["hidden_size"] // t["num_attention_heads"]
+        print(json.dumps({
+            "impl": "reference", "metric": "decode tokens/s, Qwen2.5-VL-3B dims, batch 8, 2048-token prompts",
+            "value": value, "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "bf16", "data": "synthetic (seeded uniform-random token ids, random-init weights N(0, 0.02))",
+            "config": {"model": "Qwen2.5-VL-3B text dims", "layers": layers, "layers_full": FULL_LAYERS,
+                       "hidden": t["hidden_size"], "q_heads": t["num_attention_heads"], "kv_heads": t["num_key_value_heads"],
+                       "head_dim": d, "intermediate": t["intermediate_size"], "vocab": t["vocab_size"], "global_batch": 8,
+                       "seq_len": CONTEXT_LEN, "prompt_len": PROMPT_LEN, "kv_page": PAGE, "parallelism": "single GPU"},
+            "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": None, "d2h_bytes_per_step": None},
+            "clocks": clock_record}))
+    except Exception as exc:  # the reference could not run here: say why, in one line
+        print(json.dumps({"impl": "reference", "unavailable": f"{type(exc).__name__}: {str(exc).splitlines()[0][:200]}"}))
     return 0
 
 
