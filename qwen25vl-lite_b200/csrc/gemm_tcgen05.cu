@@ -1,0 +1,352 @@
+// y[M,N] = x[M,K] . W[N,K]^T in bfloat16 on the 5th-generation tensor cores (tcgen05), for the
+// many-row products of prefill.  Both operands are K-major (x rows and W rows are contiguous in K),
+// the accumulator lives in tensor memory.
+//
+// One persistent CTA per SM, 6 warps with fixed roles:
+//   warp 0   TMA producer: one lane issues cp.async.bulk.tensor loads of a 128 x 64 tile of x and a
+//            256 x 64 tile of W (128-byte swizzle) into a ring of 4 shared-memory stages; each stage
+//            has a "full" mbarrier that counts the bytes landed;
+//   warp 1   MMA issuer: allocates 512 columns of tensor memory (two 128 x 256 float accumulators),
+//            then one lane issues tcgen05.mma (M 128, N 256, K 16) four times per stage and commits
+//            to the stage's "empty" mbarrier, and after the last K block to the accumulator's
+//            "full" mbarrier; while the epilogue drains one accumulator the next tile fills the other;
+//   warps 2-5  epilogue: each reads its quarter of the 128 accumulator rows with tcgen05.ld (a lane
+//            owns one row), applies the epilogue and stores straight to global memory.
+// Epilogues as in gemm_skinny.cu: store, + float bias, float output, SwiGLU on paired rows (8 gate
+// features followed by their 8 up features; reference formula src/qwen25vl_lite/text.py:66), and
+// add into the float residual stream.
+//
+// Tiles are walked with the row block fastest, so the CTAs that run together share W tiles through
+// L2.  Edges: rows past M and features past N are zero-filled by TMA and masked at the store.
+// Every mbarrier wait is bounded; a wait that gives up records a code in *err and the CTA runs to
+// its end (freeing its tensor memory) with invalid output.
+#include <cuda.h>
+
+#include "common.cuh"
+
+enum { T5_STORE = 0, T5_BIAS = 1, T5_F32 = 2, T5_SWIGLU = 3, T5_RESIDUAL = 4 };
+
+#define T5_BM 128
+#define T5_BN 256
+#define T5_BK 64
+#define T5_STAGES 4
+#define T5_A_BYTES (T5_BM * T5_BK * 2)
+#define T5_B_BYTES (T5_BN * T5_BK * 2)
+#define T5_STAGE_BYTES (T5_A_BYTES + T5_B_BYTES)
+#define T5_THREADS 192
+#define T5_WAIT_LIMIT (1 << 22)
+
+__device__ __forceinline__ unsigned t5_s32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void t5_mbar_init(unsigned long long* bar, int count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(t5_s32(bar)), "r"(count));
+}
+__device__ __forceinline__ void t5_mbar_expect_tx(unsigned long long* bar, unsigned bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(t5_s32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void t5_mbar_arrive(unsigned long long* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(t5_s32(bar)) : "memory");
+}
+__device__ __forceinline__ bool t5_mbar_wait(unsigned long long* bar, unsigned parity) {
+  for (int i = 0; i < T5_WAIT_LIMIT; ++i) {
+    unsigned done;
+    asm volatile(
+        "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
+        : "=r"(done) : "r"(t5_s32(bar)), "r"(parity) : "memory");
+    if (done) return true;
+  }
+  return false;
+}
+
+// 2-D tiled TMA load (no multicast): box at element coordinates (x = K index, y = row).
+__device__ __forceinline__ void t5_tma_load(void* dst, const CUtensorMap* map, int x, int y, unsigned long long* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];\n"
+      ::"r"(t5_s32(dst)), "l"(reinterpret_cast<unsigned long long>(map)), "r"(t5_s32(bar)), "r"(x), "r"(y) : "memory");
+}
+
+// Shared-memory matrix descriptor of a K-major tile with 128-byte swizzle: rows of 128 bytes, groups
+// of 8 rows 1024 bytes apart.
+__device__ __forceinline__ unsigned long long t5_smem_desc(unsigned smem_addr) {
+  unsigned long long d = 0;
+  d |= (unsigned long long)((smem_addr & 0x3FFFF) >> 4);   // start address
+  d |= (unsigned long long)1 << 16;                         // leading byte offset (unused with swizzle)
+  d |= (unsigned long long)(1024 >> 4) << 32;               // stride byte offset: next 8-row group
+  d |= (unsigned long long)1 << 46;                         // descriptor version of sm_100
+  d |= (unsigned long long)2 << 61;                         // 128-byte swizzle
+  return d;
+}
+
+// Instruction descriptor: bf16 x bf16 -> f32, both operands K-major, M 128, N 256.
+__device__ __forceinline__ unsigned t5_idesc() {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(T5_BN >> 3) << 17) | ((unsigned)(T5_BM >> 4) << 24);
+}
+
+__device__ __forceinline__ void t5_mma(unsigned tmem_d, unsigned long long adesc, unsigned long long bdesc, unsigned idesc,
+                                       unsigned accumulate) {
+  asm volatile(
+      "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n"
+      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+// The mbarrier gets one arrival when every MMA issued so far by this thread has finished.
+__device__ __forceinline__ void t5_commit(unsigned long long* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(t5_s32(bar)) : "memory");
+}
+__device__ __forceinline__ void t5_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory"); }
+__device__ __forceinline__ void t5_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory"); }
+
+// 32 consecutive float columns of this lane's accumulator row.
+__device__ __forceinline__ void t5_ld32(unsigned taddr, float (&v)[32]) {
+  unsigned r[32];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,"
+      "%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];\n"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]),
+        "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]),
+        "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr));
+  asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+#pragma unroll
+  for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+struct T5Shared {
+  unsigned long long full[T5_STAGES], empty[T5_STAGES], acc_full[2], acc_empty[2];
+  unsigned tmem_base;
+};
+
+template <int EPI>
+__global__ void __launch_bounds__(T5_THREADS, 1)
+gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
+                    const float* __restrict__ bias, void* __restrict__ out, int ldo, int M, int N, int K,
+                    int* __restrict__ err) {
+  extern __shared__ __align__(1024) unsigned char t5_smem[];
+  // the dynamic shared memory starts with the stages (1024-byte aligned for the swizzle), the barriers follow
+  unsigned char* stages = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(t5_smem) + 1023) & ~(uintptr_t)1023);
+  T5Shared* sh = reinterpret_cast<T5Shared*>(stages + T5_STAGES * T5_STAGE_BYTES);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int m_blocks = (M + T5_BM - 1) / T5_BM, n_blocks = (N + T5_BN - 1) / T5_BN;
+  const int n_tiles = m_blocks * n_blocks;
+  const int k_blocks = (K + T5_BK - 1) / T5_BK;
+
+  pdl_trigger();
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < T5_STAGES; ++s) {
+      t5_mbar_init(sh->full + s, 1);
+      t5_mbar_init(sh->empty + s, 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      t5_mbar_init(sh->acc_full + b, 1);
+      t5_mbar_init(sh->acc_empty + b, 4);
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+  }
+  if (warp == 1) {   // tensor memory: all 512 columns, two accumulators of 256
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], 512;\n" ::"r"(t5_s32(&sh->tmem_base)) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
+  }
+  t5_fence_before();
+  __syncthreads();
+  t5_fence_after();
+  const unsigned tmem_base = sh->tmem_base;
+  pdl_wait();   // x was written by the kernel before this one; the output may still be read by it
+
+  if (warp == 0) {
+    // ---- producer ----
+    if (lane == 0) {
+      bool ok = true;
+      int it = 0;
+      for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
+        const int m0 = (tile % m_blocks) * T5_BM, n0 = (tile / m_blocks) * T5_BN;
+        for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+          const int s = it % T5_STAGES;
+          if (it >= T5_STAGES && ok) {
+            ok = t5_mbar_wait(sh->empty + s, ((it / T5_STAGES) - 1) & 1);
+            if (!ok) atomicExch(err, 11);
+          }
+          unsigned char* st = stages + (size_t)s * T5_STAGE_BYTES;
+          t5_mbar_expect_tx(sh->full + s, T5_STAGE_BYTES);
+          t5_tma_load(st, &map_x, kb * T5_BK, m0, sh->full + s);
+          t5_tma_load(st + T5_A_BYTES, &map_w, kb * T5_BK, n0, sh->full + s);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ---- MMA issuer ----
+    if (lane == 0) {
+      bool ok = true;
+      const unsigned idesc = t5_idesc();
+      int it = 0, tile_it = 0;
+      for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++tile_it) {
+        const int b = tile_it & 1;
+        if (tile_it >= 2 && ok) {
+          ok = t5_mbar_wait(sh->acc_empty + b, ((tile_it >> 1) - 1) & 1);
+          if (!ok) atomicExch(err, 12);
+        }
+        t5_fence_after();
+        const unsigned acc = tmem_base + (unsigned)b * T5_BN;
+        for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+          const int s = it % T5_STAGES;
+          if (ok) {
+            ok = t5_mbar_wait(sh->full + s, (it / T5_STAGES) & 1);
+            if (!ok) atomicExch(err, 13);
+          }
+          t5_fence_after();
+          const unsigned a_addr = t5_s32(stages + (size_t)s * T5_STAGE_BYTES);
+          const unsigned long long adesc = t5_smem_desc(a_addr), bdesc = t5_smem_desc(a_addr + T5_A_BYTES);
+#pragma unroll
+          for (int k = 0; k < T5_BK / 16; ++k)   // 32 bytes further along K inside the swizzle atom: + 2 in the address field
+            t5_mma(acc, adesc + 2 * k, bdesc + 2 * k, idesc, (kb | k) != 0);
+          t5_commit(sh->empty + s);
+        }
+        t5_commit(sh->acc_full + b);
+      }
+    }
+  } else {
+    // ---- epilogue: warp w reads TMEM lanes 32 (w % 4) .. + 31 ----
+    const int quarter = warp & 3;
+    bool ok = true;
+    int tile_it = 0;
+    for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++tile_it) {
+      const int m0 = (tile % m_blocks) * T5_BM, n0 = (tile / m_blocks) * T5_BN;
+      const int b = tile_it & 1;
+      if (ok) {
+        ok = t5_mbar_wait(sh->acc_full + b, (tile_it >> 1) & 1);
+        if (!ok && lane == 0) atomicExch(err, 14);
+      }
+      t5_fence_after();
+      const int m = m0 + quarter * 32 + lane;
+      const unsigned taddr = tmem_base + ((unsigned)(quarter * 32) << 16) + (unsigned)b * T5_BN;
+#pragma unroll 1
+      for (int c = 0; c < T5_BN; c += 32) {
+        float v[32];
+        t5_ld32(taddr + c, v);
+        const int n = n0 + c;
+        if (m >= M || n >= N) continue;
+        if constexpr (EPI == T5_SWIGLU) {
+          // columns come in groups of 16: 8 gate features, then their 8 up features
+          bf16* dst = reinterpret_cast<bf16*>(out) + (size_t)m * ldo + (n >> 1);
+#pragma unroll
+          for (int grp = 0; grp < 2; ++grp) {
+            if (n + grp * 16 + 16 > N) break;
+            __align__(16) bf16 o8[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              const float gate = v[grp * 16 + j], up = v[grp * 16 + 8 + j];
+              o8[j] = __float2bfloat16_rn(gate / (1.0f + __expf(-gate)) * up);
+            }
+            *reinterpret_cast<uint4*>(dst + grp * 8) = *reinterpret_cast<const uint4*>(o8);
+          }
+        } else if constexpr (EPI == T5_F32 || EPI == T5_RESIDUAL) {
+          float* dst = reinterpret_cast<float*>(out) + (size_t)m * ldo + n;
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            if (n + j >= N) break;
+            if constexpr (EPI == T5_RESIDUAL) dst[j] += v[j];
+            else dst[j] = v[j];
+          }
+        } else {
+          bf16* dst = reinterpret_cast<bf16*>(out) + (size_t)m * ldo + n;
+          if (n + 32 <= N && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              __align__(16) bf16 o8[8];
+#pragma unroll
+              for (int j = 0; j < 8; ++j) {
+                float y = v[q * 8 + j];
+                if constexpr (EPI == T5_BIAS) y += bias[n + q * 8 + j];
+                o8[j] = __float2bfloat16_rn(y);
+              }
+              *reinterpret_cast<uint4*>(dst + q * 8) = *reinterpret_cast<const uint4*>(o8);
+            }
+          } else {
+            for (int j = 0; j < 32 && n + j < N; ++j) {
+              float y = v[j];
+              if constexpr (EPI == T5_BIAS) y += bias[n + j];
+              dst[j] = __float2bfloat16_rn(y);
+            }
+          }
+        }
+      }
+      t5_fence_before();
+      __syncwarp();
+      if (lane == 0) t5_mbar_arrive(sh->acc_empty + b);
+    }
+  }
+
+  // every warp gets here (all waits are bounded); then the tensor memory goes back
+  t5_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    t5_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, 512;\n" ::"r"(tmem_base) : "memory");
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_tiled() {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  }
+  return fn;
+}
+
+// A [rows, K] bfloat16 row-major matrix with row pitch ld (elements), boxes of box_rows x 64.
+static int make_map(CUtensorMap* map, const void* base, int rows, int K, int ld, int box_rows) {
+  EncodeTiledFn enc = encode_tiled();
+  if (!enc) return (int)cudaErrorNotSupported;
+  const cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
+  const cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+  const cuuint32_t box[2] = {T5_BK, (cuuint32_t)box_rows};
+  const cuuint32_t estr[2] = {1, 1};
+  const CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : (int)cudaErrorInvalidValue;
+}
+
+template <int EPI>
+static int launch_t5(const CUtensorMap& mx, const CUtensorMap& mw, const float* bias, void* out, int ldo, int M, int N, int K,
+                     int* err, cudaStream_t s) {
+  const size_t smem = (size_t)T5_STAGES * T5_STAGE_BYTES + 1024 + sizeof(T5Shared);
+  cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel<EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (e != cudaSuccess) return (int)e;
+  const int tiles = ((M + T5_BM - 1) / T5_BM) * ((N + T5_BN - 1) / T5_BN);
+  launch(gemm_tcgen05_kernel<EPI>, dim3(tiles < 148 ? tiles : 148), dim3(T5_THREADS), smem, s, mx, mw, bias, out, ldo, M, N, K, err);
+  return launch_status();
+}
+
+// x: [M, K] bfloat16 with row pitch ldx; W: [N, K] bfloat16 contiguous.  epi as in gemm_skinny.cu
+// (0 store, 1 + bias, 2 float out, 3 SwiGLU pairs, 4 add into float out).  Needs K % 8 == 0,
+// ldx % 8 == 0 and 16-byte aligned bases (TMA).  err: device int that gets a code if a wait gave up.
+Q25_EXPORT int q25_gemm_tcgen05_bf16(const void* W, const void* X, int ldx, const float* bias, void* out, int ldo, int M,
+                                     int N, int K, int epi, int* err, void* stream) {
+  if (M <= 0 || N <= 0) return 0;
+  if (K <= 0 || K % 8 || ldx % 8 || ((uintptr_t)W & 15) || ((uintptr_t)X & 15) || !err || (epi == T5_SWIGLU && N % 16) ||
+      (epi == T5_BIAS && !bias))
+    return (int)cudaErrorInvalidValue;
+  CUtensorMap mx, mw;
+  int r = make_map(&mx, X, M, K, ldx, T5_BM);
+  if (r) return r;
+  r = make_map(&mw, W, N, K, K, T5_BN);
+  if (r) return r;
+  cudaStream_t s = (cudaStream_t)stream;
+  switch (epi) {
+    case T5_STORE: return launch_t5<T5_STORE>(mx, mw, bias, out, ldo, M, N, K, err, s);
+    case T5_BIAS: return launch_t5<T5_BIAS>(mx, mw, bias, out, ldo, M, N, K, err, s);
+    case T5_F32: return launch_t5<T5_F32>(mx, mw, bias, out, ldo, M, N, K, err, s);
+    case T5_SWIGLU: return launch_t5<T5_SWIGLU>(mx, mw, bias, out, ldo, M, N, K, err, s);
+    case T5_RESIDUAL: return launch_t5<T5_RESIDUAL>(mx, mw, bias, out, ldo, M, N, K, err, s);
+    default: return (int)cudaErrorInvalidValue;
+  }
+}

@@ -339,6 +339,26 @@ def gemm_skinny_norm(x: torch.Tensor, norm_weight: torch.Tensor, eps: float, w: 
         out.stride(0), m, n, k, int(epilogue), error_flag(x.device).data_ptr(), _stream()), "gemm_skinny_norm")
 
 
+def gemm_tcgen05_supports(x: torch.Tensor, w: torch.Tensor) -> bool:
+    """Operands the tcgen05 / TMA product takes: bfloat16, K a multiple of 8, 16-byte aligned rows."""
+    return (x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.dim() == 2 and x.stride(1) == 1
+            and x.shape[1] % 8 == 0 and x.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0 and w.is_contiguous()
+            and w.data_ptr() % 16 == 0)
+
+
+def gemm_tcgen05(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor, epilogue: int) -> None:
+    """out = x . w^T on the tcgen05 tensor cores (TMA-fed, accumulators in tensor memory), for
+    any number of rows; epilogues as for ``gemm_skinny``."""
+    m, k = x.shape
+    n = w.shape[0]
+    if not gemm_tcgen05_supports(x, w) or w.shape[1] != k:
+        raise KernelError(f"gemm_tcgen05: unsupported operands {tuple(x.shape)} {x.dtype} x {tuple(w.shape)} {w.dtype}")
+    _skinny_out(out, m, n, epilogue, "gemm_tcgen05")
+    _check(_fn("q25_gemm_tcgen05_bf16", _UNTYPED["q25_gemm_skinny_bf16"])(
+        w.data_ptr(), x.data_ptr(), x.stride(0), _ptr(bias), out.data_ptr(), out.stride(0), m, n, k, int(epilogue),
+        error_flag(x.device).data_ptr(), _stream()), "gemm_tcgen05")
+
+
 def sample_rows(logits: torch.Tensor, temperature: Optional[torch.Tensor], seed: Optional[torch.Tensor],
                 token_index: Optional[torch.Tensor], out: torch.Tensor) -> None:
     """out[r] = argmax(logits[r]) where temperature[r] <= 0 (or temperature is None), else a

@@ -6,18 +6,26 @@
   (``csrc/gemm_skinny.cu``).  It can normalise its input on the fly (a ``DeferredNorm``)
   and add its result into the float32 residual stream, which removes the norm kernels and
   the separate residual additions from a decode step.
-* bfloat16, more rows: the library product (cuBLAS through ``torch.mm`` / ``torch.addmm``)
-  with float32 accumulation.  The reference's engine uses the same library for every
-  projection (``nn.Linear``, src/qwen25vl_lite/text.py:61-63,80-83; src/qwen25vl_lite/model.py:84).
+* bfloat16, more rows (prefill, large decode batches): the engine's tcgen05 product
+  (``csrc/gemm_tcgen05.cu``: TMA loads, accumulators in tensor memory) with the same
+  epilogues.  ``Q25VL_LARGE_GEMM=cublas`` in the environment switches these products to the
+  library (cuBLAS through ``torch.mm`` / ``torch.addmm``), which the reference's engine uses for
+  every projection (``nn.Linear``, src/qwen25vl_lite/text.py:61-63,80-83;
+  src/qwen25vl_lite/model.py:84); operands the tcgen05 kernel refuses (K not a multiple of 8,
+  unaligned rows) go there too.
 """
 
 from __future__ import annotations
 
 from typing import Optional
 
+import os
+
 import torch
 
 from . import kernels
+
+USE_TCGEN05 = os.environ.get("Q25VL_LARGE_GEMM", "tcgen05") != "cublas"
 
 
 class DeferredNorm:
@@ -59,6 +67,8 @@ class Linear:
                 return y
         if deferred:
             x = x.materialize()
+        if w.dtype == torch.bfloat16 and USE_TCGEN05 and kernels.gemm_tcgen05_supports(x, w):
+            return self._tcgen05(x, out_dtype, residual)
         if w.dtype == torch.float32:
             out = torch.empty((x.shape[0], self.out_features), dtype=torch.float32, device=x.device)
             kernels.gemm_f32(x, w, self.bias, out)
@@ -71,6 +81,22 @@ class Linear:
         if self._bias_lib is not None:
             return torch.addmm(self._bias_lib, x, w.t())
         return torch.mm(x, w.t())
+
+    def _tcgen05(self, x, out_dtype, residual):
+        w = self.weight
+        m = x.shape[0]
+        if residual is not None and self.bias is None:
+            kernels.gemm_tcgen05(x, w, None, residual, kernels.SKINNY_RESIDUAL)
+            return None
+        if out_dtype == torch.float32:
+            out = torch.empty((m, self.out_features), dtype=torch.float32, device=x.device)
+            kernels.gemm_tcgen05(x, w, None, out, kernels.SKINNY_F32)
+            if self.bias is not None:
+                out += self.bias
+            return out
+        out = torch.empty((m, self.out_features), dtype=w.dtype, device=x.device)
+        kernels.gemm_tcgen05(x, w, self.bias, out, kernels.SKINNY_BIAS if self.bias is not None else kernels.SKINNY_STORE)
+        return out
 
     def _skinny(self, x, deferred: bool, out_dtype, residual):
         """The weight-streaming kernel with the epilogue the call asks for, or NotImplemented."""

@@ -6,7 +6,7 @@ from __future__ import annotations
 
 import torch
 
-from ..ops import kernels
+from ..ops import kernels, linear
 from ..ops.linear import DeferredNorm, Linear
 from .base import FeedForward, TensorSpec, register_feed_forward
 
@@ -51,6 +51,8 @@ class SwiGLU(FeedForward):
                 h = h.materialize()
             if self.paired and kernels.gemm_skinny_supports(h, w):
                 kernels.gemm_skinny(h, w, None, act, kernels.SKINNY_SWIGLU)
+            elif self.paired and linear.USE_TCGEN05 and kernels.gemm_tcgen05_supports(h, w):
+                kernels.gemm_tcgen05(h, w, None, act, kernels.SKINNY_SWIGLU)
             else:
                 kernels.silu_mul(self.gate_up_proj(h), act, self.paired)
         return self.down_proj(act, residual=residual)

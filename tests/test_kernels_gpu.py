@@ -501,3 +501,37 @@ def test_attention_decode_fused(nq, nkv, d, section, page_size, window, splits):
     for i, s in enumerate(slots):                                # the new key and value are in the pages now
         assert np.abs(kp[s // page_size, :, s % page_size] - k_rot[i]).max() < 4e-2
         assert np.array_equal(vp[s // page_size, :, s % page_size], f64(v_raw[i]))
+
+
+@pytest.mark.parametrize("m,n,k", [(128, 256, 64), (2048, 2560, 2048), (300, 1000, 512), (17, 4752, 256), (1000, 512, 11008),
+                                   (129, 272, 72)])
+def test_gemm_tcgen05(m, n, k):
+    """The tcgen05 / TMA product against float64 on the same bfloat16 operands: whole tiles, ragged
+    edges in M, N and K, many K blocks (the ring of stages wraps), every epilogue."""
+    from qwen25vl_lite.ops import kernels
+    rng = np.random.default_rng(m + n + k)
+    x = dev(rng.standard_normal((m, k)), torch.bfloat16)
+    w = dev(rng.standard_normal((n, k)) * 0.05, torch.bfloat16)
+    bias = dev(rng.standard_normal(n), torch.float32)
+    ref = f64(x) @ f64(w).T
+    scale = max(1.0, np.abs(ref).max())
+    out = torch.full((m, n), float("nan"), dtype=torch.bfloat16, device="cuda")
+    kernels.gemm_tcgen05(x, w, None, out, kernels.SKINNY_STORE)
+    assert np.abs(f64(out) - ref).max() / scale < 1e-2
+    kernels.gemm_tcgen05(x, w, bias, out, kernels.SKINNY_BIAS)
+    assert np.abs(f64(out) - (ref + f64(bias))).max() / scale < 1e-2
+    out32 = torch.full((m, n), float("nan"), dtype=torch.float32, device="cuda")
+    kernels.gemm_tcgen05(x, w, None, out32, kernels.SKINNY_F32)
+    assert np.abs(f64(out32) - ref).max() / scale < 1e-4
+    stream0 = rng.standard_normal((m, n)) * 5
+    stream = dev(stream0, torch.float32)
+    kernels.gemm_tcgen05(x, w, None, stream, kernels.SKINNY_RESIDUAL)
+    want = f64(dev(stream0, torch.float32)) + ref
+    assert np.abs(f64(stream) - want).max() / max(1.0, np.abs(want).max()) < 1e-4
+    if n % 16 == 0:
+        act = torch.full((m, n // 2), float("nan"), dtype=torch.bfloat16, device="cuda")
+        kernels.gemm_tcgen05(x, w, None, act, kernels.SKINNY_SWIGLU)
+        pairs = ref.reshape(m, n // 16, 2, 8)
+        want = (plain.silu(pairs[:, :, 0]) * pairs[:, :, 1]).reshape(m, n // 2)
+        assert np.abs(f64(act) - want).max() / max(1.0, np.abs(want).max()) < 1e-2
+    assert int(kernels.error_flag("cuda:0")[0]) == 0
