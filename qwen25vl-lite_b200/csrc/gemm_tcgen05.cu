@@ -27,12 +27,17 @@
 enum { T5_STORE = 0, T5_BIAS = 1, T5_F32 = 2, T5_SWIGLU = 3, T5_RESIDUAL = 4 };
 
 #define T5_BM 128
-#define T5_BN 256
 #define T5_BK 64
-#define T5_STAGES 4
 #define T5_A_BYTES (T5_BM * T5_BK * 2)
-#define T5_B_BYTES (T5_BN * T5_BK * 2)
-#define T5_STAGE_BYTES (T5_A_BYTES + T5_B_BYTES)
+#define T5_MAX_STAGES 6
+
+// The feature tile is 256 wide (4 stages of 48 KB) or, where that leaves SMs idle in the last wave,
+// 128 wide (6 stages of 32 KB).
+template <int BN> struct T5Cfg {
+  static constexpr int STAGES = BN == 256 ? 4 : 6;
+  static constexpr int B_BYTES = BN * T5_BK * 2;
+  static constexpr int STAGE_BYTES = T5_A_BYTES + B_BYTES;
+};
 #define T5_THREADS 192
 #define T5_WAIT_LIMIT (1 << 22)
 
@@ -77,9 +82,9 @@ __device__ __forceinline__ unsigned long long t5_smem_desc(unsigned smem_addr) {
   return d;
 }
 
-// Instruction descriptor: bf16 x bf16 -> f32, both operands K-major, M 128, N 256.
-__device__ __forceinline__ unsigned t5_idesc() {
-  return (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(T5_BN >> 3) << 17) | ((unsigned)(T5_BM >> 4) << 24);
+// Instruction descriptor: bf16 x bf16 -> f32, both operands K-major, M 128, N = BN.
+template <int BN> __device__ __forceinline__ unsigned t5_idesc() {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(BN >> 3) << 17) | ((unsigned)(T5_BM >> 4) << 24);
 }
 
 __device__ __forceinline__ void t5_mma(unsigned tmem_d, unsigned long long adesc, unsigned long long bdesc, unsigned idesc,
@@ -112,15 +117,16 @@ __device__ __forceinline__ void t5_ld32(unsigned taddr, float (&v)[32]) {
 }
 
 struct T5Shared {
-  unsigned long long full[T5_STAGES], empty[T5_STAGES], acc_full[2], acc_empty[2];
+  unsigned long long full[T5_MAX_STAGES], empty[T5_MAX_STAGES], acc_full[2], acc_empty[2];
   unsigned tmem_base;
 };
 
-template <int EPI>
+template <int EPI, int BN>
 __global__ void __launch_bounds__(T5_THREADS, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
                     const float* __restrict__ bias, void* __restrict__ out, int ldo, int M, int N, int K,
                     int* __restrict__ err) {
+  constexpr int T5_BN = BN, T5_STAGES = T5Cfg<BN>::STAGES, T5_STAGE_BYTES = T5Cfg<BN>::STAGE_BYTES;
   extern __shared__ __align__(1024) unsigned char t5_smem[];
   // the dynamic shared memory starts with the stages (1024-byte aligned for the swizzle), the barriers follow
   unsigned char* stages = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(t5_smem) + 1023) & ~(uintptr_t)1023);
@@ -143,8 +149,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
     }
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
   }
-  if (warp == 1) {   // tensor memory: all 512 columns, two accumulators of 256
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], 512;\n" ::"r"(t5_s32(&sh->tmem_base)) : "memory");
+  if (warp == 1) {   // tensor memory: two accumulators of BN columns
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(t5_s32(&sh->tmem_base)), "n"(2 * BN) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
   }
   t5_fence_before();
@@ -177,7 +183,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
     // ---- MMA issuer ----
     if (lane == 0) {
       bool ok = true;
-      const unsigned idesc = t5_idesc();
+      const unsigned idesc = t5_idesc<BN>();
       int it = 0, tile_it = 0;
       for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++tile_it) {
         const int b = tile_it & 1;
@@ -281,7 +287,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
   __syncthreads();
   if (warp == 1) {
     t5_fence_after();
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, 512;\n" ::"r"(tmem_base) : "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "n"(2 * BN) : "memory");
   }
 }
 
@@ -315,15 +321,24 @@ static int make_map(CUtensorMap* map, const void* base, int rows, int K, int ld,
   return r == CUDA_SUCCESS ? 0 : (int)cudaErrorInvalidValue;
 }
 
-template <int EPI>
+template <int EPI, int BN>
 static int launch_t5(const CUtensorMap& mx, const CUtensorMap& mw, const float* bias, void* out, int ldo, int M, int N, int K,
                      int* err, cudaStream_t s) {
-  const size_t smem = (size_t)T5_STAGES * T5_STAGE_BYTES + 1024 + sizeof(T5Shared);
-  cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel<EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  const size_t smem = (size_t)T5Cfg<BN>::STAGES * T5Cfg<BN>::STAGE_BYTES + 1024 + sizeof(T5Shared);
+  cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel<EPI, BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return (int)e;
-  const int tiles = ((M + T5_BM - 1) / T5_BM) * ((N + T5_BN - 1) / T5_BN);
-  launch(gemm_tcgen05_kernel<EPI>, dim3(tiles < 148 ? tiles : 148), dim3(T5_THREADS), smem, s, mx, mw, bias, out, ldo, M, N, K, err);
+  const int tiles = ((M + T5_BM - 1) / T5_BM) * ((N + BN - 1) / BN);
+  launch(gemm_tcgen05_kernel<EPI, BN>, dim3(tiles < 148 ? tiles : 148), dim3(T5_THREADS), smem, s, mx, mw, bias, out, ldo, M, N, K, err);
   return launch_status();
+}
+
+// Width of the feature tile: 256 keeps the tensor cores busiest, but when its tiles fill the last
+// wave of 148 SMs badly, 128-wide tiles (twice as many, each a little less efficient) finish sooner.
+static int pick_bn(int M, int N) {
+  const long long mb = (M + T5_BM - 1) / T5_BM;
+  const long long t256 = mb * ((N + 255) / 256), t128 = mb * ((N + 127) / 128);
+  const double cost256 = (double)((t256 + 147) / 148) * 1.0, cost128 = (double)((t128 + 147) / 148) * 0.56;
+  return cost128 < cost256 ? 128 : 256;
 }
 
 // x: [M, K] bfloat16 with row pitch ldx; W: [N, K] bfloat16 contiguous.  epi as in gemm_skinny.cu
@@ -338,15 +353,20 @@ Q25_EXPORT int q25_gemm_tcgen05_bf16(const void* W, const void* X, int ldx, cons
   CUtensorMap mx, mw;
   int r = make_map(&mx, X, M, K, ldx, T5_BM);
   if (r) return r;
-  r = make_map(&mw, W, N, K, K, T5_BN);
+  const int bn = pick_bn(M, N);
+  r = make_map(&mw, W, N, K, K, bn);
   if (r) return r;
   cudaStream_t s = (cudaStream_t)stream;
+#define T5_CASE(E) \
+  case E: return bn == 256 ? launch_t5<E, 256>(mx, mw, bias, out, ldo, M, N, K, err, s) \
+                           : launch_t5<E, 128>(mx, mw, bias, out, ldo, M, N, K, err, s);
   switch (epi) {
-    case T5_STORE: return launch_t5<T5_STORE>(mx, mw, bias, out, ldo, M, N, K, err, s);
-    case T5_BIAS: return launch_t5<T5_BIAS>(mx, mw, bias, out, ldo, M, N, K, err, s);
-    case T5_F32: return launch_t5<T5_F32>(mx, mw, bias, out, ldo, M, N, K, err, s);
-    case T5_SWIGLU: return launch_t5<T5_SWIGLU>(mx, mw, bias, out, ldo, M, N, K, err, s);
-    case T5_RESIDUAL: return launch_t5<T5_RESIDUAL>(mx, mw, bias, out, ldo, M, N, K, err, s);
+    T5_CASE(T5_STORE)
+    T5_CASE(T5_BIAS)
+    T5_CASE(T5_F32)
+    T5_CASE(T5_SWIGLU)
+    T5_CASE(T5_RESIDUAL)
     default: return (int)cudaErrorInvalidValue;
   }
+#undef T5_CASE
 }

@@ -6,13 +6,13 @@
   (``csrc/gemm_skinny.cu``).  It can normalise its input on the fly (a ``DeferredNorm``)
   and add its result into the float32 residual stream, which removes the norm kernels and
   the separate residual additions from a decode step.
-* bfloat16, more rows (prefill, large decode batches): the engine's tcgen05 product
+* bfloat16, 128 rows or more (prefill): the engine's tcgen05 product
   (``csrc/gemm_tcgen05.cu``: TMA loads, accumulators in tensor memory) with the same
   epilogues.  ``Q25VL_LARGE_GEMM=cublas`` in the environment switches these products to the
   library (cuBLAS through ``torch.mm`` / ``torch.addmm``), which the reference's engine uses for
   every projection (``nn.Linear``, src/qwen25vl_lite/text.py:61-63,80-83;
-  src/qwen25vl_lite/model.py:84); operands the tcgen05 kernel refuses (K not a multiple of 8,
-  unaligned rows) go there too.
+  src/qwen25vl_lite/model.py:84); batches of 17 to 127 rows and operands the tcgen05 kernel
+  refuses (K not a multiple of 8, unaligned rows) go there too.
 """
 
 from __future__ import annotations
@@ -26,6 +26,13 @@ import torch
 from . import kernels
 
 USE_TCGEN05 = os.environ.get("Q25VL_LARGE_GEMM", "tcgen05") != "cublas"
+# The tcgen05 kernel works in tiles of 128 rows; below that (decode batches of 17 to 127 requests)
+# too few tiles would stream the weights, and the library product is used.
+TCGEN05_MIN_ROWS = 128
+
+
+def use_tcgen05(x: torch.Tensor, w: torch.Tensor) -> bool:
+    return USE_TCGEN05 and x.shape[0] >= TCGEN05_MIN_ROWS and kernels.gemm_tcgen05_supports(x, w)
 
 
 class DeferredNorm:
@@ -67,7 +74,7 @@ class Linear:
                 return y
         if deferred:
             x = x.materialize()
-        if w.dtype == torch.bfloat16 and USE_TCGEN05 and kernels.gemm_tcgen05_supports(x, w):
+        if w.dtype == torch.bfloat16 and use_tcgen05(x, w):
             return self._tcgen05(x, out_dtype, residual)
         if w.dtype == torch.float32:
             out = torch.empty((x.shape[0], self.out_features), dtype=torch.float32, device=x.device)
