@@ -4,10 +4,10 @@
 //
 // One persistent CTA per SM, 6 warps with fixed roles:
 //   warp 0   TMA producer: one lane issues cp.async.bulk.tensor loads of a 128 x 64 tile of x and a
-//            256 x 64 tile of W (128-byte swizzle) into a ring of 4 shared-memory stages; each stage
-//            has a "full" mbarrier that counts the bytes landed;
-//   warp 1   MMA issuer: allocates 512 columns of tensor memory (two 128 x 256 float accumulators),
-//            then one lane issues tcgen05.mma (M 128, N 256, K 16) four times per stage and commits
+//            BN x 64 tile of W (128-byte swizzle; BN = 256, or 128 for small problems) into a ring
+//            of 4 (6) shared-memory stages; each stage has a "full" mbarrier that counts the bytes;
+//   warp 1   MMA issuer: allocates 2 BN columns of tensor memory (two 128 x BN float accumulators),
+//            then one lane issues tcgen05.mma (M 128, N BN, K 16) four times per stage and commits
 //            to the stage's "empty" mbarrier, and after the last K block to the accumulator's
 //            "full" mbarrier; while the epilogue drains one accumulator the next tile fills the other;
 //   warps 2-5  epilogue: each reads its quarter of the 128 accumulator rows with tcgen05.ld (a lane
@@ -332,13 +332,12 @@ static int launch_t5(const CUtensorMap& mx, const CUtensorMap& mw, const float* 
   return launch_status();
 }
 
-// Width of the feature tile: 256 keeps the tensor cores busiest, but when its tiles fill the last
-// wave of 148 SMs badly, 128-wide tiles (twice as many, each a little less efficient) finish sooner.
+// Width of the feature tile.  The 128-wide MMA does half the arithmetic for the same traffic of the
+// x operand out of shared memory and runs at about 0.7 of the 256-wide one (measured), so it is
+// only used when 256-wide tiles would leave more than half of the SMs without a tile.
 static int pick_bn(int M, int N) {
-  const long long mb = (M + T5_BM - 1) / T5_BM;
-  const long long t256 = mb * ((N + 255) / 256), t128 = mb * ((N + 127) / 128);
-  const double cost256 = (double)((t256 + 147) / 148) * 1.0, cost128 = (double)((t128 + 147) / 148) * 0.56;
-  return cost128 < cost256 ? 128 : 256;
+  const long long t256 = (long long)((M + T5_BM - 1) / T5_BM) * ((N + 255) / 256);
+  return 2 * t256 <= 148 ? 128 : 256;
 }
 
 // x: [M, K] bfloat16 with row pitch ldx; W: [N, K] bfloat16 contiguous.  epi as in gemm_skinny.cu

@@ -51,7 +51,7 @@ class SwiGLU(FeedForward):
                 h = h.materialize()
             if self.paired and kernels.gemm_skinny_supports(h, w):
                 kernels.gemm_skinny(h, w, None, act, kernels.SKINNY_SWIGLU)
-            elif self.paired and linear.use_tcgen05(h, w):
+            elif self.paired and linear.use_tcgen05(h, w, fused_epilogue=True):
                 kernels.gemm_tcgen05(h, w, None, act, kernels.SKINNY_SWIGLU)
             else:
                 kernels.silu_mul(self.gate_up_proj(h), act, self.paired)
