@@ -127,24 +127,28 @@ __device__ __forceinline__ void attend_tile(const unsigned (&qf)[D / 16][4], con
   const int lane = threadIdx.x & 31, t = lane & 3;
   float s[BN / 8][4];
 #pragma unroll
-  for (int j = 0; j < BN / 8; ++j) {
-    s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f;
-    const unsigned char* krow = ks + (j * 8 + (lane & 7)) * P;
-    if constexpr (D % 32 == 0) {
+  for (int j = 0; j < BN / 8; ++j) s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f;
+  // k-step outermost: the MMAs that follow one another go to different accumulators (one per block
+  // of 8 keys), so they do not wait for each other
+  if constexpr (D % 32 == 0) {
 #pragma unroll
-      for (int kp = 0; kp < D / 32; ++kp) {
-        unsigned b[4];
-        ldmatrix_x4(b, krow + (kp * 32 + 8 * (lane >> 3)) * 2);
-        mma_bf16(s[j], qf[2 * kp], b[0], b[1]);
-        mma_bf16(s[j], qf[2 * kp + 1], b[2], b[3]);
-      }
-    } else {
+    for (int kp = 0; kp < D / 32; ++kp) {
+      unsigned b[BN / 8][4];
 #pragma unroll
-      for (int kk = 0; kk < D / 16; ++kk) {
-        unsigned b[2];
-        ldmatrix_x2(b, krow + (kk * 16 + 8 * ((lane >> 3) & 1)) * 2);
-        mma_bf16(s[j], qf[kk], b[0], b[1]);
-      }
+      for (int j = 0; j < BN / 8; ++j) ldmatrix_x4(b[j], ks + (j * 8 + (lane & 7)) * P + (kp * 32 + 8 * (lane >> 3)) * 2);
+#pragma unroll
+      for (int j = 0; j < BN / 8; ++j) mma_bf16(s[j], qf[2 * kp], b[j][0], b[j][1]);
+#pragma unroll
+      for (int j = 0; j < BN / 8; ++j) mma_bf16(s[j], qf[2 * kp + 1], b[j][2], b[j][3]);
+    }
+  } else {
+#pragma unroll
+    for (int kk = 0; kk < D / 16; ++kk) {
+      unsigned b[BN / 8][2];
+#pragma unroll
+      for (int j = 0; j < BN / 8; ++j) ldmatrix_x2(b[j], ks + (j * 8 + (lane & 7)) * P + (kk * 16 + 8 * ((lane >> 3) & 1)) * 2);
+#pragma unroll
+      for (int j = 0; j < BN / 8; ++j) mma_bf16(s[j], qf[kk], b[j][0], b[j][1]);
     }
   }
   float mx0 = -INFINITY, mx1 = -INFINITY;

@@ -217,6 +217,8 @@ class ModelRunner:
             for i, n in enumerate(q_lens):
                 if n > 1 or G > 16:
                     pairs += [(i, t) for t in range(-(-n * G // 64))]
+            # the tiles of a run's last tokens see the most keys: they go first, the short ones fill in
+            pairs.sort(key=lambda it: -(starts[it[0]] + (it[1] + 1) * 64 // G))
             tile_lists[G] = pairs
         n_work = len(decode_list) + sum(2 * len(v) + 4 for v in tile_lists.values())
         total = (N * (2 + self.axes + len(groups)) + (S + 1) + 2 * S + M + S * sum(widths) + n_work
