@@ -214,7 +214,8 @@ def run_ours(args):
     t = cfg["text_config"]
     max_batch = 64
     llm = LLM(random_config=cfg, weights_seed=0, dtype="bfloat16", num_blocks=max_batch * CONTEXT_LEN // PAGE,
-              block_size=PAGE, max_num_seqs=max_batch, max_num_batched_tokens=8192, max_model_len=CONTEXT_LEN)
+              block_size=PAGE, max_num_seqs=max_batch, max_num_batched_tokens=8192, max_model_len=CONTEXT_LEN,
+              cuda_graph=not args.no_cuda_graph)
     runner, engine = llm.runner, llm.engine
     rng = np.random.default_rng(0)
     vocab = t["vocab_size"]
@@ -340,6 +341,7 @@ def main(argv=None):
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--layers", type=int, default=None, help="fewer layers than the model has (named in config)")
     ap.add_argument("--headline-only", action="store_true", help="skip e2e and the batch 1 / 64 points")
+    ap.add_argument("--no-cuda-graph", action="store_true", help="launch decode steps kernel by kernel (for profilers)")
     args = ap.parse_args(argv)
     if args.gpus != 1:
         print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not measured")
