@@ -4,8 +4,8 @@
 // for M multiply-adds, so the kernel is built around keeping HBM busy, not the tensor cores.
 //
 //   * One persistent CTA per SM takes groups of 16 output features (16 rows of W) in turn and walks
-//     K in chunks of 1024.  A producer warp brings each chunk into shared memory with one bulk
-//     asynchronous copy per row (cp.async.bulk, 2 KB contiguous in global memory each) that signals
+//     K in chunks of 1024 or 2048.  A producer warp brings each chunk into shared memory with one bulk
+//     asynchronous copy per row (cp.async.bulk, 2 or 4 KB contiguous in global memory each) that signals
 //     an mbarrier; a ring of stages keeps several chunks in flight, across group borders too,
 //     while the eight consumer warps work.  x is copied once and stays in shared memory when it
 //     fits; otherwise its part of each chunk travels with the chunk.
@@ -27,13 +27,14 @@
 
 enum { EPI_STORE = 0, EPI_BIAS = 1, EPI_F32 = 2, EPI_SWIGLU = 3, EPI_RESIDUAL = 4 };
 
-#define GS_KC 1024                       // K elements per chunk
 #define GS_ROWS 16
-#define GS_PITCH (GS_KC * 2 + 64)        // bytes; pitch mod 128 = 64 keeps 16-byte shared loads conflict-free
 #define GS_CONSUMERS 8
-#define GS_RED_BUFS 4                    // buffers of partial sums between the MMA warps and the epilogue warp
+#define GS_RED_BUFS 2                    // buffers of partial sums between the MMA warps and the epilogue warp
 #define GS_THREADS ((GS_CONSUMERS + 2) * 32)
-#define GS_SMEM_BUDGET (220 * 1024)
+#include <stdlib.h>
+static int gs_env(const char* name, int dflt) { const char* v = getenv(name); return v ? atoi(v) : dflt; }
+static const int GS_SMEM_BUDGET = gs_env("Q25VL_SKINNY_SMEM_KB", 220) * 1024;
+static const int GS_KC_DEFAULT = gs_env("Q25VL_SKINNY_KC", 1024);     // K elements per chunk
 #define WAIT_LIMIT (1 << 22)
 
 __device__ __forceinline__ unsigned s32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
@@ -79,30 +80,48 @@ __device__ __forceinline__ void mma16816(float (&c)[4], unsigned a0, unsigned a1
 // chunk)  |  buffers of per-warp partial sums  |  mbarriers: full[S], empty[S], x, red_full[], red_empty[].
 struct SkinnyLayout {
   int xp;            // pitch of a resident x row in bytes (0: x travels with the chunks)
+  int kc;            // K elements per chunk (a multiple of 64)
+  int pitch;         // bytes between the rows of a chunk: kc * 2 + 64, so pitch mod 128 = 64 keeps 16-byte shared loads conflict-free
   int stage_bytes;
   int n_stages;
   size_t stages_off, red_off, bar_off, total;
 };
 
-static SkinnyLayout skinny_layout(int M, int K, int MT) {
+static SkinnyLayout skinny_layout_kc(int M, int K, int MT, int kc) {
   SkinnyLayout L;
-  const int n_chunks = (K + GS_KC - 1) / GS_KC;
+  L.kc = kc;
+  L.pitch = L.kc * 2 + 64;
+  const int n_chunks = (K + L.kc - 1) / L.kc;
   const size_t red = (size_t)GS_RED_BUFS * GS_CONSUMERS * 32 * MT * 4 * sizeof(float);
   const size_t bars = 64 * sizeof(unsigned long long);
   const int xrow = K * 2 + ((K * 2) % 128 == 0 ? 64 : 0);
   const size_t resident = (size_t)M * xrow;
-  const bool fits = resident + 3 * (size_t)GS_ROWS * GS_PITCH + red + bars <= GS_SMEM_BUDGET;
+  const bool fits = resident + 2 * (size_t)GS_ROWS * L.pitch + red + bars <= (size_t)GS_SMEM_BUDGET;
   L.xp = fits ? xrow : 0;
   const size_t xbytes = fits ? (resident + 127) / 128 * 128 : 0;
-  L.stage_bytes = (GS_ROWS + (fits ? 0 : M)) * GS_PITCH;
+  L.stage_bytes = (GS_ROWS + (fits ? 0 : M)) * L.pitch;
   int s = (int)((GS_SMEM_BUDGET - xbytes - red - bars) / L.stage_bytes);
   // more stages than the chunks of four row groups would never fill
   L.n_stages = s > 4 * n_chunks ? 4 * n_chunks : (s > 24 ? 24 : s);
+  if (L.n_stages < 1) L.n_stages = 1;
   L.stages_off = xbytes;
   L.red_off = L.stages_off + (size_t)L.n_stages * L.stage_bytes;
   L.bar_off = L.red_off + red;
   L.total = L.bar_off + bars;
   return L;
+}
+
+// The copy engine of an SM takes a bulk copy about every 100 cycles whatever its size (measured on
+// B200: the time of a chunk did not change from 512-byte to 2 KB rows), so with 2 KB per row the
+// requests, not the memory, bound a long stream at about 5 TB/s.  Large products therefore move
+// 4 KB per row and request (two stages of 64 KB are in flight); small ones keep 2 KB rows, whose
+// finer ring starts and drains faster.  Whether x stays resident does not depend on the choice.
+static SkinnyLayout skinny_layout(int M, int N, int K, int MT) {
+  const SkinnyLayout small = skinny_layout_kc(M, K, MT, GS_KC_DEFAULT);
+  if (GS_KC_DEFAULT != 1024 || ((long long)N * K < (32ll << 20) && K < 4096)) return small;
+  const SkinnyLayout large = skinny_layout_kc(M, K, MT, 2048);
+  if (large.n_stages < 2 || (large.xp == 0) != (small.xp == 0) || large.total > (size_t)GS_SMEM_BUDGET) return small;
+  return large;
 }
 
 // The epilogue warp: adds the MMA warps' partial sums in warp order and stores the 16 features of
@@ -187,7 +206,8 @@ gemm_skinny_kernel(const bf16* __restrict__ W, const void* __restrict__ Xv, int 
   unsigned long long* red_empty = red_full + GS_RED_BUFS;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
-  const int n_chunks = (K + GS_KC - 1) / GS_KC;
+  const int KC = L.kc, PITCH = L.pitch;
+  const int n_chunks = (K + KC - 1) / KC;
   const int groups = (N + GS_ROWS - 1) / GS_ROWS;
   const bool resident = L.xp != 0;
   const int S = L.n_stages;
@@ -222,13 +242,13 @@ gemm_skinny_kernel(const bf16* __restrict__ W, const void* __restrict__ Xv, int 
           ok = mbar_wait(empty + s, ((it / S) - 1) & 1);
           if (!ok && lane == 0) atomicExch(err, 1);
         }
-        const unsigned bytes = (unsigned)min(GS_KC, K - c * GS_KC) * 2;
+        const unsigned bytes = (unsigned)min(KC, K - c * KC) * 2;
         unsigned char* st = stages + (size_t)s * L.stage_bytes;
         if (lane == 0) mbar_expect_tx(full + s, bytes * (GS_ROWS + (resident ? 0 : M)));
         __syncwarp();
-        if (lane < GS_ROWS) bulk_copy(st + lane * GS_PITCH, src + (size_t)c * GS_KC, bytes, full + s);
+        if (lane < GS_ROWS) bulk_copy(st + lane * PITCH, src + (size_t)c * KC, bytes, full + s);
         if (!resident && lane < M)
-          bulk_copy(st + (GS_ROWS + lane) * GS_PITCH, X + (size_t)lane * ldx + (size_t)c * GS_KC, bytes, full + s);
+          bulk_copy(st + (GS_ROWS + lane) * PITCH, X + (size_t)lane * ldx + (size_t)c * KC, bytes, full + s);
       }
     }
     return;
@@ -292,13 +312,13 @@ gemm_skinny_kernel(const bf16* __restrict__ W, const void* __restrict__ Xv, int 
         if (!ok && lane == 0) atomicExch(err, 2);
       }
       const unsigned char* st = stages + (size_t)s * L.stage_bytes;
-      const unsigned char* xb = resident ? xs + (size_t)c * GS_KC * 2 : st + GS_ROWS * GS_PITCH;
-      const int xpitch = resident ? L.xp : GS_PITCH;
-      const int kblocks = min(GS_KC, K - c * GS_KC) / 32;
+      const unsigned char* xb = resident ? xs + (size_t)c * KC * 2 : st + GS_ROWS * PITCH;
+      const int xpitch = resident ? L.xp : PITCH;
+      const int kblocks = min(KC, K - c * KC) / 32;
 #pragma unroll 2
       for (int kb = warp; kb < kblocks; kb += GS_CONSUMERS) {
-        const uint4 a0 = lds128(st + g * GS_PITCH + kb * 64 + t * 16);
-        const uint4 a1 = lds128(st + (g + 8) * GS_PITCH + kb * 64 + t * 16);
+        const uint4 a0 = lds128(st + g * PITCH + kb * 64 + t * 16);
+        const uint4 a1 = lds128(st + (g + 8) * PITCH + kb * 64 + t * 16);
 #pragma unroll
         for (int mt = 0; mt < MT; ++mt) {
           const uint4 b = lds128(xb + (size_t)xrow[mt] * xpitch + kb * 64 + t * 16);
@@ -328,11 +348,11 @@ gemm_skinny_kernel(const bf16* __restrict__ W, const void* __restrict__ Xv, int 
 template <int MT, int EPI, bool NORM>
 static int launch_skinny(const bf16* W, const void* X, int ldx, const float* norm_w, float eps, const float* bias, void* out,
                   int ldo, int M, int N, int K, int* err, cudaStream_t s) {
-  const SkinnyLayout L = skinny_layout(M, K, MT);
-  if (L.n_stages < 2 && (K + GS_KC - 1) / GS_KC > 1) return (int)cudaErrorInvalidValue;
+  const SkinnyLayout L = skinny_layout(M, N, K, MT);
+  if (L.total > (size_t)GS_SMEM_BUDGET || (L.n_stages < 2 && (K + L.kc - 1) / L.kc > 1)) return (int)cudaErrorInvalidValue;
   if (NORM && L.xp == 0) return (int)cudaErrorInvalidValue;      // the normalised rows must stay resident
   cudaError_t e = cudaFuncSetAttribute(gemm_skinny_kernel<MT, EPI, NORM>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                       GS_SMEM_BUDGET);
+                                       (int)L.total);
   if (e != cudaSuccess) return (int)e;
   const int groups = (N + GS_ROWS - 1) / GS_ROWS;
   const int grid = groups < 148 ? groups : 148;          // one persistent CTA per SM
@@ -356,7 +376,7 @@ static int launch_epi(int epi, const bf16* W, const void* X, int ldx, const floa
 // Whether x of M rows and K columns stays resident in shared memory (what the norm-fused variant needs).
 Q25_EXPORT int q25_gemm_skinny_resident(int M, int K) {
   if (M <= 0 || M > 16 || K <= 0 || K % 32) return 0;
-  return skinny_layout(M, K, M <= 8 ? 1 : 2).xp != 0;
+  return skinny_layout(M, 0, K, M <= 8 ? 1 : 2).xp != 0;
 }
 
 // epi: 0 store bf16, 1 + bias then store bf16, 2 store float, 3 SwiGLU pairs (N counts gate and up
