@@ -1,0 +1,589 @@
+// A chain of weight-streaming products in ONE persistent kernel (decode steps, at most 16 rows).
+//
+// A decode step is a chain of small products, each of which needs the whole result of the one
+// before it: o-projection -> gate/up -> down -> next layer's qkv ...  Launched one by one
+// (gemm_skinny.cu), every link pays for the end of one kernel and the start of the next: the
+// stream of weights stops, the SMs drain, the next kernel's first bytes take a memory latency to
+// arrive (measured in a step: 7 to 12 us for products whose weights pass in 1.5 us).  Here the
+// links are operations of one kernel:
+//
+//   * One CTA per SM stays resident for the whole chain (cooperative launch).  Between two
+//     operations the CTAs meet at a barrier in global memory (a counter that only grows).
+//   * The producer warp does not meet anybody: weights depend on no activation, so it walks on
+//     through the operations and fills the ring of stages with the next operation's weights while
+//     the other warps are still finishing this one or stand at the barrier.  The stream from memory
+//     does not stop at a link.
+//   * Inside an operation the work is that of gemm_skinny.cu: groups of 16 output features, the
+//     weights on the 16-row side of mma.sync m16n8k16, eight MMA warps taking alternate 32-wide
+//     k blocks, an epilogue warp adding their partial sums in warp order, x resident in shared
+//     memory (read past the L1 cache, which knows nothing of what other SMs wrote since the
+//     launch), optional RMSNorm of the float residual stream on the way in (reference
+//     src/qwen25vl_lite/layers.py:27-31), epilogues store / +bias / float / SwiGLU pairs
+//     (src/qwen25vl_lite/text.py:66) / add into the residual stream.  One request brings one row
+//     of a group, up to 4 KB (the copy engine takes a request about every 100 cycles whatever its
+//     size).
+//   * K longer than 2048 is cut into slices; a CTA works in one slice, so its slice of x fits into
+//     shared memory.  The slices' partial sums go to scratch slots, and the CTA that completes a
+//     group's counter adds them in slice order and runs the epilogue: nobody waits, and the result
+//     does not depend on timing.
+//
+// Every wait (mbarrier or grid barrier) is bounded: when it gives up, the kernel records a code in
+// *err, stops waiting anywhere and runs to its end (its output is then invalid).
+#include "common.cuh"
+
+enum { EPI_STORE = 0, EPI_BIAS = 1, EPI_F32 = 2, EPI_SWIGLU = 3, EPI_RESIDUAL = 4 };
+
+#define GC_ROWS 16
+#define GC_CONSUMERS 8
+#define GC_RED_BUFS 2
+#define GC_THREADS ((GC_CONSUMERS + 2) * 32)
+#define GC_MAX_OPS 8
+#define GC_SLICE_K 2048                          // most K elements of a slice
+#define GC_PITCH (GC_SLICE_K * 2 + 64)           // bytes between rows in shared memory; mod 128 = 64: no bank conflicts
+#define GC_SLOT (GC_ROWS * GC_PITCH)             // one stage: the 16 rows of a group, one slice long
+#define GC_SMS 148
+#define GC_SMEM_LIMIT (227 * 1024)
+#define GC_WAIT_LIMIT (1 << 22)
+#define GC_GRID_WAIT_LIMIT (1 << 21)             // polls of global memory, about a second
+
+struct ChainOp {
+  const bf16* W;          // [N, K]
+  const void* X;          // bf16 [M, K], or float [M, K] when norm
+  const float* norm_w;    // [K] when norm
+  const float* bias;      // [N] when epi == EPI_BIAS
+  void* out;
+  int ldx, ldo, M, N, K, epi, norm;
+  float eps;
+  int slices, slice_k, ctas, groups;   // K cut into `slices` of `slice_k` elements; `ctas` CTAs work in each slice
+};
+
+struct ChainArgs {
+  int n_ops, n_stages;
+  int x_bytes;            // shared memory kept for x: rows * GC_PITCH
+  float* scratch;         // slots of partial sums, [slice][group][MT * 128] floats, reused by every operation
+  int* counters;          // one per group, zero before the launch and after it
+  unsigned* barrier;      // arrivals at the barriers between operations; only grows
+  unsigned barrier_base;  // its value when this launch begins
+  int* err;
+  ChainOp op[GC_MAX_OPS];
+};
+
+__device__ __forceinline__ unsigned gc_s32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void gc_mbar_init(unsigned long long* bar, int count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(gc_s32(bar)), "r"(count));
+}
+__device__ __forceinline__ void gc_expect_tx(unsigned long long* bar, unsigned bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(gc_s32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void gc_arrive(unsigned long long* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(gc_s32(bar)) : "memory");
+}
+__device__ __forceinline__ bool gc_wait(unsigned long long* bar, unsigned parity) {
+  for (int i = 0; i < GC_WAIT_LIMIT; ++i) {
+    unsigned done;
+    asm volatile(
+        "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
+        : "=r"(done) : "r"(gc_s32(bar)), "r"(parity) : "memory");
+    if (done) return true;
+  }
+  return false;
+}
+__device__ __forceinline__ void gc_bulk_copy(void* dst, const void* src, unsigned bytes, unsigned long long* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n"
+               ::"r"(gc_s32(dst)), "l"(src), "r"(bytes), "r"(gc_s32(bar)) : "memory");
+}
+__device__ __forceinline__ uint4 gc_lds128(const void* p) {
+  uint4 v;
+  asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];\n" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(gc_s32(p)));
+  return v;
+}
+__device__ __forceinline__ float4 gc_ldcg128(const float* p) {
+  float4 v;
+  asm volatile("ld.global.cg.v4.f32 {%0,%1,%2,%3}, [%4];\n" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(p));
+  return v;
+}
+__device__ __forceinline__ unsigned gc_ld_acquire(const unsigned* p) {
+  unsigned v;
+  asm volatile("ld.acquire.gpu.global.u32 %0, [%1];\n" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void gc_mma(float (&c)[4], unsigned a0, unsigned a1, unsigned a2, unsigned a3, unsigned b0,
+                                       unsigned b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// accumulator (mt, e): output feature row0 + g + 8 * (e / 2), batch column mt * 8 + 2 t + (e & 1)
+template <int MT>
+__device__ __forceinline__ void gc_store_group(const float (&acc)[MT][4], int grp, const ChainOp& op, bool has_old = false) {
+  const int lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+  const int row0 = grp * GC_ROWS;
+#pragma unroll
+  for (int mt = 0; mt < MT; ++mt) {
+#pragma unroll
+    for (int e = 0; e < 2; ++e) {
+      const int m = mt * 8 + 2 * t + e;
+      if (m >= op.M) continue;
+      if (op.epi == EPI_SWIGLU) {
+        // rows g of the group are gate features, rows g + 8 the matching up features
+        if (row0 + g + 8 < op.N) {
+          const float gate = acc[mt][e], up = acc[mt][e + 2];
+          reinterpret_cast<bf16*>(op.out)[(size_t)m * op.ldo + (row0 >> 1) + g] =
+              __float2bfloat16_rn(gate / (1.0f + __expf(-gate)) * up);
+        }
+        continue;
+      }
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        const int n = row0 + g + 8 * h;
+        if (n >= op.N) continue;
+        float v = acc[mt][e + 2 * h];
+        if (op.epi == EPI_BIAS) v += op.bias[n];
+        if (op.epi == EPI_F32) reinterpret_cast<float*>(op.out)[(size_t)m * op.ldo + n] = v;
+        else if (op.epi == EPI_RESIDUAL) {
+          float* dst = reinterpret_cast<float*>(op.out) + (size_t)m * op.ldo + n;
+          *dst = has_old ? v : __ldcg(dst) + v;       // has_old: the old value is in v already
+        }
+        else reinterpret_cast<bf16*>(op.out)[(size_t)m * op.ldo + n] = __float2bfloat16_rn(v);
+      }
+    }
+  }
+}
+
+template <int MT>
+__global__ void __launch_bounds__(GC_THREADS, 1) gemm_chain_kernel(const __grid_constant__ ChainArgs A) {
+  extern __shared__ __align__(128) unsigned char smem[];
+  const int S = A.n_stages;
+  unsigned char* xs = smem;
+  unsigned char* slots = smem + A.x_bytes;
+  float* red = reinterpret_cast<float*>(slots + (size_t)S * GC_SLOT);
+  unsigned long long* full = reinterpret_cast<unsigned long long*>(red + GC_RED_BUFS * GC_CONSUMERS * 32 * MT * 4);
+  unsigned long long* empty = full + S;
+  unsigned long long* go = empty + S;             // the operation before this one is complete on every CTA
+  unsigned long long* red_full = go + 1;
+  unsigned long long* red_empty = red_full + GC_RED_BUFS;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+  const int cta = blockIdx.x;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < S; ++s) {
+      gc_mbar_init(full + s, 1);
+      gc_mbar_init(empty + s, GC_CONSUMERS);
+    }
+    gc_mbar_init(go, 1);
+    for (int b = 0; b < GC_RED_BUFS; ++b) {
+      gc_mbar_init(red_full + b, GC_CONSUMERS);
+      gc_mbar_init(red_empty + b, 1);
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+  }
+  __syncthreads();
+
+  if (warp == GC_CONSUMERS) {
+    // ---- producer: the weights of every operation, one bulk copy per row, as stages come free ----
+    bool ok = true;
+    int s = 0, wrapped = 0;
+    unsigned parity = 1;
+    for (int k = 0; k < A.n_ops; ++k) {
+      const ChainOp& op = A.op[k];
+      const int slice = cta / op.ctas, r = cta - slice * op.ctas;
+      if (slice >= op.slices) continue;
+      const int k0 = slice * op.slice_k;
+      const unsigned bytes = (unsigned)min(op.slice_k, op.K - k0) * 2;
+      for (int grp = r; grp < op.groups; grp += op.ctas) {
+        if (wrapped && ok) {
+          ok = gc_wait(empty + s, parity);
+          if (!ok && lane == 0) atomicExch(A.err, 11);
+        }
+        unsigned char* st = slots + (size_t)s * GC_SLOT;
+        if (lane == 0) gc_expect_tx(full + s, bytes * GC_ROWS);
+        __syncwarp();
+        if (lane < GC_ROWS)
+          gc_bulk_copy(st + lane * GC_PITCH, op.W + (size_t)min(grp * GC_ROWS + lane, op.N - 1) * op.K + k0, bytes, full + s);
+        if (++s == S) { s = 0; wrapped = 1; parity ^= 1; }
+      }
+    }
+    return;
+  }
+
+  if (warp == GC_CONSUMERS + 1) {
+    // ---- epilogue warp: grid barrier, x, sums of the MMA warps' partial sums, stores ----
+    bool ok = true;
+    int rb = 0;
+    unsigned red_parity = 0;
+    for (int k = 0; k < A.n_ops; ++k) {
+      const ChainOp& op = A.op[k];
+      if (k > 0) {
+        // everything the operation before this one wrote, on every CTA, before anybody reads it
+        __threadfence();
+        __syncwarp();
+        if (lane == 0) {
+          // The counter only grows: the k-th barrier of this launch is passed when it has reached
+          // base + k * (number of CTAs).  The last arrival itself lets everybody go; nothing is
+          // reset and no second flag is written (the caller zeroes the counter between steps).
+          asm volatile("red.release.gpu.global.add.u32 [%0], 1;\n" ::"l"(A.barrier) : "memory");
+          if (ok) {
+            const unsigned target = A.barrier_base + (unsigned)k * gridDim.x;
+            int i = 0;
+            while ((int)(gc_ld_acquire(A.barrier) - target) < 0 && ++i < GC_GRID_WAIT_LIMIT) {}
+            if (i >= GC_GRID_WAIT_LIMIT) { ok = false; atomicExch(A.err, 16); }
+          }
+          gc_arrive(go);
+        }
+        ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+      }
+      const int slice = cta / op.ctas, r = cta - slice * op.ctas;
+      if (slice >= op.slices) continue;
+      const bool add_old = op.epi == EPI_RESIDUAL && op.slices == 1;
+      for (int grp = r; grp < op.groups; grp += op.ctas) {
+        float acc[MT][4];
+#pragma unroll
+        for (int mt = 0; mt < MT; ++mt) acc[mt][0] = acc[mt][1] = acc[mt][2] = acc[mt][3] = 0.f;
+        if (add_old) {
+          // the residual stream's old values, fetched while the MMA warps still work on the group
+#pragma unroll
+          for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              const int m = mt * 8 + 2 * (lane & 3) + (e & 1), n = grp * GC_ROWS + (lane >> 2) + 8 * (e >> 1);
+              if (m < op.M && n < op.N) acc[mt][e] = __ldcg(reinterpret_cast<const float*>(op.out) + (size_t)m * op.ldo + n);
+            }
+        }
+        if (ok) {
+          ok = gc_wait(red_full + rb, red_parity);
+          if (!ok && lane == 0) atomicExch(A.err, 15);
+        }
+#pragma unroll
+        for (int w = 0; w < GC_CONSUMERS; ++w) {
+          const float* src = red + (((size_t)rb * GC_CONSUMERS + w) * 32 + lane) * MT * 4;
+#pragma unroll
+          for (int mt = 0; mt < MT; ++mt) {
+            const float4 v = *reinterpret_cast<const float4*>(src + mt * 4);
+            acc[mt][0] += v.x; acc[mt][1] += v.y; acc[mt][2] += v.z; acc[mt][3] += v.w;
+          }
+        }
+        __syncwarp();
+        if (lane == 0) gc_arrive(red_empty + rb);
+        if (++rb == GC_RED_BUFS) { rb = 0; red_parity ^= 1; }
+
+        if (op.slices > 1) {
+          // a slice's share of the group: into its scratch slot; who completes the group is settled
+          // once for all groups, after the last one (one trip to memory, not one per group)
+          float* mine = A.scratch + ((size_t)slice * op.groups + grp) * (MT * 128);
+#pragma unroll
+          for (int mt = 0; mt < MT; ++mt)
+            *reinterpret_cast<float4*>(mine + mt * 128 + lane * 4) = make_float4(acc[mt][0], acc[mt][1], acc[mt][2], acc[mt][3]);
+          continue;
+        }
+        gc_store_group<MT>(acc, grp, op, add_old);
+      }
+      if (op.slices > 1) {
+        // Every slice's CTA counts its groups in; the i-th group of CTA r's list is finished by the
+        // CTA of slice (i + r) mod slices, which waits (bounded) until all slices are in, adds their
+        // shares in slice order and runs the epilogue.  All slices end at about the same time, so
+        // the wait is short, and every CTA finishes its share of the groups.
+        __threadfence();
+        __syncwarp();
+        const int n_mine = (op.groups - r + op.ctas - 1) / op.ctas;
+        for (int base = 0; base < n_mine; base += 32) {
+          const int i_mine = base + lane;
+          const bool valid = i_mine < n_mine;
+          const int my_grp = r + i_mine * op.ctas;
+          if (valid) atomicAdd(A.counters + my_grp, 1);
+          const bool owner = valid && (i_mine + r) % op.slices == slice;
+          if (owner && ok) {
+            int i = 0;
+            while ((int)gc_ld_acquire(reinterpret_cast<const unsigned*>(A.counters + my_grp)) != op.slices &&
+                   ++i < GC_GRID_WAIT_LIMIT) {}
+            if (i >= GC_GRID_WAIT_LIMIT) { ok = false; atomicExch(A.err, 18); }
+          }
+          if (owner) A.counters[my_grp] = 0;
+          ok = __all_sync(0xffffffffu, ok);
+          unsigned todo = __ballot_sync(0xffffffffu, owner);
+          while (todo) {
+            const int i = __ffs(todo) - 1;
+            todo &= todo - 1;
+            const int grp = r + (base + i) * op.ctas;
+            float acc[MT][4];
+#pragma unroll
+            for (int mt = 0; mt < MT; ++mt) acc[mt][0] = acc[mt][1] = acc[mt][2] = acc[mt][3] = 0.f;
+            const float4* slot = reinterpret_cast<const float4*>(A.scratch + (size_t)grp * (MT * 128)) + lane;
+            const size_t slice_stride = (size_t)op.groups * (MT * 32);                     // in float4
+#pragma unroll 8
+            for (int j = 0; j < op.slices; ++j) {                                          // in slice order, whoever adds
+#pragma unroll
+              for (int mt = 0; mt < MT; ++mt) {
+                const float4 v = __ldcg(slot + (size_t)j * slice_stride + mt * 32);
+                acc[mt][0] += v.x; acc[mt][1] += v.y; acc[mt][2] += v.z; acc[mt][3] += v.w;
+              }
+            }
+            gc_store_group<MT>(acc, grp, op);
+          }
+        }
+      }
+    }
+    return;
+  }
+
+  // ---- MMA warps ----
+  bool ok = true;
+  int s = 0, rb = 0;
+  unsigned parity = 0, red_parity = 1;
+  bool red_wrapped = false;
+  for (int k = 0; k < A.n_ops; ++k) {
+    const ChainOp& op = A.op[k];
+    if (k > 0 && ok) {
+      ok = gc_wait(go, (unsigned)(k - 1) & 1);
+      if (!ok && lane == 0) atomicExch(A.err, 12);
+    }
+    const int slice = cta / op.ctas, r = cta - slice * op.ctas;
+    if (slice >= op.slices) continue;
+    const int k0 = slice * op.slice_k;
+    const int klen = min(op.slice_k, op.K - k0);
+    // x is read past L1 (__ldcg): other SMs wrote it since this kernel began.  The loads of a batch
+    // are issued together; one by one, each would cost a trip to L2.
+    if (op.norm) {
+      const float* Xf = reinterpret_cast<const float*>(op.X);
+      for (int m = warp; m < op.M; m += GC_CONSUMERS) {
+        const float4* xr = reinterpret_cast<const float4*>(Xf + (size_t)m * op.ldx);
+        const int n4 = op.K / 4;
+        const float4* w4 = reinterpret_cast<const float4*>(op.norm_w + k0);
+        unsigned char* dst = xs + (size_t)m * GC_PITCH;
+        if (n4 <= 32 * 16) {
+          // the whole row in registers: one trip to L2 for the statistics and the values
+          float4 v[16];
+          float ss = 0.f;
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            const int i = j * 32 + lane;
+            v[j] = i < n4 ? __ldcg(xr + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+          }
+#pragma unroll
+          for (int j = 0; j < 16; ++j) ss += v[j].x * v[j].x + v[j].y * v[j].y + v[j].z * v[j].z + v[j].w * v[j].w;
+          const float inv = rsqrtf(warp_sum(ss) / (float)op.K + op.eps);
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            const int i = j * 32 + lane;                      // slices == 1 here: k0 == 0, klen == K
+            if (i >= n4) continue;
+            const float4 w = w4[i];
+            __nv_bfloat162 lo = __floats2bfloat162_rn(v[j].x * inv * w.x, v[j].y * inv * w.y);
+            __nv_bfloat162 hi = __floats2bfloat162_rn(v[j].z * inv * w.z, v[j].w * inv * w.w);
+            uint2 packed;
+            packed.x = *reinterpret_cast<unsigned*>(&lo);
+            packed.y = *reinterpret_cast<unsigned*>(&hi);
+            *reinterpret_cast<uint2*>(dst + (size_t)i * 8) = packed;
+          }
+          continue;
+        }
+        float ss = 0.f;
+        for (int i0 = 0; i0 < n4; i0 += 32 * 8) {
+          float4 v[8];
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            const int i = i0 + j * 32 + lane;
+            v[j] = i < n4 ? __ldcg(xr + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+          }
+#pragma unroll
+          for (int j = 0; j < 8; ++j) ss += v[j].x * v[j].x + v[j].y * v[j].y + v[j].z * v[j].z + v[j].w * v[j].w;
+        }
+        const float inv = rsqrtf(warp_sum(ss) / (float)op.K + op.eps);
+        const float4* xs4 = xr + k0 / 4;
+        const int s4 = klen / 4;
+        for (int i0 = 0; i0 < s4; i0 += 32 * 8) {
+          float4 v[8];
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            const int i = i0 + j * 32 + lane;
+            v[j] = i < s4 ? __ldcg(xs4 + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+          }
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            const int i = i0 + j * 32 + lane;
+            if (i >= s4) continue;
+            const float4 w = w4[i];
+            __nv_bfloat162 lo = __floats2bfloat162_rn(v[j].x * inv * w.x, v[j].y * inv * w.y);
+            __nv_bfloat162 hi = __floats2bfloat162_rn(v[j].z * inv * w.z, v[j].w * inv * w.w);
+            uint2 packed;
+            packed.x = *reinterpret_cast<unsigned*>(&lo);
+            packed.y = *reinterpret_cast<unsigned*>(&hi);
+            *reinterpret_cast<uint2*>(dst + (size_t)i * 8) = packed;
+          }
+        }
+      }
+    } else {
+      const bf16* X = reinterpret_cast<const bf16*>(op.X);
+      for (int m = warp; m < op.M; m += GC_CONSUMERS) {
+        const uint4* xr = reinterpret_cast<const uint4*>(X + (size_t)m * op.ldx + k0);
+        const int n16 = klen / 8;
+        for (int i0 = 0; i0 < n16; i0 += 32 * 8) {
+          uint4 v[8];
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            const int i = i0 + j * 32 + lane;
+            v[j] = i < n16 ? __ldcg(xr + i) : make_uint4(0, 0, 0, 0);
+          }
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            const int i = i0 + j * 32 + lane;
+            if (i < n16) *reinterpret_cast<uint4*>(xs + (size_t)m * GC_PITCH + (size_t)i * 16) = v[j];
+          }
+        }
+      }
+    }
+    asm volatile("bar.sync 1, %0;\n" ::"n"(GC_CONSUMERS * 32) : "memory");
+    // rows of x this thread reads for each 8-column tile (rows past M repeat the last one; their
+    // columns are never stored)
+    const unsigned char* xrow[MT];
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt) xrow[mt] = xs + (size_t)min(mt * 8 + g, op.M - 1) * GC_PITCH + t * 16;
+    const int kblocks = klen / 32;
+
+    for (int grp = r; grp < op.groups; grp += op.ctas) {
+      float acc[2][MT][4];
+#pragma unroll
+      for (int j = 0; j < 2; ++j)
+#pragma unroll
+        for (int mt = 0; mt < MT; ++mt) acc[j][mt][0] = acc[j][mt][1] = acc[j][mt][2] = acc[j][mt][3] = 0.f;
+      if (ok) {
+        ok = gc_wait(full + s, parity);
+        if (!ok && lane == 0) atomicExch(A.err, 14);
+      }
+      const unsigned char* st = slots + (size_t)s * GC_SLOT + g * GC_PITCH + t * 16;
+#pragma unroll 2
+      for (int kb = warp; kb < kblocks; kb += GC_CONSUMERS) {
+        const uint4 a0 = gc_lds128(st + kb * 64);
+        const uint4 a1 = gc_lds128(st + 8 * GC_PITCH + kb * 64);
+#pragma unroll
+        for (int mt = 0; mt < MT; ++mt) {
+          const uint4 b = gc_lds128(xrow[mt] + kb * 64);
+          gc_mma(acc[0][mt], a0.x, a1.x, a0.y, a1.y, b.x, b.y);
+          gc_mma(acc[1][mt], a0.z, a1.z, a0.w, a1.w, b.z, b.w);
+        }
+      }
+      __syncwarp();
+      if (lane == 0) gc_arrive(empty + s);
+      if (++s == S) { s = 0; parity ^= 1; }
+
+      // hand the partial sums to the epilogue warp
+      if (red_wrapped && ok) {
+        ok = gc_wait(red_empty + rb, red_parity);
+        if (!ok && lane == 0) atomicExch(A.err, 17);
+      }
+      float* dst = red + (((size_t)rb * GC_CONSUMERS + warp) * 32 + lane) * MT * 4;
+#pragma unroll
+      for (int mt = 0; mt < MT; ++mt)
+        *reinterpret_cast<float4*>(dst + mt * 4) = make_float4(acc[0][mt][0] + acc[1][mt][0], acc[0][mt][1] + acc[1][mt][1],
+                                                               acc[0][mt][2] + acc[1][mt][2], acc[0][mt][3] + acc[1][mt][3]);
+      __syncwarp();
+      if (lane == 0) gc_arrive(red_full + rb);
+      if (++rb == GC_RED_BUFS) { rb = 0; red_wrapped = true; red_parity ^= 1; }
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// The description of one operation as the caller gives it (plain C layout, read through ctypes).
+struct ChainOpDesc {
+  const void* W;
+  const void* X;
+  const float* norm_w;
+  const float* bias;
+  void* out;
+  int ldx, ldo, M, N, K, epi, norm;
+  float eps;
+  int reserved;
+};
+
+static bool chain_cut(const ChainOpDesc& d, ChainOp& op) {
+  if (d.M <= 0 || d.M > 16 || d.N <= 0 || d.K <= 0 || d.K % 32) return false;
+  if (((unsigned long long)d.W & 15) || ((unsigned long long)d.X & 15)) return false;
+  if (d.norm ? (d.ldx % 4 || !d.norm_w) : (d.ldx % 8 != 0)) return false;
+  if ((d.epi == EPI_SWIGLU && d.N % 16) || (d.epi == EPI_BIAS && !d.bias) || d.epi < 0 || d.epi > EPI_RESIDUAL) return false;
+  op.W = (const bf16*)d.W; op.X = d.X; op.norm_w = d.norm_w; op.bias = d.bias; op.out = d.out;
+  op.ldx = d.ldx; op.ldo = d.ldo; op.M = d.M; op.N = d.N; op.K = d.K; op.epi = d.epi; op.norm = d.norm; op.eps = d.eps;
+  op.groups = (d.N + GC_ROWS - 1) / GC_ROWS;
+  op.slices = (d.K + GC_SLICE_K - 1) / GC_SLICE_K;
+  op.slice_k = ((d.K + op.slices - 1) / op.slices + 31) / 32 * 32;      // nearly equal slices, whole k blocks
+  if (op.slices > GC_SMS || (long long)(op.slices - 1) * op.slice_k >= d.K) return false;
+  op.ctas = GC_SMS / op.slices;
+  if (op.ctas > op.groups) op.ctas = op.groups;
+  return true;
+}
+
+// Shared memory of the kernel for rows of x up to `rows` (8 or 16): stages that fit, and the total.
+static int chain_smem(int rows, int& n_stages, int& x_bytes) {
+  const int MT = rows <= 8 ? 1 : 2;
+  x_bytes = rows * GC_PITCH;
+  const int red = GC_RED_BUFS * GC_CONSUMERS * 32 * MT * 4 * (int)sizeof(float);
+  const int bars = 64 * (int)sizeof(unsigned long long);
+  n_stages = (GC_SMEM_LIMIT - x_bytes - red - bars) / GC_SLOT;
+  if (n_stages > 24) n_stages = 24;
+  return x_bytes + n_stages * GC_SLOT + red + bars;
+}
+
+// Floats of scratch that a chain needs (0: no operation cuts K).
+Q25_EXPORT long long q25_gemm_chain_scratch_floats(const ChainOpDesc* ops, int n_ops) {
+  long long most = 0;
+  for (int i = 0; i < n_ops; ++i) {
+    ChainOp op;
+    if (!chain_cut(ops[i], op)) return -1;
+    if (op.slices > 1) {
+      const long long need = (long long)op.slices * op.groups * (ops[i].M <= 8 ? 1 : 2) * 128;
+      if (need > most) most = need;
+    }
+  }
+  return most;
+}
+
+// Whether the device can hold the whole grid at once (one CTA per SM), which the barrier needs.
+Q25_EXPORT int q25_gemm_chain_available(void) {
+  static int known = -1;
+  if (known >= 0) return known;
+  int dev = 0, coop = 0, sms = 0, smem = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return 0;
+  cudaDeviceGetAttribute(&coop, cudaDevAttrCooperativeLaunch, dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  cudaDeviceGetAttribute(&smem, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev);
+  known = (coop && sms >= GC_SMS && smem >= GC_SMEM_LIMIT) ? 1 : 0;
+  return known;
+}
+
+// Runs ops[0 .. n_ops) (at most 8, each at most 16 rows) as one kernel; every operation may read
+// what the ones before it wrote.  scratch: q25_gemm_chain_scratch_floats() floats; counters: 65536
+// ints, zero; barrier: one unsigned int whose value when the launch begins is barrier_base (each
+// launch adds (n_ops - 1) * 148 to it); err: one int that receives a nonzero code if a wait gave up.
+Q25_EXPORT int q25_gemm_chain_bf16(const ChainOpDesc* ops, int n_ops, float* scratch, int* counters, unsigned* barrier,
+                                   unsigned barrier_base, int* err, void* stream) {
+  if (n_ops <= 0) return 0;
+  if (n_ops > GC_MAX_OPS || !counters || !barrier || !err || !q25_gemm_chain_available()) return (int)cudaErrorInvalidValue;
+  ChainArgs A;
+  A.n_ops = n_ops;
+  A.scratch = scratch; A.counters = counters; A.barrier = barrier; A.barrier_base = barrier_base; A.err = err;
+  int rows = 0;
+  for (int i = 0; i < n_ops; ++i) {
+    if (!chain_cut(ops[i], A.op[i])) return (int)cudaErrorInvalidValue;
+    if (A.op[i].groups > 65536 || (A.op[i].slices > 1 && !scratch)) return (int)cudaErrorInvalidValue;
+    if (ops[i].M > rows) rows = ops[i].M;
+  }
+  rows = rows <= 8 ? 8 : 16;
+  const int total = chain_smem(rows, A.n_stages, A.x_bytes);
+  if (A.n_stages < 2) return (int)cudaErrorInvalidValue;
+  void (*kernel)(const ChainArgs) = rows <= 8 ? gemm_chain_kernel<1> : gemm_chain_kernel<2>;
+  cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, total);
+  if (e != cudaSuccess) return (int)e;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(GC_SMS);
+  cfg.blockDim = dim3(GC_THREADS);
+  cfg.dynamicSmemBytes = (size_t)total;
+  cfg.stream = (cudaStream_t)stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeCooperative;
+  attr[0].val.cooperative = (getenv("Q25VL_CHAIN_COOP") && getenv("Q25VL_CHAIN_COOP")[0] == '0') ? 0 : 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  e = cudaLaunchKernelEx(&cfg, kernel, A);
+  if (e == cudaSuccess) e = cudaGetLastError();
+  return (int)e;
+}

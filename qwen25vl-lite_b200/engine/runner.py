@@ -169,17 +169,27 @@ class ModelRunner:
         if hit is None:
             if len(self._graphs) >= MAX_GRAPHS:
                 self._graphs.pop(next(iter(self._graphs)))
-            self.model.forward(ctx)
+            self._forward_chained(ctx)
             graph = torch.cuda.CUDAGraph()
             before = kernels.launch_count()
             with torch.cuda.graph(graph):
-                logits = self.model.forward(ctx)
+                logits = self._forward_chained(ctx)
             hit = (graph, logits, layout, kernels.launch_count() - before)
             self._graphs[key] = hit
         hit[0].replay()
         kernels.count_replayed(hit[3])
         self.graph_replays += 1
         return hit[1]
+
+    def _forward_chained(self, ctx: StepContext) -> torch.Tensor:
+        """The model's forward with the weight-streaming products of consecutive parts gathered
+        into single persistent kernels (``kernels.chain_begin``).  Only for steps whose forward
+        launches nothing but this engine's kernels, which is what ``graph_safe`` mixers promise."""
+        kernels.chain_begin()
+        try:
+            return self.model.forward(ctx)
+        finally:
+            kernels.chain_end()
 
     def step(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
         """Runs the tokens the entries bring, as one batch.  Returns float32 logits

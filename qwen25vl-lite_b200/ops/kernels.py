@@ -59,6 +59,8 @@ def load_library(name: str = "core") -> ctypes.CDLL:
 
 
 def _fn(symbol: str, argtypes, library: str = "core"):
+    if _chain and symbol not in _CHAIN_SAFE:
+        chain_flush()                       # products that wait in the chain come before this kernel
     f = _fns.get(symbol)
     if f is None:
         lib = load_library(library)
@@ -305,6 +307,8 @@ def gemm_skinny(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], 
     if not gemm_skinny_supports(x, w) or w.shape[1] != k or not w.is_contiguous():
         raise KernelError(f"gemm_skinny: unsupported operands {tuple(x.shape)} {x.dtype} x {tuple(w.shape)} {w.dtype}")
     _skinny_out(out, m, n, epilogue, "gemm_skinny")
+    if _chain is not None and _chain_add(x, None, 0.0, w, bias, out, epilogue):
+        return
     _check(_fn("q25_gemm_skinny_bf16", _UNTYPED["q25_gemm_skinny_bf16"])(
         w.data_ptr(), x.data_ptr(), x.stride(0), _ptr(bias), out.data_ptr(), out.stride(0), m, n, k, int(epilogue),
         error_flag(x.device).data_ptr(), _stream()), "gemm_skinny")
@@ -334,9 +338,112 @@ def gemm_skinny_norm(x: torch.Tensor, norm_weight: torch.Tensor, eps: float, w: 
         raise KernelError(f"gemm_skinny_norm: unsupported operands {tuple(x.shape)} {x.dtype} x {tuple(w.shape)} {w.dtype}")
     _dev(norm_weight, torch.float32, "gemm_skinny_norm norm weight")
     _skinny_out(out, m, n, epilogue, "gemm_skinny_norm")
+    if _chain is not None and _chain_add(x, norm_weight, eps, w, bias, out, epilogue):
+        return
     _check(_fn("q25_gemm_skinny_norm_bf16", [_P, _P, _I, _P, _F, _P, _P, _I, _I, _I, _I, _I, _P, _P])(
         w.data_ptr(), x.data_ptr(), x.stride(0), norm_weight.data_ptr(), float(eps), _ptr(bias), out.data_ptr(),
         out.stride(0), m, n, k, int(epilogue), error_flag(x.device).data_ptr(), _stream()), "gemm_skinny_norm")
+
+
+# ---- chains of weight-streaming products -------------------------------------------------------
+# Between ``chain_begin`` and ``chain_end`` the weight-streaming products are not launched one by
+# one: they wait in a list, and the list runs as ONE persistent kernel (``csrc/gemm_chain.cu``) as
+# soon as any other kernel of this module is asked for, so that the order of all kernels is the
+# order of the calls.  Only kernels of this module may be launched meanwhile; whoever runs a
+# library operator on the stream in between calls ``chain_flush`` first.
+
+
+class _ChainOpDesc(ctypes.Structure):
+    _fields_ = [("W", _P), ("X", _P), ("norm_w", _P), ("bias", _P), ("out", _P), ("ldx", _I), ("ldo", _I), ("M", _I),
+                ("N", _I), ("K", _I), ("epi", _I), ("norm", _I), ("eps", _F), ("reserved", _I)]
+
+
+CHAIN_MAX_OPS = 8
+CHAIN_GRID = 148                          # CTAs of the chain kernel: one per SM of a B200
+_chain_base = 0                           # value of the barrier counter when the next chain kernel begins
+_CHAIN_SAFE = {"q25_gemm_chain_bf16", "q25_gemm_chain_scratch_floats", "q25_gemm_chain_available",
+               "q25_gemm_skinny_resident", "q25_gemm_skinny_bf16", "q25_gemm_skinny_norm_bf16"}
+_chain: Optional[list] = None             # the waiting products: (description, tensors kept alive, replay as one kernel)
+_chain_state: Dict[torch.device, tuple] = {}
+_chain_scratch: Dict[torch.device, list] = {}
+
+
+def chain_available() -> bool:
+    """Whether chains can run here: a whole grid resident at once, and not switched off
+    (``Q25VL_GEMM_CHAIN=0``)."""
+    import os
+    if os.environ.get("Q25VL_GEMM_CHAIN", "1") == "0" or not torch.cuda.is_available():
+        return False
+    return bool(_fn("q25_gemm_chain_available", [])())
+
+
+def chain_begin() -> bool:
+    """Starts gathering.  The counter of the kernels' barrier starts from zero in every gathering
+    (a memset on the stream), so the values that a captured graph carries hold in every replay."""
+    global _chain, _chain_base
+    if _chain is None and chain_available():
+        _chain, _chain_base = [], 0
+        device = torch.device("cuda", torch.cuda.current_device())
+        _chain_buffers(device)[1].zero_()
+    return _chain is not None
+
+
+def _chain_buffers(device: torch.device):
+    state = _chain_state.get(device)
+    if state is None:
+        state = _chain_state[device] = (torch.zeros(65536, dtype=torch.int32, device=device),
+                                        torch.zeros(1, dtype=torch.int32, device=device))
+    return state
+
+
+def chain_end() -> None:
+    global _chain
+    if _chain is not None:
+        chain_flush()
+        _chain = None
+
+
+def _chain_add(x, norm_weight, eps, w, bias, out, epilogue) -> bool:
+    desc = _ChainOpDesc(w.data_ptr(), x.data_ptr(), _ptr(norm_weight), _ptr(bias), out.data_ptr(), x.stride(0),
+                        out.stride(0), x.shape[0], w.shape[0], w.shape[1], int(epilogue), 0 if norm_weight is None else 1,
+                        float(eps), 0)
+    _chain.append((desc, (x, norm_weight, w, bias, out)))
+    if len(_chain) == CHAIN_MAX_OPS:
+        chain_flush()
+    return True
+
+
+def chain_flush() -> None:
+    """Runs the products that wait, in order, as one kernel (a single one runs as itself)."""
+    global _chain, _chain_base
+    if not _chain:
+        return
+    waiting, _chain = _chain, None            # the launches below must not gather again
+    try:
+        if len(waiting) == 1:
+            desc, (x, norm_weight, w, bias, out) = waiting[0]
+            if norm_weight is None:
+                gemm_skinny(x, w, bias, out, desc.epi)
+            else:
+                gemm_skinny_norm(x, norm_weight, desc.eps, w, bias, out, desc.epi)
+            return
+        device = waiting[0][1][4].device
+        ops = (_ChainOpDesc * len(waiting))(*[d for d, _ in waiting])
+        need = _fn("q25_gemm_chain_scratch_floats", [_P, _I])
+        need.restype = ctypes.c_longlong
+        floats = need(ctypes.cast(ops, _P), len(waiting))
+        if floats < 0:
+            raise KernelError("gemm_chain: a product of the chain cannot be cut")
+        held = _chain_scratch.setdefault(device, [])       # never freed or moved: captured graphs keep the addresses
+        if not held or held[-1].numel() < max(floats, 1):
+            held.append(torch.empty(max(floats, 1), dtype=torch.float32, device=device))
+        counters, barrier = _chain_buffers(device)
+        _check(_fn("q25_gemm_chain_bf16", [_P, _I, _P, _P, _P, ctypes.c_uint, _P, _P])(
+            ctypes.cast(ops, _P), len(waiting), held[-1].data_ptr(), counters.data_ptr(), barrier.data_ptr(),
+            _chain_base, error_flag(device).data_ptr(), _stream()), "gemm_chain")
+        _chain_base = (_chain_base + (len(waiting) - 1) * CHAIN_GRID) & 0xFFFFFFFF
+    finally:
+        _chain = []
 
 
 def gemm_tcgen05_supports(x: torch.Tensor, w: torch.Tensor) -> bool:

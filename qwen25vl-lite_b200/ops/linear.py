@@ -79,6 +79,7 @@ class Linear:
             y = self._skinny(x, deferred, out_dtype, residual)
             if y is not NotImplemented:
                 return y
+        kernels.chain_flush()           # what follows is no chain product; products that wait come first
         if deferred:
             x = x.materialize()
         if w.dtype == torch.bfloat16 and use_tcgen05(x, w):

@@ -437,6 +437,69 @@ def test_gemm_skinny_with_norm_inside_and_residual_epilogue(m, n, k):
     assert int(kernels.error_flag("cuda:0")[0]) == 0
 
 
+@pytest.mark.parametrize("m", [1, 8, 11, 16])
+def test_gemm_chain_runs_dependent_products_as_one_kernel(m):
+    """A layer's worth of products, each reading what the one before wrote (norm inside, bias,
+    SwiGLU pairs, residual additions, a K long enough to be cut into slices, float logits), gathered
+    into one persistent kernel: the results of the products launched one by one (up to the order of
+    the sums), right against float64, and the same to the bit when run again, with the barrier and
+    the counters that the first run left."""
+    from qwen25vl_lite.ops import kernels
+    if not kernels.chain_available():
+        pytest.skip("the device cannot hold the chain kernel's whole grid")
+    rng = np.random.default_rng(40 + m)
+    hidden, inter, qkv_n, vocab = 1536, 4480, 2048, 3000
+    x0 = rng.standard_normal((m, hidden)) * 2
+    nw = [dev(1 + 0.1 * rng.standard_normal(hidden), torch.float32) for _ in range(3)]
+    w_qkv = dev(rng.standard_normal((qkv_n, hidden)) * 0.03, torch.bfloat16)
+    b_qkv = dev(rng.standard_normal(qkv_n), torch.float32)
+    w_o = dev(rng.standard_normal((hidden, qkv_n)) * 0.03, torch.bfloat16)
+    w_gu = dev(rng.standard_normal((2 * inter, hidden)) * 0.03, torch.bfloat16)
+    w_down = dev(rng.standard_normal((hidden, inter)) * 0.03, torch.bfloat16)
+    w_head = dev(rng.standard_normal((vocab, hidden)) * 0.03, torch.bfloat16)
+
+    def layer():
+        x = dev(x0, torch.float32)
+        qkv = torch.empty((m, qkv_n), dtype=torch.bfloat16, device="cuda")
+        act = torch.empty((m, inter), dtype=torch.bfloat16, device="cuda")
+        logits = torch.empty((m, vocab), dtype=torch.float32, device="cuda")
+        kernels.gemm_skinny_norm(x, nw[0], 1e-6, w_qkv, b_qkv, qkv, kernels.SKINNY_BIAS)
+        kernels.gemm_skinny(qkv, w_o, None, x, kernels.SKINNY_RESIDUAL)
+        kernels.gemm_skinny_norm(x, nw[1], 1e-6, w_gu, None, act, kernels.SKINNY_SWIGLU)
+        kernels.gemm_skinny(act, w_down, None, x, kernels.SKINNY_RESIDUAL)
+        kernels.gemm_skinny_norm(x, nw[2], 1e-6, w_head, None, logits, kernels.SKINNY_F32)
+        return x, qkv, act, logits
+
+    one_by_one = layer()
+    launches = kernels.launch_count()
+    runs = []
+    for _ in range(2):
+        assert kernels.chain_begin()
+        try:
+            runs.append(layer())
+        finally:
+            kernels.chain_end()
+        torch.cuda.synchronize()
+    assert kernels.launch_count() - launches == 2              # five products, one kernel, twice
+    chained = runs[1]
+    for a, b, c in zip(one_by_one, runs[0], runs[1]):
+        assert torch.equal(b, c)
+        assert (a.float() - b.float()).abs().max().item() <= 2e-2 * a.float().abs().max().item()
+    assert int(kernels.error_flag("cuda:0")[0]) == 0
+    # against float64 on the same bfloat16 weights
+    bf = lambda a: f64(dev(a, torch.bfloat16))
+    h = bf(plain.rms_norm(x0, f64(nw[0]), 1e-6))
+    qkv = bf(h @ f64(w_qkv).T + f64(b_qkv))
+    x1 = x0 + qkv @ f64(w_o).T
+    gu = bf(plain.rms_norm(x1, f64(nw[1]), 1e-6)) @ f64(w_gu).T
+    pairs = gu.reshape(m, -1, 2, 8)
+    act = bf((plain.silu(pairs[:, :, 0]) * pairs[:, :, 1]).reshape(m, inter))
+    x2 = x1 + act @ f64(w_down).T
+    logits = bf(plain.rms_norm(x2, f64(nw[2]), 1e-6)) @ f64(w_head).T
+    assert np.abs(f64(chained[0]) - x2).max() / np.abs(x2).max() < 2e-2
+    assert np.abs(f64(chained[3]) - logits).max() / np.abs(logits).max() < 3e-2
+
+
 def test_gemm_skinny_norm_needs_resident_rows():
     from qwen25vl_lite.ops import kernels
     x = torch.zeros((16, 11008), dtype=torch.float32, device="cuda")      # 16 rows of 11008 do not fit beside the ring
