@@ -21,35 +21,76 @@ __global__ void embed_gather_kernel(const T* __restrict__ table, const int* __re
   for (int c = threadIdx.x; c < hidden; c += blockDim.x) dst[c] = to_f32(src[c]);
 }
 
+// Four consecutive values as floats, and back (bf16: 8 bytes, float: 16 bytes at a time).
+template <typename T> __device__ __forceinline__ float4 load4(const T* p);
+template <> __device__ __forceinline__ float4 load4<float>(const float* p) { return *reinterpret_cast<const float4*>(p); }
+template <> __device__ __forceinline__ float4 load4<bf16>(const bf16* p) {
+  const uint2 raw = *reinterpret_cast<const uint2*>(p);
+  const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(&raw.x), b = *reinterpret_cast<const __nv_bfloat162*>(&raw.y);
+  return make_float4(__low2float(a), __high2float(a), __low2float(b), __high2float(b));
+}
+template <typename T> __device__ __forceinline__ void store4(T* p, float4 v);
+template <> __device__ __forceinline__ void store4<float>(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
+template <> __device__ __forceinline__ void store4<bf16>(bf16* p, float4 v) {
+  const __nv_bfloat162 a = __floats2bfloat162_rn(v.x, v.y), b = __floats2bfloat162_rn(v.z, v.w);
+  uint2 raw;
+  raw.x = *reinterpret_cast<const unsigned*>(&a);
+  raw.y = *reinterpret_cast<const unsigned*>(&b);
+  *reinterpret_cast<uint2*>(p) = raw;
+}
+
 // x[row] += delta[row] (if delta), then out[r] = rmsnorm(x[row]) * w.
 // rows == nullptr: row = r, x is updated in place.  rows != nullptr: row = rows[r], x is left
 // untouched (used for the final norm, which only the wanted positions need).
-template <typename T, bool EXACT>
+// VEC: hidden is a multiple of 4 and every row starts on a 16-byte boundary, so a thread moves four
+// values at a time.  The sum of squares is taken thread by thread, then lanes, then warps, in a fixed
+// order that depends on hidden alone.
+template <typename T, bool EXACT, bool VEC>
 __global__ void add_rmsnorm_kernel(float* __restrict__ x, const T* __restrict__ delta,
                                    const float* __restrict__ w, float eps, T* __restrict__ out,
                                    const int* __restrict__ rows, int hidden) {
   pdl_trigger();
   pdl_wait();
-  extern __shared__ float row_cache[];  // hidden floats + 32 scratch
+  extern __shared__ __align__(16) float row_cache[];  // hidden floats + 32 scratch
   float* scratch = row_cache + hidden;
   const int r = blockIdx.x;
   const int row = rows ? rows[r] : r;
   float* xr = x + (size_t)row * hidden;
   const T* dr = delta ? delta + (size_t)row * hidden : nullptr;
+  T* o = out + (size_t)r * hidden;
   float ss = 0.f;
-  for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
-    float v = xr[c];
-    if (dr) {
-      v += to_f32(dr[c]);
-      if (!rows) xr[c] = v;
+  if (VEC) {
+    for (int c = threadIdx.x * 4; c < hidden; c += blockDim.x * 4) {
+      float4 v = *reinterpret_cast<const float4*>(xr + c);
+      if (dr) {
+        const float4 d = load4<T>(dr + c);
+        v.x += d.x; v.y += d.y; v.z += d.z; v.w += d.w;
+        if (!rows) *reinterpret_cast<float4*>(xr + c) = v;
+      }
+      *reinterpret_cast<float4*>(row_cache + c) = v;
+      ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
     }
-    row_cache[c] = v;
-    ss += v * v;
+  } else {
+    for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
+      float v = xr[c];
+      if (dr) {
+        v += to_f32(dr[c]);
+        if (!rows) xr[c] = v;
+      }
+      row_cache[c] = v;
+      ss += v * v;
+    }
   }
   const float total = block_sum(ss, scratch);
   const float inv = EXACT ? 1.0f / sqrtf(total / (float)hidden + eps) : rsqrtf(total / (float)hidden + eps);
-  T* o = out + (size_t)r * hidden;
-  for (int c = threadIdx.x; c < hidden; c += blockDim.x) o[c] = from_f32<T>(row_cache[c] * inv * w[c]);
+  if (VEC) {
+    for (int c = threadIdx.x * 4; c < hidden; c += blockDim.x * 4) {
+      const float4 v = *reinterpret_cast<const float4*>(row_cache + c), ww = *reinterpret_cast<const float4*>(w + c);
+      store4<T>(o + c, make_float4(v.x * inv * ww.x, v.y * inv * ww.y, v.z * inv * ww.z, v.w * inv * ww.w));
+    }
+  } else {
+    for (int c = threadIdx.x; c < hidden; c += blockDim.x) o[c] = from_f32<T>(row_cache[c] * inv * w[c]);
+  }
 }
 
 // gu is [n, 2*inter].  paired == 0: gate in the first half of a row, up in the second.
@@ -84,11 +125,14 @@ static int add_rmsnorm(float* x, const void* delta, const float* w, float eps, v
   const size_t smem = (size_t)(hidden + 32) * sizeof(float);
   if (smem > 200 * 1024) return (int)cudaErrorInvalidValue;
   if (smem > 48 * 1024) {
-    cudaError_t e = cudaFuncSetAttribute(add_rmsnorm_kernel<T, EXACT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaError_t e = cudaFuncSetAttribute(add_rmsnorm_kernel<T, EXACT, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(add_rmsnorm_kernel<T, EXACT, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
   }
   const int threads = hidden >= 1024 ? 256 : 128;
-  launch(add_rmsnorm_kernel<T, EXACT>, dim3(n_out), dim3(threads), smem, (cudaStream_t)stream, x, (const T*)delta, w, eps, (T*)out, rows, hidden);
+  const bool vec = hidden % 4 == 0 && !(((uintptr_t)x | (uintptr_t)delta | (uintptr_t)w | (uintptr_t)out) & 15);
+  if (vec) launch(add_rmsnorm_kernel<T, EXACT, true>, dim3(n_out), dim3(threads), smem, (cudaStream_t)stream, x, (const T*)delta, w, eps, (T*)out, rows, hidden);
+  else launch(add_rmsnorm_kernel<T, EXACT, false>, dim3(n_out), dim3(threads), smem, (cudaStream_t)stream, x, (const T*)delta, w, eps, (T*)out, rows, hidden);
   return launch_status();
 }
 

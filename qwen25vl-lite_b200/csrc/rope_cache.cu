@@ -16,6 +16,34 @@
 // The pages of one cache layer are K: [num_pages, nkv, page_size, D] and V the same.
 #include "common.cuh"
 
+// Eight consecutive values as floats, and back (bf16: 16 bytes, float: 32 bytes).
+template <typename T> __device__ __forceinline__ void load8(const T* p, float (&v)[8]);
+template <> __device__ __forceinline__ void load8<float>(const float* p, float (&v)[8]) {
+  const float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
+  v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+}
+template <> __device__ __forceinline__ void load8<bf16>(const bf16* p, float (&v)[8]) {
+  const uint4 raw = *reinterpret_cast<const uint4*>(p);
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) { v[2 * i] = __low2float(h[i]); v[2 * i + 1] = __high2float(h[i]); }
+}
+template <typename T> __device__ __forceinline__ void store8(T* p, const float (&v)[8]);
+template <> __device__ __forceinline__ void store8<float>(float* p, const float (&v)[8]) {
+  *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+  *reinterpret_cast<float4*>(p + 4) = make_float4(v[4], v[5], v[6], v[7]);
+}
+template <> __device__ __forceinline__ void store8<bf16>(bf16* p, const float (&v)[8]) {
+  uint4 raw;
+  __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&raw);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+  *reinterpret_cast<uint4*>(p) = raw;
+}
+
+// One block per token.  The token's D/2 (cos, sin) pairs are computed once into shared memory;
+// then a thread takes 8 channels j .. j+7 of a head with their partners j + D/2 .. (D is a
+// multiple of 16, so both runs are whole 16- or 32-byte vectors).
 template <typename T>
 __global__ void rope_store_kernel(T* __restrict__ qkv, const int* __restrict__ pos, int n_tokens,
                                   const float* __restrict__ inv_freq, const int* __restrict__ axis,
@@ -24,39 +52,52 @@ __global__ void rope_store_kernel(T* __restrict__ qkv, const int* __restrict__ p
                                   int rotate, int store) {
   pdl_trigger();
   pdl_wait();
+  extern __shared__ float2 cs[];                       // [d / 2] (cos, sin)
   const int token = blockIdx.x;
   const int half = d >> 1;
   T* row = qkv + (size_t)token * (nq + 2 * nkv) * d;
   const int slot = store ? kv_slot[token] : -1;
   const int page = slot >= 0 ? slot / page_size : 0;
   const int off = slot >= 0 ? slot % page_size : 0;
-
-  for (int idx = threadIdx.x; idx < (nq + nkv) * half; idx += blockDim.x) {
-    const int head = idx / half, j = idx - head * half;
-    T* hp = row + (size_t)head * d;
-    const float x1 = to_f32(hp[j]), x2 = to_f32(hp[j + half]);
-    float y1 = x1, y2 = x2;
-    if (rotate) {
+  if (rotate) {
+    for (int j = threadIdx.x; j < half; j += blockDim.x) {
       const float p = (float)pos[(size_t)axis[j] * n_tokens + token];
       float s, c;
       sincosf(p * inv_freq[j], &s, &c);
-      y1 = x1 * c - x2 * s;
-      y2 = x2 * c + x1 * s;
+      cs[j] = make_float2(c, s);
+    }
+    __syncthreads();
+  }
+  const int chunks = half >> 3;                        // 8-channel runs in half a head
+  for (int idx = threadIdx.x; idx < (nq + nkv) * chunks; idx += blockDim.x) {
+    const int head = idx / chunks, j = (idx - head * chunks) << 3;
+    if (head < nq && !rotate) continue;                // q is left as it is
+    T* hp = row + (size_t)head * d;
+    float x1[8], x2[8], y1[8], y2[8];
+    load8<T>(hp + j, x1);
+    load8<T>(hp + j + half, x2);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const float2 t = rotate ? cs[j + i] : make_float2(1.f, 0.f);
+      y1[i] = x1[i] * t.x - x2[i] * t.y;
+      y2[i] = x2[i] * t.x + x1[i] * t.y;
     }
     if (head < nq) {
-      hp[j] = from_f32<T>(y1);
-      hp[j + half] = from_f32<T>(y2);
+      store8<T>(hp + j, y1);
+      store8<T>(hp + j + half, y2);
     } else if (slot >= 0) {
       T* kr = kpages + (((size_t)page * nkv + (head - nq)) * page_size + off) * d;
-      kr[j] = from_f32<T>(y1);
-      kr[j + half] = from_f32<T>(y2);
+      store8<T>(kr + j, y1);
+      store8<T>(kr + j + half, y2);
     }
   }
   if (slot >= 0) {
     const T* vsrc = row + (size_t)(nq + nkv) * d;
-    for (int idx = threadIdx.x; idx < nkv * d; idx += blockDim.x) {
+    for (int idx = threadIdx.x * 8; idx < nkv * d; idx += blockDim.x * 8) {
       const int h = idx / d, c = idx - h * d;
-      vpages[(((size_t)page * nkv + h) * page_size + off) * d + c] = vsrc[idx];
+      float v[8];
+      load8<T>(vsrc + idx, v);
+      store8<T>(vpages + (((size_t)page * nkv + h) * page_size + off) * d + c, v);
     }
   }
 }
@@ -66,8 +107,8 @@ static int rope_store(void* qkv, const int* pos, int n, const float* inv_freq, c
                       void* vpages, const int* kv_slot, int nq, int nkv, int d, int page_size, int rotate, int store,
                       void* stream) {
   if (n <= 0) return 0;
-  if (d % 2) return (int)cudaErrorInvalidValue;
-  launch(rope_store_kernel<T>, dim3(n), dim3(256), 0, (cudaStream_t)stream, (T*)qkv, pos, n, inv_freq, axis, (T*)kpages, (T*)vpages,
+  if (d % 16 || (((uintptr_t)qkv | (uintptr_t)kpages | (uintptr_t)vpages) & 15)) return (int)cudaErrorInvalidValue;
+  launch(rope_store_kernel<T>, dim3(n), dim3(256), (size_t)(d / 2) * sizeof(float2), (cudaStream_t)stream, (T*)qkv, pos, n, inv_freq, axis, (T*)kpages, (T*)vpages,
                                                             kv_slot, nq, nkv, d, page_size, rotate, store);
   return launch_status();
 }
