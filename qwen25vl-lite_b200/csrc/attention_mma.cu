@@ -466,7 +466,23 @@ struct RopeArgs {
   bf16* kpages_w;
   bf16* vpages_w;
   int* counters;          // [n_items * nkv], zero before the first launch; the kernel leaves them zero
+  const float2* angles;   // [n_tokens, D/2] (cos, sin) of every token's angles, or nullptr: computed here
 };
+
+// (cos, sin) of every token's D/2 angles: the same for every layer of a step, so a step computes
+// them once (angle[j] = pos[axis(j)] * inv_freq[j] in float, reference src/qwen25vl_lite/rope.py:48-96).
+__global__ void rope_angles_kernel(const int* __restrict__ positions, int n_tokens, const float* __restrict__ inv_freq,
+                                   const int* __restrict__ axis, int half, float2* __restrict__ out) {
+  pdl_trigger();
+  pdl_wait();
+  const int idx = blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= n_tokens * half) return;
+  const int token = idx / half, j = idx - token * half;
+  const float p = (float)positions[(size_t)axis[j] * n_tokens + token];
+  float sn, c;
+  sincosf(p * inv_freq[j], &sn, &c);
+  out[idx] = make_float2(c, sn);
+}
 
 __device__ __forceinline__ unsigned rotate_pair_lo(unsigned x1, unsigned x2, float c0, float s0, float c1, float s1) {
   const __nv_bfloat162 a = *reinterpret_cast<__nv_bfloat162*>(&x1), b = *reinterpret_cast<__nv_bfloat162*>(&x2);
@@ -512,7 +528,9 @@ __global__ void __launch_bounds__(ATTN_THREADS) attention_decode_fused_kernel(At
   load_q<D>(qf, [&](int row) { return row < G ? qbase + (size_t)row * D : (const bf16*)nullptr; });
   // the token has D/2 angles; one thread computes each (cos, sin) once for the whole CTA
   __shared__ float2 cs[HALF];
-  if (threadIdx.x < HALF) {
+  if (threadIdx.x < HALF && r.angles) {
+    cs[threadIdx.x] = r.angles[(size_t)token * HALF + threadIdx.x];
+  } else if (threadIdx.x < HALF) {
     const int j = threadIdx.x;
     // all five loads are independent of one another, so they cost one memory latency, not two
     const int ax = r.axis[j];
@@ -658,31 +676,48 @@ __global__ void __launch_bounds__(ATTN_THREADS) attention_decode_fused_kernel(At
   __syncthreads();
   if (!is_last) return;
   __threadfence();
-  // weights of the splits per row, computed once into shared memory; then the sums run without
-  // branches so that their loads are in flight together
-  float* wgt = reinterpret_cast<float*>(smem);                // [16 rows][n_splits], n_splits <= 64
-  float* inv_l = wgt + 16 * 64;                               // [16 rows]
-  for (int row = warp; row < G; row += ATTN_THREADS / 32) {     // a warp per row, lanes over the splits
+  // A thread merges four channels of one row over all splits.  The partials of 16 splits are asked
+  // for together (one trip to L2 for all of them), then weighted by exp2(m_k - M) and added in split
+  // order; with more than 16 splits the running maximum is carried as in the attention loop itself.
+  const int n4 = G * (D / 4);
+  for (int e = threadIdx.x; e < n4; e += ATTN_THREADS) {
+    const int row = e / (D / 4), c4 = e - row * (D / 4);
     const size_t base = ((size_t)item * a.nq + kvh * G + row) * a.n_splits;
-    const float m0 = lane < a.n_splits ? __ldcg(a.part_ml + (base + lane) * 2) : -INFINITY;
-    const float m1 = lane + 32 < a.n_splits ? __ldcg(a.part_ml + (base + lane + 32) * 2) : -INFINITY;
-    const float l0 = lane < a.n_splits ? __ldcg(a.part_ml + (base + lane) * 2 + 1) : 0.f;
-    const float l1 = lane + 32 < a.n_splits ? __ldcg(a.part_ml + (base + lane + 32) * 2 + 1) : 0.f;
-    const float M = warp_max(fmaxf(m0, m1));
-    const float w0 = m0 == -INFINITY ? 0.f : exp2f(m0 - M), w1 = m1 == -INFINITY ? 0.f : exp2f(m1 - M);
-    wgt[row * 64 + lane] = w0;
-    wgt[row * 64 + lane + 32] = w1;
-    const float lsum = warp_sum(l0 * w0 + l1 * w1);
-    if (lane == 0) inv_l[row] = 1.0f / lsum;
-  }
-  __syncthreads();
-  for (int idx = threadIdx.x; idx < G * D; idx += ATTN_THREADS) {
-    const int row = idx / D, c = idx - row * D;
-    const float* po = a.part_o + ((size_t)item * a.nq + kvh * G + row) * a.n_splits * D + c;
-    float acc = 0.f;
-#pragma unroll 8
-    for (int k = 0; k < a.n_splits; ++k) acc = fmaf(__ldcg(po + (size_t)k * D), wgt[row * 64 + k], acc);
-    a.out[(size_t)token * a.nq * D + (size_t)(kvh * G + row) * D + c] = __float2bfloat16_rn(acc * inv_l[row]);
+    const float2* ml_row = reinterpret_cast<const float2*>(a.part_ml) + base;
+    float M = -INFINITY, L = 0.f;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int k0 = 0; k0 < a.n_splits; k0 += 16) {
+      float2 ml[16];
+      float4 po[16];
+#pragma unroll
+      for (int j = 0; j < 16; ++j) {
+        const int kk = min(k0 + j, a.n_splits - 1);                  // always a readable address
+        ml[j] = __ldcg(ml_row + kk);
+        po[j] = __ldcg(reinterpret_cast<const float4*>(a.part_o + (base + kk) * D) + c4);
+      }
+      float mb = -INFINITY;
+#pragma unroll
+      for (int j = 0; j < 16; ++j)
+        if (k0 + j < a.n_splits) mb = fmaxf(mb, ml[j].x);
+      const float Mn = fmaxf(M, mb);
+      const float keep = M == -INFINITY ? 0.f : exp2f(M - Mn);
+      acc.x *= keep; acc.y *= keep; acc.z *= keep; acc.w *= keep;
+      L *= keep;
+#pragma unroll
+      for (int j = 0; j < 16; ++j) {
+        if (k0 + j >= a.n_splits || ml[j].x == -INFINITY) continue;
+        const float w = exp2f(ml[j].x - Mn);
+        L += ml[j].y * w;
+        acc.x = fmaf(po[j].x, w, acc.x); acc.y = fmaf(po[j].y, w, acc.y);
+        acc.z = fmaf(po[j].z, w, acc.z); acc.w = fmaf(po[j].w, w, acc.w);
+      }
+      M = Mn;
+    }
+    const float inv = 1.0f / L;
+    uint2 packed;
+    packed.x = pack_bf16(acc.x * inv, acc.y * inv);
+    packed.y = pack_bf16(acc.z * inv, acc.w * inv);
+    *reinterpret_cast<uint2*>(a.out + (size_t)token * a.nq * D + (size_t)(kvh * G + row) * D + c4 * 4) = packed;
   }
 }
 
@@ -792,7 +827,8 @@ Q25_EXPORT int q25_attention_decode_fused_bf16(const void* qkv, int qkv_stride, 
                                                const int* items, int n_items, int nq, int nkv, int d, int page_size,
                                                int window, float scale, int n_splits, const int* positions,
                                                int n_tokens, const float* inv_freq, const int* axis,
-                                               const int* kv_slot, float* scratch, int* counters, void* stream) {
+                                               const int* kv_slot, float* scratch, int* counters, const void* angles,
+                                               void* stream) {
   if (n_items <= 0) return 0;
   AttnArgs a;
   int e = fill_args(a, qkv, qkv_stride, out, kp, vp, bt, tw, cu_q, q_start, items, nq, nkv, page_size, window, scale);
@@ -806,6 +842,7 @@ Q25_EXPORT int q25_attention_decode_fused_bf16(const void* qkv, int qkv_stride, 
   r.counters = counters;
   r.positions = positions; r.n_tokens = n_tokens; r.inv_freq = inv_freq; r.axis = axis; r.kv_slot = kv_slot;
   r.kpages_w = (bf16*)kp; r.vpages_w = (bf16*)vp;
+  r.angles = (const float2*)angles;
   cudaStream_t s = (cudaStream_t)stream;
   switch (d) {
     case 32: return launch_decode_fused<32>(a, r, n_items, s);
@@ -814,6 +851,16 @@ Q25_EXPORT int q25_attention_decode_fused_bf16(const void* qkv, int qkv_stride, 
     case 128: return launch_decode_fused<128>(a, r, n_items, s);
     default: return (int)cudaErrorInvalidValue;
   }
+}
+
+// out[token][j] = (cos, sin)(positions[axis[j]][token] * inv_freq[j]) for j < half.
+Q25_EXPORT int q25_rope_angles(const int* positions, int n_tokens, const float* inv_freq, const int* axis, int half,
+                               void* out, void* stream) {
+  if (n_tokens <= 0 || half <= 0) return 0;
+  const int total = n_tokens * half;
+  launch(rope_angles_kernel, dim3((total + 127) / 128), dim3(128), 0, (cudaStream_t)stream, positions, n_tokens, inv_freq, axis,
+         half, (float2*)out);
+  return launch_status();
 }
 
 // ------------------------------------------------------------------------------------------------

@@ -88,6 +88,9 @@ class StepContext:
     host_q_lens: List[int] = field(default_factory=list)
     host_q_start: List[int] = field(default_factory=list)
     host_slots: List[int] = field(default_factory=list)
+    # what parts compute once per forward pass and share between layers (the model empties it
+    # when a pass begins); keyed by whoever puts it there
+    shared: Dict[object, object] = field(default_factory=dict)
 
     def kv(self, stop: StopRuntime) -> KVStep:
         group, k_pages, v_pages = self.cache.stop_pages(stop.index)

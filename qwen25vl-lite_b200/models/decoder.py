@@ -100,6 +100,8 @@ class DecoderModel:
     def forward(self, ctx) -> Optional[torch.Tensor]:
         """Runs the step described by ``ctx`` and returns float32 logits [wanted, vocab]
         (None when nothing is wanted)."""
+        if hasattr(ctx, "shared"):
+            ctx.shared.clear()
         x = self.embedding.forward(ctx)
         pending = None
         for stop in self.stops:

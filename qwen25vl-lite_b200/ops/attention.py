@@ -53,13 +53,21 @@ def attend(ctx, qkv, kv, position, nq: int, nkv: int, head_dim: int, window, sca
             and ctx.prefill_tiles.get(group, 0) is None
             and kernels.attention_fused_supports(qkv.dtype, head_dim, kv.page_size, group)):
         inv_freq, axis = tables()
+        # the angles are the same for every layer of the step: the first one to ask computes them
+        shared = getattr(ctx, "shared", None)
+        key = ("rope_angles", inv_freq.data_ptr())
+        angles = shared.get(key) if shared is not None else None
+        if angles is None:
+            angles = kernels.rope_angles(ctx.positions, inv_freq, axis)
+            if shared is not None:
+                shared[key] = angles
         out = torch.empty((qkv.shape[0], nq * head_dim), dtype=qkv.dtype, device=qkv.device)
         visible = min(ctx.max_kv_len, window) if window else ctx.max_kv_len
         splits = decode_splits(ctx.n_seqs, nkv, visible)
         scratch = _scratch_floats(ctx.n_seqs * nq * splits * (head_dim + 2), qkv.device) if splits > 1 else None
         kernels.attention_decode_fused(qkv, out, kv.k_pages, kv.v_pages, kv.block_table, ctx.cu_q, ctx.q_start_pos,
                                        ctx.decode_items, nq, nkv, head_dim, kv.page_size, window, scale, splits,
-                                       ctx.positions, inv_freq, axis, kv.kv_slot, scratch)
+                                       ctx.positions, inv_freq, axis, kv.kv_slot, scratch, angles)
         return out
     position.rotate_and_store(ctx, qkv, nq, nkv, head_dim, kv if store else None)
     return paged_attention(ctx, qkv, kv, nq, nkv, head_dim, window, scale)

@@ -216,13 +216,18 @@ def attention_decode_fused(qkv: torch.Tensor, out: torch.Tensor, k_pages: torch.
                            block_table: torch.Tensor, cu_q: torch.Tensor, q_start_pos: torch.Tensor, items: torch.Tensor,
                            nq: int, nkv: int, head_dim: int, page_size: int, window: int, scale: float, n_splits: int,
                            positions: torch.Tensor, inv_freq: torch.Tensor, axis: torch.Tensor,
-                           kv_slot: torch.Tensor, scratch: Optional[torch.Tensor] = None) -> None:
+                           kv_slot: torch.Tensor, scratch: Optional[torch.Tensor] = None,
+                           angles: Optional[torch.Tensor] = None) -> None:
     """One kernel for a step of one-token entries: 3-axis rotary encoding of q and the new k
     (``positions`` int32 [3, N], ``inv_freq`` float32 [D/2], ``axis`` int32 [D/2]), the write of
     the new k and v at ``kv_slot``, attention, and the merge of the ``n_splits`` key ranges
     (through ``scratch`` as for ``attention_decode``; the CTA that finishes last merges).
-    ``qkv`` is read as projected and left unchanged."""
+    ``qkv`` is read as projected and left unchanged.  ``angles``: the step's table from
+    ``rope_angles`` (the kernel computes the angles itself without it)."""
     n_items = items.shape[0]
+    if angles is not None and (angles.dtype != torch.float32 or tuple(angles.shape) != (positions.shape[1], head_dim // 2, 2)
+                               or not angles.is_contiguous()):
+        raise KernelError("attention_decode_fused: angles must be float32 [N, D/2, 2]")
     if n_splits > 1:
         need = n_items * nq * n_splits * (head_dim + 2)
         if scratch is None or scratch.dtype != torch.float32 or scratch.numel() < need:
@@ -233,12 +238,24 @@ def attention_decode_fused(qkv: torch.Tensor, out: torch.Tensor, k_pages: torch.
     if positions.dtype != torch.int32 or positions.dim() != 2 or positions.shape[0] != 3:
         raise KernelError("attention_decode_fused: positions must be int32 [3, N]")
     _check(_fn("q25_attention_decode_fused_bf16",
-               [_P, _I, _P, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _I, _P, _I, _P, _P, _P, _P, _P, _P])(
+               [_P, _I, _P, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _I, _P, _I, _P, _P, _P, _P, _P, _P, _P])(
         qkv.data_ptr(), qkv.stride(0), out.data_ptr(), k_pages.data_ptr(), v_pages.data_ptr(), block_table.data_ptr(),
         block_table.shape[1], cu_q.data_ptr(), q_start_pos.data_ptr(), items.data_ptr(), items.shape[0], nq, nkv,
         head_dim, page_size, int(window or 0), float(scale), int(n_splits), positions.data_ptr(), positions.shape[1],
         inv_freq.data_ptr(), axis.data_ptr(), kv_slot.data_ptr(), _ptr(scratch),
-        _split_counters(qkv.device, n_items * nkv).data_ptr(), _stream()), "attention_decode_fused")
+        _split_counters(qkv.device, n_items * nkv).data_ptr(), _ptr(angles), _stream()), "attention_decode_fused")
+
+
+def rope_angles(positions: torch.Tensor, inv_freq: torch.Tensor, axis: torch.Tensor) -> torch.Tensor:
+    """(cos, sin) of every token's rotary angles, float32 [N, D/2, 2]: ``positions`` int32 [axes, N],
+    ``inv_freq`` float32 [D/2], ``axis`` int32 [D/2] (which position axis drives each channel)."""
+    n, half = positions.shape[1], inv_freq.shape[0]
+    _dev(positions, torch.int32, "rope_angles positions"); _dev(inv_freq, torch.float32, "rope_angles inv_freq")
+    _dev(axis, torch.int32, "rope_angles axis")
+    out = torch.empty((n, half, 2), dtype=torch.float32, device=positions.device)
+    _check(_fn("q25_rope_angles", [_P, _I, _P, _P, _I, _P, _P])(
+        positions.data_ptr(), n, inv_freq.data_ptr(), axis.data_ptr(), half, out.data_ptr(), _stream()), "rope_angles")
+    return out
 
 
 _counters: Dict[torch.device, torch.Tensor] = {}
