@@ -6,7 +6,8 @@
 //   * every exported function is `extern "C" int q25_<name>_<f32|bf16>(..., void* stream)` and
 //     returns the cudaError_t of its launch (0 = success), so Python can call it through ctypes
 //     with raw device pointers and the stream it is recording or capturing on;
-//   * no kernel waits on another kernel or on a flag: everything is stream-ordered.
+//   * no kernel waits on another kernel: everything is stream-ordered.  Waits inside a kernel (on
+//     an mbarrier, or on the grid barrier of gemm_chain.cu) are bounded and report through a flag.
 #pragma once
 
 #include <cuda_bf16.h>
