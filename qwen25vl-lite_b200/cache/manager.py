@@ -77,6 +77,10 @@ class RequestCache:
     position_offset: int = 0      # added to a token's index to get its position when none is given
     max_position: int = -1        # largest position any of the request's tokens had
     open: bool = True
+    # per group: how many leading entries of the table have been given back (a window passed them).
+    # A table holds a page at every index from there to its end, so the book-keeping of a step is
+    # arithmetic on lengths, not a walk over the table.
+    released: List[int] = field(default_factory=list)
 
     def held_pages(self, group: int) -> List[int]:
         return [p for p in self.tables[group] if p >= 0]
@@ -146,17 +150,15 @@ class CacheManager:
         slot = self._free_slots.pop()
         for t in self.states.values():
             t[slot].zero_()
-        return RequestCache(slot, [[] for _ in self.groups])
+        return RequestCache(slot, [[] for _ in self.groups], released=[0] * len(self.groups))
 
     def pages_missing(self, req: RequestCache, upto: int) -> List[int]:
         """New pages each group must find so that tokens [req.num_tokens, upto) can run."""
         out = []
+        last = -(-upto // self.page_size)
         for g in self.groups:
-            table = req.tables[g.index]
-            last = -(-upto // self.page_size)
-            first = g.first_needed_page(req.num_tokens)
-            have = sum(1 for i in range(first, min(last, len(table))) if table[i] >= 0)
-            out.append(max(0, last - first) - have)
+            first = max(g.first_needed_page(req.num_tokens), len(req.tables[g.index]))
+            out.append(max(0, last - first))
         return out
 
     def can_hold(self, req: RequestCache, upto: int) -> bool:
@@ -172,14 +174,14 @@ class CacheManager:
             if n > g.pool.num_free:
                 raise OutOfPages(f"cache group {g.index} needs {n} more pages for {upto} tokens, "
                                  f"{g.pool.num_free} of {g.pool.num_pages} free")
-        for g in self.groups:
-            table = req.tables[g.index]
-            last = -(-upto // self.page_size)
-            if len(table) < last:
-                table.extend([-1] * (last - len(table)))
-            for i in range(g.first_needed_page(req.num_tokens), last):
-                if table[i] < 0:
-                    table[i] = g.pool.allocate(1)[0]
+        last = -(-upto // self.page_size)
+        for n, g in zip(missing, self.groups):
+            if n:
+                table = req.tables[g.index]
+                if len(table) < last - n:          # pages before the first one needed were never held
+                    table.extend([-1] * (last - n - len(table)))
+                    req.released[g.index] = len(table)
+                table.extend(g.pool.allocate(n))
 
     def advance(self, req: RequestCache, n_tokens: int) -> None:
         """``n_tokens`` more tokens are in the cache; pages wholly behind a window go back."""
@@ -188,10 +190,12 @@ class CacheManager:
             if g.window is None:
                 continue
             table = req.tables[g.index]
-            for i in range(min(g.first_needed_page(req.num_tokens), len(table))):
+            upto = min(g.first_needed_page(req.num_tokens), len(table))
+            for i in range(req.released[g.index], upto):
                 if table[i] >= 0:
                     g.pool.free([table[i]])
                     table[i] = -1
+            req.released[g.index] = max(req.released[g.index], upto)
 
     def close(self, req: RequestCache) -> None:
         """Gives back everything the request holds.  Closing twice is an error."""

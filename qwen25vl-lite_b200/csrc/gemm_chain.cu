@@ -309,6 +309,16 @@ __global__ void __launch_bounds__(GC_THREADS, 1) gemm_chain_kernel(const __grid_
             float acc[MT][4];
 #pragma unroll
             for (int mt = 0; mt < MT; ++mt) acc[mt][0] = acc[mt][1] = acc[mt][2] = acc[mt][3] = 0.f;
+            const bool add_old = op.epi == EPI_RESIDUAL;
+            if (add_old) {                      // asked for together with the slices' shares: one trip, not two
+#pragma unroll
+              for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                  const int m = mt * 8 + 2 * (lane & 3) + (e & 1), n = grp * GC_ROWS + (lane >> 2) + 8 * (e >> 1);
+                  if (m < op.M && n < op.N) acc[mt][e] = __ldcg(reinterpret_cast<const float*>(op.out) + (size_t)m * op.ldo + n);
+                }
+            }
             const float4* slot = reinterpret_cast<const float4*>(A.scratch + (size_t)grp * (MT * 128)) + lane;
             const size_t slice_stride = (size_t)op.groups * (MT * 32);                     // in float4
 #pragma unroll 8
@@ -319,7 +329,7 @@ __global__ void __launch_bounds__(GC_THREADS, 1) gemm_chain_kernel(const __grid_
                 acc[mt][0] += v.x; acc[mt][1] += v.y; acc[mt][2] += v.z; acc[mt][3] += v.w;
               }
             }
-            gc_store_group<MT>(acc, grp, op);
+            gc_store_group<MT>(acc, grp, op, add_old);
           }
         }
       }

@@ -37,10 +37,23 @@ class Request:
 
     request_id: object
     cache: RequestCache
+    # per cache group: the block table as the kernels read it (an array, no negative entries), with
+    # the table's length and released count when it was made
+    _tables: Dict[int, tuple] = field(default_factory=dict, repr=False, compare=False)
 
     @property
     def num_computed(self) -> int:
         return self.cache.num_tokens
+
+    def block_table(self, group: int) -> np.ndarray:
+        """The group's block table as an int64 array with 0 where no page is held; converted
+        again only when the table has grown or a window has released pages."""
+        table = self.cache.tables[group]
+        released = self.cache.released[group] if self.cache.released else 0
+        hit = self._tables.get(group)
+        if hit is None or hit[0] != len(table) or hit[1] != released:
+            hit = self._tables[group] = (len(table), released, np.maximum(np.asarray(table, dtype=np.int64), 0))
+        return hit[2]
 
 
 @dataclass
@@ -271,39 +284,70 @@ class ModelRunner:
             if pairs:
                 view[:] = np.asarray(pairs, dtype=np.int32).reshape(-1)
 
-        at = 0
-        r = 0
         cu[0] = 0
         last_position = []
-        for i, (e, n, s) in enumerate(zip(entries, q_lens, starts)):
-            ids = np.asarray(e.tokens, dtype=np.int64)
+        if (max(q_lens) == 1 and all(e.positions is None for e in entries)
+                and getattr(self.model.position, "default_is_linear", False)):
+            # A step of single tokens at their default positions (the usual decode step): the
+            # arrays are filled for all entries at once, and a request's block table is converted
+            # only when it has grown.
+            ids = np.fromiter((e.tokens[0] for e in entries), dtype=np.int64, count=S)
             if ids.min() < 0 or ids.max() >= self.vocab_size:
-                raise ValueError(f"request {e.request.request_id!r}: token id outside [0, {self.vocab_size})")
-            tok[at:at + n] = ids
-            if e.positions is None:
-                pos[:, at:at + n] = self.model.position.default_positions(s, n, e.request.cache.position_offset)
-            else:
-                p = np.asarray(e.positions)
-                if p.shape != (self.axes, n):
-                    raise ValueError(f"positions must be [{self.axes}, {n}], got {p.shape}")
-                pos[:, at:at + n] = p
-            last_position.append(int(pos[:, at:at + n].max()))
-            tseq[at:at + n] = i
-            cu[i + 1] = at + n
-            qs[i] = s
-            sl[i] = e.request.cache.slot
-            for w_ in e.want:
-                if not 0 <= int(w_) < n:
-                    raise ValueError(f"wanted place {w_} is outside the {n} tokens of the entry")
-                rows[r] = at + int(w_)
-                r += 1
-            logical = np.arange(s, s + n)
+                raise ValueError(f"token id outside [0, {self.vocab_size}) in a decode step")
+            st = np.asarray(starts, dtype=np.int64)
+            place = st + np.fromiter((e.request.cache.position_offset for e in entries), dtype=np.int64, count=S)
+            tok[:] = ids
+            pos[:, :] = place
+            last_position = place.tolist()
+            tseq[:] = np.arange(S)
+            cu[1:] = np.arange(1, S + 1)
+            qs[:] = st
+            sl[:] = [e.request.cache.slot for e in entries]
+            r = 0
+            for i, e in enumerate(entries):
+                for w_ in e.want:
+                    if int(w_) != 0:
+                        raise ValueError(f"wanted place {w_} is outside the 1 token of the entry")
+                    rows[r] = i
+                    r += 1
             for g, gs, gt in zip(groups, g_slot, g_tab):
-                table = np.asarray(e.request.cache.tables[g.index], dtype=np.int64)
-                gs[at:at + n] = table[logical // ps] * ps + logical % ps
-                gt[i, :len(table)] = np.maximum(table, 0)
-                gt[i, len(table):] = 0
-            at += n
+                for i, (e, s0) in enumerate(zip(entries, starts)):
+                    table = e.request.block_table(g.index)
+                    gs[i] = e.request.cache.tables[g.index][s0 // ps] * ps + s0 % ps
+                    gt[i, :len(table)] = table
+                    gt[i, len(table):] = 0
+        else:
+            at = 0
+            r = 0
+            for i, (e, n, s) in enumerate(zip(entries, q_lens, starts)):
+                ids = np.asarray(e.tokens, dtype=np.int64)
+                if ids.min() < 0 or ids.max() >= self.vocab_size:
+                    raise ValueError(f"request {e.request.request_id!r}: token id outside [0, {self.vocab_size})")
+                tok[at:at + n] = ids
+                if e.positions is None:
+                    pos[:, at:at + n] = self.model.position.default_positions(s, n, e.request.cache.position_offset)
+                else:
+                    p = np.asarray(e.positions)
+                    if p.shape != (self.axes, n):
+                        raise ValueError(f"positions must be [{self.axes}, {n}], got {p.shape}")
+                    pos[:, at:at + n] = p
+                last_position.append(int(pos[:, at:at + n].max()))
+                tseq[at:at + n] = i
+                cu[i + 1] = at + n
+                qs[i] = s
+                sl[i] = e.request.cache.slot
+                for w_ in e.want:
+                    if not 0 <= int(w_) < n:
+                        raise ValueError(f"wanted place {w_} is outside the {n} tokens of the entry")
+                    rows[r] = at + int(w_)
+                    r += 1
+                logical = np.arange(s, s + n)
+                for g, gs, gt in zip(groups, g_slot, g_tab):
+                    table = np.asarray(e.request.cache.tables[g.index], dtype=np.int64)
+                    gs[at:at + n] = table[logical // ps] * ps + logical % ps
+                    gt[i, :len(table)] = np.maximum(table, 0)
+                    gt[i, len(table):] = 0
+                at += n
 
         dev = self._device_ints
         dev[:off].copy_(self._staging[:off], non_blocking=True)

@@ -70,6 +70,10 @@ class MRope(PositionEncoding):
             axis += [a] * n
         self.axis = torch.tensor(axis, dtype=torch.int32, device=device)
 
+    # plain text: token i of a request sits at i + offset on every axis, which lets the step
+    # function fill the positions of a whole decode batch at once
+    default_is_linear = True
+
     def default_positions(self, start: int, count: int, offset: int):
         run = np.arange(start + offset, start + offset + count, dtype=np.int64)
         return np.broadcast_to(run, (self.axes, count))
