@@ -141,10 +141,13 @@ class ModelRunner:
         self.steps = 0
         # Steps that bring one token per request are launch-bound (hundreds of small kernels), so
         # they are captured once per (batch size, block-table width) and replayed.  Only when every
-        # mixer says its forward can be captured (no host-side loop over the batch).
-        mixers = [b.mixer for b in getattr(model, "blocks", [])]
-        self.cuda_graphs = bool(cuda_graphs and self.device.type == "cuda" and mixers
-                                and all(getattr(m, "graph_safe", False) for m in mixers))
+        # part of the model says its forward can be captured (``graph_safe``: a fixed sequence of this
+        # engine's kernels, no host-side loop over the batch, no library operator that synchronises).
+        blocks = getattr(model, "blocks", [])
+        parts = [p for b in blocks for p in (b.mixer, b.feed_forward, *b.norms)]
+        parts += [getattr(model, name, None) for name in ("position", "embedding", "final_norm", "head")]
+        self.cuda_graphs = bool(cuda_graphs and self.device.type == "cuda" and blocks
+                                and all(getattr(p, "graph_safe", False) for p in parts))
         self._graphs: Dict[tuple, tuple] = {}
         self.graph_replays = 0
         # kernels with bounded waits report a wait that gave up here; read back after every step
@@ -200,7 +203,7 @@ class ModelRunner:
     def _forward_chained(self, ctx: StepContext) -> torch.Tensor:
         """The model's forward with the weight-streaming products of consecutive parts gathered
         into single persistent kernels (``kernels.chain_begin``).  Only for steps whose forward
-        launches nothing but this engine's kernels, which is what ``graph_safe`` mixers promise."""
+        launches nothing but this engine's kernels, which is what ``graph_safe`` parts promise."""
         kernels.chain_begin()
         try:
             return self.model.forward(ctx)

@@ -91,7 +91,10 @@ class PositionEncoding(Part):
 class Mixer(Part):
     """The token-mixing part of a layer.
 
-    ``forward(ctx, h, stop) -> [N, H]`` in the activation dtype.  Two optional capabilities a
+    ``forward(ctx, h, stop) -> [N, H]`` in the activation dtype.  Every part may declare
+    ``graph_safe = True``: its forward is a fixed sequence of this engine's kernels (no loop over
+    the batch on the host, no library operator), so a step can be captured into a CUDA graph; a
+    model is captured only when all its parts say so.  Two more optional capabilities a
     mixer (or feed-forward) may declare as class attributes: ``accepts_residual`` -- forward
     takes ``residual=`` (the float32 stream) and may add its result into it, returning None;
     ``accepts_deferred_norm`` -- ``h`` may be an ``ops.linear.DeferredNorm`` to be normalised

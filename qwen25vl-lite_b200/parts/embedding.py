@@ -14,6 +14,8 @@ from .base import Part, TensorSpec, register_embedding, register_head
 
 @register_embedding("token_embedding")
 class TokenEmbedding(Part):
+    graph_safe = True                # forward is a fixed sequence of this engine's kernels
+
     def __init__(self, vocab_size: int, hidden_size: int):
         self.vocab_size, self.hidden_size = int(vocab_size), int(hidden_size)
         self.weight = None
@@ -32,6 +34,8 @@ class TokenEmbedding(Part):
 
 @register_head("linear_head")
 class LinearHead(Part):
+    graph_safe = True                # forward is a fixed sequence of this engine's kernels
+
     def __init__(self, vocab_size: int, hidden_size: int, tied: bool):
         self.vocab_size, self.hidden_size, self.tied = int(vocab_size), int(hidden_size), bool(tied)
         self.proj = None

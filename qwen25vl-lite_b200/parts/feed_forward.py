@@ -13,6 +13,7 @@ from .base import FeedForward, TensorSpec, register_feed_forward
 
 @register_feed_forward("swiglu")
 class SwiGLU(FeedForward):
+    graph_safe = True                # forward is a fixed sequence of this engine's kernels
     accepts_deferred_norm = True     # forward takes a DeferredNorm as its input
     accepts_residual = True          # forward can add its result into the residual stream itself
 

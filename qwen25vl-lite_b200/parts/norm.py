@@ -15,6 +15,8 @@ from .base import Norm, TensorSpec, register_norm
 
 @register_norm("rmsnorm")
 class RMSNorm(Norm):
+    graph_safe = True                # forward is a fixed sequence of this engine's kernels
+
     def __init__(self, dim: int, eps: float):
         self.dim = int(dim)
         self.eps = float(eps)

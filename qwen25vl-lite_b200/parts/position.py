@@ -50,6 +50,7 @@ def prompt_positions(num_tokens: int, image_spans: Sequence[Tuple[int, int, int,
 
 @register_position_encoding("mrope")
 class MRope(PositionEncoding):
+    graph_safe = True                # forward is a fixed sequence of this engine's kernels
     axes = 3
 
     def __init__(self, head_dim: int, theta: float, sections: Sequence[int]):

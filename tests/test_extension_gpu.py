@@ -1,6 +1,7 @@
-"""A toy mixer with state of its own, and a toy architecture around it, are registered from
-here, built, loaded and stepped without a change to the engine's files.  The toy model also
-runs one layer twice and lets one stop read another stop's cache."""
+"""Toy parts and toy architectures around them are registered from here, built, loaded and stepped
+without a change to the engine's files: a mixer with state of its own (its model also runs one layer
+twice and lets one stop read another stop's cache), a feed-forward that routes tokens to experts,
+and a position encoding with one axis and another pairing of channels."""
 
 import json
 import os
@@ -147,3 +148,148 @@ def test_toy_architecture_builds_loads_and_steps(tmp_path):
     assert np.abs(np.concatenate(got_a) - want_a).max() < 1e-4
     assert np.abs(np.concatenate(got_b) - want_b).max() < 1e-4
     assert np.abs(np.concatenate(got_a) - whole).max() < 1e-5
+
+
+# ---- a feed-forward with routing and another position encoding, defined here ----------------------
+from qwen25vl_lite.parts import (FEED_FORWARDS, POSITION_ENCODINGS, FeedForward, PositionEncoding,  # noqa: E402
+                                 register_feed_forward, register_position_encoding)
+
+EXPERTS, EXPERT_INTER, THETA2 = 3, 24, 500.0
+
+if "toy_routed" not in FEED_FORWARDS:
+    @register_feed_forward("toy_routed")
+    class ToyRouted(FeedForward):
+        """Every token goes to the one expert whose router logit is largest (logits in float32);
+        an expert is relu(h W1^T) W2^T.  The cache and the scheduler know nothing of it."""
+
+        def __init__(self, hidden_size, num_experts, expert_size):
+            self.h, self.e, self.i = hidden_size, num_experts, expert_size
+
+        def tensor_specs(self):
+            return (TensorSpec("router.weight", (self.e, self.h)), TensorSpec("w1", (self.e, self.i, self.h)),
+                    TensorSpec("w2", (self.e, self.h, self.i)))
+
+        def load(self, tensors, device, dtype):
+            self.router = tensors["router.weight"].to(device=device, dtype=torch.float32)
+            self.w1 = tensors["w1"].to(device=device, dtype=torch.float32)
+            self.w2 = tensors["w2"].to(device=device, dtype=torch.float32)
+
+        def forward(self, ctx, h):
+            x = h.float()
+            choice = (x @ self.router.T).argmax(dim=1)
+            out = torch.empty_like(x)
+            for e in range(self.e):
+                rows = (choice == e).nonzero().flatten()
+                if rows.numel():
+                    out[rows] = torch.relu(x[rows] @ self.w1[e].T) @ self.w2[e].T
+            return out.to(h.dtype)
+
+
+if "toy_rope_pairs" not in POSITION_ENCODINGS:
+    @register_position_encoding("toy_rope_pairs")
+    class ToyRopePairs(PositionEncoding):
+        """One position axis; channels (2j, 2j+1) are rotated together (not j with j + D/2).  It has
+        no tables for the fused decode kernel, so its model runs the general attention path."""
+
+        axes = 1
+
+        def __init__(self, head_dim, theta):
+            self.d, self.theta = int(head_dim), float(theta)
+
+        def load(self, tensors, device, dtype):
+            self.inv = (1.0 / self.theta ** (torch.arange(0, self.d, 2, dtype=torch.float32) / self.d)).to(device)
+
+        def default_positions(self, start, count, offset):
+            return np.arange(start + offset, start + offset + count, dtype=np.int64)[None, :]
+
+        def rotate_and_store(self, ctx, qkv, nq, nkv, head_dim, kv):
+            n = qkv.shape[0]
+            ang = ctx.positions[0].float()[:, None] * self.inv[None, :]              # [n, D/2]
+            cos, sin = ang.cos()[:, None, :], ang.sin()[:, None, :]
+            heads = qkv.view(n, nq + 2 * nkv, head_dim)
+            x = heads[:, :nq + nkv].float()
+            a, b = x[..., 0::2], x[..., 1::2]
+            y = torch.stack([a * cos - b * sin, b * cos + a * sin], dim=-1).reshape(n, nq + nkv, head_dim)
+            heads[:, :nq + nkv] = y.to(qkv.dtype)
+            if kv is not None:
+                slot = kv.kv_slot.long()
+                ok = slot >= 0
+                page, off = slot[ok] // kv.page_size, slot[ok] % kv.page_size
+                kv.k_pages[page, :, off] = heads[ok, nq:nq + nkv]
+                kv.v_pages[page, :, off] = heads[ok, nq + nkv:]
+
+
+def toy2_spec(cfg):
+    norms = lambda: (PartSpec("rmsnorm", dict(dim=HIDDEN, eps=EPS), "norm_a."), PartSpec("rmsnorm", dict(dim=HIDDEN, eps=EPS), "norm_b."))
+    attn = PartSpec("gqa_attention", dict(hidden_size=HIDDEN, num_heads=HEADS, num_kv_heads=KV, head_dim=D), "attn.")
+    layers = (
+        LayerSpec("prenorm_residual", attn, PartSpec("toy_routed", dict(hidden_size=HIDDEN, num_experts=EXPERTS, expert_size=EXPERT_INTER), "moe."),
+                  norms(), "blocks.0."),
+        LayerSpec("prenorm_residual", attn, PartSpec("swiglu", dict(hidden_size=HIDDEN, intermediate_size=INTER), "ffn."), norms(), "blocks.1."),
+    )
+    return ModelSpec(
+        embedding=PartSpec("token_embedding", dict(vocab_size=VOCAB, hidden_size=HIDDEN), "embed."),
+        layers=layers, schedule=(ScheduleEntry(0), ScheduleEntry(1)),
+        final_norm=PartSpec("rmsnorm", dict(dim=HIDDEN, eps=EPS), "final_norm."),
+        head=PartSpec("linear_head", dict(vocab_size=VOCAB, hidden_size=HIDDEN, tied=True), "head."),
+        position=PartSpec("toy_rope_pairs", dict(head_dim=D, theta=THETA2)),
+    )
+
+
+register_architecture("ToyRoutedForTest", lambda raw: dict(raw), toy2_spec, replace=True)
+
+
+def oracle2(w, ids):
+    n = len(ids)
+    pos = np.arange(n, dtype=np.float64)
+    inv = 1.0 / THETA2 ** (np.arange(0, D, 2, dtype=np.float64) / D)
+    ang = pos[:, None] * inv[None, :]
+    cos, sin = np.cos(ang)[:, None, :], np.sin(ang)[:, None, :]
+
+    def rot(x):
+        a, b = x[..., 0::2], x[..., 1::2]
+        return np.stack([a * cos - b * sin, b * cos + a * sin], axis=-1).reshape(x.shape)
+
+    x = w["embed.weight"][np.asarray(ids)]
+    for layer in (0, 1):
+        p = f"blocks.{layer}."
+        h = plain.rms_norm(x, w[p + "norm_a.weight"], EPS)
+        q = (h @ w[p + "attn.q_proj.weight"].T + w[p + "attn.q_proj.bias"]).reshape(n, HEADS, D)
+        k = (h @ w[p + "attn.k_proj.weight"].T + w[p + "attn.k_proj.bias"]).reshape(n, KV, D)
+        v = (h @ w[p + "attn.v_proj.weight"].T + w[p + "attn.v_proj.bias"]).reshape(n, KV, D)
+        x = x + plain.causal_attention(rot(q), rot(k), v).reshape(n, HEADS * D) @ w[p + "attn.o_proj.weight"].T
+        h = plain.rms_norm(x, w[p + "norm_b.weight"], EPS)
+        if layer == 0:
+            choice = (h @ w[p + "moe.router.weight"].T).argmax(axis=1)
+            out = np.zeros_like(h)
+            for t in range(n):
+                e = choice[t]
+                out[t] = np.maximum(h[t] @ w[p + "moe.w1"][e].T, 0) @ w[p + "moe.w2"][e].T
+            x = x + out
+        else:
+            x = x + plain.swiglu_mlp(h, w, p + "ffn.")
+    return plain.rms_norm(x, w["final_norm.weight"], EPS) @ w["embed.weight"].T
+
+
+def test_toy_routed_feed_forward_and_other_position_encoding(tmp_path):
+    """A feed-forward that routes tokens to experts and a position encoding with one axis and
+    another pairing of channels, both defined in this file: registered, built into a model by data,
+    loaded from a random model folder, and stepped whole, in portions and token by token."""
+    folder = write_random_model(str(tmp_path / "toy2"), {"architectures": ["ToyRoutedForTest"]}, seed=9, prefix="")
+    _, model = load_model(folder, "float32", "cuda:0")
+    runner = ModelRunner(model, 12, 8, 2)
+    assert runner.axes == 1
+    w = {k: v.astype(np.float64) for k, v in plain.read_safetensors(os.path.join(folder, "model.safetensors")).items()}
+    ids = np.random.default_rng(3).integers(0, VOCAB, size=37).tolist()
+    want = oracle2(w, ids)
+    r = runner.open_request("whole")
+    whole = runner.step([StepEntry(r, ids, list(range(37)))]).cpu().numpy()
+    runner.close_request(r)
+    assert np.abs(whole - want).max() < 1e-4
+    r = runner.open_request("cut")
+    got = [runner.step([StepEntry(r, ids[:20], list(range(20)))]).cpu().numpy(),
+           runner.step([StepEntry(r, ids[20:23], [0, 1, 2])]).cpu().numpy()]
+    got += [runner.step([StepEntry(r, [t], [0])]).cpu().numpy() for t in ids[23:]]
+    runner.close_request(r)
+    assert np.abs(np.concatenate(got) - want).max() < 1e-4
+    runner.cache.check(runner.live.values())
