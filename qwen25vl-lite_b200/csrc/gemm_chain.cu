@@ -27,9 +27,15 @@
 //     group's counter adds them in slice order and runs the epilogue: nobody waits, and the result
 //     does not depend on timing.
 //
+//   * The decode attention between a layer's qkv and o products is an operation of the chain too
+//     (the unit of attention_decode.cuh run by the eight MMA warps on 16-key tiles, in the shared
+//     memory that x otherwise takes): a layer is then one stretch of one kernel, the warps start
+//     the copies of their first key tiles while they still wait for the qkv product of the other
+//     CTAs, and the producer warp fills the ring with the o and gate/up weights meanwhile.
+//
 // Every wait (mbarrier or grid barrier) is bounded: when it gives up, the kernel records a code in
 // *err, stops waiting anywhere and runs to its end (its output is then invalid).
-#include "common.cuh"
+#include "attention_decode.cuh"
 
 enum { EPI_STORE = 0, EPI_BIAS = 1, EPI_F32 = 2, EPI_SWIGLU = 3, EPI_RESIDUAL = 4 };
 
@@ -55,11 +61,15 @@ struct ChainOp {
   int ldx, ldo, M, N, K, epi, norm;
   float eps;
   int slices, slice_k, ctas, groups;   // K cut into `slices` of `slice_k` elements; `ctas` CTAs work in each slice
+  int kind;               // 0: a product (the fields above); 1: decode attention (the fields below)
+  int attn_d, attn_units; // head size; units = entries x kv heads x key ranges
+  AttnArgs attn;
+  RopeArgs rope;
 };
 
 struct ChainArgs {
   int n_ops, n_stages;
-  int x_bytes;            // shared memory kept for x: rows * GC_PITCH
+  int x_off;              // where x (and the attention unit's memory) begins in shared memory
   float* scratch;         // slots of partial sums, [slice][group][MT * 128] floats, reused by every operation
   int* counters;          // one per group, zero before the launch and after it
   unsigned* barrier;      // arrivals at the barriers between operations; only grows
@@ -151,12 +161,14 @@ __device__ __forceinline__ void gc_store_group(const float (&acc)[MT][4], int gr
   }
 }
 
-template <int MT>
+// ATTN: whether the kernel can run attention operations (a variant of its own, so that their
+// registers and code do not weigh on chains of products alone).
+template <int MT, bool ATTN>
 __global__ void __launch_bounds__(GC_THREADS, 1) gemm_chain_kernel(const __grid_constant__ ChainArgs A) {
   extern __shared__ __align__(128) unsigned char smem[];
   const int S = A.n_stages;
-  unsigned char* xs = smem;
-  unsigned char* slots = smem + A.x_bytes;
+  unsigned char* xs = smem + A.x_off;             // x of a product, or the memory of an attention unit
+  unsigned char* slots = smem;
   float* red = reinterpret_cast<float*>(slots + (size_t)S * GC_SLOT);
   unsigned long long* full = reinterpret_cast<unsigned long long*>(red + GC_RED_BUFS * GC_CONSUMERS * 32 * MT * 4);
   unsigned long long* empty = full + S;
@@ -188,6 +200,7 @@ __global__ void __launch_bounds__(GC_THREADS, 1) gemm_chain_kernel(const __grid_
     unsigned parity = 1;
     for (int k = 0; k < A.n_ops; ++k) {
       const ChainOp& op = A.op[k];
+      if (op.kind) continue;                         // attention streams no weights
       const int slice = cta / op.ctas, r = cta - slice * op.ctas;
       if (slice >= op.slices) continue;
       const int k0 = slice * op.slice_k;
@@ -233,6 +246,17 @@ __global__ void __launch_bounds__(GC_THREADS, 1) gemm_chain_kernel(const __grid_
           gc_arrive(go);
         }
         ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+      }
+      if (op.kind) {
+        // attention: the MMA warps do everything and say so through the ring of partial-sum buffers
+        if (ok) {
+          ok = gc_wait(red_full + rb, red_parity);
+          if (!ok && lane == 0) atomicExch(A.err, 19);
+        }
+        __syncwarp();
+        if (lane == 0) gc_arrive(red_empty + rb);
+        if (++rb == GC_RED_BUFS) { rb = 0; red_parity ^= 1; }
+        continue;
       }
       const int slice = cta / op.ctas, r = cta - slice * op.ctas;
       if (slice >= op.slices) continue;
@@ -342,8 +366,43 @@ __global__ void __launch_bounds__(GC_THREADS, 1) gemm_chain_kernel(const __grid_
   int s = 0, rb = 0;
   unsigned parity = 0, red_parity = 1;
   bool red_wrapped = false;
+  const int ctid = threadIdx.x;                     // 0 .. 255 in the MMA warps
+  auto consumer_sync = [] { asm volatile("bar.sync 1, %0;\n" ::"n"(GC_CONSUMERS * 32) : "memory"); };
   for (int k = 0; k < A.n_ops; ++k) {
     const ChainOp& op = A.op[k];
+    if (ATTN && op.kind) {
+      // ---- decode attention: unit u = (entry, kv head, key range) on CTA u, u + grid, ... ----
+      const int per_item = op.attn.nkv * op.attn.n_splits;
+      consumer_sync();                               // every warp is done with x of the product before
+      int u = cta;
+      if (u < op.attn_units) {                       // the first tiles hold keys of earlier steps: no need to wait
+        if (op.attn_d == 128) DecodeUnit<128, GC_CONSUMERS, 16, 1>::prefetch(op.attn, u / per_item, (u / op.attn.n_splits) % op.attn.nkv, u % op.attn.n_splits, xs, ctid);
+        else DecodeUnit<64, GC_CONSUMERS, 16, 1>::prefetch(op.attn, u / per_item, (u / op.attn.n_splits) % op.attn.nkv, u % op.attn.n_splits, xs, ctid);
+      }
+      if (k > 0 && ok) {
+        ok = gc_wait(go, (unsigned)(k - 1) & 1);
+        if (!ok && lane == 0) atomicExch(A.err, 12);
+      }
+      for (; u < op.attn_units; u += gridDim.x) {
+        const int item = u / per_item, kvh = (u / op.attn.n_splits) % op.attn.nkv, split = u % op.attn.n_splits;
+        if (u != cta) {
+          consumer_sync();
+          if (op.attn_d == 128) DecodeUnit<128, GC_CONSUMERS, 16, 1>::prefetch(op.attn, item, kvh, split, xs, ctid);
+          else DecodeUnit<64, GC_CONSUMERS, 16, 1>::prefetch(op.attn, item, kvh, split, xs, ctid);
+        }
+        if (op.attn_d == 128) DecodeUnit<128, GC_CONSUMERS, 16, 1>::run(op.attn, op.rope, item, kvh, split, xs, ctid, consumer_sync);
+        else DecodeUnit<64, GC_CONSUMERS, 16, 1>::run(op.attn, op.rope, item, kvh, split, xs, ctid, consumer_sync);
+      }
+      __threadfence();                               // what this warp wrote, before the CTA says it is done
+      if (red_wrapped && ok) {
+        ok = gc_wait(red_empty + rb, red_parity);
+        if (!ok && lane == 0) atomicExch(A.err, 17);
+      }
+      __syncwarp();
+      if (lane == 0) gc_arrive(red_full + rb);
+      if (++rb == GC_RED_BUFS) { rb = 0; red_wrapped = true; red_parity ^= 1; }
+      continue;
+    }
     if (k > 0 && ok) {
       ok = gc_wait(go, (unsigned)(k - 1) & 1);
       if (!ok && lane == 0) atomicExch(A.err, 12);
@@ -496,6 +555,7 @@ __global__ void __launch_bounds__(GC_THREADS, 1) gemm_chain_kernel(const __grid_
 // ------------------------------------------------------------------------------------------------
 // The description of one operation as the caller gives it (plain C layout, read through ctypes).
 struct ChainOpDesc {
+  // kind 0: a product
   const void* W;
   const void* X;
   const float* norm_w;
@@ -503,10 +563,50 @@ struct ChainOpDesc {
   void* out;
   int ldx, ldo, M, N, K, epi, norm;
   float eps;
+  int kind;
+  // kind 1: decode attention, the arguments of q25_attention_decode_fused_bf16
+  const void* qkv;
+  void* attn_out;
+  void* kpages;
+  void* vpages;
+  const int* block_table;
+  const int* cu_q;
+  const int* q_start;
+  const int* items;
+  const int* positions;
+  const float* inv_freq;
+  const int* axis;
+  const int* kv_slot;
+  float* attn_scratch;
+  int* attn_counters;
+  const void* angles;
+  int qkv_stride, table_width, n_items, nq, nkv, d, page_size, window, n_splits, n_tokens;
+  float scale;
   int reserved;
 };
 
 static bool chain_cut(const ChainOpDesc& d, ChainOp& op) {
+  op.kind = d.kind;
+  if (d.kind == 1) {
+    if (d.n_items <= 0 || (d.d != 64 && d.d != 128)) return false;
+    if (fill_args(op.attn, d.qkv, d.qkv_stride, d.attn_out, d.kpages, d.vpages, d.block_table, d.table_width, d.cu_q,
+                  d.q_start, d.items, d.nq, d.nkv, d.page_size, d.window, d.scale))
+      return false;
+    if (d.nq / d.nkv > 16 || d.n_splits < 1 || d.n_splits > 64 || !d.positions || !d.inv_freq || !d.axis || !d.kv_slot ||
+        (d.n_splits > 1 && (!d.attn_scratch || !d.attn_counters)))
+      return false;
+    op.attn.n_splits = d.n_splits;
+    op.attn.part_o = d.attn_scratch;
+    op.attn.part_ml = d.attn_scratch ? d.attn_scratch + (size_t)d.n_items * d.nq * d.n_splits * d.d : nullptr;
+    op.rope.positions = d.positions; op.rope.n_tokens = d.n_tokens; op.rope.inv_freq = d.inv_freq; op.rope.axis = d.axis;
+    op.rope.kv_slot = d.kv_slot; op.rope.kpages_w = (bf16*)d.kpages; op.rope.vpages_w = (bf16*)d.vpages;
+    op.rope.counters = d.attn_counters; op.rope.angles = (const float2*)d.angles;
+    op.attn_d = d.d;
+    op.attn_units = d.n_items * d.nkv * d.n_splits;
+    op.slices = 1; op.slice_k = 0; op.ctas = GC_SMS; op.groups = 0; op.M = 0;
+    return true;
+  }
+  if (d.kind != 0) return false;
   if (d.M <= 0 || d.M > 16 || d.N <= 0 || d.K <= 0 || d.K % 32) return false;
   if (((unsigned long long)d.W & 15) || ((unsigned long long)d.X & 15)) return false;
   if (d.norm ? (d.ldx % 4 || !d.norm_w) : (d.ldx % 8 != 0)) return false;
@@ -519,18 +619,23 @@ static bool chain_cut(const ChainOpDesc& d, ChainOp& op) {
   if (op.slices > GC_SMS || (long long)(op.slices - 1) * op.slice_k >= d.K) return false;
   op.ctas = GC_SMS / op.slices;
   if (op.ctas > op.groups) op.ctas = op.groups;
+  op.attn_d = 0; op.attn_units = 0;
   return true;
 }
 
-// Shared memory of the kernel for rows of x up to `rows` (8 or 16): stages that fit, and the total.
-static int chain_smem(int rows, int& n_stages, int& x_bytes) {
+// Shared memory of the kernel: the ring of stages, the partial-sum buffers and the barriers, then
+// room for x of up to `rows` rows (8 or 16) or, with an attention operation, for its unit.
+static int chain_smem(int rows, bool attention, int& n_stages, int& x_off) {
   const int MT = rows <= 8 ? 1 : 2;
-  x_bytes = rows * GC_PITCH;
+  int tail = rows * GC_PITCH;
+  const int unit = DecodeUnit<128, GC_CONSUMERS, 16, 1>::SMEM;
+  if (attention && tail < unit) tail = unit;
   const int red = GC_RED_BUFS * GC_CONSUMERS * 32 * MT * 4 * (int)sizeof(float);
-  const int bars = 64 * (int)sizeof(unsigned long long);
-  n_stages = (GC_SMEM_LIMIT - x_bytes - red - bars) / GC_SLOT;
+  const int bars = 1024;
+  n_stages = (GC_SMEM_LIMIT - tail - red - bars) / GC_SLOT;
   if (n_stages > 24) n_stages = 24;
-  return x_bytes + n_stages * GC_SLOT + red + bars;
+  x_off = n_stages * GC_SLOT + red + bars;
+  return x_off + tail;
 }
 
 // Floats of scratch that a chain needs (0: no operation cuts K).
@@ -539,7 +644,7 @@ Q25_EXPORT long long q25_gemm_chain_scratch_floats(const ChainOpDesc* ops, int n
   for (int i = 0; i < n_ops; ++i) {
     ChainOp op;
     if (!chain_cut(ops[i], op)) return -1;
-    if (op.slices > 1) {
+    if (op.kind == 0 && op.slices > 1) {
       const long long need = (long long)op.slices * op.groups * (ops[i].M <= 8 ? 1 : 2) * 128;
       if (need > most) most = need;
     }
@@ -560,10 +665,14 @@ Q25_EXPORT int q25_gemm_chain_available(void) {
   return known;
 }
 
-// Runs ops[0 .. n_ops) (at most 8, each at most 16 rows) as one kernel; every operation may read
-// what the ones before it wrote.  scratch: q25_gemm_chain_scratch_floats() floats; counters: 65536
-// ints, zero; barrier: one unsigned int whose value when the launch begins is barrier_base (each
-// launch adds (n_ops - 1) * 148 to it); err: one int that receives a nonzero code if a wait gave up.
+// Size of the description struct, so that a caller that builds it elsewhere can check its layout.
+Q25_EXPORT int q25_gemm_chain_desc_bytes(void) { return (int)sizeof(ChainOpDesc); }
+
+// Runs ops[0 .. n_ops) (at most 8; products of at most 16 rows, decode attentions of head size 64 or
+// 128) as one kernel; every operation may read what the ones before it wrote.  scratch:
+// q25_gemm_chain_scratch_floats() floats; counters: 65536 ints, zero; barrier: one unsigned int whose
+// value when the launch begins is barrier_base (each launch adds (n_ops - 1) * 148 to it); err: one
+// int that receives a nonzero code if a wait gave up.
 Q25_EXPORT int q25_gemm_chain_bf16(const ChainOpDesc* ops, int n_ops, float* scratch, int* counters, unsigned* barrier,
                                    unsigned barrier_base, int* err, void* stream) {
   if (n_ops <= 0) return 0;
@@ -572,15 +681,18 @@ Q25_EXPORT int q25_gemm_chain_bf16(const ChainOpDesc* ops, int n_ops, float* scr
   A.n_ops = n_ops;
   A.scratch = scratch; A.counters = counters; A.barrier = barrier; A.barrier_base = barrier_base; A.err = err;
   int rows = 0;
+  bool attention = false;
   for (int i = 0; i < n_ops; ++i) {
     if (!chain_cut(ops[i], A.op[i])) return (int)cudaErrorInvalidValue;
+    if (A.op[i].kind) { attention = true; continue; }
     if (A.op[i].groups > 65536 || (A.op[i].slices > 1 && !scratch)) return (int)cudaErrorInvalidValue;
     if (ops[i].M > rows) rows = ops[i].M;
   }
   rows = rows <= 8 ? 8 : 16;
-  const int total = chain_smem(rows, A.n_stages, A.x_bytes);
+  const int total = chain_smem(rows, attention, A.n_stages, A.x_off);
   if (A.n_stages < 2) return (int)cudaErrorInvalidValue;
-  void (*kernel)(const ChainArgs) = rows <= 8 ? gemm_chain_kernel<1> : gemm_chain_kernel<2>;
+  void (*kernel)(const ChainArgs) = attention ? (rows <= 8 ? gemm_chain_kernel<1, true> : gemm_chain_kernel<2, true>)
+                                              : (rows <= 8 ? gemm_chain_kernel<1, false> : gemm_chain_kernel<2, false>);
   cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, total);
   if (e != cudaSuccess) return (int)e;
   cudaLaunchConfig_t cfg = {};
@@ -590,7 +702,7 @@ Q25_EXPORT int q25_gemm_chain_bf16(const ChainOpDesc* ops, int n_ops, float* scr
   cfg.stream = (cudaStream_t)stream;
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeCooperative;
-  attr[0].val.cooperative = (getenv("Q25VL_CHAIN_COOP") && getenv("Q25VL_CHAIN_COOP")[0] == '0') ? 0 : 1;
+  attr[0].val.cooperative = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
   e = cudaLaunchKernelEx(&cfg, kernel, A);

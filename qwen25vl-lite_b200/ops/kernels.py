@@ -237,6 +237,25 @@ def attention_decode_fused(qkv: torch.Tensor, out: torch.Tensor, k_pages: torch.
                           f"group {nq // nkv} or splits {n_splits}")
     if positions.dtype != torch.int32 or positions.dim() != 2 or positions.shape[0] != 3:
         raise KernelError("attention_decode_fused: positions must be int32 [3, N]")
+    if _chain is not None and CHAIN_ATTENTION and head_dim in (64, 128):
+        # an operation of the chain: it runs between the qkv product before it and the o product after
+        counters = _split_counters(qkv.device, n_items * nkv)
+        desc = _ChainOpDesc(kind=1, qkv=qkv.data_ptr(), attn_out=out.data_ptr(), kpages=k_pages.data_ptr(),
+                            vpages=v_pages.data_ptr(), block_table=block_table.data_ptr(), cu_q=cu_q.data_ptr(),
+                            q_start=q_start_pos.data_ptr(), items=items.data_ptr(), positions=positions.data_ptr(),
+                            inv_freq=inv_freq.data_ptr(), axis=axis.data_ptr(), kv_slot=kv_slot.data_ptr(),
+                            attn_scratch=_ptr(scratch), attn_counters=counters.data_ptr(), angles=_ptr(angles),
+                            qkv_stride=qkv.stride(0), table_width=block_table.shape[1], n_items=n_items, nq=nq, nkv=nkv,
+                            d=head_dim, page_size=page_size, window=int(window or 0), n_splits=int(n_splits),
+                            n_tokens=positions.shape[1], scale=float(scale))
+        keep = (qkv, out, k_pages, v_pages, block_table, cu_q, q_start_pos, items, positions, inv_freq, axis, kv_slot,
+                scratch, counters, angles)
+        args = (qkv, out, k_pages, v_pages, block_table, cu_q, q_start_pos, items, nq, nkv, head_dim, page_size, window,
+                scale, n_splits, positions, inv_freq, axis, kv_slot, scratch, angles)
+        _chain.append((desc, keep, lambda: attention_decode_fused(*args)))
+        if len(_chain) == CHAIN_MAX_OPS:
+            chain_flush()
+        return
     _check(_fn("q25_attention_decode_fused_bf16",
                [_P, _I, _P, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _I, _P, _I, _P, _P, _P, _P, _P, _P, _P])(
         qkv.data_ptr(), qkv.stride(0), out.data_ptr(), k_pages.data_ptr(), v_pages.data_ptr(), block_table.data_ptr(),
@@ -371,14 +390,26 @@ def gemm_skinny_norm(x: torch.Tensor, norm_weight: torch.Tensor, eps: float, w: 
 
 
 class _ChainOpDesc(ctypes.Structure):
+    """One operation of a chain as ``csrc/gemm_chain.cu`` reads it (``ChainOpDesc``): a product
+    (kind 0) or a decode attention (kind 1, the arguments of ``attention_decode_fused``)."""
     _fields_ = [("W", _P), ("X", _P), ("norm_w", _P), ("bias", _P), ("out", _P), ("ldx", _I), ("ldo", _I), ("M", _I),
-                ("N", _I), ("K", _I), ("epi", _I), ("norm", _I), ("eps", _F), ("reserved", _I)]
+                ("N", _I), ("K", _I), ("epi", _I), ("norm", _I), ("eps", _F), ("kind", _I),
+                ("qkv", _P), ("attn_out", _P), ("kpages", _P), ("vpages", _P), ("block_table", _P), ("cu_q", _P),
+                ("q_start", _P), ("items", _P), ("positions", _P), ("inv_freq", _P), ("axis", _P), ("kv_slot", _P),
+                ("attn_scratch", _P), ("attn_counters", _P), ("angles", _P),
+                ("qkv_stride", _I), ("table_width", _I), ("n_items", _I), ("nq", _I), ("nkv", _I), ("d", _I),
+                ("page_size", _I), ("window", _I), ("n_splits", _I), ("n_tokens", _I), ("scale", _F), ("reserved", _I)]
 
 
 CHAIN_MAX_OPS = 8
+# Whether the decode attention joins the chains as an operation.  Measured on B200 at the 3B sizes it
+# does not pay: a step took 2.57 ms with it against 2.28 ms without, because every barrier costs
+# the lateness of the slowest CTA (3 to 4 us with the attention's merge tail) where a kernel boundary
+# costs about as much.  The operation stays (``Q25VL_CHAIN_ATTENTION=1``) and is tested.
+CHAIN_ATTENTION = __import__("os").environ.get("Q25VL_CHAIN_ATTENTION", "0") == "1"
 CHAIN_GRID = 148                          # CTAs of the chain kernel: one per SM of a B200
 _chain_base = 0                           # value of the barrier counter when the next chain kernel begins
-_CHAIN_SAFE = {"q25_gemm_chain_bf16", "q25_gemm_chain_scratch_floats", "q25_gemm_chain_available",
+_CHAIN_SAFE = {"q25_gemm_chain_bf16", "q25_gemm_chain_scratch_floats", "q25_gemm_chain_available", "q25_gemm_chain_desc_bytes",
                "q25_gemm_skinny_resident", "q25_gemm_skinny_bf16", "q25_gemm_skinny_norm_bf16"}
 _chain: Optional[list] = None             # the waiting products: (description, tensors kept alive, replay as one kernel)
 _chain_state: Dict[torch.device, tuple] = {}
@@ -391,7 +422,11 @@ def chain_available() -> bool:
     import os
     if os.environ.get("Q25VL_GEMM_CHAIN", "1") == "0" or not torch.cuda.is_available():
         return False
-    return bool(_fn("q25_gemm_chain_available", [])())
+    if not _fn("q25_gemm_chain_available", [])():
+        return False
+    if _fn("q25_gemm_chain_desc_bytes", [])() != ctypes.sizeof(_ChainOpDesc):
+        raise KernelError("gemm_chain: the operation description here and in the library differ in layout")
+    return True
 
 
 def chain_begin() -> bool:
@@ -421,10 +456,14 @@ def chain_end() -> None:
 
 
 def _chain_add(x, norm_weight, eps, w, bias, out, epilogue) -> bool:
-    desc = _ChainOpDesc(w.data_ptr(), x.data_ptr(), _ptr(norm_weight), _ptr(bias), out.data_ptr(), x.stride(0),
-                        out.stride(0), x.shape[0], w.shape[0], w.shape[1], int(epilogue), 0 if norm_weight is None else 1,
-                        float(eps), 0)
-    _chain.append((desc, (x, norm_weight, w, bias, out)))
+    desc = _ChainOpDesc(W=w.data_ptr(), X=x.data_ptr(), norm_w=_ptr(norm_weight), bias=_ptr(bias), out=out.data_ptr(),
+                        ldx=x.stride(0), ldo=out.stride(0), M=x.shape[0], N=w.shape[0], K=w.shape[1], epi=int(epilogue),
+                        norm=0 if norm_weight is None else 1, eps=float(eps), kind=0)
+    if norm_weight is None:
+        alone = lambda: gemm_skinny(x, w, bias, out, int(epilogue))
+    else:
+        alone = lambda: gemm_skinny_norm(x, norm_weight, float(eps), w, bias, out, int(epilogue))
+    _chain.append((desc, (x, norm_weight, w, bias, out), alone))
     if len(_chain) == CHAIN_MAX_OPS:
         chain_flush()
     return True
@@ -438,14 +477,10 @@ def chain_flush() -> None:
     waiting, _chain = _chain, None            # the launches below must not gather again
     try:
         if len(waiting) == 1:
-            desc, (x, norm_weight, w, bias, out) = waiting[0]
-            if norm_weight is None:
-                gemm_skinny(x, w, bias, out, desc.epi)
-            else:
-                gemm_skinny_norm(x, norm_weight, desc.eps, w, bias, out, desc.epi)
+            waiting[0][2]()                       # the operation's own kernel
             return
-        device = waiting[0][1][4].device
-        ops = (_ChainOpDesc * len(waiting))(*[d for d, _ in waiting])
+        device = next(t for t in waiting[0][1] if t is not None).device
+        ops = (_ChainOpDesc * len(waiting))(*[w_[0] for w_ in waiting])
         need = _fn("q25_gemm_chain_scratch_floats", [_P, _I])
         need.restype = ctypes.c_longlong
         floats = need(ctypes.cast(ops, _P), len(waiting))
