@@ -126,7 +126,7 @@ def run_reference(args):
     repository's models, kernels or engine is imported on this path."""
     ref = os.path.join(ROOT, "baseline", "_ref")
     if not os.path.isdir(os.path.join(ref, "qwen25vl_lite")):
-        print(json.dumps({"impl": "reference", "unavailable": "baseline/_ref is not installed (see DESIGN.md)"}))
+        print(json.dumps({"impl": "reference", "unavailable": "the reference is not installed under baseline/_ref"}))
         return 0
     sys.path.insert(0, ref)
     try:
@@ -336,7 +336,7 @@ def run_ours(args):
 def main(argv=None):
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=128)
+    ap.add_argument("--steps", type=int, default=256)
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--layers", type=int, default=None, help="fewer layers than the model has (named in config)")
