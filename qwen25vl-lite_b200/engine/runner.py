@@ -204,6 +204,8 @@ class ModelRunner:
         """The model's forward with the weight-streaming products of consecutive parts gathered
         into single persistent kernels (``kernels.chain_begin``).  Only for steps whose forward
         launches nothing but this engine's kernels, which is what ``graph_safe`` parts promise."""
+        if self.dtype != torch.bfloat16:                  # the 32-bit path has no weight-streaming products
+            return self.model.forward(ctx)
         kernels.chain_begin()
         try:
             return self.model.forward(ctx)

@@ -28,10 +28,11 @@ NVCC_FLAGS = [
 ]
 
 # library name -> sources.  "core" holds every kernel of the 32-bit path and the generic
-# bfloat16 ones; "bf16" holds the tensor-core kernels that only the serving path loads.
+# bfloat16 ones; "bf16" holds the tensor-core kernels that only the serving path loads, so a
+# 32-bit run compiles (at its first call) only what it needs.
 LIBRARIES: Dict[str, List[str]] = {
-    "core": ["elementwise.cu", "rope_cache.cu", "attention_generic.cu", "attention_mma.cu", "gemm_f32.cu", "gemm_skinny.cu", "gemm_chain.cu", "gemm_tcgen05.cu",
-             "sampling.cu"],
+    "core": ["elementwise.cu", "rope_cache.cu", "attention_generic.cu", "gemm_f32.cu", "sampling.cu"],
+    "bf16": ["attention_mma.cu", "gemm_skinny.cu", "gemm_chain.cu", "gemm_tcgen05.cu"],
 }
 
 

@@ -58,12 +58,17 @@ def load_library(name: str = "core") -> ctypes.CDLL:
     return lib
 
 
-def _fn(symbol: str, argtypes, library: str = "core"):
+# symbols of the tensor-core kernels, which only the bfloat16 path loads (and so compiles)
+_BF16_SYMBOLS = ("q25_attention_decode", "q25_attention_prefill", "q25_gemm_skinny", "q25_gemm_chain", "q25_gemm_tcgen05",
+                 "q25_rope_angles")
+
+
+def _fn(symbol: str, argtypes, library: Optional[str] = None):
     if _chain and symbol not in _CHAIN_SAFE:
         chain_flush()                       # products that wait in the chain come before this kernel
     f = _fns.get(symbol)
     if f is None:
-        lib = load_library(library)
+        lib = load_library(library or ("bf16" if symbol.startswith(_BF16_SYMBOLS) else "core"))
         try:
             f = getattr(lib, symbol)
         except AttributeError as exc:

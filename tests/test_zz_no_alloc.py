@@ -20,7 +20,7 @@ SCRATCH_FLOATS = 4 * 1024 * 1024
 
 def _symbols():
     from qwen25vl_lite.ops import kernels
-    lib = kernels.load_library("core")
+    lib = kernels.load_library("bf16")
     fn = lib.q25_attention_decode_bf16_noalloc
     fn.argtypes = [P, I, P, P, P, P, I, P, P, P, I, I, I, I, I, I, F, I, P]
     fn.restype = I
