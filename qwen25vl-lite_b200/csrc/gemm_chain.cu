@@ -22,10 +22,13 @@
 //     (src/qwen25vl_lite/text.py:66) / add into the residual stream.  One request brings one row
 //     of a group, up to 4 KB (the copy engine takes a request about every 100 cycles whatever its
 //     size).
-//   * K longer than 2048 is cut into slices; a CTA works in one slice, so its slice of x fits into
-//     shared memory.  The slices' partial sums go to scratch slots, and the CTA that completes a
-//     group's counter adds them in slice order and runs the epilogue: nobody waits, and the result
-//     does not depend on timing.
+//   * K longer than 2048 is cut into slices, so that a slice of x fits into shared memory.  With
+//     few groups per CTA (a down projection: 128 groups) a CTA takes the slices of its group one
+//     after the other: the sums stay in registers, and the next slice of x arrives (cp.async into the
+//     other of two buffers) while this one is multiplied.  With many groups per CTA every CTA works
+//     in one slice; the slices' partial sums go to scratch slots, and an owner CTA, when all slices
+//     have counted themselves in, adds them in slice order and runs the epilogue.  Either way the
+//     result does not depend on timing.
 //
 //   * The decode attention between a layer's qkv and o products is an operation of the chain too
 //     (the unit of attention_decode.cuh run by the eight MMA warps on 16-key tiles, in the shared
@@ -61,6 +64,7 @@ struct ChainOp {
   int ldx, ldo, M, N, K, epi, norm;
   float eps;
   int slices, slice_k, ctas, groups;   // K cut into `slices` of `slice_k` elements; `ctas` CTAs work in each slice
+  int seq;                // 1: the K slices are taken one after the other by the same CTA (see below)
   int kind;               // 0: a product (the fields above); 1: decode attention (the fields below)
   int attn_d, attn_units; // head size; units = entries x kv heads x key ranges
   AttnArgs attn;
@@ -201,6 +205,25 @@ __global__ void __launch_bounds__(GC_THREADS, 1) gemm_chain_kernel(const __grid_
     for (int k = 0; k < A.n_ops; ++k) {
       const ChainOp& op = A.op[k];
       if (op.kind) continue;                         // attention streams no weights
+      if (op.seq) {
+        for (int grp = cta; grp < op.groups; grp += op.ctas) {
+          for (int j = 0; j < op.slices; ++j) {
+            const int k0 = j * op.slice_k;
+            const unsigned bytes = (unsigned)min(op.slice_k, op.K - k0) * 2;
+            if (wrapped && ok) {
+              ok = gc_wait(empty + s, parity);
+              if (!ok && lane == 0) atomicExch(A.err, 11);
+            }
+            unsigned char* st = slots + (size_t)s * GC_SLOT;
+            if (lane == 0) gc_expect_tx(full + s, bytes * GC_ROWS);
+            __syncwarp();
+            if (lane < GC_ROWS)
+              gc_bulk_copy(st + lane * GC_PITCH, op.W + (size_t)min(grp * GC_ROWS + lane, op.N - 1) * op.K + k0, bytes, full + s);
+            if (++s == S) { s = 0; wrapped = 1; parity ^= 1; }
+          }
+        }
+        continue;
+      }
       const int slice = cta / op.ctas, r = cta - slice * op.ctas;
       if (slice >= op.slices) continue;
       const int k0 = slice * op.slice_k;
@@ -258,9 +281,10 @@ __global__ void __launch_bounds__(GC_THREADS, 1) gemm_chain_kernel(const __grid_
         if (++rb == GC_RED_BUFS) { rb = 0; red_parity ^= 1; }
         continue;
       }
-      const int slice = cta / op.ctas, r = cta - slice * op.ctas;
-      if (slice >= op.slices) continue;
-      const bool add_old = op.epi == EPI_RESIDUAL && op.slices == 1;
+      const bool sliced = op.slices > 1 && !op.seq;    // the slices are other CTAs' and meet in scratch memory
+      const int slice = op.seq ? 0 : cta / op.ctas, r = op.seq ? cta : cta - slice * op.ctas;
+      if (op.seq ? cta >= op.ctas : slice >= op.slices) continue;
+      const bool add_old = op.epi == EPI_RESIDUAL && !sliced;
       for (int grp = r; grp < op.groups; grp += op.ctas) {
         float acc[MT][4];
 #pragma unroll
@@ -292,7 +316,7 @@ __global__ void __launch_bounds__(GC_THREADS, 1) gemm_chain_kernel(const __grid_
         if (lane == 0) gc_arrive(red_empty + rb);
         if (++rb == GC_RED_BUFS) { rb = 0; red_parity ^= 1; }
 
-        if (op.slices > 1) {
+        if (sliced) {
           // a slice's share of the group: into its scratch slot; who completes the group is settled
           // once for all groups, after the last one (one trip to memory, not one per group)
           float* mine = A.scratch + ((size_t)slice * op.groups + grp) * (MT * 128);
@@ -303,7 +327,7 @@ __global__ void __launch_bounds__(GC_THREADS, 1) gemm_chain_kernel(const __grid_
         }
         gc_store_group<MT>(acc, grp, op, add_old);
       }
-      if (op.slices > 1) {
+      if (sliced) {
         // Every slice's CTA counts its groups in; the i-th group of CTA r's list is finished by the
         // CTA of slice (i + r) mod slices, which waits (bounded) until all slices are in, adds their
         // shares in slice order and runs the epilogue.  All slices end at about the same time, so
@@ -406,6 +430,75 @@ __global__ void __launch_bounds__(GC_THREADS, 1) gemm_chain_kernel(const __grid_
     if (k > 0 && ok) {
       ok = gc_wait(go, (unsigned)(k - 1) & 1);
       if (!ok && lane == 0) atomicExch(A.err, 12);
+    }
+    if (op.seq) {
+      // ---- the K slices of a group one after the other; x slices through two buffers ----
+      if (cta >= op.ctas) continue;
+      const bf16* X = reinterpret_cast<const bf16*>(op.X);
+      const int xbuf_bytes = (op.M * GC_PITCH + 127) / 128 * 128;
+      const int my_groups = (op.groups - cta + op.ctas - 1) / op.ctas;
+      const int n_items = my_groups * op.slices;
+      auto fetch_x = [&](int item) {                  // the x slice of item (group, slice) into buffer item & 1
+        const int j = item % op.slices;
+        const int k0 = j * op.slice_k, chunks = min(op.slice_k, op.K - k0) / 8;     // 16-byte chunks of a row
+        unsigned char* dst = xs + (size_t)(item & 1) * xbuf_bytes;
+        for (int idx = ctid; idx < op.M * chunks; idx += GC_CONSUMERS * 32) {
+          const int row = idx / chunks, c = idx - row * chunks;
+          cp_async16(dst + (size_t)row * GC_PITCH + c * 16, X + (size_t)row * op.ldx + k0 + c * 8, true);
+        }
+        cp_async_commit();
+      };
+      fetch_x(0);
+      float acc[2][MT][4];
+      for (int item = 0; item < n_items; ++item) {
+        const int j = item % op.slices;
+        cp_async_wait<0>();
+        consumer_sync();                              // this item's x is in, and nobody reads the other buffer any more
+        if (item + 1 < n_items) fetch_x(item + 1);
+        if (j == 0) {
+#pragma unroll
+          for (int q = 0; q < 2; ++q)
+#pragma unroll
+            for (int mt = 0; mt < MT; ++mt) acc[q][mt][0] = acc[q][mt][1] = acc[q][mt][2] = acc[q][mt][3] = 0.f;
+        }
+        const unsigned char* xb = xs + (size_t)(item & 1) * xbuf_bytes + t * 16;
+        const int kblocks = min(op.slice_k, op.K - j * op.slice_k) / 32;
+        if (ok) {
+          ok = gc_wait(full + s, parity);
+          if (!ok && lane == 0) atomicExch(A.err, 14);
+        }
+        const unsigned char* st = slots + (size_t)s * GC_SLOT + g * GC_PITCH + t * 16;
+#pragma unroll 2
+        for (int kb = warp; kb < kblocks; kb += GC_CONSUMERS) {
+          const uint4 a0 = gc_lds128(st + kb * 64);
+          const uint4 a1 = gc_lds128(st + 8 * GC_PITCH + kb * 64);
+#pragma unroll
+          for (int mt = 0; mt < MT; ++mt) {
+            const uint4 b = gc_lds128(xb + (size_t)min(mt * 8 + g, op.M - 1) * GC_PITCH + kb * 64);
+            gc_mma(acc[0][mt], a0.x, a1.x, a0.y, a1.y, b.x, b.y);
+            gc_mma(acc[1][mt], a0.z, a1.z, a0.w, a1.w, b.z, b.w);
+          }
+        }
+        __syncwarp();
+        if (lane == 0) gc_arrive(empty + s);
+        if (++s == S) { s = 0; parity ^= 1; }
+        if (j + 1 < op.slices) continue;
+        // the group is complete: hand the sums to the epilogue warp
+        if (red_wrapped && ok) {
+          ok = gc_wait(red_empty + rb, red_parity);
+          if (!ok && lane == 0) atomicExch(A.err, 17);
+        }
+        float* dst = red + (((size_t)rb * GC_CONSUMERS + warp) * 32 + lane) * MT * 4;
+#pragma unroll
+        for (int mt = 0; mt < MT; ++mt)
+          *reinterpret_cast<float4*>(dst + mt * 4) = make_float4(acc[0][mt][0] + acc[1][mt][0], acc[0][mt][1] + acc[1][mt][1],
+                                                                 acc[0][mt][2] + acc[1][mt][2], acc[0][mt][3] + acc[1][mt][3]);
+        __syncwarp();
+        if (lane == 0) gc_arrive(red_full + rb);
+        if (++rb == GC_RED_BUFS) { rb = 0; red_wrapped = true; red_parity ^= 1; }
+      }
+      consumer_sync();                                // x of the next operation goes where these buffers are
+      continue;
     }
     const int slice = cta / op.ctas, r = cta - slice * op.ctas;
     if (slice >= op.slices) continue;
@@ -603,7 +696,7 @@ static bool chain_cut(const ChainOpDesc& d, ChainOp& op) {
     op.rope.counters = d.attn_counters; op.rope.angles = (const float2*)d.angles;
     op.attn_d = d.d;
     op.attn_units = d.n_items * d.nkv * d.n_splits;
-    op.slices = 1; op.slice_k = 0; op.ctas = GC_SMS; op.groups = 0; op.M = 0;
+    op.slices = 1; op.slice_k = 0; op.ctas = GC_SMS; op.groups = 0; op.M = 0; op.seq = 0;
     return true;
   }
   if (d.kind != 0) return false;
@@ -619,15 +712,19 @@ static bool chain_cut(const ChainOpDesc& d, ChainOp& op) {
   if (op.slices > GC_SMS || (long long)(op.slices - 1) * op.slice_k >= d.K) return false;
   op.ctas = GC_SMS / op.slices;
   if (op.ctas > op.groups) op.ctas = op.groups;
+  // few groups per CTA, no norm, at most 8 rows (two x buffers fit): the slices one after the other
+  op.seq = (op.slices > 1 && !d.norm && d.M <= 8 && op.groups <= 2 * GC_SMS) ? 1 : 0;
+  if (op.seq) op.ctas = op.groups < GC_SMS ? op.groups : GC_SMS;
   op.attn_d = 0; op.attn_units = 0;
   return true;
 }
 
 // Shared memory of the kernel: the ring of stages, the partial-sum buffers and the barriers, then
 // room for x of up to `rows` rows (8 or 16) or, with an attention operation, for its unit.
-static int chain_smem(int rows, bool attention, int& n_stages, int& x_off) {
+static int chain_smem(int rows, bool attention, bool two_x_buffers, int& n_stages, int& x_off) {
   const int MT = rows <= 8 ? 1 : 2;
   int tail = rows * GC_PITCH;
+  if (two_x_buffers) tail = 2 * ((8 * GC_PITCH + 127) / 128 * 128);
   const int unit = DecodeUnit<128, GC_CONSUMERS, 16, 1>::SMEM;
   if (attention && tail < unit) tail = unit;
   const int red = GC_RED_BUFS * GC_CONSUMERS * 32 * MT * 4 * (int)sizeof(float);
@@ -644,7 +741,7 @@ Q25_EXPORT long long q25_gemm_chain_scratch_floats(const ChainOpDesc* ops, int n
   for (int i = 0; i < n_ops; ++i) {
     ChainOp op;
     if (!chain_cut(ops[i], op)) return -1;
-    if (op.kind == 0 && op.slices > 1) {
+    if (op.kind == 0 && op.slices > 1 && !op.seq) {
       const long long need = (long long)op.slices * op.groups * (ops[i].M <= 8 ? 1 : 2) * 128;
       if (need > most) most = need;
     }
@@ -681,15 +778,16 @@ Q25_EXPORT int q25_gemm_chain_bf16(const ChainOpDesc* ops, int n_ops, float* scr
   A.n_ops = n_ops;
   A.scratch = scratch; A.counters = counters; A.barrier = barrier; A.barrier_base = barrier_base; A.err = err;
   int rows = 0;
-  bool attention = false;
+  bool attention = false, seq = false;
   for (int i = 0; i < n_ops; ++i) {
     if (!chain_cut(ops[i], A.op[i])) return (int)cudaErrorInvalidValue;
     if (A.op[i].kind) { attention = true; continue; }
-    if (A.op[i].groups > 65536 || (A.op[i].slices > 1 && !scratch)) return (int)cudaErrorInvalidValue;
+    if (A.op[i].seq) seq = true;
+    if (A.op[i].groups > 65536 || (A.op[i].slices > 1 && !A.op[i].seq && !scratch)) return (int)cudaErrorInvalidValue;
     if (ops[i].M > rows) rows = ops[i].M;
   }
   rows = rows <= 8 ? 8 : 16;
-  const int total = chain_smem(rows, attention, A.n_stages, A.x_off);
+  const int total = chain_smem(rows, attention, seq, A.n_stages, A.x_off);
   if (A.n_stages < 2) return (int)cudaErrorInvalidValue;
   void (*kernel)(const ChainArgs) = attention ? (rows <= 8 ? gemm_chain_kernel<1, true> : gemm_chain_kernel<2, true>)
                                               : (rows <= 8 ? gemm_chain_kernel<1, false> : gemm_chain_kernel<2, false>);
