@@ -85,3 +85,37 @@ def test_command_line(model_dirs):
     assert res.stdout.strip().splitlines()[-1] == str(plain.greedy_generate(cfg, w, prompt, 5))
     res = subprocess.run(cmd[:-2], cwd=ROOT, capture_output=True, text=True, timeout=300)
     assert res.returncode == 2 and "--prompt-token-ids is required" in res.stderr
+
+
+@pytest.mark.parametrize("hidden,heads,kv_heads,inter,batch", [(3584, 28, 4, 18944, 8), (5120, 40, 8, 27648, 13), (2048, 16, 2, 11008, 3)])
+def test_captured_decode_steps_agree_with_kernel_by_kernel_steps_at_full_layer_sizes(hidden, heads, kv_heads, inter, batch):
+    """Layer sizes of the 7B, 32B and 3B models (one layer, small vocabulary, random weights): decode
+    steps replayed from CUDA graphs, where the products run as chains of one persistent kernel with K
+    cut into slices, against the same steps launched kernel by kernel.  Query groups of 7, 5 and 8
+    heads, widths that are no power of two, 8, 13 and 3 rows."""
+    import torch
+    from qwen25vl_lite import LLM
+    from qwen25vl_lite.engine.runner import StepEntry
+    from qwen25vl_lite.ops import kernels
+    config = {"architectures": ["Qwen2_5_VLForConditionalGeneration"], "tie_word_embeddings": False,
+              "text_config": {"hidden_size": hidden, "num_hidden_layers": 1, "num_attention_heads": heads,
+                              "num_key_value_heads": kv_heads, "intermediate_size": inter, "vocab_size": 3000,
+                              "rms_norm_eps": 1e-6, "rope_theta": 1000000.0,
+                              "rope_scaling": {"type": "mrope", "mrope_section": [16, 24, 24]},
+                              "sliding_window": 32768, "use_sliding_window": False}}
+    outs = []
+    for graphs in (True, False):
+        llm = LLM(random_config=config, weights_seed=2, dtype="bfloat16", num_blocks=16 * 24, block_size=16, max_num_seqs=16,
+                  max_num_batched_tokens=4096, max_model_len=384, cuda_graph=graphs)
+        runner = llm.runner
+        rng = np.random.default_rng(8)
+        reqs = [runner.open_request(i) for i in range(batch)]
+        runner.step([StepEntry(r, rng.integers(0, 3000, size=int(rng.integers(5, 200))).tolist(), []) for r in reqs])
+        got = [runner.step([StepEntry(r, [int(rng.integers(0, 3000))], [0]) for r in reqs]).float().cpu().numpy() for _ in range(3)]
+        assert runner.graph_replays == (3 if graphs else 0)
+        assert int(kernels.error_flag("cuda:0")[0]) == 0
+        outs.append(np.stack(got))
+        del llm, runner
+        torch.cuda.empty_cache()
+    graph, eager = outs
+    assert np.abs(graph - eager).max() <= 2e-2 * np.abs(eager).max()
