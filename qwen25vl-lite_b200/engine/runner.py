@@ -219,6 +219,21 @@ class ModelRunner:
         the cache and every request's count has advanced."""
         if not entries:
             return None
+        return self._pack(entries)()
+
+    def prepare_decode(self, requests: Sequence[Request]):
+        """Everything of a step in which each of ``requests`` brings one token at its default
+        position and wants its logits, except the tokens themselves: pages, block tables, slots
+        and positions are packed now (while the step before still runs on the device), and
+        ``launch_prepared`` only has to add the token ids.  Nothing else may be stepped between."""
+        return self._pack([StepEntry(r, (0,), (0,)) for r in requests])
+
+    def launch_prepared(self, prepared, tokens: Sequence[int]) -> torch.Tensor:
+        return prepared(tokens)
+
+    def _pack(self, entries: Sequence[StepEntry]):
+        """Builds the step's arrays in the staging buffer; returns the function that runs the step
+        (optionally with other token ids than the entries brought, for ``prepare_decode``)."""
         if int(self._error_host[0]) != 0:
             raise kernels.KernelError(f"a kernel of the previous step gave up waiting (code {int(self._error_host[0])}); "
                                       "its results are invalid")
@@ -354,6 +369,17 @@ class ModelRunner:
                     gt[i, len(table):] = 0
                 at += n
 
+        return lambda tokens=None: self._run_packed(
+            tokens, entries, q_lens, starts, widths, graph_key, off, N, S, M, ps, tok, tok_s, pos_s, tseq_s, cu_s, qs_s, sl_s,
+            rows_s, g_slot_s, g_tab_s, dec_s, decode_list, tile_s, last_position)
+
+    def _run_packed(self, tokens, entries, q_lens, starts, widths, graph_key, off, N, S, M, ps, tok, tok_s, pos_s, tseq_s,
+                    cu_s, qs_s, sl_s, rows_s, g_slot_s, g_tab_s, dec_s, decode_list, tile_s, last_position):
+        if tokens is not None:
+            ids = np.asarray(tokens, dtype=np.int64)
+            if ids.shape != (N,) or ids.min() < 0 or ids.max() >= self.vocab_size:
+                raise ValueError(f"a prepared step needs {N} token ids in [0, {self.vocab_size})")
+            tok[:] = ids
         dev = self._device_ints
         dev[:off].copy_(self._staging[:off], non_blocking=True)
         if self._staging_free is not None:

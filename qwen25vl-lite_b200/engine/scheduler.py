@@ -145,6 +145,7 @@ class LLMEngine:
         self.finished: List[RequestOutput] = []
         self.stats_ = EngineStats()
         self._next_id = 0
+        self._prepared = None                 # the next decode step, packed ahead (see ``step``)
 
     # ---- requests ----------------------------------------------------------------------
     def add_request(self, prompt_token_ids: Seq[int], sampling_params: Optional[SamplingParams] = None, *,
@@ -269,38 +270,79 @@ class LLMEngine:
 
     # ---- stepping ----------------------------------------------------------------------
     def step(self) -> List[RequestOutput]:
-        """One scheduling iteration and one batch; returns the requests that finished."""
+        """One scheduling iteration and one batch; returns the requests that finished.
+
+        While the device runs a step whose requests will all decode one more token, the host
+        already packs the next step (pages, block tables, positions: everything but the token
+        ids), so that between two decode steps only the sampled ids have to travel."""
         t0 = time.perf_counter()
-        scheduled = self.schedule()
-        by_id = {s.seq_id: s for s in self.running}
+        prepared, self._prepared = self._prepared, None
         entries, samplers = [], []
         decoded = 0
-        for seq_id, n in scheduled.items():
-            seq = by_id[seq_id]
-            start = seq.num_computed
-            reaches_end = start + n == seq.num_tokens
-            entries.append(StepEntry(seq.request, seq.tokens(start, start + n), [n - 1] if reaches_end else [],
-                                     seq.positions(start, start + n)))
-            if reaches_end:
-                samplers.append(seq)
-            if n == 1 and seq.output_token_ids:
-                decoded += 1
-                self.stats_.decode_tokens += 1
-            else:
-                self.stats_.prefill_tokens += n
+        if prepared is not None and not self.waiting and [s.seq_id for s in self.running] == prepared[1] \
+                and all(s.pending == 1 for s in self.running):
+            samplers = list(self.running)
+            decoded = len(samplers)
+            self.stats_.decode_tokens += decoded
+            logits = self.runner.launch_prepared(prepared[0], [s.output_token_ids[-1] for s in samplers])
+        else:
+            scheduled = self.schedule()
+            by_id = {s.seq_id: s for s in self.running}
+            for seq_id, n in scheduled.items():
+                seq = by_id[seq_id]
+                start = seq.num_computed
+                reaches_end = start + n == seq.num_tokens
+                entries.append(StepEntry(seq.request, seq.tokens(start, start + n), [n - 1] if reaches_end else [],
+                                         seq.positions(start, start + n)))
+                if reaches_end:
+                    samplers.append(seq)
+                if n == 1 and seq.output_token_ids:
+                    decoded += 1
+                    self.stats_.decode_tokens += 1
+                else:
+                    self.stats_.prefill_tokens += n
+            logits = self.runner.step(entries) if entries else None
         done: List[RequestOutput] = []
-        if entries:
-            logits = self.runner.step(entries)
-            if samplers:
-                tokens = self.sampler.sample(
-                    logits, [s.params for s in samplers], [s.seed for s in samplers],
+        if samplers:
+            args = (logits, [s.params for s in samplers], [s.seed for s in samplers],
                     [len(s.output_token_ids) for s in samplers], [s.output_token_ids for s in samplers])
-                for seq, token in zip(samplers, tokens):
-                    self._accept(seq, int(token), done)
+            if hasattr(self.sampler, "sample_async"):
+                pending = self.sampler.sample_async(*args)
+                self._prepared = self._prepare_next(samplers)          # host work under the device's step
+                tokens = self.sampler.collect(pending)
+            else:
+                tokens = self.sampler.sample(*args)
+            for seq, token in zip(samplers, tokens):
+                self._accept(seq, int(token), done)
+            if done:
+                self._prepared = None
         self.stats_.steps += 1
         self.stats_.record_step(time.perf_counter() - t0, decoded)
         self.finished.extend(done)
         return done
+
+    def _prepare_next(self, samplers: List[Sequence]):
+        """Packs the next step while this one runs, if it is known already: nothing waits, every
+        running request has just reached its end (so it decodes one token next), none of them
+        ends by length with the token being drawn, and the pages are there.  Returns (what the
+        runner prepared, the ids of the requests in order) or None.  A request that ends by its
+        token, or anything else that changes the batch, makes ``step`` drop the preparation; the
+        pages it took stay with their requests."""
+        runner = self.runner
+        if self.waiting or not hasattr(runner, "prepare_decode") or len(samplers) != len(self.running) \
+                or len(self.running) > self.ecfg.max_num_batched_tokens:
+            return None
+        for seq in self.running:
+            if seq.prompt_positions is not None and seq.num_computed < len(seq.prompt_token_ids):
+                return None
+            if len(seq.output_token_ids) + 1 >= seq.params.max_tokens or seq.num_tokens + 1 >= self.ecfg.max_model_len:
+                return None
+        try:
+            for seq in self.running:
+                runner.cache.ensure(seq.request.cache, seq.num_computed + 1)
+        except OutOfPages:
+            return None
+        return runner.prepare_decode([seq.request for seq in self.running]), [s.seq_id for s in self.running]
 
     def _accept(self, seq: Sequence, token: int, done: List[RequestOutput]) -> None:
         seq.output_token_ids.append(token)

@@ -56,6 +56,7 @@ def filter_scores(scores: torch.Tensor, top_k: int, min_p: float, top_p: float) 
 class Sampler:
     def __init__(self, device):
         self.device = torch.device(device)
+        self._host = None                     # pinned buffer the sampled ids are copied to
 
     def _upload(self, values, dtype) -> torch.Tensor:
         return torch.tensor(values, dtype=dtype).to(self.device, non_blocking=True)
@@ -66,9 +67,25 @@ class Sampler:
 
         ``seeds[r]`` and ``token_indices[r]`` key the draw of row r; ``previous[r]`` are the
         tokens generated so far (only read for rows with penalties)."""
+        return self.collect(self.sample_async(logits, params, seeds, token_indices, previous))
+
+    def collect(self, pending) -> List[int]:
+        """Waits for the draw that ``sample_async`` started and returns its token ids."""
+        if pending is None:
+            return []
+        host, event, rows = pending
+        if event is None:
+            return host
+        event.synchronize()
+        return host[:rows].tolist()
+
+    def sample_async(self, logits: torch.Tensor, params: Sequence[SamplingParams], seeds: Sequence[int],
+                     token_indices: Sequence[int], previous: Optional[Sequence[Sequence[int]]] = None):
+        """Starts the draw and the copy of its result to pinned host memory; the host is free until
+        ``collect``."""
         rows = logits.shape[0]
         if rows == 0:
-            return []
+            return None
         if any(p.has_penalties for p in params):
             logits = logits.clone()
             ids: List[int] = []
@@ -102,4 +119,11 @@ class Sampler:
             kernels.sample_rows(logits, self._upload(temps, torch.float32),
                                 torch.from_numpy(seed_arr).to(self.device, non_blocking=True),
                                 self._upload([int(t) for t in token_indices], torch.int32), out)
-        return out.tolist()
+        if self.device.type != "cuda":
+            return out.tolist(), None, rows
+        if self._host is None or self._host.numel() < rows:
+            self._host = torch.empty(max(rows, 64), dtype=torch.int32, pin_memory=True)
+        self._host[:rows].copy_(out, non_blocking=True)
+        event = torch.cuda.Event()
+        event.record()
+        return self._host, event, rows

@@ -229,3 +229,61 @@ def test_abort_and_stats():
     assert [o.seq_id for o in outs] == [b]
     st = engine.stats()
     assert st["finished"] == 1 and st["running"] == 0 and st["kv_blocks_used"] == 0 and st["generated_tokens"] == 4
+
+
+# ---- the next decode step packed while this one runs ------------------------------------------------
+class PreparingRunner(FakeRunner):
+    """A step function that also offers ``prepare_decode`` / ``launch_prepared`` and counts them."""
+
+    prepared = launched = 0
+
+    def prepare_decode(self, requests):
+        self.prepared += 1
+        for r in requests:
+            assert self.cache.pages_missing(r.cache, r.cache.num_tokens + 1) == [0]      # the engine took the pages first
+        return list(requests)
+
+    def launch_prepared(self, prepared, tokens):
+        from qwen25vl_lite.engine.runner import StepEntry
+        self.launched += 1
+        assert len(tokens) == len(prepared)
+        return self.step([StepEntry(r, [t], [0]) for r, t in zip(prepared, tokens)])
+
+
+class AsyncSampler(FakeSampler):
+    def sample_async(self, rows, params, seeds, token_indices, previous):
+        return [next_token(h) for h in rows]
+
+    def collect(self, pending):
+        return pending
+
+
+def test_prepared_decode_steps_change_nothing():
+    """With a step function that can pack a decode step ahead, the engine uses it whenever the
+    next batch is known (all running requests decode, nothing waits, nobody ends by length), drops
+    it when a request ends by its token or a new one arrives, and the outputs are those of plain
+    scheduling: no token lost, repeated or out of order, pages right at every step."""
+    prompts = [[5, 6, 7], list(range(20, 31)), [9] * 6, [1, 2]]
+    lengths = [9, 14, 5, 11]
+    eos = next_token([5, 6, 7] + expected([5, 6, 7], 4))                    # request 0 ends by its 5th token
+    ecfg = EngineConfig(num_blocks=64, block_size=4, max_num_seqs=3)
+    runner = PreparingRunner(64, 4, ecfg.max_num_seqs)
+    engine = LLMEngine(runner, AsyncSampler(), ecfg, eos_token_id=eos)
+    runner._requests = _LiveView(engine)
+    ids = [engine.add_request(p, SamplingParams(max_tokens=n, ignore_eos=i != 0)) for i, (p, n) in enumerate(zip(prompts[:3], lengths))]
+    outs = {}
+    late = None
+    for step in range(200):
+        if step == 6:
+            late = engine.add_request(prompts[3], SamplingParams(max_tokens=lengths[3], ignore_eos=True))   # arrives mid-run
+        for o in engine.step():
+            outs[o.seq_id] = o
+        if not engine.has_work():
+            break
+    assert runner.launched > 5 and runner.prepared >= runner.launched          # some preparations were dropped
+    want0 = expected(prompts[0], lengths[0])
+    assert outs[ids[0]].output_token_ids == want0[:want0.index(eos) + 1] and outs[ids[0]].finish_reason == "stop"
+    for i in (1, 2):
+        assert outs[ids[i]].output_token_ids == expected(prompts[i], lengths[i])
+    assert outs[late].output_token_ids == expected(prompts[3], lengths[3])
+    runner.cache.check([])
