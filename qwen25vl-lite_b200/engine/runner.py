@@ -97,6 +97,7 @@ class StepContext:
     # query-group size G the (entry, 64-row tile) pairs of the other entries
     decode_items: Optional[torch.Tensor] = None
     prefill_tiles: Dict[int, Optional[torch.Tensor]] = field(default_factory=dict)
+    prefill_tiles128: Dict[int, Optional[torch.Tensor]] = field(default_factory=dict)    # the same in 128-row tiles
     # host copies, for parts written with torch operators (toy parts in tests)
     host_q_lens: List[int] = field(default_factory=list)
     host_q_start: List[int] = field(default_factory=list)
@@ -111,6 +112,7 @@ class StepContext:
                       group.page_size)
 
 
+PREFILL_TILE_ROWS = (64, 128)   # row tiles of the two prefill attention kernels (mma.sync, tcgen05)
 GRAPH_WIDTH_STEP = 16      # block-table widths of captured steps are rounded up to this many pages
 MAX_GRAPHS = 32
 
@@ -257,15 +259,16 @@ class ModelRunner:
 
         # ---- pack ----
         decode_list = [i for i, n in enumerate(q_lens) if n == 1]
-        tile_lists = {}
+        tile_lists = {}                                   # (group size, rows of a tile) -> (entry, tile) pairs
         for G in self.group_sizes:
-            pairs = []
-            for i, n in enumerate(q_lens):
-                if n > 1 or G > 16:
-                    pairs += [(i, t) for t in range(-(-n * G // 64))]
-            # the tiles of a run's last tokens see the most keys: they go first, the short ones fill in
-            pairs.sort(key=lambda it: -(starts[it[0]] + (it[1] + 1) * 64 // G))
-            tile_lists[G] = pairs
+            for rows in PREFILL_TILE_ROWS:
+                pairs = []
+                for i, n in enumerate(q_lens):
+                    if n > 1 or G > 16:
+                        pairs += [(i, t) for t in range(-(-n * G // rows))]
+                # the tiles of a run's last tokens see the most keys: they go first, the short ones fill in
+                pairs.sort(key=lambda it: -(starts[it[0]] + (it[1] + 1) * rows // G))
+                tile_lists[(G, rows)] = pairs
         n_work = len(decode_list) + sum(2 * len(v) + 4 for v in tile_lists.values())
         total = (N * (2 + self.axes + len(groups)) + (S + 1) + 2 * S + M + S * sum(widths) + n_work
                  + 4 * (8 + 2 * len(groups)))
@@ -299,8 +302,8 @@ class ModelRunner:
         dec, dec_s = take(len(decode_list))
         dec[:] = decode_list
         tile_s = {}
-        for G, pairs in tile_lists.items():
-            view, tile_s[G] = take(2 * len(pairs))
+        for key, pairs in tile_lists.items():
+            view, tile_s[key] = take(2 * len(pairs))
             if pairs:
                 view[:] = np.asarray(pairs, dtype=np.int32).reshape(-1)
 
@@ -399,7 +402,8 @@ class ModelRunner:
             group_block_table=[d(s_, (S, w)) for s_, w in zip(g_tab_s, widths)],
             cache=self.cache,
             decode_items=d(dec_s) if decode_list else None,
-            prefill_tiles={G: (d(sp, (sp[1] // 2, 2)) if sp[1] else None) for G, sp in tile_s.items()},
+            prefill_tiles={G: (d(sp, (sp[1] // 2, 2)) if sp[1] else None) for (G, rows), sp in tile_s.items() if rows == 64},
+            prefill_tiles128={G: (d(sp, (sp[1] // 2, 2)) if sp[1] else None) for (G, rows), sp in tile_s.items() if rows == 128},
             host_q_lens=q_lens, host_q_start=starts,
             host_slots=[e.request.cache.slot for e in entries],
         )

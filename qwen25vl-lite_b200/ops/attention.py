@@ -20,6 +20,9 @@ import torch
 from . import kernels
 
 SM_COUNT = 148
+# which kernel attends runs of tokens at head size 128: "tcgen05" (scores and P.V on the 5th-generation
+# tensor cores) or "mma" (mma.sync, the kernel of every other head size)
+PREFILL_ATTENTION = __import__("os").environ.get("Q25VL_PREFILL_ATTENTION", "tcgen05")
 _scratch = {}
 
 
@@ -92,6 +95,12 @@ def paged_attention(ctx, qkv, kv, nq: int, nkv: int, head_dim: int, window, scal
                                  ctx.decode_items, nq, nkv, head_dim, kv.page_size, window, scale, splits, scratch)
     tiles = ctx.prefill_tiles[group]
     if tiles is not None:
-        kernels.attention_prefill(qkv, out, kv.k_pages, kv.v_pages, kv.block_table, ctx.cu_q, ctx.q_start_pos, tiles,
-                                  nq, nkv, head_dim, kv.page_size, window, scale)
+        tiles128 = getattr(ctx, "prefill_tiles128", {}).get(group)
+        if PREFILL_ATTENTION == "tcgen05" and tiles128 is not None and group <= 128 \
+                and kernels.attention_tcgen05_supports(qkv.dtype, head_dim, kv.page_size, qkv):
+            kernels.attention_prefill_tcgen05(qkv, out, kv.k_pages, kv.v_pages, kv.block_table, ctx.cu_q, ctx.q_start_pos,
+                                              tiles128, nq, nkv, head_dim, kv.page_size, window, scale)
+        else:
+            kernels.attention_prefill(qkv, out, kv.k_pages, kv.v_pages, kv.block_table, ctx.cu_q, ctx.q_start_pos, tiles,
+                                      nq, nkv, head_dim, kv.page_size, window, scale)
     return out

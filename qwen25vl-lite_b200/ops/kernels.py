@@ -305,6 +305,29 @@ def attention_prefill(qkv: torch.Tensor, out: torch.Tensor, k_pages: torch.Tenso
         head_dim, page_size, int(window or 0), float(scale), _stream()), "attention_prefill")
 
 
+def attention_tcgen05_supports(dtype: torch.dtype, head_dim: int, page_size: int, qkv: Optional[torch.Tensor] = None) -> bool:
+    """What the tcgen05 prefill attention takes: bfloat16, head size 128, a page size that is a power
+    of two, 16-byte aligned rows."""
+    if dtype != torch.bfloat16 or head_dim != 128 or page_size < 1 or page_size & (page_size - 1):
+        return False
+    return qkv is None or (qkv.data_ptr() % 16 == 0 and qkv.stride(0) % 8 == 0 and qkv.stride(1) == 1)
+
+
+def attention_prefill_tcgen05(qkv: torch.Tensor, out: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor,
+                              block_table: torch.Tensor, cu_q: torch.Tensor, q_start_pos: torch.Tensor,
+                              tiles: torch.Tensor, nq: int, nkv: int, head_dim: int, page_size: int, window: int,
+                              scale: float) -> None:
+    """``attention_prefill`` on the tcgen05 tensor cores (scores and P.V in tensor memory); ``tiles``
+    is int32 [n, 2]: (entry, row tile) with row tiles of 128 rows."""
+    if not attention_tcgen05_supports(qkv.dtype, head_dim, page_size, qkv):
+        raise KernelError(f"attention_prefill_tcgen05: unsupported head size {head_dim}, page size {page_size} or layout")
+    _check(_fn("q25_attention_prefill_tcgen05_bf16", [_P, _I, _P, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _P, _P])(
+        qkv.data_ptr(), qkv.stride(0), out.data_ptr(), k_pages.data_ptr(), v_pages.data_ptr(), block_table.data_ptr(),
+        block_table.shape[1], cu_q.data_ptr(), q_start_pos.data_ptr(), tiles.data_ptr(), tiles.shape[0], nq, nkv,
+        head_dim, page_size, int(window or 0), float(scale), error_flag(qkv.device).data_ptr(), _stream()),
+        "attention_prefill_tcgen05")
+
+
 def gemm_f32(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor) -> None:
     """out[M,N] = a[M,K] . w[N,K]^T + bias, plain float32 FMA."""
     m, k = a.shape

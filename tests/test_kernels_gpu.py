@@ -293,6 +293,29 @@ def test_attention_tensor_core_kernels(nq, nkv, d, page_size, window, splits):
     assert np.abs(f64(out) - ref).max() < 3e-2
 
 
+@pytest.mark.parametrize("nq,nkv,page_size,window", [(16, 2, 16, None), (8, 8, 4, None), (28, 4, 16, 150), (5, 1, 32, None), (40, 8, 8, 64)])
+def test_attention_prefill_tcgen05(nq, nkv, page_size, window):
+    """The tcgen05 prefill attention (scores and P.V in tensor memory, head size 128) against the
+    oracle: runs that start inside a cached prefix, runs shorter and longer than a 128-row tile,
+    groups of 8, 1, 7 and 5 query heads, small and large pages, windows that cut the keys."""
+    from qwen25vl_lite.ops import kernels
+    d = 128
+    rng = np.random.default_rng(21)
+    lens, q_lens = [300, 37, 130, 64, 517, 333, 9], [300, 37, 2, 17, 200, 70, 9]
+    c = paged_case(rng, lens, q_lens, nq, nkv, d, page_size, torch.bfloat16)
+    G = nq // nkv
+    tiles = [(i, t) for i, n in enumerate(q_lens) for t in range(-(-n * G // 128))]
+    out = torch.zeros((c["qkv"].shape[0], nq * d), dtype=torch.bfloat16, device="cuda")
+    assert kernels.attention_tcgen05_supports(torch.bfloat16, d, page_size, c["qkv"])
+    kernels.attention_prefill_tcgen05(c["qkv"], out, c["k_pages"], c["v_pages"], c["table"], c["cu"], c["start"],
+                                      dev(np.asarray(tiles, np.int32)), nq, nkv, d, page_size, window or 0, d ** -0.5)
+    torch.cuda.synchronize()
+    assert int(kernels.error_flag("cuda:0")[0]) == 0
+    ref = attention_oracle(c["dense"], window)
+    assert np.abs(f64(out) - ref).max() < 3e-2
+    assert not kernels.attention_tcgen05_supports(torch.bfloat16, 64, page_size)
+
+
 @pytest.mark.parametrize("q_len", [1, 5])
 def test_tensor_core_attention_finds_a_far_key_and_the_window_edge(q_len):
     """As for the general kernel: one dominant key on page edges, at both ends, and just inside /
