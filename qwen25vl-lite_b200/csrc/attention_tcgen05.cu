@@ -4,35 +4,40 @@
 // 156-175, src/qwen25vl_lite/attention.py:143-148): S = Q K^T * D^-1/2, a query at position a sees
 // keys j <= a (and j > a - window), softmax over the keys in float, O = P V.
 //
-// A CTA takes 128 rows = (token, query head of one kv group) pairs of one entry, so one pass over a
-// kv head's keys serves the whole group, and walks the keys in tiles of 64:
-//   * Q (once) and every K and V tile are written to shared memory in the 128-byte-swizzled layout
-//     that the tensor core reads: rows of 64 values (128 bytes), 8 rows per 1 KB atom, the 16-byte
-//     chunk c of row r at chunk c ^ (r % 8).  K and V come from their pages by 16-byte cp.async.
-//   * thread 0 issues tcgen05.mma: S[128 x 64] = Q . K^T (both operands K-major, 8 steps of 16 over
-//     the head size) into tensor memory; every thread owns one row (one lane of tensor memory),
-//     reads its 64 scores with tcgen05.ld, does the running softmax alone (no shuffles), and writes
-//     its row of P as bfloat16 into shared memory, again swizzled;
-//   * thread 0 issues O_tile[128 x 128] = P . V (P K-major; V is read as it lies, a row of 128
-//     head-size values per key: the MN-major operand form, 64-value halves 8 KB apart, groups of 8 keys
-//     1 KB apart) into a second accumulator; every thread adds its row of it, scaled by the
-//     softmax correction, to the output row it keeps in registers.
-// Two CTAs fit an SM (98 KB of shared memory, 256 of the 512 tensor-memory columns each), so one
-// CTA's softmax runs under the other's products.  K/V tiles are double-buffered; P is written where
-// the K tile was, which the tensor core has finished with once S is there.
+// A CTA takes RT row tiles (RT = 1 or 2) of 128 rows = (token, query head of one kv group) pairs of
+// one entry, so one pass over a kv head's keys serves the whole group (and with RT = 2 twice as many
+// tokens), and walks the keys in tiles of 64.  Its threads have two roles that meet only at
+// mbarriers:
+//   * the row threads, one per row (= one lane of tensor memory): they copy Q (once) and the K and V
+//     tiles from their pages into shared memory by 16-byte cp.async, in the 128-byte-swizzled layout
+//     the tensor core reads (rows of 64 values, 8 rows per 1 KB atom, chunk c of row r at c ^ (r % 8));
+//     they read their 64 scores of a tile with tcgen05.ld, do the running softmax alone (no
+//     shuffles), and write their row of P as bfloat16 pairs back into the tensor-memory columns the
+//     scores came from;
+//   * one thread of the warp after them issues tcgen05.mma: S[128 x 64] = Q . K^T per row tile (both
+//     operands K-major in shared memory, 8 steps of 16 over the head size) into one of two score
+//     buffers in tensor memory, and O[128 x 128] += P . V with P read from tensor memory and V read
+//     as it lies (a row of 128 head-size values per key: the MN-major operand form, 64-value halves
+//     8 KB apart, groups of 8 keys 1 KB apart).
+// The scores of tile t + 1 are computed while the rows work on tile t; a row asks for K(t + 2) and
+// V(t) when tile t begins and waits for them when its softmax of tile t is done, so in the steady
+// state it waits for no product and no copy.  The output accumulates in tensor memory over all
+// tiles; the exponentials use a lazy maximum (see below), so it is rescaled only rarely.
+// RT = 1: two CTAs to an SM (99 KB of shared memory, 256 of the 512 tensor-memory columns each);
+// RT = 2: one (131 KB, all 512 columns), half the key and value traffic per row.
 //
 // Every mbarrier wait is bounded; a wait that gives up records a code in *err, and the CTA runs to
-// its end (freeing its tensor memory) with invalid output.
+// its end (freeing its tensor memory) with invalid output.  A parity wait cannot tell "not yet" from
+// "two phases on", so every wait here is provably within one phase of its barrier.
 #include "attention_decode.cuh"
 
-#define A5_ROWS 128
+#define A5_ROWS 128                          // rows of a row tile; a CTA has RT of them
 #define A5_BN 64
 #define A5_D 128
-#define A5_THREADS 128
 #define A5_WAIT_LIMIT (1 << 22)
-#define A5_Q_BYTES (2 * A5_ROWS * 128)            // two 64-value halves of 128 rows
+#define A5_Q_BYTES (2 * A5_ROWS * 128)            // a row tile of Q: two 64-value halves of 128 rows
 #define A5_KV_BYTES (2 * A5_BN * 128)             // two halves of 64 keys
-#define A5_SMEM (A5_Q_BYTES + 4 * A5_KV_BYTES + 1024 + 1024)  // P (128 rows x 128 bytes) takes the place of the K tile it came from
+#define A5_SMEM(RT) ((RT) * A5_Q_BYTES + 4 * A5_KV_BYTES + 2048 + 1024)  // Q, two K and two V tiles, barriers and key rows, room to align
 
 __device__ __forceinline__ unsigned a5_s32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ void a5_mbar_init(unsigned long long* bar, int count) {
@@ -113,254 +118,364 @@ __device__ __forceinline__ float a5_ex2(float x) {
   return y;
 }
 
+// The larger of three (one instruction on sm_100).
+__device__ __forceinline__ float a5_max3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;\n" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
+
 // Byte offset of the 16-byte chunk c (0..7) of row r inside a swizzled block of 128-byte rows.
 __device__ __forceinline__ int a5_swz(int r, int c) { return (r >> 3) * 1024 + (r & 7) * 128 + ((c ^ (r & 7)) << 4); }
 
-// Keys [key0, key0 + 64) of one kv head into a swizzled K tile and V tile (zeros past last_key).
-__device__ __forceinline__ void a5_load_kv(unsigned char* ks, unsigned char* vs, const AttnArgs& a, const int* table, int kvh,
-                                           int key0, int last_key, int tid) {
-  const int ps_mask = (1 << a.page_shift) - 1;
+// The same 32 columns written from packed words, e.g. 64 bfloat16 probabilities of this thread's row.
+__device__ __forceinline__ void a5_st32u(unsigned taddr, const unsigned (&v)[32]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,"
+      "%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};\n"
+      ::"r"(taddr), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]), "r"(v[8]), "r"(v[9]),
+        "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15]), "r"(v[16]), "r"(v[17]), "r"(v[18]), "r"(v[19]),
+        "r"(v[20]), "r"(v[21]), "r"(v[22]), "r"(v[23]), "r"(v[24]), "r"(v[25]), "r"(v[26]), "r"(v[27]), "r"(v[28]), "r"(v[29]),
+        "r"(v[30]), "r"(v[31])
+      : "memory");
+  asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory");
+}
+__device__ __forceinline__ void a5_mbar_arrive(unsigned long long* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(a5_s32(bar)) : "memory");
+}
+// The product with the A operand in tensor memory: lane = row, 16 bfloat16 of a row in 8 columns.
+__device__ __forceinline__ void a5_mma_ts(unsigned tmem_d, unsigned tmem_a, unsigned long long bdesc, unsigned idesc,
+                                          unsigned accumulate) {
+  asm volatile(
+      "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n}\n"
+      ::"r"(tmem_d), "r"(tmem_a), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+
+// Where key kidx of a kv head lies: its row in the pages seen as [rows, D]; -1 past last_key.
+__device__ __forceinline__ int a5_key_row(const AttnArgs& a, const int* __restrict__ table, int kvh, int kidx, int last_key) {
+  if (kidx > last_key) return -1;
+  return (((__ldg(table + (kidx >> a.page_shift)) * a.nkv + kvh) << a.page_shift)) + (kidx & ((1 << a.page_shift) - 1));
+}
+
+// A tile of 64 keys from their pages into a swizzled tile (zeros for rows[key] < 0): 1,024 copies
+// of 16 bytes shared among the NROW row threads.  rows: the 64 keys' rows, in shared memory.
+template <int NROW>
+__device__ __forceinline__ void a5_load_tile(unsigned char* dst_tile, const bf16* __restrict__ pages, const int* rows, int tid) {
+  constexpr int N = A5_BN * 16 / NROW;
+  // all rows first: the copies are volatile statements, and a read between two of them would wait for its turn
+  int row[N];
 #pragma unroll
-  for (int i = 0; i < A5_BN * 16 / A5_THREADS; ++i) {
-    const int idx = tid + i * A5_THREADS;
+  for (int i = 0; i < N; ++i) row[i] = rows[(tid + i * NROW) >> 4];
+#pragma unroll
+  for (int i = 0; i < N; ++i) {
+    const int idx = tid + i * NROW;
     const int key = idx >> 4, cc = idx & 15;
-    const int kidx = key0 + key;
-    const bool valid = kidx <= last_key;
-    const int kc = valid ? kidx : last_key;             // a readable address also for the zero-filled rows
-    const int page = table[kc >> a.page_shift];
-    const size_t off = ((((size_t)page * a.nkv + kvh) << a.page_shift) + (kc & ps_mask)) * A5_D + cc * 8;
-    const int dst = (cc >> 3) * (A5_BN * 128) + a5_swz(key, cc & 7);
-    cp_async16(ks + dst, a.kpages + off, valid);
-    cp_async16(vs + dst, a.vpages + off, valid);
+    cp_async16(dst_tile + (cc >> 3) * (A5_BN * 128) + a5_swz(key, cc & 7), pages + (size_t)max(row[i], 0) * A5_D + cc * 8, row[i] >= 0);
   }
 }
 
-__global__ void __launch_bounds__(A5_THREADS, 2) attention_prefill_tcgen05_kernel(AttnArgs a, int* __restrict__ err) {
+struct A5Bars {
+  unsigned long long s_full[2];   // scores of a tile are in their buffer (one arrival: tcgen05.commit)
+  unsigned long long k_full[2];   // a K tile has landed (every row thread arrives for its copies)
+  unsigned long long pv_ready[2]; // P of a tile is in tensor memory and its V tile has landed (every row thread); two, since
+                                  // a row may be a tile ahead of another: the scores of the next tile are there early
+  unsigned long long pv_done[2];  // the product P V of a tile is done (tcgen05.commit); two, so that a wait is never
+                                  // two phases away from its barrier, where a parity wait would be wrong
+  unsigned tmem;
+};
+
+template <int RT>
+__global__ void __launch_bounds__(128 * RT + 32, 3 - RT) attention_prefill_tcgen05_kernel(AttnArgs a, int* __restrict__ err) {
+  constexpr int NROW = 128 * RT, ROWS = A5_ROWS * RT;   // one thread per row; the warp after them issues the products
+  constexpr int TMEM_COLS = 256 * RT, O_COL = 128 * RT; // per row tile two score buffers of 64 columns, then the outputs
   pdl_trigger();
   pdl_wait();
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   unsigned char* q_s = smem;
-  unsigned char* kv_s = q_s + A5_Q_BYTES;                 // stage s: K at kv_s + s * 2 * KV, V right after it
-  unsigned long long* s_bar = reinterpret_cast<unsigned long long*>(kv_s + 4 * A5_KV_BYTES);
-  unsigned long long* pv_bar = s_bar + 1;
-  unsigned* tmem_slot = reinterpret_cast<unsigned*>(pv_bar + 1);
+  unsigned char* k_s = q_s + RT * A5_Q_BYTES;             // two K tiles
+  unsigned char* v_s = k_s + 2 * A5_KV_BYTES;             // two V tiles
+  A5Bars* bars = reinterpret_cast<A5Bars*>(v_s + 2 * A5_KV_BYTES);
+  int* key_rows = reinterpret_cast<int*>(v_s + 2 * A5_KV_BYTES + 128);   // [4 tiles][64 keys]: see below
 
   const int tid = threadIdx.x, warp = tid >> 5;
   const int seq = a.items[2 * blockIdx.x], row_tile = a.items[2 * blockIdx.x + 1], kvh = blockIdx.y;
   const int G = a.nq / a.nkv;
   const int q0 = a.cu_q[seq], q_len = a.cu_q[seq + 1] - q0, start = a.q_start_pos[seq];
   const int n_rows = q_len * G;
-  const int R0 = row_tile * A5_ROWS;
+  const int R0 = row_tile * ROWS;
   const int* table = a.block_table + (size_t)seq * a.table_width;
-
-  if (tid == 0) {
-    a5_mbar_init(s_bar, 1);
-    a5_mbar_init(pv_bar, 1);
-    asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
-  }
-  if (warp == 0) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(a5_s32(tmem_slot)), "n"(256) : "memory");
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
-  }
-
-  // this thread's row
-  const int R = R0 + tid;
-  const bool live = R < n_rows;
-  const int tok = live ? R / G : 0, head = live ? R - tok * G : 0;
-  const int hi = live ? start + tok : -1;
-  const int lo = live ? (a.window > 0 ? max(0, hi - a.window + 1) : 0) : 0;
   // key range of the CTA
-  const int c_first = R0 / G, c_last = min(R0 + A5_ROWS - 1, n_rows - 1) / G;
+  const int c_first = R0 / G, c_last = min(R0 + ROWS - 1, n_rows - 1) / G;
   const int c_hi = start + c_last;
   const int c_lo = a.window > 0 ? max(0, start + c_first - a.window + 1) : 0;
   const int key_begin = c_lo & ~(A5_BN - 1);
   const int n_tiles = (c_hi - key_begin) / A5_BN + 1;
 
-  // first K/V tile on its way, then Q
-  a5_load_kv(kv_s, kv_s + A5_KV_BYTES, a, table, kvh, key_begin, c_hi, tid);
-  cp_async_commit();
-  {
+  if (tid == 0) {
+    a5_mbar_init(bars->s_full, 1);
+    a5_mbar_init(bars->s_full + 1, 1);
+    a5_mbar_init(bars->k_full, NROW);
+    a5_mbar_init(bars->k_full + 1, NROW);
+    a5_mbar_init(bars->pv_ready, NROW);
+    a5_mbar_init(bars->pv_ready + 1, NROW);
+    a5_mbar_init(bars->pv_done, 1);
+    a5_mbar_init(bars->pv_done + 1, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+  }
+  if (warp == NROW / 32) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(a5_s32(&bars->tmem)), "n"(TMEM_COLS) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
+  }
+
+  // this thread's row (threads of the last warp have none)
+  const int R = R0 + tid;
+  const bool live = tid < NROW && R < n_rows;
+  const int tok = live ? R / G : 0, head = live ? R - tok * G : 0;
+  const int hi = live ? start + tok : -1;
+  const int lo = live ? (a.window > 0 ? max(0, hi - a.window + 1) : 0) : 0;
+
+  // Where the keys lie.  The page lookup is a trip to the L2, so it runs three tiles ahead: the
+  // lanes of a warp that stand first look up the rows of the keys that their warp copies (key
+  // (tid + i * NROW) / 16 for copy i), when tile t begins for tile t + 3, and leave them in shared
+  // memory when it ends; the warp reads them a tile later for K and three tiles later for V.
+  // Writers and readers are lanes of one warp, so __syncwarp orders them.
+  constexpr int N_COPIES = A5_BN * 16 / NROW;
+  const int lane = tid & 31;
+  const int my_key = 2 * warp + (lane & 1) + (NROW / 16) * (lane >> 1);      // for lanes < 2 * N_COPIES
+  const bool looks_up = tid < NROW && lane < 2 * N_COPIES;
+  if (looks_up) {
+#pragma unroll
+    for (int j = 0; j < 3; ++j)
+      if (j < n_tiles) key_rows[j * A5_BN + my_key] = a5_key_row(a, table, kvh, key_begin + j * A5_BN + my_key, c_hi);
+  }
+  __syncwarp();
+  // The first two K tiles, the first V tile and Q.  After that a row asks for K(t + 2) and V(t) when
+  // tile t begins and waits for them when its part of tile t is done, a softmax later: at its fence
+  // nothing of its own is in flight.
+  if (tid < NROW) {
+    a5_load_tile<NROW>(k_s, a.kpages, key_rows, tid);
+    if (n_tiles > 1) a5_load_tile<NROW>(k_s + A5_KV_BYTES, a.kpages, key_rows + A5_BN, tid);
+    a5_load_tile<NROW>(v_s, a.vpages, key_rows, tid);
+    cp_async_commit();
     const uint4* src = reinterpret_cast<const uint4*>(a.qkv + (size_t)(q0 + tok) * a.qkv_stride + (size_t)(kvh * G + head) * A5_D);
 #pragma unroll
     for (int cc = 0; cc < 16; ++cc) {
       const uint4 v = live ? __ldcg(src + cc) : make_uint4(0, 0, 0, 0);
-      *reinterpret_cast<uint4*>(q_s + (cc >> 3) * (A5_ROWS * 128) + a5_swz(tid, cc & 7)) = v;
+      *reinterpret_cast<uint4*>(q_s + (tid >> 7) * A5_Q_BYTES + (cc >> 3) * (A5_ROWS * 128) + a5_swz(tid & 127, cc & 7)) = v;
     }
+    cp_async_wait<0>();
+    a5_proxy_fence();                                    // Q and this thread's part of K and V, visible to the tensor core
   }
-  a5_proxy_fence();
   a5_fence_before();
-  __syncthreads();
+  __syncthreads();                                       // barriers initialised, tensor memory allocated
   a5_fence_after();
-  const unsigned tmem_base = *tmem_slot;
-  const unsigned t_s = tmem_base + ((unsigned)(warp * 32) << 16);           // this warp's lanes: scores
-  const unsigned t_pv = t_s + 128;                                          // and the P V product
-
-  // Running softmax with a lazy maximum: the exponentials use m_used, which follows the true maximum
-  // only when that has grown by more than 8 (a factor 256, far inside the range of bfloat16 and of
-  // the float sums).  The output rows then accumulate in tensor memory over all tiles and are read,
-  // scaled and written back only on those rare occasions, not once per tile.
-  float m_used = -INFINITY, l = 0.f;
-  bool ok = true;
+  const unsigned tmem_base = bars->tmem;
   const unsigned idesc_s = a5_idesc(A5_BN, false), idesc_pv = a5_idesc(A5_D, true);
-  const int min_hi = start + c_first;                                       // the least any live row of the CTA sees
-  const int max_lo = a.window > 0 ? max(0, start + c_last - a.window + 1) : 0;
-  const bool all_live = R0 + A5_ROWS <= n_rows;
+  bool ok = true;
 
-  for (int tile = 0; tile < n_tiles; ++tile) {
-    const int stage = tile & 1;
-    unsigned char* k_s = kv_s + (size_t)stage * 2 * A5_KV_BYTES;
-    unsigned char* v_s = k_s + A5_KV_BYTES;
-    // the product P V of the tile before: done before its shared memory is loaded into again and
-    // before anybody rescales the output rows
-    if (tile > 0 && ok) {
-      ok = a5_mbar_wait(pv_bar, (unsigned)(tile - 1) & 1);
-      if (!ok && (tid & 31) == 0) atomicExch(err, 22);
-    }
-    a5_fence_after();
-    if (tile + 1 < n_tiles) {
-      unsigned char* nk = kv_s + (size_t)(stage ^ 1) * 2 * A5_KV_BYTES;
-      a5_load_kv(nk, nk + A5_KV_BYTES, a, table, kvh, key_begin + (tile + 1) * A5_BN, c_hi, tid);
-    }
-    cp_async_commit();
-    cp_async_wait<1>();
-    a5_proxy_fence();                                  // the copies of this thread, visible to the tensor core
-    a5_fence_before();
-    __syncthreads();
-    const int key0 = key_begin + tile * A5_BN;
-    if (tid == 0) {
-      a5_fence_after();
+  if (tid == NROW) {
+    // ---- the thread that issues the products ----
+    auto scores = [&](int t) {                            // S(t) = Q . K(t)^T into score buffer t % 2 of every row tile
+      const unsigned char* kt = k_s + (size_t)(t & 1) * A5_KV_BYTES;
 #pragma unroll
-      for (int ks = 0; ks < A5_D / 16; ++ks) {          // 16 values of the head size per step: 32 bytes along a row
-        const unsigned long long ad = a5_desc(a5_s32(q_s) + (ks >> 2) * (A5_ROWS * 128) + (ks & 3) * 32, 16, 1024);
-        const unsigned long long bd = a5_desc(a5_s32(k_s) + (ks >> 2) * (A5_BN * 128) + (ks & 3) * 32, 16, 1024);
-        a5_mma(tmem_base, ad, bd, idesc_s, ks != 0);
-      }
-      a5_commit(s_bar);
-    }
-    if (ok) {
-      ok = a5_mbar_wait(s_bar, (unsigned)tile & 1);
-      if (!ok && (tid & 31) == 0) atomicExch(err, 21);
-    }
-    a5_fence_after();
-
-    // this row's 64 scores
-    float s[A5_BN];
-    {
-      float part[32];
-      a5_ld32(t_s, part);
+      for (int rt = 0; rt < RT; ++rt) {
 #pragma unroll
-      for (int j = 0; j < 32; ++j) s[j] = part[j];
-      a5_ld32(t_s + 32, part);
-#pragma unroll
-      for (int j = 0; j < 32; ++j) s[32 + j] = part[j];
-    }
-    const bool need_mask = !all_live || key0 + A5_BN - 1 > min_hi || key0 < max_lo;      // the same for the whole CTA
-    if (need_mask) {
-#pragma unroll
-      for (int j = 0; j < A5_BN; ++j) {
-        const int kidx = key0 + j;
-        s[j] = (kidx >= lo && kidx <= hi) ? s[j] : -INFINITY;
-      }
-    }
-    float mx = s[0];
-#pragma unroll
-    for (int j = 1; j < A5_BN; ++j) mx = fmaxf(mx, s[j]);
-    mx *= a.scale_log2;                                  // the scale is positive: the maximum of the scaled scores
-    const bool grow = mx > m_used + 8.0f || (m_used == -INFINITY && mx != -INFINITY);
-    if (__any_sync(0xffffffffu, grow)) {
-      const float factor = grow ? (m_used == -INFINITY ? 0.f : a5_ex2(m_used - mx)) : 1.0f;
-      if (grow) m_used = mx;
-      l *= factor;
-      if (tile > 0) {                                    // the rows in tensor memory follow (warp-wide: lanes that keep theirs multiply by 1)
-#pragma unroll
-        for (int c = 0; c < A5_D / 32; ++c) {
-          float part[32];
-          a5_ld32(t_pv + c * 32, part);
-#pragma unroll
-          for (int j = 0; j < 32; ++j) part[j] *= factor;
-          a5_st32(t_pv + c * 32, part);
+        for (int ks = 0; ks < A5_D / 16; ++ks) {          // 16 values of the head size per step: 32 bytes along a row
+          const unsigned long long ad = a5_desc(a5_s32(q_s) + rt * A5_Q_BYTES + (ks >> 2) * (A5_ROWS * 128) + (ks & 3) * 32, 16, 1024);
+          const unsigned long long bd = a5_desc(a5_s32(kt) + (ks >> 2) * (A5_BN * 128) + (ks & 3) * 32, 16, 1024);
+          a5_mma(tmem_base + rt * 128 + (unsigned)(t & 1) * A5_BN, ad, bd, idesc_s, ks != 0);
         }
       }
+      a5_commit(bars->s_full + (t & 1));
+    };
+    auto fail = [&](int code) { ok = false; atomicExch(err, code); };
+    if (!a5_mbar_wait(bars->k_full, 0)) fail(21);
+    a5_fence_after();
+    scores(0);
+    if (n_tiles > 1) {
+      if (ok && !a5_mbar_wait(bars->k_full + 1, 0)) fail(21);
+      a5_fence_after();
+      scores(1);
     }
-    const float neg_m = m_used == -INFINITY ? 0.f : -m_used;
-    float sum = 0.f;
+    for (int t = 0; t < n_tiles; ++t) {
+      if (ok && !a5_mbar_wait(bars->pv_ready + (t & 1), (unsigned)(t >> 1) & 1)) fail(22);
+      a5_fence_after();
+      const unsigned char* vt = v_s + (size_t)(t & 1) * A5_KV_BYTES;
 #pragma unroll
-    for (int c = 0; c < 8; ++c) {
-      unsigned w[4];
+      for (int rt = 0; rt < RT; ++rt) {
 #pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const float p0 = a5_ex2(fmaf(s[c * 8 + 2 * e], a.scale_log2, neg_m));
-        const float p1 = a5_ex2(fmaf(s[c * 8 + 2 * e + 1], a.scale_log2, neg_m));
+        for (int ks = 0; ks < A5_BN / 16; ++ks) {         // 16 keys per step: 8 columns of P, 2 KB down V
+          const unsigned long long bd = a5_desc(a5_s32(vt) + ks * 2048, A5_BN * 128, 1024);
+          a5_mma_ts(tmem_base + O_COL + rt * 128, tmem_base + rt * 128 + (unsigned)(t & 1) * A5_BN + ks * 8, bd, idesc_pv,
+                    (t | ks) != 0);
+        }
+      }
+      a5_commit(bars->pv_done + (t & 1));
+      if (t + 2 < n_tiles) {
+        // the score buffer holds P(t) until this product is done; K(t + 2) was asked for a tile ago
+        if (ok && !a5_mbar_wait(bars->pv_done + (t & 1), (unsigned)(t >> 1) & 1)) fail(23);
+        if (ok && !a5_mbar_wait(bars->k_full + (t & 1), (unsigned)((t + 2) >> 1) & 1)) fail(21);
+        a5_fence_after();
+        scores(t + 2);
+      }
+    }
+  } else if (tid < NROW) {
+    // ---- the rows ----
+    a5_mbar_arrive(bars->k_full);                         // K(0) and K(1), after the fence above
+    if (n_tiles > 1) a5_mbar_arrive(bars->k_full + 1);
+    const unsigned t_lane = tmem_base + ((unsigned)((warp & 3) * 32) << 16) + (warp >> 2) * 128;   // this row tile's score buffers
+    const unsigned t_o = tmem_base + ((unsigned)((warp & 3) * 32) << 16) + O_COL + (warp >> 2) * 128;
+    // Running softmax with a lazy maximum: the exponentials use m_used, which follows the true maximum
+    // only when that has grown by more than 8 (a factor 256, far inside the range of bfloat16 and of
+    // the float sums), so the output rows in tensor memory are read, scaled and written back only
+    // on those rare occasions, not once per tile.
+    float m_used = -INFINITY, l = 0.f;
+    const int min_hi = start + c_first;                                       // the least any live row of the CTA sees
+    const int max_lo = a.window > 0 ? max(0, start + c_last - a.window + 1) : 0;
+    const bool all_live = R0 + ROWS <= n_rows;
+
+    for (int tile = 0; tile < n_tiles; ++tile) {
+      const int stage = tile & 1;
+      const int key0 = key_begin + tile * A5_BN;
+      if (ok && !a5_mbar_wait(bars->s_full + stage, (unsigned)(tile >> 1) & 1)) {
+        ok = false;
+        atomicExch(err, 24);
+      }
+      a5_fence_after();
+      // K(t + 2) goes where K(t) was, which the scores are done with; V(t) where V(t - 2) was, whose
+      // product was done before the scores of this tile were asked for
+      if (tile + 2 < n_tiles)
+        a5_load_tile<NROW>(k_s + (size_t)stage * A5_KV_BYTES, a.kpages, key_rows + ((tile + 2) & 3) * A5_BN, tid);
+      if (tile > 0) a5_load_tile<NROW>(v_s + (size_t)stage * A5_KV_BYTES, a.vpages, key_rows + (tile & 3) * A5_BN, tid);
+      cp_async_commit();
+      int row_ahead = -1;                                  // asked for now, stored when the tile ends
+      if (looks_up && tile + 3 < n_tiles) row_ahead = a5_key_row(a, table, kvh, key0 + 3 * A5_BN + my_key, c_hi);
+
+      // this row's 64 scores
+      float s[A5_BN];
+      {
+        float part[32];
+        a5_ld32(t_lane + stage * A5_BN, part);
+#pragma unroll
+        for (int j = 0; j < 32; ++j) s[j] = part[j];
+        a5_ld32(t_lane + stage * A5_BN + 32, part);
+#pragma unroll
+        for (int j = 0; j < 32; ++j) s[32 + j] = part[j];
+      }
+      const bool need_mask = !all_live || key0 + A5_BN - 1 > min_hi || key0 < max_lo;      // the same for the whole CTA
+      if (need_mask) {
+#pragma unroll
+        for (int j = 0; j < A5_BN; ++j) {
+          const int kidx = key0 + j;
+          s[j] = (kidx >= lo && kidx <= hi) ? s[j] : -INFINITY;
+        }
+      }
+      float mx0 = a5_max3(s[0], s[1], s[2]), mx1 = a5_max3(s[3], s[4], s[5]);   // two chains of three-input maxima
+#pragma unroll
+      for (int j = 6; j + 3 < A5_BN; j += 4) {
+        mx0 = a5_max3(mx0, s[j], s[j + 1]);
+        mx1 = a5_max3(mx1, s[j + 2], s[j + 3]);
+      }
+      float mx = a5_max3(mx0, mx1, fmaxf(s[A5_BN - 2], s[A5_BN - 1]));
+      mx *= a.scale_log2;                                  // the scale is positive: the maximum of the scaled scores
+      const bool grow = mx > m_used + 8.0f || (m_used == -INFINITY && mx != -INFINITY);
+      if (__any_sync(0xffffffffu, grow)) {
+        const float factor = grow ? (m_used == -INFINITY ? 0.f : a5_ex2(m_used - mx)) : 1.0f;
+        if (grow) m_used = mx;
+        l *= factor;
+        if (tile > 0) {                                    // the rows in tensor memory follow (warp-wide: lanes that keep theirs multiply by 1)
+          if (ok && !a5_mbar_wait(bars->pv_done + (stage ^ 1), (unsigned)((tile - 1) >> 1) & 1)) {   // nobody adds to them meanwhile
+            ok = false;
+            atomicExch(err, 25);
+          }
+          a5_fence_after();
+#pragma unroll
+          for (int c = 0; c < A5_D / 32; ++c) {
+            float part[32];
+            a5_ld32(t_o + c * 32, part);
+#pragma unroll
+            for (int j = 0; j < 32; ++j) part[j] *= factor;
+            a5_st32(t_o + c * 32, part);
+          }
+        }
+      }
+      const float neg_m = m_used == -INFINITY ? 0.f : -m_used;
+      float sum = 0.f;
+      unsigned w[A5_BN / 2];
+#pragma unroll
+      for (int e = 0; e < A5_BN / 2; ++e) {
+        const float p0 = a5_ex2(fmaf(s[2 * e], a.scale_log2, neg_m));
+        const float p1 = a5_ex2(fmaf(s[2 * e + 1], a.scale_log2, neg_m));
         sum += p0 + p1;
         w[e] = pack_bf16(p0, p1);
       }
-      *reinterpret_cast<uint4*>(k_s + a5_swz(tid, c)) = make_uint4(w[0], w[1], w[2], w[3]);   // P where K was: S is done with it
+      l += sum;
+      a5_st32u(t_lane + stage * A5_BN, w);                 // P where the scores were: 64 bfloat16 in 32 columns
+      if (looks_up && tile + 3 < n_tiles) key_rows[((tile + 3) & 3) * A5_BN + my_key] = row_ahead;
+      __syncwarp();
+      // the copies asked for when the tile began have had a softmax's time to land
+      cp_async_wait<0>();
+      a5_proxy_fence();
+      a5_fence_before();
+      if (tile + 2 < n_tiles) a5_mbar_arrive(bars->k_full + stage);
+      a5_mbar_arrive(bars->pv_ready + stage);
     }
-    l += sum;
-    a5_proxy_fence();
-    a5_fence_before();
-    __syncthreads();
-    if (tid == 0) {
-      a5_fence_after();
-#pragma unroll
-      for (int ks = 0; ks < A5_BN / 16; ++ks) {          // 16 keys per step: 32 bytes along a row of P, 2 KB down V
-        const unsigned long long ad = a5_desc(a5_s32(k_s) + ks * 32, 16, 1024);
-        const unsigned long long bd = a5_desc(a5_s32(v_s) + ks * 2048, A5_BN * 128, 1024);
-        a5_mma(tmem_base + 128, ad, bd, idesc_pv, (tile | ks) != 0);
-      }
-      a5_commit(pv_bar);
+    if (ok && !a5_mbar_wait(bars->pv_done + ((n_tiles - 1) & 1), (unsigned)((n_tiles - 1) >> 1) & 1)) {
+      ok = false;
+      atomicExch(err, 27);
     }
-  }
-  cp_async_wait<0>();
-  if (ok) {
-    ok = a5_mbar_wait(pv_bar, (unsigned)(n_tiles - 1) & 1);
-    if (!ok && (tid & 31) == 0) atomicExch(err, 23);
-  }
-  a5_fence_after();
+    a5_fence_after();
 
-  {
     const float inv = live && l > 0.f ? 1.0f / l : 0.f;
     bf16* dst = a.out + (size_t)(q0 + tok) * a.nq * A5_D + (size_t)(kvh * G + head) * A5_D;
 #pragma unroll
     for (int c = 0; c < A5_D / 32; ++c) {                 // tcgen05.ld is warp-wide: dead rows read too, and store nothing
       float part[32];
-      a5_ld32(t_pv + c * 32, part);
+      a5_ld32(t_o + c * 32, part);
       if (!live) continue;
 #pragma unroll
       for (int q = 0; q < 4; ++q) {
-        uint4 w;
-        w.x = pack_bf16(part[q * 8] * inv, part[q * 8 + 1] * inv);
-        w.y = pack_bf16(part[q * 8 + 2] * inv, part[q * 8 + 3] * inv);
-        w.z = pack_bf16(part[q * 8 + 4] * inv, part[q * 8 + 5] * inv);
-        w.w = pack_bf16(part[q * 8 + 6] * inv, part[q * 8 + 7] * inv);
-        *reinterpret_cast<uint4*>(dst + c * 32 + q * 8) = w;
+        uint4 o;
+        o.x = pack_bf16(part[q * 8] * inv, part[q * 8 + 1] * inv);
+        o.y = pack_bf16(part[q * 8 + 2] * inv, part[q * 8 + 3] * inv);
+        o.z = pack_bf16(part[q * 8 + 4] * inv, part[q * 8 + 5] * inv);
+        o.w = pack_bf16(part[q * 8 + 6] * inv, part[q * 8 + 7] * inv);
+        *reinterpret_cast<uint4*>(dst + c * 32 + q * 8) = o;
       }
     }
   }
   // every thread gets here (all waits are bounded); then the tensor memory goes back
   a5_fence_before();
   __syncthreads();
-  if (warp == 0) {
+  if (warp == NROW / 32) {
     a5_fence_after();
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "n"(256) : "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "n"(TMEM_COLS) : "memory");
   }
 }
 
-// items: (entry, 128-row tile) pairs; otherwise the arguments of q25_attention_prefill_bf16.  Head size
-// 128 only.  err: one int that receives a nonzero code if a wait gave up.
+template <int RT>
+static int launch_a5(const AttnArgs& a, int n_tiles, int nkv, int* err, cudaStream_t stream) {
+  cudaError_t ce = cudaFuncSetAttribute(attention_prefill_tcgen05_kernel<RT>, cudaFuncAttributeMaxDynamicSharedMemorySize, A5_SMEM(RT));
+  if (ce != cudaSuccess) return (int)ce;
+  launch(attention_prefill_tcgen05_kernel<RT>, dim3(n_tiles, nkv), dim3(128 * RT + 32), (size_t)A5_SMEM(RT), stream, a, err);
+  return launch_status();
+}
+
+// items: (entry, row tile) pairs with row tiles of tile_rows = 128 or 256 rows (one or two row tiles
+// to a CTA; two halve the traffic of keys and values from the L2); otherwise the arguments of
+// q25_attention_prefill_bf16.  Head size 128 only.  err: one int that receives a nonzero code if a
+// wait gave up.
 Q25_EXPORT int q25_attention_prefill_tcgen05_bf16(const void* qkv, int qkv_stride, void* out, const void* kp, const void* vp,
                                                   const int* bt, int tw, const int* cu_q, const int* q_start,
-                                                  const int* tiles, int n_tiles, int nq, int nkv, int d, int page_size,
-                                                  int window, float scale, int* err, void* stream) {
+                                                  const int* tiles, int n_tiles, int tile_rows, int nq, int nkv, int d,
+                                                  int page_size, int window, float scale, int* err, void* stream) {
   if (n_tiles <= 0) return 0;
-  if (d != A5_D || !err) return (int)cudaErrorInvalidValue;
+  if (d != A5_D || !err || (tile_rows != 128 && tile_rows != 256)) return (int)cudaErrorInvalidValue;
   AttnArgs a;
   int e = fill_args(a, qkv, qkv_stride, out, kp, vp, bt, tw, cu_q, q_start, tiles, nq, nkv, page_size, window, scale);
   if (e) return e;
   if (((uintptr_t)qkv & 15) || (qkv_stride % 8) || ((uintptr_t)out & 15)) return (int)cudaErrorInvalidValue;
-  cudaError_t ce = cudaFuncSetAttribute(attention_prefill_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, A5_SMEM);
-  if (ce != cudaSuccess) return (int)ce;
-  launch(attention_prefill_tcgen05_kernel, dim3(n_tiles, nkv), dim3(A5_THREADS), (size_t)A5_SMEM, (cudaStream_t)stream, a, err);
-  return launch_status();
+  return tile_rows == 128 ? launch_a5<1>(a, n_tiles, nkv, err, (cudaStream_t)stream)
+                          : launch_a5<2>(a, n_tiles, nkv, err, (cudaStream_t)stream);
 }

@@ -109,9 +109,9 @@ def test_rope_store(dtype, nq, nkv, d, section):
     assert float(k2.abs().max()) == 0 and torch.equal(qkv, qkv0)
 
 
-def paged_case(rng, lens, q_lens, nq, nkv, d, page_size, dtype, n_pages=None):
+def paged_case(rng, lens, q_lens, nq, nkv, d, page_size, dtype, n_pages=None, key_gain=None):
     """Random requests laid out in shuffled pages.  Returns tensors for the kernel and the
-    dense per-request q, k, v for the oracle."""
+    dense per-request q, k, v for the oracle.  key_gain(L) gives a factor for the key at each position."""
     total_pages = sum(-(-L // page_size) for L in lens)
     n_pages = n_pages or total_pages + 3
     order = rng.permutation(n_pages)
@@ -122,16 +122,20 @@ def paged_case(rng, lens, q_lens, nq, nkv, d, page_size, dtype, n_pages=None):
     dense, qs, token_seq, cu, start = [], [], [], [0], []
     at = 0
     for s, (L, ql) in enumerate(zip(lens, q_lens)):
-        k = torch.as_tensor(rng.standard_normal((L, nkv, d))).to(dtype)
+        k = rng.standard_normal((L, nkv, d))
+        if key_gain is not None:
+            k = k * np.asarray(key_gain(L))[:, None, None]
+        k = torch.as_tensor(k).to(dtype)
         v = torch.as_tensor(rng.standard_normal((L, nkv, d))).to(dtype)
         q = torch.as_tensor(rng.standard_normal((ql, nq, d))).to(dtype)
         npg = -(-L // page_size)
         table[s, :npg] = order[at:at + npg]
         at += npg
-        for j in range(L):
-            pg = table[s, j // page_size]
-            k_pages[pg, :, j % page_size] = k[j].cuda()
-            v_pages[pg, :, j % page_size] = v[j].cuda()
+        pad = npg * page_size - L
+        pages_of = torch.as_tensor(table[s, :npg].astype(np.int64), device="cuda")
+        for src, dst in ((k, k_pages), (v, v_pages)):
+            whole = torch.cat([src, torch.zeros((pad, nkv, d), dtype=dtype)]).cuda()
+            dst[pages_of] = whole.view(npg, page_size, nkv, d).permute(0, 2, 1, 3)
         dense.append((q, k, v))
         qs.append(q)
         token_seq += [s] * ql
@@ -293,27 +297,62 @@ def test_attention_tensor_core_kernels(nq, nkv, d, page_size, window, splits):
     assert np.abs(f64(out) - ref).max() < 3e-2
 
 
+@pytest.mark.parametrize("tile_rows", [128, 256])
 @pytest.mark.parametrize("nq,nkv,page_size,window", [(16, 2, 16, None), (8, 8, 4, None), (28, 4, 16, 150), (5, 1, 32, None), (40, 8, 8, 64)])
-def test_attention_prefill_tcgen05(nq, nkv, page_size, window):
-    """The tcgen05 prefill attention (scores and P.V in tensor memory, head size 128) against the
-    oracle: runs that start inside a cached prefix, runs shorter and longer than a 128-row tile,
-    groups of 8, 1, 7 and 5 query heads, small and large pages, windows that cut the keys."""
+def test_attention_prefill_tcgen05(nq, nkv, page_size, window, tile_rows):
+    """The tcgen05 prefill attention (scores, P and outputs in tensor memory, head size 128) against
+    the oracle: runs that start inside a cached prefix, runs shorter and longer than a row tile,
+    groups of 8, 1, 7 and 5 query heads, small and large pages, windows that cut the keys; one and
+    two row tiles to a CTA."""
     from qwen25vl_lite.ops import kernels
     d = 128
     rng = np.random.default_rng(21)
     lens, q_lens = [300, 37, 130, 64, 517, 333, 9], [300, 37, 2, 17, 200, 70, 9]
     c = paged_case(rng, lens, q_lens, nq, nkv, d, page_size, torch.bfloat16)
     G = nq // nkv
-    tiles = [(i, t) for i, n in enumerate(q_lens) for t in range(-(-n * G // 128))]
+    tiles = [(i, t) for i, n in enumerate(q_lens) for t in range(-(-n * G // tile_rows))]
     out = torch.zeros((c["qkv"].shape[0], nq * d), dtype=torch.bfloat16, device="cuda")
     assert kernels.attention_tcgen05_supports(torch.bfloat16, d, page_size, c["qkv"])
     kernels.attention_prefill_tcgen05(c["qkv"], out, c["k_pages"], c["v_pages"], c["table"], c["cu"], c["start"],
-                                      dev(np.asarray(tiles, np.int32)), nq, nkv, d, page_size, window or 0, d ** -0.5)
+                                      dev(np.asarray(tiles, np.int32)), nq, nkv, d, page_size, window or 0, d ** -0.5,
+                                      tile_rows=tile_rows)
     torch.cuda.synchronize()
     assert int(kernels.error_flag("cuda:0")[0]) == 0
     ref = attention_oracle(c["dense"], window)
     assert np.abs(f64(out) - ref).max() < 3e-2
     assert not kernels.attention_tcgen05_supports(torch.bfloat16, 64, page_size)
+
+
+@pytest.mark.parametrize("tile_rows", [128, 256])
+def test_attention_prefill_tcgen05_long_runs_repeat_exactly(tile_rows):
+    """Many key tiles per CTA, more CTAs than the GPU holds at once, and scores that keep growing
+    along the keys, so that the rows in tensor memory are rescaled again and again: against the
+    oracle, and eight launches give the same bits (the rows of a CTA, the thread that issues the
+    products and the copies meet only at barriers; a missed one shows as a difference between runs)."""
+    from qwen25vl_lite.ops import kernels
+    nq, nkv, d, page_size = 16, 2, 128, 16
+    rng = np.random.default_rng(22)
+    lens, q_lens = [1500, 1100, 300], [1000, 1100, 90]
+    # keys grow with their position in every run: the running maximum of a row moves by far more
+    # than the lazy threshold over its keys
+    c = paged_case(rng, lens, q_lens, nq, nkv, d, page_size, torch.bfloat16, key_gain=lambda L: 1.0 + 5.0 * np.arange(L) / L)
+    dense = c["dense"]
+    G = nq // nkv
+    tiles = [(i, t) for i, n in enumerate(q_lens) for t in range(-(-n * G // tile_rows))]
+    tiles.sort(key=lambda it: -(lens[it[0]] - q_lens[it[0]] + (it[1] + 1) * tile_rows // G))
+    items = dev(np.asarray(tiles, np.int32))
+    outs = []
+    for _ in range(8):
+        out = torch.full((c["qkv"].shape[0], nq * d), 3.0, dtype=torch.bfloat16, device="cuda")
+        kernels.attention_prefill_tcgen05(c["qkv"], out, c["k_pages"], c["v_pages"], c["table"], c["cu"], c["start"],
+                                          items, nq, nkv, d, page_size, 0, d ** -0.5, tile_rows=tile_rows)
+        outs.append(out)
+    torch.cuda.synchronize()
+    assert int(kernels.error_flag("cuda:0")[0]) == 0
+    for o in outs[1:]:
+        assert torch.equal(o, outs[0])
+    ref = attention_oracle(dense, None)
+    assert np.abs(f64(outs[0]) - ref).max() < 3e-2
 
 
 @pytest.mark.parametrize("q_len", [1, 5])
