@@ -157,6 +157,29 @@ __device__ __forceinline__ int a5_key_row(const AttnArgs& a, const int* __restri
   return (((__ldg(table + (kidx >> a.page_shift)) * a.nkv + kvh) << a.page_shift)) + (kidx & ((1 << a.page_shift) - 1));
 }
 
+// The same for pages of 16 tokens or more, where a block of 16 keys of a tile is 4 KB in one piece:
+// warp w of a row tile copies block w, every lane 8 (with two row tiles 4) pieces of 16 bytes at
+// block + (lane + 32 j) * 16, so a copy's addresses are one base and constants (copies whose
+// addresses each take a 64-bit multiply-add cost the warp three times as long to issue).
+// block_row: the row of the block's first key in the pages seen as [rows, D]; n_valid: how many of
+// its 16 keys exist (the others are filled with zeros).
+template <int NROW>
+__device__ __forceinline__ void a5_load_block(unsigned char* dst_tile, const bf16* __restrict__ pages, int block_row, int n_valid,
+                                              int warp, int lane) {
+  constexpr int PER = 8 * 128 / NROW;                  // copies per lane
+  const int blk = warp & 3, j0 = (warp >> 2) * PER;
+  const int h = lane >> 4, cc = lane & 15;
+  const unsigned char* src = reinterpret_cast<const unsigned char*>(pages + (size_t)block_row * A5_D) + lane * 16;
+  unsigned char* dst = dst_tile + (cc >> 3) * (A5_BN * 128) + blk * 2048 + h * 128;
+  const int x = ((cc & 7) ^ h) << 4;
+#pragma unroll
+  for (int jj = 0; jj < PER; ++jj) {
+    const int j = j0 + jj;                             // key of the block: h + 2 j; its row in the tile: 16 blk + h + 2 j
+    const int r7 = (2 * jj) & 7;                       // (row % 8) without h (PER is 4 or 8: 2 j0 is a multiple of 8)
+    cp_async16(dst + (j >> 2) * 1024 + r7 * 128 + (x ^ (r7 << 4)), src + j * 512, h + 2 * j < n_valid);
+  }
+}
+
 // A tile of 64 keys from their pages into a swizzled tile (zeros for rows[key] < 0): 1,024 copies
 // of 16 bytes shared among the NROW row threads.  rows: the 64 keys' rows, in shared memory.
 template <int NROW>
@@ -240,10 +263,26 @@ __global__ void __launch_bounds__(128 * RT + 32, 3 - RT) attention_prefill_tcgen
   // (tid + i * NROW) / 16 for copy i), when tile t begins for tile t + 3, and leave them in shared
   // memory when it ends; the warp reads them a tile later for K and three tiles later for V.
   // Writers and readers are lanes of one warp, so __syncwarp orders them.
+  // With pages of 16 tokens or more a warp needs one row per tile, that of its block of 16 keys:
+  // every lane keeps those of the tiles t, t + 1 and t + 2 in registers and asks for the page of t + 3.
   constexpr int N_COPIES = A5_BN * 16 / NROW;
   const int lane = tid & 31;
+  const bool blocks = a.page_shift >= 4;
+  const int block_key = key_begin + 16 * (warp & 3);                          // first key of this warp's block in tile 0
+  auto block_row = [&](int page, int kfirst) { return ((page * a.nkv + kvh) << a.page_shift) + (kfirst & ((1 << a.page_shift) - 1)); };
+  auto block_valid = [&](int kfirst) { return min(max(c_hi - kfirst + 1, 0), 16); };
+  int rb0 = 0, rb1 = 0, rb2 = 0;
+  if (blocks && tid < NROW) {
+    const int k0 = block_key, k1 = block_key + A5_BN, k2 = block_key + 2 * A5_BN;
+    const int p0 = k0 <= c_hi ? __ldg(table + (k0 >> a.page_shift)) : 0;
+    const int p1 = k1 <= c_hi ? __ldg(table + (k1 >> a.page_shift)) : 0;
+    const int p2 = k2 <= c_hi ? __ldg(table + (k2 >> a.page_shift)) : 0;
+    rb0 = k0 <= c_hi ? block_row(p0, k0) : 0;
+    rb1 = k1 <= c_hi ? block_row(p1, k1) : 0;
+    rb2 = k2 <= c_hi ? block_row(p2, k2) : 0;
+  }
   const int my_key = 2 * warp + (lane & 1) + (NROW / 16) * (lane >> 1);      // for lanes < 2 * N_COPIES
-  const bool looks_up = tid < NROW && lane < 2 * N_COPIES;
+  const bool looks_up = !blocks && tid < NROW && lane < 2 * N_COPIES;
   if (looks_up) {
 #pragma unroll
     for (int j = 0; j < 3; ++j)
@@ -254,9 +293,15 @@ __global__ void __launch_bounds__(128 * RT + 32, 3 - RT) attention_prefill_tcgen
   // tile t begins and waits for them when its part of tile t is done, a softmax later: at its fence
   // nothing of its own is in flight.
   if (tid < NROW) {
-    a5_load_tile<NROW>(k_s, a.kpages, key_rows, tid);
-    if (n_tiles > 1) a5_load_tile<NROW>(k_s + A5_KV_BYTES, a.kpages, key_rows + A5_BN, tid);
-    a5_load_tile<NROW>(v_s, a.vpages, key_rows, tid);
+    if (blocks) {
+      a5_load_block<NROW>(k_s, a.kpages, rb0, block_valid(block_key), warp, lane);
+      if (n_tiles > 1) a5_load_block<NROW>(k_s + A5_KV_BYTES, a.kpages, rb1, block_valid(block_key + A5_BN), warp, lane);
+      a5_load_block<NROW>(v_s, a.vpages, rb0, block_valid(block_key), warp, lane);
+    } else {
+      a5_load_tile<NROW>(k_s, a.kpages, key_rows, tid);
+      if (n_tiles > 1) a5_load_tile<NROW>(k_s + A5_KV_BYTES, a.kpages, key_rows + A5_BN, tid);
+      a5_load_tile<NROW>(v_s, a.vpages, key_rows, tid);
+    }
     cp_async_commit();
     const uint4* src = reinterpret_cast<const uint4*>(a.qkv + (size_t)(q0 + tok) * a.qkv_stride + (size_t)(kvh * G + head) * A5_D);
 #pragma unroll
@@ -345,12 +390,21 @@ __global__ void __launch_bounds__(128 * RT + 32, 3 - RT) attention_prefill_tcgen
       a5_fence_after();
       // K(t + 2) goes where K(t) was, which the scores are done with; V(t) where V(t - 2) was, whose
       // product was done before the scores of this tile were asked for
-      if (tile + 2 < n_tiles)
-        a5_load_tile<NROW>(k_s + (size_t)stage * A5_KV_BYTES, a.kpages, key_rows + ((tile + 2) & 3) * A5_BN, tid);
-      if (tile > 0) a5_load_tile<NROW>(v_s + (size_t)stage * A5_KV_BYTES, a.vpages, key_rows + (tile & 3) * A5_BN, tid);
-      cp_async_commit();
-      int row_ahead = -1;                                  // asked for now, stored when the tile ends
-      if (looks_up && tile + 3 < n_tiles) row_ahead = a5_key_row(a, table, kvh, key0 + 3 * A5_BN + my_key, c_hi);
+      const int kb = block_key + tile * A5_BN;             // this warp's block in this tile
+      int row_ahead = -1, page_ahead = 0;                  // asked for now, used when the tile ends
+      if (blocks) {
+        if (tile + 2 < n_tiles)
+          a5_load_block<NROW>(k_s + (size_t)stage * A5_KV_BYTES, a.kpages, rb2, block_valid(kb + 2 * A5_BN), warp, lane);
+        if (tile > 0) a5_load_block<NROW>(v_s + (size_t)stage * A5_KV_BYTES, a.vpages, rb0, block_valid(kb), warp, lane);
+        cp_async_commit();
+        if (kb + 3 * A5_BN <= c_hi) page_ahead = __ldg(table + ((kb + 3 * A5_BN) >> a.page_shift));
+      } else {
+        if (tile + 2 < n_tiles)
+          a5_load_tile<NROW>(k_s + (size_t)stage * A5_KV_BYTES, a.kpages, key_rows + ((tile + 2) & 3) * A5_BN, tid);
+        if (tile > 0) a5_load_tile<NROW>(v_s + (size_t)stage * A5_KV_BYTES, a.vpages, key_rows + (tile & 3) * A5_BN, tid);
+        cp_async_commit();
+        if (looks_up && tile + 3 < n_tiles) row_ahead = a5_key_row(a, table, kvh, key0 + 3 * A5_BN + my_key, c_hi);
+      }
 
       // this row's 64 scores
       float s[A5_BN];
@@ -412,8 +466,14 @@ __global__ void __launch_bounds__(128 * RT + 32, 3 - RT) attention_prefill_tcgen
       }
       l += sum;
       a5_st32u(t_lane + stage * A5_BN, w);                 // P where the scores were: 64 bfloat16 in 32 columns
-      if (looks_up && tile + 3 < n_tiles) key_rows[((tile + 3) & 3) * A5_BN + my_key] = row_ahead;
-      __syncwarp();
+      if (blocks) {
+        rb0 = rb1;
+        rb1 = rb2;
+        rb2 = kb + 3 * A5_BN <= c_hi ? block_row(page_ahead, kb + 3 * A5_BN) : 0;
+      } else {
+        if (looks_up && tile + 3 < n_tiles) key_rows[((tile + 3) & 3) * A5_BN + my_key] = row_ahead;
+        __syncwarp();
+      }
       // the copies asked for when the tile began have had a softmax's time to land
       cp_async_wait<0>();
       a5_proxy_fence();
