@@ -295,6 +295,11 @@ def run_ours(args):
             engine.abort(s.seq_id)
         return batch * steps / dt
 
+    if args.only_batch:             # for profiler runs at another batch size: that decode loop alone, a short line
+        tok_s, ms, launches, ctx = decode_device(args.only_batch, args.steps, args.warmup)
+        print(json.dumps({"decode_batch": args.only_batch, "tokens_per_s": tok_s, "ms_per_step": ms, "layers": layers,
+                          "context": ctx, "gpu_launches": launches}))
+        return 0
     clocks = ClockSampler()
     clocks.start()
     value, ms_per_step, launches, ctx = decode_device(8, args.steps, args.warmup)
@@ -342,6 +347,7 @@ def main(argv=None):
     ap.add_argument("--layers", type=int, default=None, help="fewer layers than the model has (named in config)")
     ap.add_argument("--headline-only", action="store_true", help="skip e2e and the batch 1 / 64 points")
     ap.add_argument("--no-cuda-graph", action="store_true", help="launch decode steps kernel by kernel (for profilers)")
+    ap.add_argument("--only-batch", type=int, default=0, help="time decode steps at this batch size only (for profilers)")
     args = ap.parse_args(argv)
     if args.gpus != 1:
         print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not measured")

@@ -33,6 +33,9 @@ __device__ __forceinline__ void cp_async16(void* dst, const void* src, bool vali
   const int n = valid ? 16 : 0;  // src-size 0: the 16 bytes are filled with zeros
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(smem_u32(dst)), "l"(src), "r"(n));
 }
+__device__ __forceinline__ void cp_async16_whole(void* dst, const void* src) {     // without the size operand
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(smem_u32(dst)), "l"(src));
+}
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
 template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
 
@@ -79,14 +82,49 @@ __device__ __forceinline__ void load_q(unsigned (&qf)[D / 16][4], RowPtr row_ptr
 }
 
 // Copies keys [key0, key0 + BN) of one kv head into a tile (zeros past last_key), by NT threads of
-// which this is number `tid`.  The loop is unrolled and free of branches, so the block-table
-// look-ups of all its iterations are in flight together instead of one after the other.
+// which this is number `tid`.  key0 is a multiple of BN.
+//
+// With pages of 16 tokens or more, a block of 16 keys lies in one page in one piece of 16 rows: a
+// thread's copies of a block then read block + (tid + i * NT) * 16, one 64-bit base and constants.
+// (Copies whose source addresses each need a look-up and a 64-bit multiply-add take a warp about
+// three times as long to issue, which is most of what a copy costs the warp.)  Smaller pages, or a
+// block whose chunks do not divide among the threads, take the general loop; it is unrolled and
+// free of branches, so the block-table look-ups of all its iterations are in flight together.
 template <int D, int BN, int NT>
 __device__ __forceinline__ void load_kv_tile(unsigned char* ks, unsigned char* vs, const AttnArgs& a, const int* table,
                                              int kvh, int key0, int last_key, int tid) {
   constexpr int CH = D / 8;  // 16-byte chunks in a row
   static_assert((BN * CH) % NT == 0, "the chunks of a tile divide evenly among the threads");
   const int ps_mask = (1 << a.page_shift) - 1;
+  if constexpr (BN % 16 == 0 && (16 * CH) % NT == 0) {
+    if (a.page_shift >= 4) {
+      constexpr int NB = BN / 16, PER = 16 * CH / NT;
+      const unsigned char* kb[NB];
+      const unsigned char* vb[NB];
+#pragma unroll
+      for (int b = 0; b < NB; ++b) {
+        const int kf = key0 + 16 * b;                      // a multiple of 16: the block does not straddle pages
+        const bool any = kf <= last_key;
+        const int page = table[(any ? kf : last_key) >> a.page_shift];
+        const size_t off = (((((size_t)page * a.nkv + kvh) << a.page_shift) + (any ? (kf & ps_mask) : 0)) * D + (size_t)tid * 8) * sizeof(bf16);
+        kb[b] = reinterpret_cast<const unsigned char*>(a.kpages) + off;
+        vb[b] = reinterpret_cast<const unsigned char*>(a.vpages) + off;
+      }
+#pragma unroll
+      for (int b = 0; b < NB; ++b) {
+#pragma unroll
+        for (int i = 0; i < PER; ++i) {
+          const int c = tid + i * NT;
+          const int key = c / CH, ch = c - key * CH;
+          const bool valid = key0 + 16 * b + key <= last_key;
+          const int dst = (16 * b + key) * Tile<D>::PITCH + ch * 16;
+          cp_async16(ks + dst, kb[b] + i * NT * 16, valid);
+          cp_async16(vs + dst, vb[b] + i * NT * 16, valid);
+        }
+      }
+      return;
+    }
+  }
 #pragma unroll
   for (int i = 0; i < BN * CH / NT; ++i) {
     const int idx = tid + i * NT;
@@ -100,6 +138,45 @@ __device__ __forceinline__ void load_kv_tile(unsigned char* ks, unsigned char* v
     cp_async16(vs + key * Tile<D>::PITCH + ch * 16, a.vpages + off, valid);
   }
 }
+
+// The copies of a block of 16 keys that starts at key kf (a multiple of 16) and lies in `page` (pages
+// of 16 tokens or more), by the 32 lanes of a warp: D / 16 pairs (one piece of K, one of V) per lane.
+// The caller has looked the page up, ahead of time if it can.  (The load/store unit of an SM takes one
+// such copy of 32 x 16 bytes about every 4 cycles: with 8 warps copying, 16 pairs cost each of them
+// about 700 cycles, whether issued in one go or spread over the tile's arithmetic.)
+template <int D>
+struct BlockCopy {
+  static constexpr int CH = D / 8, PAIRS = 16 * CH / 32;
+  unsigned char *ks, *vs;
+  const unsigned char *kb, *vb;
+  int n_valid, lane;
+
+  __device__ __forceinline__ void set(unsigned char* ks_, unsigned char* vs_, const AttnArgs& a, int page, int kvh, int kf, int last_key,
+                                      int lane_) {
+    ks = ks_; vs = vs_; lane = lane_;
+    n_valid = min(max(last_key - kf + 1, 0), 16);
+    const size_t off = (((((size_t)page * a.nkv + kvh) << a.page_shift) + (n_valid > 0 ? (kf & ((1 << a.page_shift) - 1)) : 0)) * D
+                        + (size_t)lane * 8) * sizeof(bf16);
+    kb = reinterpret_cast<const unsigned char*>(a.kpages) + off;
+    vb = reinterpret_cast<const unsigned char*>(a.vpages) + off;
+  }
+  __device__ __forceinline__ void pair(int i) const {       // i < PAIRS, a constant after unrolling
+    const int c = lane + i * 32;
+    const int key = c / CH, ch = c - key * CH;
+    const int dst = key * Tile<D>::PITCH + ch * 16;
+    if (n_valid == 16) {                                     // every key exists: copies without a size operand
+      cp_async16_whole(ks + dst, kb + i * 512);
+      cp_async16_whole(vs + dst, vb + i * 512);
+    } else {
+      cp_async16(ks + dst, kb + i * 512, key < n_valid);
+      cp_async16(vs + dst, vb + i * 512, key < n_valid);
+    }
+  }
+  __device__ __forceinline__ void all() const {
+#pragma unroll
+    for (int i = 0; i < PAIRS; ++i) pair(i);
+  }
+};
 
 // One tile of keys for the warp's 16 rows: scores, mask, running softmax, O += P V.
 // hi0/hi1 (lo0/lo1): last (first) visible key of rows g and g+8; a row that sees nothing has hi < lo.
@@ -267,15 +344,41 @@ struct DecodeUnit {
     return R;
   }
 
-  // Starts the copies of each warp's first tile.  They read only keys and values of earlier steps,
-  // so a caller may issue them before the kernel (or operation) that produces q has finished.
+  // Starts the copies of each warp's first tiles (all stages but one; with one stage, that one).
+  // They read only keys and values of earlier steps, so a caller may issue them before the kernel
+  // (or operation) that produces q has finished.
+  static constexpr int AHEAD = STAGES > 1 ? STAGES - 1 : 1;
   __device__ static __forceinline__ void prefetch(const AttnArgs& a, int item, int kvh, int split, unsigned char* smem, int tid) {
     const Range R = range(a, item, split);
     const int warp = tid >> 5, lane = tid & 31;
     unsigned char* wbuf = smem + TILES_OFF + (size_t)warp * STAGES * 2 * TILE;
-    const int tile = R.t_begin + warp;
-    if (tile < R.t_end) load_kv_tile<D, BN, 32>(wbuf, wbuf + TILE, a, R.table, kvh, R.first_tile_key + tile * BN, R.p, lane);
-    cp_async_commit();
+    if (BN == 16 && a.page_shift >= 4) {               // one page per tile: all look-ups first, then all copies
+      int page[AHEAD];
+#pragma unroll
+      for (int s = 0; s < AHEAD; ++s) {
+        const int tile = R.t_begin + warp + s * WARPS;
+        page[s] = tile < R.t_end ? R.table[min(R.first_tile_key + tile * BN, R.p) >> a.page_shift] : 0;
+      }
+#pragma unroll
+      for (int s = 0; s < AHEAD; ++s) {
+        const int tile = R.t_begin + warp + s * WARPS;
+        unsigned char* sb = wbuf + (size_t)s * 2 * TILE;
+        if (tile < R.t_end) {
+          BlockCopy<D> bc;
+          bc.set(sb, sb + TILE, a, page[s], kvh, R.first_tile_key + tile * BN, R.p, lane);
+          bc.all();
+        }
+        cp_async_commit();
+      }
+      return;
+    }
+#pragma unroll
+    for (int s = 0; s < AHEAD; ++s) {
+      const int tile = R.t_begin + warp + s * WARPS;
+      unsigned char* sb = wbuf + (size_t)s * 2 * TILE;
+      if (tile < R.t_end) load_kv_tile<D, BN, 32>(sb, sb + TILE, a, R.table, kvh, R.first_tile_key + tile * BN, R.p, lane);
+      cp_async_commit();
+    }
   }
 
   template <typename Sync>
@@ -333,15 +436,30 @@ struct DecodeUnit {
     for (int nb = 0; nb < D / 8; ++nb) o[nb][0] = o[nb][1] = o[nb][2] = o[nb][3] = 0.f;
 
     int stage = 0;
+    // With one page per tile the page of the tile to ask for next is looked up an iteration before
+    // it is needed: asked for in the same iteration, the copies would wait for the trip to the table.
+    const bool page_per_tile = STAGES >= 2 && BN == 16 && a.page_shift >= 4;
+    int page_ahead = 0;
+    if (page_per_tile && tile + AHEAD * WARPS < R.t_end)
+      page_ahead = R.table[min(R.first_tile_key + (tile + AHEAD * WARPS) * BN, p) >> a.page_shift];
     for (; tile < R.t_end; tile += WARPS) {
-      const int next = tile + WARPS;
-      if constexpr (STAGES == 2) {
+      const int next = tile + AHEAD * WARPS;
+      if constexpr (STAGES >= 2) {
+        const int ns = stage + STAGES - 1 >= STAGES ? stage - 1 : stage + STAGES - 1;
+        unsigned char* nb = wbuf + (size_t)ns * 2 * TILE;
         if (next < R.t_end) {
-          unsigned char* nb = wbuf + (size_t)(stage ^ 1) * 2 * TILE;
-          load_kv_tile<D, BN, 32>(nb, nb + TILE, a, R.table, kvh, R.first_tile_key + next * BN, p, lane);
+          if (page_per_tile) {
+            BlockCopy<D> bc;
+            bc.set(nb, nb + TILE, a, page_ahead, kvh, R.first_tile_key + next * BN, p, lane);
+            bc.all();
+          } else {
+            load_kv_tile<D, BN, 32>(nb, nb + TILE, a, R.table, kvh, R.first_tile_key + next * BN, p, lane);
+          }
         }
         cp_async_commit();
-        cp_async_wait<1>();
+        if (page_per_tile && next + WARPS < R.t_end)
+          page_ahead = R.table[min(R.first_tile_key + (next + WARPS) * BN, p) >> a.page_shift];
+        cp_async_wait<STAGES - 1>();
       } else {
         cp_async_wait<0>();
       }
@@ -381,8 +499,8 @@ struct DecodeUnit {
       const bool need_mask = key0 < lo || key0 + BN - 1 > p;
       attend_tile<D, BN>(qf, cb, cb + TILE, key0, lo, p, lo, p, need_mask, a.scale_log2, m, l, o);
       __syncwarp();
-      if constexpr (STAGES == 2) {
-        stage ^= 1;
+      if constexpr (STAGES >= 2) {
+        stage = stage + 1 == STAGES ? 0 : stage + 1;
       } else {
         if (next < R.t_end) load_kv_tile<D, BN, 32>(wbuf, wbuf + TILE, a, R.table, kvh, R.first_tile_key + next * BN, p, lane);
         cp_async_commit();
