@@ -108,7 +108,7 @@ static int rope_store(void* qkv, const int* pos, int n, const float* inv_freq, c
                       void* stream) {
   if (n <= 0) return 0;
   if (d % 16 || (((uintptr_t)qkv | (uintptr_t)kpages | (uintptr_t)vpages) & 15)) return (int)cudaErrorInvalidValue;
-  launch(rope_store_kernel<T>, dim3(n), dim3(256), (size_t)(d / 2) * sizeof(float2), (cudaStream_t)stream, (T*)qkv, pos, n, inv_freq, axis, (T*)kpages, (T*)vpages,
+  launch(rope_store_kernel<T>, dim3(n), dim3(128), (size_t)(d / 2) * sizeof(float2), (cudaStream_t)stream, (T*)qkv, pos, n, inv_freq, axis, (T*)kpages, (T*)vpages,
                                                             kv_slot, nq, nkv, d, page_size, rotate, store);
   return launch_status();
 }

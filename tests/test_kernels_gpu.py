@@ -377,6 +377,49 @@ def test_tensor_core_attention_finds_a_far_key_and_the_window_edge(q_len):
         assert np.abs(f64(out) - ref).max() < 3e-2
 
 
+@pytest.mark.parametrize("tile_rows", [128, 256])
+def test_tcgen05_prefill_attention_finds_a_far_key_and_the_window_edge(tile_rows):
+    """The tcgen05 prefill kernel with one dominant key: on the edges of pages and of its 64-key
+    tiles, at both ends of the keys, just inside and just outside the window; the matching query
+    is the last of a run of 70 (so the key lies many tiles before the diagonal) and, in a second
+    run of the batch, a query in the middle of a row tile."""
+    from qwen25vl_lite.ops import kernels
+    nq, nkv, d, ps = 8, 2, 128, 16
+    lens, q_lens = [700, 300], [70, 300]
+    for key, window, visible in [(0, None, True), (15, None, True), (16, None, True), (63, None, True), (64, None, True),
+                                 (351, None, True), (629, None, True), (699, None, True), (700 - 60, 60, True), (700 - 61, 60, False)]:
+        rng = np.random.default_rng(key)
+        c = paged_case(rng, lens, q_lens, nq, nkv, d, ps, torch.bfloat16)
+        dense = [list(t) for t in c["dense"]]
+        q, k, v = dense[0]
+        k = k.clone()
+        k[key, 0] = (q[-1, 0] * 3).to(torch.bfloat16)      # the last query's head 0 matches this key
+        c["k_pages"][int(c["table"][0, key // ps]), 0, key % ps] = k[key, 0].cuda()
+        dense[0][1] = k
+        # second run: query 150 (of 300, head 5 = kv head 1) matches key 100, which every later query sees too
+        q2, k2, v2 = dense[1]
+        k2 = k2.clone()
+        k2[100, 1] = (q2[150, 5] * 3).to(torch.bfloat16)
+        c["k_pages"][int(c["table"][1, 100 // ps]), 1, 100 % ps] = k2[100, 1].cuda()
+        dense[1][1] = k2
+        G = nq // nkv
+        tiles = [(i, t) for i, n in enumerate(q_lens) for t in range(-(-n * G // tile_rows))]
+        out = torch.zeros((c["qkv"].shape[0], nq * d), dtype=torch.bfloat16, device="cuda")
+        kernels.attention_prefill_tcgen05(c["qkv"], out, c["k_pages"], c["v_pages"], c["table"], c["cu"], c["start"],
+                                          dev(np.asarray(tiles, np.int32)), nq, nkv, d, ps, window or 0, d ** -0.5,
+                                          tile_rows=tile_rows)
+        torch.cuda.synchronize()
+        assert int(kernels.error_flag("cuda:0")[0]) == 0
+        o = f64(out)
+        hit = np.abs(o[69, :d] - f64(v)[key, 0]).max() < 6e-2
+        assert hit == visible, f"key {key} window {window}: found={hit}"
+        in_window = window is None or 150 - 100 < window
+        hit2 = np.abs(o[70 + 150, 5 * d:6 * d] - f64(v2)[100, 1]).max() < 6e-2
+        assert hit2 == in_window
+        ref = attention_oracle([tuple(t) for t in dense], window)
+        assert np.abs(o - ref).max() < 3e-2
+
+
 def test_decode_splits_heuristic():
     from qwen25vl_lite.ops.attention import decode_splits
     assert decode_splits(1, 2, 100) == 1                  # short context: nothing to split
