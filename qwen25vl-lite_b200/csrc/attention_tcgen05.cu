@@ -4,18 +4,17 @@
 // 156-175, src/qwen25vl_lite/attention.py:143-148): S = Q K^T * D^-1/2, a query at position a sees
 // keys j <= a (and j > a - window), softmax over the keys in float, O = P V.
 //
-// A CTA takes RT row tiles (RT = 1 or 2) of 128 rows = (token, query head of one kv group) pairs of
-// one entry, so one pass over a kv head's keys serves the whole group (and with RT = 2 twice as many
-// tokens), and walks the keys in tiles of 64.  Its threads have two roles that meet only at
-// mbarriers:
+// A CTA takes 128 rows = (token, query head of one kv group) pairs of one entry, so one pass over a
+// kv head's keys serves the whole group, and walks the keys in tiles of 64.  Its threads have two
+// roles that meet only at mbarriers:
 //   * the row threads, one per row (= one lane of tensor memory): they copy Q (once) and the K and V
 //     tiles from their pages into shared memory by 16-byte cp.async, in the 128-byte-swizzled layout
 //     the tensor core reads (rows of 64 values, 8 rows per 1 KB atom, chunk c of row r at c ^ (r % 8));
 //     they read their 64 scores of a tile with tcgen05.ld, do the running softmax alone (no
 //     shuffles), and write their row of P as bfloat16 pairs back into the tensor-memory columns the
 //     scores came from;
-//   * one thread of the warp after them issues tcgen05.mma: S[128 x 64] = Q . K^T per row tile (both
-//     operands K-major in shared memory, 8 steps of 16 over the head size) into one of two score
+//   * one thread of the warp after them issues tcgen05.mma: S[128 x 64] = Q . K^T (both operands
+//     K-major in shared memory, 8 steps of 16 over the head size) into one of two score
 //     buffers in tensor memory, and O[128 x 128] += P . V with P read from tensor memory and V read
 //     as it lies (a row of 128 head-size values per key: the MN-major operand form, 64-value halves
 //     8 KB apart, groups of 8 keys 1 KB apart).
@@ -23,21 +22,24 @@
 // V(t) when tile t begins and waits for them when its softmax of tile t is done, so in the steady
 // state it waits for no product and no copy.  The output accumulates in tensor memory over all
 // tiles; the exponentials use a lazy maximum (see below), so it is rescaled only rarely.
-// RT = 1: two CTAs to an SM (99 KB of shared memory, 256 of the 512 tensor-memory columns each);
-// RT = 2: one (131 KB, all 512 columns), half the key and value traffic per row.
+// Two CTAs fit an SM (99 KB of shared memory, 256 of the 512 tensor-memory columns each).  (Two row
+// tiles to a CTA, which halve the key and value traffic per row, were slower at every length tried:
+// 8,192 tokens 375 against 298 us.)
 //
 // Every mbarrier wait is bounded; a wait that gives up records a code in *err, and the CTA runs to
 // its end (freeing its tensor memory) with invalid output.  A parity wait cannot tell "not yet" from
 // "two phases on", so every wait here is provably within one phase of its barrier.
 #include "attention_decode.cuh"
 
-#define A5_ROWS 128                          // rows of a row tile; a CTA has RT of them
+#define A5_ROWS 128
+#define A5_NROW 128                          // row threads
+#define A5_THREADS (A5_NROW + 32)             // and the warp that issues the products
 #define A5_BN 64
 #define A5_D 128
 #define A5_WAIT_LIMIT (1 << 22)
-#define A5_Q_BYTES (2 * A5_ROWS * 128)            // a row tile of Q: two 64-value halves of 128 rows
+#define A5_Q_BYTES (2 * A5_ROWS * 128)            // Q: two 64-value halves of 128 rows
 #define A5_KV_BYTES (2 * A5_BN * 128)             // two halves of 64 keys
-#define A5_SMEM(RT) ((RT) * A5_Q_BYTES + 4 * A5_KV_BYTES + 2048 + 1024)  // Q, two K and two V tiles, barriers and key rows, room to align
+#define A5_SMEM (A5_Q_BYTES + 4 * A5_KV_BYTES + 2048 + 1024)  // Q, two K and two V tiles, barriers and key rows, room to align
 
 __device__ __forceinline__ unsigned a5_s32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ void a5_mbar_init(unsigned long long* bar, int count) {
@@ -158,16 +160,15 @@ __device__ __forceinline__ int a5_key_row(const AttnArgs& a, const int* __restri
 }
 
 // The same for pages of 16 tokens or more, where a block of 16 keys of a tile is 4 KB in one piece:
-// warp w of a row tile copies block w, every lane 8 (with two row tiles 4) pieces of 16 bytes at
+// warp w copies block w, every lane 8 pieces of 16 bytes at
 // block + (lane + 32 j) * 16, so a copy's addresses are one base and constants (copies whose
 // addresses each take a 64-bit multiply-add cost the warp three times as long to issue).
 // block_row: the row of the block's first key in the pages seen as [rows, D]; n_valid: how many of
 // its 16 keys exist (the others are filled with zeros).
-template <int NROW>
 __device__ __forceinline__ void a5_load_block(unsigned char* dst_tile, const bf16* __restrict__ pages, int block_row, int n_valid,
                                               int warp, int lane) {
-  constexpr int PER = 8 * 128 / NROW;                  // copies per lane
-  const int blk = warp & 3, j0 = (warp >> 2) * PER;
+  constexpr int PER = 8;                               // copies per lane
+  const int blk = warp & 3, j0 = 0;
   const int h = lane >> 4, cc = lane & 15;
   const unsigned char* src = reinterpret_cast<const unsigned char*>(pages + (size_t)block_row * A5_D) + lane * 16;
   unsigned char* dst = dst_tile + (cc >> 3) * (A5_BN * 128) + blk * 2048 + h * 128;
@@ -175,23 +176,22 @@ __device__ __forceinline__ void a5_load_block(unsigned char* dst_tile, const bf1
 #pragma unroll
   for (int jj = 0; jj < PER; ++jj) {
     const int j = j0 + jj;                             // key of the block: h + 2 j; its row in the tile: 16 blk + h + 2 j
-    const int r7 = (2 * jj) & 7;                       // (row % 8) without h (PER is 4 or 8: 2 j0 is a multiple of 8)
+    const int r7 = (2 * jj) & 7;                       // (row % 8) without h
     cp_async16(dst + (j >> 2) * 1024 + r7 * 128 + (x ^ (r7 << 4)), src + j * 512, h + 2 * j < n_valid);
   }
 }
 
 // A tile of 64 keys from their pages into a swizzled tile (zeros for rows[key] < 0): 1,024 copies
-// of 16 bytes shared among the NROW row threads.  rows: the 64 keys' rows, in shared memory.
-template <int NROW>
+// of 16 bytes shared among the row threads.  rows: the 64 keys' rows, in shared memory.
 __device__ __forceinline__ void a5_load_tile(unsigned char* dst_tile, const bf16* __restrict__ pages, const int* rows, int tid) {
-  constexpr int N = A5_BN * 16 / NROW;
+  constexpr int N = A5_BN * 16 / A5_NROW;
   // all rows first: the copies are volatile statements, and a read between two of them would wait for its turn
   int row[N];
 #pragma unroll
-  for (int i = 0; i < N; ++i) row[i] = rows[(tid + i * NROW) >> 4];
+  for (int i = 0; i < N; ++i) row[i] = rows[(tid + i * A5_NROW) >> 4];
 #pragma unroll
   for (int i = 0; i < N; ++i) {
-    const int idx = tid + i * NROW;
+    const int idx = tid + i * A5_NROW;
     const int key = idx >> 4, cc = idx & 15;
     cp_async16(dst_tile + (cc >> 3) * (A5_BN * 128) + a5_swz(key, cc & 7), pages + (size_t)max(row[i], 0) * A5_D + cc * 8, row[i] >= 0);
   }
@@ -207,16 +207,15 @@ struct A5Bars {
   unsigned tmem;
 };
 
-template <int RT>
-__global__ void __launch_bounds__(128 * RT + 32, 3 - RT) attention_prefill_tcgen05_kernel(AttnArgs a, int* __restrict__ err) {
-  constexpr int NROW = 128 * RT, ROWS = A5_ROWS * RT;   // one thread per row; the warp after them issues the products
-  constexpr int TMEM_COLS = 256 * RT, O_COL = 128 * RT; // per row tile two score buffers of 64 columns, then the outputs
+__global__ void __launch_bounds__(A5_THREADS, 2) attention_prefill_tcgen05_kernel(AttnArgs a, int* __restrict__ err) {
+  constexpr int NROW = A5_NROW, ROWS = A5_ROWS;         // one thread per row; the warp after them issues the products
+  constexpr int TMEM_COLS = 256, O_COL = 128;           // two score buffers of 64 columns, then the outputs
   pdl_trigger();
   pdl_wait();
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   unsigned char* q_s = smem;
-  unsigned char* k_s = q_s + RT * A5_Q_BYTES;             // two K tiles
+  unsigned char* k_s = q_s + A5_Q_BYTES;                  // two K tiles
   unsigned char* v_s = k_s + 2 * A5_KV_BYTES;             // two V tiles
   A5Bars* bars = reinterpret_cast<A5Bars*>(v_s + 2 * A5_KV_BYTES);
   int* key_rows = reinterpret_cast<int*>(v_s + 2 * A5_KV_BYTES + 128);   // [4 tiles][64 keys]: see below
@@ -294,20 +293,20 @@ __global__ void __launch_bounds__(128 * RT + 32, 3 - RT) attention_prefill_tcgen
   // nothing of its own is in flight.
   if (tid < NROW) {
     if (blocks) {
-      a5_load_block<NROW>(k_s, a.kpages, rb0, block_valid(block_key), warp, lane);
-      if (n_tiles > 1) a5_load_block<NROW>(k_s + A5_KV_BYTES, a.kpages, rb1, block_valid(block_key + A5_BN), warp, lane);
-      a5_load_block<NROW>(v_s, a.vpages, rb0, block_valid(block_key), warp, lane);
+      a5_load_block(k_s, a.kpages, rb0, block_valid(block_key), warp, lane);
+      if (n_tiles > 1) a5_load_block(k_s + A5_KV_BYTES, a.kpages, rb1, block_valid(block_key + A5_BN), warp, lane);
+      a5_load_block(v_s, a.vpages, rb0, block_valid(block_key), warp, lane);
     } else {
-      a5_load_tile<NROW>(k_s, a.kpages, key_rows, tid);
-      if (n_tiles > 1) a5_load_tile<NROW>(k_s + A5_KV_BYTES, a.kpages, key_rows + A5_BN, tid);
-      a5_load_tile<NROW>(v_s, a.vpages, key_rows, tid);
+      a5_load_tile(k_s, a.kpages, key_rows, tid);
+      if (n_tiles > 1) a5_load_tile(k_s + A5_KV_BYTES, a.kpages, key_rows + A5_BN, tid);
+      a5_load_tile(v_s, a.vpages, key_rows, tid);
     }
     cp_async_commit();
     const uint4* src = reinterpret_cast<const uint4*>(a.qkv + (size_t)(q0 + tok) * a.qkv_stride + (size_t)(kvh * G + head) * A5_D);
 #pragma unroll
     for (int cc = 0; cc < 16; ++cc) {
       const uint4 v = live ? __ldcg(src + cc) : make_uint4(0, 0, 0, 0);
-      *reinterpret_cast<uint4*>(q_s + (tid >> 7) * A5_Q_BYTES + (cc >> 3) * (A5_ROWS * 128) + a5_swz(tid & 127, cc & 7)) = v;
+      *reinterpret_cast<uint4*>(q_s + (cc >> 3) * (A5_ROWS * 128) + a5_swz(tid, cc & 7)) = v;
     }
     cp_async_wait<0>();
     a5_proxy_fence();                                    // Q and this thread's part of K and V, visible to the tensor core
@@ -321,16 +320,13 @@ __global__ void __launch_bounds__(128 * RT + 32, 3 - RT) attention_prefill_tcgen
 
   if (tid == NROW) {
     // ---- the thread that issues the products ----
-    auto scores = [&](int t) {                            // S(t) = Q . K(t)^T into score buffer t % 2 of every row tile
+    auto scores = [&](int t) {                            // S(t) = Q . K(t)^T into score buffer t % 2
       const unsigned char* kt = k_s + (size_t)(t & 1) * A5_KV_BYTES;
 #pragma unroll
-      for (int rt = 0; rt < RT; ++rt) {
-#pragma unroll
-        for (int ks = 0; ks < A5_D / 16; ++ks) {          // 16 values of the head size per step: 32 bytes along a row
-          const unsigned long long ad = a5_desc(a5_s32(q_s) + rt * A5_Q_BYTES + (ks >> 2) * (A5_ROWS * 128) + (ks & 3) * 32, 16, 1024);
-          const unsigned long long bd = a5_desc(a5_s32(kt) + (ks >> 2) * (A5_BN * 128) + (ks & 3) * 32, 16, 1024);
-          a5_mma(tmem_base + rt * 128 + (unsigned)(t & 1) * A5_BN, ad, bd, idesc_s, ks != 0);
-        }
+      for (int ks = 0; ks < A5_D / 16; ++ks) {            // 16 values of the head size per step: 32 bytes along a row
+        const unsigned long long ad = a5_desc(a5_s32(q_s) + (ks >> 2) * (A5_ROWS * 128) + (ks & 3) * 32, 16, 1024);
+        const unsigned long long bd = a5_desc(a5_s32(kt) + (ks >> 2) * (A5_BN * 128) + (ks & 3) * 32, 16, 1024);
+        a5_mma(tmem_base + (unsigned)(t & 1) * A5_BN, ad, bd, idesc_s, ks != 0);
       }
       a5_commit(bars->s_full + (t & 1));
     };
@@ -348,13 +344,9 @@ __global__ void __launch_bounds__(128 * RT + 32, 3 - RT) attention_prefill_tcgen
       a5_fence_after();
       const unsigned char* vt = v_s + (size_t)(t & 1) * A5_KV_BYTES;
 #pragma unroll
-      for (int rt = 0; rt < RT; ++rt) {
-#pragma unroll
-        for (int ks = 0; ks < A5_BN / 16; ++ks) {         // 16 keys per step: 8 columns of P, 2 KB down V
-          const unsigned long long bd = a5_desc(a5_s32(vt) + ks * 2048, A5_BN * 128, 1024);
-          a5_mma_ts(tmem_base + O_COL + rt * 128, tmem_base + rt * 128 + (unsigned)(t & 1) * A5_BN + ks * 8, bd, idesc_pv,
-                    (t | ks) != 0);
-        }
+      for (int ks = 0; ks < A5_BN / 16; ++ks) {           // 16 keys per step: 8 columns of P, 2 KB down V
+        const unsigned long long bd = a5_desc(a5_s32(vt) + ks * 2048, A5_BN * 128, 1024);
+        a5_mma_ts(tmem_base + O_COL, tmem_base + (unsigned)(t & 1) * A5_BN + ks * 8, bd, idesc_pv, (t | ks) != 0);
       }
       a5_commit(bars->pv_done + (t & 1));
       if (t + 2 < n_tiles) {
@@ -369,8 +361,8 @@ __global__ void __launch_bounds__(128 * RT + 32, 3 - RT) attention_prefill_tcgen
     // ---- the rows ----
     a5_mbar_arrive(bars->k_full);                         // K(0) and K(1), after the fence above
     if (n_tiles > 1) a5_mbar_arrive(bars->k_full + 1);
-    const unsigned t_lane = tmem_base + ((unsigned)((warp & 3) * 32) << 16) + (warp >> 2) * 128;   // this row tile's score buffers
-    const unsigned t_o = tmem_base + ((unsigned)((warp & 3) * 32) << 16) + O_COL + (warp >> 2) * 128;
+    const unsigned t_lane = tmem_base + ((unsigned)(warp * 32) << 16);          // this warp's lanes: the score buffers
+    const unsigned t_o = t_lane + O_COL;                                         // and the outputs
     // Running softmax with a lazy maximum: the exponentials use m_used, which follows the true maximum
     // only when that has grown by more than 8 (a factor 256, far inside the range of bfloat16 and of
     // the float sums), so the output rows in tensor memory are read, scaled and written back only
@@ -394,14 +386,14 @@ __global__ void __launch_bounds__(128 * RT + 32, 3 - RT) attention_prefill_tcgen
       int row_ahead = -1, page_ahead = 0;                  // asked for now, used when the tile ends
       if (blocks) {
         if (tile + 2 < n_tiles)
-          a5_load_block<NROW>(k_s + (size_t)stage * A5_KV_BYTES, a.kpages, rb2, block_valid(kb + 2 * A5_BN), warp, lane);
-        if (tile > 0) a5_load_block<NROW>(v_s + (size_t)stage * A5_KV_BYTES, a.vpages, rb0, block_valid(kb), warp, lane);
+          a5_load_block(k_s + (size_t)stage * A5_KV_BYTES, a.kpages, rb2, block_valid(kb + 2 * A5_BN), warp, lane);
+        if (tile > 0) a5_load_block(v_s + (size_t)stage * A5_KV_BYTES, a.vpages, rb0, block_valid(kb), warp, lane);
         cp_async_commit();
         if (kb + 3 * A5_BN <= c_hi) page_ahead = __ldg(table + ((kb + 3 * A5_BN) >> a.page_shift));
       } else {
         if (tile + 2 < n_tiles)
-          a5_load_tile<NROW>(k_s + (size_t)stage * A5_KV_BYTES, a.kpages, key_rows + ((tile + 2) & 3) * A5_BN, tid);
-        if (tile > 0) a5_load_tile<NROW>(v_s + (size_t)stage * A5_KV_BYTES, a.vpages, key_rows + (tile & 3) * A5_BN, tid);
+          a5_load_tile(k_s + (size_t)stage * A5_KV_BYTES, a.kpages, key_rows + ((tile + 2) & 3) * A5_BN, tid);
+        if (tile > 0) a5_load_tile(v_s + (size_t)stage * A5_KV_BYTES, a.vpages, key_rows + (tile & 3) * A5_BN, tid);
         cp_async_commit();
         if (looks_up && tile + 3 < n_tiles) row_ahead = a5_key_row(a, table, kvh, key0 + 3 * A5_BN + my_key, c_hi);
       }
@@ -514,28 +506,21 @@ __global__ void __launch_bounds__(128 * RT + 32, 3 - RT) attention_prefill_tcgen
   }
 }
 
-template <int RT>
-static int launch_a5(const AttnArgs& a, int n_tiles, int nkv, int* err, cudaStream_t stream) {
-  cudaError_t ce = cudaFuncSetAttribute(attention_prefill_tcgen05_kernel<RT>, cudaFuncAttributeMaxDynamicSharedMemorySize, A5_SMEM(RT));
-  if (ce != cudaSuccess) return (int)ce;
-  launch(attention_prefill_tcgen05_kernel<RT>, dim3(n_tiles, nkv), dim3(128 * RT + 32), (size_t)A5_SMEM(RT), stream, a, err);
-  return launch_status();
-}
-
-// items: (entry, row tile) pairs with row tiles of tile_rows = 128 or 256 rows (one or two row tiles
-// to a CTA; two halve the traffic of keys and values from the L2); otherwise the arguments of
+// items: (entry, row tile) pairs with row tiles of 128 rows; otherwise the arguments of
 // q25_attention_prefill_bf16.  Head size 128 only.  err: one int that receives a nonzero code if a
 // wait gave up.
 Q25_EXPORT int q25_attention_prefill_tcgen05_bf16(const void* qkv, int qkv_stride, void* out, const void* kp, const void* vp,
                                                   const int* bt, int tw, const int* cu_q, const int* q_start,
-                                                  const int* tiles, int n_tiles, int tile_rows, int nq, int nkv, int d,
-                                                  int page_size, int window, float scale, int* err, void* stream) {
+                                                  const int* tiles, int n_tiles, int nq, int nkv, int d, int page_size,
+                                                  int window, float scale, int* err, void* stream) {
   if (n_tiles <= 0) return 0;
-  if (d != A5_D || !err || (tile_rows != 128 && tile_rows != 256)) return (int)cudaErrorInvalidValue;
+  if (d != A5_D || !err) return (int)cudaErrorInvalidValue;
   AttnArgs a;
   int e = fill_args(a, qkv, qkv_stride, out, kp, vp, bt, tw, cu_q, q_start, tiles, nq, nkv, page_size, window, scale);
   if (e) return e;
   if (((uintptr_t)qkv & 15) || (qkv_stride % 8) || ((uintptr_t)out & 15)) return (int)cudaErrorInvalidValue;
-  return tile_rows == 128 ? launch_a5<1>(a, n_tiles, nkv, err, (cudaStream_t)stream)
-                          : launch_a5<2>(a, n_tiles, nkv, err, (cudaStream_t)stream);
+  cudaError_t ce = cudaFuncSetAttribute(attention_prefill_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, A5_SMEM);
+  if (ce != cudaSuccess) return (int)ce;
+  launch(attention_prefill_tcgen05_kernel, dim3(n_tiles, nkv), dim3(A5_THREADS), (size_t)A5_SMEM, (cudaStream_t)stream, a, err);
+  return launch_status();
 }

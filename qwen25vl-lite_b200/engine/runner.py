@@ -28,7 +28,6 @@ import torch
 
 from ..cache.manager import CacheManager, RequestCache
 from ..models.decoder import DecoderModel, StopRuntime
-from ..ops import attention as attention_ops
 from ..ops import kernels
 
 
@@ -99,7 +98,6 @@ class StepContext:
     decode_items: Optional[torch.Tensor] = None
     prefill_tiles: Dict[int, Optional[torch.Tensor]] = field(default_factory=dict)
     prefill_tiles128: Dict[int, Optional[torch.Tensor]] = field(default_factory=dict)    # the same in 128-row tiles
-    prefill_tiles256: Dict[int, Optional[torch.Tensor]] = field(default_factory=dict)    # and in 256-row tiles
     # host copies, for parts written with torch operators (toy parts in tests)
     host_q_lens: List[int] = field(default_factory=list)
     host_q_start: List[int] = field(default_factory=list)
@@ -114,8 +112,7 @@ class StepContext:
                       group.page_size)
 
 
-# row tiles of the prefill attention kernels: mma.sync 64, tcgen05 128 (256 with two row tiles to a CTA)
-PREFILL_TILE_ROWS = (64, 128, 256) if attention_ops.TCGEN05_ROW_TILES == 2 else (64, 128)
+PREFILL_TILE_ROWS = (64, 128)   # row tiles of the two prefill attention kernels (mma.sync, tcgen05)
 GRAPH_WIDTH_STEP = 16      # block-table widths of captured steps are rounded up to this many pages
 MAX_GRAPHS = 32
 
@@ -407,7 +404,6 @@ class ModelRunner:
             decode_items=d(dec_s) if decode_list else None,
             prefill_tiles={G: (d(sp, (sp[1] // 2, 2)) if sp[1] else None) for (G, rows), sp in tile_s.items() if rows == 64},
             prefill_tiles128={G: (d(sp, (sp[1] // 2, 2)) if sp[1] else None) for (G, rows), sp in tile_s.items() if rows == 128},
-            prefill_tiles256={G: (d(sp, (sp[1] // 2, 2)) if sp[1] else None) for (G, rows), sp in tile_s.items() if rows == 256},
             host_q_lens=q_lens, host_q_start=starts,
             host_slots=[e.request.cache.slot for e in entries],
         )

@@ -23,9 +23,6 @@ SM_COUNT = 148
 # which kernel attends runs of tokens at head size 128: "tcgen05" (scores and P.V on the 5th-generation
 # tensor cores) or "mma" (mma.sync, the kernel of every other head size)
 PREFILL_ATTENTION = __import__("os").environ.get("Q25VL_PREFILL_ATTENTION", "tcgen05")
-# row tiles of 128 rows that a CTA of the tcgen05 kernel takes: 1 (two CTAs to an SM; the faster one at every
-# size measured) or 2 (half the key and value traffic per row)
-TCGEN05_ROW_TILES = int(__import__("os").environ.get("Q25VL_TCGEN05_ROW_TILES", "1"))
 _scratch = {}
 
 
@@ -99,13 +96,10 @@ def paged_attention(ctx, qkv, kv, nq: int, nkv: int, head_dim: int, window, scal
     tiles = ctx.prefill_tiles[group]
     if tiles is not None:
         tiles128 = getattr(ctx, "prefill_tiles128", {}).get(group)
-        tiles256 = getattr(ctx, "prefill_tiles256", {}).get(group)
         if PREFILL_ATTENTION == "tcgen05" and tiles128 is not None and group <= 128 \
                 and kernels.attention_tcgen05_supports(qkv.dtype, head_dim, kv.page_size, qkv):
-            wide = TCGEN05_ROW_TILES == 2 and tiles256 is not None
             kernels.attention_prefill_tcgen05(qkv, out, kv.k_pages, kv.v_pages, kv.block_table, ctx.cu_q, ctx.q_start_pos,
-                                              tiles256 if wide else tiles128, nq, nkv, head_dim, kv.page_size, window, scale,
-                                              tile_rows=256 if wide else 128)
+                                              tiles128, nq, nkv, head_dim, kv.page_size, window, scale)
         else:
             kernels.attention_prefill(qkv, out, kv.k_pages, kv.v_pages, kv.block_table, ctx.cu_q, ctx.q_start_pos, tiles,
                                       nq, nkv, head_dim, kv.page_size, window, scale)

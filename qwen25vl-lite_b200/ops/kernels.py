@@ -318,17 +318,14 @@ def attention_tcgen05_supports(dtype: torch.dtype, head_dim: int, page_size: int
 def attention_prefill_tcgen05(qkv: torch.Tensor, out: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor,
                               block_table: torch.Tensor, cu_q: torch.Tensor, q_start_pos: torch.Tensor,
                               tiles: torch.Tensor, nq: int, nkv: int, head_dim: int, page_size: int, window: int,
-                              scale: float, tile_rows: int = 128) -> None:
+                              scale: float) -> None:
     """``attention_prefill`` on the tcgen05 tensor cores (scores, P and the outputs in tensor memory);
-    ``tiles`` is int32 [n, 2]: (entry, row tile) with row tiles of ``tile_rows`` = 128 or 256 rows
-    (256: two row tiles share a CTA and its key and value tiles)."""
+    ``tiles`` is int32 [n, 2]: (entry, row tile) with row tiles of 128 rows."""
     if not attention_tcgen05_supports(qkv.dtype, head_dim, page_size, qkv):
         raise KernelError(f"attention_prefill_tcgen05: unsupported head size {head_dim}, page size {page_size} or layout")
-    if tile_rows not in (128, 256):
-        raise KernelError(f"attention_prefill_tcgen05: row tiles of {tile_rows} rows; 128 or 256 are built")
-    _check(_fn("q25_attention_prefill_tcgen05_bf16", [_P, _I, _P, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _F, _P, _P])(
+    _check(_fn("q25_attention_prefill_tcgen05_bf16", [_P, _I, _P, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _P, _P])(
         qkv.data_ptr(), qkv.stride(0), out.data_ptr(), k_pages.data_ptr(), v_pages.data_ptr(), block_table.data_ptr(),
-        block_table.shape[1], cu_q.data_ptr(), q_start_pos.data_ptr(), tiles.data_ptr(), tiles.shape[0], tile_rows, nq, nkv,
+        block_table.shape[1], cu_q.data_ptr(), q_start_pos.data_ptr(), tiles.data_ptr(), tiles.shape[0], nq, nkv,
         head_dim, page_size, int(window or 0), float(scale), error_flag(qkv.device).data_ptr(), _stream()),
         "attention_prefill_tcgen05")
 

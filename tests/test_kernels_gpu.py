@@ -297,25 +297,22 @@ def test_attention_tensor_core_kernels(nq, nkv, d, page_size, window, splits):
     assert np.abs(f64(out) - ref).max() < 3e-2
 
 
-@pytest.mark.parametrize("tile_rows", [128, 256])
 @pytest.mark.parametrize("nq,nkv,page_size,window", [(16, 2, 16, None), (8, 8, 4, None), (28, 4, 16, 150), (5, 1, 32, None), (40, 8, 8, 64)])
-def test_attention_prefill_tcgen05(nq, nkv, page_size, window, tile_rows):
+def test_attention_prefill_tcgen05(nq, nkv, page_size, window):
     """The tcgen05 prefill attention (scores, P and outputs in tensor memory, head size 128) against
     the oracle: runs that start inside a cached prefix, runs shorter and longer than a row tile,
-    groups of 8, 1, 7 and 5 query heads, small and large pages, windows that cut the keys; one and
-    two row tiles to a CTA."""
+    groups of 8, 1, 7 and 5 query heads, small and large pages, windows that cut the keys."""
     from qwen25vl_lite.ops import kernels
     d = 128
     rng = np.random.default_rng(21)
     lens, q_lens = [300, 37, 130, 64, 517, 333, 9], [300, 37, 2, 17, 200, 70, 9]
     c = paged_case(rng, lens, q_lens, nq, nkv, d, page_size, torch.bfloat16)
     G = nq // nkv
-    tiles = [(i, t) for i, n in enumerate(q_lens) for t in range(-(-n * G // tile_rows))]
+    tiles = [(i, t) for i, n in enumerate(q_lens) for t in range(-(-n * G // 128))]
     out = torch.zeros((c["qkv"].shape[0], nq * d), dtype=torch.bfloat16, device="cuda")
     assert kernels.attention_tcgen05_supports(torch.bfloat16, d, page_size, c["qkv"])
     kernels.attention_prefill_tcgen05(c["qkv"], out, c["k_pages"], c["v_pages"], c["table"], c["cu"], c["start"],
-                                      dev(np.asarray(tiles, np.int32)), nq, nkv, d, page_size, window or 0, d ** -0.5,
-                                      tile_rows=tile_rows)
+                                      dev(np.asarray(tiles, np.int32)), nq, nkv, d, page_size, window or 0, d ** -0.5)
     torch.cuda.synchronize()
     assert int(kernels.error_flag("cuda:0")[0]) == 0
     ref = attention_oracle(c["dense"], window)
@@ -323,8 +320,7 @@ def test_attention_prefill_tcgen05(nq, nkv, page_size, window, tile_rows):
     assert not kernels.attention_tcgen05_supports(torch.bfloat16, 64, page_size)
 
 
-@pytest.mark.parametrize("tile_rows", [128, 256])
-def test_attention_prefill_tcgen05_long_runs_repeat_exactly(tile_rows):
+def test_attention_prefill_tcgen05_long_runs_repeat_exactly():
     """Many key tiles per CTA, more CTAs than the GPU holds at once, and scores that keep growing
     along the keys, so that the rows in tensor memory are rescaled again and again: against the
     oracle, and eight launches give the same bits (the rows of a CTA, the thread that issues the
@@ -338,14 +334,14 @@ def test_attention_prefill_tcgen05_long_runs_repeat_exactly(tile_rows):
     c = paged_case(rng, lens, q_lens, nq, nkv, d, page_size, torch.bfloat16, key_gain=lambda L: 1.0 + 5.0 * np.arange(L) / L)
     dense = c["dense"]
     G = nq // nkv
-    tiles = [(i, t) for i, n in enumerate(q_lens) for t in range(-(-n * G // tile_rows))]
-    tiles.sort(key=lambda it: -(lens[it[0]] - q_lens[it[0]] + (it[1] + 1) * tile_rows // G))
+    tiles = [(i, t) for i, n in enumerate(q_lens) for t in range(-(-n * G // 128))]
+    tiles.sort(key=lambda it: -(lens[it[0]] - q_lens[it[0]] + (it[1] + 1) * 128 // G))
     items = dev(np.asarray(tiles, np.int32))
     outs = []
     for _ in range(8):
         out = torch.full((c["qkv"].shape[0], nq * d), 3.0, dtype=torch.bfloat16, device="cuda")
         kernels.attention_prefill_tcgen05(c["qkv"], out, c["k_pages"], c["v_pages"], c["table"], c["cu"], c["start"],
-                                          items, nq, nkv, d, page_size, 0, d ** -0.5, tile_rows=tile_rows)
+                                          items, nq, nkv, d, page_size, 0, d ** -0.5)
         outs.append(out)
     torch.cuda.synchronize()
     assert int(kernels.error_flag("cuda:0")[0]) == 0
@@ -377,8 +373,7 @@ def test_tensor_core_attention_finds_a_far_key_and_the_window_edge(q_len):
         assert np.abs(f64(out) - ref).max() < 3e-2
 
 
-@pytest.mark.parametrize("tile_rows", [128, 256])
-def test_tcgen05_prefill_attention_finds_a_far_key_and_the_window_edge(tile_rows):
+def test_tcgen05_prefill_attention_finds_a_far_key_and_the_window_edge():
     """The tcgen05 prefill kernel with one dominant key: on the edges of pages and of its 64-key
     tiles, at both ends of the keys, just inside and just outside the window; the matching query
     is the last of a run of 70 (so the key lies many tiles before the diagonal) and, in a second
@@ -403,11 +398,10 @@ def test_tcgen05_prefill_attention_finds_a_far_key_and_the_window_edge(tile_rows
         c["k_pages"][int(c["table"][1, 100 // ps]), 1, 100 % ps] = k2[100, 1].cuda()
         dense[1][1] = k2
         G = nq // nkv
-        tiles = [(i, t) for i, n in enumerate(q_lens) for t in range(-(-n * G // tile_rows))]
+        tiles = [(i, t) for i, n in enumerate(q_lens) for t in range(-(-n * G // 128))]
         out = torch.zeros((c["qkv"].shape[0], nq * d), dtype=torch.bfloat16, device="cuda")
         kernels.attention_prefill_tcgen05(c["qkv"], out, c["k_pages"], c["v_pages"], c["table"], c["cu"], c["start"],
-                                          dev(np.asarray(tiles, np.int32)), nq, nkv, d, ps, window or 0, d ** -0.5,
-                                          tile_rows=tile_rows)
+                                          dev(np.asarray(tiles, np.int32)), nq, nkv, d, ps, window or 0, d ** -0.5)
         torch.cuda.synchronize()
         assert int(kernels.error_flag("cuda:0")[0]) == 0
         o = f64(out)
