@@ -37,6 +37,7 @@
 #define A5_BN 64
 #define A5_D 128
 #define A5_WAIT_LIMIT (1 << 22)
+#define A5_SMS 148                           // SMs of a B200
 #define A5_Q_BYTES (2 * A5_ROWS * 128)            // Q: two 64-value halves of 128 rows
 #define A5_KV_BYTES (2 * A5_BN * 128)             // two halves of 64 keys
 #define A5_SMEM (A5_Q_BYTES + 4 * A5_KV_BYTES + 2048 + 1024)  // Q, two K and two V tiles, barriers and key rows, room to align
@@ -221,7 +222,16 @@ __global__ void __launch_bounds__(A5_THREADS, 2) attention_prefill_tcgen05_kerne
   int* key_rows = reinterpret_cast<int*>(v_s + 2 * A5_KV_BYTES + 128);   // [4 tiles][64 keys]: see below
 
   const int tid = threadIdx.x, warp = tid >> 5;
-  const int seq = a.items[2 * blockIdx.x], row_tile = a.items[2 * blockIdx.x + 1], kvh = blockIdx.y;
+  // Which (row tile, kv head) this CTA takes.  The list comes heaviest first.  Two CTAs share an SM
+  // and its throughput, and the first 148 CTAs of a grid go one to each SM, the next 148 join them in
+  // the same order: with 149 to 296 CTAs in all, CTA 148 + s therefore takes the s-th lightest piece
+  // of work, so that every SM gets a heavy and a light one (2,048 tokens in 256 pieces: the busiest
+  // SM has 34 key tiles instead of 61).  Larger grids are taken in order: CTAs start as others end.
+  const int n_work = gridDim.x;
+  const int work = (n_work > A5_SMS && n_work <= 2 * A5_SMS && (int)blockIdx.x >= A5_SMS)
+                       ? n_work - 1 - ((int)blockIdx.x - A5_SMS) : (int)blockIdx.x;
+  const int item = work / a.nkv, kvh = work - item * a.nkv;
+  const int seq = a.items[2 * item], row_tile = a.items[2 * item + 1];
   const int G = a.nq / a.nkv;
   const int q0 = a.cu_q[seq], q_len = a.cu_q[seq + 1] - q0, start = a.q_start_pos[seq];
   const int n_rows = q_len * G;
@@ -521,6 +531,6 @@ Q25_EXPORT int q25_attention_prefill_tcgen05_bf16(const void* qkv, int qkv_strid
   if (((uintptr_t)qkv & 15) || (qkv_stride % 8) || ((uintptr_t)out & 15)) return (int)cudaErrorInvalidValue;
   cudaError_t ce = cudaFuncSetAttribute(attention_prefill_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, A5_SMEM);
   if (ce != cudaSuccess) return (int)ce;
-  launch(attention_prefill_tcgen05_kernel, dim3(n_tiles, nkv), dim3(A5_THREADS), (size_t)A5_SMEM, (cudaStream_t)stream, a, err);
+  launch(attention_prefill_tcgen05_kernel, dim3(n_tiles * nkv), dim3(A5_THREADS), (size_t)A5_SMEM, (cudaStream_t)stream, a, err);
   return launch_status();
 }
