@@ -30,90 +30,18 @@
 // its end (freeing its tensor memory) with invalid output.  A parity wait cannot tell "not yet" from
 // "two phases on", so every wait here is provably within one phase of its barrier.
 #include "attention_decode.cuh"
+#include "tcgen05.cuh"
 
 #define A5_ROWS 128
 #define A5_NROW 128                          // row threads
 #define A5_THREADS (A5_NROW + 32)             // and the warp that issues the products
 #define A5_BN 64
 #define A5_D 128
-#define A5_WAIT_LIMIT (1 << 22)
 #define A5_SMS 148                           // SMs of a B200
 #define A5_Q_BYTES (2 * A5_ROWS * 128)            // Q: two 64-value halves of 128 rows
 #define A5_KV_BYTES (2 * A5_BN * 128)             // two halves of 64 keys
 #define A5_SMEM (A5_Q_BYTES + 4 * A5_KV_BYTES + 2048 + 1024)  // Q, two K and two V tiles, barriers and key rows, room to align
 
-__device__ __forceinline__ unsigned a5_s32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
-__device__ __forceinline__ void a5_mbar_init(unsigned long long* bar, int count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(a5_s32(bar)), "r"(count));
-}
-__device__ __forceinline__ bool a5_mbar_wait(unsigned long long* bar, unsigned parity) {
-  for (int i = 0; i < A5_WAIT_LIMIT; ++i) {
-    unsigned done;
-    asm volatile(
-        "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
-        : "=r"(done) : "r"(a5_s32(bar)), "r"(parity) : "memory");
-    if (done) return true;
-  }
-  return false;
-}
-// Shared-memory matrix descriptor, 128-byte swizzle.  lbo / sbo in bytes.
-__device__ __forceinline__ unsigned long long a5_desc(unsigned smem_addr, unsigned lbo, unsigned sbo) {
-  unsigned long long d = 0;
-  d |= (unsigned long long)((smem_addr & 0x3FFFF) >> 4);
-  d |= (unsigned long long)(lbo >> 4) << 16;
-  d |= (unsigned long long)(sbo >> 4) << 32;
-  d |= (unsigned long long)1 << 46;                         // descriptor version of sm_100
-  d |= (unsigned long long)2 << 61;                         // 128-byte swizzle
-  return d;
-}
-// bf16 x bf16 -> f32, M 128, N n; b_mn: the B operand is MN-major (else K-major); A is K-major.
-__device__ __forceinline__ unsigned a5_idesc(int n, bool b_mn) {
-  return (1u << 4) | (1u << 7) | (1u << 10) | ((b_mn ? 1u : 0u) << 16) | ((unsigned)(n >> 3) << 17) | ((unsigned)(A5_ROWS >> 4) << 24);
-}
-__device__ __forceinline__ void a5_mma(unsigned tmem_d, unsigned long long adesc, unsigned long long bdesc, unsigned idesc,
-                                       unsigned accumulate) {
-  asm volatile(
-      "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n"
-      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
-}
-__device__ __forceinline__ void a5_commit(unsigned long long* bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(a5_s32(bar)) : "memory");
-}
-__device__ __forceinline__ void a5_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory"); }
-__device__ __forceinline__ void a5_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory"); }
-__device__ __forceinline__ void a5_proxy_fence() { asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory"); }
-// 32 consecutive float columns of this thread's lane of tensor memory.
-__device__ __forceinline__ void a5_ld32(unsigned taddr, float (&v)[32]) {
-  unsigned r[32];
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,"
-      "%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];\n"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
-        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]),
-        "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]),
-        "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-      : "r"(taddr));
-  asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
-#pragma unroll
-  for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
-}
-
-// The same 32 columns written back.
-__device__ __forceinline__ void a5_st32(unsigned taddr, const float (&v)[32]) {
-  asm volatile(
-      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,"
-      "%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};\n"
-      ::"r"(taddr), "r"(__float_as_uint(v[0])), "r"(__float_as_uint(v[1])), "r"(__float_as_uint(v[2])), "r"(__float_as_uint(v[3])),
-        "r"(__float_as_uint(v[4])), "r"(__float_as_uint(v[5])), "r"(__float_as_uint(v[6])), "r"(__float_as_uint(v[7])),
-        "r"(__float_as_uint(v[8])), "r"(__float_as_uint(v[9])), "r"(__float_as_uint(v[10])), "r"(__float_as_uint(v[11])),
-        "r"(__float_as_uint(v[12])), "r"(__float_as_uint(v[13])), "r"(__float_as_uint(v[14])), "r"(__float_as_uint(v[15])),
-        "r"(__float_as_uint(v[16])), "r"(__float_as_uint(v[17])), "r"(__float_as_uint(v[18])), "r"(__float_as_uint(v[19])),
-        "r"(__float_as_uint(v[20])), "r"(__float_as_uint(v[21])), "r"(__float_as_uint(v[22])), "r"(__float_as_uint(v[23])),
-        "r"(__float_as_uint(v[24])), "r"(__float_as_uint(v[25])), "r"(__float_as_uint(v[26])), "r"(__float_as_uint(v[27])),
-        "r"(__float_as_uint(v[28])), "r"(__float_as_uint(v[29])), "r"(__float_as_uint(v[30])), "r"(__float_as_uint(v[31]))
-      : "memory");
-  asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory");
-}
 // 2^x on the special-function unit (exact enough for probabilities that are rounded to bfloat16; 2^-inf = 0).
 __device__ __forceinline__ float a5_ex2(float x) {
   float y;
@@ -130,29 +58,6 @@ __device__ __forceinline__ float a5_max3(float a, float b, float c) {
 
 // Byte offset of the 16-byte chunk c (0..7) of row r inside a swizzled block of 128-byte rows.
 __device__ __forceinline__ int a5_swz(int r, int c) { return (r >> 3) * 1024 + (r & 7) * 128 + ((c ^ (r & 7)) << 4); }
-
-// The same 32 columns written from packed words, e.g. 64 bfloat16 probabilities of this thread's row.
-__device__ __forceinline__ void a5_st32u(unsigned taddr, const unsigned (&v)[32]) {
-  asm volatile(
-      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,"
-      "%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};\n"
-      ::"r"(taddr), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]), "r"(v[8]), "r"(v[9]),
-        "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15]), "r"(v[16]), "r"(v[17]), "r"(v[18]), "r"(v[19]),
-        "r"(v[20]), "r"(v[21]), "r"(v[22]), "r"(v[23]), "r"(v[24]), "r"(v[25]), "r"(v[26]), "r"(v[27]), "r"(v[28]), "r"(v[29]),
-        "r"(v[30]), "r"(v[31])
-      : "memory");
-  asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory");
-}
-__device__ __forceinline__ void a5_mbar_arrive(unsigned long long* bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(a5_s32(bar)) : "memory");
-}
-// The product with the A operand in tensor memory: lane = row, 16 bfloat16 of a row in 8 columns.
-__device__ __forceinline__ void a5_mma_ts(unsigned tmem_d, unsigned tmem_a, unsigned long long bdesc, unsigned idesc,
-                                          unsigned accumulate) {
-  asm volatile(
-      "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n}\n"
-      ::"r"(tmem_d), "r"(tmem_a), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
-}
 
 // Where key kidx of a kv head lies: its row in the pages seen as [rows, D]; -1 past last_key.
 __device__ __forceinline__ int a5_key_row(const AttnArgs& a, const int* __restrict__ table, int kvh, int kidx, int last_key) {
@@ -245,18 +150,18 @@ __global__ void __launch_bounds__(A5_THREADS, 2) attention_prefill_tcgen05_kerne
   const int n_tiles = (c_hi - key_begin) / A5_BN + 1;
 
   if (tid == 0) {
-    a5_mbar_init(bars->s_full, 1);
-    a5_mbar_init(bars->s_full + 1, 1);
-    a5_mbar_init(bars->k_full, NROW);
-    a5_mbar_init(bars->k_full + 1, NROW);
-    a5_mbar_init(bars->pv_ready, NROW);
-    a5_mbar_init(bars->pv_ready + 1, NROW);
-    a5_mbar_init(bars->pv_done, 1);
-    a5_mbar_init(bars->pv_done + 1, 1);
+    tc5_mbar_init(bars->s_full, 1);
+    tc5_mbar_init(bars->s_full + 1, 1);
+    tc5_mbar_init(bars->k_full, NROW);
+    tc5_mbar_init(bars->k_full + 1, NROW);
+    tc5_mbar_init(bars->pv_ready, NROW);
+    tc5_mbar_init(bars->pv_ready + 1, NROW);
+    tc5_mbar_init(bars->pv_done, 1);
+    tc5_mbar_init(bars->pv_done + 1, 1);
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
   }
   if (warp == NROW / 32) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(a5_s32(&bars->tmem)), "n"(TMEM_COLS) : "memory");
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(tc5_s32(&bars->tmem)), "n"(TMEM_COLS) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
   }
 
@@ -319,13 +224,13 @@ __global__ void __launch_bounds__(A5_THREADS, 2) attention_prefill_tcgen05_kerne
       *reinterpret_cast<uint4*>(q_s + (cc >> 3) * (A5_ROWS * 128) + a5_swz(tid, cc & 7)) = v;
     }
     cp_async_wait<0>();
-    a5_proxy_fence();                                    // Q and this thread's part of K and V, visible to the tensor core
+    tc5_proxy_fence();                                    // Q and this thread's part of K and V, visible to the tensor core
   }
-  a5_fence_before();
+  tc5_fence_before();
   __syncthreads();                                       // barriers initialised, tensor memory allocated
-  a5_fence_after();
+  tc5_fence_after();
   const unsigned tmem_base = bars->tmem;
-  const unsigned idesc_s = a5_idesc(A5_BN, false), idesc_pv = a5_idesc(A5_D, true);
+  const unsigned idesc_s = tc5_idesc(A5_BN, false), idesc_pv = tc5_idesc(A5_D, true);
   bool ok = true;
 
   if (tid == NROW) {
@@ -334,43 +239,43 @@ __global__ void __launch_bounds__(A5_THREADS, 2) attention_prefill_tcgen05_kerne
       const unsigned char* kt = k_s + (size_t)(t & 1) * A5_KV_BYTES;
 #pragma unroll
       for (int ks = 0; ks < A5_D / 16; ++ks) {            // 16 values of the head size per step: 32 bytes along a row
-        const unsigned long long ad = a5_desc(a5_s32(q_s) + (ks >> 2) * (A5_ROWS * 128) + (ks & 3) * 32, 16, 1024);
-        const unsigned long long bd = a5_desc(a5_s32(kt) + (ks >> 2) * (A5_BN * 128) + (ks & 3) * 32, 16, 1024);
-        a5_mma(tmem_base + (unsigned)(t & 1) * A5_BN, ad, bd, idesc_s, ks != 0);
+        const unsigned long long ad = tc5_desc(tc5_s32(q_s) + (ks >> 2) * (A5_ROWS * 128) + (ks & 3) * 32, 16, 1024);
+        const unsigned long long bd = tc5_desc(tc5_s32(kt) + (ks >> 2) * (A5_BN * 128) + (ks & 3) * 32, 16, 1024);
+        tc5_mma(tmem_base + (unsigned)(t & 1) * A5_BN, ad, bd, idesc_s, ks != 0);
       }
-      a5_commit(bars->s_full + (t & 1));
+      tc5_commit(bars->s_full + (t & 1));
     };
     auto fail = [&](int code) { ok = false; atomicExch(err, code); };
-    if (!a5_mbar_wait(bars->k_full, 0)) fail(21);
-    a5_fence_after();
+    if (!tc5_mbar_wait(bars->k_full, 0)) fail(21);
+    tc5_fence_after();
     scores(0);
     if (n_tiles > 1) {
-      if (ok && !a5_mbar_wait(bars->k_full + 1, 0)) fail(21);
-      a5_fence_after();
+      if (ok && !tc5_mbar_wait(bars->k_full + 1, 0)) fail(21);
+      tc5_fence_after();
       scores(1);
     }
     for (int t = 0; t < n_tiles; ++t) {
-      if (ok && !a5_mbar_wait(bars->pv_ready + (t & 1), (unsigned)(t >> 1) & 1)) fail(22);
-      a5_fence_after();
+      if (ok && !tc5_mbar_wait(bars->pv_ready + (t & 1), (unsigned)(t >> 1) & 1)) fail(22);
+      tc5_fence_after();
       const unsigned char* vt = v_s + (size_t)(t & 1) * A5_KV_BYTES;
 #pragma unroll
       for (int ks = 0; ks < A5_BN / 16; ++ks) {           // 16 keys per step: 8 columns of P, 2 KB down V
-        const unsigned long long bd = a5_desc(a5_s32(vt) + ks * 2048, A5_BN * 128, 1024);
-        a5_mma_ts(tmem_base + O_COL, tmem_base + (unsigned)(t & 1) * A5_BN + ks * 8, bd, idesc_pv, (t | ks) != 0);
+        const unsigned long long bd = tc5_desc(tc5_s32(vt) + ks * 2048, A5_BN * 128, 1024);
+        tc5_mma_ts(tmem_base + O_COL, tmem_base + (unsigned)(t & 1) * A5_BN + ks * 8, bd, idesc_pv, (t | ks) != 0);
       }
-      a5_commit(bars->pv_done + (t & 1));
+      tc5_commit(bars->pv_done + (t & 1));
       if (t + 2 < n_tiles) {
         // the score buffer holds P(t) until this product is done; K(t + 2) was asked for a tile ago
-        if (ok && !a5_mbar_wait(bars->pv_done + (t & 1), (unsigned)(t >> 1) & 1)) fail(23);
-        if (ok && !a5_mbar_wait(bars->k_full + (t & 1), (unsigned)((t + 2) >> 1) & 1)) fail(21);
-        a5_fence_after();
+        if (ok && !tc5_mbar_wait(bars->pv_done + (t & 1), (unsigned)(t >> 1) & 1)) fail(23);
+        if (ok && !tc5_mbar_wait(bars->k_full + (t & 1), (unsigned)((t + 2) >> 1) & 1)) fail(21);
+        tc5_fence_after();
         scores(t + 2);
       }
     }
   } else if (tid < NROW) {
     // ---- the rows ----
-    a5_mbar_arrive(bars->k_full);                         // K(0) and K(1), after the fence above
-    if (n_tiles > 1) a5_mbar_arrive(bars->k_full + 1);
+    tc5_mbar_arrive(bars->k_full);                         // K(0) and K(1), after the fence above
+    if (n_tiles > 1) tc5_mbar_arrive(bars->k_full + 1);
     const unsigned t_lane = tmem_base + ((unsigned)(warp * 32) << 16);          // this warp's lanes: the score buffers
     const unsigned t_o = t_lane + O_COL;                                         // and the outputs
     // Running softmax with a lazy maximum: the exponentials use m_used, which follows the true maximum
@@ -385,11 +290,11 @@ __global__ void __launch_bounds__(A5_THREADS, 2) attention_prefill_tcgen05_kerne
     for (int tile = 0; tile < n_tiles; ++tile) {
       const int stage = tile & 1;
       const int key0 = key_begin + tile * A5_BN;
-      if (ok && !a5_mbar_wait(bars->s_full + stage, (unsigned)(tile >> 1) & 1)) {
+      if (ok && !tc5_mbar_wait(bars->s_full + stage, (unsigned)(tile >> 1) & 1)) {
         ok = false;
         atomicExch(err, 24);
       }
-      a5_fence_after();
+      tc5_fence_after();
       // K(t + 2) goes where K(t) was, which the scores are done with; V(t) where V(t - 2) was, whose
       // product was done before the scores of this tile were asked for
       const int kb = block_key + tile * A5_BN;             // this warp's block in this tile
@@ -412,10 +317,10 @@ __global__ void __launch_bounds__(A5_THREADS, 2) attention_prefill_tcgen05_kerne
       float s[A5_BN];
       {
         float part[32];
-        a5_ld32(t_lane + stage * A5_BN, part);
+        tc5_ld32(t_lane + stage * A5_BN, part);
 #pragma unroll
         for (int j = 0; j < 32; ++j) s[j] = part[j];
-        a5_ld32(t_lane + stage * A5_BN + 32, part);
+        tc5_ld32(t_lane + stage * A5_BN + 32, part);
 #pragma unroll
         for (int j = 0; j < 32; ++j) s[32 + j] = part[j];
       }
@@ -441,18 +346,18 @@ __global__ void __launch_bounds__(A5_THREADS, 2) attention_prefill_tcgen05_kerne
         if (grow) m_used = mx;
         l *= factor;
         if (tile > 0) {                                    // the rows in tensor memory follow (warp-wide: lanes that keep theirs multiply by 1)
-          if (ok && !a5_mbar_wait(bars->pv_done + (stage ^ 1), (unsigned)((tile - 1) >> 1) & 1)) {   // nobody adds to them meanwhile
+          if (ok && !tc5_mbar_wait(bars->pv_done + (stage ^ 1), (unsigned)((tile - 1) >> 1) & 1)) {   // nobody adds to them meanwhile
             ok = false;
             atomicExch(err, 25);
           }
-          a5_fence_after();
+          tc5_fence_after();
 #pragma unroll
           for (int c = 0; c < A5_D / 32; ++c) {
             float part[32];
-            a5_ld32(t_o + c * 32, part);
+            tc5_ld32(t_o + c * 32, part);
 #pragma unroll
             for (int j = 0; j < 32; ++j) part[j] *= factor;
-            a5_st32(t_o + c * 32, part);
+            tc5_st32(t_o + c * 32, part);
           }
         }
       }
@@ -467,7 +372,7 @@ __global__ void __launch_bounds__(A5_THREADS, 2) attention_prefill_tcgen05_kerne
         w[e] = pack_bf16(p0, p1);
       }
       l += sum;
-      a5_st32u(t_lane + stage * A5_BN, w);                 // P where the scores were: 64 bfloat16 in 32 columns
+      tc5_st32u(t_lane + stage * A5_BN, w);                 // P where the scores were: 64 bfloat16 in 32 columns
       if (blocks) {
         rb0 = rb1;
         rb1 = rb2;
@@ -478,23 +383,23 @@ __global__ void __launch_bounds__(A5_THREADS, 2) attention_prefill_tcgen05_kerne
       }
       // the copies asked for when the tile began have had a softmax's time to land
       cp_async_wait<0>();
-      a5_proxy_fence();
-      a5_fence_before();
-      if (tile + 2 < n_tiles) a5_mbar_arrive(bars->k_full + stage);
-      a5_mbar_arrive(bars->pv_ready + stage);
+      tc5_proxy_fence();
+      tc5_fence_before();
+      if (tile + 2 < n_tiles) tc5_mbar_arrive(bars->k_full + stage);
+      tc5_mbar_arrive(bars->pv_ready + stage);
     }
-    if (ok && !a5_mbar_wait(bars->pv_done + ((n_tiles - 1) & 1), (unsigned)((n_tiles - 1) >> 1) & 1)) {
+    if (ok && !tc5_mbar_wait(bars->pv_done + ((n_tiles - 1) & 1), (unsigned)((n_tiles - 1) >> 1) & 1)) {
       ok = false;
       atomicExch(err, 27);
     }
-    a5_fence_after();
+    tc5_fence_after();
 
     const float inv = live && l > 0.f ? 1.0f / l : 0.f;
     bf16* dst = a.out + (size_t)(q0 + tok) * a.nq * A5_D + (size_t)(kvh * G + head) * A5_D;
 #pragma unroll
     for (int c = 0; c < A5_D / 32; ++c) {                 // tcgen05.ld is warp-wide: dead rows read too, and store nothing
       float part[32];
-      a5_ld32(t_o + c * 32, part);
+      tc5_ld32(t_o + c * 32, part);
       if (!live) continue;
 #pragma unroll
       for (int q = 0; q < 4; ++q) {
@@ -508,10 +413,10 @@ __global__ void __launch_bounds__(A5_THREADS, 2) attention_prefill_tcgen05_kerne
     }
   }
   // every thread gets here (all waits are bounded); then the tensor memory goes back
-  a5_fence_before();
+  tc5_fence_before();
   __syncthreads();
   if (warp == NROW / 32) {
-    a5_fence_after();
+    tc5_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "n"(TMEM_COLS) : "memory");
   }
 }

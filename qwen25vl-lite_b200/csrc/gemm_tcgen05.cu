@@ -23,6 +23,7 @@
 #include <cuda.h>
 
 #include "common.cuh"
+#include "tcgen05.cuh"
 
 enum { T5_STORE = 0, T5_BIAS = 1, T5_F32 = 2, T5_SWIGLU = 3, T5_RESIDUAL = 4 };
 
@@ -39,81 +40,12 @@ template <int BN> struct T5Cfg {
   static constexpr int STAGE_BYTES = T5_A_BYTES + B_BYTES;
 };
 #define T5_THREADS 192
-#define T5_WAIT_LIMIT (1 << 22)
-
-__device__ __forceinline__ unsigned t5_s32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void t5_mbar_init(unsigned long long* bar, int count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(t5_s32(bar)), "r"(count));
-}
-__device__ __forceinline__ void t5_mbar_expect_tx(unsigned long long* bar, unsigned bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(t5_s32(bar)), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void t5_mbar_arrive(unsigned long long* bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(t5_s32(bar)) : "memory");
-}
-__device__ __forceinline__ bool t5_mbar_wait(unsigned long long* bar, unsigned parity) {
-  for (int i = 0; i < T5_WAIT_LIMIT; ++i) {
-    unsigned done;
-    asm volatile(
-        "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
-        : "=r"(done) : "r"(t5_s32(bar)), "r"(parity) : "memory");
-    if (done) return true;
-  }
-  return false;
-}
 
 // 2-D tiled TMA load (no multicast): box at element coordinates (x = K index, y = row).
 __device__ __forceinline__ void t5_tma_load(void* dst, const CUtensorMap* map, int x, int y, unsigned long long* bar) {
   asm volatile(
       "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];\n"
-      ::"r"(t5_s32(dst)), "l"(reinterpret_cast<unsigned long long>(map)), "r"(t5_s32(bar)), "r"(x), "r"(y) : "memory");
-}
-
-// Shared-memory matrix descriptor of a K-major tile with 128-byte swizzle: rows of 128 bytes, groups
-// of 8 rows 1024 bytes apart.
-__device__ __forceinline__ unsigned long long t5_smem_desc(unsigned smem_addr) {
-  unsigned long long d = 0;
-  d |= (unsigned long long)((smem_addr & 0x3FFFF) >> 4);   // start address
-  d |= (unsigned long long)1 << 16;                         // leading byte offset (unused with swizzle)
-  d |= (unsigned long long)(1024 >> 4) << 32;               // stride byte offset: next 8-row group
-  d |= (unsigned long long)1 << 46;                         // descriptor version of sm_100
-  d |= (unsigned long long)2 << 61;                         // 128-byte swizzle
-  return d;
-}
-
-// Instruction descriptor: bf16 x bf16 -> f32, both operands K-major, M 128, N = BN.
-template <int BN> __device__ __forceinline__ unsigned t5_idesc() {
-  return (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(BN >> 3) << 17) | ((unsigned)(T5_BM >> 4) << 24);
-}
-
-__device__ __forceinline__ void t5_mma(unsigned tmem_d, unsigned long long adesc, unsigned long long bdesc, unsigned idesc,
-                                       unsigned accumulate) {
-  asm volatile(
-      "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n"
-      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
-}
-// The mbarrier gets one arrival when every MMA issued so far by this thread has finished.
-__device__ __forceinline__ void t5_commit(unsigned long long* bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(t5_s32(bar)) : "memory");
-}
-__device__ __forceinline__ void t5_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory"); }
-__device__ __forceinline__ void t5_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory"); }
-
-// 32 consecutive float columns of this lane's accumulator row.
-__device__ __forceinline__ void t5_ld32(unsigned taddr, float (&v)[32]) {
-  unsigned r[32];
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,"
-      "%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];\n"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
-        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]),
-        "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]),
-        "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-      : "r"(taddr));
-  asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
-#pragma unroll
-  for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+      ::"r"(tc5_s32(dst)), "l"(reinterpret_cast<unsigned long long>(map)), "r"(tc5_s32(bar)), "r"(x), "r"(y) : "memory");
 }
 
 struct T5Shared {
@@ -140,22 +72,22 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
   pdl_trigger();
   if (threadIdx.x == 0) {
     for (int s = 0; s < T5_STAGES; ++s) {
-      t5_mbar_init(sh->full + s, 1);
-      t5_mbar_init(sh->empty + s, 1);
+      tc5_mbar_init(sh->full + s, 1);
+      tc5_mbar_init(sh->empty + s, 1);
     }
     for (int b = 0; b < 2; ++b) {
-      t5_mbar_init(sh->acc_full + b, 1);
-      t5_mbar_init(sh->acc_empty + b, 4);
+      tc5_mbar_init(sh->acc_full + b, 1);
+      tc5_mbar_init(sh->acc_empty + b, 4);
     }
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
   }
   if (warp == 1) {   // tensor memory: two accumulators of BN columns
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(t5_s32(&sh->tmem_base)), "n"(2 * BN) : "memory");
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(tc5_s32(&sh->tmem_base)), "n"(2 * BN) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
   }
-  t5_fence_before();
+  tc5_fence_before();
   __syncthreads();
-  t5_fence_after();
+  tc5_fence_after();
   const unsigned tmem_base = sh->tmem_base;
   pdl_wait();   // x was written by the kernel before this one; the output may still be read by it
 
@@ -169,11 +101,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
         for (int kb = 0; kb < k_blocks; ++kb, ++it) {
           const int s = it % T5_STAGES;
           if (it >= T5_STAGES && ok) {
-            ok = t5_mbar_wait(sh->empty + s, ((it / T5_STAGES) - 1) & 1);
+            ok = tc5_mbar_wait(sh->empty + s, ((it / T5_STAGES) - 1) & 1);
             if (!ok) atomicExch(err, 11);
           }
           unsigned char* st = stages + (size_t)s * T5_STAGE_BYTES;
-          t5_mbar_expect_tx(sh->full + s, T5_STAGE_BYTES);
+          tc5_mbar_expect_tx(sh->full + s, T5_STAGE_BYTES);
           t5_tma_load(st, &map_x, kb * T5_BK, m0, sh->full + s);
           t5_tma_load(st + T5_A_BYTES, &map_w, kb * T5_BK, n0, sh->full + s);
         }
@@ -183,31 +115,31 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
     // ---- MMA issuer ----
     if (lane == 0) {
       bool ok = true;
-      const unsigned idesc = t5_idesc<BN>();
+      const unsigned idesc = tc5_idesc(BN, false);
       int it = 0, tile_it = 0;
       for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++tile_it) {
         const int b = tile_it & 1;
         if (tile_it >= 2 && ok) {
-          ok = t5_mbar_wait(sh->acc_empty + b, ((tile_it >> 1) - 1) & 1);
+          ok = tc5_mbar_wait(sh->acc_empty + b, ((tile_it >> 1) - 1) & 1);
           if (!ok) atomicExch(err, 12);
         }
-        t5_fence_after();
+        tc5_fence_after();
         const unsigned acc = tmem_base + (unsigned)b * T5_BN;
         for (int kb = 0; kb < k_blocks; ++kb, ++it) {
           const int s = it % T5_STAGES;
           if (ok) {
-            ok = t5_mbar_wait(sh->full + s, (it / T5_STAGES) & 1);
+            ok = tc5_mbar_wait(sh->full + s, (it / T5_STAGES) & 1);
             if (!ok) atomicExch(err, 13);
           }
-          t5_fence_after();
-          const unsigned a_addr = t5_s32(stages + (size_t)s * T5_STAGE_BYTES);
-          const unsigned long long adesc = t5_smem_desc(a_addr), bdesc = t5_smem_desc(a_addr + T5_A_BYTES);
+          tc5_fence_after();
+          const unsigned a_addr = tc5_s32(stages + (size_t)s * T5_STAGE_BYTES);
+          const unsigned long long adesc = tc5_desc(a_addr, 16, 1024), bdesc = tc5_desc(a_addr + T5_A_BYTES, 16, 1024);
 #pragma unroll
           for (int k = 0; k < T5_BK / 16; ++k)   // 32 bytes further along K inside the swizzle atom: + 2 in the address field
-            t5_mma(acc, adesc + 2 * k, bdesc + 2 * k, idesc, (kb | k) != 0);
-          t5_commit(sh->empty + s);
+            tc5_mma(acc, adesc + 2 * k, bdesc + 2 * k, idesc, (kb | k) != 0);
+          tc5_commit(sh->empty + s);
         }
-        t5_commit(sh->acc_full + b);
+        tc5_commit(sh->acc_full + b);
       }
     }
   } else {
@@ -219,16 +151,16 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
       const int m0 = (tile % m_blocks) * T5_BM, n0 = (tile / m_blocks) * T5_BN;
       const int b = tile_it & 1;
       if (ok) {
-        ok = t5_mbar_wait(sh->acc_full + b, (tile_it >> 1) & 1);
+        ok = tc5_mbar_wait(sh->acc_full + b, (tile_it >> 1) & 1);
         if (!ok && lane == 0) atomicExch(err, 14);
       }
-      t5_fence_after();
+      tc5_fence_after();
       const int m = m0 + quarter * 32 + lane;
       const unsigned taddr = tmem_base + ((unsigned)(quarter * 32) << 16) + (unsigned)b * T5_BN;
 #pragma unroll 1
       for (int c = 0; c < T5_BN; c += 32) {
         float v[32];
-        t5_ld32(taddr + c, v);
+        tc5_ld32(taddr + c, v);
         const int n = n0 + c;
         if (m >= M || n >= N) continue;
         if constexpr (EPI == T5_SWIGLU) {
@@ -276,17 +208,17 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
           }
         }
       }
-      t5_fence_before();
+      tc5_fence_before();
       __syncwarp();
-      if (lane == 0) t5_mbar_arrive(sh->acc_empty + b);
+      if (lane == 0) tc5_mbar_arrive(sh->acc_empty + b);
     }
   }
 
   // every warp gets here (all waits are bounded); then the tensor memory goes back
-  t5_fence_before();
+  tc5_fence_before();
   __syncthreads();
   if (warp == 1) {
-    t5_fence_after();
+    tc5_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "n"(2 * BN) : "memory");
   }
 }
