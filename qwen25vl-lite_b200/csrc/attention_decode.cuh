@@ -19,7 +19,7 @@ struct AttnArgs {
   int table_width;
   const int* cu_q;
   const int* q_start_pos;
-  const int* items;   // decode: entry index per blockIdx.x; prefill: (entry, row tile) pairs
+  const int* items;   // decode: entry index per blockIdx.x (null: entry i is token i, one token each); prefill: (entry, row tile) pairs
   int nq, nkv, page_shift, window;
   float scale_log2;
   int n_splits;
@@ -322,7 +322,8 @@ struct DecodeUnit {
   static constexpr int HALF = D / 2;
   static constexpr int TILES_OFF = 1024;
   static constexpr int KV_BYTES = WARPS * STAGES * 2 * TILE;
-  static constexpr int MERGE_BYTES = (WARPS * 16 * 2 + WARPS * 16 * D) * (int)sizeof(float);
+  static constexpr int SLAB_P = D + 8;                 // floats per row of a warp's output in the merge: the rows of a quad's lanes fall into different banks
+  static constexpr int MERGE_BYTES = (WARPS * 16 * 2 + WARPS * 16 * SLAB_P + 16 * 2) * (int)sizeof(float);
   static constexpr int SMEM = TILES_OFF + (KV_BYTES > MERGE_BYTES ? KV_BYTES : MERGE_BYTES);
   static_assert(D % 32 == 0, "the rotation pairs channel j with j + D/2 inside one thread");
   static_assert(HALF * 8 + 16 <= TILES_OFF, "the angles and the flag fit before the tiles");
@@ -331,8 +332,8 @@ struct DecodeUnit {
 
   __device__ static __forceinline__ Range range(const AttnArgs& a, int item, int split) {
     Range R;
-    R.seq = a.items[item];
-    R.token = a.cu_q[R.seq];
+    R.seq = a.items ? a.items[item] : item;              // without the list: one trip to memory less
+    R.token = a.items ? a.cu_q[R.seq] : item;
     R.p = a.q_start_pos[R.seq];
     R.lo = a.window > 0 ? max(0, R.p - a.window + 1) : 0;
     R.first_tile_key = R.lo & ~(BN - 1);
@@ -349,7 +350,9 @@ struct DecodeUnit {
   // (or operation) that produces q has finished.
   static constexpr int AHEAD = STAGES > 1 ? STAGES - 1 : 1;
   __device__ static __forceinline__ void prefetch(const AttnArgs& a, int item, int kvh, int split, unsigned char* smem, int tid) {
-    const Range R = range(a, item, split);
+    prefetch(a, range(a, item, split), kvh, smem, tid);
+  }
+  __device__ static __forceinline__ void prefetch(const AttnArgs& a, const Range& R, int kvh, unsigned char* smem, int tid) {
     const int warp = tid >> 5, lane = tid & 31;
     unsigned char* wbuf = smem + TILES_OFF + (size_t)warp * STAGES * 2 * TILE;
     if (BN == 16 && a.page_shift >= 4) {               // one page per tile: all look-ups first, then all copies
@@ -381,9 +384,12 @@ struct DecodeUnit {
     }
   }
 
+  // prefetch_here: the caller has not called prefetch(); the first tiles are asked for here, after the
+  // loads of q and of the angles are on their way, so that those do not queue behind the trip to
+  // the block table.
   template <typename Sync>
   __device__ static __forceinline__ void run(const AttnArgs& a, const RopeArgs& r, int item, int kvh, int split,
-                                             unsigned char* smem, int tid, Sync sync) {
+                                             unsigned char* smem, int tid, Sync sync, bool prefetch_here = false) {
     constexpr int NT = WARPS * 32;
     const Range R = range(a, item, split);
     const int warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
@@ -400,9 +406,32 @@ struct DecodeUnit {
     const bf16* qbase = a.qkv + (size_t)token * a.qkv_stride + (size_t)kvh * G * D;
     load_q<D>(qf, [&](int row) { return row < G ? qbase + (size_t)row * D : (const bf16*)nullptr; });
     // the token has D/2 angles; from the step's table, or computed here once for the whole unit
+    // the unit that holds the last tile patches the token's own key and value into it: their raw values and
+    // the slot, asked for now, are there when the loop gets to that tile
+    constexpr int KI = (HALF + 31) / 32, VI = (D + 31) / 32;
+    const bool owns_last = R.t_end == R.n_tiles && R.t_begin < R.t_end;
+    const bf16* kv_new = a.qkv + (size_t)token * a.qkv_stride + (size_t)(a.nq + kvh) * D;
+    const unsigned short* kraw = reinterpret_cast<const unsigned short*>(kv_new);
+    const unsigned short* vraw = reinterpret_cast<const unsigned short*>(kv_new + (size_t)a.nkv * D);
+    unsigned short k1_new[KI], k2_new[KI], v_newv[VI];
+    int slot_new = -1;
+    if (owns_last) {
+      slot_new = r.kv_slot[token];
+#pragma unroll
+      for (int i = 0; i < KI; ++i) {
+        const int j = lane + 32 * i;
+        k1_new[i] = j < HALF ? __ldcg(kraw + j) : (unsigned short)0;
+        k2_new[i] = j < HALF ? __ldcg(kraw + j + HALF) : (unsigned short)0;
+      }
+#pragma unroll
+      for (int i = 0; i < VI; ++i) v_newv[i] = lane + 32 * i < D ? __ldcg(vraw + lane + 32 * i) : (unsigned short)0;
+    }
+    float2 angle_of_tid = make_float2(1.f, 0.f);
+    if (r.angles && tid < HALF) angle_of_tid = __ldg(r.angles + (size_t)token * HALF + tid);
+    if (prefetch_here) prefetch(a, R, kvh, smem, tid);
     for (int j = tid; j < HALF; j += NT) {
       if (r.angles) {
-        cs[j] = r.angles[(size_t)token * HALF + j];
+        cs[j] = j == tid ? angle_of_tid : r.angles[(size_t)token * HALF + j];
       } else {
         // all five loads are independent of one another, so they cost one memory latency, not two
         const int ax = r.axis[j];
@@ -468,31 +497,35 @@ struct DecodeUnit {
       unsigned char* cb = wbuf + (size_t)stage * 2 * TILE;
       if (tile == R.n_tiles - 1) {
         // the token's own key and value: rotate k, patch both into the tile, store both to the pages
-        const bf16* kv_new = a.qkv + (size_t)token * a.qkv_stride + (size_t)(a.nq + kvh) * D;
-        const bf16* v_new = kv_new + (size_t)a.nkv * D;
-        const int slot = r.kv_slot[token];
+        const int slot = slot_new;
         const size_t page_off = slot >= 0 ? ((((size_t)(slot >> a.page_shift) * a.nkv + kvh) << a.page_shift)
                                              + (slot & ((1 << a.page_shift) - 1))) * D : 0;
         bf16* krow = reinterpret_cast<bf16*>(cb + (p - key0) * P);
         bf16* vrow = reinterpret_cast<bf16*>(cb + TILE + (p - key0) * P);
-        const unsigned short* kraw = reinterpret_cast<const unsigned short*>(kv_new);
-        const unsigned short* vraw = reinterpret_cast<const unsigned short*>(v_new);
-        for (int j = lane; j < HALF; j += 32) {
-          const float cj = cs[j].x, sn = cs[j].y;
-          const float x1 = __bfloat162float(__ushort_as_bfloat16(__ldcg(kraw + j)));
-          const float x2 = __bfloat162float(__ushort_as_bfloat16(__ldcg(kraw + j + HALF)));
-          const bf16 y1 = __float2bfloat16_rn(x1 * cj - x2 * sn), y2 = __float2bfloat16_rn(x2 * cj + x1 * sn);
-          krow[j] = y1;
-          krow[j + HALF] = y2;
-          if (slot >= 0) {
-            r.kpages_w[page_off + j] = y1;
-            r.kpages_w[page_off + j + HALF] = y2;
+#pragma unroll
+        for (int i = 0; i < KI; ++i) {
+          const int j = lane + 32 * i;
+          if (j < HALF) {
+            const float cj = cs[j].x, sn = cs[j].y;
+            const float x1 = __bfloat162float(__ushort_as_bfloat16(k1_new[i]));
+            const float x2 = __bfloat162float(__ushort_as_bfloat16(k2_new[i]));
+            const bf16 y1 = __float2bfloat16_rn(x1 * cj - x2 * sn), y2 = __float2bfloat16_rn(x2 * cj + x1 * sn);
+            krow[j] = y1;
+            krow[j + HALF] = y2;
+            if (slot >= 0) {
+              r.kpages_w[page_off + j] = y1;
+              r.kpages_w[page_off + j + HALF] = y2;
+            }
           }
         }
-        for (int c = lane; c < D; c += 32) {
-          const bf16 v = __ushort_as_bfloat16(__ldcg(vraw + c));
-          vrow[c] = v;
-          if (slot >= 0) r.vpages_w[page_off + c] = v;
+#pragma unroll
+        for (int i = 0; i < VI; ++i) {
+          const int c = lane + 32 * i;
+          if (c < D) {
+            const bf16 v = __ushort_as_bfloat16(v_newv[i]);
+            vrow[c] = v;
+            if (slot >= 0) r.vpages_w[page_off + c] = v;
+          }
         }
         __syncwarp();
       }
@@ -513,7 +546,7 @@ struct DecodeUnit {
     // merge the warps of the unit, keep the result in shared memory
     sync();
     float* ml = reinterpret_cast<float*>(smem + TILES_OFF);     // [WARPS][16 rows][2]
-    float* slab = ml + WARPS * 16 * 2;                          // [WARPS][16 rows][D]
+    float* slab = ml + WARPS * 16 * 2;                          // [WARPS][16 rows][SLAB_P]
     if (t == 0) {
       ml[(warp * 16 + g) * 2] = m[0];
       ml[(warp * 16 + g) * 2 + 1] = l[0];
@@ -531,30 +564,45 @@ struct DecodeUnit {
     }
 #pragma unroll
     for (int nb = 0; nb < D / 8; ++nb) {
-      float* r0 = slab + ((size_t)warp * 16 + g) * D + nb * 8 + 2 * t;
-      float* r1 = slab + ((size_t)warp * 16 + g + 8) * D + nb * 8 + 2 * t;
+      float* r0 = slab + ((size_t)warp * 16 + g) * SLAB_P + nb * 8 + 2 * t;
+      float* r1 = slab + ((size_t)warp * 16 + g + 8) * SLAB_P + nb * 8 + 2 * t;
       r0[0] = o[nb][0] * f[0];
       r0[1] = o[nb][1] * f[0];
       r1[0] = o[nb][2] * f[1];
       r1[1] = o[nb][3] * f[1];
     }
-    sync();
-    for (int idx = tid; idx < G * D; idx += NT) {
-      const int row = idx / D, c = idx - row * D;
+    // the rows' maxima and sums over the warps, once per row
+    float* rowstat = slab + WARPS * 16 * SLAB_P;                // [16 rows][2]
+    if (tid < 16) {
       float mm = -INFINITY;
-      for (int w = 0; w < WARPS; ++w) mm = fmaxf(mm, ml[(w * 16 + row) * 2]);
-      float lsum = 0.f, acc = 0.f;
+      for (int w = 0; w < WARPS; ++w) mm = fmaxf(mm, ml[(w * 16 + tid) * 2]);
+      float lsum = 0.f;
       for (int w = 0; w < WARPS; ++w) {
-        const float mw = ml[(w * 16 + row) * 2];
-        lsum += mw == -INFINITY ? 0.f : ml[(w * 16 + row) * 2 + 1] * exp2f(mw - mm);
-        acc += slab[((size_t)w * 16 + row) * D + c];
+        const float mw = ml[(w * 16 + tid) * 2];
+        lsum += mw == -INFINITY ? 0.f : ml[(w * 16 + tid) * 2 + 1] * exp2f(mw - mm);
       }
+      rowstat[2 * tid] = mm;
+      rowstat[2 * tid + 1] = lsum;
+    }
+    sync();
+    for (int idx = tid; idx < G * (D / 4); idx += NT) {         // four channels of a row
+      const int row = idx / (D / 4), c = (idx - row * (D / 4)) * 4;
+      float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+      for (int w = 0; w < WARPS; ++w) {
+        const float4 v = *reinterpret_cast<const float4*>(slab + ((size_t)w * 16 + row) * SLAB_P + c);
+        acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+      }
+      const float mm = rowstat[2 * row], lsum = rowstat[2 * row + 1];
       const int head = kvh * G + row;
       if (a.n_splits == 1) {
-        a.out[(size_t)token * a.nq * D + (size_t)head * D + c] = __float2bfloat16_rn(acc / lsum);
+        const float inv = 1.0f / lsum;
+        uint2 packed;
+        packed.x = pack_bf16(acc.x * inv, acc.y * inv);
+        packed.y = pack_bf16(acc.z * inv, acc.w * inv);
+        *reinterpret_cast<uint2*>(a.out + (size_t)token * a.nq * D + (size_t)head * D + c) = packed;
       } else {
         const size_t pi = ((size_t)item * a.nq + head) * a.n_splits + split;
-        a.part_o[pi * D + c] = acc;
+        *reinterpret_cast<float4*>(a.part_o + pi * D + c) = acc;
         if (c == 0) {
           a.part_ml[pi * 2] = mm;
           a.part_ml[pi * 2 + 1] = lsum;

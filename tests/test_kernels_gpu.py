@@ -657,7 +657,8 @@ def test_attention_decode_fused(nq, nkv, d, section, page_size, window, splits, 
         kernels.attention_decode_fused(qkv, out, c["k_pages"], c["v_pages"], c["table"], c["cu"], c["start"],
                                        dev(np.arange(n, dtype=np.int32)), nq, nkv, d, page_size, window or 0, d ** -0.5,
                                        splits, dev(positions.astype(np.int32)), rope.inv_freq, rope.axis,
-                                       dev(np.asarray(slots, np.int32)), scratch if splits > 1 else None, max_keys=max_keys)
+                                       dev(np.asarray(slots, np.int32)), scratch if splits > 1 else None, max_keys=max_keys,
+                                       dense=max_keys > 0)    # the items are 0 .. n-1 here: with and without the list
     assert torch.equal(qkv, qkv_before)                          # the projections are left as they were
     ref = attention_oracle(dense, window)
     assert np.abs(f64(out) - ref).max() < 4e-2
