@@ -391,43 +391,41 @@ struct DecodeUnit {
   __device__ static __forceinline__ void run(const AttnArgs& a, const RopeArgs& r, int item, int kvh, int split,
                                              unsigned char* smem, int tid, Sync sync, bool prefetch_here = false) {
     constexpr int NT = WARPS * 32;
-    const Range R = range(a, item, split);
     const int warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
     const int G = a.nq / a.nkv;
-    const int token = R.token, p = R.p, lo = R.lo;
-    float2* cs = reinterpret_cast<float2*>(smem);
-    int* is_last = reinterpret_cast<int*>(smem + HALF * 8);
-    unsigned char* wbuf = smem + TILES_OFF + (size_t)warp * STAGES * 2 * TILE;
-    int tile = R.t_begin + warp;
-
-    // q of the group's heads, rotated in registers: channels j and j + D/2 sit in k-steps ks and
+    // Everything that needs only the token is asked for before the entry's position is (the position
+    // decides the key range, the block-table look-ups follow it): one trip to memory, not three.
+    const int token = a.items ? a.cu_q[a.items[item]] : item;
+    // q of the group's heads, rotated in registers later: channels j and j + D/2 sit in k-steps ks and
     // ks + D/32 of the same thread
     unsigned qf[D / 16][4];
     const bf16* qbase = a.qkv + (size_t)token * a.qkv_stride + (size_t)kvh * G * D;
     load_q<D>(qf, [&](int row) { return row < G ? qbase + (size_t)row * D : (const bf16*)nullptr; });
-    // the token has D/2 angles; from the step's table, or computed here once for the whole unit
-    // the unit that holds the last tile patches the token's own key and value into it: their raw values and
-    // the slot, asked for now, are there when the loop gets to that tile
+    // the token's own key, value and slot: the unit that holds the last tile patches them into it
     constexpr int KI = (HALF + 31) / 32, VI = (D + 31) / 32;
-    const bool owns_last = R.t_end == R.n_tiles && R.t_begin < R.t_end;
     const bf16* kv_new = a.qkv + (size_t)token * a.qkv_stride + (size_t)(a.nq + kvh) * D;
     const unsigned short* kraw = reinterpret_cast<const unsigned short*>(kv_new);
     const unsigned short* vraw = reinterpret_cast<const unsigned short*>(kv_new + (size_t)a.nkv * D);
     unsigned short k1_new[KI], k2_new[KI], v_newv[VI];
-    int slot_new = -1;
-    if (owns_last) {
-      slot_new = r.kv_slot[token];
+    const int slot_new = r.kv_slot[token];
 #pragma unroll
-      for (int i = 0; i < KI; ++i) {
-        const int j = lane + 32 * i;
-        k1_new[i] = j < HALF ? __ldcg(kraw + j) : (unsigned short)0;
-        k2_new[i] = j < HALF ? __ldcg(kraw + j + HALF) : (unsigned short)0;
-      }
-#pragma unroll
-      for (int i = 0; i < VI; ++i) v_newv[i] = lane + 32 * i < D ? __ldcg(vraw + lane + 32 * i) : (unsigned short)0;
+    for (int i = 0; i < KI; ++i) {
+      const int j = lane + 32 * i;
+      k1_new[i] = j < HALF ? __ldcg(kraw + j) : (unsigned short)0;
+      k2_new[i] = j < HALF ? __ldcg(kraw + j + HALF) : (unsigned short)0;
     }
+#pragma unroll
+    for (int i = 0; i < VI; ++i) v_newv[i] = lane + 32 * i < D ? __ldcg(vraw + lane + 32 * i) : (unsigned short)0;
+    // the token has D/2 angles; from the step's table, or computed below once for the whole unit
     float2 angle_of_tid = make_float2(1.f, 0.f);
     if (r.angles && tid < HALF) angle_of_tid = __ldg(r.angles + (size_t)token * HALF + tid);
+
+    const Range R = range(a, item, split);
+    const int p = R.p, lo = R.lo;
+    float2* cs = reinterpret_cast<float2*>(smem);
+    int* is_last = reinterpret_cast<int*>(smem + HALF * 8);
+    unsigned char* wbuf = smem + TILES_OFF + (size_t)warp * STAGES * 2 * TILE;
+    int tile = R.t_begin + warp;
     if (prefetch_here) prefetch(a, R, kvh, smem, tid);
     for (int j = tid; j < HALF; j += NT) {
       if (r.angles) {
