@@ -276,11 +276,10 @@ __global__ void rope_angles_kernel(const int* __restrict__ positions, int n_toke
   out[idx] = make_float2(c, sn);
 }
 
-// The fused decode kernel in two shapes (warps of a CTA, keys of a warp's tile, stages of tiles per
-// warp), both of 8 warps.  At most 8 tiles of 32 keys per CTA (the launch is a chain of latencies):
-// a tile per warp, all asked for at once, no loop.  More keys per CTA (a loop of many tiles per
-// warp, which should keep the memory busy): tiles of 16 = one page look-up per tile, made an
-// iteration ahead, 3 stages (210 KB of shared memory at head size 128).
+// The fused decode kernel: 8 warps, a warp's tile is 16 keys = one page look-up, made an iteration
+// ahead, 3 stages of tiles per warp (210 KB of shared memory at head size 128).  A shape without a
+// loop (a 32-key tile per warp, all asked for at once) was no faster where it applies (at most 256
+// keys per CTA) and is not kept.
 template <int D, int WARPS, int BN, int STAGES>
 __global__ void __launch_bounds__(WARPS * 32) attention_decode_fused_kernel(AttnArgs a, RopeArgs r) {
   pdl_trigger();
@@ -302,10 +301,7 @@ static int launch_decode_fused_shape(const AttnArgs& a, const RopeArgs& r, int n
 }
 
 template <int D>
-static int launch_decode_fused(const AttnArgs& a, const RopeArgs& r, int n_items, int max_keys, cudaStream_t s) {
-  // tiles of 32 keys that the longest entry gives a CTA (the kernel's own split of the tiles); unknown: many
-  const int tiles = (max_keys + 31) / 32 + 1, per_cta = (tiles + a.n_splits - 1) / a.n_splits;
-  if (max_keys > 0 && per_cta <= 8) return launch_decode_fused_shape<D, 8, 32, 1>(a, r, n_items, s);
+static int launch_decode_fused(const AttnArgs& a, const RopeArgs& r, int n_items, cudaStream_t s) {
   return launch_decode_fused_shape<D, 8, 16, 3>(a, r, n_items, s);
 }
 
@@ -387,8 +383,7 @@ Q25_EXPORT int q25_attention_prefill_bf16(const void* qkv, int qkv_stride, void*
 // Fused decode step of attention: rotates q and the new k by the 3-axis rotary encoding, stores the new
 // k and v at kv_slot, attends, merges the n_splits key ranges (scratch as for q25_attention_decode_bf16,
 // counters: n_items * nkv ints that are zero and stay zero).  qkv holds the un-rotated projections
-// and is not modified.  Head sizes 32, 64, 96, 128; groups of at most 16.  max_keys: how many keys the longest
-// entry sees (0: unknown); it only chooses the shape of the kernel.  dense: the items are 0 .. n_items - 1 and every
+// and is not modified.  Head sizes 32, 64, 96, 128; groups of at most 16.  dense: the items are 0 .. n_items - 1 and every
 // entry has one token (token i belongs to entry i): the kernel then reads neither items nor cu_q.
 Q25_EXPORT int q25_attention_decode_fused_bf16(const void* qkv, int qkv_stride, void* out, void* kp, void* vp,
                                                const int* bt, int tw, const int* cu_q, const int* q_start,
@@ -396,7 +391,7 @@ Q25_EXPORT int q25_attention_decode_fused_bf16(const void* qkv, int qkv_stride, 
                                                int window, float scale, int n_splits, const int* positions,
                                                int n_tokens, const float* inv_freq, const int* axis,
                                                const int* kv_slot, float* scratch, int* counters, const void* angles,
-                                               int max_keys, int dense, void* stream) {
+                                               int dense, void* stream) {
   if (n_items <= 0) return 0;
   AttnArgs a;
   int e = fill_args(a, qkv, qkv_stride, out, kp, vp, bt, tw, cu_q, q_start, items, nq, nkv, page_size, window, scale);
@@ -414,10 +409,10 @@ Q25_EXPORT int q25_attention_decode_fused_bf16(const void* qkv, int qkv_stride, 
   r.angles = (const float2*)angles;
   cudaStream_t s = (cudaStream_t)stream;
   switch (d) {
-    case 32: return launch_decode_fused<32>(a, r, n_items, max_keys, s);
-    case 64: return launch_decode_fused<64>(a, r, n_items, max_keys, s);
-    case 96: return launch_decode_fused<96>(a, r, n_items, max_keys, s);
-    case 128: return launch_decode_fused<128>(a, r, n_items, max_keys, s);
+    case 32: return launch_decode_fused<32>(a, r, n_items, s);
+    case 64: return launch_decode_fused<64>(a, r, n_items, s);
+    case 96: return launch_decode_fused<96>(a, r, n_items, s);
+    case 128: return launch_decode_fused<128>(a, r, n_items, s);
     default: return (int)cudaErrorInvalidValue;
   }
 }

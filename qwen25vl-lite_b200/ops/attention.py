@@ -70,7 +70,7 @@ def attend(ctx, qkv, kv, position, nq: int, nkv: int, head_dim: int, window, sca
         scratch = _scratch_floats(ctx.n_seqs * nq * splits * (head_dim + 2), qkv.device) if splits > 1 else None
         kernels.attention_decode_fused(qkv, out, kv.k_pages, kv.v_pages, kv.block_table, ctx.cu_q, ctx.q_start_pos,
                                        ctx.decode_items, nq, nkv, head_dim, kv.page_size, window, scale, splits,
-                                       ctx.positions, inv_freq, axis, kv.kv_slot, scratch, angles, max_keys=visible,
+                                       ctx.positions, inv_freq, axis, kv.kv_slot, scratch, angles,
                                        dense=True)          # every entry of the step is one token, in order
         return out
     position.rotate_and_store(ctx, qkv, nq, nkv, head_dim, kv if store else None)

@@ -222,14 +222,13 @@ def attention_decode_fused(qkv: torch.Tensor, out: torch.Tensor, k_pages: torch.
                            nq: int, nkv: int, head_dim: int, page_size: int, window: int, scale: float, n_splits: int,
                            positions: torch.Tensor, inv_freq: torch.Tensor, axis: torch.Tensor,
                            kv_slot: torch.Tensor, scratch: Optional[torch.Tensor] = None,
-                           angles: Optional[torch.Tensor] = None, max_keys: int = 0, dense: bool = False) -> None:
+                           angles: Optional[torch.Tensor] = None, dense: bool = False) -> None:
     """One kernel for a step of one-token entries: 3-axis rotary encoding of q and the new k
     (``positions`` int32 [3, N], ``inv_freq`` float32 [D/2], ``axis`` int32 [D/2]), the write of
     the new k and v at ``kv_slot``, attention, and the merge of the ``n_splits`` key ranges
     (through ``scratch`` as for ``attention_decode``; the CTA that finishes last merges).
     ``qkv`` is read as projected and left unchanged.  ``angles``: the step's table from
-    ``rope_angles`` (the kernel computes the angles itself without it).  ``max_keys``: how many keys
-    the longest entry sees (0: unknown); with at most 8 tiles of 32 per split a kernel without a loop runs.
+    ``rope_angles`` (the kernel computes the angles itself without it).
     ``dense``: ``items`` is 0 .. n-1 and every entry has exactly one token (the kernel then skips two look-ups)."""
     n_items = items.shape[0]
     if angles is not None and (angles.dtype != torch.float32 or tuple(angles.shape) != (positions.shape[1], head_dim // 2, 2)
@@ -258,18 +257,18 @@ def attention_decode_fused(qkv: torch.Tensor, out: torch.Tensor, k_pages: torch.
         keep = (qkv, out, k_pages, v_pages, block_table, cu_q, q_start_pos, items, positions, inv_freq, axis, kv_slot,
                 scratch, counters, angles)
         args = (qkv, out, k_pages, v_pages, block_table, cu_q, q_start_pos, items, nq, nkv, head_dim, page_size, window,
-                scale, n_splits, positions, inv_freq, axis, kv_slot, scratch, angles, max_keys, dense)
+                scale, n_splits, positions, inv_freq, axis, kv_slot, scratch, angles, dense)
         _chain.append((desc, keep, lambda: attention_decode_fused(*args)))
         if len(_chain) == CHAIN_MAX_OPS:
             chain_flush()
         return
     _check(_fn("q25_attention_decode_fused_bf16",
-               [_P, _I, _P, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _I, _P, _I, _P, _P, _P, _P, _P, _P, _I, _I, _P])(
+               [_P, _I, _P, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _I, _P, _I, _P, _P, _P, _P, _P, _P, _I, _P])(
         qkv.data_ptr(), qkv.stride(0), out.data_ptr(), k_pages.data_ptr(), v_pages.data_ptr(), block_table.data_ptr(),
         block_table.shape[1], cu_q.data_ptr(), q_start_pos.data_ptr(), items.data_ptr(), items.shape[0], nq, nkv,
         head_dim, page_size, int(window or 0), float(scale), int(n_splits), positions.data_ptr(), positions.shape[1],
         inv_freq.data_ptr(), axis.data_ptr(), kv_slot.data_ptr(), _ptr(scratch),
-        _split_counters(qkv.device, n_items * nkv).data_ptr(), _ptr(angles), int(max_keys), int(bool(dense)),
+        _split_counters(qkv.device, n_items * nkv).data_ptr(), _ptr(angles), int(bool(dense)),
         _stream()), "attention_decode_fused")
 
 

@@ -609,15 +609,15 @@ def test_gemm_skinny_norm_needs_resident_rows():
                                  torch.empty((16, 32), dtype=torch.bfloat16, device="cuda"), kernels.SKINNY_STORE)
 
 
-@pytest.mark.parametrize("max_keys", [0, 10 ** 6])
+@pytest.mark.parametrize("dense", [False, True])
 @pytest.mark.parametrize("splits", [1, 2, 5, 19])
 @pytest.mark.parametrize("nq,nkv,d,section,page_size,window", [
     (16, 2, 128, (16, 24, 24), 16, None), (6, 1, 32, (4, 6, 6), 8, None), (8, 2, 64, (8, 12, 12), 16, 70),
     (12, 4, 96, (16, 16, 16), 4, None), (3, 3, 64, (10, 11, 11), 32, 33)])
-def test_attention_decode_fused(nq, nkv, d, section, page_size, window, splits, max_keys):
+def test_attention_decode_fused(nq, nkv, d, section, page_size, window, splits, dense):
     """The one-kernel decode step of attention: rotary encoding of q and the new k inside the
-    kernel, the new k and v written to their page slot, merge of the splits; in both shapes of the
-    kernel (the one for a tile or two per warp, and the one for long loops that ``max_keys`` asks for)."""
+    kernel, the new k and v written to their page slot, merge of the splits; with the list of items
+    and without it (``dense``: the items are 0 .. n-1 here)."""
     from qwen25vl_lite.ops import kernels
     from qwen25vl_lite.parts.position import MRope
     rng = np.random.default_rng(12)
@@ -657,8 +657,7 @@ def test_attention_decode_fused(nq, nkv, d, section, page_size, window, splits, 
         kernels.attention_decode_fused(qkv, out, c["k_pages"], c["v_pages"], c["table"], c["cu"], c["start"],
                                        dev(np.arange(n, dtype=np.int32)), nq, nkv, d, page_size, window or 0, d ** -0.5,
                                        splits, dev(positions.astype(np.int32)), rope.inv_freq, rope.axis,
-                                       dev(np.asarray(slots, np.int32)), scratch if splits > 1 else None, max_keys=max_keys,
-                                       dense=max_keys > 0)    # the items are 0 .. n-1 here: with and without the list
+                                       dev(np.asarray(slots, np.int32)), scratch if splits > 1 else None, dense=dense)
     assert torch.equal(qkv, qkv_before)                          # the projections are left as they were
     ref = attention_oracle(dense, window)
     assert np.abs(f64(out) - ref).max() < 4e-2
