@@ -3,7 +3,6 @@ without a change to the engine's files: a mixer with state of its own (its model
 twice and lets one stop read another stop's cache), a feed-forward that routes tokens to experts,
 and a position encoding with one axis and another pairing of channels."""
 
-import json
 import os
 
 import numpy as np
