@@ -146,6 +146,7 @@ class LLMEngine:
         self.stats_ = EngineStats()
         self._next_id = 0
         self._prepared = None                 # the next decode step, packed ahead (see ``step``)
+        self._launched = None                 # the next decode step, already on the device: (logits, its requests)
 
     # ---- requests ----------------------------------------------------------------------
     def add_request(self, prompt_token_ids: Seq[int], sampling_params: Optional[SamplingParams] = None, *,
@@ -274,12 +275,19 @@ class LLMEngine:
 
         While the device runs a step whose requests will all decode one more token, the host
         already packs the next step (pages, block tables, positions: everything but the token
-        ids), so that between two decode steps only the sampled ids have to travel."""
+        ids), so that between two decode steps only the sampled ids have to travel.  When those ids
+        end no request, that next step is even launched before this call does its bookkeeping and
+        returns (``_launched``): the next call starts at its sampling."""
         t0 = time.perf_counter()
         prepared, self._prepared = self._prepared, None
+        launched, self._launched = self._launched, None
         entries, samplers = [], []
         decoded = 0
-        if prepared is not None and not self.waiting and [s.seq_id for s in self.running] == prepared[1] \
+        if launched is not None:
+            logits, samplers = launched                    # the step is running already
+            decoded = len(samplers)
+            self.stats_.decode_tokens += decoded
+        elif prepared is not None and not self.waiting and [s.seq_id for s in self.running] == prepared[1] \
                 and all(s.pending == 1 for s in self.running):
             samplers = list(self.running)
             decoded = len(samplers)
@@ -310,10 +318,15 @@ class LLMEngine:
                 pending = self.sampler.sample_async(*args)
                 self._prepared = self._prepare_next(samplers)          # host work under the device's step
                 tokens = self.sampler.collect(pending)
+                if self._prepared is not None and not any(self._ends(seq, int(tok)) for seq, tok in zip(samplers, tokens)):
+                    # nobody ends: the next step goes to the device now, the bookkeeping follows under it
+                    next_logits = self.runner.launch_prepared(self._prepared[0], [int(tok) for tok in tokens])
+                    self._launched, self._prepared = (next_logits, samplers), None
             else:
                 tokens = self.sampler.sample(*args)
             for seq, token in zip(samplers, tokens):
-                self._accept(seq, int(token), done)
+                if seq.status == "running":                # a request aborted while its step ran draws nothing
+                    self._accept(seq, int(token), done)
             if done:
                 self._prepared = None
         self.stats_.steps += 1
@@ -343,6 +356,13 @@ class LLMEngine:
         except OutOfPages:
             return None
         return runner.prepare_decode([seq.request for seq in self.running]), [s.seq_id for s in self.running]
+
+    def _ends(self, seq: Sequence, token: int) -> bool:
+        """Whether this token, drawn now, ends the request by what it is (ends by length are known
+        before the token is drawn and keep ``_prepare_next`` from preparing anything)."""
+        p = seq.params
+        return (self.eos_token_id is not None and token == self.eos_token_id and not p.ignore_eos) \
+            or token in (p.stop_token_ids or ())
 
     def _accept(self, seq: Sequence, token: int, done: List[RequestOutput]) -> None:
         seq.output_token_ids.append(token)

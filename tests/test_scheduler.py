@@ -287,3 +287,33 @@ def test_prepared_decode_steps_change_nothing():
         assert outs[ids[i]].output_token_ids == expected(prompts[i], lengths[i])
     assert outs[late].output_token_ids == expected(prompts[3], lengths[3])
     runner.cache.check([])
+
+
+def test_next_step_is_launched_before_the_bookkeeping_and_survives_an_abort():
+    """When the drawn tokens end no request, the engine hands the packed next step to the device
+    inside the same ``step`` call (the next call starts at its sampling).  A request aborted while
+    such a step runs draws nothing from it; the others go on as if nothing had happened."""
+    prompts = [[5, 6, 7], list(range(20, 31)), [9] * 6]
+    ecfg = EngineConfig(num_blocks=64, block_size=4, max_num_seqs=3)
+    runner = PreparingRunner(64, 4, ecfg.max_num_seqs)
+    engine = LLMEngine(runner, AsyncSampler(), ecfg, eos_token_id=None)
+    runner._requests = _LiveView(engine)
+    ids = [engine.add_request(p, SamplingParams(max_tokens=12, ignore_eos=True)) for p in prompts]
+    outs = {}
+    early = 0
+    for step in range(200):
+        before = runner.launched
+        for o in engine.step():
+            outs[o.seq_id] = o
+        if engine._launched is not None:
+            early += 1
+            assert runner.launched == before + 1 or runner.launched == before + 2     # this call's own launch, and the next one's
+        if step == 5:
+            assert engine._launched is not None and engine.abort(ids[1])               # its step is on the device
+        if not engine.has_work():
+            break
+    assert early >= 5
+    assert ids[1] not in outs
+    for i in (0, 2):
+        assert outs[ids[i]].output_token_ids == expected(prompts[i], 12)
+    runner.cache.check([])
