@@ -317,3 +317,48 @@ def test_next_step_is_launched_before_the_bookkeeping_and_survives_an_abort():
     for i in (0, 2):
         assert outs[ids[i]].output_token_ids == expected(prompts[i], 12)
     runner.cache.check([])
+
+
+@pytest.mark.parametrize("seed", range(8))
+def test_random_arrivals_stops_and_aborts_with_steps_packed_and_launched_ahead(seed):
+    """Requests of random lengths arrive at random steps, some end by a stop token, some are
+    aborted, the pool is small enough for preemptions: every finished request has exactly the
+    tokens of its own history (the fake step function derives each token from all before it), no
+    page is lost, and the steps that are packed or launched ahead are really used."""
+    import random
+    rng = random.Random(seed)
+    ecfg = EngineConfig(num_blocks=40, block_size=4, max_num_seqs=4, max_num_batched_tokens=16)
+    runner = PreparingRunner(40, 4, ecfg.max_num_seqs)
+    engine = LLMEngine(runner, AsyncSampler(), ecfg, eos_token_id=None)
+    runner._requests = _LiveView(engine)
+    plans, outs, aborted = {}, {}, set()
+    to_add = 10
+    for step in range(2000):
+        if to_add and rng.random() < 0.3:
+            prompt = [rng.randrange(VOCAB) for _ in range(rng.randint(1, 20))]
+            n = rng.randint(1, 25)
+            full = expected(prompt, n)
+            stop = full[rng.randrange(len(full))] if rng.random() < 0.4 else None      # ends early by this token
+            sid = engine.add_request(prompt, SamplingParams(max_tokens=n, ignore_eos=True,
+                                                            stop_token_ids=(stop,) if stop is not None else ()))
+            plans[sid] = (prompt, n, stop)
+            to_add -= 1
+        if engine.running and rng.random() < 0.03:
+            victim = rng.choice(engine.running).seq_id
+            assert engine.abort(victim)
+            aborted.add(victim)
+        for o in engine.step():
+            outs[o.seq_id] = o
+        if not to_add and not engine.has_work():
+            break
+    assert not engine.has_work()
+    for sid, (prompt, n, stop) in plans.items():
+        if sid in aborted:
+            assert sid not in outs
+            continue
+        full = expected(prompt, n)
+        want = full[:full.index(stop) + 1] if stop is not None else full
+        assert outs[sid].output_token_ids == want, (sid, prompt, n, stop)
+        assert outs[sid].finish_reason == ("stop" if stop is not None else "length")
+    assert runner.launched > 0
+    runner.cache.check([])
