@@ -178,18 +178,21 @@ class ModelRunner:
         self._staging_np = self._staging.numpy()
         self._device_ints = torch.empty(n_ints, dtype=torch.int32, device=self.device)
 
-    def _replay(self, key, ctx: StepContext, layout) -> torch.Tensor:
+    def _replay(self, key, make_ctx, layout) -> torch.Tensor:
         """Runs a one-token-per-request step from its captured graph.  The step's int arrays sit
         at the same device addresses for the same key (same counts, same packing order), so a
         replay only needs the new values, which ``step`` has already copied.  The first step
         of a key runs once uncaptured (library warm-up; writing the same keys and values
-        twice changes nothing), then is captured and replayed."""
+        twice changes nothing), then is captured and replayed.  ``make_ctx`` builds the step's
+        context; a replay does not need it (a dozen tensor views that would stand between the
+        sampled ids and the launch)."""
         hit = self._graphs.get(key)
         if hit is not None and hit[2] != layout:
             hit = None                                  # the staging buffer was re-allocated since
         if hit is None:
             if len(self._graphs) >= MAX_GRAPHS:
                 self._graphs.pop(next(iter(self._graphs)))
+            ctx = make_ctx()
             self._forward_chained(ctx)
             graph = torch.cuda.CUDAGraph()
             before = kernels.launch_count()
@@ -392,7 +395,7 @@ class ModelRunner:
             t = dev[span[0]:span[0] + span[1]]
             return t if shape is None else t.view(shape)
 
-        ctx = StepContext(
+        make_ctx = lambda: StepContext(
             dtype=self.dtype, device=self.device, n_tokens=N, n_seqs=S,
             token_ids=d(tok_s), positions=d(pos_s, (self.axes, N)), token_seq=d(tseq_s), cu_q=d(cu_s),
             q_start_pos=d(qs_s), slot_ids=d(sl_s), logit_rows=d(rows_s) if M else None,
@@ -408,9 +411,9 @@ class ModelRunner:
             host_slots=[e.request.cache.slot for e in entries],
         )
         if graph_key is None:
-            logits = self.model.forward(ctx)
+            logits = self.model.forward(make_ctx())
         else:
-            logits = self._replay(graph_key, ctx, (dev.data_ptr(), off))
+            logits = self._replay(graph_key, make_ctx, (dev.data_ptr(), off))
 
         if self.device.type == "cuda":
             self._error_host.copy_(kernels.error_flag(self.device), non_blocking=True)
