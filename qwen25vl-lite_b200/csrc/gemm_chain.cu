@@ -252,8 +252,9 @@ __global__ void __launch_bounds__(GC_THREADS, 1) gemm_chain_kernel(const __grid_
     for (int k = 0; k < A.n_ops; ++k) {
       const ChainOp& op = A.op[k];
       if (k > 0) {
-        // everything the operation before this one wrote, on every CTA, before anybody reads it
-        __threadfence();
+        // everything the operation before this one wrote, on every CTA, before anybody reads it: the
+        // lanes' stores meet at __syncwarp, and the release of the first lane's add carries them all
+        // (a fence by each of the 32 lanes first cost about a third of a microsecond per barrier)
         __syncwarp();
         if (lane == 0) {
           // The counter only grows: the k-th barrier of this launch is passed when it has reached
