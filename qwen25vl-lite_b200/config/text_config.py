@@ -7,9 +7,12 @@ differences that are deliberate:
 * sizes are never defaulted.  The reference fills every absent key with the 3B value
   (config.py:81-95), so a flat config silently becomes a 3B model; here a missing size is
   an error that names the key.
-* ``use_sliding_window`` is honoured.  The reference parses ``sliding_window`` /
+* ``use_sliding_window: true`` is refused.  The reference parses ``sliding_window`` /
   ``use_sliding_window`` and derives ``layer_types()`` (config.py:93-94, 105-109) but its
-  attention never consults them; here the same per-layer pattern selects a windowed mixer.
+  attention never consults them (src/qwen25vl_lite/text.py:156-175), so a file that sets the
+  flag would silently run full attention there.  Here it is an error that says so, instead of
+  logits that nobody asked for; ``sliding_window`` itself is kept as read.
+* ``eos_token_id`` defaults to 151645 when config.json has none, as config.py:147,188 does.
 """
 
 from __future__ import annotations
@@ -32,6 +35,9 @@ REQUIRED_SIZES = (
 )
 
 
+DEFAULT_EOS_TOKEN_ID = 151645      # the reference's default (src/qwen25vl_lite/config.py:147,188)
+
+
 class ConfigError(ValueError):
     """A config.json that cannot describe a model this engine can build."""
 
@@ -50,7 +56,7 @@ class Qwen25VLTextConfig:
     tie_word_embeddings: bool = True
     sliding_window: Optional[int] = None
     use_sliding_window: bool = False
-    eos_token_id: Optional[int] = None
+    eos_token_id: Optional[int] = DEFAULT_EOS_TOKEN_ID
     max_position_embeddings: Optional[int] = None
 
     # ---- derived -------------------------------------------------------------------
@@ -62,14 +68,6 @@ class Qwen25VLTextConfig:
     @property
     def num_key_value_groups(self) -> int:
         return self.num_attention_heads // self.num_key_value_heads
-
-    def layer_windows(self) -> Tuple[Optional[int], ...]:
-        """Window of each layer, None for full attention.  Same pattern as the reference's
-        ``layer_types()`` (config.py:105-109): with ``use_sliding_window`` the layers with
-        even index slide, the others see everything."""
-        if not self.use_sliding_window:
-            return tuple(None for _ in range(self.num_hidden_layers))
-        return tuple(int(self.sliding_window) if (i + 1) % 2 else None for i in range(self.num_hidden_layers))
 
     def num_params(self) -> int:
         """Parameter count, as config.py:120-134 accounts it."""
@@ -102,8 +100,10 @@ class Qwen25VLTextConfig:
             raise ConfigError(f"mrope_section needs three entries (t, h, w), got {list(self.mrope_section)}")
         if not self.rms_norm_eps > 0 or not self.rope_theta > 0:
             raise ConfigError("rms_norm_eps and rope_theta must be positive")
-        if self.use_sliding_window and (self.sliding_window is None or int(self.sliding_window) <= 0):
-            raise ConfigError("use_sliding_window needs a positive sliding_window")
+        if self.use_sliding_window:
+            raise ConfigError(
+                "use_sliding_window=true is not supported: the decoder this engine restates never applies a window "
+                "(it parses the key and attends to every key); set use_sliding_window to false")
 
     # ---- reading / writing ---------------------------------------------------------
     @classmethod
@@ -129,7 +129,7 @@ class Qwen25VLTextConfig:
             where = "config.json" if flat else "config.json (text_config)"
             raise ConfigError(f"{where} lacks required key(s): {', '.join(missing)}")
         tie = text.get("tie_word_embeddings", raw.get("tie_word_embeddings", True))
-        eos = raw.get("eos_token_id", text.get("eos_token_id"))
+        eos = raw.get("eos_token_id", text.get("eos_token_id", DEFAULT_EOS_TOKEN_ID))
         if isinstance(eos, (list, tuple)):
             eos = eos[0] if eos else None
         window = text.get("sliding_window")

@@ -18,10 +18,18 @@ from ..config.text_config import Qwen25VLTextConfig
 ARCHITECTURE = "Qwen2_5_VLForConditionalGeneration"
 
 
-def build_spec(cfg: Qwen25VLTextConfig) -> ModelSpec:
+def build_spec(cfg: Qwen25VLTextConfig, layer_windows=None) -> ModelSpec:
+    """``layer_windows``: a window per layer (None = all keys) for builders of *other*
+    architectures that reuse this make-up; this architecture's own config.json never sets one
+    (the reference parses ``sliding_window`` and attends to every key,
+    src/qwen25vl_lite/text.py:156-175)."""
     h, d = cfg.hidden_size, cfg.head_dim
     layers = []
-    for i, window in enumerate(cfg.layer_windows()):
+    if layer_windows is None:
+        layer_windows = [None] * cfg.num_hidden_layers
+    if len(layer_windows) != cfg.num_hidden_layers:
+        raise ValueError(f"{len(layer_windows)} windows for {cfg.num_hidden_layers} layers")
+    for i, window in enumerate(layer_windows):
         layers.append(LayerSpec(
             block="prenorm_residual",
             mixer=PartSpec("gqa_attention", dict(hidden_size=h, num_heads=cfg.num_attention_heads,

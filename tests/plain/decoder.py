@@ -232,12 +232,14 @@ def swiglu_mlp(x: np.ndarray, w: Dict[str, np.ndarray], prefix: str) -> np.ndarr
 
 
 def layer_windows(cfg: dict) -> List[Optional[int]]:
-    """config.py:105-109 (layer_types): with use_sliding_window every layer whose index is
-    even is a sliding-window layer, the others attend to everything; without it all layers
-    are full attention."""
+    """text.py:156-175 -- the reference's attention sees every key: ``sliding_window`` and
+    ``use_sliding_window`` are parsed (config.py:93-94,105-109) and never consulted, so every
+    layer's window is None.  A test architecture that does window lists its windows under
+    ``layer_windows`` (None = all keys)."""
     n = cfg["num_hidden_layers"]
-    if cfg.get("use_sliding_window", False):
-        return [int(cfg["sliding_window"]) if (i + 1) % 2 else None for i in range(n)]
+    if cfg.get("layer_windows") is not None:
+        assert len(cfg["layer_windows"]) == n
+        return [None if v is None else int(v) for v in cfg["layer_windows"]]
     return [None] * n
 
 
@@ -252,10 +254,11 @@ def decoder_layer(x: np.ndarray, w: Dict[str, np.ndarray], i: int, cfg: dict,
 
 
 def forward_logits(cfg: dict, w: Dict[str, np.ndarray], token_ids: Sequence[int],
-                   positions: Optional[np.ndarray] = None) -> np.ndarray:
+                   positions: Optional[np.ndarray] = None, rows: Optional[Sequence[int]] = None) -> np.ndarray:
     """text.py:213,243-279; model.py:84-86,200-202 -- embed, layers, final norm, head (the
     embedding table again when tied and no lm_head.weight is stored).  Logits for every
-    position, [N, V]."""
+    position, [N, V], or for the positions ``rows`` only (model.py:200-202 keeps the wanted
+    positions before the head; a large vocabulary makes that worth it here too)."""
     ids = np.asarray(token_ids, dtype=np.int64)
     n = ids.shape[0]
     dtype = w["embed_tokens.weight"].dtype
@@ -266,6 +269,8 @@ def forward_logits(cfg: dict, w: Dict[str, np.ndarray], token_ids: Sequence[int]
     x = w["embed_tokens.weight"][ids]
     for i, window in enumerate(layer_windows(cfg)):
         x = decoder_layer(x, w, i, cfg, cos, sin, window)
+    if rows is not None:
+        x = x[np.asarray(rows, dtype=np.int64)]
     x = rms_norm(x, w["norm.weight"], cfg["rms_norm_eps"])
     head = w["lm_head.weight"] if "lm_head.weight" in w else w["embed_tokens.weight"]
     return x @ head.T
@@ -378,4 +383,28 @@ def greedy_generate(cfg: dict, w: Dict[str, np.ndarray], prompt: Sequence[int], 
         out.append(tok)
         pos = np.concatenate([pos, decode_positions(len(ids), rope_delta)], axis=1)
         ids.append(tok)
+    return out
+
+
+def generation_margins(cfg: dict, w: Dict[str, np.ndarray], prompt: Sequence[int], generated: Sequence[int],
+                       positions: Optional[np.ndarray] = None, rope_delta: int = 0,
+                       temperature: float = 0.0, seed: int = 0) -> List[float]:
+    """How far each generated token is from the one this implementation would have chosen at its
+    place, given the tokens before it: ``max(score) - score[token]`` with score = logits for
+    greedy, logits / T + the draw's noise otherwise (the choice is an argmax either way,
+    sampling.py:67-72 and ``sample`` above).  0 means the same choice; an engine that rounds
+    differently (bfloat16) may pick a token whose score is within its rounding of the best, and
+    teacher forcing keeps one such pick from derailing the comparison of the later ones."""
+    ids = list(prompt) + [int(t) for t in generated]
+    n0 = len(prompt)
+    pos = text_positions(n0) if positions is None else np.asarray(positions)
+    tail = [decode_positions(n, rope_delta) for n in range(n0, len(ids))]
+    pos = np.concatenate([pos] + tail, axis=1) if tail else pos
+    logits = forward_logits(cfg, w, ids, pos, rows=list(range(n0 - 1, len(ids) - 1)))
+    out = []
+    for k, tok in enumerate(generated):
+        s = logits[k].astype(np.float64)
+        if temperature > 0:
+            s = s / temperature + gumbel_noise(seed, k, s.shape[-1]).astype(np.float64)
+        out.append(float(s.max() - s[int(tok)]))
     return out

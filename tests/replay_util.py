@@ -59,11 +59,13 @@ def portions(requests: Dict[str, Sequence[int]], sizes: Sequence[int]) -> List[d
     return steps
 
 
-def mixed(requests: Dict[str, Sequence[int]], seed: int, max_live: int = 4, decode_tail: int = 6) -> List[dict]:
+def mixed(requests: Dict[str, Sequence[int]], seed: int, max_live: int = 4, decode_tail: int = 6,
+          chosen_share: float = 0.75, longest: int = 24) -> List[dict]:
     """Up to ``max_live`` requests at a time; every step takes a random subset of the live
-    ones and gives each a portion of random size (down to two tokens) while it is in its
-    prompt, single tokens over its last ``decode_tail`` tokens; a finished request ends and
-    the next one starts, so pages are used again."""
+    ones (each with probability ``chosen_share``) and gives each a portion of random size (two
+    to ``longest`` - 1 tokens) while it is in its prompt, single tokens over its last
+    ``decode_tail`` tokens; a finished request ends and the next one starts, so pages are used
+    again."""
     rng = np.random.default_rng(seed)
     todo = list(requests.items())
     live: Dict[str, List] = {}
@@ -72,7 +74,7 @@ def mixed(requests: Dict[str, Sequence[int]], seed: int, max_live: int = 4, deco
         while todo and len(live) < max_live:
             rid, ids = todo.pop(0)
             live[rid] = [list(ids), 0]
-        chosen = [rid for rid in live if rng.random() < 0.75] or [next(iter(live))]
+        chosen = [rid for rid in live if rng.random() < chosen_share] or [next(iter(live))]
         entries, end = [], []
         for rid in chosen:
             ids, at = live[rid]
@@ -80,7 +82,7 @@ def mixed(requests: Dict[str, Sequence[int]], seed: int, max_live: int = 4, deco
             if left <= decode_tail:
                 n = 1
             else:
-                n = int(min(rng.integers(2, 24), left - decode_tail))
+                n = int(min(rng.integers(2, longest), left - decode_tail))
             entries.append({"id": rid, "tokens": ids[at:at + n], "want": list(range(n))})
             live[rid][1] = at + n
             if at + n == len(ids):
@@ -104,11 +106,12 @@ def max_live_tokens(steps: List[dict]) -> int:
     return worst
 
 
-def run_in_process(model_dir: str, dtype: str, steps: List[dict], max_tokens: int, page_size: int = 16):
+def run_in_process(model_dir: str, dtype: str, steps: List[dict], max_tokens: int, page_size: int = 16,
+                   max_requests: int = 8):
     """Replays through the engine's trace session; returns {request id: [len, vocab] logits}."""
     from qwen25vl_lite.engine.trace import TraceSession, make_runner
 
-    runner = make_runner(model_dir, dtype, max_tokens, page_size)
+    runner = make_runner(model_dir, dtype, max_tokens, page_size, max_requests)
     session = TraceSession(runner, None)
     return collect(steps, [session.run_step(s) for s in steps]), runner
 

@@ -14,7 +14,7 @@ def test_reads_text_config_and_rope_scaling():
     assert (cfg.hidden_size, cfg.num_hidden_layers, cfg.num_attention_heads, cfg.num_key_value_heads) == (192, 3, 6, 1)
     assert cfg.head_dim == 32 and cfg.mrope_section == (4, 6, 6) and cfg.rope_theta == 1e6
     assert cfg.rms_norm_eps == 1e-5 and cfg.tie_word_embeddings is False
-    assert cfg.layer_windows() == (None, None, None)
+    assert cfg.sliding_window == 4096 and cfg.use_sliding_window is False
 
 
 def test_flat_config_and_rope_parameters_and_top_level_keys():
@@ -54,9 +54,23 @@ def test_validation():
             Qwen25VLTextConfig.from_dict(raw)
 
 
-def test_window_pattern_follows_the_reference_layer_types():
-    cfg = Qwen25VLTextConfig.from_dict(TINY_C)
-    assert cfg.layer_windows() == (24, None, 24, None)     # config.py:105-109: even layers slide
+def test_use_sliding_window_is_refused_and_no_layer_of_the_architecture_windows():
+    """The reference parses the flag and attends to every key (text.py:156-175); here the flag is
+    an error, and a config.json of this architecture can never switch a window on."""
+    raw = copy.deepcopy(TINY_A)
+    raw["text_config"].update(use_sliding_window=True, sliding_window=24)
+    with pytest.raises(ConfigError, match="use_sliding_window=true is not supported"):
+        Qwen25VLTextConfig.from_dict(raw)
+    arch = resolve_architecture(TINY_A)
+    spec = arch.build_spec(arch.config_from_dict(TINY_B))          # sliding_window 4096, flag false
+    assert all(layer.mixer.params["window"] is None for layer in spec.layers)
+
+
+def test_eos_token_id_defaults_as_in_the_reference():
+    assert Qwen25VLTextConfig.from_dict(TINY_A).eos_token_id == 151645          # config.py:147,188
+    raw = copy.deepcopy(TINY_A)
+    raw["eos_token_id"] = [7, 9]
+    assert Qwen25VLTextConfig.from_dict(raw).eos_token_id == 7
 
 
 def test_round_trip_and_param_count():
@@ -71,8 +85,10 @@ def test_round_trip_and_param_count():
 def test_registry():
     assert "Qwen2_5_VLForConditionalGeneration" in known_architectures()
     arch = resolve_architecture(TINY_A)
-    spec = arch.build_spec(arch.config_from_dict(TINY_C))
-    assert len(spec.layers) == 4 and [s.layer for s in spec.schedule] == [0, 1, 2, 3]
+    spec = arch.build_spec(arch.config_from_dict(TINY_B))
+    assert len(spec.layers) == 3 and [s.layer for s in spec.schedule] == [0, 1, 2]
+    windowed = resolve_architecture(TINY_C)                        # an architecture the tests register
+    spec = windowed.build_spec(windowed.config_from_dict(TINY_C))
     assert spec.layers[0].mixer.params["window"] == 24 and spec.layers[1].mixer.params["window"] is None
     with pytest.raises(ValueError, match="unknown architecture.*known architectures.*Qwen2_5_VL"):
         resolve_architecture({"architectures": ["LlamaForCausalLM"]})

@@ -64,13 +64,109 @@ def test_preemption_on_the_device_changes_nothing(model_dirs):
     assert tight.runner.cache.pages_in_use() == [0, 0]
 
 
-def test_bfloat16_generation_runs(model_dirs, tmp_path):
+def test_preemption_recomputes_a_request_with_an_image_run_exactly(model_dirs):
+    """tiny-B, pages of 8, a pool too small for both requests: the newer one, whose prompt carries
+    a 12-token image run (grid t1 x h3 x w4, so its text resumes at a position offset of its own),
+    is preempted after it has generated tokens and comes back with prompt + generated to
+    recompute.  Its tokens must be those of the plain decoder run without any cache: positions of
+    the recomputed generated tokens continue from the image run's offset
+    (src/qwen25vl_lite/rope.py:235-247), and its sampling keys go on where they stopped."""
     from qwen25vl_lite import LLM, SamplingParams
+    text, image = _prompts("B", (23, 40), 26)
+    spans = [(9, 1, 3, 4)]
+    params = SamplingParams(temperature=0.8, seed=3, max_tokens=30, ignore_eos=True)
+    llm = LLM(model_dirs["B"], dtype="float32", num_blocks=13, block_size=8, max_num_seqs=2)
+    first = llm.engine.add_request(text, params)
+    second = llm.engine.add_request(image, params, image_spans=spans)
+    generated_when_preempted = None
+    while llm.engine.has_work():
+        llm.engine.step()
+        for seq in llm.engine.waiting:
+            if seq.seq_id == second and seq.preemptions and generated_when_preempted is None:
+                generated_when_preempted = len(seq.output_token_ids)
+    outs = {o.seq_id: o for o in llm.engine.finished}
+    assert outs[second].metrics["preemptions"] >= 1 and generated_when_preempted and generated_when_preempted >= 2
+    cfg, w = plain.load_model_dir(model_dirs["B"], np.float64)
+    pos, delta = plain.prompt_positions(len(image), spans)
+    assert delta != 0
+    assert outs[second].output_token_ids == plain.greedy_generate(cfg, w, image, 30, pos, delta, temperature=0.8, seed=3)
+    assert outs[first].output_token_ids == plain.greedy_generate(cfg, w, text, 30, temperature=0.8, seed=3)
+    assert llm.runner.cache.pages_in_use() == [0]
+
+
+def test_abort_while_the_next_step_is_already_on_the_device(model_dirs):
+    """The engine launches the next decode step before it returns from ``step``; a request
+    aborted at that moment draws nothing from that step, its pages go back at once (the step's
+    writes into them are ordered before any later use), and the others go on exactly."""
+    from qwen25vl_lite import LLM, SamplingParams
+    prompts = _prompts("A", (5, 11, 17), 27)
+    llm = LLM(model_dirs["A"], dtype="float32", num_blocks=64, block_size=4, max_num_seqs=4)
+    ids = [llm.engine.add_request(p, SamplingParams(max_tokens=12, ignore_eos=True)) for p in prompts]
+    aborted_with = None
+    for _ in range(200):
+        if not llm.engine.has_work():
+            break
+        llm.engine.step()
+        if aborted_with is None and llm.engine._launched is not None and len(llm.engine.running) == 3 \
+                and len(llm.engine.running[1].output_token_ids) >= 3:
+            victim = next(s for s in llm.engine.running if s.seq_id == ids[1])
+            aborted_with = list(victim.output_token_ids)
+            assert llm.engine.abort(ids[1])
+    assert aborted_with is not None, "no step was ever launched ahead"
+    assert not llm.engine.has_work()
+    outs = {o.seq_id: o for o in llm.engine.finished}
+    assert ids[1] not in outs
+    cfg, w = plain.load_model_dir(model_dirs["A"], np.float64)
+    for i in (0, 2):
+        assert outs[ids[i]].output_token_ids == plain.greedy_generate(cfg, w, prompts[i], 12)
+    assert aborted_with == plain.greedy_generate(cfg, w, prompts[1], 12)[:len(aborted_with)]
+    assert llm.runner.cache.pages_in_use() == [0]
+    llm.runner.cache.check([])
+
+
+def test_without_chunked_prefill_on_the_device(model_dirs):
+    """``enable_chunked_prefill=False`` (the reference's --no-chunked-prefill,
+    src/qwen25vl_lite/engine.py:649-654,673-678): a prompt runs whole or waits for a step with
+    room for all of it; the tokens are the plain decoder's."""
+    from qwen25vl_lite import LLM, SamplingParams
+    prompts = _prompts("B", (9, 30, 17, 26), 28)
+    llm = LLM(model_dirs["B"], dtype="float32", num_blocks=64, block_size=8, max_num_seqs=4, max_num_batched_tokens=32,
+              enable_chunked_prefill=False)
+    fed = []
+    step = llm.runner.step
+    llm.runner.step = lambda entries: (fed.append([len(e.tokens) for e in entries]), step(entries))[1]
+    outs = llm.generate(prompts, SamplingParams(max_tokens=5, ignore_eos=True))
+    whole = {9, 30, 17, 26}
+    assert all(n == 1 or n in whole for f in fed for n in f) and all(sum(f) <= 32 for f in fed)
+    cfg, w = plain.load_model_dir(model_dirs["B"], np.float64)
+    for p, o in zip(prompts, outs):
+        assert o.output_token_ids == plain.greedy_generate(cfg, w, p, 5)
+
+
+@pytest.mark.parametrize("name,temperature", [("B", 0.7), ("D", 0.0), ("D", 0.9), ("E", 0.0)])
+def test_bfloat16_generation_agrees_with_the_plain_decoder(name, temperature, tmp_path):
+    """bfloat16 generation (prompt portions, then decode steps replayed from CUDA graphs) against
+    the plain decoder on the same bfloat16-rounded weights: every generated token must be the plain
+    decoder's own choice at its place, or score within bfloat16 rounding of it; and a second run
+    with the same seed repeats the tokens."""
+    from qwen25vl_lite import LLM, SamplingParams
+    from test_replay_gpu import TOL
     from tiny_models import make_model_dir
-    llm = LLM(make_model_dir(tmp_path, "B", "bfloat16"), dtype="bfloat16", num_blocks=32, block_size=16)
-    outs = llm.generate(_prompts("B", (12, 33), 24), SamplingParams(max_tokens=10, temperature=0.7, seed=5, ignore_eos=True))
-    assert [len(o.output_token_ids) for o in outs] == [10, 10]
-    again = llm.generate(_prompts("B", (12, 33), 24), SamplingParams(max_tokens=10, temperature=0.7, seed=5, ignore_eos=True))
+    folder = make_model_dir(tmp_path, name, "bfloat16")
+    llm = LLM(folder, dtype="bfloat16", num_blocks=48, block_size=16, max_num_batched_tokens=24)
+    prompts = _prompts(name, (12, 33, 70), 24)
+    params = SamplingParams(max_tokens=24, temperature=temperature, seed=5, ignore_eos=True)
+    outs = llm.generate(prompts, params)
+    assert [len(o.output_token_ids) for o in outs] == [24, 24, 24]
+    assert llm.runner.graph_replays > 0
+    cfg, w = plain.load_model_dir(folder, np.float64)
+    tol = TOL["bfloat16", name]
+    for p, o in zip(prompts, outs):
+        margins = plain.generation_margins(cfg, w, p, o.output_token_ids, temperature=temperature, seed=5)
+        bound = 2 * tol / temperature if temperature > 0 else 2 * tol       # both scores may be off by tol (/ T)
+        assert max(margins) <= bound, f"prompt of {len(p)} tokens: margins {margins}"
+        assert sum(m == 0.0 for m in margins) >= 16, f"prompt of {len(p)} tokens: margins {margins}"
+    again = llm.generate(prompts, params)
     assert [o.output_token_ids for o in again] == [o.output_token_ids for o in outs]     # seeded: reproducible
 
 

@@ -130,3 +130,30 @@ def test_missing_files(tmp_path):
     (tmp_path / "config.json").write_text(json.dumps(TINY_A))
     with pytest.raises(FileNotFoundError, match="safetensors"):
         load_model(str(tmp_path), "float32", "cpu")
+
+
+def test_sharded_folder_with_an_index(model_dirs, tmp_path):
+    """``model.safetensors.index.json`` naming two shards (src/qwen25vl_lite/model.py:312-327): every
+    tensor is found in whichever shard holds it, and a tensor in no shard is reported missing."""
+    src = SafetensorsFile(os.path.join(model_dirs["B"], "model.safetensors"))
+    names = src.names()
+    half = len(names) // 2
+    folder = tmp_path / "sharded"
+    os.makedirs(folder)
+    shards = {"model-00001-of-00002.safetensors": names[:half], "model-00002-of-00002.safetensors": names[half:]}
+    for fname, part in shards.items():
+        write_safetensors(str(folder / fname), [(n, src.tensor(n).clone()) for n in part])
+    with open(folder / "model.safetensors.index.json", "w") as fh:
+        json.dump({"metadata": {}, "weight_map": {n: f for f, part in shards.items() for n in part}}, fh)
+    with open(os.path.join(model_dirs["B"], "config.json")) as a, open(folder / "config.json", "w") as b:
+        b.write(a.read())
+    _, sharded = load_model(str(folder), "float32", "cpu")
+    _, single = load_model(model_dirs["B"], "float32", "cpu")
+    for a, b in zip(sharded.blocks, single.blocks):
+        assert torch.equal(a.mixer.qkv_proj.weight, b.mixer.qkv_proj.weight)
+        assert torch.equal(a.feed_forward.down_proj.weight, b.feed_forward.down_proj.weight)
+    assert torch.equal(sharded.head.proj.weight, single.head.proj.weight)
+    os.remove(folder / "model-00002-of-00002.safetensors")
+    write_safetensors(str(folder / "model-00002-of-00002.safetensors"), [(n, src.tensor(n).clone()) for n in names[half:-1]])
+    with pytest.raises(WeightsError, match="missing tensors"):
+        load_model(str(folder), "float32", "cpu")
