@@ -1,14 +1,17 @@
 #!/usr/bin/env python3
-"""Decode and prefill throughput of the engine at Qwen2.5-VL-3B sizes, random bfloat16 weights.
+"""Decode and prefill throughput of the engine at Qwen2.5-VL sizes, random bfloat16 weights.
 
-    python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference] [--config 3b|7b-trace|32b]
 
-One "step" is one decode step of the whole batch.  The headline ``value`` is decoded tokens
-a second at batch 8 after 2,048-token prompts (context capacity 4,096), timed on the device
-over exactly K steps that are fed back-to-back; ``e2e`` is the same through the public
-entry point (scheduler, host tokens in and out every step).  The same line carries the
-2,048-token prefill, the decode step's HBM roofline, decode at batch 1 and 64, the clocks
-seen while timing, and the number of this engine's kernel launches in the timed region.
+One "step" is one decode step of the whole batch.  The default run (``--config 3b``) has the 3B
+layer sizes: the headline ``value`` is decoded tokens a second at batch 8 after 2,048-token
+prompts (context capacity 4,096), timed on the device over exactly K steps that are fed
+back-to-back; ``e2e`` is the same through the public entry point (scheduler, host tokens in and
+out every step).  The same line carries the 2,048-token prefill, the decode step's HBM roofline,
+decode at batch 1 and 64, the clocks seen while timing, and the number of this engine's kernel
+launches in the timed region.  ``--config 7b-trace`` runs a continuous-batching trace of 128
+requests at the 7B sizes, ``--config 32b`` decode at batch 1 / 8 / 32 after 8,192-token prompts and
+a 2,048-token prefill at the 32B sizes; each prints one line of its own.
 The engine is single-GPU: for --gpus N > 1 one line says so and the exit code is 2.
 """
 
@@ -26,18 +29,25 @@ import time
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
-# Qwen2.5-VL-3B text decoder sizes (BASELINE.json configs[2])
-CONFIG_3B = {
-    "architectures": ["Qwen2_5_VLForConditionalGeneration"],
-    "model_type": "qwen2_5_vl",
-    "tie_word_embeddings": True,
-    "text_config": {
-        "hidden_size": 2048, "num_hidden_layers": 36, "num_attention_heads": 16, "num_key_value_heads": 2,
-        "intermediate_size": 11008, "vocab_size": 151936, "rms_norm_eps": 1e-6, "rope_theta": 1000000.0,
-        "rope_scaling": {"type": "mrope", "mrope_section": [16, 24, 24]},
-        "sliding_window": 32768, "use_sliding_window": False,
-    },
-}
+
+def _sizes(hidden, layers, heads, kv_heads, inter, vocab, tied):
+    return {
+        "architectures": ["Qwen2_5_VLForConditionalGeneration"],
+        "model_type": "qwen2_5_vl",
+        "tie_word_embeddings": tied,
+        "text_config": {
+            "hidden_size": hidden, "num_hidden_layers": layers, "num_attention_heads": heads,
+            "num_key_value_heads": kv_heads, "intermediate_size": inter, "vocab_size": vocab, "rms_norm_eps": 1e-6,
+            "rope_theta": 1000000.0, "rope_scaling": {"type": "mrope", "mrope_section": [16, 24, 24]},
+            "sliding_window": 32768, "use_sliding_window": False,
+        },
+    }
+
+
+# the text decoder sizes of the Qwen2.5-VL releases (3B: the headline configuration)
+CONFIG_3B = _sizes(2048, 36, 16, 2, 11008, 151936, True)
+CONFIG_7B = _sizes(3584, 28, 28, 4, 18944, 152064, False)
+CONFIG_32B = _sizes(5120, 64, 40, 8, 27648, 152064, False)
 FULL_LAYERS = 36
 PROMPT_LEN = 2048
 CONTEXT_LEN = 4096
@@ -99,24 +109,6 @@ class ClockSampler:
                     reasons.add(n)
         return {"sm_mhz": statistics.median(mhz) if mhz else None, "sm_max_mhz": mx, "reasons": sorted(reasons),
                 "samples": len(mhz)}
-
-
-def matmul_flops_per_token(t, layers):
-    h, d = t["hidden_size"], t["hidden_size"] // t["num_attention_heads"]
-    nq, nkv, inter = t["num_attention_heads"], t["num_key_value_heads"], t["intermediate_size"]
-    return layers * 2 * (h * (nq + 2 * nkv) * d + nq * d * h + 3 * h * inter)
-
-
-def weight_bytes(t, layers):
-    h, d = t["hidden_size"], t["hidden_size"] // t["num_attention_heads"]
-    nq, nkv, inter = t["num_attention_heads"], t["num_key_value_heads"], t["intermediate_size"]
-    per_layer = h * (nq + 2 * nkv) * d + nq * d * h + 3 * h * inter
-    return 2 * (layers * per_layer + t["vocab_size"] * h)      # bf16; the head is the embedding table (tied)
-
-
-def kv_bytes_per_token(t, layers):
-    d = t["hidden_size"] // t["num_attention_heads"]
-    return layers * 2 * t["num_key_value_heads"] * d * 2
 
 
 def run_reference(args):
@@ -191,7 +183,8 @@ def run_reference(args):
             "config": {"model": "Qwen2.5-VL-3B text dims", "layers": layers, "layers_full": FULL_LAYERS,
                        "hidden": t["hidden_size"], "q_heads": t["num_attention_heads"], "kv_heads": t["num_key_value_heads"],
                        "head_dim": d, "intermediate": t["intermediate_size"], "vocab": t["vocab_size"], "global_batch": 8,
-                       "seq_len": CONTEXT_LEN, "prompt_len": PROMPT_LEN, "kv_page": PAGE, "parallelism": "single GPU"},
+                       "seq_len": CONTEXT_LEN, "prompt_len": PROMPT_LEN, "kv_page": PAGE, "parallelism": "single GPU",
+                       "l2": "weights read per step exceed L2 (126 MB)", "peaks": load_peaks()["source"]},
             "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": None, "d2h_bytes_per_step": None},
             "clocks": clock_record}))
     except Exception as exc:  # the reference could not run here: say why, in one line
@@ -199,19 +192,32 @@ def run_reference(args):
     return 0
 
 
+def _base_line(metric, value, args, ms_per_step, cfg, layers, batch, seq_len, prompt_len, peaks, extra_config=None):
+    t = cfg["text_config"]
+    config = {"model": metric.split(",")[1].strip() if "," in metric else metric, "layers": layers,
+              "layers_full": t["num_hidden_layers"], "hidden": t["hidden_size"], "q_heads": t["num_attention_heads"],
+              "kv_heads": t["num_key_value_heads"], "head_dim": t["hidden_size"] // t["num_attention_heads"],
+              "intermediate": t["intermediate_size"], "vocab": t["vocab_size"], "global_batch": batch, "seq_len": seq_len,
+              "prompt_len": prompt_len, "kv_page": PAGE, "parallelism": "single GPU",
+              "l2": "weights read per step exceed L2 (126 MB)", "peaks": peaks["source"]}
+    config.update(extra_config or {})
+    return {"metric": metric, "value": value, "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+            "data": "synthetic (seeded uniform-random token ids, random-init weights N(0, 0.02))", "config": config}
+
+
 def run_ours(args):
     import numpy as np
     import torch
 
-    from qwen25vl_lite import LLM, SamplingParams
-    from qwen25vl_lite.engine.runner import StepEntry
-    from qwen25vl_lite.ops import kernels
+    from qwen25vl_lite import LLM
+    from qwen25vl_lite.engine import benchmark as B
 
     peaks = load_peaks()
     cfg = json.loads(json.dumps(CONFIG_3B))
     layers = args.layers or FULL_LAYERS
-    cfg["text_config"]["num_hidden_layers"] = layers
     t = cfg["text_config"]
+    full_layers, t["num_hidden_layers"] = t["num_hidden_layers"], layers
     max_batch = 64
     llm = LLM(random_config=cfg, weights_seed=0, dtype="bfloat16", num_blocks=max_batch * CONTEXT_LEN // PAGE,
               block_size=PAGE, max_num_seqs=max_batch, max_num_batched_tokens=8192, max_model_len=CONTEXT_LEN,
@@ -219,121 +225,143 @@ def run_ours(args):
     runner, engine = llm.runner, llm.engine
     rng = np.random.default_rng(0)
     vocab = t["vocab_size"]
-    dev = torch.device("cuda:0")
-
-    def prompts(n):
-        return [rng.integers(0, vocab, size=PROMPT_LEN).tolist() for _ in range(n)]
 
     # ---- prefill: one prompt of 2,048 tokens, one step -------------------------------------
-    def prefill_once():
-        req = runner.open_request("prefill")
-        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        ids = prompts(1)[0]
-        torch.cuda.synchronize()
-        a.record()
-        runner.step([StepEntry(req, ids, [PROMPT_LEN - 1])])
-        b.record()
-        torch.cuda.synchronize()
-        runner.close_request(req)
-        return a.elapsed_time(b)
-
-    for _ in range(3):
-        prefill_once()
-    prefill_ms = statistics.median(prefill_once() for _ in range(5))
-    d = t["hidden_size"] // t["num_attention_heads"]
-    prefill_flops = (PROMPT_LEN * matmul_flops_per_token(t, layers) + 2 * vocab * t["hidden_size"]
-                     + layers * 4 * t["num_attention_heads"] * d * PROMPT_LEN * (PROMPT_LEN + 1) // 2)
+    prefill_ms = B.time_prefill(runner, PROMPT_LEN, vocab, rng)
     prefill = {"value": PROMPT_LEN / (prefill_ms / 1e3), "tokens": PROMPT_LEN, "ms": prefill_ms,
-               "frac": prefill_flops / (prefill_ms / 1e3) / (peaks["bf16_tflops"] * 1e12)}
-
-    # ---- decode, device-timed: K steps fed back-to-back with given tokens -------------------
-    def decode_device(batch, steps, warmup, sample=True):
-        reqs = [runner.open_request(f"d{i}") for i in range(batch)]
-        ps = prompts(batch)
-        for i in range(0, batch, 4):
-            runner.step([StepEntry(r, p, []) for r, p in zip(reqs[i:i + 4], ps[i:i + 4])])
-        feed = rng.integers(0, vocab, size=(steps + warmup, batch))
-        out = torch.empty(batch, dtype=torch.int32, device=dev)
-
-        def one(k):
-            logits = runner.step([StepEntry(r, [int(feed[k, i])], [0]) for i, r in enumerate(reqs)])
-            kernels.sample_rows(logits, None, None, None, out)
-
-        for k in range(warmup):
-            one(k)
-        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        torch.cuda.synchronize()
-        launches0 = kernels.launch_count()
-        a.record()
-        for k in range(warmup, warmup + steps):
-            one(k)
-        b.record()
-        torch.cuda.synchronize()
-        ms = a.elapsed_time(b)
-        launches = kernels.launch_count() - launches0
-        ctx = PROMPT_LEN + warmup + steps // 2
-        for r in reqs:
-            runner.close_request(r)
-        return batch * steps / (ms / 1e3), ms / steps, launches, ctx
-
-    # ---- decode, end to end: the public entry point, host tokens in and out -----------------
-    def decode_e2e(batch, steps, warmup):
-        params = SamplingParams(max_tokens=warmup + steps + 8, ignore_eos=True)
-        for p in prompts(batch):
-            engine.add_request(p, params)
-        while engine.waiting or any(s.pending > 1 for s in engine.running):
-            engine.step()
-        for _ in range(warmup):
-            engine.step()
-        torch.cuda.synchronize()
-        t0 = time.perf_counter()
-        for _ in range(steps):
-            engine.step()
-        torch.cuda.synchronize()
-        dt = time.perf_counter() - t0
-        for s in list(engine.running):
-            engine.abort(s.seq_id)
-        return batch * steps / dt
+               "frac": B.prefill_flops(t, layers, PROMPT_LEN) / (prefill_ms / 1e3) / (peaks["bf16_tflops"] * 1e12)}
 
     if args.only_batch:             # for profiler runs at another batch size: that decode loop alone, a short line
-        tok_s, ms, launches, ctx = decode_device(args.only_batch, args.steps, args.warmup)
-        print(json.dumps({"decode_batch": args.only_batch, "tokens_per_s": tok_s, "ms_per_step": ms, "layers": layers,
-                          "context": ctx, "gpu_launches": launches}))
+        r = B.time_decode_steps(runner, args.only_batch, PROMPT_LEN, args.steps, args.warmup, vocab, rng)
+        print(json.dumps({"decode_batch": args.only_batch, "tokens_per_s": r["tokens_per_s"], "ms_per_step": r["ms_per_step"],
+                          "layers": layers, "context": r["context"], "gpu_launches": r["launches"]}))
         return 0
     clocks = ClockSampler()
     clocks.start()
-    value, ms_per_step, launches, ctx = decode_device(8, args.steps, args.warmup)
+    head = B.time_decode_steps(runner, 8, PROMPT_LEN, args.steps, args.warmup, vocab, rng)
     clock_record = clocks.stop()
+    points = {}
     if args.headline_only:          # for profiler runs: the headline loop and the prefill alone
-        e2e_value = b1 = b64 = None
+        e2e_value = None
     else:
-        e2e_value = decode_e2e(8, args.steps, args.warmup)
-        small = max(8, args.steps // 4)
-        b1, _, _, _ = decode_device(1, small, args.warmup)
-        b64, _, _, _ = decode_device(64, small, args.warmup)
+        e2e_value = B.time_decode_e2e(engine, 8, PROMPT_LEN, args.steps, args.warmup, vocab, rng)
+        for b in (1, 16, 17, 32, 64):      # every point over as many steps as the headline
+            points[f"decode_b{b}"] = B.time_decode_steps(runner, b, PROMPT_LEN, args.steps, args.warmup, vocab, rng)["tokens_per_s"]
 
-    step_bytes = weight_bytes(t, layers) + 8 * ctx * kv_bytes_per_token(t, layers)
-    achieved = step_bytes / (ms_per_step / 1e3) / 1e9
+    ctx = head["context"]
+    step_bytes = B.weight_bytes(t, layers) + 8 * ctx * B.kv_bytes_per_token(t, layers)
+    achieved = step_bytes / (head["ms_per_step"] / 1e3) / 1e9
     n_groups = len(runner.cache.groups)
     h2d = 4 * (8 * (2 + 3 + n_groups) + 9 + 16 + 8 + 8 * n_groups * (-(-(ctx + 1) // PAGE)))
-    line = {
-        "metric": "decode tokens/s, Qwen2.5-VL-3B dims, batch 8, 2048-token prompts", "value": value, "unit": "tokens/s",
-        "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
-        "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic (seeded uniform-random token ids, "
-        "random-init weights N(0, 0.02))",
-        "config": {"model": "Qwen2.5-VL-3B text dims", "layers": layers, "layers_full": FULL_LAYERS, "hidden": t["hidden_size"],
-                   "q_heads": t["num_attention_heads"], "kv_heads": t["num_key_value_heads"], "head_dim": d,
-                   "intermediate": t["intermediate_size"], "vocab": vocab, "global_batch": 8, "seq_len": CONTEXT_LEN,
-                   "prompt_len": PROMPT_LEN, "kv_page": PAGE, "parallelism": "single GPU",
-                   "l2": "weights read per step (6.2 GB) exceed L2 (126 MB)", "peaks": peaks["source"]},
+    t["num_hidden_layers"] = full_layers
+    line = _base_line("decode tokens/s, Qwen2.5-VL-3B dims, batch 8, 2048-token prompts", head["tokens_per_s"], args,
+                      head["ms_per_step"], cfg, layers, 8, CONTEXT_LEN, PROMPT_LEN, peaks)
+    line["config"]["model"] = "Qwen2.5-VL-3B text dims"
+    line.update({
         "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 8 * 4},
-        "gpu_launches": launches,
+        "gpu_launches": head["launches"],
         "prefill": prefill,
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
                      "frac": achieved / peaks["hbm_gbs"]},
-        "points": {"decode_b1": b1, "decode_b64": b64},
+        "points": points,
         "clocks": clock_record,
-    }
+    })
+    print(json.dumps(line))
+    return 0
+
+
+def run_32b(args):
+    """Decode at batch 1, 8 and 32 after 8,192-token prompts and one 2,048-token prefill at the 32B
+    sizes (65.5 GB of bfloat16 weights, up to 70 GB of cache)."""
+    import numpy as np
+
+    from qwen25vl_lite import LLM
+    from qwen25vl_lite.engine import benchmark as B
+
+    peaks = load_peaks()
+    cfg = json.loads(json.dumps(CONFIG_32B))
+    t = cfg["text_config"]
+    layers = args.layers or t["num_hidden_layers"]
+    full_layers, t["num_hidden_layers"] = t["num_hidden_layers"], layers
+    prompt_len, context = 8192, 8192 + 256
+    llm = LLM(random_config=cfg, weights_seed=0, dtype="bfloat16", num_blocks=32 * (-(-context // PAGE)), block_size=PAGE,
+              max_num_seqs=32, max_num_batched_tokens=8192, max_model_len=context, cuda_graph=not args.no_cuda_graph)
+    rng = np.random.default_rng(0)
+    vocab = t["vocab_size"]
+    prefill_ms = B.time_prefill(llm.runner, PROMPT_LEN, vocab, rng, warmup=2, repeats=3)
+    prefill = {"value": PROMPT_LEN / (prefill_ms / 1e3), "tokens": PROMPT_LEN, "ms": prefill_ms,
+               "frac": B.prefill_flops(t, layers, PROMPT_LEN) / (prefill_ms / 1e3) / (peaks["bf16_tflops"] * 1e12)}
+    clocks = ClockSampler()
+    clocks.start()
+    points, roofs, launches = {}, {}, 0
+    for b in (8, 1, 32):
+        r = B.time_decode_steps(llm.runner, b, prompt_len, args.steps, args.warmup, vocab, rng, prefill_group=1)
+        points[f"decode_b{b}"] = r["tokens_per_s"]
+        step_bytes = B.weight_bytes(t, layers) + b * r["context"] * B.kv_bytes_per_token(t, layers)
+        roofs[f"decode_b{b}"] = step_bytes / (r["ms_per_step"] / 1e3) / 1e9 / peaks["hbm_gbs"]
+        if b == 8:
+            head, launches = r, r["launches"]
+    clock_record = clocks.stop()
+    t["num_hidden_layers"] = full_layers
+    line = _base_line("decode tokens/s, Qwen2.5-VL-32B dims, batch 8, 8192-token prompts", head["tokens_per_s"], args,
+                      head["ms_per_step"], cfg, layers, 8, context, prompt_len, peaks)
+    line["config"]["model"] = "Qwen2.5-VL-32B text dims"
+    line.update({"gpu_launches": launches, "prefill": prefill, "points": points,
+                 "roofline": {"bound": "hbm", "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": roofs["decode_b8"],
+                              "frac_b1": roofs["decode_b1"], "frac_b32": roofs["decode_b32"]},
+                 "clocks": clock_record})
+    print(json.dumps(line))
+    return 0
+
+
+def run_7b_trace(args):
+    """A continuous-batching trace at the 7B sizes: 128 requests arrive at once, prompt lengths
+    uniform in [128, 4096], output lengths uniform in [32, 512] (seed 3), at most 8,192 tokens a
+    request, steps of at most 2,048 tokens.  The ideal time it is compared with: the prompts'
+    flops at the sustained tensor peak plus, for every decode step, the weights once and the
+    live requests' cache at the measured copy bandwidth."""
+    import numpy as np
+
+    from qwen25vl_lite import LLM
+    from qwen25vl_lite.engine import benchmark as B
+
+    peaks = load_peaks()
+    cfg = json.loads(json.dumps(CONFIG_7B))
+    t = cfg["text_config"]
+    layers = args.layers or t["num_hidden_layers"]
+    full_layers, t["num_hidden_layers"] = t["num_hidden_layers"], layers
+    n_requests, context = 128, 8192
+    rng = np.random.default_rng(3)
+    prompt_lens = rng.integers(128, 4097, size=n_requests)
+    output_lens = rng.integers(32, 513, size=n_requests)
+    pages = int(sum(-(-(p + o) // PAGE) for p, o in zip(prompt_lens, output_lens))) + n_requests
+    llm = LLM(random_config=cfg, weights_seed=0, dtype="bfloat16", num_blocks=pages, block_size=PAGE, max_num_seqs=n_requests,
+              max_num_batched_tokens=2048, max_model_len=context, cuda_graph=not args.no_cuda_graph)
+    vocab = t["vocab_size"]
+    warm = B.random_prompts(rng, vocab, [300] * 4)
+    B.run_trace(llm.engine, warm, [8] * 4)                       # compile, allocate, touch every path once
+    prompts = B.random_prompts(rng, vocab, prompt_lens)
+    clocks = ClockSampler()
+    clocks.start()
+    launches0 = __import__("qwen25vl_lite.ops.kernels", fromlist=["x"]).launch_count()
+    r = B.run_trace(llm.engine, prompts, output_lens)
+    launches = __import__("qwen25vl_lite.ops.kernels", fromlist=["x"]).launch_count() - launches0
+    clock_record = clocks.stop()
+    flops = sum(B.prefill_flops(t, layers, int(p)) for p in prompt_lens)
+    kvb = B.kv_bytes_per_token(t, layers)
+    cache_bytes = sum(kvb * (int(p) * int(o) + int(o) * (int(o) - 1) // 2) for p, o in zip(prompt_lens, output_lens))
+    decode_steps = int(output_lens.max())                        # at least this many steps read the weights
+    ideal = flops / (peaks["bf16_tflops_sustained"] * 1e12) + (decode_steps * B.weight_bytes(t, layers) + cache_bytes) / (peaks["hbm_gbs"] * 1e9)
+    t["num_hidden_layers"] = full_layers
+    line = _base_line("generated tokens/s, Qwen2.5-VL-7B dims, continuous-batching trace of 128 requests",
+                      r["generated_tokens_per_s"], args, 1e3 * r["wall_s"] / max(r["steps"], 1), cfg, layers, n_requests,
+                      context, int(prompt_lens.mean()), peaks, {"chunk_budget": 2048})
+    line["config"]["model"] = "Qwen2.5-VL-7B text dims"
+    line["steps"], line["warmup"] = int(r["steps"]), 0
+    line.update({"gpu_launches": launches, "trace": r,
+                 "roofline": {"bound": "tensor (prompts) + hbm (decode steps)", "ideal_s": ideal, "wall_s": r["wall_s"],
+                              "frac": ideal / r["wall_s"]},
+                 "clocks": clock_record})
     print(json.dumps(line))
     return 0
 
@@ -348,6 +376,8 @@ def main(argv=None):
     ap.add_argument("--headline-only", action="store_true", help="skip e2e and the batch 1 / 64 points")
     ap.add_argument("--no-cuda-graph", action="store_true", help="launch decode steps kernel by kernel (for profilers)")
     ap.add_argument("--only-batch", type=int, default=0, help="time decode steps at this batch size only (for profilers)")
+    ap.add_argument("--config", default="3b", choices=["3b", "7b-trace", "32b"],
+                    help="3b: the headline line (default); 7b-trace, 32b: the other workloads, one line each")
     args = ap.parse_args(argv)
     if args.gpus != 1:
         print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not measured")
@@ -355,8 +385,11 @@ def main(argv=None):
     if args.warmup < 3:
         args.warmup = 3
     if args.impl == "reference":
+        if args.config != "3b":
+            print(json.dumps({"impl": "reference", "unavailable": "the reference arm measures the 3b configuration only"}))
+            return 0
         return run_reference(args)
-    return run_ours(args)
+    return {"3b": run_ours, "7b-trace": run_7b_trace, "32b": run_32b}[args.config](args)
 
 
 if __name__ == "__main__":

@@ -6,9 +6,11 @@ feature: ``--model --dtype --num-blocks --block-size --max-num-seqs
 --max-num-batched-tokens --max-model-len --no-chunked-prefill --prompt-token-ids
 --temperature --top-p --max-tokens`` (cli.py:634-673, 706-713); as there, a missing
 ``--prompt-token-ids`` prints a message and exits with 2 and the result is the printed list
-of generated ids (cli.py:267-278).  Added: ``--top-k --min-p --seed --ignore-eos`` and
-``random-model`` (writes a model folder from a config and a seed) and ``replay`` (trace
-replay).  The reference's quantisation, vision, prefix-cache, backend and server options
+of generated ids (cli.py:267-278).  Added: ``--top-k --min-p --seed --ignore-eos``;
+``--random-weights --weights-seed S`` (``--model`` then only has to hold a config.json: the
+weights are drawn on the device from the seed); ``random-model`` (writes a model folder from a
+config and a seed), ``replay`` (trace replay) and ``bench`` (one prefill and a run of decode
+steps, timed).  The reference's quantisation, vision, prefix-cache, backend and server options
 have no counterpart here.
 """
 
@@ -29,20 +31,31 @@ def _add_engine_options(p: argparse.ArgumentParser) -> None:
     p.add_argument("--max-num-batched-tokens", type=int, default=4096)
     p.add_argument("--max-model-len", type=int, default=32768)
     p.add_argument("--no-chunked-prefill", action="store_true")
+    p.add_argument("--random-weights", action="store_true",
+                   help="draw the weights from --weights-seed; --model then names a config.json or a folder with one")
+    p.add_argument("--weights-seed", type=int, default=0)
+
+
+def _llm(args):
+    from .engine.llm import LLM
+
+    options = dict(dtype=args.dtype, device=args.device, num_blocks=args.num_blocks, block_size=args.block_size,
+                   max_num_seqs=args.max_num_seqs, max_num_batched_tokens=args.max_num_batched_tokens,
+                   max_model_len=args.max_model_len, enable_chunked_prefill=not args.no_chunked_prefill)
+    if args.random_weights:
+        from .config.text_config import read_config_json
+        return LLM(random_config=read_config_json(args.model), weights_seed=args.weights_seed, **options)
+    return LLM(args.model, **options)
 
 
 def cmd_generate(args) -> int:
     if not args.prompt_token_ids:
         print("--prompt-token-ids is required (this CLI does not bundle a tokenizer)", file=sys.stderr)
         return 2
-    from .engine.llm import LLM
     from .sampling.params import SamplingParams
 
     ids = [int(t) for t in args.prompt_token_ids.split(",")]
-    llm = LLM(args.model, dtype=args.dtype, device=args.device, num_blocks=args.num_blocks,
-              block_size=args.block_size, max_num_seqs=args.max_num_seqs,
-              max_num_batched_tokens=args.max_num_batched_tokens, max_model_len=args.max_model_len,
-              enable_chunked_prefill=not args.no_chunked_prefill)
+    llm = _llm(args)
     params = SamplingParams(temperature=args.temperature, top_p=args.top_p, top_k=args.top_k, min_p=args.min_p,
                             max_tokens=args.max_tokens, seed=args.seed, ignore_eos=args.ignore_eos)
     outs = llm.generate([ids], params)
@@ -57,6 +70,18 @@ def cmd_random_model(args) -> int:
         config = json.load(fh)
     write_random_model(args.out, config, args.seed, args.storage_dtype)
     print(args.out)
+    return 0
+
+
+def cmd_bench(args) -> int:
+    from .engine.benchmark import quick_bench
+
+    need = args.batch * (-(-(args.prompt_len + args.steps + 16) // args.block_size))
+    args.num_blocks = max(args.num_blocks, need)
+    args.max_num_seqs = max(args.max_num_seqs, args.batch)
+    args.max_num_batched_tokens = max(args.max_num_batched_tokens, args.prompt_len)
+    args.max_model_len = max(args.max_model_len, args.prompt_len + args.steps + 16)
+    print(json.dumps(quick_bench(_llm(args), args.batch, args.prompt_len, args.steps)))
     return 0
 
 
@@ -85,6 +110,13 @@ def build_parser() -> argparse.ArgumentParser:
     p.add_argument("--seed", type=int, default=None)
     p.add_argument("--ignore-eos", action="store_true")
     p.set_defaults(func=cmd_generate)
+
+    p = sub.add_parser("bench", help="time one prefill and a run of decode steps; prints one JSON line")
+    _add_engine_options(p)
+    p.add_argument("--batch", type=int, default=8)
+    p.add_argument("--prompt-len", type=int, default=2048)
+    p.add_argument("--steps", type=int, default=64)
+    p.set_defaults(func=cmd_bench, dtype="bfloat16")
 
     p = sub.add_parser("random-model", help="write a model folder with random weights")
     p.add_argument("--config", required=True, help="a config.json")

@@ -34,6 +34,8 @@ class LayerSpec:
     feed_forward: PartSpec
     norms: Tuple[PartSpec, ...]
     prefix: str = ""
+    # the position encoding this layer's mixer applies; None: the model's (``ModelSpec.position``)
+    position: Optional[PartSpec] = None
 
 
 @dataclass(frozen=True)
@@ -53,6 +55,8 @@ class ModelSpec:
     schedule: Tuple[ScheduleEntry, ...]
     final_norm: PartSpec
     head: PartSpec
+    # defines the tokens' positions (how many axes, where plain text sits) and is what every layer
+    # applies that names no encoding of its own
     position: PartSpec
     # checkpoint naming: prefixes that may precede every decoder tensor name, tried in this
     # order, and prefixes of tensors that belong to parts this engine does not build.

@@ -136,6 +136,8 @@ __global__ void __launch_bounds__(ATTN_THREADS) attention_decode_kernel(AttnArgs
 }
 
 // out = sum_i 2^(m_i - M) O_i / sum_i 2^(m_i - M) l_i over the splits; one warp per (entry, head).
+// Any number of splits: the lanes stride over them for the maximum and the sum, and every lane
+// walks all of them for its channels (the weight of a split is a broadcast load and one exp2).
 template <int D>
 __global__ void attention_combine_kernel(AttnArgs a, int n_items) {
   pdl_trigger();
@@ -145,24 +147,25 @@ __global__ void attention_combine_kernel(AttnArgs a, int n_items) {
   const int item = w / a.nq, head = w - item * a.nq;
   const int token = a.cu_q[a.items[item]];
   const size_t base = ((size_t)item * a.nq + head) * a.n_splits;
-  // lanes over the splits for the maximum and the sum (n_splits <= 64), then over the channels
-  float m0 = lane < a.n_splits ? a.part_ml[(base + lane) * 2] : -INFINITY;
-  float m1 = lane + 32 < a.n_splits ? a.part_ml[(base + lane + 32) * 2] : -INFINITY;
-  const float M = warp_max(fmaxf(m0, m1));
-  const float w0 = m0 == -INFINITY ? 0.f : exp2f(m0 - M), w1 = m1 == -INFINITY ? 0.f : exp2f(m1 - M);
+  const float2* ml = reinterpret_cast<const float2*>(a.part_ml) + base;
+  float mx = -INFINITY;
+  for (int i = lane; i < a.n_splits; i += 32) mx = fmaxf(mx, ml[i].x);
+  const float M = warp_max(mx);
   float lpart = 0.f;
-  if (lane < a.n_splits) lpart += a.part_ml[(base + lane) * 2 + 1] * w0;
-  if (lane + 32 < a.n_splits) lpart += a.part_ml[(base + lane + 32) * 2 + 1] * w1;
+  for (int i = lane; i < a.n_splits; i += 32) {
+    const float2 v = ml[i];
+    if (v.x != -INFINITY) lpart += v.y * exp2f(v.x - M);
+  }
   const float inv = 1.0f / warp_sum(lpart);
-  for (int c0 = 0; c0 < D; c0 += 32) {      // every lane takes part in the shuffles, also past D
-    const int c = c0 + lane;
+  for (int c = lane; c < D; c += 32) {
     float acc = 0.f;
 #pragma unroll 4
     for (int i = 0; i < a.n_splits; ++i) {
-      const float wi = __shfl_sync(0xffffffffu, i < 32 ? w0 : w1, i & 31);
-      if (c < D) acc = fmaf(a.part_o[(base + i) * D + c], wi, acc);
+      const float mi = ml[i].x;
+      const float wi = mi == -INFINITY ? 0.f : exp2f(mi - M);
+      acc = fmaf(a.part_o[(base + i) * D + c], wi, acc);
     }
-    if (c < D) a.out[(size_t)token * a.nq * D + (size_t)head * D + c] = __float2bfloat16_rn(acc * inv);
+    a.out[(size_t)token * a.nq * D + (size_t)head * D + c] = __float2bfloat16_rn(acc * inv);
   }
 }
 

@@ -19,7 +19,9 @@
 //   * A call needs n_items * nq * n_splits * (head_dim + 2) floats when n_splits > 1 (none for one
 //     split).  A call that needs more than the array holds is refused: the function returns
 //     Q25_NOALLOC_TOO_LARGE and launches nothing; q25_attention_decode_noalloc_error() then gives
-//     a message with both numbers.  Use fewer splits, or the allocating entry point.
+//     a message with both numbers.  Use fewer splits, or the allocating entry point.  The number
+//     of splits itself has no limit of its own (the combine step walks any number of partials);
+//     the array's size is the only bound.
 //   * The first call on a device looks up the array's device address (cudaGetSymbolAddress, with
 //     that device current) and keeps it; later calls on that device reuse it.  Make that first
 //     call before any stream capture begins.

@@ -37,7 +37,6 @@
 #define A5_THREADS (A5_NROW + 32)             // and the warp that issues the products
 #define A5_BN 64
 #define A5_D 128
-#define A5_SMS 148                           // SMs of a B200
 #define A5_Q_BYTES (2 * A5_ROWS * 128)            // Q: two 64-value halves of 128 rows
 #define A5_KV_BYTES (2 * A5_BN * 128)             // two halves of 64 keys
 #define A5_SMEM (A5_Q_BYTES + 4 * A5_KV_BYTES + 2048 + 1024)  // Q, two K and two V tiles, barriers and key rows, room to align
@@ -113,7 +112,7 @@ struct A5Bars {
   unsigned tmem;
 };
 
-__global__ void __launch_bounds__(A5_THREADS, 2) attention_prefill_tcgen05_kernel(AttnArgs a, int* __restrict__ err) {
+__global__ void __launch_bounds__(A5_THREADS, 2) attention_prefill_tcgen05_kernel(AttnArgs a, int n_sms, int* __restrict__ err) {
   constexpr int NROW = A5_NROW, ROWS = A5_ROWS;         // one thread per row; the warp after them issues the products
   constexpr int TMEM_COLS = 256, O_COL = 128;           // two score buffers of 64 columns, then the outputs
   pdl_trigger();
@@ -133,8 +132,8 @@ __global__ void __launch_bounds__(A5_THREADS, 2) attention_prefill_tcgen05_kerne
   // of work, so that every SM gets a heavy and a light one (2,048 tokens in 256 pieces: the busiest
   // SM has 34 key tiles instead of 61).  Larger grids are taken in order: CTAs start as others end.
   const int n_work = gridDim.x;
-  const int work = (n_work > A5_SMS && n_work <= 2 * A5_SMS && (int)blockIdx.x >= A5_SMS)
-                       ? n_work - 1 - ((int)blockIdx.x - A5_SMS) : (int)blockIdx.x;
+  const int work = (n_work > n_sms && n_work <= 2 * n_sms && (int)blockIdx.x >= n_sms)
+                       ? n_work - 1 - ((int)blockIdx.x - n_sms) : (int)blockIdx.x;
   const int item = work / a.nkv, kvh = work - item * a.nkv;
   const int seq = a.items[2 * item], row_tile = a.items[2 * item + 1];
   const int G = a.nq / a.nkv;
@@ -150,18 +149,18 @@ __global__ void __launch_bounds__(A5_THREADS, 2) attention_prefill_tcgen05_kerne
   const int n_tiles = (c_hi - key_begin) / A5_BN + 1;
 
   if (tid == 0) {
-    tc5_mbar_init(bars->s_full, 1);
-    tc5_mbar_init(bars->s_full + 1, 1);
-    tc5_mbar_init(bars->k_full, NROW);
-    tc5_mbar_init(bars->k_full + 1, NROW);
-    tc5_mbar_init(bars->pv_ready, NROW);
-    tc5_mbar_init(bars->pv_ready + 1, NROW);
-    tc5_mbar_init(bars->pv_done, 1);
-    tc5_mbar_init(bars->pv_done + 1, 1);
+    mbar_init(bars->s_full, 1);
+    mbar_init(bars->s_full + 1, 1);
+    mbar_init(bars->k_full, NROW);
+    mbar_init(bars->k_full + 1, NROW);
+    mbar_init(bars->pv_ready, NROW);
+    mbar_init(bars->pv_ready + 1, NROW);
+    mbar_init(bars->pv_done, 1);
+    mbar_init(bars->pv_done + 1, 1);
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
   }
   if (warp == NROW / 32) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(tc5_s32(&bars->tmem)), "n"(TMEM_COLS) : "memory");
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_u32(&bars->tmem)), "n"(TMEM_COLS) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
   }
 
@@ -239,43 +238,43 @@ __global__ void __launch_bounds__(A5_THREADS, 2) attention_prefill_tcgen05_kerne
       const unsigned char* kt = k_s + (size_t)(t & 1) * A5_KV_BYTES;
 #pragma unroll
       for (int ks = 0; ks < A5_D / 16; ++ks) {            // 16 values of the head size per step: 32 bytes along a row
-        const unsigned long long ad = tc5_desc(tc5_s32(q_s) + (ks >> 2) * (A5_ROWS * 128) + (ks & 3) * 32, 16, 1024);
-        const unsigned long long bd = tc5_desc(tc5_s32(kt) + (ks >> 2) * (A5_BN * 128) + (ks & 3) * 32, 16, 1024);
+        const unsigned long long ad = tc5_desc(smem_u32(q_s) + (ks >> 2) * (A5_ROWS * 128) + (ks & 3) * 32, 16, 1024);
+        const unsigned long long bd = tc5_desc(smem_u32(kt) + (ks >> 2) * (A5_BN * 128) + (ks & 3) * 32, 16, 1024);
         tc5_mma(tmem_base + (unsigned)(t & 1) * A5_BN, ad, bd, idesc_s, ks != 0);
       }
       tc5_commit(bars->s_full + (t & 1));
     };
     auto fail = [&](int code) { ok = false; atomicExch(err, code); };
-    if (!tc5_mbar_wait(bars->k_full, 0)) fail(21);
+    if (!mbar_wait(bars->k_full, 0)) fail(21);
     tc5_fence_after();
     scores(0);
     if (n_tiles > 1) {
-      if (ok && !tc5_mbar_wait(bars->k_full + 1, 0)) fail(21);
+      if (ok && !mbar_wait(bars->k_full + 1, 0)) fail(21);
       tc5_fence_after();
       scores(1);
     }
     for (int t = 0; t < n_tiles; ++t) {
-      if (ok && !tc5_mbar_wait(bars->pv_ready + (t & 1), (unsigned)(t >> 1) & 1)) fail(22);
+      if (ok && !mbar_wait(bars->pv_ready + (t & 1), (unsigned)(t >> 1) & 1)) fail(22);
       tc5_fence_after();
       const unsigned char* vt = v_s + (size_t)(t & 1) * A5_KV_BYTES;
 #pragma unroll
       for (int ks = 0; ks < A5_BN / 16; ++ks) {           // 16 keys per step: 8 columns of P, 2 KB down V
-        const unsigned long long bd = tc5_desc(tc5_s32(vt) + ks * 2048, A5_BN * 128, 1024);
+        const unsigned long long bd = tc5_desc(smem_u32(vt) + ks * 2048, A5_BN * 128, 1024);
         tc5_mma_ts(tmem_base + O_COL, tmem_base + (unsigned)(t & 1) * A5_BN + ks * 8, bd, idesc_pv, (t | ks) != 0);
       }
       tc5_commit(bars->pv_done + (t & 1));
       if (t + 2 < n_tiles) {
         // the score buffer holds P(t) until this product is done; K(t + 2) was asked for a tile ago
-        if (ok && !tc5_mbar_wait(bars->pv_done + (t & 1), (unsigned)(t >> 1) & 1)) fail(23);
-        if (ok && !tc5_mbar_wait(bars->k_full + (t & 1), (unsigned)((t + 2) >> 1) & 1)) fail(21);
+        if (ok && !mbar_wait(bars->pv_done + (t & 1), (unsigned)(t >> 1) & 1)) fail(23);
+        if (ok && !mbar_wait(bars->k_full + (t & 1), (unsigned)((t + 2) >> 1) & 1)) fail(21);
         tc5_fence_after();
         scores(t + 2);
       }
     }
   } else if (tid < NROW) {
     // ---- the rows ----
-    tc5_mbar_arrive(bars->k_full);                         // K(0) and K(1), after the fence above
-    if (n_tiles > 1) tc5_mbar_arrive(bars->k_full + 1);
+    mbar_arrive(bars->k_full);                         // K(0) and K(1), after the fence above
+    if (n_tiles > 1) mbar_arrive(bars->k_full + 1);
     const unsigned t_lane = tmem_base + ((unsigned)(warp * 32) << 16);          // this warp's lanes: the score buffers
     const unsigned t_o = t_lane + O_COL;                                         // and the outputs
     // Running softmax with a lazy maximum: the exponentials use m_used, which follows the true maximum
@@ -290,7 +289,7 @@ __global__ void __launch_bounds__(A5_THREADS, 2) attention_prefill_tcgen05_kerne
     for (int tile = 0; tile < n_tiles; ++tile) {
       const int stage = tile & 1;
       const int key0 = key_begin + tile * A5_BN;
-      if (ok && !tc5_mbar_wait(bars->s_full + stage, (unsigned)(tile >> 1) & 1)) {
+      if (ok && !mbar_wait(bars->s_full + stage, (unsigned)(tile >> 1) & 1)) {
         ok = false;
         atomicExch(err, 24);
       }
@@ -346,7 +345,7 @@ __global__ void __launch_bounds__(A5_THREADS, 2) attention_prefill_tcgen05_kerne
         if (grow) m_used = mx;
         l *= factor;
         if (tile > 0) {                                    // the rows in tensor memory follow (warp-wide: lanes that keep theirs multiply by 1)
-          if (ok && !tc5_mbar_wait(bars->pv_done + (stage ^ 1), (unsigned)((tile - 1) >> 1) & 1)) {   // nobody adds to them meanwhile
+          if (ok && !mbar_wait(bars->pv_done + (stage ^ 1), (unsigned)((tile - 1) >> 1) & 1)) {   // nobody adds to them meanwhile
             ok = false;
             atomicExch(err, 25);
           }
@@ -385,10 +384,10 @@ __global__ void __launch_bounds__(A5_THREADS, 2) attention_prefill_tcgen05_kerne
       cp_async_wait<0>();
       tc5_proxy_fence();
       tc5_fence_before();
-      if (tile + 2 < n_tiles) tc5_mbar_arrive(bars->k_full + stage);
-      tc5_mbar_arrive(bars->pv_ready + stage);
+      if (tile + 2 < n_tiles) mbar_arrive(bars->k_full + stage);
+      mbar_arrive(bars->pv_ready + stage);
     }
-    if (ok && !tc5_mbar_wait(bars->pv_done + ((n_tiles - 1) & 1), (unsigned)((n_tiles - 1) >> 1) & 1)) {
+    if (ok && !mbar_wait(bars->pv_done + ((n_tiles - 1) & 1), (unsigned)((n_tiles - 1) >> 1) & 1)) {
       ok = false;
       atomicExch(err, 27);
     }
@@ -436,6 +435,7 @@ Q25_EXPORT int q25_attention_prefill_tcgen05_bf16(const void* qkv, int qkv_strid
   if (((uintptr_t)qkv & 15) || (qkv_stride % 8) || ((uintptr_t)out & 15)) return (int)cudaErrorInvalidValue;
   cudaError_t ce = cudaFuncSetAttribute(attention_prefill_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, A5_SMEM);
   if (ce != cudaSuccess) return (int)ce;
-  launch(attention_prefill_tcgen05_kernel, dim3(n_tiles * nkv), dim3(A5_THREADS), (size_t)A5_SMEM, (cudaStream_t)stream, a, err);
+  launch(attention_prefill_tcgen05_kernel, dim3(n_tiles * nkv), dim3(A5_THREADS), (size_t)A5_SMEM, (cudaStream_t)stream, a,
+         device_sm_count(), err);
   return launch_status();
 }

@@ -54,6 +54,40 @@ __device__ __forceinline__ float block_sum(float v, float* scratch) {
   return total;
 }
 
+// ---- shared memory addresses, mbarriers, bulk copies -------------------------------------------------
+// Thin wrappers of the PTX that every kernel with asynchronous copies uses.  A wait on an mbarrier
+// polls at most MBAR_WAIT_LIMIT times and says whether the phase completed: the caller records an
+// error code and runs on to its end.  A parity wait cannot tell "not yet" from "two phases on" (nor
+// from "a phase behind"), so a waiter must stay within one phase of its barrier.
+#define MBAR_WAIT_LIMIT (1 << 22)
+
+__device__ __forceinline__ unsigned smem_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(unsigned long long* bar, int count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(unsigned long long* bar, unsigned bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(unsigned long long* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ bool mbar_wait(unsigned long long* bar, unsigned parity) {
+  for (int i = 0; i < MBAR_WAIT_LIMIT; ++i) {
+    unsigned done;
+    asm volatile(
+        "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
+        : "=r"(done) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+    if (done) return true;
+  }
+  return false;
+}
+// One contiguous piece of global memory into shared memory (both 16-byte aligned, a multiple of 16
+// bytes); the bytes are counted on the mbarrier.
+__device__ __forceinline__ void bulk_copy(void* dst, const void* src, unsigned bytes, unsigned long long* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n"
+               ::"r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar)) : "memory");
+}
+
 // ---- programmatic dependent launch -----------------------------------------------------------------
 // Every kernel of the engine is launched with the attribute that lets it be scheduled while the
 // kernel before it in the stream is still running; it calls pdl_trigger() at its top (the next one
@@ -93,6 +127,20 @@ static inline void launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_
   cfg.numAttrs = 1;
   const cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
   if (e != cudaSuccess && q25_launch_error == cudaSuccess) q25_launch_error = e;
+}
+
+// Streaming multiprocessors of the current device (asked once per device): persistent grids and
+// split heuristics are sized from it.  148 on the B200 the kernels were tuned on.
+static inline int device_sm_count() {
+  static int known[64];
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 0;
+  if (known[dev] == 0) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return 0;
+    known[dev] = n;
+  }
+  return known[dev];
 }
 
 // Error of the launches since the last call (0 = none).

@@ -141,7 +141,8 @@ static int silu_mul(const void* gu, void* out, int n, int inter, int paired, voi
   if (n <= 0) return 0;
   const size_t total = (size_t)n * inter;
   size_t blocks = (total + 255) / 256;
-  if (blocks > 148 * 16) blocks = 148 * 16;
+  const size_t most = (size_t)(device_sm_count() > 0 ? device_sm_count() : 148) * 16;
+  if (blocks > most) blocks = most;
   launch(silu_mul_kernel<T>, dim3((unsigned)blocks), dim3(256), 0, (cudaStream_t)stream, (const T*)gu, (T*)out, n, inter, paired);
   return launch_status();
 }
@@ -152,3 +153,6 @@ Q25_EXPORT int q25_add_rmsnorm_f32(float* x, const void* d, const float* w, floa
 Q25_EXPORT int q25_add_rmsnorm_bf16(float* x, const void* d, const float* w, float eps, void* o, const int* rows, int n, int h, void* s) { return add_rmsnorm<bf16, false>(x, d, w, eps, o, rows, n, h, s); }
 Q25_EXPORT int q25_silu_mul_f32(const void* gu, void* o, int n, int inter, int paired, void* s) { return silu_mul<float>(gu, o, n, inter, paired, s); }
 Q25_EXPORT int q25_silu_mul_bf16(const void* gu, void* o, int n, int inter, int paired, void* s) { return silu_mul<bf16>(gu, o, n, inter, paired, s); }
+
+// Streaming multiprocessors of the current device (0 if it cannot be read).
+Q25_EXPORT int q25_sm_count(void) { return device_sm_count(); }

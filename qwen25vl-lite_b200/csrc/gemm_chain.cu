@@ -30,15 +30,9 @@
 //     have counted themselves in, adds them in slice order and runs the epilogue.  Either way the
 //     result does not depend on timing.
 //
-//   * The decode attention between a layer's qkv and o products is an operation of the chain too
-//     (the unit of attention_decode.cuh run by the eight MMA warps on 16-key tiles, in the shared
-//     memory that x otherwise takes): a layer is then one stretch of one kernel, the warps start
-//     the copies of their first key tiles while they still wait for the qkv product of the other
-//     CTAs, and the producer warp fills the ring with the o and gate/up weights meanwhile.
-//
 // Every wait (mbarrier or grid barrier) is bounded: when it gives up, the kernel records a code in
 // *err, stops waiting anywhere and runs to its end (its output is then invalid).
-#include "attention_decode.cuh"
+#include "common.cuh"
 
 enum { EPI_STORE = 0, EPI_BIAS = 1, EPI_F32 = 2, EPI_SWIGLU = 3, EPI_RESIDUAL = 4 };
 
@@ -50,9 +44,7 @@ enum { EPI_STORE = 0, EPI_BIAS = 1, EPI_F32 = 2, EPI_SWIGLU = 3, EPI_RESIDUAL = 
 #define GC_SLICE_K 2048                          // most K elements of a slice
 #define GC_PITCH (GC_SLICE_K * 2 + 64)           // bytes between rows in shared memory; mod 128 = 64: no bank conflicts
 #define GC_SLOT (GC_ROWS * GC_PITCH)             // one stage: the 16 rows of a group, one slice long
-#define GC_SMS 148
 #define GC_SMEM_LIMIT (227 * 1024)
-#define GC_WAIT_LIMIT (1 << 22)
 #define GC_GRID_WAIT_LIMIT (1 << 21)             // polls of global memory, about a second
 
 struct ChainOp {
@@ -65,15 +57,11 @@ struct ChainOp {
   float eps;
   int slices, slice_k, ctas, groups;   // K cut into `slices` of `slice_k` elements; `ctas` CTAs work in each slice
   int seq;                // 1: the K slices are taken one after the other by the same CTA (see below)
-  int kind;               // 0: a product (the fields above); 1: decode attention (the fields below)
-  int attn_d, attn_units; // head size; units = entries x kv heads x key ranges
-  AttnArgs attn;
-  RopeArgs rope;
 };
 
 struct ChainArgs {
   int n_ops, n_stages;
-  int x_off;              // where x (and the attention unit's memory) begins in shared memory
+  int x_off;              // where x begins in shared memory
   float* scratch;         // slots of partial sums, [slice][group][MT * 128] floats, reused by every operation
   int* counters;          // one per group, zero before the launch and after it
   unsigned* barrier;      // arrivals at the barriers between operations; only grows
@@ -82,33 +70,16 @@ struct ChainArgs {
   ChainOp op[GC_MAX_OPS];
 };
 
-__device__ __forceinline__ unsigned gc_s32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
-__device__ __forceinline__ void gc_mbar_init(unsigned long long* bar, int count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(gc_s32(bar)), "r"(count));
+// cp.async of 16 bytes (zeros when !valid) and its group bookkeeping: x slices of the sequential K walk
+__device__ __forceinline__ void cp_async16(void* dst, const void* src, bool valid) {
+  const int n = valid ? 16 : 0;
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(smem_u32(dst)), "l"(src), "r"(n));
 }
-__device__ __forceinline__ void gc_expect_tx(unsigned long long* bar, unsigned bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(gc_s32(bar)), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void gc_arrive(unsigned long long* bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(gc_s32(bar)) : "memory");
-}
-__device__ __forceinline__ bool gc_wait(unsigned long long* bar, unsigned parity) {
-  for (int i = 0; i < GC_WAIT_LIMIT; ++i) {
-    unsigned done;
-    asm volatile(
-        "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
-        : "=r"(done) : "r"(gc_s32(bar)), "r"(parity) : "memory");
-    if (done) return true;
-  }
-  return false;
-}
-__device__ __forceinline__ void gc_bulk_copy(void* dst, const void* src, unsigned bytes, unsigned long long* bar) {
-  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n"
-               ::"r"(gc_s32(dst)), "l"(src), "r"(bytes), "r"(gc_s32(bar)) : "memory");
-}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
 __device__ __forceinline__ uint4 gc_lds128(const void* p) {
   uint4 v;
-  asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];\n" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(gc_s32(p)));
+  asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];\n" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(smem_u32(p)));
   return v;
 }
 __device__ __forceinline__ float4 gc_ldcg128(const float* p) {
@@ -165,13 +136,11 @@ __device__ __forceinline__ void gc_store_group(const float (&acc)[MT][4], int gr
   }
 }
 
-// ATTN: whether the kernel can run attention operations (a variant of its own, so that their
-// registers and code do not weigh on chains of products alone).
-template <int MT, bool ATTN>
+template <int MT>
 __global__ void __launch_bounds__(GC_THREADS, 1) gemm_chain_kernel(const __grid_constant__ ChainArgs A) {
   extern __shared__ __align__(128) unsigned char smem[];
   const int S = A.n_stages;
-  unsigned char* xs = smem + A.x_off;             // x of a product, or the memory of an attention unit
+  unsigned char* xs = smem + A.x_off;             // x of a product
   unsigned char* slots = smem;
   float* red = reinterpret_cast<float*>(slots + (size_t)S * GC_SLOT);
   unsigned long long* full = reinterpret_cast<unsigned long long*>(red + GC_RED_BUFS * GC_CONSUMERS * 32 * MT * 4);
@@ -185,13 +154,13 @@ __global__ void __launch_bounds__(GC_THREADS, 1) gemm_chain_kernel(const __grid_
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < S; ++s) {
-      gc_mbar_init(full + s, 1);
-      gc_mbar_init(empty + s, GC_CONSUMERS);
+      mbar_init(full + s, 1);
+      mbar_init(empty + s, GC_CONSUMERS);
     }
-    gc_mbar_init(go, 1);
+    mbar_init(go, 1);
     for (int b = 0; b < GC_RED_BUFS; ++b) {
-      gc_mbar_init(red_full + b, GC_CONSUMERS);
-      gc_mbar_init(red_empty + b, 1);
+      mbar_init(red_full + b, GC_CONSUMERS);
+      mbar_init(red_empty + b, 1);
     }
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
   }
@@ -204,21 +173,20 @@ __global__ void __launch_bounds__(GC_THREADS, 1) gemm_chain_kernel(const __grid_
     unsigned parity = 1;
     for (int k = 0; k < A.n_ops; ++k) {
       const ChainOp& op = A.op[k];
-      if (op.kind) continue;                         // attention streams no weights
       if (op.seq) {
         for (int grp = cta; grp < op.groups; grp += op.ctas) {
           for (int j = 0; j < op.slices; ++j) {
             const int k0 = j * op.slice_k;
             const unsigned bytes = (unsigned)min(op.slice_k, op.K - k0) * 2;
             if (wrapped && ok) {
-              ok = gc_wait(empty + s, parity);
+              ok = mbar_wait(empty + s, parity);
               if (!ok && lane == 0) atomicExch(A.err, 11);
             }
             unsigned char* st = slots + (size_t)s * GC_SLOT;
-            if (lane == 0) gc_expect_tx(full + s, bytes * GC_ROWS);
+            if (lane == 0) mbar_expect_tx(full + s, bytes * GC_ROWS);
             __syncwarp();
             if (lane < GC_ROWS)
-              gc_bulk_copy(st + lane * GC_PITCH, op.W + (size_t)min(grp * GC_ROWS + lane, op.N - 1) * op.K + k0, bytes, full + s);
+              bulk_copy(st + lane * GC_PITCH, op.W + (size_t)min(grp * GC_ROWS + lane, op.N - 1) * op.K + k0, bytes, full + s);
             if (++s == S) { s = 0; wrapped = 1; parity ^= 1; }
           }
         }
@@ -230,14 +198,14 @@ __global__ void __launch_bounds__(GC_THREADS, 1) gemm_chain_kernel(const __grid_
       const unsigned bytes = (unsigned)min(op.slice_k, op.K - k0) * 2;
       for (int grp = r; grp < op.groups; grp += op.ctas) {
         if (wrapped && ok) {
-          ok = gc_wait(empty + s, parity);
+          ok = mbar_wait(empty + s, parity);
           if (!ok && lane == 0) atomicExch(A.err, 11);
         }
         unsigned char* st = slots + (size_t)s * GC_SLOT;
-        if (lane == 0) gc_expect_tx(full + s, bytes * GC_ROWS);
+        if (lane == 0) mbar_expect_tx(full + s, bytes * GC_ROWS);
         __syncwarp();
         if (lane < GC_ROWS)
-          gc_bulk_copy(st + lane * GC_PITCH, op.W + (size_t)min(grp * GC_ROWS + lane, op.N - 1) * op.K + k0, bytes, full + s);
+          bulk_copy(st + lane * GC_PITCH, op.W + (size_t)min(grp * GC_ROWS + lane, op.N - 1) * op.K + k0, bytes, full + s);
         if (++s == S) { s = 0; wrapped = 1; parity ^= 1; }
       }
     }
@@ -267,20 +235,9 @@ __global__ void __launch_bounds__(GC_THREADS, 1) gemm_chain_kernel(const __grid_
             while ((int)(gc_ld_acquire(A.barrier) - target) < 0 && ++i < GC_GRID_WAIT_LIMIT) {}
             if (i >= GC_GRID_WAIT_LIMIT) { ok = false; atomicExch(A.err, 16); }
           }
-          gc_arrive(go);
+          mbar_arrive(go);
         }
         ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
-      }
-      if (op.kind) {
-        // attention: the MMA warps do everything and say so through the ring of partial-sum buffers
-        if (ok) {
-          ok = gc_wait(red_full + rb, red_parity);
-          if (!ok && lane == 0) atomicExch(A.err, 19);
-        }
-        __syncwarp();
-        if (lane == 0) gc_arrive(red_empty + rb);
-        if (++rb == GC_RED_BUFS) { rb = 0; red_parity ^= 1; }
-        continue;
       }
       const bool sliced = op.slices > 1 && !op.seq;    // the slices are other CTAs' and meet in scratch memory
       const int slice = op.seq ? 0 : cta / op.ctas, r = op.seq ? cta : cta - slice * op.ctas;
@@ -301,7 +258,7 @@ __global__ void __launch_bounds__(GC_THREADS, 1) gemm_chain_kernel(const __grid_
             }
         }
         if (ok) {
-          ok = gc_wait(red_full + rb, red_parity);
+          ok = mbar_wait(red_full + rb, red_parity);
           if (!ok && lane == 0) atomicExch(A.err, 15);
         }
 #pragma unroll
@@ -314,7 +271,7 @@ __global__ void __launch_bounds__(GC_THREADS, 1) gemm_chain_kernel(const __grid_
           }
         }
         __syncwarp();
-        if (lane == 0) gc_arrive(red_empty + rb);
+        if (lane == 0) mbar_arrive(red_empty + rb);
         if (++rb == GC_RED_BUFS) { rb = 0; red_parity ^= 1; }
 
         if (sliced) {
@@ -395,41 +352,8 @@ __global__ void __launch_bounds__(GC_THREADS, 1) gemm_chain_kernel(const __grid_
   auto consumer_sync = [] { asm volatile("bar.sync 1, %0;\n" ::"n"(GC_CONSUMERS * 32) : "memory"); };
   for (int k = 0; k < A.n_ops; ++k) {
     const ChainOp& op = A.op[k];
-    if (ATTN && op.kind) {
-      // ---- decode attention: unit u = (entry, kv head, key range) on CTA u, u + grid, ... ----
-      const int per_item = op.attn.nkv * op.attn.n_splits;
-      consumer_sync();                               // every warp is done with x of the product before
-      int u = cta;
-      if (u < op.attn_units) {                       // the first tiles hold keys of earlier steps: no need to wait
-        if (op.attn_d == 128) DecodeUnit<128, GC_CONSUMERS, 16, 1>::prefetch(op.attn, u / per_item, (u / op.attn.n_splits) % op.attn.nkv, u % op.attn.n_splits, xs, ctid);
-        else DecodeUnit<64, GC_CONSUMERS, 16, 1>::prefetch(op.attn, u / per_item, (u / op.attn.n_splits) % op.attn.nkv, u % op.attn.n_splits, xs, ctid);
-      }
-      if (k > 0 && ok) {
-        ok = gc_wait(go, (unsigned)(k - 1) & 1);
-        if (!ok && lane == 0) atomicExch(A.err, 12);
-      }
-      for (; u < op.attn_units; u += gridDim.x) {
-        const int item = u / per_item, kvh = (u / op.attn.n_splits) % op.attn.nkv, split = u % op.attn.n_splits;
-        if (u != cta) {
-          consumer_sync();
-          if (op.attn_d == 128) DecodeUnit<128, GC_CONSUMERS, 16, 1>::prefetch(op.attn, item, kvh, split, xs, ctid);
-          else DecodeUnit<64, GC_CONSUMERS, 16, 1>::prefetch(op.attn, item, kvh, split, xs, ctid);
-        }
-        if (op.attn_d == 128) DecodeUnit<128, GC_CONSUMERS, 16, 1>::run(op.attn, op.rope, item, kvh, split, xs, ctid, consumer_sync);
-        else DecodeUnit<64, GC_CONSUMERS, 16, 1>::run(op.attn, op.rope, item, kvh, split, xs, ctid, consumer_sync);
-      }
-      __threadfence();                               // what this warp wrote, before the CTA says it is done
-      if (red_wrapped && ok) {
-        ok = gc_wait(red_empty + rb, red_parity);
-        if (!ok && lane == 0) atomicExch(A.err, 17);
-      }
-      __syncwarp();
-      if (lane == 0) gc_arrive(red_full + rb);
-      if (++rb == GC_RED_BUFS) { rb = 0; red_wrapped = true; red_parity ^= 1; }
-      continue;
-    }
     if (k > 0 && ok) {
-      ok = gc_wait(go, (unsigned)(k - 1) & 1);
+      ok = mbar_wait(go, (unsigned)(k - 1) & 1);
       if (!ok && lane == 0) atomicExch(A.err, 12);
     }
     if (op.seq) {
@@ -465,7 +389,7 @@ __global__ void __launch_bounds__(GC_THREADS, 1) gemm_chain_kernel(const __grid_
         const unsigned char* xb = xs + (size_t)(item & 1) * xbuf_bytes + t * 16;
         const int kblocks = min(op.slice_k, op.K - j * op.slice_k) / 32;
         if (ok) {
-          ok = gc_wait(full + s, parity);
+          ok = mbar_wait(full + s, parity);
           if (!ok && lane == 0) atomicExch(A.err, 14);
         }
         const unsigned char* st = slots + (size_t)s * GC_SLOT + g * GC_PITCH + t * 16;
@@ -481,12 +405,12 @@ __global__ void __launch_bounds__(GC_THREADS, 1) gemm_chain_kernel(const __grid_
           }
         }
         __syncwarp();
-        if (lane == 0) gc_arrive(empty + s);
+        if (lane == 0) mbar_arrive(empty + s);
         if (++s == S) { s = 0; parity ^= 1; }
         if (j + 1 < op.slices) continue;
         // the group is complete: hand the sums to the epilogue warp
         if (red_wrapped && ok) {
-          ok = gc_wait(red_empty + rb, red_parity);
+          ok = mbar_wait(red_empty + rb, red_parity);
           if (!ok && lane == 0) atomicExch(A.err, 17);
         }
         float* dst = red + (((size_t)rb * GC_CONSUMERS + warp) * 32 + lane) * MT * 4;
@@ -495,7 +419,7 @@ __global__ void __launch_bounds__(GC_THREADS, 1) gemm_chain_kernel(const __grid_
           *reinterpret_cast<float4*>(dst + mt * 4) = make_float4(acc[0][mt][0] + acc[1][mt][0], acc[0][mt][1] + acc[1][mt][1],
                                                                  acc[0][mt][2] + acc[1][mt][2], acc[0][mt][3] + acc[1][mt][3]);
         __syncwarp();
-        if (lane == 0) gc_arrive(red_full + rb);
+        if (lane == 0) mbar_arrive(red_full + rb);
         if (++rb == GC_RED_BUFS) { rb = 0; red_wrapped = true; red_parity ^= 1; }
       }
       consumer_sync();                                // x of the next operation goes where these buffers are
@@ -610,7 +534,7 @@ __global__ void __launch_bounds__(GC_THREADS, 1) gemm_chain_kernel(const __grid_
 #pragma unroll
         for (int mt = 0; mt < MT; ++mt) acc[j][mt][0] = acc[j][mt][1] = acc[j][mt][2] = acc[j][mt][3] = 0.f;
       if (ok) {
-        ok = gc_wait(full + s, parity);
+        ok = mbar_wait(full + s, parity);
         if (!ok && lane == 0) atomicExch(A.err, 14);
       }
       const unsigned char* st = slots + (size_t)s * GC_SLOT + g * GC_PITCH + t * 16;
@@ -626,12 +550,12 @@ __global__ void __launch_bounds__(GC_THREADS, 1) gemm_chain_kernel(const __grid_
         }
       }
       __syncwarp();
-      if (lane == 0) gc_arrive(empty + s);
+      if (lane == 0) mbar_arrive(empty + s);
       if (++s == S) { s = 0; parity ^= 1; }
 
       // hand the partial sums to the epilogue warp
       if (red_wrapped && ok) {
-        ok = gc_wait(red_empty + rb, red_parity);
+        ok = mbar_wait(red_empty + rb, red_parity);
         if (!ok && lane == 0) atomicExch(A.err, 17);
       }
       float* dst = red + (((size_t)rb * GC_CONSUMERS + warp) * 32 + lane) * MT * 4;
@@ -640,7 +564,7 @@ __global__ void __launch_bounds__(GC_THREADS, 1) gemm_chain_kernel(const __grid_
         *reinterpret_cast<float4*>(dst + mt * 4) = make_float4(acc[0][mt][0] + acc[1][mt][0], acc[0][mt][1] + acc[1][mt][1],
                                                                acc[0][mt][2] + acc[1][mt][2], acc[0][mt][3] + acc[1][mt][3]);
       __syncwarp();
-      if (lane == 0) gc_arrive(red_full + rb);
+      if (lane == 0) mbar_arrive(red_full + rb);
       if (++rb == GC_RED_BUFS) { rb = 0; red_wrapped = true; red_parity ^= 1; }
     }
   }
@@ -649,7 +573,6 @@ __global__ void __launch_bounds__(GC_THREADS, 1) gemm_chain_kernel(const __grid_
 // ------------------------------------------------------------------------------------------------
 // The description of one operation as the caller gives it (plain C layout, read through ctypes).
 struct ChainOpDesc {
-  // kind 0: a product
   const void* W;
   const void* X;
   const float* norm_w;
@@ -657,50 +580,12 @@ struct ChainOpDesc {
   void* out;
   int ldx, ldo, M, N, K, epi, norm;
   float eps;
-  int kind;
-  // kind 1: decode attention, the arguments of q25_attention_decode_fused_bf16
-  const void* qkv;
-  void* attn_out;
-  void* kpages;
-  void* vpages;
-  const int* block_table;
-  const int* cu_q;
-  const int* q_start;
-  const int* items;
-  const int* positions;
-  const float* inv_freq;
-  const int* axis;
-  const int* kv_slot;
-  float* attn_scratch;
-  int* attn_counters;
-  const void* angles;
-  int qkv_stride, table_width, n_items, nq, nkv, d, page_size, window, n_splits, n_tokens;
-  float scale;
   int reserved;
 };
 
 static bool chain_cut(const ChainOpDesc& d, ChainOp& op) {
-  op.kind = d.kind;
-  if (d.kind == 1) {
-    if (d.n_items <= 0 || (d.d != 64 && d.d != 128)) return false;
-    if (fill_args(op.attn, d.qkv, d.qkv_stride, d.attn_out, d.kpages, d.vpages, d.block_table, d.table_width, d.cu_q,
-                  d.q_start, d.items, d.nq, d.nkv, d.page_size, d.window, d.scale))
-      return false;
-    if (d.nq / d.nkv > 16 || d.n_splits < 1 || d.n_splits > 64 || !d.positions || !d.inv_freq || !d.axis || !d.kv_slot ||
-        (d.n_splits > 1 && (!d.attn_scratch || !d.attn_counters)))
-      return false;
-    op.attn.n_splits = d.n_splits;
-    op.attn.part_o = d.attn_scratch;
-    op.attn.part_ml = d.attn_scratch ? d.attn_scratch + (size_t)d.n_items * d.nq * d.n_splits * d.d : nullptr;
-    op.rope.positions = d.positions; op.rope.n_tokens = d.n_tokens; op.rope.inv_freq = d.inv_freq; op.rope.axis = d.axis;
-    op.rope.kv_slot = d.kv_slot; op.rope.kpages_w = (bf16*)d.kpages; op.rope.vpages_w = (bf16*)d.vpages;
-    op.rope.counters = d.attn_counters; op.rope.angles = (const float2*)d.angles;
-    op.attn_d = d.d;
-    op.attn_units = d.n_items * d.nkv * d.n_splits;
-    op.slices = 1; op.slice_k = 0; op.ctas = GC_SMS; op.groups = 0; op.M = 0; op.seq = 0;
-    return true;
-  }
-  if (d.kind != 0) return false;
+  const int sms = device_sm_count();
+  if (sms <= 0) return false;
   if (d.M <= 0 || d.M > 16 || d.N <= 0 || d.K <= 0 || d.K % 32) return false;
   if (((unsigned long long)d.W & 15) || ((unsigned long long)d.X & 15)) return false;
   if (d.norm ? (d.ldx % 4 || !d.norm_w) : (d.ldx % 8 != 0)) return false;
@@ -710,24 +595,21 @@ static bool chain_cut(const ChainOpDesc& d, ChainOp& op) {
   op.groups = (d.N + GC_ROWS - 1) / GC_ROWS;
   op.slices = (d.K + GC_SLICE_K - 1) / GC_SLICE_K;
   op.slice_k = ((d.K + op.slices - 1) / op.slices + 31) / 32 * 32;      // nearly equal slices, whole k blocks
-  if (op.slices > GC_SMS || (long long)(op.slices - 1) * op.slice_k >= d.K) return false;
-  op.ctas = GC_SMS / op.slices;
+  if (op.slices > sms || (long long)(op.slices - 1) * op.slice_k >= d.K) return false;
+  op.ctas = sms / op.slices;
   if (op.ctas > op.groups) op.ctas = op.groups;
   // few groups per CTA, no norm, at most 8 rows (two x buffers fit): the slices one after the other
-  op.seq = (op.slices > 1 && !d.norm && d.M <= 8 && op.groups <= 2 * GC_SMS) ? 1 : 0;
-  if (op.seq) op.ctas = op.groups < GC_SMS ? op.groups : GC_SMS;
-  op.attn_d = 0; op.attn_units = 0;
+  op.seq = (op.slices > 1 && !d.norm && d.M <= 8 && op.groups <= 2 * sms) ? 1 : 0;
+  if (op.seq) op.ctas = op.groups < sms ? op.groups : sms;
   return true;
 }
 
 // Shared memory of the kernel: the ring of stages, the partial-sum buffers and the barriers, then
-// room for x of up to `rows` rows (8 or 16) or, with an attention operation, for its unit.
-static int chain_smem(int rows, bool attention, bool two_x_buffers, int& n_stages, int& x_off) {
+// room for x of up to `rows` rows (8 or 16).
+static int chain_smem(int rows, bool two_x_buffers, int& n_stages, int& x_off) {
   const int MT = rows <= 8 ? 1 : 2;
   int tail = rows * GC_PITCH;
   if (two_x_buffers) tail = 2 * ((8 * GC_PITCH + 127) / 128 * 128);
-  const int unit = DecodeUnit<128, GC_CONSUMERS, 16, 1>::SMEM;
-  if (attention && tail < unit) tail = unit;
   const int red = GC_RED_BUFS * GC_CONSUMERS * 32 * MT * 4 * (int)sizeof(float);
   const int bars = 1024;
   n_stages = (GC_SMEM_LIMIT - tail - red - bars) / GC_SLOT;
@@ -742,7 +624,7 @@ Q25_EXPORT long long q25_gemm_chain_scratch_floats(const ChainOpDesc* ops, int n
   for (int i = 0; i < n_ops; ++i) {
     ChainOp op;
     if (!chain_cut(ops[i], op)) return -1;
-    if (op.kind == 0 && op.slices > 1 && !op.seq) {
+    if (op.slices > 1 && !op.seq) {
       const long long need = (long long)op.slices * op.groups * (ops[i].M <= 8 ? 1 : 2) * 128;
       if (need > most) most = need;
     }
@@ -759,18 +641,21 @@ Q25_EXPORT int q25_gemm_chain_available(void) {
   cudaDeviceGetAttribute(&coop, cudaDevAttrCooperativeLaunch, dev);
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   cudaDeviceGetAttribute(&smem, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev);
-  known = (coop && sms >= GC_SMS && smem >= GC_SMEM_LIMIT) ? 1 : 0;
+  known = (coop && sms > 0 && smem >= GC_SMEM_LIMIT) ? 1 : 0;
   return known;
 }
 
 // Size of the description struct, so that a caller that builds it elsewhere can check its layout.
 Q25_EXPORT int q25_gemm_chain_desc_bytes(void) { return (int)sizeof(ChainOpDesc); }
 
-// Runs ops[0 .. n_ops) (at most 8; products of at most 16 rows, decode attentions of head size 64 or
-// 128) as one kernel; every operation may read what the ones before it wrote.  scratch:
-// q25_gemm_chain_scratch_floats() floats; counters: 65536 ints, zero; barrier: one unsigned int whose
-// value when the launch begins is barrier_base (each launch adds (n_ops - 1) * 148 to it); err: one
-// int that receives a nonzero code if a wait gave up.
+// CTAs of the kernel: one per SM of the current device.
+Q25_EXPORT int q25_gemm_chain_grid(void) { return device_sm_count(); }
+
+// Runs ops[0 .. n_ops) (at most 8 products of at most 16 rows) as one kernel; every operation may
+// read what the ones before it wrote.  scratch: q25_gemm_chain_scratch_floats() floats; counters:
+// 65536 ints, zero; barrier: one unsigned int whose value when the launch begins is barrier_base
+// (each launch adds (n_ops - 1) * q25_gemm_chain_grid() to it); err: one int that receives a
+// nonzero code if a wait gave up.
 Q25_EXPORT int q25_gemm_chain_bf16(const ChainOpDesc* ops, int n_ops, float* scratch, int* counters, unsigned* barrier,
                                    unsigned barrier_base, int* err, void* stream) {
   if (n_ops <= 0) return 0;
@@ -779,23 +664,21 @@ Q25_EXPORT int q25_gemm_chain_bf16(const ChainOpDesc* ops, int n_ops, float* scr
   A.n_ops = n_ops;
   A.scratch = scratch; A.counters = counters; A.barrier = barrier; A.barrier_base = barrier_base; A.err = err;
   int rows = 0;
-  bool attention = false, seq = false;
+  bool seq = false;
   for (int i = 0; i < n_ops; ++i) {
     if (!chain_cut(ops[i], A.op[i])) return (int)cudaErrorInvalidValue;
-    if (A.op[i].kind) { attention = true; continue; }
     if (A.op[i].seq) seq = true;
     if (A.op[i].groups > 65536 || (A.op[i].slices > 1 && !A.op[i].seq && !scratch)) return (int)cudaErrorInvalidValue;
     if (ops[i].M > rows) rows = ops[i].M;
   }
   rows = rows <= 8 ? 8 : 16;
-  const int total = chain_smem(rows, attention, seq, A.n_stages, A.x_off);
+  const int total = chain_smem(rows, seq, A.n_stages, A.x_off);
   if (A.n_stages < 2) return (int)cudaErrorInvalidValue;
-  void (*kernel)(const ChainArgs) = attention ? (rows <= 8 ? gemm_chain_kernel<1, true> : gemm_chain_kernel<2, true>)
-                                              : (rows <= 8 ? gemm_chain_kernel<1, false> : gemm_chain_kernel<2, false>);
+  void (*kernel)(const ChainArgs) = rows <= 8 ? gemm_chain_kernel<1> : gemm_chain_kernel<2>;
   cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, total);
   if (e != cudaSuccess) return (int)e;
   cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(GC_SMS);
+  cfg.gridDim = dim3(device_sm_count());
   cfg.blockDim = dim3(GC_THREADS);
   cfg.dynamicSmemBytes = (size_t)total;
   cfg.stream = (cudaStream_t)stream;

@@ -21,7 +21,7 @@
 //     8 gate features followed by their 8 up features, so silu(gate) * up is formed in registers
 //     (reference formula src/qwen25vl_lite/text.py:66).
 //
-// Every wait on an mbarrier is bounded: after WAIT_LIMIT polls the kernel records an error code in
+// Every wait on an mbarrier is bounded: after MBAR_WAIT_LIMIT polls the kernel records an error code in
 // *err, stops waiting anywhere, and runs to its end (its output is then invalid).
 #include "common.cuh"
 
@@ -31,41 +31,12 @@ enum { EPI_STORE = 0, EPI_BIAS = 1, EPI_F32 = 2, EPI_SWIGLU = 3, EPI_RESIDUAL = 
 #define GS_CONSUMERS 8
 #define GS_RED_BUFS 2                    // buffers of partial sums between the MMA warps and the epilogue warp
 #define GS_THREADS ((GS_CONSUMERS + 2) * 32)
-#include <stdlib.h>
-static int gs_env(const char* name, int dflt) { const char* v = getenv(name); return v ? atoi(v) : dflt; }
-static const int GS_SMEM_BUDGET = gs_env("Q25VL_SKINNY_SMEM_KB", 220) * 1024;
-static const int GS_KC_DEFAULT = gs_env("Q25VL_SKINNY_KC", 1024);     // K elements per chunk
-#define WAIT_LIMIT (1 << 22)
+#define GS_SMEM_BUDGET (220 * 1024)       // shared memory a CTA may take
+#define GS_KC_DEFAULT 1024                // K elements per chunk of a small product (2 KB rows)
 
-__device__ __forceinline__ unsigned s32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_init(unsigned long long* bar, int count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(s32(bar)), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(unsigned long long* bar, unsigned bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(s32(bar)), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(unsigned long long* bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(s32(bar)) : "memory");
-}
-// Polls until the phase with the given parity has completed, at most WAIT_LIMIT times.
-__device__ __forceinline__ bool mbar_wait(unsigned long long* bar, unsigned parity) {
-  for (int i = 0; i < WAIT_LIMIT; ++i) {
-    unsigned done;
-    asm volatile(
-        "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
-        : "=r"(done) : "r"(s32(bar)), "r"(parity) : "memory");
-    if (done) return true;
-  }
-  return false;
-}
-__device__ __forceinline__ void bulk_copy(void* dst, const void* src, unsigned bytes, unsigned long long* bar) {
-  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n"
-               ::"r"(s32(dst)), "l"(src), "r"(bytes), "r"(s32(bar)) : "memory");
-}
 __device__ __forceinline__ uint4 lds128(const void* p) {
   uint4 v;
-  asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];\n" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(s32(p)));
+  asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];\n" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(smem_u32(p)));
   return v;
 }
 __device__ __forceinline__ void mma16816(float (&c)[4], unsigned a0, unsigned a1, unsigned a2, unsigned a3,
@@ -118,7 +89,7 @@ static SkinnyLayout skinny_layout_kc(int M, int K, int MT, int kc) {
 // finer ring starts and drains faster.  Whether x stays resident does not depend on the choice.
 static SkinnyLayout skinny_layout(int M, int N, int K, int MT) {
   const SkinnyLayout small = skinny_layout_kc(M, K, MT, GS_KC_DEFAULT);
-  if (GS_KC_DEFAULT != 1024 || ((long long)N * K < (32ll << 20) && K < 4096)) return small;
+  if ((long long)N * K < (32ll << 20) && K < 4096) return small;
   const SkinnyLayout large = skinny_layout_kc(M, K, MT, 2048);
   if (large.n_stages < 2 || (large.xp == 0) != (small.xp == 0) || large.total > (size_t)GS_SMEM_BUDGET) return small;
   return large;
@@ -355,7 +326,9 @@ static int launch_skinny(const bf16* W, const void* X, int ldx, const float* nor
                                        (int)L.total);
   if (e != cudaSuccess) return (int)e;
   const int groups = (N + GS_ROWS - 1) / GS_ROWS;
-  const int grid = groups < 148 ? groups : 148;          // one persistent CTA per SM
+  const int sms = device_sm_count();
+  if (sms <= 0) return (int)cudaErrorInvalidDevice;
+  const int grid = groups < sms ? groups : sms;          // one persistent CTA per SM
   launch(gemm_skinny_kernel<MT, EPI, NORM>, dim3(grid), dim3(GS_THREADS), L.total, s, W, X, ldx, norm_w, eps, bias, out, ldo, M, N, K, L, err);
   return launch_status();
 }

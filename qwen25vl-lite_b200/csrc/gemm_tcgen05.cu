@@ -45,7 +45,7 @@ template <int BN> struct T5Cfg {
 __device__ __forceinline__ void t5_tma_load(void* dst, const CUtensorMap* map, int x, int y, unsigned long long* bar) {
   asm volatile(
       "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];\n"
-      ::"r"(tc5_s32(dst)), "l"(reinterpret_cast<unsigned long long>(map)), "r"(tc5_s32(bar)), "r"(x), "r"(y) : "memory");
+      ::"r"(smem_u32(dst)), "l"(reinterpret_cast<unsigned long long>(map)), "r"(smem_u32(bar)), "r"(x), "r"(y) : "memory");
 }
 
 struct T5Shared {
@@ -72,24 +72,27 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
   pdl_trigger();
   if (threadIdx.x == 0) {
     for (int s = 0; s < T5_STAGES; ++s) {
-      tc5_mbar_init(sh->full + s, 1);
-      tc5_mbar_init(sh->empty + s, 1);
+      mbar_init(sh->full + s, 1);
+      mbar_init(sh->empty + s, 1);
     }
     for (int b = 0; b < 2; ++b) {
-      tc5_mbar_init(sh->acc_full + b, 1);
-      tc5_mbar_init(sh->acc_empty + b, 4);
+      mbar_init(sh->acc_full + b, 1);
+      mbar_init(sh->acc_empty + b, 4);
     }
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
   }
+  // x was written by the kernel before this one; the output may still be read by it.  The tensor
+  // memory is asked for only after that kernel has finished: a CTA that held columns while it waited
+  // could starve a CTA of the earlier kernel on the same SM that still has to allocate its own.
+  pdl_wait();
   if (warp == 1) {   // tensor memory: two accumulators of BN columns
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(tc5_s32(&sh->tmem_base)), "n"(2 * BN) : "memory");
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_u32(&sh->tmem_base)), "n"(2 * BN) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
   }
   tc5_fence_before();
   __syncthreads();
   tc5_fence_after();
   const unsigned tmem_base = sh->tmem_base;
-  pdl_wait();   // x was written by the kernel before this one; the output may still be read by it
 
   if (warp == 0) {
     // ---- producer ----
@@ -101,11 +104,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
         for (int kb = 0; kb < k_blocks; ++kb, ++it) {
           const int s = it % T5_STAGES;
           if (it >= T5_STAGES && ok) {
-            ok = tc5_mbar_wait(sh->empty + s, ((it / T5_STAGES) - 1) & 1);
+            ok = mbar_wait(sh->empty + s, ((it / T5_STAGES) - 1) & 1);
             if (!ok) atomicExch(err, 11);
           }
           unsigned char* st = stages + (size_t)s * T5_STAGE_BYTES;
-          tc5_mbar_expect_tx(sh->full + s, T5_STAGE_BYTES);
+          mbar_expect_tx(sh->full + s, T5_STAGE_BYTES);
           t5_tma_load(st, &map_x, kb * T5_BK, m0, sh->full + s);
           t5_tma_load(st + T5_A_BYTES, &map_w, kb * T5_BK, n0, sh->full + s);
         }
@@ -120,7 +123,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
       for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++tile_it) {
         const int b = tile_it & 1;
         if (tile_it >= 2 && ok) {
-          ok = tc5_mbar_wait(sh->acc_empty + b, ((tile_it >> 1) - 1) & 1);
+          ok = mbar_wait(sh->acc_empty + b, ((tile_it >> 1) - 1) & 1);
           if (!ok) atomicExch(err, 12);
         }
         tc5_fence_after();
@@ -128,11 +131,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
         for (int kb = 0; kb < k_blocks; ++kb, ++it) {
           const int s = it % T5_STAGES;
           if (ok) {
-            ok = tc5_mbar_wait(sh->full + s, (it / T5_STAGES) & 1);
+            ok = mbar_wait(sh->full + s, (it / T5_STAGES) & 1);
             if (!ok) atomicExch(err, 13);
           }
           tc5_fence_after();
-          const unsigned a_addr = tc5_s32(stages + (size_t)s * T5_STAGE_BYTES);
+          const unsigned a_addr = smem_u32(stages + (size_t)s * T5_STAGE_BYTES);
           const unsigned long long adesc = tc5_desc(a_addr, 16, 1024), bdesc = tc5_desc(a_addr + T5_A_BYTES, 16, 1024);
 #pragma unroll
           for (int k = 0; k < T5_BK / 16; ++k)   // 32 bytes further along K inside the swizzle atom: + 2 in the address field
@@ -151,7 +154,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
       const int m0 = (tile % m_blocks) * T5_BM, n0 = (tile / m_blocks) * T5_BN;
       const int b = tile_it & 1;
       if (ok) {
-        ok = tc5_mbar_wait(sh->acc_full + b, (tile_it >> 1) & 1);
+        ok = mbar_wait(sh->acc_full + b, (tile_it >> 1) & 1);
         if (!ok && lane == 0) atomicExch(err, 14);
       }
       tc5_fence_after();
@@ -210,7 +213,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
       }
       tc5_fence_before();
       __syncwarp();
-      if (lane == 0) tc5_mbar_arrive(sh->acc_empty + b);
+      if (lane == 0) mbar_arrive(sh->acc_empty + b);
     }
   }
 
@@ -260,7 +263,9 @@ static int launch_t5(const CUtensorMap& mx, const CUtensorMap& mw, const float* 
   cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel<EPI, BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return (int)e;
   const int tiles = ((M + T5_BM - 1) / T5_BM) * ((N + BN - 1) / BN);
-  launch(gemm_tcgen05_kernel<EPI, BN>, dim3(tiles < 148 ? tiles : 148), dim3(T5_THREADS), smem, s, mx, mw, bias, out, ldo, M, N, K, err);
+  const int sms = device_sm_count();
+  if (sms <= 0) return (int)cudaErrorInvalidDevice;
+  launch(gemm_tcgen05_kernel<EPI, BN>, dim3(tiles < sms ? tiles : sms), dim3(T5_THREADS), smem, s, mx, mw, bias, out, ldo, M, N, K, err);
   return launch_status();
 }
 
@@ -269,7 +274,7 @@ static int launch_t5(const CUtensorMap& mx, const CUtensorMap& mw, const float* 
 // only used when 256-wide tiles would leave more than half of the SMs without a tile.
 static int pick_bn(int M, int N) {
   const long long t256 = (long long)((M + T5_BM - 1) / T5_BM) * ((N + 255) / 256);
-  return 2 * t256 <= 148 ? 128 : 256;
+  return 2 * t256 <= device_sm_count() ? 128 : 256;
 }
 
 // x: [M, K] bfloat16 with row pitch ldx; W: [N, K] bfloat16 contiguous.  epi as in gemm_skinny.cu

@@ -129,7 +129,8 @@ __global__ void apply_penalties_kernel(float* __restrict__ logits, size_t ld, in
 // Chunks a row is cut into: enough blocks to fill the GPU when there are few rows.
 Q25_EXPORT int q25_sample_chunks(int rows, int vocab) {
   if (vocab < 16384) return 1;
-  int want = (2 * 148 + rows - 1) / rows;
+  const int sms = device_sm_count() > 0 ? device_sm_count() : 148;
+  int want = (2 * sms + rows - 1) / rows;
   int most = (vocab + 4095) / 4096;
   int c = want < most ? want : most;
   return c < 1 ? 1 : c;

@@ -4,32 +4,11 @@
 // Conventions: shared-memory operands are tiles in the 128-byte swizzle (rows of 128 bytes, 8 rows
 // per 1 KB atom, the 16-byte chunk c of row r at chunk c ^ (r % 8)); accumulators are 128 lanes
 // (rows) by N 32-bit columns of tensor memory; a thread of warp w reads lane 32 (w % 4) + its lane
-// index.  Every mbarrier wait is bounded (TC5_WAIT_LIMIT polls) and says whether it succeeded: the
-// caller records an error code and runs on to its end.  A parity wait cannot tell "not yet" from
-// "two phases on" (nor from "a phase behind"), so a waiter must be within one phase of its barrier.
+// index.  The mbarrier wrappers (bounded waits) are those of common.cuh.
 #pragma once
 
 #include "common.cuh"
 
-#define TC5_WAIT_LIMIT (1 << 22)
-
-__device__ __forceinline__ unsigned tc5_s32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
-__device__ __forceinline__ void tc5_mbar_init(unsigned long long* bar, int count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(tc5_s32(bar)), "r"(count));
-}
-__device__ __forceinline__ bool tc5_mbar_wait(unsigned long long* bar, unsigned parity) {
-  for (int i = 0; i < TC5_WAIT_LIMIT; ++i) {
-    unsigned done;
-    asm volatile(
-        "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
-        : "=r"(done) : "r"(tc5_s32(bar)), "r"(parity) : "memory");
-    if (done) return true;
-  }
-  return false;
-}
-__device__ __forceinline__ void tc5_mbar_expect_tx(unsigned long long* bar, unsigned bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(tc5_s32(bar)), "r"(bytes) : "memory");
-}
 // Shared-memory matrix descriptor, 128-byte swizzle.  lbo / sbo in bytes.
 __device__ __forceinline__ unsigned long long tc5_desc(unsigned smem_addr, unsigned lbo, unsigned sbo) {
   unsigned long long d = 0;
@@ -51,7 +30,7 @@ __device__ __forceinline__ void tc5_mma(unsigned tmem_d, unsigned long long ades
       ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
 }
 __device__ __forceinline__ void tc5_commit(unsigned long long* bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(tc5_s32(bar)) : "memory");
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(smem_u32(bar)) : "memory");
 }
 __device__ __forceinline__ void tc5_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory"); }
 __device__ __forceinline__ void tc5_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory"); }
@@ -99,9 +78,6 @@ __device__ __forceinline__ void tc5_st32u(unsigned taddr, const unsigned (&v)[32
         "r"(v[30]), "r"(v[31])
       : "memory");
   asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory");
-}
-__device__ __forceinline__ void tc5_mbar_arrive(unsigned long long* bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(tc5_s32(bar)) : "memory");
 }
 // The product with the A operand in tensor memory: lane = row, 16 bfloat16 of a row in 8 columns.
 __device__ __forceinline__ void tc5_mma_ts(unsigned tmem_d, unsigned tmem_a, unsigned long long bdesc, unsigned idesc,

@@ -61,7 +61,19 @@ class StepEntry:
     request: Request
     tokens: Sequence[int]
     want: Sequence[int] = ()                     # indices into ``tokens``
-    positions: Optional[np.ndarray] = None       # [axes, len(tokens)]; None = plain text
+    # [axes, k] for the first k <= len(tokens) tokens; the others (all of them with None) are plain
+    # text and sit where the model's position encoding puts plain text after what came before
+    positions: Optional[np.ndarray] = None
+
+
+@dataclass
+class HostStep:
+    """A step's shape as the host knows it, for parts that plan work lists for their kernels."""
+
+    q_lens: List[int]          # tokens each entry brings
+    starts: List[int]          # tokens each entry's request already has in the cache
+    n_tokens: int
+    n_seqs: int
 
 
 @dataclass
@@ -93,11 +105,8 @@ class StepContext:
     group_kv_slot: List[torch.Tensor]
     group_block_table: List[torch.Tensor]
     cache: CacheManager
-    # work lists of the tensor-core attention kernels: entries that bring one token, and per
-    # query-group size G the (entry, 64-row tile) pairs of the other entries
-    decode_items: Optional[torch.Tensor] = None
-    prefill_tiles: Dict[int, Optional[torch.Tensor]] = field(default_factory=dict)
-    prefill_tiles128: Dict[int, Optional[torch.Tensor]] = field(default_factory=dict)    # the same in 128-row tiles
+    # device copies of what the parts' ``plan_step`` returned, by plan key and array name
+    plans: Dict[object, Dict[str, Optional[torch.Tensor]]] = field(default_factory=dict)
     # host copies, for parts written with torch operators (toy parts in tests)
     host_q_lens: List[int] = field(default_factory=list)
     host_q_start: List[int] = field(default_factory=list)
@@ -106,13 +115,16 @@ class StepContext:
     # when a pass begins); keyed by whoever puts it there
     shared: Dict[object, object] = field(default_factory=dict)
 
+    def plan(self, part) -> Dict[str, Optional[torch.Tensor]]:
+        """The work lists ``part.plan_step`` asked for, on the device (None for an empty one)."""
+        return self.plans[part.plan_key()]
+
     def kv(self, stop: StopRuntime) -> KVStep:
         group, k_pages, v_pages = self.cache.stop_pages(stop.index)
         return KVStep(k_pages, v_pages, self.group_kv_slot[group.index], self.group_block_table[group.index],
                       group.page_size)
 
 
-PREFILL_TILE_ROWS = (64, 128)   # row tiles of the two prefill attention kernels (mma.sync, tcgen05)
 GRAPH_WIDTH_STEP = 16      # block-table widths of captured steps are rounded up to this many pages
 MAX_GRAPHS = 32
 
@@ -131,10 +143,12 @@ class ModelRunner:
         self.cache.allocate_device(self.device, self.dtype)
         for stop in model.stops:
             stop.state = self.cache.states.get(stop.index)
+        self.position = model.position             # defines the tokens' positions
         self.axes = model.position.axes
-        # query heads per kv head of every attention mixer, for the attention work lists
-        blocks = getattr(model, "blocks", [])
-        self.group_sizes = sorted({int(b.mixer.rows_per_token) for b in blocks if hasattr(b.mixer, "rows_per_token")})
+        # parts whose kernels read work lists built per step: one planner per distinct plan key
+        self._planners: Dict[object, object] = {}
+        for part in model.planning_parts() if hasattr(model, "planning_parts") else ():
+            self._planners.setdefault(part.plan_key(), part)
         self.vocab_size = model.head.vocab_size
         self._staging: Optional[torch.Tensor] = None
         self._staging_free = torch.cuda.Event() if self.device.type == "cuda" else None
@@ -147,7 +161,8 @@ class ModelRunner:
         # engine's kernels, no host-side loop over the batch, no library operator that synchronises).
         blocks = getattr(model, "blocks", [])
         parts = [p for b in blocks for p in (b.mixer, b.feed_forward, *b.norms)]
-        parts += [getattr(model, name, None) for name in ("position", "embedding", "final_norm", "head")]
+        parts += [getattr(model, name, None) for name in ("embedding", "final_norm", "head")]
+        parts += model.position_encodings() if hasattr(model, "position_encodings") else [model.position]
         self.cuda_graphs = bool(cuda_graphs and self.device.type == "cuda" and blocks
                                 and all(getattr(p, "graph_safe", False) for p in parts))
         self._graphs: Dict[tuple, tuple] = {}
@@ -239,9 +254,7 @@ class ModelRunner:
     def _pack(self, entries: Sequence[StepEntry]):
         """Builds the step's arrays in the staging buffer; returns the function that runs the step
         (optionally with other token ids than the entries brought, for ``prepare_decode``)."""
-        if int(self._error_host[0]) != 0:
-            raise kernels.KernelError(f"a kernel of the previous step gave up waiting (code {int(self._error_host[0])}); "
-                                      "its results are invalid")
+        self.check_kernel_errors()
         ps = self.cache.page_size
         groups = self.cache.groups
         q_lens = [len(e.tokens) for e in entries]
@@ -261,18 +274,10 @@ class ModelRunner:
         M = sum(len(e.want) for e in entries)
 
         # ---- pack ----
-        decode_list = [i for i, n in enumerate(q_lens) if n == 1]
-        tile_lists = {}                                   # (group size, rows of a tile) -> (entry, tile) pairs
-        for G in self.group_sizes:
-            for rows in PREFILL_TILE_ROWS:
-                pairs = []
-                for i, n in enumerate(q_lens):
-                    if n > 1 or G > 16:
-                        pairs += [(i, t) for t in range(-(-n * G // rows))]
-                # the tiles of a run's last tokens see the most keys: they go first, the short ones fill in
-                pairs.sort(key=lambda it: -(starts[it[0]] + (it[1] + 1) * rows // G))
-                tile_lists[(G, rows)] = pairs
-        n_work = len(decode_list) + sum(2 * len(v) + 4 for v in tile_lists.values())
+        host = HostStep(q_lens, starts, N, S)
+        plans = {key: {name: np.ascontiguousarray(a, dtype=np.int32).reshape(-1)
+                       for name, a in part.plan_step(host).items()} for key, part in self._planners.items()}
+        n_work = sum(a.shape[0] + 4 for p in plans.values() for a in p.values())
         total = (N * (2 + self.axes + len(groups)) + (S + 1) + 2 * S + M + S * sum(widths) + n_work
                  + 4 * (8 + 2 * len(groups)))
         self._reserve(total)
@@ -302,18 +307,16 @@ class ModelRunner:
             b, b_s = take(S * w)
             g_slot.append(a); g_slot_s.append(a_s); g_tab.append(b.reshape(S, w)); g_tab_s.append(b_s)
 
-        dec, dec_s = take(len(decode_list))
-        dec[:] = decode_list
-        tile_s = {}
-        for key, pairs in tile_lists.items():
-            view, tile_s[key] = take(2 * len(pairs))
-            if pairs:
-                view[:] = np.asarray(pairs, dtype=np.int32).reshape(-1)
+        plan_s = {}
+        for key, arrays in plans.items():
+            for name, a in arrays.items():
+                view, plan_s[key, name] = take(a.shape[0])
+                view[:] = a
 
         cu[0] = 0
         last_position = []
         if (max(q_lens) == 1 and all(e.positions is None for e in entries)
-                and getattr(self.model.position, "default_is_linear", False)):
+                and getattr(self.position, "default_is_linear", False)):
             # A step of single tokens at their default positions (the usual decode step): the
             # arrays are filled for all entries at once, and a request's block table is converted
             # only when it has grown.
@@ -350,13 +353,18 @@ class ModelRunner:
                 if ids.min() < 0 or ids.max() >= self.vocab_size:
                     raise ValueError(f"request {e.request.request_id!r}: token id outside [0, {self.vocab_size})")
                 tok[at:at + n] = ids
+                cache = e.request.cache
                 if e.positions is None:
-                    pos[:, at:at + n] = self.model.position.default_positions(s, n, e.request.cache.position_offset)
+                    pos[:, at:at + n] = self.position.default_positions(s, n, cache.position_offset)
                 else:
                     p = np.asarray(e.positions)
-                    if p.shape != (self.axes, n):
-                        raise ValueError(f"positions must be [{self.axes}, {n}], got {p.shape}")
-                    pos[:, at:at + n] = p
+                    k = p.shape[1] if p.ndim == 2 else -1
+                    if p.ndim != 2 or p.shape[0] != self.axes or not 0 < k <= n:
+                        raise ValueError(f"positions must be [{self.axes}, 1..{n}], got {p.shape}")
+                    pos[:, at:at + k] = p
+                    if k < n:     # plain text after tokens that brought their positions
+                        offset = self.position.offset_after(max(cache.max_position, int(p.max())), s + k)
+                        pos[:, at + k:at + n] = self.position.default_positions(s + k, n - k, offset)
                 last_position.append(int(pos[:, at:at + n].max()))
                 tseq[at:at + n] = i
                 cu[i + 1] = at + n
@@ -377,10 +385,10 @@ class ModelRunner:
 
         return lambda tokens=None: self._run_packed(
             tokens, entries, q_lens, starts, widths, graph_key, off, N, S, M, ps, tok, tok_s, pos_s, tseq_s, cu_s, qs_s, sl_s,
-            rows_s, g_slot_s, g_tab_s, dec_s, decode_list, tile_s, last_position)
+            rows_s, g_slot_s, g_tab_s, plan_s, last_position)
 
     def _run_packed(self, tokens, entries, q_lens, starts, widths, graph_key, off, N, S, M, ps, tok, tok_s, pos_s, tseq_s,
-                    cu_s, qs_s, sl_s, rows_s, g_slot_s, g_tab_s, dec_s, decode_list, tile_s, last_position):
+                    cu_s, qs_s, sl_s, rows_s, g_slot_s, g_tab_s, plan_s, last_position):
         if tokens is not None:
             ids = np.asarray(tokens, dtype=np.int64)
             if ids.shape != (N,) or ids.min() < 0 or ids.max() >= self.vocab_size:
@@ -404,9 +412,7 @@ class ModelRunner:
             group_kv_slot=[d(s_) for s_ in g_slot_s],
             group_block_table=[d(s_, (S, w)) for s_, w in zip(g_tab_s, widths)],
             cache=self.cache,
-            decode_items=d(dec_s) if decode_list else None,
-            prefill_tiles={G: (d(sp, (sp[1] // 2, 2)) if sp[1] else None) for (G, rows), sp in tile_s.items() if rows == 64},
-            prefill_tiles128={G: (d(sp, (sp[1] // 2, 2)) if sp[1] else None) for (G, rows), sp in tile_s.items() if rows == 128},
+            plans=self._plan_views(plan_s, d),
             host_q_lens=q_lens, host_q_start=starts,
             host_slots=[e.request.cache.slot for e in entries],
         )
@@ -418,11 +424,29 @@ class ModelRunner:
         if self.device.type == "cuda":
             self._error_host.copy_(kernels.error_flag(self.device), non_blocking=True)
         for e, n, p_max in zip(entries, q_lens, last_position):
-            # plain text that follows resumes one past the largest position seen so far
-            # (the reference's rope_delta = max(pos) + 1 - length, src/qwen25vl_lite/rope.py:235)
+            # where plain text that follows resumes is the position encoding's to say
             c = e.request.cache
             c.max_position = max(c.max_position, p_max)
             self.cache.advance(c, n)
-            c.position_offset = c.max_position + 1 - c.num_tokens
+            c.position_offset = self.position.offset_after(c.max_position, c.num_tokens)
         self.steps += 1
         return logits
+
+    @staticmethod
+    def _plan_views(plan_s, d):
+        plans: Dict[object, Dict[str, Optional[torch.Tensor]]] = {}
+        for (key, name), span in plan_s.items():
+            plans.setdefault(key, {})[name] = d(span) if span[1] else None
+        return plans
+
+    def check_kernel_errors(self) -> None:
+        """Raises if a kernel of a step whose results have reached the host gave up one of its
+        bounded waits (the flag travels to the host after every step, behind the step's kernels
+        and before anything that reads its logits).  The flag is cleared, so that one failed
+        step does not condemn the steps after it."""
+        code = int(self._error_host[0])
+        if code != 0:
+            self._error_host.zero_()
+            if self.device.type == "cuda":
+                kernels.error_flag(self.device).zero_()
+            raise kernels.KernelError(f"a kernel of a step gave up waiting (code {code}); the step's results are invalid")

@@ -45,7 +45,11 @@ from .runner import Request, StepEntry
 
 @dataclass
 class RequestOutput:
-    """What the caller gets back for a finished request (engine.py:96-112)."""
+    """A finished request as its caller sees it.  The attribute names (and the keys of
+    ``metrics``) are those of the reference's record (src/qwen25vl_lite/engine.py:96-112), so code
+    written against that engine reads these unchanged.  ``finish_reason`` is ``"stop"`` (the
+    end-of-sequence token or one of ``stop_token_ids``) or ``"length"`` (``max_tokens`` or the
+    engine's ``max_model_len``)."""
 
     seq_id: int
     prompt_token_ids: List[int]
@@ -53,13 +57,16 @@ class RequestOutput:
     finish_reason: str
     metrics: Dict[str, float] = field(default_factory=dict)
 
-    @property
-    def num_prompt_tokens(self) -> int:
-        return len(self.prompt_token_ids)
+    num_prompt_tokens = property(lambda self: len(self.prompt_token_ids))
+    num_output_tokens = property(lambda self: len(self.output_token_ids))
 
-    @property
-    def num_output_tokens(self) -> int:
-        return len(self.output_token_ids)
+    @classmethod
+    def of(cls, seq: "Sequence", reason: str, now: float) -> "RequestOutput":
+        first = seq.first_token_at if seq.first_token_at is not None else now
+        timing = {"ttft_s": max(first - seq.arrival, 0.0), "elapsed_s": max(now - seq.arrival, 0.0)}
+        counts = {"prompt_tokens": float(len(seq.prompt_token_ids)), "completion_tokens": float(len(seq.output_token_ids)),
+                  "preemptions": float(seq.preemptions)}
+        return cls(seq.seq_id, list(seq.prompt_token_ids), list(seq.output_token_ids), reason, {**counts, **timing})
 
 
 @dataclass
@@ -69,7 +76,6 @@ class Sequence:
     params: SamplingParams
     seed: int
     prompt_positions: Optional[np.ndarray] = None      # [axes, len(prompt)] or None (plain text)
-    rope_delta: int = 0
     priority: int = 0
     output_token_ids: List[int] = field(default_factory=list)
     request: Optional[Request] = None                  # live handle of the step function
@@ -97,17 +103,14 @@ class Sequence:
         return (self.prompt_token_ids[start:] if start < p else []) + self.output_token_ids[max(start - p, 0):end - p]
 
     def positions(self, start: int, end: int) -> Optional[np.ndarray]:
-        """Explicit positions of tokens [start, end) when the prompt came with positions."""
-        if self.prompt_positions is None:
+        """The positions the prompt brought for tokens [start, end): those of the prompt's share
+        of the range, None when the range lies behind the prompt.  Generated tokens (a range may
+        reach into them when a preempted request is recomputed) bring none: where they sit
+        follows from what came before them, and the step function asks the model's position
+        encoding for it."""
+        if self.prompt_positions is None or start >= len(self.prompt_token_ids):
             return None
-        p = len(self.prompt_token_ids)
-        cols = []
-        if start < p:
-            cols.append(self.prompt_positions[:, start:min(end, p)])
-        if end > p:
-            run = np.arange(max(start, p), end, dtype=np.int64) + self.rope_delta
-            cols.append(np.broadcast_to(run, (self.prompt_positions.shape[0], run.shape[0])))
-        return np.concatenate(cols, axis=1)
+        return self.prompt_positions[:, start:min(end, len(self.prompt_token_ids))]
 
 
 @dataclass
@@ -163,17 +166,17 @@ class LLMEngine:
             raise ValueError("prompt is empty")
         if len(ids) > self.ecfg.max_model_len:
             raise ValueError(f"prompt of {len(ids)} tokens exceeds max_model_len {self.ecfg.max_model_len}")
-        rope_delta = 0
         if image_spans is not None and positions is None:
-            from ..parts.position import prompt_positions
-            positions, rope_delta = prompt_positions(len(ids), image_spans)
+            encoding = getattr(self.runner, "position", None)
+            if not hasattr(encoding, "prompt_positions"):
+                raise ValueError("image_spans given, but the model's position encoding does not place image runs")
+            positions = encoding.prompt_positions(len(ids), image_spans)
         if positions is not None:
             positions = np.asarray(positions, dtype=np.int64)
             if positions.ndim != 2 or positions.shape[1] != len(ids):
                 raise ValueError(f"positions must be [axes, {len(ids)}], got {positions.shape}")
-            rope_delta = int(positions.max()) + 1 - len(ids)
         seq = Sequence(self._next_id, ids, params, params.seed if params.seed is not None else new_seed(),
-                       positions, rope_delta, priority)
+                       positions, priority)
         probe_pages = -(-len(ids) // self.ecfg.block_size)
         if all(g.window is None for g in self.runner.cache.groups) and probe_pages > self.runner.cache.num_pages:
             raise ValueError(f"prompt of {len(ids)} tokens needs {probe_pages} pages, the pool has "
@@ -318,12 +321,14 @@ class LLMEngine:
                 pending = self.sampler.sample_async(*args)
                 self._prepared = self._prepare_next(samplers)          # host work under the device's step
                 tokens = self.sampler.collect(pending)
+                self._check_step()                         # the step's results are on the host: was it whole?
                 if self._prepared is not None and not any(self._ends(seq, int(tok)) for seq, tok in zip(samplers, tokens)):
                     # nobody ends: the next step goes to the device now, the bookkeeping follows under it
                     next_logits = self.runner.launch_prepared(self._prepared[0], [int(tok) for tok in tokens])
                     self._launched, self._prepared = (next_logits, samplers), None
             else:
                 tokens = self.sampler.sample(*args)
+                self._check_step()
             for seq, token in zip(samplers, tokens):
                 if seq.status == "running":                # a request aborted while its step ran draws nothing
                     self._accept(seq, int(token), done)
@@ -364,59 +369,67 @@ class LLMEngine:
         return (self.eos_token_id is not None and token == self.eos_token_id and not p.ignore_eos) \
             or token in (p.stop_token_ids or ())
 
+    def _check_step(self) -> None:
+        """Before a step's tokens are accepted: did one of its kernels give up a bounded wait?"""
+        check = getattr(self.runner, "check_kernel_errors", None)
+        if check is not None:
+            check()
+
+    def _length_reason(self, seq: Sequence) -> Optional[str]:
+        """Ends that do not depend on which token was drawn."""
+        if len(seq.output_token_ids) >= seq.params.max_tokens or seq.num_tokens >= self.ecfg.max_model_len:
+            return "length"
+        return None
+
     def _accept(self, seq: Sequence, token: int, done: List[RequestOutput]) -> None:
+        """Takes a drawn token into the request and retires the request if that ends it: by the
+        token itself first (``_ends``), else by length (src/qwen25vl_lite/engine.py:831-872 has the
+        same precedence)."""
+        now = time.time()
+        if seq.first_token_at is None:
+            seq.first_token_at = now
         seq.output_token_ids.append(token)
         self.stats_.generated_tokens += 1
-        if seq.first_token_at is None:
-            seq.first_token_at = time.time()
-        p = seq.params
-        reason = None
-        if self.eos_token_id is not None and token == self.eos_token_id and not p.ignore_eos:
-            reason = "stop"
-        elif token in set(p.stop_token_ids or ()):
-            reason = "stop"
-        elif len(seq.output_token_ids) >= p.max_tokens:
-            reason = "length"
-        elif seq.num_tokens >= self.ecfg.max_model_len:
-            reason = "length"
-        if reason is None:
-            return
-        seq.status = "finished"
+        reason = "stop" if self._ends(seq, token) else self._length_reason(seq)
+        if reason is not None:
+            self._retire(seq, reason, done, now)
+
+    def _retire(self, seq: Sequence, reason: str, done: List[RequestOutput], now: float) -> None:
         self._release(seq)
         self.running.remove(seq)
+        seq.status = "finished"
         self.stats_.finished += 1
-        done.append(RequestOutput(
-            seq.seq_id, list(seq.prompt_token_ids), list(seq.output_token_ids), reason,
-            {"prompt_tokens": float(len(seq.prompt_token_ids)),
-             "completion_tokens": float(len(seq.output_token_ids)),
-             "ttft_s": max(0.0, seq.first_token_at - seq.arrival),
-             "elapsed_s": time.time() - seq.arrival,
-             "preemptions": float(seq.preemptions)}))
+        done.append(RequestOutput.of(seq, reason, now))
 
     # ---- driver ------------------------------------------------------------------------
     def run_until_complete(self, max_steps: int = 1_000_000, max_stall: int = 64) -> List[RequestOutput]:
-        """Steps until every request has finished.  ``max_stall`` steps in a row without
-        progress raise instead of spinning (engine.py:878-905)."""
-        steps = stall = 0
-        last = self._progress()
-        while self.has_work() and steps < max_steps:
+        """Steps until no request is left and returns every finished request so far.  A scheduler
+        that cannot move (for instance a prompt that never fits the step budget with chunking
+        off) would spin for ever: after ``max_stall`` steps in a row that changed nothing, and
+        after ``max_steps`` steps in all, this raises (the reference guards its loop the same way,
+        src/qwen25vl_lite/engine.py:878-905)."""
+        idle, seen = 0, self._signature()
+        for _ in range(max_steps):
+            if not self.has_work():
+                break
             self.step()
-            steps += 1
-            now = self._progress()
-            if now == last:
-                stall += 1
-                if stall >= max_stall:
-                    raise RuntimeError(f"scheduler made no progress for {max_stall} steps "
-                                       f"(waiting={len(self.waiting)} running={len(self.running)})")
-            else:
-                stall, last = 0, now
-        if self.has_work():
-            raise RuntimeError(f"engine did not finish within {max_steps} steps")
+            now = self._signature()
+            idle = idle + 1 if now == seen else 0
+            seen = now
+            if idle >= max_stall:
+                raise RuntimeError(f"{max_stall} steps in a row changed nothing: {len(self.waiting)} request(s) waiting, "
+                                   f"{len(self.running)} running; the scheduler cannot place them")
+        else:
+            if self.has_work():
+                raise RuntimeError(f"{max_steps} steps did not finish the requests: {len(self.waiting)} waiting, "
+                                   f"{len(self.running)} running")
+        self._check_step()
         return self.finished
 
-    def _progress(self):
-        return (len(self.waiting), len(self.running), len(self.finished), self.stats_.preemptions,
-                sum(s.num_computed + len(s.output_token_ids) for s in self.running))
+    def _signature(self):
+        """Changes whenever a step moved anything: queue lengths, preemptions, tokens held or generated."""
+        work = sum(s.num_computed + len(s.output_token_ids) for s in self.running)
+        return (len(self.waiting), len(self.running), len(self.finished), self.stats_.preemptions, work)
 
     def stats(self) -> Dict[str, float]:
         st = self.stats_

@@ -47,10 +47,11 @@ class TraceSession:
         out = None
         if logits is not None:
             out = logits.to("cpu").numpy().astype("<f4", copy=False)
-            if self.out_dir:
-                out.tofile(os.path.join(self.out_dir, f"{record['step']}.f32"))
         elif self.runner.device.type == "cuda":
             torch.cuda.synchronize(self.runner.device)
+        self.runner.check_kernel_errors()          # before the logits count: did a kernel give up a wait?
+        if out is not None and self.out_dir:
+            out.tofile(os.path.join(self.out_dir, f"{record['step']}.f32"))
         for rid in record.get("end", []):
             req = self.requests.pop(rid, None)
             if req is None:

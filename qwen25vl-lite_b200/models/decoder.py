@@ -33,14 +33,18 @@ class DecoderModel:
     def __init__(self, spec: ModelSpec):
         spec.validate()
         self.spec = spec
-        self.position = parts.build_part(parts.POSITION_ENCODINGS, spec.position, "position encoding")
+        # the encoding that defines the tokens' positions; a layer that names another one gets that
+        # (equal descriptions are built once)
+        self._positions: Dict[str, parts.PositionEncoding] = {}
+        self.position = self._position_for(spec.position)
         self.embedding = parts.build_part(parts.EMBEDDINGS, spec.embedding, "embedding")
         self.blocks: List[parts.Block] = []
         self._named_parts: List[Tuple[str, parts.Part]] = [(spec.embedding.prefix, self.embedding)]
         for layer in spec.layers:
             if layer.block not in parts.BLOCKS:
                 raise ValueError(f"unknown block kind {layer.block!r}; known: {sorted(parts.BLOCKS)}")
-            mixer = parts.build_part(parts.MIXERS, layer.mixer, "mixer", position=self.position)
+            mixer = parts.build_part(parts.MIXERS, layer.mixer, "mixer",
+                                     position=self._position_for(layer.position or spec.position))
             ffn = parts.build_part(parts.FEED_FORWARDS, layer.feed_forward, "feed-forward")
             norms = [parts.build_part(parts.NORMS, n, "norm") for n in layer.norms]
             self.blocks.append(parts.BLOCKS[layer.block](mixer, ffn, norms))
@@ -56,6 +60,23 @@ class DecoderModel:
         self.dtype: Optional[torch.dtype] = None
         self.device = None
 
+    def _position_for(self, pspec) -> parts.PositionEncoding:
+        key = repr((pspec.kind, sorted(pspec.params.items(), key=lambda kv: kv[0])))
+        if key not in self._positions:
+            part = parts.build_part(parts.POSITION_ENCODINGS, pspec, "position encoding")
+            if part.axes > getattr(self, "position", part).axes:
+                raise ValueError(f"a layer's position encoding reads {part.axes} axes, the model's positions have "
+                                 f"{self.position.axes}")
+            self._positions[key] = part
+        return self._positions[key]
+
+    def position_encodings(self) -> List[parts.PositionEncoding]:
+        return list(self._positions.values())
+
+    def planning_parts(self) -> List[parts.Part]:
+        """The parts whose kernels read work lists that the step function packs (``plan_step``)."""
+        return [part for _, part in self._named_parts if hasattr(part, "plan_step")]
+
     # ---- weights -----------------------------------------------------------------------
     def expected_tensors(self) -> Dict[str, parts.TensorSpec]:
         """Canonical (un-prefixed) checkpoint name -> what is expected under it."""
@@ -69,14 +90,20 @@ class DecoderModel:
         """``get_tensor(canonical name)`` returns a CPU tensor; ``available`` is the set of
         canonical names the checkpoint has."""
         self.device, self.dtype = torch.device(device), dtype
-        self.position.load({}, device, dtype)
+        for position in self._positions.values():
+            position.load({}, device, dtype)
+        # A part may offer tensors it holds on the device to the parts loaded after it
+        # (``exports``, by canonical name) and take such tensors instead of loading its own
+        # (``imports``): how a tied output head comes to read the embedding table.
+        shared: Dict[str, torch.Tensor] = {}
         for prefix, part in self._named_parts:
             tensors = {ts.name: get_tensor(prefix + ts.name) for ts in part.tensor_specs()
                        if (prefix + ts.name) in available}
-            if part is self.head:
-                part.load(tensors, device, dtype, tied_weight=self.embedding.weight)
-            else:
-                part.load(tensors, device, dtype)
+            wanted = {name: shared[name] for name in part.imports() if name in shared}
+            if wanted:
+                part.receive(wanted)
+            part.load(tensors, device, dtype)
+            shared.update({prefix + name: t for name, t in part.exports().items()})
 
     def weight_bytes(self) -> int:
         seen, total = set(), 0

@@ -1,4 +1,4 @@
-"""Choice of the attention kernels for a step.
+"""Choice of the attention kernels for a step, and the work lists those kernels read.
 
 bfloat16 with a head size and page size the tensor-core kernels take (``csrc/attention_mma.cu``):
 
@@ -7,23 +7,48 @@ bfloat16 with a head size and page size the tensor-core kernels take (``csrc/att
   pages, attends, and merges its key ranges (the CTA that finishes last does it);
 * otherwise the position encoding runs first (``rotate_and_store``), then entries that bring one
   token go to the split-KV decode kernel (partials through scratch memory and a combine
-  kernel) and runs of tokens to the prefill kernel.
+  kernel) and runs of tokens to the prefill kernel (tcgen05 at head size 128, mma.sync else).
 
 Everything else (float32, other sizes) goes to the general kernel
 (``csrc/attention_generic.cu``) after ``rotate_and_store``.
+
+The tensor-core kernels walk work lists: the entries that bring one token, and (entry, row tile)
+pairs for the others.  ``plan_step`` builds them on the host from the step's shape; the step
+function packs whatever a part's ``plan_step`` returns into the step's one transfer and hands
+the device copies back through ``ctx.plan(part)``.
 """
 
 from __future__ import annotations
 
+from typing import Dict
+
+import numpy as np
 import torch
 
 from . import kernels
 
-SM_COUNT = 148
-# which kernel attends runs of tokens at head size 128: "tcgen05" (scores and P.V on the 5th-generation
-# tensor cores) or "mma" (mma.sync, the kernel of every other head size)
-PREFILL_ATTENTION = __import__("os").environ.get("Q25VL_PREFILL_ATTENTION", "tcgen05")
+PREFILL_TILE_ROWS = (64, 128)   # row tiles of the two prefill attention kernels (mma.sync, tcgen05)
 _scratch = {}
+
+
+def plan_step(host, group: int) -> Dict[str, np.ndarray]:
+    """Work lists for a mixer whose kv heads each serve ``group`` query heads.  ``host`` describes
+    the step (``q_lens``: tokens each entry brings, ``starts``: tokens it already has in the cache).
+
+    ``decode_items``: the entries that bring one token (groups of more than 16 heads do not fit the
+    decode kernel's 16 rows and go with the runs).  ``tiles64`` / ``tiles128``: flat (entry, tile)
+    pairs of the other entries, a tile being 64 or 128 consecutive rows of the entry's (token, head
+    of the group) pairs; the tiles of a run's last tokens see the most keys, so they go first and
+    the short ones fill in behind them."""
+    q_lens, starts = host.q_lens, host.starts
+    runs = [i for i, n in enumerate(q_lens) if n > 1 or group > 16]
+    run_set = set(runs)
+    out = {"decode_items": np.asarray([i for i in range(len(q_lens)) if i not in run_set], dtype=np.int32)}
+    for rows in PREFILL_TILE_ROWS:
+        pairs = [(i, t) for i in runs for t in range(-(-q_lens[i] * group // rows))]
+        pairs.sort(key=lambda it: -(starts[it[0]] + (it[1] + 1) * rows // group))
+        out[f"tiles{rows}"] = np.asarray(pairs, dtype=np.int32).reshape(-1)
+    return out
 
 
 def decode_splits(n_items: int, nkv: int, max_kv_len: int, most: int = 64) -> int:
@@ -32,7 +57,7 @@ def decode_splits(n_items: int, nkv: int, max_kv_len: int, most: int = 64) -> in
     own (the kernel's shared memory allows one CTA per SM, a second wave doubles the time), as
     long as a range keeps at least 256 keys (two 32-key tiles per warp)."""
     by_work = max(1, -(-max_kv_len // 256))
-    by_sms = max(1, SM_COUNT // max(1, n_items * nkv))
+    by_sms = max(1, kernels.sm_count() // max(1, n_items * nkv))
     return int(min(by_work, by_sms, most))
 
 
@@ -45,63 +70,66 @@ def _scratch_floats(n: int, device) -> torch.Tensor:
     return buf
 
 
-def attend(ctx, qkv, kv, position, nq: int, nkv: int, head_dim: int, window, scale: float, store: bool) -> torch.Tensor:
+def _pairs(flat):
+    return None if flat is None else flat.view(-1, 2)
+
+
+def attend(ctx, plan, qkv, kv, position, nq: int, nkv: int, head_dim: int, window, scale: float, store: bool) -> torch.Tensor:
     """Position-encodes q and k, writes this step's k and v into the pages (``store``), and
     attends.  qkv: [N, (nq + 2 nkv) * D] as projected; kv: the stop's pages, slots and block
-    table for this step.  Returns [N, nq * D]."""
+    table for this step; plan: the device copies of what ``plan_step`` returned (None entries
+    for empty lists).  Returns [N, nq * D]."""
     window = int(window or 0)
     group = nq // nkv
-    tables = getattr(position, "rope_tables", None)
-    if (store and tables is not None and ctx.decode_items is not None and ctx.decode_items.shape[0] == ctx.n_seqs
-            and ctx.prefill_tiles.get(group, 0) is None
+    tables = position.rope_tables() if hasattr(position, "rope_tables") else None
+    decode_items = plan.get("decode_items")
+    if (store and tables is not None and decode_items is not None and decode_items.shape[0] == ctx.n_seqs
+            and plan.get("tiles64") is None
             and kernels.attention_fused_supports(qkv.dtype, head_dim, kv.page_size, group)):
-        inv_freq, axis = tables()
-        # the angles are the same for every layer of the step: the first one to ask computes them
-        shared = getattr(ctx, "shared", None)
-        key = ("rope_angles", inv_freq.data_ptr())
-        angles = shared.get(key) if shared is not None else None
+        inv_freq, axis = tables
+        # the angles are the same for every layer of the step that shares the tables: the first
+        # one to ask computes them
+        key = ("rope_angles", inv_freq.data_ptr(), axis.data_ptr())
+        angles = ctx.shared.get(key)
         if angles is None:
-            angles = kernels.rope_angles(ctx.positions, inv_freq, axis)
-            if shared is not None:
-                shared[key] = angles
+            angles = ctx.shared[key] = kernels.rope_angles(ctx.positions, inv_freq, axis)
         out = torch.empty((qkv.shape[0], nq * head_dim), dtype=qkv.dtype, device=qkv.device)
         visible = min(ctx.max_kv_len, window) if window else ctx.max_kv_len
         splits = decode_splits(ctx.n_seqs, nkv, visible)
         scratch = _scratch_floats(ctx.n_seqs * nq * splits * (head_dim + 2), qkv.device) if splits > 1 else None
         kernels.attention_decode_fused(qkv, out, kv.k_pages, kv.v_pages, kv.block_table, ctx.cu_q, ctx.q_start_pos,
-                                       ctx.decode_items, nq, nkv, head_dim, kv.page_size, window, scale, splits,
+                                       decode_items, nq, nkv, head_dim, kv.page_size, window, scale, splits,
                                        ctx.positions, inv_freq, axis, kv.kv_slot, scratch, angles,
                                        dense=True)          # every entry of the step is one token, in order
         return out
     position.rotate_and_store(ctx, qkv, nq, nkv, head_dim, kv if store else None)
-    return paged_attention(ctx, qkv, kv, nq, nkv, head_dim, window, scale)
+    return paged_attention(ctx, plan, qkv, kv, nq, nkv, head_dim, window, scale)
 
 
-def paged_attention(ctx, qkv, kv, nq: int, nkv: int, head_dim: int, window, scale: float) -> torch.Tensor:
+def paged_attention(ctx, plan, qkv, kv, nq: int, nkv: int, head_dim: int, window, scale: float) -> torch.Tensor:
     """qkv: [N, (nq + 2 nkv) * D] with q already position-encoded and this step's keys and
     values already in the pages.  Returns [N, nq * D]."""
     out = torch.empty((qkv.shape[0], nq * head_dim), dtype=qkv.dtype, device=qkv.device)
     window = int(window or 0)
     group = nq // nkv
-    if not kernels.attention_mma_supports(qkv.dtype, head_dim, kv.page_size) or group not in ctx.prefill_tiles:
+    if not kernels.attention_mma_supports(qkv.dtype, head_dim, kv.page_size):
         kernels.paged_attention_generic(qkv, out, kv.k_pages, kv.v_pages, kv.block_table, ctx.token_seq, ctx.cu_q,
                                         ctx.q_start_pos, nq, nkv, head_dim, kv.page_size, window, scale)
         return out
-    if ctx.decode_items is not None and group <= 16:
-        n_items = ctx.decode_items.shape[0]
+    decode_items = plan.get("decode_items")
+    if decode_items is not None:
+        n_items = decode_items.shape[0]
         visible = min(ctx.max_kv_len, window) if window else ctx.max_kv_len
         splits = decode_splits(n_items, nkv, visible)
         scratch = _scratch_floats(n_items * nq * splits * (head_dim + 2), qkv.device) if splits > 1 else None
         kernels.attention_decode(qkv, out, kv.k_pages, kv.v_pages, kv.block_table, ctx.cu_q, ctx.q_start_pos,
-                                 ctx.decode_items, nq, nkv, head_dim, kv.page_size, window, scale, splits, scratch)
-    tiles = ctx.prefill_tiles[group]
-    if tiles is not None:
-        tiles128 = getattr(ctx, "prefill_tiles128", {}).get(group)
-        if PREFILL_ATTENTION == "tcgen05" and tiles128 is not None and group <= 128 \
-                and kernels.attention_tcgen05_supports(qkv.dtype, head_dim, kv.page_size, qkv):
+                                 decode_items, nq, nkv, head_dim, kv.page_size, window, scale, splits, scratch)
+    tiles64, tiles128 = _pairs(plan.get("tiles64")), _pairs(plan.get("tiles128"))
+    if tiles64 is not None:
+        if tiles128 is not None and group <= 128 and kernels.attention_tcgen05_supports(qkv.dtype, head_dim, kv.page_size, qkv):
             kernels.attention_prefill_tcgen05(qkv, out, kv.k_pages, kv.v_pages, kv.block_table, ctx.cu_q, ctx.q_start_pos,
                                               tiles128, nq, nkv, head_dim, kv.page_size, window, scale)
         else:
-            kernels.attention_prefill(qkv, out, kv.k_pages, kv.v_pages, kv.block_table, ctx.cu_q, ctx.q_start_pos, tiles,
+            kernels.attention_prefill(qkv, out, kv.k_pages, kv.v_pages, kv.block_table, ctx.cu_q, ctx.q_start_pos, tiles64,
                                       nq, nkv, head_dim, kv.page_size, window, scale)
     return out

@@ -87,6 +87,25 @@ def _typed(base: str, dtype: torch.dtype):
 
 
 _launches = 0
+_sm_count: Dict[int, int] = {}
+
+
+def sm_count() -> int:
+    """Streaming multiprocessors of the current device, asked once (148 on the B200 the kernels'
+    heuristics were measured on); grids and split counts are derived from it."""
+    dev = torch.cuda.current_device() if torch.cuda.is_available() else -1
+    n = _sm_count.get(dev)
+    if n is None:
+        n = int(_fn("q25_sm_count", [], "core")()) if dev >= 0 else 148
+        if n <= 0:
+            raise KernelError("cannot read the device's multiprocessor count")
+        _sm_count[dev] = n
+    return n
+
+
+def chain_grid() -> int:
+    """CTAs of the chain kernel (one per SM); its barrier counter advances by this per barrier."""
+    return int(_fn("q25_gemm_chain_grid", [])())
 
 
 def launch_count() -> int:
@@ -223,8 +242,8 @@ def attention_decode_fused(qkv: torch.Tensor, out: torch.Tensor, k_pages: torch.
                            positions: torch.Tensor, inv_freq: torch.Tensor, axis: torch.Tensor,
                            kv_slot: torch.Tensor, scratch: Optional[torch.Tensor] = None,
                            angles: Optional[torch.Tensor] = None, dense: bool = False) -> None:
-    """One kernel for a step of one-token entries: 3-axis rotary encoding of q and the new k
-    (``positions`` int32 [3, N], ``inv_freq`` float32 [D/2], ``axis`` int32 [D/2]), the write of
+    """One kernel for a step of one-token entries: rotary encoding of q and the new k
+    (``positions`` int32 [axes, N], ``inv_freq`` float32 [D/2], ``axis`` int32 [D/2]), the write of
     the new k and v at ``kv_slot``, attention, and the merge of the ``n_splits`` key ranges
     (through ``scratch`` as for ``attention_decode``; the CTA that finishes last merges).
     ``qkv`` is read as projected and left unchanged.  ``angles``: the step's table from
@@ -241,27 +260,9 @@ def attention_decode_fused(qkv: torch.Tensor, out: torch.Tensor, k_pages: torch.
     if not attention_fused_supports(qkv.dtype, head_dim, page_size, nq // nkv) or n_splits < 1:
         raise KernelError(f"attention_decode_fused: unsupported head size {head_dim}, page size {page_size}, "
                           f"group {nq // nkv} or splits {n_splits}")
-    if positions.dtype != torch.int32 or positions.dim() != 2 or positions.shape[0] != 3:
-        raise KernelError("attention_decode_fused: positions must be int32 [3, N]")
-    if _chain is not None and CHAIN_ATTENTION and head_dim in (64, 128):
-        # an operation of the chain: it runs between the qkv product before it and the o product after
-        counters = _split_counters(qkv.device, n_items * nkv)
-        desc = _ChainOpDesc(kind=1, qkv=qkv.data_ptr(), attn_out=out.data_ptr(), kpages=k_pages.data_ptr(),
-                            vpages=v_pages.data_ptr(), block_table=block_table.data_ptr(), cu_q=cu_q.data_ptr(),
-                            q_start=q_start_pos.data_ptr(), items=items.data_ptr(), positions=positions.data_ptr(),
-                            inv_freq=inv_freq.data_ptr(), axis=axis.data_ptr(), kv_slot=kv_slot.data_ptr(),
-                            attn_scratch=_ptr(scratch), attn_counters=counters.data_ptr(), angles=_ptr(angles),
-                            qkv_stride=qkv.stride(0), table_width=block_table.shape[1], n_items=n_items, nq=nq, nkv=nkv,
-                            d=head_dim, page_size=page_size, window=int(window or 0), n_splits=int(n_splits),
-                            n_tokens=positions.shape[1], scale=float(scale))
-        keep = (qkv, out, k_pages, v_pages, block_table, cu_q, q_start_pos, items, positions, inv_freq, axis, kv_slot,
-                scratch, counters, angles)
-        args = (qkv, out, k_pages, v_pages, block_table, cu_q, q_start_pos, items, nq, nkv, head_dim, page_size, window,
-                scale, n_splits, positions, inv_freq, axis, kv_slot, scratch, angles, dense)
-        _chain.append((desc, keep, lambda: attention_decode_fused(*args)))
-        if len(_chain) == CHAIN_MAX_OPS:
-            chain_flush()
-        return
+    if positions.dtype != torch.int32 or positions.dim() != 2 or (angles is None and positions.shape[0] != 3):
+        raise KernelError("attention_decode_fused: positions must be int32 [axes, N]; without an angle table the kernel "
+                          "computes the angles itself and reads three axes")
     _check(_fn("q25_attention_decode_fused_bf16",
                [_P, _I, _P, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _I, _P, _I, _P, _P, _P, _P, _P, _P, _I, _P])(
         qkv.data_ptr(), qkv.stride(0), out.data_ptr(), k_pages.data_ptr(), v_pages.data_ptr(), block_table.data_ptr(),
@@ -420,37 +421,24 @@ def gemm_skinny_norm(x: torch.Tensor, norm_weight: torch.Tensor, eps: float, w: 
 
 
 class _ChainOpDesc(ctypes.Structure):
-    """One operation of a chain as ``csrc/gemm_chain.cu`` reads it (``ChainOpDesc``): a product
-    (kind 0) or a decode attention (kind 1, the arguments of ``attention_decode_fused``)."""
+    """One product of a chain as ``csrc/gemm_chain.cu`` reads it (``ChainOpDesc``)."""
     _fields_ = [("W", _P), ("X", _P), ("norm_w", _P), ("bias", _P), ("out", _P), ("ldx", _I), ("ldo", _I), ("M", _I),
-                ("N", _I), ("K", _I), ("epi", _I), ("norm", _I), ("eps", _F), ("kind", _I),
-                ("qkv", _P), ("attn_out", _P), ("kpages", _P), ("vpages", _P), ("block_table", _P), ("cu_q", _P),
-                ("q_start", _P), ("items", _P), ("positions", _P), ("inv_freq", _P), ("axis", _P), ("kv_slot", _P),
-                ("attn_scratch", _P), ("attn_counters", _P), ("angles", _P),
-                ("qkv_stride", _I), ("table_width", _I), ("n_items", _I), ("nq", _I), ("nkv", _I), ("d", _I),
-                ("page_size", _I), ("window", _I), ("n_splits", _I), ("n_tokens", _I), ("scale", _F), ("reserved", _I)]
+                ("N", _I), ("K", _I), ("epi", _I), ("norm", _I), ("eps", _F), ("reserved", _I)]
 
 
 CHAIN_MAX_OPS = 8
-# Whether the decode attention joins the chains as an operation.  Measured on B200 at the 3B sizes it
-# does not pay: a step took 2.57 ms with it against 2.28 ms without, because every barrier costs
-# the lateness of the slowest CTA (3 to 4 us with the attention's merge tail) where a kernel boundary
-# costs about as much.  The operation stays (``Q25VL_CHAIN_ATTENTION=1``) and is tested.
-CHAIN_ATTENTION = __import__("os").environ.get("Q25VL_CHAIN_ATTENTION", "0") == "1"
-CHAIN_GRID = 148                          # CTAs of the chain kernel: one per SM of a B200
 _chain_base = 0                           # value of the barrier counter when the next chain kernel begins
 _CHAIN_SAFE = {"q25_gemm_chain_bf16", "q25_gemm_chain_scratch_floats", "q25_gemm_chain_available", "q25_gemm_chain_desc_bytes",
-               "q25_gemm_skinny_resident", "q25_gemm_skinny_bf16", "q25_gemm_skinny_norm_bf16"}
+               "q25_gemm_chain_grid", "q25_sm_count", "q25_gemm_skinny_resident", "q25_gemm_skinny_bf16",
+               "q25_gemm_skinny_norm_bf16"}
 _chain: Optional[list] = None             # the waiting products: (description, tensors kept alive, replay as one kernel)
 _chain_state: Dict[torch.device, tuple] = {}
 _chain_scratch: Dict[torch.device, list] = {}
 
 
 def chain_available() -> bool:
-    """Whether chains can run here: a whole grid resident at once, and not switched off
-    (``Q25VL_GEMM_CHAIN=0``)."""
-    import os
-    if os.environ.get("Q25VL_GEMM_CHAIN", "1") == "0" or not torch.cuda.is_available():
+    """Whether chains can run here: a CUDA device that holds the kernel's whole grid at once."""
+    if not torch.cuda.is_available():
         return False
     if not _fn("q25_gemm_chain_available", [])():
         return False
@@ -488,7 +476,7 @@ def chain_end() -> None:
 def _chain_add(x, norm_weight, eps, w, bias, out, epilogue) -> bool:
     desc = _ChainOpDesc(W=w.data_ptr(), X=x.data_ptr(), norm_w=_ptr(norm_weight), bias=_ptr(bias), out=out.data_ptr(),
                         ldx=x.stride(0), ldo=out.stride(0), M=x.shape[0], N=w.shape[0], K=w.shape[1], epi=int(epilogue),
-                        norm=0 if norm_weight is None else 1, eps=float(eps), kind=0)
+                        norm=0 if norm_weight is None else 1, eps=float(eps))
     if norm_weight is None:
         alone = lambda: gemm_skinny(x, w, bias, out, int(epilogue))
     else:
@@ -523,7 +511,7 @@ def chain_flush() -> None:
         _check(_fn("q25_gemm_chain_bf16", [_P, _I, _P, _P, _P, ctypes.c_uint, _P, _P])(
             ctypes.cast(ops, _P), len(waiting), held[-1].data_ptr(), counters.data_ptr(), barrier.data_ptr(),
             _chain_base, error_flag(device).data_ptr(), _stream()), "gemm_chain")
-        _chain_base = (_chain_base + (len(waiting) - 1) * CHAIN_GRID) & 0xFFFFFFFF
+        _chain_base = (_chain_base + (len(waiting) - 1) * chain_grid()) & 0xFFFFFFFF
     finally:
         _chain = []
 

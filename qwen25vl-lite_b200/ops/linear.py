@@ -10,7 +10,7 @@
   (``csrc/gemm_tcgen05.cu``: TMA loads, accumulators in tensor memory) with the same
   epilogues, or the library product (cuBLAS through ``torch.mm`` / ``torch.addmm``), which the
   reference's engine uses for every projection (``nn.Linear``,
-  src/qwen25vl_lite/text.py:61-63,80-83; src/qwen25vl_lite/model.py:84); see ``LARGE_GEMM``.
+  src/qwen25vl_lite/text.py:61-63,80-83; src/qwen25vl_lite/model.py:84); see ``use_tcgen05``.
   Batches of 17 to 127 rows and operands the tcgen05 kernel refuses (K not a multiple of 8,
   unaligned rows) go to the library.
 """
@@ -19,27 +19,21 @@ from __future__ import annotations
 
 from typing import Optional
 
-import os
-
 import torch
 
 from . import kernels
 
-# Which kernel takes the many-row products.  Measured on B200 at 3B sizes and 2,048 rows, the
-# one-CTA tcgen05 kernel reaches 1.10-1.20 PFLOP/s where cuBLAS (two-CTA kernels) reaches
-# 1.43-1.47, so by default ("auto") it takes the products where its fused epilogue saves a kernel
-# and a round trip through memory (gate_up with SwiGLU: 168 us against 126 + 75 us), and the
-# library takes the others.  "tcgen05" sends every product to the engine's kernel, "cublas" none.
-LARGE_GEMM = os.environ.get("Q25VL_LARGE_GEMM", "auto")
 # The tcgen05 kernel works in tiles of 128 rows; below that (decode batches of 17 to 127 requests)
 # too few tiles would stream the weights, and the library product is used.
 TCGEN05_MIN_ROWS = 128
 
 
 def use_tcgen05(x: torch.Tensor, w: torch.Tensor, fused_epilogue: bool = False) -> bool:
-    if LARGE_GEMM == "cublas" or (LARGE_GEMM == "auto" and not fused_epilogue):
-        return False
-    return x.shape[0] >= TCGEN05_MIN_ROWS and kernels.gemm_tcgen05_supports(x, w)
+    """Which kernel takes a many-row product.  Measured on B200 at 3B sizes and 2,048 rows, the
+    one-CTA tcgen05 kernel reaches 1.10-1.27 PFLOP/s where cuBLAS (two-CTA kernels) reaches
+    1.43-1.47, so it takes the products where its fused epilogue saves a kernel and a round trip
+    through memory (gate_up with SwiGLU: 168 us against 126 + 75 us), and the library the others."""
+    return fused_epilogue and x.shape[0] >= TCGEN05_MIN_ROWS and kernels.gemm_tcgen05_supports(x, w)
 
 
 class DeferredNorm:

@@ -65,9 +65,17 @@ class GQAAttention(Mixer):
     accepts_deferred_norm = True     # forward takes a DeferredNorm as its input
     accepts_residual = True          # forward can add its result into the residual stream itself
 
+    def plan_key(self):
+        """Mixers with equal keys read the same work lists, which are then built once a step."""
+        return ("gqa_attention", self.rows_per_token)
+
+    def plan_step(self, host):
+        """The attention kernels' work lists for a step of this shape (int32 arrays by name)."""
+        return attention_ops.plan_step(host, self.rows_per_token)
+
     def forward(self, ctx, h, stop, residual=None):
         """Returns the update of the residual stream, or None after adding it into ``residual``."""
         qkv = self.qkv_proj(h)
-        out = attention_ops.attend(ctx, qkv, ctx.kv(stop), self.position, self.num_heads, self.num_kv_heads,
-                                   self.head_dim, self.window, self.scale, stop.owns_cache)
+        out = attention_ops.attend(ctx, ctx.plan(self), qkv, ctx.kv(stop), self.position, self.num_heads,
+                                   self.num_kv_heads, self.head_dim, self.window, self.scale, stop.owns_cache)
         return self.o_proj(out, residual=residual)

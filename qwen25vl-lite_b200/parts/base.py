@@ -56,6 +56,19 @@ class Part:
     def load(self, tensors: Dict[str, torch.Tensor], device, dtype: torch.dtype) -> None:
         pass
 
+    # Sharing of device tensors between parts (a tied output head reads the embedding table):
+    # after ``load`` a part's ``exports()`` are offered to the parts that follow it under their
+    # canonical checkpoint names; a part that lists a name in ``imports()`` is handed it through
+    # ``receive`` before its own ``load``.
+    def exports(self) -> Dict[str, torch.Tensor]:
+        return {}
+
+    def imports(self) -> Sequence[str]:
+        return ()
+
+    def receive(self, tensors: Dict[str, torch.Tensor]) -> None:
+        pass
+
 
 class Norm(Part):
     """``forward(ctx, x, delta, rows=None) -> h``: x (float32 residual stream, [N, H]) takes
@@ -68,21 +81,37 @@ class Norm(Part):
 
 
 class PositionEncoding(Part):
-    """How positions reach queries and keys.
+    """How positions reach queries and keys, and what a token's position is when nobody says.
 
-    ``axes``: how many integers describe one token's position.
+    A model has one encoding that defines its tokens' positions (``ModelSpec.position``): how many
+    integers describe a position (``axes``), and the positions of plain text.  A layer may apply
+    another encoding to those same positions (``LayerSpec.position``), or none.
+
     ``default_positions(start, count, offset)``: positions of ``count`` tokens of plain text
     starting at index ``start`` of a request whose per-request offset is ``offset``
     -> int array [axes, count].
+    ``offset_after(max_position, num_tokens)``: the request's offset once ``num_tokens`` tokens
+    with positions up to ``max_position`` are in: where plain text resumes after tokens that
+    brought positions of their own.
+    ``default_is_linear``: set True when ``default_positions`` is ``start + offset + i`` on every
+    axis, which lets the step function fill a whole batch of single tokens at once.
     ``rotate_and_store(ctx, qkv, ...)``: encode q and k in place and write k, v to the pages.
-    Optional ``rope_tables() -> (inv_freq, axis)``: a 3-axis rotary encoding that lets the fused
-    decode attention kernel do the rotation itself.
+    Optional ``rope_tables() -> (inv_freq float32 [D/2], axis int32 [D/2])``: a rotary encoding
+    (channel j turns by ``position[axis[j]] * inv_freq[j]``, any number of axes) that lets the
+    fused decode attention kernel do the rotation itself.
+    Optional ``prompt_positions(num_tokens, image_spans)``: positions of a prompt with image runs.
     """
 
     axes = 1
+    default_is_linear = False
 
     def default_positions(self, start: int, count: int, offset: int):
         raise NotImplementedError
+
+    def offset_after(self, max_position: int, num_tokens: int) -> int:
+        """Plain text resumes one past the largest position seen so far (the reference's
+        ``rope_delta = max(pos) + 1 - length``, src/qwen25vl_lite/rope.py:235)."""
+        return int(max_position) + 1 - int(num_tokens)
 
     def rotate_and_store(self, ctx, qkv, nq, nkv, head_dim, kv):
         raise NotImplementedError
@@ -105,6 +134,13 @@ class Mixer(Part):
     state tensor [max_seqs, *shape] when ``state_need`` asked for one, indexed by
     ``ctx.slot_ids``.  A mixer with state must process a request's tokens in order and must
     give the same result wherever the run of tokens is cut.
+
+    A part whose kernels read per-step work lists may define ``plan_step(host) -> {name: int32
+    array}`` (``host.q_lens``, ``host.starts``, ``host.n_tokens``, ``host.n_seqs`` describe the
+    step) and ``plan_key()`` (parts with equal keys share one plan).  The step function packs the
+    arrays into its one transfer; ``ctx.plan(part)`` returns their device copies by name (None for
+    an empty array).  The sizes may depend only on ``q_lens``, so that a captured step finds them at
+    the same place in every replay.
     """
 
     def cache_need(self) -> Optional[KVCacheNeed]:

@@ -83,6 +83,10 @@ class MRope(PositionEncoding):
         """(inv_freq float32 [D/2], axis int32 [D/2]) for kernels that rotate by themselves."""
         return self.inv_freq, self.axis
 
+    def prompt_positions(self, num_tokens: int, image_spans):
+        """Positions [3, num_tokens] of a prompt whose image runs are ``(start, t, h, w)``."""
+        return prompt_positions(num_tokens, image_spans)[0]
+
     def rotate_and_store(self, ctx, qkv, nq, nkv, head_dim, kv):
         """kv: the pages and slots of the stop's cache group, or None to store nothing."""
         if head_dim != self.head_dim:

@@ -24,17 +24,20 @@ class SamplingParams:
     stop_token_ids: Sequence[int] = field(default_factory=tuple)
     ignore_eos: bool = False
 
+    # (field, what its value must satisfy, the rule in words); the same rules as sampling.py:30-41
+    _RULES = (
+        ("temperature", lambda v: v >= 0, "0 (greedy) or more"),
+        ("top_p", lambda v: 0.0 < v <= 1.0, "above 0 and at most 1"),
+        ("max_tokens", lambda v: v >= 1, "at least 1"),
+        ("repetition_penalty", lambda v: v > 0, "above 0 (1 switches it off)"),
+        ("min_p", lambda v: 0.0 <= v <= 1.0, "between 0 and 1"),
+    )
+
     def validate(self) -> None:
-        if self.temperature < 0:
-            raise ValueError("temperature must be >= 0")
-        if not 0.0 < self.top_p <= 1.0:
-            raise ValueError("top_p must be in (0, 1]")
-        if self.max_tokens <= 0:
-            raise ValueError("max_tokens must be positive")
-        if self.repetition_penalty <= 0:
-            raise ValueError("repetition_penalty must be positive")
-        if not 0.0 <= self.min_p <= 1.0:
-            raise ValueError("min_p must be in [0, 1]")
+        for name, holds, rule in self._RULES:
+            value = getattr(self, name)
+            if not holds(value):
+                raise ValueError(f"SamplingParams.{name} = {value!r}: must be {rule}")
 
     @property
     def has_penalties(self) -> bool:

@@ -292,3 +292,131 @@ def test_toy_routed_feed_forward_and_other_position_encoding(tmp_path):
     runner.close_request(r)
     assert np.abs(np.concatenate(got) - want).max() < 1e-4
     runner.cache.check(runner.live.values())
+
+
+# ---- layers that differ in their position encoding ---------------------------------------------------
+D3, HEADS3, KV3, HIDDEN3, THETA3 = 64, 4, 2, 256, 3000.0
+
+if "toy_rope_1axis" not in POSITION_ENCODINGS:
+    @register_position_encoding("toy_rope_1axis")
+    class ToyRope1Axis(PositionEncoding):
+        """A rotary encoding with ONE position axis that pairs channel j with j + D/2 and hands out
+        its tables, so that one-token steps take the fused decode attention kernel; everything
+        else goes through the engine's rotate-and-store kernel with those same tables."""
+
+        axes = 1
+        default_is_linear = True
+        graph_safe = True
+
+        def __init__(self, head_dim, theta):
+            self.d, self.theta = int(head_dim), float(theta)
+
+        def load(self, tensors, device, dtype):
+            self.inv = (1.0 / self.theta ** (torch.arange(0, self.d, 2, dtype=torch.float32) / self.d)).to(device)
+            self.axis = torch.zeros(self.d // 2, dtype=torch.int32, device=device)
+
+        def default_positions(self, start, count, offset):
+            return np.arange(start + offset, start + offset + count, dtype=np.int64)[None, :]
+
+        def rope_tables(self):
+            return self.inv, self.axis
+
+        def rotate_and_store(self, ctx, qkv, nq, nkv, head_dim, kv):
+            from qwen25vl_lite.ops import kernels
+            if kv is None:
+                kernels.rope_store(qkv, ctx.positions, self.inv, self.axis, None, None, None, nq, nkv, head_dim, 1)
+            else:
+                kernels.rope_store(qkv, ctx.positions, self.inv, self.axis, kv.k_pages, kv.v_pages, kv.kv_slot, nq, nkv,
+                                   head_dim, kv.page_size)
+
+    @register_position_encoding("toy_no_position")
+    class ToyNoPosition(PositionEncoding):
+        """No encoding at all: keys and values are stored as projected (a layer that relies on the
+        causal mask alone).  It defines no positions of its own, so it can only be a layer's
+        encoding, never the model's."""
+
+        axes = 0
+        graph_safe = True
+
+        def rotate_and_store(self, ctx, qkv, nq, nkv, head_dim, kv):
+            from qwen25vl_lite.ops import kernels
+            if kv is not None:
+                kernels.rope_store(qkv, None, None, None, kv.k_pages, kv.v_pages, kv.kv_slot, nq, nkv, head_dim, kv.page_size)
+
+
+def toy3_spec(cfg):
+    norms = lambda: (PartSpec("rmsnorm", dict(dim=HIDDEN3, eps=EPS), "norm_a."), PartSpec("rmsnorm", dict(dim=HIDDEN3, eps=EPS), "norm_b."))
+    attn = PartSpec("gqa_attention", dict(hidden_size=HIDDEN3, num_heads=HEADS3, num_kv_heads=KV3, head_dim=D3), "attn.")
+    ffn = PartSpec("swiglu", dict(hidden_size=HIDDEN3, intermediate_size=96), "ffn.")
+    layers = (
+        LayerSpec("prenorm_residual", attn, ffn, norms(), "blocks.0."),                               # the model's encoding
+        LayerSpec("prenorm_residual", attn, ffn, norms(), "blocks.1.", position=PartSpec("toy_no_position")),
+        LayerSpec("prenorm_residual", attn, ffn, norms(), "blocks.2.",
+                  position=PartSpec("toy_rope_1axis", dict(head_dim=D3, theta=7.0 * THETA3))),         # another theta
+    )
+    return ModelSpec(
+        embedding=PartSpec("token_embedding", dict(vocab_size=VOCAB, hidden_size=HIDDEN3), "embed."),
+        layers=layers, schedule=(ScheduleEntry(0), ScheduleEntry(1), ScheduleEntry(2)),
+        final_norm=PartSpec("rmsnorm", dict(dim=HIDDEN3, eps=EPS), "final_norm."),
+        head=PartSpec("linear_head", dict(vocab_size=VOCAB, hidden_size=HIDDEN3, tied=True, tied_to="embed.weight"), "head."),
+        position=PartSpec("toy_rope_1axis", dict(head_dim=D3, theta=THETA3)),
+    )
+
+
+register_architecture("ToyMixedPositionsForTest", lambda raw: dict(raw), toy3_spec, replace=True)
+
+
+def oracle3(w, ids):
+    n = len(ids)
+    pos = np.arange(n, dtype=np.float64)
+
+    def rot(x, theta):
+        if theta is None:
+            return x
+        inv = 1.0 / theta ** (np.arange(0, D3, 2, dtype=np.float64) / D3)
+        ang = pos[:, None] * inv[None, :]
+        cos, sin = np.cos(ang)[:, None, :], np.sin(ang)[:, None, :]
+        a, b = x[..., :D3 // 2], x[..., D3 // 2:]
+        return np.concatenate([a * cos - b * sin, b * cos + a * sin], axis=-1)
+
+    x = w["embed.weight"][np.asarray(ids)]
+    for layer, theta in enumerate((THETA3, None, 7.0 * THETA3)):
+        p = f"blocks.{layer}."
+        h = plain.rms_norm(x, w[p + "norm_a.weight"], EPS)
+        q = (h @ w[p + "attn.q_proj.weight"].T + w[p + "attn.q_proj.bias"]).reshape(n, HEADS3, D3)
+        k = (h @ w[p + "attn.k_proj.weight"].T + w[p + "attn.k_proj.bias"]).reshape(n, KV3, D3)
+        v = (h @ w[p + "attn.v_proj.weight"].T + w[p + "attn.v_proj.bias"]).reshape(n, KV3, D3)
+        x = x + plain.causal_attention(rot(q, theta), rot(k, theta), v).reshape(n, HEADS3 * D3) @ w[p + "attn.o_proj.weight"].T
+        x = x + plain.swiglu_mlp(plain.rms_norm(x, w[p + "norm_b.weight"], EPS), w, p + "ffn.")
+    return plain.rms_norm(x, w["final_norm.weight"], EPS) @ w["embed.weight"].T
+
+
+@pytest.mark.parametrize("dtype,tol", [("float32", 1e-4), ("bfloat16", 3e-2)])
+def test_layers_with_different_position_encodings(tmp_path, dtype, tol):
+    """Three layers of one model: the model's one-axis rotary encoding, no encoding at all, and the
+    same rotary kind with another base -- all three kinds defined in this file, named layer by
+    layer in the model's description.  Stepped whole, in portions and token by token (in bfloat16
+    from CUDA graphs: the rotary layers through the fused decode attention with their one-axis
+    tables, the layer without encoding through the split-KV decode kernel)."""
+    folder = write_random_model(str(tmp_path / "toy3"), {"architectures": ["ToyMixedPositionsForTest"]}, seed=10,
+                                storage_dtype=dtype, prefix="")
+    _, model = load_model(folder, dtype, "cuda:0")
+    assert len(model.position_encodings()) == 3
+    runner = ModelRunner(model, 16, 16, 2)
+    assert runner.axes == 1 and runner.cuda_graphs
+    w = {k: v.astype(np.float64) for k, v in plain.read_safetensors(os.path.join(folder, "model.safetensors")).items()}
+    ids = np.random.default_rng(4).integers(0, VOCAB, size=90).tolist()
+    want = oracle3(w, ids)
+    r = runner.open_request("whole")
+    whole = runner.step([StepEntry(r, ids, list(range(90)))]).cpu().numpy()
+    runner.close_request(r)
+    assert np.abs(whole - want).max() < tol
+    r = runner.open_request("cut")
+    got = [runner.step([StepEntry(r, ids[:40], list(range(40)))]).cpu().numpy(),
+           runner.step([StepEntry(r, ids[40:43], [0, 1, 2])]).cpu().numpy()]
+    got += [runner.step([StepEntry(r, [t], [0])]).cpu().numpy() for t in ids[43:]]
+    runner.close_request(r)
+    assert np.abs(np.concatenate(got) - want).max() < tol
+    if dtype == "bfloat16":
+        assert runner.graph_replays >= 40
+    runner.cache.check(runner.live.values())

@@ -150,8 +150,7 @@ def test_bfloat16_generation_agrees_with_the_plain_decoder(name, temperature, tm
     decoder's own choice at its place, or score within bfloat16 rounding of it; and a second run
     with the same seed repeats the tokens."""
     from qwen25vl_lite import LLM, SamplingParams
-    from test_replay_gpu import TOL
-    from tiny_models import make_model_dir
+    from tiny_models import BF16_TOLERANCE, make_model_dir
     folder = make_model_dir(tmp_path, name, "bfloat16")
     llm = LLM(folder, dtype="bfloat16", num_blocks=48, block_size=16, max_num_batched_tokens=24)
     prompts = _prompts(name, (12, 33, 70), 24)
@@ -160,7 +159,7 @@ def test_bfloat16_generation_agrees_with_the_plain_decoder(name, temperature, tm
     assert [len(o.output_token_ids) for o in outs] == [24, 24, 24]
     assert llm.runner.graph_replays > 0
     cfg, w = plain.load_model_dir(folder, np.float64)
-    tol = TOL["bfloat16", name]
+    tol = BF16_TOLERANCE[name]
     for p, o in zip(prompts, outs):
         margins = plain.generation_margins(cfg, w, p, o.output_token_ids, temperature=temperature, seed=5)
         bound = 2 * tol / temperature if temperature > 0 else 2 * tol       # both scores may be off by tol (/ T)
@@ -215,3 +214,43 @@ def test_captured_decode_steps_agree_with_kernel_by_kernel_steps_at_full_layer_s
         torch.cuda.empty_cache()
     graph, eager = outs
     assert np.abs(graph - eager).max() <= 2e-2 * np.abs(eager).max()
+
+
+def test_a_kernel_that_gave_up_a_wait_fails_the_step_and_only_that_step(model_dirs):
+    """Kernels with bounded waits report a wait that ran out through a flag on the device.  The flag
+    is set here by hand (no kernel is made to hang): the generation whose step carried it must
+    raise before any token of that step is accepted, the trace session likewise before it hands
+    logits out, and the next call works, because raising clears the flag."""
+    from qwen25vl_lite import LLM, SamplingParams
+    from qwen25vl_lite.engine.trace import TraceSession
+    from qwen25vl_lite.ops import kernels
+    llm = LLM(model_dirs["A"], dtype="float32", num_blocks=32, block_size=4, max_num_seqs=2)
+    prompt = _prompts("A", (9,), 29)
+    params = SamplingParams(max_tokens=3, ignore_eos=True)
+    want = llm.generate(prompt, params)[0].output_token_ids
+    kernels.error_flag("cuda:0").fill_(14)
+    with pytest.raises(kernels.KernelError, match="code 14"):
+        llm.generate(prompt, params)
+    for seq in list(llm.engine.running) + list(llm.engine.waiting):
+        llm.engine.abort(seq.seq_id)
+    assert int(kernels.error_flag("cuda:0")[0]) == 0
+    assert llm.generate(prompt, params)[0].output_token_ids == want
+    session = TraceSession(llm.runner, None)
+    kernels.error_flag("cuda:0").fill_(3)
+    with pytest.raises(kernels.KernelError, match="code 3"):
+        session.run_step({"step": 0, "entries": [{"id": "x", "tokens": prompt[0], "want": [8]}], "end": ["x"]})
+    assert int(kernels.error_flag("cuda:0")[0]) == 0
+
+
+def test_generate_with_random_weights_from_the_command_line(model_dirs):
+    """``generate --random-weights --weights-seed S``: --model only has to hold a config.json."""
+    cmd = [sys.executable, "-m", "qwen25vl_lite.cli", "generate", "--model", os.path.join(model_dirs["A"], "config.json"),
+           "--random-weights", "--weights-seed", "7", "--dtype", "float32", "--block-size", "4", "--num-blocks", "32",
+           "--max-tokens", "4", "--ignore-eos", "--prompt-token-ids", "5,6,7"]
+    runs = [subprocess.run(cmd, cwd=ROOT, capture_output=True, text=True, timeout=300) for _ in range(2)]
+    assert all(r.returncode == 0 for r in runs), runs[0].stderr
+    ids = [eval(r.stdout.strip().splitlines()[-1]) for r in runs]
+    assert ids[0] == ids[1] and len(ids[0]) == 4 and all(0 <= t < 256 for t in ids[0])
+    cmd[cmd.index("7")] = "8"
+    other = subprocess.run(cmd, cwd=ROOT, capture_output=True, text=True, timeout=300)
+    assert other.returncode == 0 and len(eval(other.stdout.strip().splitlines()[-1])) == 4

@@ -47,14 +47,18 @@ def load_random(part, rng, dtype, **kw):
 class Shell:
     """What the step function needs of a model, around one callable."""
 
-    def __init__(self, fn, position, dtype, needs=(), vocab=1 << 20):
+    def __init__(self, fn, position, dtype, needs=(), vocab=1 << 20, planning=()):
         self.fn, self.position, self.dtype, self.device = fn, position, dtype, torch.device("cuda")
+        self._planning = list(planning)
         self.stops = [StopRuntime(i, 0, n.cache_of, n.cache_of is None) for i, n in enumerate(needs)]
         self._needs = list(needs)
         self.head = SimpleNamespace(vocab_size=vocab)
 
     def stop_needs(self):
         return self._needs
+
+    def planning_parts(self):
+        return self._planning
 
     def forward(self, ctx):
         return self.fn(ctx)
@@ -103,7 +107,8 @@ def test_embedding_and_head_parts(dtype):
     x = emb.forward(ctx)
     assert x.dtype == torch.float32 and np.array_equal(f64(x), we["weight"][ids])
     tied = parts.HEADS["linear_head"](vocab_size=301, hidden_size=40, tied=True)
-    tied.load({}, "cuda", dtype, tied_weight=emb.weight)
+    tied.receive({"embed_tokens.weight": emb.weight})
+    tied.load({}, "cuda", dtype)
     h = rand(rng, (5, 40)).to(dtype)
     logits = tied.forward(ctx, h.cuda())
     assert logits.dtype == torch.float32 and np.abs(f64(logits) - f64(h) @ we["weight"].T).max() < tol(dtype)
@@ -124,7 +129,8 @@ def test_attention_part_in_portions(dtype, nq, nkv, d, section, window):
                                          position=rope, window=window)
     w = load_random(attn, rng, dtype)
     inputs = {}
-    shell = Shell(lambda ctx: attn.forward(ctx, inputs["h"], shell.stops[0]), rope, dtype, [StopNeeds(attn.cache_need())])
+    shell = Shell(lambda ctx: attn.forward(ctx, inputs["h"], shell.stops[0]), rope, dtype, [StopNeeds(attn.cache_need())],
+                  planning=[attn])
     runner = ModelRunner(shell, 32, 8, 4)
     n_a, n_b = 45, 20
     h_a, h_b = rand(rng, (n_a, hidden)).to(dtype), rand(rng, (n_b, hidden)).to(dtype)
@@ -173,7 +179,7 @@ def test_block_part(dtype):
         pending = block.forward(ctx, x, None, shell.stops[0])
         return x if pending is None else x + pending.float()       # None: the block added it itself
 
-    shell = Shell(fn, rope, dtype, [StopNeeds(attn.cache_need())])
+    shell = Shell(fn, rope, dtype, [StopNeeds(attn.cache_need())], planning=[attn])
     runner = ModelRunner(shell, 8, 8, 2)
     out = runner.step([StepEntry(runner.open_request("a"), [0] * 23, [])])
     cfg = {"num_attention_heads": nq, "num_key_value_heads": nkv, "hidden_size": hidden, "rms_norm_eps": 1e-6}

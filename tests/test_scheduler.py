@@ -125,7 +125,7 @@ def test_without_chunked_prefill_a_prompt_runs_whole_or_not_at_all():
     assert runner.batches[0] == [(0, 20, 1)]               # the second prompt does not fit beside the first
     engine.run_until_complete()
     engine.add_request(list(range(40)), SamplingParams(max_tokens=2))
-    with pytest.raises(RuntimeError, match="no progress"):
+    with pytest.raises(RuntimeError, match="changed nothing"):
         engine.run_until_complete(max_stall=8)
 
 

@@ -65,7 +65,8 @@ def test_no_alloc_entry_point_matches_the_allocating_one_twice_in_a_row():
     for seed, lens, nq, nkv, d, ps, window, splits in [
             (1, [700, 33, 1, 260], 16, 2, 128, 16, 0, 6),
             (2, [90, 301, 150], 6, 1, 32, 8, 100, 3),
-            (3, [64, 65], 4, 2, 64, 16, 0, 1)]:
+            (3, [64, 65], 4, 2, 64, 16, 0, 1),
+            (5, [2300, 17], 8, 2, 64, 16, 0, 70)]:       # more splits than a warp has lanes, twice over
         c = _case(seed, lens, nq, nkv, d, ps)
         code, got = _no_alloc(fn, c, len(lens), nq, nkv, d, ps, window, splits)
         assert code == 0, msg().decode()
