@@ -382,30 +382,33 @@ struct DecodeUnit {
     }
   }
 
-  // prefetch_here: the caller has not called prefetch(); the first tiles are asked for here, after the
-  // loads of q and of the angles are on their way, so that those do not queue behind the trip to
-  // the block table.
-  template <typename Sync>
+  // What does not depend on the kernel before this one comes first: the entry's position and block
+  // table (step metadata, copied before any kernel of the step ran) and the copies of the first
+  // tiles of keys and values (written by earlier steps).  wait() then waits for that kernel
+  // (programmatic dependent launch: this prologue overlaps its tail), and q, the token's own key and
+  // value and the angles are asked for together: one trip to memory.
+  template <typename Sync, typename Wait>
   __device__ static __forceinline__ void run(const AttnArgs& a, const RopeArgs& r, int item, int kvh, int split,
-                                             unsigned char* smem, int tid, Sync sync, bool prefetch_here = false) {
+                                             unsigned char* smem, int tid, Sync sync, Wait wait) {
     constexpr int NT = WARPS * 32;
     const int warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
     const int G = a.nq / a.nkv;
-    // Everything that needs only the token is asked for before the entry's position is (the position
-    // decides the key range, the block-table look-ups follow it): one trip to memory, not three.
-    const int token = a.items ? a.cu_q[a.items[item]] : item;
+    const Range R = range(a, item, split);
+    const int token = R.token;
+    const int slot_new = r.kv_slot[token];
+    prefetch(a, R, kvh, smem, tid);
+    wait();
     // q of the group's heads, rotated in registers later: channels j and j + D/2 sit in k-steps ks and
     // ks + D/32 of the same thread
     unsigned qf[D / 16][4];
     const bf16* qbase = a.qkv + (size_t)token * a.qkv_stride + (size_t)kvh * G * D;
     load_q<D>(qf, [&](int row) { return row < G ? qbase + (size_t)row * D : (const bf16*)nullptr; });
-    // the token's own key, value and slot: the unit that holds the last tile patches them into it
+    // the token's own key and value: the unit that holds the last tile patches them into it
     constexpr int KI = (HALF + 31) / 32, VI = (D + 31) / 32;
     const bf16* kv_new = a.qkv + (size_t)token * a.qkv_stride + (size_t)(a.nq + kvh) * D;
     const unsigned short* kraw = reinterpret_cast<const unsigned short*>(kv_new);
     const unsigned short* vraw = reinterpret_cast<const unsigned short*>(kv_new + (size_t)a.nkv * D);
     unsigned short k1_new[KI], k2_new[KI], v_newv[VI];
-    const int slot_new = r.kv_slot[token];
 #pragma unroll
     for (int i = 0; i < KI; ++i) {
       const int j = lane + 32 * i;
@@ -416,18 +419,16 @@ struct DecodeUnit {
     for (int i = 0; i < VI; ++i) v_newv[i] = lane + 32 * i < D ? __ldcg(vraw + lane + 32 * i) : (unsigned short)0;
     // the token has D/2 angles; from the step's table, or computed below once for the whole unit
     float2 angle_of_tid = make_float2(1.f, 0.f);
-    if (r.angles && tid < HALF) angle_of_tid = __ldg(r.angles + (size_t)token * HALF + tid);
+    if (r.angles && tid < HALF) angle_of_tid = __ldcg(r.angles + (size_t)token * HALF + tid);
 
-    const Range R = range(a, item, split);
     const int p = R.p, lo = R.lo;
     float2* cs = reinterpret_cast<float2*>(smem);
     int* is_last = reinterpret_cast<int*>(smem + HALF * 8);
     unsigned char* wbuf = smem + TILES_OFF + (size_t)warp * STAGES * 2 * TILE;
     int tile = R.t_begin + warp;
-    if (prefetch_here) prefetch(a, R, kvh, smem, tid);
     for (int j = tid; j < HALF; j += NT) {
       if (r.angles) {
-        cs[j] = j == tid ? angle_of_tid : r.angles[(size_t)token * HALF + j];
+        cs[j] = j == tid ? angle_of_tid : __ldcg(r.angles + (size_t)token * HALF + j);
       } else {
         // all five loads are independent of one another, so they cost one memory latency, not two
         const int ax = r.axis[j];

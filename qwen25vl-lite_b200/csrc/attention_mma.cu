@@ -286,11 +286,10 @@ __global__ void rope_angles_kernel(const int* __restrict__ positions, int n_toke
 template <int D, int WARPS, int BN, int STAGES>
 __global__ void __launch_bounds__(WARPS * 32) attention_decode_fused_kernel(AttnArgs a, RopeArgs r) {
   pdl_trigger();
-  pdl_wait();
   extern __shared__ __align__(16) unsigned char smem[];
   using Unit = DecodeUnit<D, WARPS, BN, STAGES>;
-  // the first tiles' copies start inside, before the position-encoding arithmetic
-  Unit::run(a, r, blockIdx.x, blockIdx.y, blockIdx.z, smem, threadIdx.x, [] { __syncthreads(); }, true);
+  // the look-ups and the first tiles' copies inside come before the wait for the kernel that made q
+  Unit::run(a, r, blockIdx.x, blockIdx.y, blockIdx.z, smem, threadIdx.x, [] { __syncthreads(); }, [] { pdl_wait(); });
 }
 
 

@@ -7,8 +7,14 @@
 // arrive (measured in a step: 7 to 12 us for products whose weights pass in 1.5 us).  Here the
 // links are operations of one kernel:
 //
-//   * One CTA per SM stays resident for the whole chain (cooperative launch).  Between two
+//   * One CTA per SM stays resident for the whole chain: the grid has as many CTAs as the device has
+//     SMs and a CTA's shared memory leaves room for no second one, so every CTA finds an SM as soon
+//     as the kernels before this one have left it, and all are resident together.  Between two
 //     operations the CTAs meet at a barrier in global memory (a counter that only grows).
+//   * The kernel is launched like every other kernel of the engine (programmatic dependent launch,
+//     common.cuh): its CTAs start on the SMs that the kernel before it has already left, set up
+//     their barriers and start the stream of weights, and only the warps that read x or write the
+//     output wait for that kernel to finish.
 //   * The producer warp does not meet anybody: weights depend on no activation, so it walks on
 //     through the operations and fills the ring of stages with the next operation's weights while
 //     the other warps are still finishing this one or stand at the barrier.  The stream from memory
@@ -99,6 +105,33 @@ __device__ __forceinline__ void gc_mma(float (&c)[4], unsigned a0, unsigned a1, 
                : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
+// The weights a CTA streams are a sequence of items, one stage of the ring each: for every operation
+// in order the CTA's groups, and for an operation that walks K sequentially the slices of each
+// group.  Advances (k, grp, j) = (operation, group, slice) to the next item; start with k = -1.
+__device__ __forceinline__ bool item_next(const ChainArgs& A, int cta, int& k, int& grp, int& j) {
+  if (k >= 0) {
+    const ChainOp& op = A.op[k];
+    if (op.seq) {
+      if (++j < op.slices) return true;
+      j = 0;
+    }
+    grp += op.ctas;
+    if (grp < op.groups) return true;
+  }
+  for (++k; k < A.n_ops; ++k) {
+    const ChainOp& op = A.op[k];
+    if (op.seq) {
+      grp = cta; j = 0;
+    } else {
+      j = cta / op.ctas;
+      if (j >= op.slices) continue;
+      grp = cta - j * op.ctas;
+    }
+    if (grp < op.groups) return true;
+  }
+  return false;
+}
+
 // accumulator (mt, e): output feature row0 + g + 8 * (e / 2), batch column mt * 8 + 2 t + (e & 1)
 template <int MT>
 __device__ __forceinline__ void gc_store_group(const float (&acc)[MT][4], int grp, const ChainOp& op, bool has_old = false) {
@@ -165,55 +198,39 @@ __global__ void __launch_bounds__(GC_THREADS, 1) gemm_chain_kernel(const __grid_
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
   }
   __syncthreads();
+  pdl_trigger();
 
   if (warp == GC_CONSUMERS) {
     // ---- producer: the weights of every operation, one bulk copy per row, as stages come free ----
+    // (Asking for the items further ahead to be brought into the L2 cache while the ring is full --
+    // cp.async.bulk.prefetch.L2, two to eight items ahead, or the first megabytes of the next kernel's
+    // weights at the end -- made a step slower by 5 to 30 % or changed nothing, measured on B200: the
+    // operations wait at their barriers and for their rows of x, not for the weights.)
     bool ok = true;
     int s = 0, wrapped = 0;
     unsigned parity = 1;
-    for (int k = 0; k < A.n_ops; ++k) {
-      const ChainOp& op = A.op[k];
-      if (op.seq) {
-        for (int grp = cta; grp < op.groups; grp += op.ctas) {
-          for (int j = 0; j < op.slices; ++j) {
-            const int k0 = j * op.slice_k;
-            const unsigned bytes = (unsigned)min(op.slice_k, op.K - k0) * 2;
-            if (wrapped && ok) {
-              ok = mbar_wait(empty + s, parity);
-              if (!ok && lane == 0) atomicExch(A.err, 11);
-            }
-            unsigned char* st = slots + (size_t)s * GC_SLOT;
-            if (lane == 0) mbar_expect_tx(full + s, bytes * GC_ROWS);
-            __syncwarp();
-            if (lane < GC_ROWS)
-              bulk_copy(st + lane * GC_PITCH, op.W + (size_t)min(grp * GC_ROWS + lane, op.N - 1) * op.K + k0, bytes, full + s);
-            if (++s == S) { s = 0; wrapped = 1; parity ^= 1; }
-          }
-        }
-        continue;
-      }
-      const int slice = cta / op.ctas, r = cta - slice * op.ctas;
-      if (slice >= op.slices) continue;
-      const int k0 = slice * op.slice_k;
+    int ck = -1, cg = 0, cj = 0;
+    while (item_next(A, cta, ck, cg, cj)) {
+      const ChainOp& op = A.op[ck];
+      const int k0 = cj * op.slice_k;
       const unsigned bytes = (unsigned)min(op.slice_k, op.K - k0) * 2;
-      for (int grp = r; grp < op.groups; grp += op.ctas) {
-        if (wrapped && ok) {
-          ok = mbar_wait(empty + s, parity);
-          if (!ok && lane == 0) atomicExch(A.err, 11);
-        }
-        unsigned char* st = slots + (size_t)s * GC_SLOT;
-        if (lane == 0) mbar_expect_tx(full + s, bytes * GC_ROWS);
-        __syncwarp();
-        if (lane < GC_ROWS)
-          bulk_copy(st + lane * GC_PITCH, op.W + (size_t)min(grp * GC_ROWS + lane, op.N - 1) * op.K + k0, bytes, full + s);
-        if (++s == S) { s = 0; wrapped = 1; parity ^= 1; }
+      if (wrapped && ok) {
+        ok = mbar_wait(empty + s, parity);
+        if (!ok && lane == 0) atomicExch(A.err, 11);
       }
+      unsigned char* st = slots + (size_t)s * GC_SLOT;
+      if (lane == 0) mbar_expect_tx(full + s, bytes * GC_ROWS);
+      __syncwarp();
+      if (lane < GC_ROWS)
+        bulk_copy(st + lane * GC_PITCH, op.W + (size_t)min(cg * GC_ROWS + lane, op.N - 1) * op.K + k0, bytes, full + s);
+      if (++s == S) { s = 0; wrapped = 1; parity ^= 1; }
     }
     return;
   }
 
   if (warp == GC_CONSUMERS + 1) {
     // ---- epilogue warp: grid barrier, x, sums of the MMA warps' partial sums, stores ----
+    pdl_wait();                 // the first operation's output may still be read (or be written) by the kernel before
     bool ok = true;
     int rb = 0;
     unsigned red_parity = 0;
@@ -344,6 +361,7 @@ __global__ void __launch_bounds__(GC_THREADS, 1) gemm_chain_kernel(const __grid_
   }
 
   // ---- MMA warps ----
+  pdl_wait();                   // x of the first operation comes from the kernel before this one
   bool ok = true;
   int s = 0, rb = 0;
   unsigned parity = 0, red_parity = 1;
@@ -677,17 +695,7 @@ Q25_EXPORT int q25_gemm_chain_bf16(const ChainOpDesc* ops, int n_ops, float* scr
   void (*kernel)(const ChainArgs) = rows <= 8 ? gemm_chain_kernel<1> : gemm_chain_kernel<2>;
   cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, total);
   if (e != cudaSuccess) return (int)e;
-  cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(device_sm_count());
-  cfg.blockDim = dim3(GC_THREADS);
-  cfg.dynamicSmemBytes = (size_t)total;
-  cfg.stream = (cudaStream_t)stream;
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeCooperative;
-  attr[0].val.cooperative = 1;
-  cfg.attrs = attr;
-  cfg.numAttrs = 1;
-  e = cudaLaunchKernelEx(&cfg, kernel, A);
-  if (e == cudaSuccess) e = cudaGetLastError();
+  launch(kernel, dim3(device_sm_count()), dim3(GC_THREADS), (size_t)total, (cudaStream_t)stream, A);
+  e = (cudaError_t)launch_status();
   return (int)e;
 }

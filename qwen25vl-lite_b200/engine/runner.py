@@ -20,6 +20,7 @@ Per step, for S entries holding N tokens in all (everything int32):
 
 from __future__ import annotations
 
+import gc
 from dataclasses import dataclass, field
 from typing import Dict, List, Optional, Sequence
 
@@ -211,8 +212,17 @@ class ModelRunner:
             self._forward_chained(ctx)
             graph = torch.cuda.CUDAGraph()
             before = kernels.launch_count()
-            with torch.cuda.graph(graph):
-                logits = self._forward_chained(ctx)
+            # No garbage collection while the stream captures: a dead cycle that holds CUDA graphs
+            # or pinned memory (a discarded engine) would be torn down in the middle of the capture,
+            # and the calls that does are not allowed then; they invalidate the capture.
+            collecting = gc.isenabled()
+            gc.disable()
+            try:
+                with torch.cuda.graph(graph):
+                    logits = self._forward_chained(ctx)
+            finally:
+                if collecting:
+                    gc.enable()
             hit = (graph, logits, layout, kernels.launch_count() - before)
             self._graphs[key] = hit
         hit[0].replay()
@@ -448,5 +458,5 @@ class ModelRunner:
         if code != 0:
             self._error_host.zero_()
             if self.device.type == "cuda":
-                kernels.error_flag(self.device).zero_()
+                kernels.reset_after_error(self.device)
             raise kernels.KernelError(f"a kernel of a step gave up waiting (code {code}); the step's results are invalid")

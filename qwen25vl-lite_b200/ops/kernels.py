@@ -536,6 +536,18 @@ def gemm_tcgen05(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor],
         error_flag(x.device).data_ptr(), _stream()), "gemm_tcgen05")
 
 
+def reset_after_error(device) -> None:
+    """After a bounded wait gave up: the error flag, and every flag or counter that kernels leave
+    zero when they finish normally, back to zero."""
+    device = torch.device(device)
+    for table in (_error_flags, _counters):
+        if device in table:
+            table[device].zero_()
+    if device in _chain_state:
+        for t in _chain_state[device]:
+            t.zero_()
+
+
 def sample_rows(logits: torch.Tensor, temperature: Optional[torch.Tensor], seed: Optional[torch.Tensor],
                 token_index: Optional[torch.Tensor], out: torch.Tensor) -> None:
     """out[r] = argmax(logits[r]) where temperature[r] <= 0 (or temperature is None), else a

@@ -29,10 +29,19 @@ TCGEN05_MIN_ROWS = 128
 
 
 def use_tcgen05(x: torch.Tensor, w: torch.Tensor, fused_epilogue: bool = False) -> bool:
-    """Which kernel takes a many-row product.  Measured on B200 at 3B sizes and 2,048 rows, the
-    one-CTA tcgen05 kernel reaches 1.10-1.27 PFLOP/s where cuBLAS (two-CTA kernels) reaches
-    1.43-1.47, so it takes the products where its fused epilogue saves a kernel and a round trip
-    through memory (gate_up with SwiGLU: 168 us against 126 + 75 us), and the library the others."""
+    """Which kernel takes a product of more than 16 rows.  Measured on B200 at 3B sizes:
+
+    * 2,048 rows (prefill): the one-CTA tcgen05 kernel reaches 1.10-1.27 PFLOP/s where cuBLAS
+      (two-CTA kernels) reaches 1.43-1.47, so it takes the products where its fused epilogue saves a
+      kernel and a round trip through memory (gate_up with SwiGLU: 168 us against 126 + 75 us),
+      and the library the others;
+    * 17 to 127 rows (decode steps of that many requests): the products are streams of the weights
+      and three of the four have 16 or 20 tiles of 128 features for 148 SMs.  A stream-K variant of
+      the tcgen05 kernel (units of (tile, K block) dealt evenly to all SMs, segment sums handed
+      between CTAs in float and added in K order) was built and measured: 12 / 9 / 26 / 18 us for
+      qkv / o / gate_up / down at 17 rows against cuBLAS's 5 / 5 / 16 / 17 us.  What it loses is not
+      the stream but its tail: sums through L2, a counter, a poll, another pass, per product.  It
+      is not kept; these products go to the library until they run chained like those of 16 rows."""
     return fused_epilogue and x.shape[0] >= TCGEN05_MIN_ROWS and kernels.gemm_tcgen05_supports(x, w)
 
 

@@ -65,7 +65,8 @@ class LinearHead(Part):
                                  f"is not [{self.vocab_size}, {self.hidden_size}]")
             self.proj = Linear(self._tied_weight)
         else:
-            raise ValueError("output head has no weight and is not tied")
+            raise ValueError("output head has no weight of its own" + (f" and no earlier part holds {self.tied_to!r}, "
+                             "which it is tied to" if self.tied else " and is not tied"))
 
     def forward(self, ctx, h):
         return self.proj(h, out_dtype=torch.float32)

@@ -64,7 +64,7 @@ def toy_spec(cfg):
         layers=layers,
         schedule=(ScheduleEntry(0), ScheduleEntry(1), ScheduleEntry(0), ScheduleEntry(1, cache_of=1)),
         final_norm=PartSpec("rmsnorm", dict(dim=HIDDEN, eps=EPS), "final_norm."),
-        head=PartSpec("linear_head", dict(vocab_size=VOCAB, hidden_size=HIDDEN, tied=True), "head."),
+        head=PartSpec("linear_head", dict(vocab_size=VOCAB, hidden_size=HIDDEN, tied=True, tied_to="embed.weight"), "head."),
         position=PartSpec("mrope", dict(head_dim=D, theta=10000.0, sections=(2, 3, 3))),
     )
 
@@ -230,7 +230,7 @@ def toy2_spec(cfg):
         embedding=PartSpec("token_embedding", dict(vocab_size=VOCAB, hidden_size=HIDDEN), "embed."),
         layers=layers, schedule=(ScheduleEntry(0), ScheduleEntry(1)),
         final_norm=PartSpec("rmsnorm", dict(dim=HIDDEN, eps=EPS), "final_norm."),
-        head=PartSpec("linear_head", dict(vocab_size=VOCAB, hidden_size=HIDDEN, tied=True), "head."),
+        head=PartSpec("linear_head", dict(vocab_size=VOCAB, hidden_size=HIDDEN, tied=True, tied_to="embed.weight"), "head."),
         position=PartSpec("toy_rope_pairs", dict(head_dim=D, theta=THETA2)),
     )
 

@@ -668,7 +668,8 @@ def test_attention_decode_fused(nq, nkv, d, section, page_size, window, splits, 
 
 
 @pytest.mark.parametrize("m,n,k", [(128, 256, 64), (2048, 2560, 2048), (300, 1000, 512), (17, 4752, 256), (1000, 512, 11008),
-                                   (129, 272, 72)])
+                                   (129, 272, 72), (40, 2048, 2048), (64, 2560, 2048), (17, 2048, 11008), (100, 22016, 2048),
+                                   (33, 144, 4160), (127, 151936, 256)])
 def test_gemm_tcgen05(m, n, k):
     """The tcgen05 / TMA product against float64 on the same bfloat16 operands: whole tiles, ragged
     edges in M, N and K, many K blocks (the ring of stages wraps), every epilogue."""
@@ -699,3 +700,6 @@ def test_gemm_tcgen05(m, n, k):
         want = (plain.silu(pairs[:, :, 0]) * pairs[:, :, 1]).reshape(m, n // 2)
         assert np.abs(f64(act) - want).max() / max(1.0, np.abs(want).max()) < 1e-2
     assert int(kernels.error_flag("cuda:0")[0]) == 0
+    again = torch.empty_like(out32)
+    kernels.gemm_tcgen05(x, w, None, again, kernels.SKINNY_F32)
+    assert torch.equal(again, out32)
