@@ -219,9 +219,10 @@ def run_ours(args):
     t = cfg["text_config"]
     full_layers, t["num_hidden_layers"] = t["num_hidden_layers"], layers
     max_batch = 64
-    llm = LLM(random_config=cfg, weights_seed=0, dtype="bfloat16", num_blocks=max_batch * CONTEXT_LEN // PAGE,
+    llm = LLM(random_config=cfg, weights_seed=0, dtype=args.dtype, num_blocks=max_batch * CONTEXT_LEN // PAGE,
               block_size=PAGE, max_num_seqs=max_batch, max_num_batched_tokens=8192, max_model_len=CONTEXT_LEN,
               cuda_graph=not args.no_cuda_graph)
+    element = 2 if args.dtype == "bfloat16" else 4
     runner, engine = llm.runner, llm.engine
     rng = np.random.default_rng(0)
     vocab = t["vocab_size"]
@@ -249,7 +250,7 @@ def run_ours(args):
             points[f"decode_b{b}"] = B.time_decode_steps(runner, b, PROMPT_LEN, args.steps, args.warmup, vocab, rng)["tokens_per_s"]
 
     ctx = head["context"]
-    step_bytes = B.weight_bytes(t, layers) + 8 * ctx * B.kv_bytes_per_token(t, layers)
+    step_bytes = B.weight_bytes(t, layers, element) + 8 * ctx * B.kv_bytes_per_token(t, layers, element)
     achieved = step_bytes / (head["ms_per_step"] / 1e3) / 1e9
     n_groups = len(runner.cache.groups)
     h2d = 4 * (8 * (2 + 3 + n_groups) + 9 + 16 + 8 + 8 * n_groups * (-(-(ctx + 1) // PAGE)))
@@ -257,6 +258,9 @@ def run_ours(args):
     line = _base_line("decode tokens/s, Qwen2.5-VL-3B dims, batch 8, 2048-token prompts", head["tokens_per_s"], args,
                       head["ms_per_step"], cfg, layers, 8, CONTEXT_LEN, PROMPT_LEN, peaks)
     line["config"]["model"] = "Qwen2.5-VL-3B text dims"
+    if args.dtype == "float32":      # the true 32-bit path: plain FMA products, no tensor cores, so no tensor-peak fraction
+        line["dtype"] = "fp32"
+        prefill["frac"] = None
     line.update({
         "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 8 * 4},
         "gpu_launches": head["launches"],
@@ -376,6 +380,8 @@ def main(argv=None):
     ap.add_argument("--headline-only", action="store_true", help="skip e2e and the batch 1 / 64 points")
     ap.add_argument("--no-cuda-graph", action="store_true", help="launch decode steps kernel by kernel (for profilers)")
     ap.add_argument("--only-batch", type=int, default=0, help="time decode steps at this batch size only (for profilers)")
+    ap.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"],
+                    help="float32 times the true 32-bit path of the 3b configuration (fewer --layers advised)")
     ap.add_argument("--config", default="3b", choices=["3b", "7b-trace", "32b"],
                     help="3b: the headline line (default); 7b-trace, 32b: the other workloads, one line each")
     args = ap.parse_args(argv)

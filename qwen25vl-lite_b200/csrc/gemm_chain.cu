@@ -68,6 +68,7 @@ struct ChainOp {
 struct ChainArgs {
   int n_ops, n_stages;
   int x_off;              // where x begins in shared memory
+  int stash_off;          // where a norm operation's weights wait in shared memory (-1: no room, they are read in place)
   float* scratch;         // slots of partial sums, [slice][group][MT * 128] floats, reused by every operation
   int* counters;          // one per group, zero before the launch and after it
   unsigned* barrier;      // arrivals at the barriers between operations; only grows
@@ -174,6 +175,7 @@ __global__ void __launch_bounds__(GC_THREADS, 1) gemm_chain_kernel(const __grid_
   extern __shared__ __align__(128) unsigned char smem[];
   const int S = A.n_stages;
   unsigned char* xs = smem + A.x_off;             // x of a product
+  const float4* stash = A.stash_off >= 0 ? reinterpret_cast<const float4*>(smem + A.stash_off) : nullptr;
   unsigned char* slots = smem;
   float* red = reinterpret_cast<float*>(slots + (size_t)S * GC_SLOT);
   unsigned long long* full = reinterpret_cast<unsigned long long*>(red + GC_RED_BUFS * GC_CONSUMERS * 32 * MT * 4);
@@ -370,6 +372,17 @@ __global__ void __launch_bounds__(GC_THREADS, 1) gemm_chain_kernel(const __grid_
   auto consumer_sync = [] { asm volatile("bar.sync 1, %0;\n" ::"n"(GC_CONSUMERS * 32) : "memory"); };
   for (int k = 0; k < A.n_ops; ++k) {
     const ChainOp& op = A.op[k];
+    // The norm weights of this operation are asked for before the wait at the barrier (nothing
+    // writes them): read after it, they cost a second trip to memory behind the one for x, and
+    // they are cold, every layer having its own.
+    const bool stashed = op.norm && stash != nullptr && cta / op.ctas < op.slices;
+    if (stashed) {
+      const int sl = cta / op.ctas;
+      const int k0s = sl * op.slice_k, n4s = min(op.slice_k, op.K - k0s) / 4;
+      for (int i = ctid; i < n4s; i += GC_CONSUMERS * 32)
+        cp_async16(smem + A.stash_off + (size_t)i * 16, op.norm_w + k0s + (size_t)i * 4, true);
+      cp_async_commit();
+    }
     if (k > 0 && ok) {
       ok = mbar_wait(go, (unsigned)(k - 1) & 1);
       if (!ok && lane == 0) atomicExch(A.err, 12);
@@ -451,10 +464,14 @@ __global__ void __launch_bounds__(GC_THREADS, 1) gemm_chain_kernel(const __grid_
     // are issued together; one by one, each would cost a trip to L2.
     if (op.norm) {
       const float* Xf = reinterpret_cast<const float*>(op.X);
+      if (stashed) {
+        cp_async_wait<0>();
+        asm volatile("bar.sync 1, %0;\n" ::"n"(GC_CONSUMERS * 32) : "memory");      // every thread's share of them is in
+      }
       for (int m = warp; m < op.M; m += GC_CONSUMERS) {
         const float4* xr = reinterpret_cast<const float4*>(Xf + (size_t)m * op.ldx);
         const int n4 = op.K / 4;
-        const float4* w4 = reinterpret_cast<const float4*>(op.norm_w + k0);
+        const float4* w4 = stashed ? stash : reinterpret_cast<const float4*>(op.norm_w + k0);
         unsigned char* dst = xs + (size_t)m * GC_PITCH;
         if (n4 <= 32 * 16) {
           // the whole row in registers: one trip to L2 for the statistics and the values
@@ -624,7 +641,8 @@ static bool chain_cut(const ChainOpDesc& d, ChainOp& op) {
 
 // Shared memory of the kernel: the ring of stages, the partial-sum buffers and the barriers, then
 // room for x of up to `rows` rows (8 or 16).
-static int chain_smem(int rows, bool two_x_buffers, int& n_stages, int& x_off) {
+// `stash`: bytes for a norm operation's weights behind x, if that costs no stage of the ring.
+static int chain_smem(int rows, bool two_x_buffers, int stash, int& n_stages, int& x_off, int& stash_off) {
   const int MT = rows <= 8 ? 1 : 2;
   int tail = rows * GC_PITCH;
   if (two_x_buffers) tail = 2 * ((8 * GC_PITCH + 127) / 128 * 128);
@@ -632,8 +650,11 @@ static int chain_smem(int rows, bool two_x_buffers, int& n_stages, int& x_off) {
   const int bars = 1024;
   n_stages = (GC_SMEM_LIMIT - tail - red - bars) / GC_SLOT;
   if (n_stages > 24) n_stages = 24;
+  stash = (stash + 127) / 128 * 128;
   x_off = n_stages * GC_SLOT + red + bars;
-  return x_off + tail;
+  const bool room = stash > 0 && x_off + tail + stash <= GC_SMEM_LIMIT;
+  stash_off = room ? x_off + tail : -1;
+  return x_off + tail + (room ? stash : 0);
 }
 
 // Floats of scratch that a chain needs (0: no operation cuts K).
@@ -681,16 +702,17 @@ Q25_EXPORT int q25_gemm_chain_bf16(const ChainOpDesc* ops, int n_ops, float* scr
   ChainArgs A;
   A.n_ops = n_ops;
   A.scratch = scratch; A.counters = counters; A.barrier = barrier; A.barrier_base = barrier_base; A.err = err;
-  int rows = 0;
+  int rows = 0, stash = 0;
   bool seq = false;
   for (int i = 0; i < n_ops; ++i) {
     if (!chain_cut(ops[i], A.op[i])) return (int)cudaErrorInvalidValue;
     if (A.op[i].seq) seq = true;
+    if (A.op[i].norm && A.op[i].slice_k * 4 > stash) stash = A.op[i].slice_k * 4;
     if (A.op[i].groups > 65536 || (A.op[i].slices > 1 && !A.op[i].seq && !scratch)) return (int)cudaErrorInvalidValue;
     if (ops[i].M > rows) rows = ops[i].M;
   }
   rows = rows <= 8 ? 8 : 16;
-  const int total = chain_smem(rows, seq, A.n_stages, A.x_off);
+  const int total = chain_smem(rows, seq, stash, A.n_stages, A.x_off, A.stash_off);
   if (A.n_stages < 2) return (int)cudaErrorInvalidValue;
   void (*kernel)(const ChainArgs) = rows <= 8 ? gemm_chain_kernel<1> : gemm_chain_kernel<2>;
   cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, total);
