@@ -53,6 +53,56 @@ struct T5Shared {
   unsigned tmem_base;
 };
 
+// The epilogue of 32 consecutive features n .. n + 31 of row m, from their float sums (m < M, n < N).
+template <int EPI>
+__device__ __forceinline__ void t5_emit32(const float (&v)[32], int m, int n, int N, const float* __restrict__ bias,
+                                          void* __restrict__ out, int ldo) {
+  if constexpr (EPI == T5_SWIGLU) {
+    // columns come in groups of 16: 8 gate features, then their 8 up features
+    bf16* dst = reinterpret_cast<bf16*>(out) + (size_t)m * ldo + (n >> 1);
+#pragma unroll
+    for (int grp = 0; grp < 2; ++grp) {
+      if (n + grp * 16 + 16 > N) break;
+      __align__(16) bf16 o8[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const float gate = v[grp * 16 + j], up = v[grp * 16 + 8 + j];
+        o8[j] = __float2bfloat16_rn(gate / (1.0f + __expf(-gate)) * up);
+      }
+      *reinterpret_cast<uint4*>(dst + grp * 8) = *reinterpret_cast<const uint4*>(o8);
+    }
+  } else if constexpr (EPI == T5_F32 || EPI == T5_RESIDUAL) {
+    float* dst = reinterpret_cast<float*>(out) + (size_t)m * ldo + n;
+#pragma unroll
+    for (int j = 0; j < 32; ++j) {
+      if (n + j >= N) break;
+      if constexpr (EPI == T5_RESIDUAL) dst[j] += v[j];
+      else dst[j] = v[j];
+    }
+  } else {
+    bf16* dst = reinterpret_cast<bf16*>(out) + (size_t)m * ldo + n;
+    if (n + 32 <= N && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        __align__(16) bf16 o8[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          float y = v[q * 8 + j];
+          if constexpr (EPI == T5_BIAS) y += bias[n + q * 8 + j];
+          o8[j] = __float2bfloat16_rn(y);
+        }
+        *reinterpret_cast<uint4*>(dst + q * 8) = *reinterpret_cast<const uint4*>(o8);
+      }
+    } else {
+      for (int j = 0; j < 32 && n + j < N; ++j) {
+        float y = v[j];
+        if constexpr (EPI == T5_BIAS) y += bias[n + j];
+        dst[j] = __float2bfloat16_rn(y);
+      }
+    }
+  }
+}
+
 template <int EPI, int BN>
 __global__ void __launch_bounds__(T5_THREADS, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
@@ -166,50 +216,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
         tc5_ld32(taddr + c, v);
         const int n = n0 + c;
         if (m >= M || n >= N) continue;
-        if constexpr (EPI == T5_SWIGLU) {
-          // columns come in groups of 16: 8 gate features, then their 8 up features
-          bf16* dst = reinterpret_cast<bf16*>(out) + (size_t)m * ldo + (n >> 1);
-#pragma unroll
-          for (int grp = 0; grp < 2; ++grp) {
-            if (n + grp * 16 + 16 > N) break;
-            __align__(16) bf16 o8[8];
-#pragma unroll
-            for (int j = 0; j < 8; ++j) {
-              const float gate = v[grp * 16 + j], up = v[grp * 16 + 8 + j];
-              o8[j] = __float2bfloat16_rn(gate / (1.0f + __expf(-gate)) * up);
-            }
-            *reinterpret_cast<uint4*>(dst + grp * 8) = *reinterpret_cast<const uint4*>(o8);
-          }
-        } else if constexpr (EPI == T5_F32 || EPI == T5_RESIDUAL) {
-          float* dst = reinterpret_cast<float*>(out) + (size_t)m * ldo + n;
-#pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            if (n + j >= N) break;
-            if constexpr (EPI == T5_RESIDUAL) dst[j] += v[j];
-            else dst[j] = v[j];
-          }
-        } else {
-          bf16* dst = reinterpret_cast<bf16*>(out) + (size_t)m * ldo + n;
-          if (n + 32 <= N && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
-#pragma unroll
-            for (int q = 0; q < 4; ++q) {
-              __align__(16) bf16 o8[8];
-#pragma unroll
-              for (int j = 0; j < 8; ++j) {
-                float y = v[q * 8 + j];
-                if constexpr (EPI == T5_BIAS) y += bias[n + q * 8 + j];
-                o8[j] = __float2bfloat16_rn(y);
-              }
-              *reinterpret_cast<uint4*>(dst + q * 8) = *reinterpret_cast<const uint4*>(o8);
-            }
-          } else {
-            for (int j = 0; j < 32 && n + j < N; ++j) {
-              float y = v[j];
-              if constexpr (EPI == T5_BIAS) y += bias[n + j];
-              dst[j] = __float2bfloat16_rn(y);
-            }
-          }
-        }
+        t5_emit32<EPI>(v, m, n, N, bias, out, ldo);
       }
       tc5_fence_before();
       __syncwarp();
@@ -223,6 +230,201 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
   if (warp == 1) {
     tc5_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "n"(2 * BN) : "memory");
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// The same product on PAIRS of CTAs (tcgen05 with cta_group::2), for 256 rows and more.
+//
+// A cluster of two CTAs (on the two SMs of a pair) takes a tile of 256 rows x 256 features.  Each
+// CTA loads its own 128 rows of x and its own 128 of the tile's 256 rows of W (a stage is 32 KB, so
+// six fit); one thread of the first CTA issues tcgen05.mma.cta_group::2 (M 256, N 256, K 16), which
+// reads both CTAs' shared memory at the same offsets and leaves each CTA's 128 rows x 256 columns of
+// sums in that CTA's tensor memory.  Per instruction an SM reads half as many bytes of W from its
+// shared memory as in the one-CTA kernel, whose tensor pipe waits for shared memory 27 % of the time.
+//
+// Who signals whom: the TMA loads of both CTAs count their bytes on the FIRST CTA's "full" barrier
+// (the barrier operand with the peer bit cleared; that CTA's producer expects the bytes of both);
+// the MMA thread's commits arrive at the "empty" barrier of the stage and at the accumulator's
+// "full" barrier in BOTH CTAs (tcgen05.commit with a CTA mask); the epilogue warps of both CTAs
+// arrive at the first CTA's accumulator-"empty" barrier (the second CTA's with a remote arrive).
+// The loads use no cluster multicast.  Every wait is bounded; the two CTAs meet at a cluster barrier
+// after the barriers are set up and before the tensor memory goes back.
+#define P2_STAGES 6
+#define P2_BN 256
+#define P2_HALF_BYTES (128 * T5_BK * 2)                 // this CTA's 128 of the tile's 256 rows of W, 64 values of K
+#define P2_STAGE_BYTES (T5_A_BYTES + P2_HALF_BYTES)
+#define P2_PEER_MASK 0xFEFFFFFFu                        // a shared-memory address of either CTA -> the same place in the first
+
+struct P2Shared {
+  unsigned long long full[P2_STAGES], empty[P2_STAGES], acc_full[2], acc_empty[2];
+  unsigned tmem_base;
+};
+
+__device__ __forceinline__ unsigned p2_cta_rank() {
+  unsigned r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;\n" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void p2_cluster_sync() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n barrier.cluster.wait.acquire.aligned;\n" ::: "memory");
+}
+__device__ __forceinline__ void p2_tma_load(void* dst, const CUtensorMap* map, int x, int y, unsigned long long* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];\n"
+      ::"r"(smem_u32(dst)), "l"(reinterpret_cast<unsigned long long>(map)), "r"(smem_u32(bar) & P2_PEER_MASK), "r"(x), "r"(y)
+      : "memory");
+}
+__device__ __forceinline__ void p2_mma(unsigned tmem_d, unsigned long long adesc, unsigned long long bdesc, unsigned idesc,
+                                      unsigned accumulate) {
+  const unsigned zero = 0;     // no output lane is switched off
+  asm volatile(
+      "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
+      " tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5, %5, %5, %5, %5}, p;\n}\n"
+      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(zero) : "memory");
+}
+// The MMAs issued so far are done: an arrival at this barrier in both CTAs of the pair.
+__device__ __forceinline__ void p2_commit(unsigned long long* bar) {
+  const unsigned short both = 3;
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;\n"
+               ::"r"(smem_u32(bar)), "h"(both) : "memory");
+}
+// An arrival at the first CTA's barrier, from either CTA.
+__device__ __forceinline__ void p2_arrive_first(unsigned long long* bar) {
+  asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];\n" ::"r"(smem_u32(bar) & P2_PEER_MASK) : "memory");
+}
+// bf16 x bf16 -> f32, M 256 over the pair, N n, both operands K-major.
+__device__ __forceinline__ unsigned p2_idesc(int n) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(n >> 3) << 17) | ((unsigned)(256 >> 4) << 24);
+}
+
+template <int EPI>
+__global__ void __launch_bounds__(T5_THREADS, 1)
+gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
+                         const float* __restrict__ bias, void* __restrict__ out, int ldo, int M, int N, int K,
+                         int* __restrict__ err) {
+  extern __shared__ __align__(1024) unsigned char t5_smem[];
+  unsigned char* stages = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(t5_smem) + 1023) & ~(uintptr_t)1023);
+  P2Shared* sh = reinterpret_cast<P2Shared*>(stages + P2_STAGES * P2_STAGE_BYTES);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int rank = (int)p2_cta_rank();                  // 0: issues the MMAs and owns the barriers both CTAs signal
+  const int pair = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
+  const int m_blocks = (M + 255) / 256, n_blocks = (N + P2_BN - 1) / P2_BN;
+  const int n_tiles = m_blocks * n_blocks;
+  const int k_blocks = (K + T5_BK - 1) / T5_BK;
+
+  pdl_trigger();
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < P2_STAGES; ++s) {
+      mbar_init(sh->full + s, 1);
+      mbar_init(sh->empty + s, 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(sh->acc_full + b, 1);
+      mbar_init(sh->acc_empty + b, 8);                  // four epilogue warps of each CTA
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+  }
+  // x was written by the kernel before this one, the output may still be read by it, and tensor
+  // memory is asked for only when that kernel has gone (see the one-CTA kernel)
+  pdl_wait();
+  p2_cluster_sync();                                    // the other CTA's barriers exist before anything signals them
+  if (warp == 1) {   // tensor memory: two accumulators of 256 columns, in both CTAs (the same warp of each asks)
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_u32(&sh->tmem_base)), "n"(512) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;\n" ::: "memory");
+  }
+  tc5_fence_before();
+  __syncthreads();
+  tc5_fence_after();
+  const unsigned tmem_base = sh->tmem_base;
+
+  if (warp == 0) {
+    // ---- producer (each CTA for its own halves) ----
+    if (lane == 0) {
+      bool ok = true;
+      int it = 0;
+      for (int tile = pair; tile < n_tiles; tile += n_pairs) {
+        const int m0 = (tile % m_blocks) * 256 + rank * 128, n0 = (tile / m_blocks) * P2_BN + rank * 128;
+        for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+          const int s = it % P2_STAGES;
+          if (it >= P2_STAGES && ok) {
+            ok = mbar_wait(sh->empty + s, ((it / P2_STAGES) - 1) & 1);
+            if (!ok) atomicExch(err, 31);
+          }
+          unsigned char* st = stages + (size_t)s * P2_STAGE_BYTES;
+          if (rank == 0) mbar_expect_tx(sh->full + s, 2 * P2_STAGE_BYTES);
+          p2_tma_load(st, &map_x, kb * T5_BK, m0, sh->full + s);
+          p2_tma_load(st + T5_A_BYTES, &map_w, kb * T5_BK, n0, sh->full + s);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ---- MMA issuer: one thread of the first CTA, for the pair ----
+    if (lane == 0 && rank == 0) {
+      bool ok = true;
+      const unsigned idesc = p2_idesc(P2_BN);
+      int it = 0, tile_it = 0;
+      for (int tile = pair; tile < n_tiles; tile += n_pairs, ++tile_it) {
+        const int b = tile_it & 1;
+        if (tile_it >= 2 && ok) {
+          ok = mbar_wait(sh->acc_empty + b, ((tile_it >> 1) - 1) & 1);
+          if (!ok) atomicExch(err, 32);
+        }
+        tc5_fence_after();
+        const unsigned acc = tmem_base + (unsigned)b * P2_BN;
+        for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+          const int s = it % P2_STAGES;
+          if (ok) {
+            ok = mbar_wait(sh->full + s, (it / P2_STAGES) & 1);
+            if (!ok) atomicExch(err, 33);
+          }
+          tc5_fence_after();
+          const unsigned a_addr = smem_u32(stages + (size_t)s * P2_STAGE_BYTES);
+          const unsigned long long adesc = tc5_desc(a_addr, 16, 1024), bdesc = tc5_desc(a_addr + T5_A_BYTES, 16, 1024);
+#pragma unroll
+          for (int k = 0; k < T5_BK / 16; ++k) p2_mma(acc, adesc + 2 * k, bdesc + 2 * k, idesc, (kb | k) != 0);
+          p2_commit(sh->empty + s);
+        }
+        p2_commit(sh->acc_full + b);
+      }
+    }
+  } else {
+    // ---- epilogue: each CTA its own 128 rows; warp w reads TMEM lanes 32 (w % 4) .. + 31 ----
+    const int quarter = warp & 3;
+    bool ok = true;
+    int tile_it = 0;
+    for (int tile = pair; tile < n_tiles; tile += n_pairs, ++tile_it) {
+      const int m0 = (tile % m_blocks) * 256 + rank * 128, n0 = (tile / m_blocks) * P2_BN;
+      const int b = tile_it & 1;
+      if (ok) {
+        ok = mbar_wait(sh->acc_full + b, (tile_it >> 1) & 1);
+        if (!ok && lane == 0) atomicExch(err, 34);
+      }
+      tc5_fence_after();
+      const int m = m0 + quarter * 32 + lane;
+      const unsigned taddr = tmem_base + ((unsigned)(quarter * 32) << 16) + (unsigned)b * P2_BN;
+#pragma unroll 1
+      for (int c = 0; c < P2_BN; c += 32) {
+        float v[32];
+        tc5_ld32(taddr + c, v);
+        const int n = n0 + c;
+        if (m >= M || n >= N) continue;
+        t5_emit32<EPI>(v, m, n, N, bias, out, ldo);
+      }
+      tc5_fence_before();
+      __syncwarp();
+      if (lane == 0) p2_arrive_first(sh->acc_empty + b);
+    }
+  }
+
+  // all threads of both CTAs get here (all waits are bounded): neither CTA leaves, or gives its
+  // tensor memory back, while the other may still signal it or compute into it
+  tc5_fence_before();
+  p2_cluster_sync();
+  if (warp == 1) {
+    tc5_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "n"(512) : "memory");
   }
 }
 
@@ -269,6 +471,35 @@ static int launch_t5(const CUtensorMap& mx, const CUtensorMap& mw, const float* 
   return launch_status();
 }
 
+template <int EPI>
+static int launch_pair(const CUtensorMap& mx, const CUtensorMap& mw, const float* bias, void* out, int ldo, int M, int N, int K,
+                       int* err, cudaStream_t s) {
+  const size_t smem = (size_t)P2_STAGES * P2_STAGE_BYTES + 1024 + sizeof(P2Shared);
+  cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_pair_kernel<EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (e != cudaSuccess) return (int)e;
+  const int sms = device_sm_count();
+  if (sms < 2) return (int)cudaErrorInvalidDevice;
+  const int tiles = ((M + 255) / 256) * ((N + P2_BN - 1) / P2_BN);
+  const int pairs = tiles < sms / 2 ? tiles : sms / 2;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(2 * pairs);
+  cfg.blockDim = dim3(T5_THREADS);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = s;
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = pdl_enabled() ? 1 : 0;
+  cfg.attrs = attr;
+  cfg.numAttrs = 2;
+  e = cudaLaunchKernelEx(&cfg, gemm_tcgen05_pair_kernel<EPI>, mx, mw, bias, out, ldo, M, N, K, err);
+  if (e == cudaSuccess) e = cudaGetLastError();
+  return (int)e;
+}
+
 // Width of the feature tile.  The 128-wide MMA does half the arithmetic for the same traffic of the
 // x operand out of shared memory and runs at about 0.7 of the 256-wide one (measured), so it is
 // only used when 256-wide tiles would leave more than half of the SMs without a tile.
@@ -289,10 +520,22 @@ Q25_EXPORT int q25_gemm_tcgen05_bf16(const void* W, const void* X, int ldx, cons
   CUtensorMap mx, mw;
   int r = make_map(&mx, X, M, K, ldx, T5_BM);
   if (r) return r;
+  cudaStream_t s = (cudaStream_t)stream;
+  if (M >= 256 && N >= 256) {      // CTA pairs, tiles of 256 x 256: each CTA loads boxes of 128 rows of x and of W
+    r = make_map(&mw, W, N, K, K, 128);
+    if (r) return r;
+    switch (epi) {
+      case T5_STORE: return launch_pair<T5_STORE>(mx, mw, bias, out, ldo, M, N, K, err, s);
+      case T5_BIAS: return launch_pair<T5_BIAS>(mx, mw, bias, out, ldo, M, N, K, err, s);
+      case T5_F32: return launch_pair<T5_F32>(mx, mw, bias, out, ldo, M, N, K, err, s);
+      case T5_SWIGLU: return launch_pair<T5_SWIGLU>(mx, mw, bias, out, ldo, M, N, K, err, s);
+      case T5_RESIDUAL: return launch_pair<T5_RESIDUAL>(mx, mw, bias, out, ldo, M, N, K, err, s);
+      default: return (int)cudaErrorInvalidValue;
+    }
+  }
   const int bn = pick_bn(M, N);
   r = make_map(&mw, W, N, K, K, bn);
   if (r) return r;
-  cudaStream_t s = (cudaStream_t)stream;
 #define T5_CASE(E) \
   case E: return bn == 256 ? launch_t5<E, 256>(mx, mw, bias, out, ldo, M, N, K, err, s) \
                            : launch_t5<E, 128>(mx, mw, bias, out, ldo, M, N, K, err, s);

@@ -31,10 +31,11 @@ TCGEN05_MIN_ROWS = 128
 def use_tcgen05(x: torch.Tensor, w: torch.Tensor, fused_epilogue: bool = False) -> bool:
     """Which kernel takes a product of more than 16 rows.  Measured on B200 at 3B sizes:
 
-    * 2,048 rows (prefill): the one-CTA tcgen05 kernel reaches 1.10-1.27 PFLOP/s where cuBLAS
-      (two-CTA kernels) reaches 1.43-1.47, so it takes the products where its fused epilogue saves a
-      kernel and a round trip through memory (gate_up with SwiGLU: 168 us against 126 + 75 us),
-      and the library the others;
+    * 2,048 rows (prefill): the engine's tcgen05 kernel (pairs of CTAs from 256 rows on) reaches
+      1.22 PFLOP/s on the wide products where cuBLAS reaches 1.46-1.48, and on the narrow ones
+      (qkv, o: 80 and 64 tiles of 256 x 256 for 74 pairs of SMs) 0.64-0.79 against 1.2.  So it
+      takes the products where its fused epilogue saves a kernel and a round trip through memory
+      (gate_up with SwiGLU: about 150 us against 125 + 75 us), and the library the others;
     * 17 to 127 rows (decode steps of that many requests): the products are streams of the weights
       and three of the four have 16 or 20 tiles of 128 features for 148 SMs.  A stream-K variant of
       the tcgen05 kernel (units of (tile, K block) dealt evenly to all SMs, segment sums handed
