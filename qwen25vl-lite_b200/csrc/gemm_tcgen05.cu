@@ -237,8 +237,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
 // The same product on PAIRS of CTAs (tcgen05 with cta_group::2), for 256 rows and more.
 //
 // A cluster of two CTAs (on the two SMs of a pair) takes a tile of 256 rows x 256 features.  Each
-// CTA loads its own 128 rows of x and its own 128 of the tile's 256 rows of W (a stage is 32 KB, so
-// six fit); one thread of the first CTA issues tcgen05.mma.cta_group::2 (M 256, N 256, K 16), which
+// CTA loads its own 128 rows of x and its own 128 of the tile's 256 rows of W, two K blocks of 64 to
+// a stage (64 KB; three stages.  Measured at 2,048 rows: 151 / 147 / 159 us for gate/up and
+// 76 / 67 / 76 us for down with one / two / three K blocks a stage: fewer, larger stages save
+// barrier round trips until too few are left to hide the loads); one thread of the first CTA issues tcgen05.mma.cta_group::2 (M 256, N 256, K 16), which
 // reads both CTAs' shared memory at the same offsets and leaves each CTA's 128 rows x 256 columns of
 // sums in that CTA's tensor memory.  Per instruction an SM reads half as many bytes of W from its
 // shared memory as in the one-CTA kernel, whose tensor pipe waits for shared memory 27 % of the time.
@@ -250,10 +252,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
 // arrive at the first CTA's accumulator-"empty" barrier (the second CTA's with a remote arrive).
 // The loads use no cluster multicast.  Every wait is bounded; the two CTAs meet at a cluster barrier
 // after the barriers are set up and before the tensor memory goes back.
-#define P2_STAGES 6
+#define P2_KPS 2                                        // K blocks of 64 in a stage
+#define P2_STAGES 3
 #define P2_BN 256
 #define P2_HALF_BYTES (128 * T5_BK * 2)                 // this CTA's 128 of the tile's 256 rows of W, 64 values of K
-#define P2_STAGE_BYTES (T5_A_BYTES + P2_HALF_BYTES)
+#define P2_STAGE_BYTES (P2_KPS * (T5_A_BYTES + P2_HALF_BYTES))
 #define P2_PEER_MASK 0xFEFFFFFFu                        // a shared-memory address of either CTA -> the same place in the first
 
 struct P2Shared {
@@ -298,10 +301,31 @@ __device__ __forceinline__ unsigned p2_idesc(int n) {
   return (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(n >> 3) << 17) | ((unsigned)(256 >> 4) << 24);
 }
 
+// The tiles a pair takes: whole waves of 256 x 256 tiles round-robin; if the tiles left over fill
+// at most half of the pairs, each is cut into two halves of 128 features, so that the last wave
+// takes half as long (a prefill's gate/up product has 688 tiles for 74 pairs: 9 waves and 22 tiles).
+struct P2Units {
+  int n_pairs, pair, waves, rest, first_rest, count;
+  bool halves;
+  __device__ __forceinline__ P2Units(int n_tiles, int n_pairs_, int pair_) : n_pairs(n_pairs_), pair(pair_) {
+    waves = n_tiles / n_pairs;
+    first_rest = waves * n_pairs;
+    rest = n_tiles - first_rest;
+    halves = rest > 0 && 2 * rest <= n_pairs;
+    count = waves + ((halves ? pair < 2 * rest : pair < rest) ? 1 : 0);
+  }
+  // unit i of this pair: its tile, the first feature inside the tile, and how many features wide it is
+  __device__ __forceinline__ void get(int i, int& tile, int& n_off, int& width) const {
+    if (i < waves) { tile = pair + i * n_pairs; n_off = 0; width = P2_BN; return; }
+    if (halves) { tile = first_rest + (pair >> 1); n_off = (pair & 1) * 128; width = 128; return; }
+    tile = first_rest + pair; n_off = 0; width = P2_BN;
+  }
+};
+
 template <int EPI>
 __global__ void __launch_bounds__(T5_THREADS, 1)
 gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
-                         const float* __restrict__ bias, void* __restrict__ out, int ldo, int M, int N, int K,
+                         const __grid_constant__ CUtensorMap map_w64, const float* __restrict__ bias, void* __restrict__ out, int ldo, int M, int N, int K,
                          int* __restrict__ err) {
   extern __shared__ __align__(1024) unsigned char t5_smem[];
   unsigned char* stages = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(t5_smem) + 1023) & ~(uintptr_t)1023);
@@ -312,7 +336,8 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
   const int pair = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
   const int m_blocks = (M + 255) / 256, n_blocks = (N + P2_BN - 1) / P2_BN;
   const int n_tiles = m_blocks * n_blocks;
-  const int k_blocks = (K + T5_BK - 1) / T5_BK;
+  const int k_blocks = (K + P2_KPS * T5_BK - 1) / (P2_KPS * T5_BK);     // stages of P2_KPS blocks of 64
+  const P2Units units(n_tiles, n_pairs, pair);
 
   pdl_trigger();
   if (threadIdx.x == 0) {
@@ -344,8 +369,12 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
     if (lane == 0) {
       bool ok = true;
       int it = 0;
-      for (int tile = pair; tile < n_tiles; tile += n_pairs) {
-        const int m0 = (tile % m_blocks) * 256 + rank * 128, n0 = (tile / m_blocks) * P2_BN + rank * 128;
+      for (int u = 0; u < units.count; ++u) {
+        int tile, n_off, width;
+        units.get(u, tile, n_off, width);
+        const int m0 = (tile % m_blocks) * 256 + rank * 128, n0 = (tile / m_blocks) * P2_BN + n_off + rank * (width / 2);
+        const CUtensorMap* mw = width == P2_BN ? &map_w : &map_w64;      // boxes of 128 or of 64 rows of W
+        const unsigned bytes = 2 * P2_KPS * (T5_A_BYTES + (unsigned)(width / 2) * T5_BK * 2);
         for (int kb = 0; kb < k_blocks; ++kb, ++it) {
           const int s = it % P2_STAGES;
           if (it >= P2_STAGES && ok) {
@@ -353,9 +382,12 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
             if (!ok) atomicExch(err, 31);
           }
           unsigned char* st = stages + (size_t)s * P2_STAGE_BYTES;
-          if (rank == 0) mbar_expect_tx(sh->full + s, 2 * P2_STAGE_BYTES);
-          p2_tma_load(st, &map_x, kb * T5_BK, m0, sh->full + s);
-          p2_tma_load(st + T5_A_BYTES, &map_w, kb * T5_BK, n0, sh->full + s);
+          if (rank == 0) mbar_expect_tx(sh->full + s, bytes);
+#pragma unroll
+          for (int j = 0; j < P2_KPS; ++j) {             // (a box past K is filled with zeros and still counts its bytes)
+            p2_tma_load(st + j * (T5_A_BYTES + P2_HALF_BYTES), &map_x, (kb * P2_KPS + j) * T5_BK, m0, sh->full + s);
+            p2_tma_load(st + j * (T5_A_BYTES + P2_HALF_BYTES) + T5_A_BYTES, mw, (kb * P2_KPS + j) * T5_BK, n0, sh->full + s);
+          }
         }
       }
     }
@@ -363,9 +395,11 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
     // ---- MMA issuer: one thread of the first CTA, for the pair ----
     if (lane == 0 && rank == 0) {
       bool ok = true;
-      const unsigned idesc = p2_idesc(P2_BN);
-      int it = 0, tile_it = 0;
-      for (int tile = pair; tile < n_tiles; tile += n_pairs, ++tile_it) {
+      int it = 0;
+      for (int tile_it = 0; tile_it < units.count; ++tile_it) {
+        int tile, n_off, width;
+        units.get(tile_it, tile, n_off, width);
+        const unsigned idesc = p2_idesc(width);
         const int b = tile_it & 1;
         if (tile_it >= 2 && ok) {
           ok = mbar_wait(sh->acc_empty + b, ((tile_it >> 1) - 1) & 1);
@@ -380,10 +414,13 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
             if (!ok) atomicExch(err, 33);
           }
           tc5_fence_after();
-          const unsigned a_addr = smem_u32(stages + (size_t)s * P2_STAGE_BYTES);
-          const unsigned long long adesc = tc5_desc(a_addr, 16, 1024), bdesc = tc5_desc(a_addr + T5_A_BYTES, 16, 1024);
 #pragma unroll
-          for (int k = 0; k < T5_BK / 16; ++k) p2_mma(acc, adesc + 2 * k, bdesc + 2 * k, idesc, (kb | k) != 0);
+          for (int j = 0; j < P2_KPS; ++j) {
+            const unsigned a_addr = smem_u32(stages + (size_t)s * P2_STAGE_BYTES + j * (T5_A_BYTES + P2_HALF_BYTES));
+            const unsigned long long adesc = tc5_desc(a_addr, 16, 1024), bdesc = tc5_desc(a_addr + T5_A_BYTES, 16, 1024);
+#pragma unroll
+            for (int k = 0; k < T5_BK / 16; ++k) p2_mma(acc, adesc + 2 * k, bdesc + 2 * k, idesc, (kb | j | k) != 0);
+          }
           p2_commit(sh->empty + s);
         }
         p2_commit(sh->acc_full + b);
@@ -393,9 +430,10 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
     // ---- epilogue: each CTA its own 128 rows; warp w reads TMEM lanes 32 (w % 4) .. + 31 ----
     const int quarter = warp & 3;
     bool ok = true;
-    int tile_it = 0;
-    for (int tile = pair; tile < n_tiles; tile += n_pairs, ++tile_it) {
-      const int m0 = (tile % m_blocks) * 256 + rank * 128, n0 = (tile / m_blocks) * P2_BN;
+    for (int tile_it = 0; tile_it < units.count; ++tile_it) {
+      int tile, n_off, width;
+      units.get(tile_it, tile, n_off, width);
+      const int m0 = (tile % m_blocks) * 256 + rank * 128, n0 = (tile / m_blocks) * P2_BN + n_off;
       const int b = tile_it & 1;
       if (ok) {
         ok = mbar_wait(sh->acc_full + b, (tile_it >> 1) & 1);
@@ -405,7 +443,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
       const int m = m0 + quarter * 32 + lane;
       const unsigned taddr = tmem_base + ((unsigned)(quarter * 32) << 16) + (unsigned)b * P2_BN;
 #pragma unroll 1
-      for (int c = 0; c < P2_BN; c += 32) {
+      for (int c = 0; c < width; c += 32) {
         float v[32];
         tc5_ld32(taddr + c, v);
         const int n = n0 + c;
@@ -472,8 +510,8 @@ static int launch_t5(const CUtensorMap& mx, const CUtensorMap& mw, const float* 
 }
 
 template <int EPI>
-static int launch_pair(const CUtensorMap& mx, const CUtensorMap& mw, const float* bias, void* out, int ldo, int M, int N, int K,
-                       int* err, cudaStream_t s) {
+static int launch_pair(const CUtensorMap& mx, const CUtensorMap& mw, const CUtensorMap& mw64, const float* bias, void* out,
+                       int ldo, int M, int N, int K, int* err, cudaStream_t s) {
   const size_t smem = (size_t)P2_STAGES * P2_STAGE_BYTES + 1024 + sizeof(P2Shared);
   cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_pair_kernel<EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return (int)e;
@@ -495,7 +533,7 @@ static int launch_pair(const CUtensorMap& mx, const CUtensorMap& mw, const float
   attr[1].val.programmaticStreamSerializationAllowed = pdl_enabled() ? 1 : 0;
   cfg.attrs = attr;
   cfg.numAttrs = 2;
-  e = cudaLaunchKernelEx(&cfg, gemm_tcgen05_pair_kernel<EPI>, mx, mw, bias, out, ldo, M, N, K, err);
+  e = cudaLaunchKernelEx(&cfg, gemm_tcgen05_pair_kernel<EPI>, mx, mw, mw64, bias, out, ldo, M, N, K, err);
   if (e == cudaSuccess) e = cudaGetLastError();
   return (int)e;
 }
@@ -522,14 +560,16 @@ Q25_EXPORT int q25_gemm_tcgen05_bf16(const void* W, const void* X, int ldx, cons
   if (r) return r;
   cudaStream_t s = (cudaStream_t)stream;
   if (M >= 256 && N >= 256) {      // CTA pairs, tiles of 256 x 256: each CTA loads boxes of 128 rows of x and of W
+    CUtensorMap mw64;
     r = make_map(&mw, W, N, K, K, 128);
+    if (!r) r = make_map(&mw64, W, N, K, K, 64);
     if (r) return r;
     switch (epi) {
-      case T5_STORE: return launch_pair<T5_STORE>(mx, mw, bias, out, ldo, M, N, K, err, s);
-      case T5_BIAS: return launch_pair<T5_BIAS>(mx, mw, bias, out, ldo, M, N, K, err, s);
-      case T5_F32: return launch_pair<T5_F32>(mx, mw, bias, out, ldo, M, N, K, err, s);
-      case T5_SWIGLU: return launch_pair<T5_SWIGLU>(mx, mw, bias, out, ldo, M, N, K, err, s);
-      case T5_RESIDUAL: return launch_pair<T5_RESIDUAL>(mx, mw, bias, out, ldo, M, N, K, err, s);
+      case T5_STORE: return launch_pair<T5_STORE>(mx, mw, mw64, bias, out, ldo, M, N, K, err, s);
+      case T5_BIAS: return launch_pair<T5_BIAS>(mx, mw, mw64, bias, out, ldo, M, N, K, err, s);
+      case T5_F32: return launch_pair<T5_F32>(mx, mw, mw64, bias, out, ldo, M, N, K, err, s);
+      case T5_SWIGLU: return launch_pair<T5_SWIGLU>(mx, mw, mw64, bias, out, ldo, M, N, K, err, s);
+      case T5_RESIDUAL: return launch_pair<T5_RESIDUAL>(mx, mw, mw64, bias, out, ldo, M, N, K, err, s);
       default: return (int)cudaErrorInvalidValue;
     }
   }
