@@ -128,6 +128,7 @@ class StepContext:
 
 GRAPH_WIDTH_STEP = 16      # block-table widths of captured steps are rounded up to this many pages
 MAX_GRAPHS = 32
+CAPTURE_ON_USE = 3         # a (batch size, table width) is captured when it comes for the third time
 
 
 class ModelRunner:
@@ -167,6 +168,7 @@ class ModelRunner:
         self.cuda_graphs = bool(cuda_graphs and self.device.type == "cuda" and blocks
                                 and all(getattr(p, "graph_safe", False) for p in parts))
         self._graphs: Dict[tuple, tuple] = {}
+        self._graph_seen: Dict[tuple, int] = {}
         self.graph_replays = 0
         # kernels with bounded waits report a wait that gave up here; read back after every step
         # and looked at before the next one
@@ -197,19 +199,22 @@ class ModelRunner:
     def _replay(self, key, make_ctx, layout) -> torch.Tensor:
         """Runs a one-token-per-request step from its captured graph.  The step's int arrays sit
         at the same device addresses for the same key (same counts, same packing order), so a
-        replay only needs the new values, which ``step`` has already copied.  The first step
-        of a key runs once uncaptured (library warm-up; writing the same keys and values
-        twice changes nothing), then is captured and replayed.  ``make_ctx`` builds the step's
-        context; a replay does not need it (a dozen tensor views that would stand between the
-        sampled ids and the launch)."""
+        replay only needs the new values, which ``step`` has already copied.  A key's first
+        steps run uncaptured (kernel by kernel, the products chained); when it comes for the third
+        time it is captured and replayed from then on: capturing costs tens of steps' worth of
+        time, and while requests of a batch end one after the other most keys come only once or
+        twice.  ``make_ctx`` builds the step's context; a replay does not need it (a dozen tensor
+        views that would stand between the sampled ids and the launch)."""
         hit = self._graphs.get(key)
         if hit is not None and hit[2] != layout:
             hit = None                                  # the staging buffer was re-allocated since
         if hit is None:
+            seen = self._graph_seen[key] = self._graph_seen.get(key, 0) + 1
+            if seen < CAPTURE_ON_USE:
+                return self._forward_chained(make_ctx())
             if len(self._graphs) >= MAX_GRAPHS:
                 self._graphs.pop(next(iter(self._graphs)))
             ctx = make_ctx()
-            self._forward_chained(ctx)
             graph = torch.cuda.CUDAGraph()
             before = kernels.launch_count()
             # No garbage collection while the stream captures: a dead cycle that holds CUDA graphs

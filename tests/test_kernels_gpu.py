@@ -307,6 +307,14 @@ def test_attention_prefill_tcgen05(nq, nkv, page_size, window):
     rng = np.random.default_rng(21)
     lens, q_lens = [300, 37, 130, 64, 517, 333, 9], [300, 37, 2, 17, 200, 70, 9]
     c = paged_case(rng, lens, q_lens, nq, nkv, d, page_size, torch.bfloat16)
+    if window:
+        # pages wholly behind the window of a run's first query were given back: their places in the
+        # block table read as a live page of another request
+        table = c["table"].cpu().numpy()
+        for i, (L, ql) in enumerate(zip(lens, q_lens)):
+            passed = max(0, L - ql + 1 - window) // page_size
+            table[i, :passed] = table[(i + 1) % len(lens), 0]
+        c["table"] = dev(table)
     G = nq // nkv
     tiles = [(i, t) for i, n in enumerate(q_lens) for t in range(-(-n * G // 128))]
     out = torch.zeros((c["qkv"].shape[0], nq * d), dtype=torch.bfloat16, device="cuda")
@@ -638,6 +646,13 @@ def test_attention_decode_fused(nq, nkv, d, section, page_size, window, splits, 
     q_rot = plain.apply_mrope(q_raw, cos, sin)
     k_rot = plain.apply_mrope(f64(k_raw), cos, sin)
     table = c["table"].cpu().numpy()
+    if window:
+        # pages that a window has passed are given back while the request goes on, and their places
+        # in its block table read as some page or other: here as a live page of another request
+        for i, L in enumerate(lens):
+            passed = max(0, L - window) // page_size
+            table[i, :passed] = table[(i + 1) % len(lens), 0]
+        c["table"] = dev(table)
     slots, dense = [], []
     for i, L in enumerate(lens):
         page = int(table[i, (L - 1) // page_size])
