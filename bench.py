@@ -287,7 +287,8 @@ def run_32b(args):
     t = cfg["text_config"]
     layers = args.layers or t["num_hidden_layers"]
     full_layers, t["num_hidden_layers"] = t["num_hidden_layers"], layers
-    prompt_len, context = 8192, 8192 + 256
+    prompt_len = 8192
+    context = prompt_len + args.steps + args.warmup + 64              # every timed and warm-up step adds a token
     llm = LLM(random_config=cfg, weights_seed=0, dtype="bfloat16", num_blocks=32 * (-(-context // PAGE)), block_size=PAGE,
               max_num_seqs=32, max_num_batched_tokens=8192, max_model_len=context, cuda_graph=not args.no_cuda_graph)
     rng = np.random.default_rng(0)

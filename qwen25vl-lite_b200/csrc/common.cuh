@@ -88,6 +88,20 @@ __device__ __forceinline__ void bulk_copy(void* dst, const void* src, unsigned b
                ::"r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar)) : "memory");
 }
 
+// The same for data that is read once and never again (a stream of weights): the cache policy asks
+// L2 to give these lines up first, so that what a step reads again and again (activations, partial
+// sums, the rows of the cache just written) is not pushed out by gigabytes that pass through.
+__device__ __forceinline__ unsigned long long l2_evict_first() {
+  unsigned long long policy;
+  asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;\n" : "=l"(policy));
+  return policy;
+}
+__device__ __forceinline__ void bulk_copy_once(void* dst, const void* src, unsigned bytes, unsigned long long* bar,
+                                               unsigned long long policy) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1], %2, [%3], %4;\n"
+               ::"r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar)), "l"(policy) : "memory");
+}
+
 // ---- programmatic dependent launch -----------------------------------------------------------------
 // Every kernel of the engine is launched with the attribute that lets it be scheduled while the
 // kernel before it in the stream is still running; it calls pdl_trigger() at its top (the next one

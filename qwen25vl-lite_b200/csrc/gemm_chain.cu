@@ -34,7 +34,15 @@
 //     other of two buffers) while this one is multiplied.  With many groups per CTA every CTA works
 //     in one slice; the slices' partial sums go to scratch slots, and an owner CTA, when all slices
 //     have counted themselves in, adds them in slice order and runs the epilogue.  Either way the
-//     result does not depend on timing.
+//     result does not depend on timing.  Up to 8 rows of a width that is cut but not long (3584,
+//     5120) stay in shared memory whole, and a CTA walks the slices of its groups over them: no
+//     scratch memory and nothing to finish afterwards (the owners' round of a wide gate/up product,
+//     sixteen groups a CTA, cost 13 to 23 us of a layer's 130).
+//   * A stage of the ring is as long as the longest slice of the chain, and the host picks the cut
+//     (chain_plan below) that leaves the most bytes in flight: what a CTA can have on its way from
+//     memory, about two stages of 64 KB at a width of 2048, is what bounds its share of the
+//     bandwidth when few CTAs stream (a short operation, the tail of an uneven one).  At a width of
+//     3584 three stages of 60 KB fit if no operation keeps two buffers of x.
 //
 // Every wait (mbarrier or grid barrier) is bounded: when it gives up, the kernel records a code in
 // *err, stops waiting anywhere and runs to its end (its output is then invalid).
@@ -48,8 +56,6 @@ enum { EPI_STORE = 0, EPI_BIAS = 1, EPI_F32 = 2, EPI_SWIGLU = 3, EPI_RESIDUAL = 
 #define GC_THREADS ((GC_CONSUMERS + 2) * 32)
 #define GC_MAX_OPS 8
 #define GC_SLICE_K 2048                          // most K elements of a slice
-#define GC_PITCH (GC_SLICE_K * 2 + 64)           // bytes between rows in shared memory; mod 128 = 64: no bank conflicts
-#define GC_SLOT (GC_ROWS * GC_PITCH)             // one stage: the 16 rows of a group, one slice long
 #define GC_SMEM_LIMIT (227 * 1024)
 #define GC_GRID_WAIT_LIMIT (1 << 21)             // polls of global memory, about a second
 
@@ -62,13 +68,18 @@ struct ChainOp {
   int ldx, ldo, M, N, K, epi, norm;
   float eps;
   int slices, slice_k, ctas, groups;   // K cut into `slices` of `slice_k` elements; `ctas` CTAs work in each slice
-  int seq;                // 1: the K slices are taken one after the other by the same CTA (see below)
+  int seq;                // the K slices of a group are taken one after the other by the same CTA (see below):
+                          // 1 with the slices of x through two buffers, 2 with x whole in shared memory
+  int xp;                 // bytes between the rows of x in shared memory
 };
 
 struct ChainArgs {
   int n_ops, n_stages;
+  int pitch;              // bytes between rows in shared memory: the longest slice, padded so that pitch mod 128 = 64 (no bank conflicts)
+  int slot;               // one stage: the 16 rows of a group, one slice long
   int x_off;              // where x begins in shared memory
   int stash_off;          // where a norm operation's weights wait in shared memory (-1: no room, they are read in place)
+  int stash_bytes;
   float* scratch;         // slots of partial sums, [slice][group][MT * 128] floats, reused by every operation
   int* counters;          // one per group, zero before the launch and after it
   unsigned* barrier;      // arrivals at the barriers between operations; only grows
@@ -170,18 +181,113 @@ __device__ __forceinline__ void gc_store_group(const float (&acc)[MT][4], int gr
   }
 }
 
+// One copy of the store code for the owners' round, which runs once per operation: inlined there
+// for every group of a batch, it is a third of the kernel's code, fetched cold every time.
+template <int MT>
+__device__ __noinline__ void gc_store_group_once(float4 a, float4 b, int grp, const ChainOp& op, bool has_old) {
+  float acc[MT][4];
+  acc[0][0] = a.x; acc[0][1] = a.y; acc[0][2] = a.z; acc[0][3] = a.w;
+  if (MT > 1) { acc[MT - 1][0] = b.x; acc[MT - 1][1] = b.y; acc[MT - 1][2] = b.z; acc[MT - 1][3] = b.w; }
+  gc_store_group<MT>(acc, grp, op, has_old);
+}
+
+// The owners' round of an operation whose slices were other CTAs'.  The i-th group of list r (the
+// groups r, r + ctas, ...) is finished by the CTA of slice (i + r) mod slices, and there by MMA warp
+// (i / slices) mod 8: the warp waits (bounded) until every slice has counted the group in, adds
+// the slices' shares in slice order and runs the epilogue.  G groups at a time and J slices of each
+// per trip to memory, and every load of a trip is asked for before any is used and depends on no
+// condition (behind a branch each, they wait for one another): a place that is not wanted (past the
+// last group of the batch, past the last slice, outside the output) reads a neighbour that is, and
+// a select drops what it brought.  One warp doing this for all sixteen groups of a CTA, group by
+// group, took 23 us after a wide gate/up product; eight warps with their loads batched take 4.
+template <int MT, int G, int J>
+__device__ __forceinline__ bool gc_finish_groups(const ChainArgs& A, const ChainOp& op, int r, int slice, int warp, bool ok) {
+  const int lane = threadIdx.x & 31;
+  const bool add_old = op.epi == EPI_RESIDUAL;
+  const size_t slice_stride = (size_t)op.groups * (MT * 32);                         // in float4
+  const int n_list = (op.groups - r + op.ctas - 1) / op.ctas;                        // groups in list r
+  const int first = ((slice - r) % op.slices + op.slices) % op.slices + warp * op.slices, step = GC_CONSUMERS * op.slices;
+  for (int i0 = first; i0 < n_list; i0 += G * step) {
+    int grp[G], n = 0;
+#pragma unroll
+    for (int q = 0; q < G; ++q) {
+      const bool in = i0 + q * step < n_list;
+      grp[q] = in ? r + (i0 + q * step) * op.ctas : grp[0];
+      n += in ? 1 : 0;
+    }
+    if (lane < n && ok) {                        // lane q waits for group q of the batch
+      int mine = grp[0];
+#pragma unroll
+      for (int q = 1; q < G; ++q) mine = lane == q ? grp[q] : mine;
+      int i = 0;
+      while ((int)gc_ld_acquire(reinterpret_cast<const unsigned*>(A.counters + mine)) != op.slices && ++i < GC_GRID_WAIT_LIMIT) {}
+      if (i >= GC_GRID_WAIT_LIMIT) { ok = false; atomicExch(A.err, 18); }
+      A.counters[mine] = 0;                      // left as it was found, for the next operation and the next launch
+    }
+    ok = __all_sync(0xffffffffu, ok);
+    float acc[G][MT][4];
+    if (add_old) {                               // asked for together with the slices' shares: one trip, not two
+#pragma unroll
+      for (int q = 0; q < G; ++q)
+#pragma unroll
+        for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const int m = mt * 8 + 2 * (lane & 3) + (e & 1), f = grp[q] * GC_ROWS + (lane >> 2) + 8 * (e >> 1);
+            const float old = __ldcg(reinterpret_cast<const float*>(op.out) + (size_t)min(m, op.M - 1) * op.ldo + min(f, op.N - 1));
+            acc[q][mt][e] = (m < op.M && f < op.N) ? old : 0.f;
+          }
+    } else {
+#pragma unroll
+      for (int q = 0; q < G; ++q)
+#pragma unroll
+        for (int mt = 0; mt < MT; ++mt) acc[q][mt][0] = acc[q][mt][1] = acc[q][mt][2] = acc[q][mt][3] = 0.f;
+    }
+    for (int j0 = 0; j0 < op.slices; j0 += J) {
+      float4 v[G][J][MT];
+#pragma unroll
+      for (int q = 0; q < G; ++q)
+#pragma unroll
+        for (int jj = 0; jj < J; ++jj)
+#pragma unroll
+          for (int mt = 0; mt < MT; ++mt)
+            v[q][jj][mt] = __ldcg(reinterpret_cast<const float4*>(A.scratch + (size_t)grp[q] * (MT * 128)) + lane +
+                                  (size_t)min(j0 + jj, op.slices - 1) * slice_stride + mt * 32);
+#pragma unroll
+      for (int q = 0; q < G; ++q)
+#pragma unroll
+        for (int jj = 0; jj < J; ++jj) {
+          const bool in = j0 + jj < op.slices;
+#pragma unroll
+          for (int mt = 0; mt < MT; ++mt) {
+            acc[q][mt][0] += in ? v[q][jj][mt].x : 0.f; acc[q][mt][1] += in ? v[q][jj][mt].y : 0.f;
+            acc[q][mt][2] += in ? v[q][jj][mt].z : 0.f; acc[q][mt][3] += in ? v[q][jj][mt].w : 0.f;
+          }
+        }
+    }
+#pragma unroll
+    for (int q = 0; q < G; ++q)
+      if (q < n)
+        gc_store_group_once<MT>(make_float4(acc[q][0][0], acc[q][0][1], acc[q][0][2], acc[q][0][3]),
+                                make_float4(acc[q][MT - 1][0], acc[q][MT - 1][1], acc[q][MT - 1][2], acc[q][MT - 1][3]),
+                                grp[q], op, add_old);
+  }
+  return ok;
+}
+
 template <int MT>
 __global__ void __launch_bounds__(GC_THREADS, 1) gemm_chain_kernel(const __grid_constant__ ChainArgs A) {
   extern __shared__ __align__(128) unsigned char smem[];
-  const int S = A.n_stages;
+  const int S = A.n_stages, P = A.pitch, SLOT = A.slot;
   unsigned char* xs = smem + A.x_off;             // x of a product
   const float4* stash = A.stash_off >= 0 ? reinterpret_cast<const float4*>(smem + A.stash_off) : nullptr;
   unsigned char* slots = smem;
-  float* red = reinterpret_cast<float*>(slots + (size_t)S * GC_SLOT);
+  float* red = reinterpret_cast<float*>(slots + (size_t)S * SLOT);
   unsigned long long* full = reinterpret_cast<unsigned long long*>(red + GC_RED_BUFS * GC_CONSUMERS * 32 * MT * 4);
   unsigned long long* empty = full + S;
   unsigned long long* go = empty + S;             // the operation before this one is complete on every CTA
-  unsigned long long* red_full = go + 1;
+  unsigned long long* fixed = go + 1;             // the MMA warps have finished the groups this CTA owns (an operation cut across CTAs)
+  unsigned long long* red_full = fixed + 1;
   unsigned long long* red_empty = red_full + GC_RED_BUFS;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
@@ -193,6 +299,7 @@ __global__ void __launch_bounds__(GC_THREADS, 1) gemm_chain_kernel(const __grid_
       mbar_init(empty + s, GC_CONSUMERS);
     }
     mbar_init(go, 1);
+    mbar_init(fixed, GC_CONSUMERS);
     for (int b = 0; b < GC_RED_BUFS; ++b) {
       mbar_init(red_full + b, GC_CONSUMERS);
       mbar_init(red_empty + b, 1);
@@ -212,6 +319,7 @@ __global__ void __launch_bounds__(GC_THREADS, 1) gemm_chain_kernel(const __grid_
     int s = 0, wrapped = 0;
     unsigned parity = 1;
     int ck = -1, cg = 0, cj = 0;
+    const unsigned long long once = l2_evict_first();
     while (item_next(A, cta, ck, cg, cj)) {
       const ChainOp& op = A.op[ck];
       const int k0 = cj * op.slice_k;
@@ -220,11 +328,11 @@ __global__ void __launch_bounds__(GC_THREADS, 1) gemm_chain_kernel(const __grid_
         ok = mbar_wait(empty + s, parity);
         if (!ok && lane == 0) atomicExch(A.err, 11);
       }
-      unsigned char* st = slots + (size_t)s * GC_SLOT;
+      unsigned char* st = slots + (size_t)s * SLOT;
       if (lane == 0) mbar_expect_tx(full + s, bytes * GC_ROWS);
       __syncwarp();
       if (lane < GC_ROWS)
-        bulk_copy(st + lane * GC_PITCH, op.W + (size_t)min(cg * GC_ROWS + lane, op.N - 1) * op.K + k0, bytes, full + s);
+        bulk_copy_once(st + lane * P, op.W + (size_t)min(cg * GC_ROWS + lane, op.N - 1) * op.K + k0, bytes, full + s, once);
       if (++s == S) { s = 0; wrapped = 1; parity ^= 1; }
     }
     return;
@@ -236,9 +344,18 @@ __global__ void __launch_bounds__(GC_THREADS, 1) gemm_chain_kernel(const __grid_
     bool ok = true;
     int rb = 0;
     unsigned red_parity = 0;
+    unsigned fixed_parity = 0;
     for (int k = 0; k < A.n_ops; ++k) {
       const ChainOp& op = A.op[k];
       if (k > 0) {
+        if (A.op[k - 1].slices > 1 && !A.op[k - 1].seq) {
+          // what this CTA's MMA warps stored for the groups it owns belongs to the operation before too
+          if (ok) {
+            ok = mbar_wait(fixed, fixed_parity);
+            if (!ok && lane == 0) atomicExch(A.err, 19);
+          }
+          fixed_parity ^= 1;
+        }
         // everything the operation before this one wrote, on every CTA, before anybody reads it: the
         // lanes' stores meet at __syncwarp, and the release of the first lane's add carries them all
         // (a fence by each of the 32 lanes first cost about a third of a microsecond per barrier)
@@ -305,58 +422,11 @@ __global__ void __launch_bounds__(GC_THREADS, 1) gemm_chain_kernel(const __grid_
         gc_store_group<MT>(acc, grp, op, add_old);
       }
       if (sliced) {
-        // Every slice's CTA counts its groups in; the i-th group of CTA r's list is finished by the
-        // CTA of slice (i + r) mod slices, which waits (bounded) until all slices are in, adds their
-        // shares in slice order and runs the epilogue.  All slices end at about the same time, so
-        // the wait is short, and every CTA finishes its share of the groups.
+        // This slice's shares of the CTA's groups are written: every group is counted in, and the
+        // MMA warps of the CTA that owns it (gc_finish_groups) will see all slices there.
         __threadfence();
         __syncwarp();
-        const int n_mine = (op.groups - r + op.ctas - 1) / op.ctas;
-        for (int base = 0; base < n_mine; base += 32) {
-          const int i_mine = base + lane;
-          const bool valid = i_mine < n_mine;
-          const int my_grp = r + i_mine * op.ctas;
-          if (valid) atomicAdd(A.counters + my_grp, 1);
-          const bool owner = valid && (i_mine + r) % op.slices == slice;
-          if (owner && ok) {
-            int i = 0;
-            while ((int)gc_ld_acquire(reinterpret_cast<const unsigned*>(A.counters + my_grp)) != op.slices &&
-                   ++i < GC_GRID_WAIT_LIMIT) {}
-            if (i >= GC_GRID_WAIT_LIMIT) { ok = false; atomicExch(A.err, 18); }
-          }
-          if (owner) A.counters[my_grp] = 0;
-          ok = __all_sync(0xffffffffu, ok);
-          unsigned todo = __ballot_sync(0xffffffffu, owner);
-          while (todo) {
-            const int i = __ffs(todo) - 1;
-            todo &= todo - 1;
-            const int grp = r + (base + i) * op.ctas;
-            float acc[MT][4];
-#pragma unroll
-            for (int mt = 0; mt < MT; ++mt) acc[mt][0] = acc[mt][1] = acc[mt][2] = acc[mt][3] = 0.f;
-            const bool add_old = op.epi == EPI_RESIDUAL;
-            if (add_old) {                      // asked for together with the slices' shares: one trip, not two
-#pragma unroll
-              for (int mt = 0; mt < MT; ++mt)
-#pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                  const int m = mt * 8 + 2 * (lane & 3) + (e & 1), n = grp * GC_ROWS + (lane >> 2) + 8 * (e >> 1);
-                  if (m < op.M && n < op.N) acc[mt][e] = __ldcg(reinterpret_cast<const float*>(op.out) + (size_t)m * op.ldo + n);
-                }
-            }
-            const float4* slot = reinterpret_cast<const float4*>(A.scratch + (size_t)grp * (MT * 128)) + lane;
-            const size_t slice_stride = (size_t)op.groups * (MT * 32);                     // in float4
-#pragma unroll 8
-            for (int j = 0; j < op.slices; ++j) {                                          // in slice order, whoever adds
-#pragma unroll
-              for (int mt = 0; mt < MT; ++mt) {
-                const float4 v = __ldcg(slot + (size_t)j * slice_stride + mt * 32);
-                acc[mt][0] += v.x; acc[mt][1] += v.y; acc[mt][2] += v.z; acc[mt][3] += v.w;
-              }
-            }
-            gc_store_group<MT>(acc, grp, op, add_old);
-          }
-        }
+        for (int grp = r + lane * op.ctas; grp < op.groups; grp += 32 * op.ctas) atomicAdd(A.counters + grp, 1);
       }
     }
     return;
@@ -375,23 +445,29 @@ __global__ void __launch_bounds__(GC_THREADS, 1) gemm_chain_kernel(const __grid_
     // The norm weights of this operation are asked for before the wait at the barrier (nothing
     // writes them): read after it, they cost a second trip to memory behind the one for x, and
     // they are cold, every layer having its own.
-    const bool stashed = op.norm && stash != nullptr && cta / op.ctas < op.slices;
+    const int slice = op.seq ? 0 : cta / op.ctas, r = cta - slice * op.ctas;
+    const bool mine = op.seq ? cta < op.ctas : slice < op.slices;                // this CTA has a share of the operation
+    const int k0 = op.seq ? 0 : slice * op.slice_k;                              // the columns of x it needs
+    const int klen = op.seq ? op.K : min(op.slice_k, op.K - k0);
+    const bool stashed = op.norm && stash != nullptr && mine && klen * 4 <= A.stash_bytes;
     if (stashed) {
-      const int sl = cta / op.ctas;
-      const int k0s = sl * op.slice_k, n4s = min(op.slice_k, op.K - k0s) / 4;
-      for (int i = ctid; i < n4s; i += GC_CONSUMERS * 32)
-        cp_async16(smem + A.stash_off + (size_t)i * 16, op.norm_w + k0s + (size_t)i * 4, true);
+      for (int i = ctid; i < klen / 4; i += GC_CONSUMERS * 32)
+        cp_async16(smem + A.stash_off + (size_t)i * 16, op.norm_w + k0 + (size_t)i * 4, true);
       cp_async_commit();
+    } else if (op.norm && mine) {
+      // no room for them there: at least they are brought near (L1) meanwhile
+      for (int i = ctid; i < (klen * 4 + 127) / 128; i += GC_CONSUMERS * 32)
+        asm volatile("prefetch.global.L1 [%0];\n" ::"l"(reinterpret_cast<const char*>(op.norm_w + k0) + (size_t)i * 128));
     }
     if (k > 0 && ok) {
       ok = mbar_wait(go, (unsigned)(k - 1) & 1);
       if (!ok && lane == 0) atomicExch(A.err, 12);
     }
-    if (op.seq) {
+    if (op.seq == 1) {
       // ---- the K slices of a group one after the other; x slices through two buffers ----
       if (cta >= op.ctas) continue;
       const bf16* X = reinterpret_cast<const bf16*>(op.X);
-      const int xbuf_bytes = (op.M * GC_PITCH + 127) / 128 * 128;
+      const int xbuf_bytes = (op.M * P + 127) / 128 * 128;
       const int my_groups = (op.groups - cta + op.ctas - 1) / op.ctas;
       const int n_items = my_groups * op.slices;
       auto fetch_x = [&](int item) {                  // the x slice of item (group, slice) into buffer item & 1
@@ -400,7 +476,7 @@ __global__ void __launch_bounds__(GC_THREADS, 1) gemm_chain_kernel(const __grid_
         unsigned char* dst = xs + (size_t)(item & 1) * xbuf_bytes;
         for (int idx = ctid; idx < op.M * chunks; idx += GC_CONSUMERS * 32) {
           const int row = idx / chunks, c = idx - row * chunks;
-          cp_async16(dst + (size_t)row * GC_PITCH + c * 16, X + (size_t)row * op.ldx + k0 + c * 8, true);
+          cp_async16(dst + (size_t)row * P + c * 16, X + (size_t)row * op.ldx + k0 + c * 8, true);
         }
         cp_async_commit();
       };
@@ -423,14 +499,14 @@ __global__ void __launch_bounds__(GC_THREADS, 1) gemm_chain_kernel(const __grid_
           ok = mbar_wait(full + s, parity);
           if (!ok && lane == 0) atomicExch(A.err, 14);
         }
-        const unsigned char* st = slots + (size_t)s * GC_SLOT + g * GC_PITCH + t * 16;
+        const unsigned char* st = slots + (size_t)s * SLOT + g * P + t * 16;
 #pragma unroll 2
         for (int kb = warp; kb < kblocks; kb += GC_CONSUMERS) {
           const uint4 a0 = gc_lds128(st + kb * 64);
-          const uint4 a1 = gc_lds128(st + 8 * GC_PITCH + kb * 64);
+          const uint4 a1 = gc_lds128(st + 8 * P + kb * 64);
 #pragma unroll
           for (int mt = 0; mt < MT; ++mt) {
-            const uint4 b = gc_lds128(xb + (size_t)min(mt * 8 + g, op.M - 1) * GC_PITCH + kb * 64);
+            const uint4 b = gc_lds128(xb + (size_t)min(mt * 8 + g, op.M - 1) * P + kb * 64);
             gc_mma(acc[0][mt], a0.x, a1.x, a0.y, a1.y, b.x, b.y);
             gc_mma(acc[1][mt], a0.z, a1.z, a0.w, a1.w, b.z, b.w);
           }
@@ -456,82 +532,86 @@ __global__ void __launch_bounds__(GC_THREADS, 1) gemm_chain_kernel(const __grid_
       consumer_sync();                                // x of the next operation goes where these buffers are
       continue;
     }
-    const int slice = cta / op.ctas, r = cta - slice * op.ctas;
-    if (slice >= op.slices) continue;
-    const int k0 = slice * op.slice_k;
-    const int klen = min(op.slice_k, op.K - k0);
+    const bool sliced = op.slices > 1 && !op.seq;    // the slices are other CTAs' and meet in scratch memory
+    if (!mine) {
+      if (sliced && lane == 0) mbar_arrive(fixed);
+      continue;
+    }
+    const int XP = op.xp;
     // x is read past L1 (__ldcg): other SMs wrote it since this kernel began.  The loads of a batch
-    // are issued together; one by one, each would cost a trip to L2.
+    // are issued together (one by one, each would cost a trip to L2), and none of them depends on a
+    // condition: a lane past the end of its row reads the row's last place and drops it.
     if (op.norm) {
       const float* Xf = reinterpret_cast<const float*>(op.X);
       if (stashed) {
         cp_async_wait<0>();
         asm volatile("bar.sync 1, %0;\n" ::"n"(GC_CONSUMERS * 32) : "memory");      // every thread's share of them is in
       }
+      const int n4 = op.K / 4, a4 = k0 / 4, s4 = klen / 4;
+      const float4* w4 = stashed ? stash : reinterpret_cast<const float4*>(op.norm_w + k0);
+      const float4 zero4 = make_float4(0.f, 0.f, 0.f, 0.f);
+      auto sq = [](const float4& q) { return q.x * q.x + q.y * q.y + q.z * q.z + q.w * q.w; };
+      auto put = [&](unsigned char* dst, int i, const float4& q, float inv) {        // normalised values i of the CTA's columns
+        const float4 w = w4[i];
+        __nv_bfloat162 lo = __floats2bfloat162_rn(q.x * inv * w.x, q.y * inv * w.y);
+        __nv_bfloat162 hi = __floats2bfloat162_rn(q.z * inv * w.z, q.w * inv * w.w);
+        uint2 packed;
+        packed.x = *reinterpret_cast<unsigned*>(&lo);
+        packed.y = *reinterpret_cast<unsigned*>(&hi);
+        *reinterpret_cast<uint2*>(dst + (size_t)i * 8) = packed;
+      };
       for (int m = warp; m < op.M; m += GC_CONSUMERS) {
         const float4* xr = reinterpret_cast<const float4*>(Xf + (size_t)m * op.ldx);
-        const int n4 = op.K / 4;
-        const float4* w4 = stashed ? stash : reinterpret_cast<const float4*>(op.norm_w + k0);
-        unsigned char* dst = xs + (size_t)m * GC_PITCH;
-        if (n4 <= 32 * 16) {
-          // the whole row in registers: one trip to L2 for the statistics and the values
+        unsigned char* dst = xs + (size_t)m * XP;
+        if (s4 <= 32 * 16) {
+          // The CTA's columns of the row (all of it, or a slice of at most 2048 values) stay in
+          // registers, 16 float4 a lane; the rest of a longer row is read for the sum of squares
+          // only, in batches of the same size.
           float4 v[16];
-          float ss = 0.f;
 #pragma unroll
           for (int j = 0; j < 16; ++j) {
             const int i = j * 32 + lane;
-            v[j] = i < n4 ? __ldcg(xr + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+            const float4 q = __ldcg(xr + a4 + min(i, s4 - 1));
+            v[j] = i < s4 ? q : zero4;
+          }
+          float ss = 0.f;
+          const int rest = n4 - s4;
+          for (int i0 = 0; i0 < rest; i0 += 32 * 16) {
+            float4 u[16];
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              const int i = min(i0 + j * 32 + lane, rest - 1);       // the i-th float4 of the row outside the slice
+              u[j] = __ldcg(xr + (i < a4 ? i : i + s4));
+            }
+#pragma unroll
+            for (int j = 0; j < 16; ++j) ss += i0 + j * 32 + lane < rest ? sq(u[j]) : 0.f;
           }
 #pragma unroll
-          for (int j = 0; j < 16; ++j) ss += v[j].x * v[j].x + v[j].y * v[j].y + v[j].z * v[j].z + v[j].w * v[j].w;
+          for (int j = 0; j < 16; ++j) ss += sq(v[j]);
           const float inv = rsqrtf(warp_sum(ss) / (float)op.K + op.eps);
 #pragma unroll
-          for (int j = 0; j < 16; ++j) {
-            const int i = j * 32 + lane;                      // slices == 1 here: k0 == 0, klen == K
-            if (i >= n4) continue;
-            const float4 w = w4[i];
-            __nv_bfloat162 lo = __floats2bfloat162_rn(v[j].x * inv * w.x, v[j].y * inv * w.y);
-            __nv_bfloat162 hi = __floats2bfloat162_rn(v[j].z * inv * w.z, v[j].w * inv * w.w);
-            uint2 packed;
-            packed.x = *reinterpret_cast<unsigned*>(&lo);
-            packed.y = *reinterpret_cast<unsigned*>(&hi);
-            *reinterpret_cast<uint2*>(dst + (size_t)i * 8) = packed;
-          }
+          for (int j = 0; j < 16; ++j)
+            if (j * 32 + lane < s4) put(dst, j * 32 + lane, v[j], inv);
           continue;
         }
+        // All of a row that is longer than the registers hold: once for the sum of squares and once
+        // more, from L2, for the values.
         float ss = 0.f;
-        for (int i0 = 0; i0 < n4; i0 += 32 * 8) {
-          float4 v[8];
+        for (int i0 = 0; i0 < n4; i0 += 32 * 16) {
+          float4 u[16];
 #pragma unroll
-          for (int j = 0; j < 8; ++j) {
-            const int i = i0 + j * 32 + lane;
-            v[j] = i < n4 ? __ldcg(xr + i) : make_float4(0.f, 0.f, 0.f, 0.f);
-          }
+          for (int j = 0; j < 16; ++j) u[j] = __ldcg(xr + min(i0 + j * 32 + lane, n4 - 1));
 #pragma unroll
-          for (int j = 0; j < 8; ++j) ss += v[j].x * v[j].x + v[j].y * v[j].y + v[j].z * v[j].z + v[j].w * v[j].w;
+          for (int j = 0; j < 16; ++j) ss += i0 + j * 32 + lane < n4 ? sq(u[j]) : 0.f;
         }
         const float inv = rsqrtf(warp_sum(ss) / (float)op.K + op.eps);
-        const float4* xs4 = xr + k0 / 4;
-        const int s4 = klen / 4;
-        for (int i0 = 0; i0 < s4; i0 += 32 * 8) {
-          float4 v[8];
+        for (int i0 = 0; i0 < s4; i0 += 32 * 16) {
+          float4 u[16];
 #pragma unroll
-          for (int j = 0; j < 8; ++j) {
-            const int i = i0 + j * 32 + lane;
-            v[j] = i < s4 ? __ldcg(xs4 + i) : make_float4(0.f, 0.f, 0.f, 0.f);
-          }
+          for (int j = 0; j < 16; ++j) u[j] = __ldcg(xr + a4 + min(i0 + j * 32 + lane, s4 - 1));
 #pragma unroll
-          for (int j = 0; j < 8; ++j) {
-            const int i = i0 + j * 32 + lane;
-            if (i >= s4) continue;
-            const float4 w = w4[i];
-            __nv_bfloat162 lo = __floats2bfloat162_rn(v[j].x * inv * w.x, v[j].y * inv * w.y);
-            __nv_bfloat162 hi = __floats2bfloat162_rn(v[j].z * inv * w.z, v[j].w * inv * w.w);
-            uint2 packed;
-            packed.x = *reinterpret_cast<unsigned*>(&lo);
-            packed.y = *reinterpret_cast<unsigned*>(&hi);
-            *reinterpret_cast<uint2*>(dst + (size_t)i * 8) = packed;
-          }
+          for (int j = 0; j < 16; ++j)
+            if (i0 + j * 32 + lane < s4) put(dst, i0 + j * 32 + lane, u[j], inv);
         }
       }
     } else {
@@ -542,14 +622,11 @@ __global__ void __launch_bounds__(GC_THREADS, 1) gemm_chain_kernel(const __grid_
         for (int i0 = 0; i0 < n16; i0 += 32 * 8) {
           uint4 v[8];
 #pragma unroll
-          for (int j = 0; j < 8; ++j) {
-            const int i = i0 + j * 32 + lane;
-            v[j] = i < n16 ? __ldcg(xr + i) : make_uint4(0, 0, 0, 0);
-          }
+          for (int j = 0; j < 8; ++j) v[j] = __ldcg(xr + min(i0 + j * 32 + lane, n16 - 1));
 #pragma unroll
           for (int j = 0; j < 8; ++j) {
             const int i = i0 + j * 32 + lane;
-            if (i < n16) *reinterpret_cast<uint4*>(xs + (size_t)m * GC_PITCH + (size_t)i * 16) = v[j];
+            if (i < n16) *reinterpret_cast<uint4*>(xs + (size_t)m * XP + (size_t)i * 16) = v[j];
           }
         }
       }
@@ -559,34 +636,40 @@ __global__ void __launch_bounds__(GC_THREADS, 1) gemm_chain_kernel(const __grid_
     // columns are never stored)
     const unsigned char* xrow[MT];
 #pragma unroll
-    for (int mt = 0; mt < MT; ++mt) xrow[mt] = xs + (size_t)min(mt * 8 + g, op.M - 1) * GC_PITCH + t * 16;
-    const int kblocks = klen / 32;
+    for (int mt = 0; mt < MT; ++mt) xrow[mt] = xs + (size_t)min(mt * 8 + g, op.M - 1) * XP + t * 16;
 
+    // The groups of this CTA; of each, the slice that is this CTA's, or, over x whole, all slices
+    // one after the other with the sums staying in registers.
+    const int walk = op.seq ? op.slices : 1;
     for (int grp = r; grp < op.groups; grp += op.ctas) {
       float acc[2][MT][4];
 #pragma unroll
       for (int j = 0; j < 2; ++j)
 #pragma unroll
         for (int mt = 0; mt < MT; ++mt) acc[j][mt][0] = acc[j][mt][1] = acc[j][mt][2] = acc[j][mt][3] = 0.f;
-      if (ok) {
-        ok = mbar_wait(full + s, parity);
-        if (!ok && lane == 0) atomicExch(A.err, 14);
-      }
-      const unsigned char* st = slots + (size_t)s * GC_SLOT + g * GC_PITCH + t * 16;
-#pragma unroll 2
-      for (int kb = warp; kb < kblocks; kb += GC_CONSUMERS) {
-        const uint4 a0 = gc_lds128(st + kb * 64);
-        const uint4 a1 = gc_lds128(st + 8 * GC_PITCH + kb * 64);
-#pragma unroll
-        for (int mt = 0; mt < MT; ++mt) {
-          const uint4 b = gc_lds128(xrow[mt] + kb * 64);
-          gc_mma(acc[0][mt], a0.x, a1.x, a0.y, a1.y, b.x, b.y);
-          gc_mma(acc[1][mt], a0.z, a1.z, a0.w, a1.w, b.z, b.w);
+      for (int j = 0; j < walk; ++j) {
+        const int kj = op.seq ? j * op.slice_k : 0;                 // where in the resident x this stage begins
+        const int kblocks = (op.seq ? min(op.slice_k, op.K - kj) : klen) / 32;
+        if (ok) {
+          ok = mbar_wait(full + s, parity);
+          if (!ok && lane == 0) atomicExch(A.err, 14);
         }
+        const unsigned char* st = slots + (size_t)s * SLOT + g * P + t * 16;
+#pragma unroll 2
+        for (int kb = warp; kb < kblocks; kb += GC_CONSUMERS) {
+          const uint4 a0 = gc_lds128(st + kb * 64);
+          const uint4 a1 = gc_lds128(st + 8 * P + kb * 64);
+#pragma unroll
+          for (int mt = 0; mt < MT; ++mt) {
+            const uint4 b = gc_lds128(xrow[mt] + kj * 2 + kb * 64);
+            gc_mma(acc[0][mt], a0.x, a1.x, a0.y, a1.y, b.x, b.y);
+            gc_mma(acc[1][mt], a0.z, a1.z, a0.w, a1.w, b.z, b.w);
+          }
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(empty + s);
+        if (++s == S) { s = 0; parity ^= 1; }
       }
-      __syncwarp();
-      if (lane == 0) mbar_arrive(empty + s);
-      if (++s == S) { s = 0; parity ^= 1; }
 
       // hand the partial sums to the epilogue warp
       if (red_wrapped && ok) {
@@ -601,6 +684,14 @@ __global__ void __launch_bounds__(GC_THREADS, 1) gemm_chain_kernel(const __grid_
       __syncwarp();
       if (lane == 0) mbar_arrive(red_full + rb);
       if (++rb == GC_RED_BUFS) { rb = 0; red_wrapped = true; red_parity ^= 1; }
+    }
+    if (sliced) {
+      // few slices: a warp may own several groups; many: one or none, and all its slices in one trip
+      ok = op.slices <= 2   ? gc_finish_groups<MT, 4 / MT, 2>(A, op, r, slice, warp, ok)
+           : op.slices <= 4 ? gc_finish_groups<MT, 2, 4 / MT>(A, op, r, slice, warp, ok)
+                            : gc_finish_groups<MT, 1, 16 / MT>(A, op, r, slice, warp, ok);
+      __syncwarp();
+      if (lane == 0) mbar_arrive(fixed);
     }
   }
 }
@@ -618,7 +709,17 @@ struct ChainOpDesc {
   int reserved;
 };
 
-static bool chain_cut(const ChainOpDesc& d, ChainOp& op) {
+// Bytes between rows of a stage (and of x) for `k` elements a row: pitch mod 128 = 64 keeps the
+// 16-byte shared loads of eight rows on different banks.
+static int chain_pitch(int k) { return k * 2 + ((k * 2) % 128 == 0 ? 64 : 0); }
+
+enum { CUT_ONLY = 0, CUT_OR_SEQ = 1, CUT_SEQ_OR_WALK = 2 };
+#define GC_WALK_X_BYTES (96 * 1024)      // most shared memory that x whole may take
+
+// Cuts one operation: K into slices of at most `limit` elements, the slices either to different
+// CTAs (their shares meet in scratch memory) or, where `ways` allows and it pays, one after the
+// other to the same CTA.  Leaves the pitch of x for the caller where x is a slice (op.xp = 0).
+static bool chain_cut(const ChainOpDesc& d, ChainOp& op, int limit, int ways) {
   const int sms = device_sm_count();
   if (sms <= 0) return false;
   if (d.M <= 0 || d.M > 16 || d.N <= 0 || d.K <= 0 || d.K % 32) return false;
@@ -628,43 +729,143 @@ static bool chain_cut(const ChainOpDesc& d, ChainOp& op) {
   op.W = (const bf16*)d.W; op.X = d.X; op.norm_w = d.norm_w; op.bias = d.bias; op.out = d.out;
   op.ldx = d.ldx; op.ldo = d.ldo; op.M = d.M; op.N = d.N; op.K = d.K; op.epi = d.epi; op.norm = d.norm; op.eps = d.eps;
   op.groups = (d.N + GC_ROWS - 1) / GC_ROWS;
-  op.slices = (d.K + GC_SLICE_K - 1) / GC_SLICE_K;
-  op.slice_k = ((d.K + op.slices - 1) / op.slices + 31) / 32 * 32;      // nearly equal slices, whole k blocks
-  if (op.slices > sms || (long long)(op.slices - 1) * op.slice_k >= d.K) return false;
-  op.ctas = sms / op.slices;
-  if (op.ctas > op.groups) op.ctas = op.groups;
-  // few groups per CTA, no norm, at most 8 rows (two x buffers fit): the slices one after the other
-  op.seq = (op.slices > 1 && !d.norm && d.M <= 8 && op.groups <= 2 * sms) ? 1 : 0;
-  if (op.seq) op.ctas = op.groups < sms ? op.groups : sms;
+  // nearly equal slices of whole k blocks; sms / slices CTAs work in each
+  auto cut = [&](int slices, int& slice_k, int& ctas, double& busy) {
+    slice_k = ((d.K + slices - 1) / slices + 31) / 32 * 32;
+    if (slices > sms || (long long)(slices - 1) * slice_k >= d.K) return false;
+    ctas = sms / slices < op.groups ? sms / slices : op.groups;
+    busy = (double)op.groups * slices / ((double)((op.groups + ctas - 1) / ctas) * sms);     // share of the CTAs' time that is work
+    return true;
+  };
+  double busy_cut;
+  op.slices = (d.K + limit - 1) / limit;
+  if (!cut(op.slices, op.slice_k, op.ctas, busy_cut)) return false;
+  op.seq = 0;
+  op.xp = 0;
+  if (op.slices == 1) return true;
+  const int seq_ctas = op.groups < sms ? op.groups : sms;
+  const double busy_seq = (double)op.groups / ((double)((op.groups + seq_ctas - 1) / seq_ctas) * sms);
+  // Up to 8 rows of a K that is cut but not long: x whole in shared memory and every CTA walks the
+  // slices of its groups, unless the groups divide so badly among the CTAs that way that the cut
+  // across CTAs, with its round of finishing, keeps a fifth more of them busy.
+  if (ways >= CUT_SEQ_OR_WALK && d.M <= 8 && 8 * chain_pitch(d.K) <= GC_WALK_X_BYTES && busy_cut <= 1.2 * busy_seq) {
+    op.seq = 2; op.ctas = seq_ctas; op.xp = chain_pitch(d.K);
+    return true;
+  }
+  // A few more slices, not much shorter, when the CTAs then divide the work better (15 slices
+  // employ 135 of 148 CTAs, 16 employ 144).
+  for (int s = op.slices + 1; s <= op.slices + 3; ++s) {
+    int slice_k, ctas;
+    double busy;
+    if (!cut(s, slice_k, ctas, busy) || slice_k * 100 < op.slice_k * 85) break;
+    if (busy > 1.03 * busy_cut) { op.slices = s; op.slice_k = slice_k; op.ctas = ctas; busy_cut = busy; break; }
+  }
+  // Few groups per CTA, no norm, at most 8 rows (two x buffers fit): the slices one after the other
+  // with the slices of x following them, unless the groups divide so badly among the CTAs that way
+  // (224 groups on 148 CTAs: half of them stream a second group alone) that the cut across CTAs
+  // keeps a tenth more of them busy.
+  if (ways >= CUT_OR_SEQ && !d.norm && d.M <= 8 && op.groups <= 2 * sms && busy_cut <= 1.1 * busy_seq) {
+    op.seq = 1; op.ctas = seq_ctas;
+  }
   return true;
 }
 
 // Shared memory of the kernel: the ring of stages, the partial-sum buffers and the barriers, then
-// room for x of up to `rows` rows (8 or 16).
+// `x_bytes` for x.
 // `stash`: bytes for a norm operation's weights behind x, if that costs no stage of the ring.
-static int chain_smem(int rows, bool two_x_buffers, int stash, int& n_stages, int& x_off, int& stash_off) {
+static int chain_smem(int rows, int pitch, int x_bytes, int stash, int& n_stages, int& x_off, int& stash_off) {
   const int MT = rows <= 8 ? 1 : 2;
-  int tail = rows * GC_PITCH;
-  if (two_x_buffers) tail = 2 * ((8 * GC_PITCH + 127) / 128 * 128);
   const int red = GC_RED_BUFS * GC_CONSUMERS * 32 * MT * 4 * (int)sizeof(float);
   const int bars = 1024;
-  n_stages = (GC_SMEM_LIMIT - tail - red - bars) / GC_SLOT;
+  const int slot = GC_ROWS * pitch;
+  x_bytes = (x_bytes + 127) / 128 * 128;
+  n_stages = (GC_SMEM_LIMIT - x_bytes - red - bars) / slot;
   if (n_stages > 24) n_stages = 24;
   stash = (stash + 127) / 128 * 128;
-  x_off = n_stages * GC_SLOT + red + bars;
-  const bool room = stash > 0 && x_off + tail + stash <= GC_SMEM_LIMIT;
-  stash_off = room ? x_off + tail : -1;
-  return x_off + tail + (room ? stash : 0);
+  x_off = n_stages * slot + red + bars;
+  const bool room = stash > 0 && x_off + x_bytes + stash <= GC_SMEM_LIMIT;
+  stash_off = room ? x_off + x_bytes : -1;
+  return x_off + x_bytes + (room ? stash : 0);
 }
 
-// Floats of scratch that a chain needs (0: no operation cuts K).
-Q25_EXPORT long long q25_gemm_chain_scratch_floats(const ChainOpDesc* ops, int n_ops) {
-  long long most = 0;
+// One way of cutting a whole chain: the operations into A.op, the pitch of the stages, and what x
+// needs (the most of: a slice's rows, two buffers of them, or the rows whole).
+static bool chain_cut_all(const ChainOpDesc* ops, int n_ops, int rows, int limit, int ways, ChainArgs& A, int& x_bytes, int& stash) {
+  int kmax = 0;
   for (int i = 0; i < n_ops; ++i) {
-    ChainOp op;
-    if (!chain_cut(ops[i], op)) return -1;
+    if (!chain_cut(ops[i], A.op[i], limit, ways) || A.op[i].groups > 65536) return false;
+    if (A.op[i].slice_k > kmax) kmax = A.op[i].slice_k;
+  }
+  A.pitch = chain_pitch(kmax);
+  A.slot = GC_ROWS * A.pitch;
+  x_bytes = stash = 0;
+  for (int i = 0; i < n_ops; ++i) {
+    ChainOp& op = A.op[i];
+    if (op.seq != 2) op.xp = A.pitch;
+    const int need = op.seq == 1 ? 2 * ((8 * A.pitch + 127) / 128 * 128) : rows * op.xp;
+    if (need > x_bytes) x_bytes = need;
+    const int w_bytes = (op.seq == 2 ? op.K : op.slice_k) * 4;
+    if (op.norm && w_bytes <= 8192 && w_bytes > stash) stash = w_bytes;     // longer ones are read in place
+  }
+  return true;
+}
+
+// Cuts every operation of a chain and lays out shared memory.  What a CTA can have on its way
+// from memory is the ring: stages x slice length, less the half stage that is on average being
+// handed over (a ring of two leaves the copy engine idle from the moment a stage is handed over
+// until it is free again).  Every way of cutting (x whole where possible; operations that keep
+// two buffers of x; slices to different CTAs only) is tried with slice limits from 2048 down
+// (rows of 2.3 KB still keep the copy engine's request rate above the memory's; an operation
+// that fits in one slice is never cut for it), and marked by that length averaged over the
+// operations' weights.  The best mark wins, except that x whole is taken from three quarters of
+// the best mark on: it has nothing to finish afterwards.  Returns the kernel's shared memory in
+// bytes, 0 if the chain cannot run.
+static int chain_plan(const ChainOpDesc* ops, int n_ops, ChainArgs& A) {
+  if (n_ops <= 0 || n_ops > GC_MAX_OPS) return 0;
+  int rows = 0, whole = 0;
+  for (int i = 0; i < n_ops; ++i) {
+    if (ops[i].M > rows) rows = ops[i].M;
+    if (ops[i].K <= GC_SLICE_K && ops[i].K > whole) whole = ops[i].K;
+  }
+  rows = rows <= 8 ? 8 : 16;
+  double mark[3] = {-1.0, -1.0, -1.0};
+  int limit_of[3] = {0, 0, 0}, x_bytes, stash, x_off;
+  for (int ways = CUT_ONLY; ways <= CUT_SEQ_OR_WALK; ++ways)
+    for (int limit = GC_SLICE_K; limit >= 1152 && limit >= whole; limit -= 32) {
+      if (!chain_cut_all(ops, n_ops, rows, limit, ways, A, x_bytes, stash)) continue;
+      chain_smem(rows, A.pitch, x_bytes, 0, A.n_stages, x_off, A.stash_off);
+      if (A.n_stages < 2) continue;
+      bool short_rows = false;
+      for (int i = 0; i < n_ops; ++i) short_rows |= A.op[i].slices > 1 && A.op[i].slice_k < 1152;
+      if (short_rows) continue;
+      double sum = 0.0, weights = 0.0;
+      for (int i = 0; i < n_ops; ++i) {
+        const double w = (double)ops[i].N * ops[i].K;
+        sum += w * (A.n_stages - 0.5) * A.op[i].slice_k;
+        weights += w;
+      }
+      if (sum / weights > mark[ways] * 1.0001) { mark[ways] = sum / weights; limit_of[ways] = limit; }
+    }
+  int ways = mark[CUT_OR_SEQ] >= mark[CUT_ONLY] ? CUT_OR_SEQ : CUT_ONLY;
+  if (mark[CUT_SEQ_OR_WALK] >= 0.75 * mark[ways]) ways = CUT_SEQ_OR_WALK;
+  if (mark[ways] < 0.0) return 0;
+  A.n_ops = n_ops;
+  if (!chain_cut_all(ops, n_ops, rows, limit_of[ways], ways, A, x_bytes, stash)) return 0;
+  A.stash_bytes = stash;
+  return chain_smem(rows, A.pitch, x_bytes, stash, A.n_stages, A.x_off, A.stash_off);
+}
+
+// Floats of scratch that a chain needs (0: no operation's slices meet there; -1: it cannot run).
+Q25_EXPORT long long q25_gemm_chain_scratch_floats(const ChainOpDesc* ops, int n_ops) {
+  ChainArgs A;
+  if (!chain_plan(ops, n_ops, A)) return -1;
+  long long most = 0;
+  int rows = 0;
+  for (int i = 0; i < n_ops; ++i) rows = ops[i].M > rows ? ops[i].M : rows;
+  for (int i = 0; i < n_ops; ++i) {
+    const ChainOp& op = A.op[i];
     if (op.slices > 1 && !op.seq) {
-      const long long need = (long long)op.slices * op.groups * (ops[i].M <= 8 ? 1 : 2) * 128;
+      const long long need = (long long)op.slices * op.groups * (rows <= 8 ? 1 : 2) * 128;
       if (need > most) most = need;
     }
   }
@@ -700,20 +901,14 @@ Q25_EXPORT int q25_gemm_chain_bf16(const ChainOpDesc* ops, int n_ops, float* scr
   if (n_ops <= 0) return 0;
   if (n_ops > GC_MAX_OPS || !counters || !barrier || !err || !q25_gemm_chain_available()) return (int)cudaErrorInvalidValue;
   ChainArgs A;
-  A.n_ops = n_ops;
+  const int total = chain_plan(ops, n_ops, A);
+  if (!total || A.n_stages < 2) return (int)cudaErrorInvalidValue;
   A.scratch = scratch; A.counters = counters; A.barrier = barrier; A.barrier_base = barrier_base; A.err = err;
-  int rows = 0, stash = 0;
-  bool seq = false;
+  int rows = 0;
   for (int i = 0; i < n_ops; ++i) {
-    if (!chain_cut(ops[i], A.op[i])) return (int)cudaErrorInvalidValue;
-    if (A.op[i].seq) seq = true;
-    if (A.op[i].norm && A.op[i].slice_k * 4 > stash) stash = A.op[i].slice_k * 4;
-    if (A.op[i].groups > 65536 || (A.op[i].slices > 1 && !A.op[i].seq && !scratch)) return (int)cudaErrorInvalidValue;
+    if (A.op[i].slices > 1 && !A.op[i].seq && !scratch) return (int)cudaErrorInvalidValue;
     if (ops[i].M > rows) rows = ops[i].M;
   }
-  rows = rows <= 8 ? 8 : 16;
-  const int total = chain_smem(rows, seq, stash, A.n_stages, A.x_off, A.stash_off);
-  if (A.n_stages < 2) return (int)cudaErrorInvalidValue;
   void (*kernel)(const ChainArgs) = rows <= 8 ? gemm_chain_kernel<1> : gemm_chain_kernel<2>;
   cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, total);
   if (e != cudaSuccess) return (int)e;

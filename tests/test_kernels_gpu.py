@@ -544,18 +544,21 @@ def test_gemm_skinny_with_norm_inside_and_residual_epilogue(m, n, k):
     assert int(kernels.error_flag("cuda:0")[0]) == 0
 
 
+@pytest.mark.parametrize("sizes", [(1536, 4480, 2048, 3000), (2304, 5184, 2560, 3016), (3584, 4736, 4608, 2000)])
 @pytest.mark.parametrize("m", [1, 8, 11, 16])
-def test_gemm_chain_runs_dependent_products_as_one_kernel(m):
+def test_gemm_chain_runs_dependent_products_as_one_kernel(m, sizes):
     """A layer's worth of products, each reading what the one before wrote (norm inside, bias,
     SwiGLU pairs, residual additions, a K long enough to be cut into slices, float logits), gathered
     into one persistent kernel: the results of the products launched one by one (up to the order of
     the sums), right against float64, and the same to the bit when run again, with the barrier and
-    the counters that the first run left."""
+    the counters that the first run left.  The wider sizes have rows longer than a slice under the
+    norms too (every CTA normalises its slice of a row whose statistics it reads whole) and a
+    ring of more, shorter stages."""
     from qwen25vl_lite.ops import kernels
     if not kernels.chain_available():
         pytest.skip("the device cannot hold the chain kernel's whole grid")
     rng = np.random.default_rng(40 + m)
-    hidden, inter, qkv_n, vocab = 1536, 4480, 2048, 3000
+    hidden, inter, qkv_n, vocab = sizes
     x0 = rng.standard_normal((m, hidden)) * 2
     nw = [dev(1 + 0.1 * rng.standard_normal(hidden), torch.float32) for _ in range(3)]
     w_qkv = dev(rng.standard_normal((qkv_n, hidden)) * 0.03, torch.bfloat16)
