@@ -81,12 +81,19 @@ class ClockSampler:
         self.lines = []
 
     def start(self):
+        """Returns when the first sample has come (or after five seconds): nvidia-smi's own start
+        can hold the driver for up to a second, which must not fall into what is timed."""
         try:
             self.proc = subprocess.Popen(["nvidia-smi", "-i", "0", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
                                           "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             threading.Thread(target=self._read, daemon=True).start()
         except OSError:
             self.proc = None
+            return
+        deadline = time.time() + 5.0
+        while not self.lines and time.time() < deadline and self.proc.poll() is None:
+            time.sleep(0.02)
+        del self.lines[:]
 
     def _read(self):
         for line in self.proc.stdout:

@@ -205,6 +205,7 @@ gemm_skinny_kernel(const bf16* __restrict__ W, const void* __restrict__ Xv, int 
     if (!resident) pdl_wait();                     // x travels with the chunks
     bool ok = true;
     int it = 0;
+    const unsigned long long once = l2_evict_first();      // the weights pass through L2 once; what the step reads again stays
     for (int grp = blockIdx.x; grp < groups; grp += gridDim.x) {
       const bf16* src = W + (size_t)min(grp * GS_ROWS + (lane & 15), N - 1) * K;
       for (int c = 0; c < n_chunks; ++c, ++it) {
@@ -217,7 +218,7 @@ gemm_skinny_kernel(const bf16* __restrict__ W, const void* __restrict__ Xv, int 
         unsigned char* st = stages + (size_t)s * L.stage_bytes;
         if (lane == 0) mbar_expect_tx(full + s, bytes * (GS_ROWS + (resident ? 0 : M)));
         __syncwarp();
-        if (lane < GS_ROWS) bulk_copy(st + lane * PITCH, src + (size_t)c * KC, bytes, full + s);
+        if (lane < GS_ROWS) bulk_copy_once(st + lane * PITCH, src + (size_t)c * KC, bytes, full + s, once);
         if (!resident && lane < M)
           bulk_copy(st + (GS_ROWS + lane) * PITCH, X + (size_t)lane * ldx + (size_t)c * KC, bytes, full + s);
       }

@@ -169,6 +169,8 @@ class ModelRunner:
                                 and all(getattr(p, "graph_safe", False) for p in parts))
         self._graphs: Dict[tuple, tuple] = {}
         self._graph_seen: Dict[tuple, int] = {}
+        self._capture_stream = None
+        self._graph_pool = None
         self.graph_replays = 0
         # kernels with bounded waits report a wait that gave up here; read back after every step
         # and looked at before the next one
@@ -223,8 +225,7 @@ class ModelRunner:
             collecting = gc.isenabled()
             gc.disable()
             try:
-                with torch.cuda.graph(graph):
-                    logits = self._forward_chained(ctx)
+                logits = self._capture(graph, ctx)
             finally:
                 if collecting:
                     gc.enable()
@@ -234,6 +235,26 @@ class ModelRunner:
         kernels.count_replayed(hit[3])
         self.graph_replays += 1
         return hit[1]
+
+    def _capture(self, graph, ctx: StepContext) -> torch.Tensor:
+        """Captures one step into ``graph`` on a side stream that follows the current one.  The
+        ``torch.cuda.graph`` context manager would first synchronise the device and hand the
+        allocator's cached memory back to the driver, 70 ms with a few tens of GB cached: more
+        than ten decode steps for every captured shape, over five seconds of a 128-request trace.
+        All graphs draw their buffers from one pool; they never run at the same time."""
+        if self._capture_stream is None:
+            self._capture_stream = torch.cuda.Stream(device=self.device)
+            self._graph_pool = torch.cuda.graph_pool_handle()
+        side, main = self._capture_stream, torch.cuda.current_stream(self.device)
+        side.wait_stream(main)
+        with torch.cuda.stream(side):
+            graph.capture_begin(pool=self._graph_pool)
+            try:
+                logits = self._forward_chained(ctx)
+            finally:
+                graph.capture_end()
+        main.wait_stream(side)
+        return logits
 
     def _forward_chained(self, ctx: StepContext) -> torch.Tensor:
         """The model's forward with the weight-streaming products of consecutive parts gathered
