@@ -66,7 +66,7 @@ class CacheGroup:
         return 2 * len(self.stops) * self.need.kv_heads * self.need.head_dim * element_size
 
 
-@dataclass
+@dataclass(eq=False)
 class RequestCache:
     """What one live request holds: a state slot and, per group, its block table (the
     physical page of each logical page; -1 where none is held)."""

@@ -32,7 +32,7 @@ from ..models.decoder import DecoderModel, StopRuntime
 from ..ops import kernels
 
 
-@dataclass
+@dataclass(eq=False)
 class Request:
     """A live request as the step function sees it."""
 

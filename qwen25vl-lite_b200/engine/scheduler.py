@@ -69,7 +69,7 @@ class RequestOutput:
         return cls(seq.seq_id, list(seq.prompt_token_ids), list(seq.output_token_ids), reason, {**counts, **timing})
 
 
-@dataclass
+@dataclass(eq=False)          # a request is equal to itself only: membership tests must not compare token lists
 class Sequence:
     seq_id: int
     prompt_token_ids: List[int]
@@ -228,7 +228,7 @@ class LLMEngine:
         cache = self.runner.cache
         for want_decode in (True, False):
             for seq in list(self.running):
-                if seq not in self.running or seq.seq_id in scheduled or (seq.pending == 1) != want_decode:
+                if seq.status != "running" or seq.seq_id in scheduled or (seq.pending == 1) != want_decode:
                     continue
                 n = self._portion(seq, budget)
                 if n <= 0:
