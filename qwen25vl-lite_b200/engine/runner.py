@@ -101,6 +101,7 @@ class StepContext:
     q_start_pos: torch.Tensor
     slot_ids: torch.Tensor
     logit_rows: Optional[torch.Tensor]
+    logits_every_row: bool       # every entry brings one token and wants its logits: logit_rows is 0 .. n_tokens - 1
     max_q_len: int
     max_kv_len: int
     group_kv_slot: List[torch.Tensor]
@@ -443,6 +444,7 @@ class ModelRunner:
             dtype=self.dtype, device=self.device, n_tokens=N, n_seqs=S,
             token_ids=d(tok_s), positions=d(pos_s, (self.axes, N)), token_seq=d(tseq_s), cu_q=d(cu_s),
             q_start_pos=d(qs_s), slot_ids=d(sl_s), logit_rows=d(rows_s) if M else None,
+            logits_every_row=(M == N == S and all(list(e.want) == [0] for e in entries)),
             max_q_len=max(q_lens),
             max_kv_len=(max(widths) * ps if graph_key else max(s + n for s, n in zip(starts, q_lens))),
             group_kv_slot=[d(s_) for s_ in g_slot_s],

@@ -135,5 +135,9 @@ class DecoderModel:
             pending = self.blocks[stop.layer].forward(ctx, x, pending, stop)
         if ctx.logit_rows is None or ctx.logit_rows.shape[0] == 0:
             return None
-        h = self.final_norm.forward(ctx, x, pending, rows=ctx.logit_rows)
+        # a step of single tokens that all want their logits needs no gather, and a head that can
+        # normalise inside its product then gets the norm handed on instead of its result
+        rows = None if getattr(ctx, "logits_every_row", False) else ctx.logit_rows
+        h = self.final_norm.forward(ctx, x, pending, rows=rows,
+                                    defer=rows is None and getattr(self.head, "accepts_deferred_norm", False))
         return self.head.forward(ctx, h)

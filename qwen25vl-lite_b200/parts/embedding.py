@@ -38,6 +38,7 @@ class TokenEmbedding(Part):
 @register_head("linear_head")
 class LinearHead(Part):
     graph_safe = True                # forward is a fixed sequence of this engine's kernels
+    accepts_deferred_norm = True     # its product is a ``Linear``, which normalises inside the kernel when it can
 
     def __init__(self, vocab_size: int, hidden_size: int, tied: bool, tied_to: str = "embed_tokens.weight"):
         """``tied``: without a weight of its own in the checkpoint the head reads the tensor that
