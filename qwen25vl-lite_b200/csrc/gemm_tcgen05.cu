@@ -4,9 +4,10 @@
 //
 // One persistent CTA per SM, 6 warps with fixed roles:
 //   warp 0   TMA producer: one lane issues cp.async.bulk.tensor loads of a 128 x 64 tile of x and a
-//            BN x 64 tile of W (128-byte swizzle; BN = 256, or 128 for small problems) into a ring
-//            of 4 (6) shared-memory stages; each stage has a "full" mbarrier that counts the bytes;
-//   warp 1   MMA issuer: allocates 2 BN columns of tensor memory (two 128 x BN float accumulators),
+//            BN x 64 tile of W (128-byte swizzle; BN = 256, or what fills the SMs best, see pick_bn)
+//            into a ring of 4 to 6 shared-memory stages; each stage has a "full" mbarrier that counts
+//            the bytes;
+//   warp 1   MMA issuer: allocates 512 columns of tensor memory (two 128 x BN float accumulators),
 //            then one lane issues tcgen05.mma (M 128, N BN, K 16) four times per stage and commits
 //            to the stage's "empty" mbarrier, and after the last K block to the accumulator's
 //            "full" mbarrier; while the epilogue drains one accumulator the next tile fills the other;
@@ -32,13 +33,15 @@ enum { T5_STORE = 0, T5_BIAS = 1, T5_F32 = 2, T5_SWIGLU = 3, T5_RESIDUAL = 4 };
 #define T5_A_BYTES (T5_BM * T5_BK * 2)
 #define T5_MAX_STAGES 6
 
-// The feature tile is 256 wide (4 stages of 48 KB) or, where that leaves SMs idle in the last wave,
-// 128 wide (6 stages of 32 KB).
-template <int BN> struct T5Cfg {
-  static constexpr int STAGES = BN == 256 ? 4 : 6;
-  static constexpr int B_BYTES = BN * T5_BK * 2;
-  static constexpr int STAGE_BYTES = T5_A_BYTES + B_BYTES;
-};
+// The feature tile is `bn` wide, a multiple of 32 up to 256 that the host picks (pick_bn): a stage
+// of the ring is 16 KB of x and bn x 128 bytes of W, and as many stages as fit in 200 KB, six at most
+// (4 stages of 48 KB at 256, 6 of 32 KB at 128).
+#define T5_MAX_BN 256
+static inline int t5_stage_bytes(int bn) { return T5_A_BYTES + bn * T5_BK * 2; }
+static inline int t5_stages(int bn) {
+  const int s = (200 * 1024) / t5_stage_bytes(bn);
+  return s > T5_MAX_STAGES ? T5_MAX_STAGES : s;
+}
 #define T5_THREADS 192
 
 // 2-D tiled TMA load (no multicast): box at element coordinates (x = K index, y = row).
@@ -103,12 +106,12 @@ __device__ __forceinline__ void t5_emit32(const float (&v)[32], int m, int n, in
   }
 }
 
-template <int EPI, int BN>
+template <int EPI>
 __global__ void __launch_bounds__(T5_THREADS, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
                     const float* __restrict__ bias, void* __restrict__ out, int ldo, int M, int N, int K,
-                    int* __restrict__ err) {
-  constexpr int T5_BN = BN, T5_STAGES = T5Cfg<BN>::STAGES, T5_STAGE_BYTES = T5Cfg<BN>::STAGE_BYTES;
+                    int bn, int n_stages, int* __restrict__ err) {
+  const int T5_BN = bn, T5_STAGES = n_stages, T5_STAGE_BYTES = T5_A_BYTES + bn * T5_BK * 2;
   extern __shared__ __align__(1024) unsigned char t5_smem[];
   // the dynamic shared memory starts with the stages (1024-byte aligned for the swizzle), the barriers follow
   unsigned char* stages = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(t5_smem) + 1023) & ~(uintptr_t)1023);
@@ -135,8 +138,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
   // memory is asked for only after that kernel has finished: a CTA that held columns while it waited
   // could starve a CTA of the earlier kernel on the same SM that still has to allocate its own.
   pdl_wait();
-  if (warp == 1) {   // tensor memory: two accumulators of BN columns
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_u32(&sh->tmem_base)), "n"(2 * BN) : "memory");
+  if (warp == 1) {   // tensor memory: two accumulators of up to 256 columns (the CTA has its SM to itself)
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_u32(&sh->tmem_base)), "n"(2 * T5_MAX_BN) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
   }
   tc5_fence_before();
@@ -158,7 +161,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
             if (!ok) atomicExch(err, 11);
           }
           unsigned char* st = stages + (size_t)s * T5_STAGE_BYTES;
-          mbar_expect_tx(sh->full + s, T5_STAGE_BYTES);
+          mbar_expect_tx(sh->full + s, (unsigned)T5_STAGE_BYTES);
           t5_tma_load(st, &map_x, kb * T5_BK, m0, sh->full + s);
           t5_tma_load(st + T5_A_BYTES, &map_w, kb * T5_BK, n0, sh->full + s);
         }
@@ -168,7 +171,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
     // ---- MMA issuer ----
     if (lane == 0) {
       bool ok = true;
-      const unsigned idesc = tc5_idesc(BN, false);
+      const unsigned idesc = tc5_idesc(T5_BN, false);
       int it = 0, tile_it = 0;
       for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++tile_it) {
         const int b = tile_it & 1;
@@ -177,7 +180,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
           if (!ok) atomicExch(err, 12);
         }
         tc5_fence_after();
-        const unsigned acc = tmem_base + (unsigned)b * T5_BN;
+        const unsigned acc = tmem_base + (unsigned)b * T5_MAX_BN;
         for (int kb = 0; kb < k_blocks; ++kb, ++it) {
           const int s = it % T5_STAGES;
           if (ok) {
@@ -209,7 +212,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
       }
       tc5_fence_after();
       const int m = m0 + quarter * 32 + lane;
-      const unsigned taddr = tmem_base + ((unsigned)(quarter * 32) << 16) + (unsigned)b * T5_BN;
+      const unsigned taddr = tmem_base + ((unsigned)(quarter * 32) << 16) + (unsigned)b * T5_MAX_BN;
 #pragma unroll 1
       for (int c = 0; c < T5_BN; c += 32) {
         float v[32];
@@ -229,7 +232,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
   __syncthreads();
   if (warp == 1) {
     tc5_fence_after();
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "n"(2 * BN) : "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "n"(2 * T5_MAX_BN) : "memory");
   }
 }
 
@@ -496,16 +499,20 @@ static int make_map(CUtensorMap* map, const void* base, int rows, int K, int ld,
   return r == CUDA_SUCCESS ? 0 : (int)cudaErrorInvalidValue;
 }
 
-template <int EPI, int BN>
+template <int EPI>
 static int launch_t5(const CUtensorMap& mx, const CUtensorMap& mw, const float* bias, void* out, int ldo, int M, int N, int K,
-                     int* err, cudaStream_t s) {
-  const size_t smem = (size_t)T5Cfg<BN>::STAGES * T5Cfg<BN>::STAGE_BYTES + 1024 + sizeof(T5Shared);
-  cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel<EPI, BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+                     int bn, int* err, cudaStream_t s) {
+  const int stages = t5_stages(bn);
+  // the kernel may take the most any width needs: the attribute is set once per kernel, not per width
+  const size_t most = (size_t)200 * 1024 + 1024 + sizeof(T5Shared);
+  const size_t smem = (size_t)stages * t5_stage_bytes(bn) + 1024 + sizeof(T5Shared);
+  cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel<EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)most);
   if (e != cudaSuccess) return (int)e;
-  const int tiles = ((M + T5_BM - 1) / T5_BM) * ((N + BN - 1) / BN);
+  const int tiles = ((M + T5_BM - 1) / T5_BM) * ((N + bn - 1) / bn);
   const int sms = device_sm_count();
   if (sms <= 0) return (int)cudaErrorInvalidDevice;
-  launch(gemm_tcgen05_kernel<EPI, BN>, dim3(tiles < sms ? tiles : sms), dim3(T5_THREADS), smem, s, mx, mw, bias, out, ldo, M, N, K, err);
+  launch(gemm_tcgen05_kernel<EPI>, dim3(tiles < sms ? tiles : sms), dim3(T5_THREADS), smem, s, mx, mw, bias, out, ldo, M, N, K,
+         bn, stages, err);
   return launch_status();
 }
 
@@ -538,12 +545,26 @@ static int launch_pair(const CUtensorMap& mx, const CUtensorMap& mw, const CUten
   return (int)e;
 }
 
-// Width of the feature tile.  The 128-wide MMA does half the arithmetic for the same traffic of the
-// x operand out of shared memory and runs at about 0.7 of the 256-wide one (measured), so it is
-// only used when 256-wide tiles would leave more than half of the SMs without a tile.
+// Width of the feature tile.  Up to 128 rows (one tile of rows: a decode step of that many requests)
+// the product is a stream of the weights, a tile's time is its width, and the width is the multiple
+// of 32 for which (waves of tiles over the SMs) x (width) is least: 22,016 features are 86 tiles of
+// 256 on 148 SMs but 138 of 160 (23 -> 15 us), 37,888 are 148 of 256.  With more rows the 256-wide
+// MMA counts: the 128-wide one does half the arithmetic for the same traffic of the x operand out
+// of shared memory and runs at about 0.7 of it (measured), so it is only used when 256-wide tiles
+// would leave more than half of the SMs without a tile.
 static int pick_bn(int M, int N) {
-  const long long t256 = (long long)((M + T5_BM - 1) / T5_BM) * ((N + 255) / 256);
-  return 2 * t256 <= device_sm_count() ? 128 : 256;
+  const int sms = device_sm_count();
+  if (M > T5_BM) {
+    const long long t256 = (long long)((M + T5_BM - 1) / T5_BM) * ((N + 255) / 256);
+    return 2 * t256 <= sms ? 128 : 256;
+  }
+  int best = T5_MAX_BN;
+  long long best_cost = -1;
+  for (int bn = T5_MAX_BN; bn >= 64; bn -= 32) {
+    const long long tiles = (N + bn - 1) / bn, cost = ((tiles + sms - 1) / sms) * bn;
+    if (best_cost < 0 || cost < best_cost) { best = bn; best_cost = cost; }
+  }
+  return best;
 }
 
 // x: [M, K] bfloat16 with row pitch ldx; W: [N, K] bfloat16 contiguous.  epi as in gemm_skinny.cu
@@ -577,8 +598,7 @@ Q25_EXPORT int q25_gemm_tcgen05_bf16(const void* W, const void* X, int ldx, cons
   r = make_map(&mw, W, N, K, K, bn);
   if (r) return r;
 #define T5_CASE(E) \
-  case E: return bn == 256 ? launch_t5<E, 256>(mx, mw, bias, out, ldo, M, N, K, err, s) \
-                           : launch_t5<E, 128>(mx, mw, bias, out, ldo, M, N, K, err, s);
+  case E: return launch_t5<E>(mx, mw, bias, out, ldo, M, N, K, bn, err, s);
   switch (epi) {
     T5_CASE(T5_STORE)
     T5_CASE(T5_BIAS)

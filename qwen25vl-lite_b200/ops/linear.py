@@ -11,8 +11,8 @@
   epilogues, or the library product (cuBLAS through ``torch.mm`` / ``torch.addmm``), which the
   reference's engine uses for every projection (``nn.Linear``,
   src/qwen25vl_lite/text.py:61-63,80-83; src/qwen25vl_lite/model.py:84); see ``use_tcgen05``.
-  Batches of 17 to 127 rows and operands the tcgen05 kernel refuses (K not a multiple of 8,
-  unaligned rows) go to the library.
+  Batches of 17 to 127 rows (but for the largest gate/up products) and operands the tcgen05
+  kernel refuses (K not a multiple of 8, unaligned rows) go to the library.
 """
 
 from __future__ import annotations
@@ -23,27 +23,37 @@ import torch
 
 from . import kernels
 
-# The tcgen05 kernel works in tiles of 128 rows; below that (decode batches of 17 to 127 requests)
-# too few tiles would stream the weights, and the library product is used.
+# The tcgen05 kernel works in tiles of 128 rows; with fewer rows (decode batches of 17 to 127
+# requests) the product is a stream of the weights, and it takes only the large ones (see below).
 TCGEN05_MIN_ROWS = 128
 
 
 def use_tcgen05(x: torch.Tensor, w: torch.Tensor, fused_epilogue: bool = False) -> bool:
-    """Which kernel takes a product of more than 16 rows.  Measured on B200 at 3B sizes:
+    """Which kernel takes a product of more than 16 rows.  Measured on B200:
 
-    * 2,048 rows (prefill): the engine's tcgen05 kernel (pairs of CTAs from 256 rows on) reaches
-      1.22 PFLOP/s on the wide products where cuBLAS reaches 1.46-1.48, and on the narrow ones
-      (qkv, o: 80 and 64 tiles of 256 x 256 for 74 pairs of SMs) 0.64-0.79 against 1.2.  So it
-      takes the products where its fused epilogue saves a kernel and a round trip through memory
-      (gate_up with SwiGLU: about 150 us against 125 + 75 us), and the library the others;
-    * 17 to 127 rows (decode steps of that many requests): the products are streams of the weights
-      and three of the four have 16 or 20 tiles of 128 features for 148 SMs.  A stream-K variant of
-      the tcgen05 kernel (units of (tile, K block) dealt evenly to all SMs, segment sums handed
-      between CTAs in float and added in K order) was built and measured: 12 / 9 / 26 / 18 us for
-      qkv / o / gate_up / down at 17 rows against cuBLAS's 5 / 5 / 16 / 17 us.  What it loses is not
-      the stream but its tail: sums through L2, a counter, a poll, another pass, per product.  It
-      is not kept; these products go to the library until they run chained like those of 16 rows."""
-    return fused_epilogue and x.shape[0] >= TCGEN05_MIN_ROWS and kernels.gemm_tcgen05_supports(x, w)
+    * 2,048 rows (prefill, 3B sizes): the engine's tcgen05 kernel (pairs of CTAs from 256 rows on)
+      reaches 1.22 PFLOP/s on the wide products where cuBLAS reaches 1.46-1.48 (at the 7B sizes
+      1.72 on gate/up), and on the narrow ones (qkv, o: 80 and 64 tiles of 256 x 256 for 74 pairs of
+      SMs) 0.64-0.79 against 1.2.  So it takes the products where its fused epilogue saves a kernel
+      and a round trip through memory (gate_up with SwiGLU: about 150 us against 125 + 75 us), and
+      the library the others;
+    * 17 to 127 rows (decode steps of that many requests): the products are streams of the weights.
+      One CTA per SM takes one tile of all rows x ``bn`` features, ``bn`` picked so that the tiles
+      fill the SMs once; the stream then runs at the copy bandwidth, but launch, the first trip to
+      memory and the epilogue (about 8 us together) are not hidden behind anything, where the
+      library's smaller tiles overlap one another (3 us).  With the SwiGLU epilogue fused, against
+      library product + SiLU-mul kernel: 23 against 19 to 23 us at the 3B sizes (45 M weights),
+      53 against 51 / 54 / 58 us at 32 / 64 / 98 rows at 7B (136 M), 94 to 98 against 101 to 111 us
+      at 32B (283 M).  So it takes gate_up from 64 rows at 2**27 weights and from 17 rows at 2**28.
+      A stream-K variant (units of (tile, K block) dealt evenly to all SMs, segment sums handed
+      between CTAs in float and added in K order) was built and measured too: 12 / 9 / 26 / 18 us
+      for qkv / o / gate_up / down at 17 rows of the 3B sizes against cuBLAS's 5 / 5 / 16 / 17 us.
+      What it loses is not the stream but its tail: sums through L2, a counter, a poll, another
+      pass, per product.  It is not kept."""
+    if not fused_epilogue or not kernels.gemm_tcgen05_supports(x, w):
+        return False
+    rows, weights = x.shape[0], w.shape[0] * w.shape[1]
+    return rows >= TCGEN05_MIN_ROWS or (rows >= 64 and weights >= 1 << 27) or (rows > kernels.SKINNY_MAX_ROWS and weights >= 1 << 28)
 
 
 class DeferredNorm:

@@ -687,10 +687,13 @@ def test_attention_decode_fused(nq, nkv, d, section, page_size, window, splits, 
 
 @pytest.mark.parametrize("m,n,k", [(128, 256, 64), (2048, 2560, 2048), (300, 1000, 512), (17, 4752, 256), (1000, 512, 11008),
                                    (129, 272, 72), (40, 2048, 2048), (64, 2560, 2048), (17, 2048, 11008), (100, 22016, 2048),
-                                   (33, 144, 4160), (127, 151936, 256), (2048, 9700, 128), (700, 5000, 320)])
+                                   (33, 144, 4160), (127, 151936, 256), (2048, 9700, 128), (700, 5000, 320),
+                                   (32, 55296, 128), (98, 37888, 64), (20, 33000, 96)])
 def test_gemm_tcgen05(m, n, k):
     """The tcgen05 / TMA product against float64 on the same bfloat16 operands: whole tiles, ragged
-    edges in M, N and K, many K blocks (the ring of stages wraps), every epilogue."""
+    edges in M, N and K, many K blocks (the ring of stages wraps), every epilogue.  Up to 128 rows
+    the width of a feature tile follows from the number of features (64 to 256 in steps of 32:
+    160 for 22,016 features, 192 for 55,296, 224 for 33,000)."""
     from qwen25vl_lite.ops import kernels
     rng = np.random.default_rng(m + n + k)
     x = dev(rng.standard_normal((m, k)), torch.bfloat16)
