@@ -1,11 +1,13 @@
-// A chain of weight-streaming products in ONE persistent kernel (decode steps, at most 16 rows).
+// y[M,N] = x[M,K] . W[N,K]^T for a handful of rows (decode steps: M = live requests <= 8), bfloat16,
+// as one operation or as a chain of up to eight in ONE persistent kernel.
 //
-// A decode step is a chain of small products, each of which needs the whole result of the one
-// before it: o-projection -> gate/up -> down -> next layer's qkv ...  Launched one by one
-// (gemm_skinny.cu), every link pays for the end of one kernel and the start of the next: the
-// stream of weights stops, the SMs drain, the next kernel's first bytes take a memory latency to
-// arrive (measured in a step: 7 to 12 us for products whose weights pass in 1.5 us).  Here the
-// links are operations of one kernel:
+// With so few rows a product is a stream of its weights: every byte of W is read once and used for M
+// multiply-adds, so the kernel is built around keeping HBM busy, not the tensor cores.  And a decode
+// step is a chain of such products, each of which needs the whole result of the one before it:
+// o-projection -> gate/up -> down -> next layer's qkv ...  Launched one by one, every link pays
+// for the end of one kernel and the start of the next: the stream of weights stops, the SMs drain,
+// the next kernel's first bytes take a memory latency to arrive (measured in a step: 7 to 12 us
+// for products whose weights pass in 1.5 us).  Here the links are operations of one kernel:
 //
 //   * One CTA per SM stays resident for the whole chain: the grid has as many CTAs as the device has
 //     SMs and a CTA's shared memory leaves room for no second one, so every CTA finds an SM as soon
@@ -19,8 +21,12 @@
 //     through the operations and fills the ring of stages with the next operation's weights while
 //     the other warps are still finishing this one or stand at the barrier.  The stream from memory
 //     does not stop at a link.
-//   * Inside an operation the work is that of gemm_skinny.cu: groups of 16 output features, the
-//     weights on the 16-row side of mma.sync m16n8k16, eight MMA warps taking alternate 32-wide
+//   * Inside an operation: groups of 16 output features (16 rows of W), the weights on the 16-row
+//     side of mma.sync m16n8k16 (the operands are swapped: W is "A", x^T is "B", 8 batch columns
+//     per instruction; a thread reads 16 contiguous bytes of a row from shared memory and feeds
+//     them to two MMAs, and since a dot product does not care about the order of its terms the 8
+//     values take the MMA's k slots in memory order and x is read with the same assignment), eight
+//     MMA warps taking alternate 32-wide
 //     k blocks, an epilogue warp adding their partial sums in warp order, x resident in shared
 //     memory (read past the L1 cache, which knows nothing of what other SMs wrote since the
 //     launch), optional RMSNorm of the float residual stream on the way in (reference
@@ -51,6 +57,9 @@
 enum { EPI_STORE = 0, EPI_BIAS = 1, EPI_F32 = 2, EPI_SWIGLU = 3, EPI_RESIDUAL = 4 };
 
 #define GC_ROWS 16
+#define GC_MAX_M 8                               // rows of x: one 8-column tile of the MMA (MT = 1).  A second tile
+                                                 // (9 to 16 rows) was measured slower than the library's products
+                                                 // at every size and is not instantiated.
 #define GC_CONSUMERS 8
 #define GC_RED_BUFS 2
 #define GC_THREADS ((GC_CONSUMERS + 2) * 32)
@@ -722,7 +731,7 @@ enum { CUT_ONLY = 0, CUT_OR_SEQ = 1, CUT_SEQ_OR_WALK = 2 };
 static bool chain_cut(const ChainOpDesc& d, ChainOp& op, int limit, int ways) {
   const int sms = device_sm_count();
   if (sms <= 0) return false;
-  if (d.M <= 0 || d.M > 16 || d.N <= 0 || d.K <= 0 || d.K % 32) return false;
+  if (d.M <= 0 || d.M > GC_MAX_M || d.N <= 0 || d.K <= 0 || d.K % 32) return false;
   if (((unsigned long long)d.W & 15) || ((unsigned long long)d.X & 15)) return false;
   if (d.norm ? (d.ldx % 4 || !d.norm_w) : (d.ldx % 8 != 0)) return false;
   if ((d.epi == EPI_SWIGLU && d.N % 16) || (d.epi == EPI_BIAS && !d.bias) || d.epi < 0 || d.epi > EPI_RESIDUAL) return false;
@@ -745,10 +754,10 @@ static bool chain_cut(const ChainOpDesc& d, ChainOp& op, int limit, int ways) {
   if (op.slices == 1) return true;
   const int seq_ctas = op.groups < sms ? op.groups : sms;
   const double busy_seq = (double)op.groups / ((double)((op.groups + seq_ctas - 1) / seq_ctas) * sms);
-  // Up to 8 rows of a K that is cut but not long: x whole in shared memory and every CTA walks the
+  // A K that is cut but not long: x whole in shared memory and every CTA walks the
   // slices of its groups, unless the groups divide so badly among the CTAs that way that the cut
   // across CTAs, with its round of finishing, keeps a fifth more of them busy.
-  if (ways >= CUT_SEQ_OR_WALK && d.M <= 8 && 8 * chain_pitch(d.K) <= GC_WALK_X_BYTES && busy_cut <= 1.2 * busy_seq) {
+  if (ways >= CUT_SEQ_OR_WALK && GC_MAX_M * chain_pitch(d.K) <= GC_WALK_X_BYTES && busy_cut <= 1.2 * busy_seq) {
     op.seq = 2; op.ctas = seq_ctas; op.xp = chain_pitch(d.K);
     return true;
   }
@@ -760,11 +769,11 @@ static bool chain_cut(const ChainOpDesc& d, ChainOp& op, int limit, int ways) {
     if (!cut(s, slice_k, ctas, busy) || slice_k * 100 < op.slice_k * 85) break;
     if (busy > 1.03 * busy_cut) { op.slices = s; op.slice_k = slice_k; op.ctas = ctas; busy_cut = busy; break; }
   }
-  // Few groups per CTA, no norm, at most 8 rows (two x buffers fit): the slices one after the other
+  // Few groups per CTA, no norm: the slices one after the other
   // with the slices of x following them, unless the groups divide so badly among the CTAs that way
   // (224 groups on 148 CTAs: half of them stream a second group alone) that the cut across CTAs
   // keeps a tenth more of them busy.
-  if (ways >= CUT_OR_SEQ && !d.norm && d.M <= 8 && op.groups <= 2 * sms && busy_cut <= 1.1 * busy_seq) {
+  if (ways >= CUT_OR_SEQ && !d.norm && op.groups <= 2 * sms && busy_cut <= 1.1 * busy_seq) {
     op.seq = 1; op.ctas = seq_ctas;
   }
   return true;
@@ -774,7 +783,7 @@ static bool chain_cut(const ChainOpDesc& d, ChainOp& op, int limit, int ways) {
 // `x_bytes` for x.
 // `stash`: bytes for a norm operation's weights behind x, if that costs no stage of the ring.
 static int chain_smem(int rows, int pitch, int x_bytes, int stash, int& n_stages, int& x_off, int& stash_off) {
-  const int MT = rows <= 8 ? 1 : 2;
+  const int MT = (rows + 7) / 8;
   const int red = GC_RED_BUFS * GC_CONSUMERS * 32 * MT * 4 * (int)sizeof(float);
   const int bars = 1024;
   const int slot = GC_ROWS * pitch;
@@ -802,7 +811,7 @@ static bool chain_cut_all(const ChainOpDesc* ops, int n_ops, int rows, int limit
   for (int i = 0; i < n_ops; ++i) {
     ChainOp& op = A.op[i];
     if (op.seq != 2) op.xp = A.pitch;
-    const int need = op.seq == 1 ? 2 * ((8 * A.pitch + 127) / 128 * 128) : rows * op.xp;
+    const int need = op.seq == 1 ? 2 * ((rows * A.pitch + 127) / 128 * 128) : rows * op.xp;
     if (need > x_bytes) x_bytes = need;
     const int w_bytes = (op.seq == 2 ? op.K : op.slice_k) * 4;
     if (op.norm && w_bytes <= 8192 && w_bytes > stash) stash = w_bytes;     // longer ones are read in place
@@ -822,12 +831,10 @@ static bool chain_cut_all(const ChainOpDesc* ops, int n_ops, int rows, int limit
 // bytes, 0 if the chain cannot run.
 static int chain_plan(const ChainOpDesc* ops, int n_ops, ChainArgs& A) {
   if (n_ops <= 0 || n_ops > GC_MAX_OPS) return 0;
-  int rows = 0, whole = 0;
-  for (int i = 0; i < n_ops; ++i) {
-    if (ops[i].M > rows) rows = ops[i].M;
+  int whole = 0;
+  for (int i = 0; i < n_ops; ++i)
     if (ops[i].K <= GC_SLICE_K && ops[i].K > whole) whole = ops[i].K;
-  }
-  rows = rows <= 8 ? 8 : 16;
+  const int rows = GC_MAX_M;                     // shared memory is laid out for a full tile of rows
   double mark[3] = {-1.0, -1.0, -1.0};
   int limit_of[3] = {0, 0, 0}, x_bytes, stash, x_off;
   for (int ways = CUT_ONLY; ways <= CUT_SEQ_OR_WALK; ++ways)
@@ -860,12 +867,10 @@ Q25_EXPORT long long q25_gemm_chain_scratch_floats(const ChainOpDesc* ops, int n
   ChainArgs A;
   if (!chain_plan(ops, n_ops, A)) return -1;
   long long most = 0;
-  int rows = 0;
-  for (int i = 0; i < n_ops; ++i) rows = ops[i].M > rows ? ops[i].M : rows;
   for (int i = 0; i < n_ops; ++i) {
     const ChainOp& op = A.op[i];
     if (op.slices > 1 && !op.seq) {
-      const long long need = (long long)op.slices * op.groups * (rows <= 8 ? 1 : 2) * 128;
+      const long long need = (long long)op.slices * op.groups * 128;
       if (need > most) most = need;
     }
   }
@@ -891,7 +896,7 @@ Q25_EXPORT int q25_gemm_chain_desc_bytes(void) { return (int)sizeof(ChainOpDesc)
 // CTAs of the kernel: one per SM of the current device.
 Q25_EXPORT int q25_gemm_chain_grid(void) { return device_sm_count(); }
 
-// Runs ops[0 .. n_ops) (at most 8 products of at most 16 rows) as one kernel; every operation may
+// Runs ops[0 .. n_ops) (at most 8 products of at most 8 rows) as one kernel; every operation may
 // read what the ones before it wrote.  scratch: q25_gemm_chain_scratch_floats() floats; counters:
 // 65536 ints, zero; barrier: one unsigned int whose value when the launch begins is barrier_base
 // (each launch adds (n_ops - 1) * q25_gemm_chain_grid() to it); err: one int that receives a
@@ -904,12 +909,9 @@ Q25_EXPORT int q25_gemm_chain_bf16(const ChainOpDesc* ops, int n_ops, float* scr
   const int total = chain_plan(ops, n_ops, A);
   if (!total || A.n_stages < 2) return (int)cudaErrorInvalidValue;
   A.scratch = scratch; A.counters = counters; A.barrier = barrier; A.barrier_base = barrier_base; A.err = err;
-  int rows = 0;
-  for (int i = 0; i < n_ops; ++i) {
+  for (int i = 0; i < n_ops; ++i)
     if (A.op[i].slices > 1 && !A.op[i].seq && !scratch) return (int)cudaErrorInvalidValue;
-    if (ops[i].M > rows) rows = ops[i].M;
-  }
-  void (*kernel)(const ChainArgs) = rows <= 8 ? gemm_chain_kernel<1> : gemm_chain_kernel<2>;
+  void (*kernel)(const ChainArgs) = gemm_chain_kernel<1>;
   cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, total);
   if (e != cudaSuccess) return (int)e;
   launch(kernel, dim3(device_sm_count()), dim3(GC_THREADS), (size_t)total, (cudaStream_t)stream, A);

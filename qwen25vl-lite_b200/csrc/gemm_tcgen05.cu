@@ -13,7 +13,7 @@
 //            "full" mbarrier; while the epilogue drains one accumulator the next tile fills the other;
 //   warps 2-5  epilogue: each reads its quarter of the 128 accumulator rows with tcgen05.ld (a lane
 //            owns one row), applies the epilogue and stores straight to global memory.
-// Epilogues as in gemm_skinny.cu: store, + float bias, float output, SwiGLU on paired rows (8 gate
+// Epilogues as in gemm_chain.cu: store, + float bias, float output, SwiGLU on paired rows (8 gate
 // features followed by their 8 up features; reference formula src/qwen25vl_lite/text.py:66), and
 // add into the float residual stream.
 //
@@ -567,7 +567,7 @@ static int pick_bn(int M, int N) {
   return best;
 }
 
-// x: [M, K] bfloat16 with row pitch ldx; W: [N, K] bfloat16 contiguous.  epi as in gemm_skinny.cu
+// x: [M, K] bfloat16 with row pitch ldx; W: [N, K] bfloat16 contiguous.  epi as in gemm_chain.cu
 // (0 store, 1 + bias, 2 float out, 3 SwiGLU pairs, 4 add into float out).  Needs K % 8 == 0,
 // ldx % 8 == 0 and 16-byte aligned bases (TMA).  err: device int that gets a code if a wait gave up.
 Q25_EXPORT int q25_gemm_tcgen05_bf16(const void* W, const void* X, int ldx, const float* bias, void* out, int ldo, int M,

@@ -32,7 +32,7 @@ NVCC_FLAGS = [
 # 32-bit run compiles (at its first call) only what it needs.
 LIBRARIES: Dict[str, List[str]] = {
     "core": ["elementwise.cu", "rope_cache.cu", "attention_generic.cu", "gemm_f32.cu", "sampling.cu"],
-    "bf16": ["attention_mma.cu", "attention_tcgen05.cu", "gemm_skinny.cu", "gemm_chain.cu", "gemm_tcgen05.cu"],
+    "bf16": ["attention_mma.cu", "attention_tcgen05.cu", "gemm_chain.cu", "gemm_tcgen05.cu"],
 }
 
 

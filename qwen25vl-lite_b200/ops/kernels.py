@@ -31,7 +31,7 @@ _UNTYPED = {
     "q25_attention_decode_bf16": [_P, _I, _P, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _I, _P, _P],
     "q25_attention_prefill_bf16": [_P, _I, _P, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _P],
     "q25_gemm_f32": [_P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P],
-    "q25_gemm_skinny_bf16": [_P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _P, _P],
+    "q25_gemm_tcgen05_bf16": [_P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _P, _P],
     "q25_sample_rows": [_P, _LL, _I, _I, _P, _P, _P, _P, _P, _P],
     "q25_apply_penalties": [_P, _LL, _I, _I, _P, _P, _P, _P, _P, _P, _P],
 }
@@ -59,7 +59,7 @@ def load_library(name: str = "core") -> ctypes.CDLL:
 
 
 # symbols of the tensor-core kernels, which only the bfloat16 path loads (and so compiles)
-_BF16_SYMBOLS = ("q25_attention_decode", "q25_attention_prefill", "q25_gemm_skinny", "q25_gemm_chain", "q25_gemm_tcgen05",
+_BF16_SYMBOLS = ("q25_attention_decode", "q25_attention_prefill", "q25_gemm_chain", "q25_gemm_tcgen05",
                  "q25_rope_angles")
 
 
@@ -346,7 +346,11 @@ def gemm_f32(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out
 
 
 SKINNY_STORE, SKINNY_BIAS, SKINNY_F32, SKINNY_SWIGLU, SKINNY_RESIDUAL = 0, 1, 2, 3, 4
-SKINNY_MAX_ROWS = 16
+# Rows the weight-streaming kernel takes: the 8 batch columns of one m16n8k16 MMA.  A variant with two
+# column tiles ran 9 to 16 rows; measured against the library path on B200 it lost at every size (a
+# decode step of 9 / 12 / 16 requests at the 3B sizes 2.64 / 2.66 / 2.65 ms against 2.43 / 2.55 / 2.59,
+# 14 layers of the 7B sizes 2.55 / 2.61 / 2.75 against 1.92 / 2.02 / 2.02 ms) and is gone.
+SKINNY_MAX_ROWS = 8
 _error_flags: Dict[torch.device, torch.Tensor] = {}
 
 
@@ -365,20 +369,18 @@ def gemm_skinny_supports(x: torch.Tensor, w: torch.Tensor) -> bool:
 
 
 def gemm_skinny(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor, epilogue: int) -> None:
-    """out = x . w^T for at most 16 rows of x, streaming the weights once (bfloat16).
+    """out = x . w^T for at most 8 rows of x, streaming the weights once (bfloat16).
     ``epilogue``: SKINNY_STORE, SKINNY_BIAS (float32 bias), SKINNY_F32 (float32 out),
     SKINNY_SWIGLU (w rows are groups of 8 gate + 8 up features; out has half as many columns)
-    or SKINNY_RESIDUAL (out is float32 and the product is added into it)."""
+    or SKINNY_RESIDUAL (out is float32 and the product is added into it).  Runs as an operation
+    of the chain kernel (``csrc/gemm_chain.cu``): at once and alone, or, between ``chain_begin``
+    and ``chain_end``, together with the products around it."""
     m, k = x.shape
     n = w.shape[0]
     if not gemm_skinny_supports(x, w) or w.shape[1] != k or not w.is_contiguous():
         raise KernelError(f"gemm_skinny: unsupported operands {tuple(x.shape)} {x.dtype} x {tuple(w.shape)} {w.dtype}")
     _skinny_out(out, m, n, epilogue, "gemm_skinny")
-    if _chain is not None and _chain_add(x, None, 0.0, w, bias, out, epilogue):
-        return
-    _check(_fn("q25_gemm_skinny_bf16", _UNTYPED["q25_gemm_skinny_bf16"])(
-        w.data_ptr(), x.data_ptr(), x.stride(0), _ptr(bias), out.data_ptr(), out.stride(0), m, n, k, int(epilogue),
-        error_flag(x.device).data_ptr(), _stream()), "gemm_skinny")
+    _chain_add(x, None, 0.0, w, bias, out, epilogue)
 
 
 def _skinny_out(out: torch.Tensor, m: int, n: int, epilogue: int, what: str) -> None:
@@ -386,38 +388,37 @@ def _skinny_out(out: torch.Tensor, m: int, n: int, epilogue: int, what: str) -> 
     want = torch.float32 if epilogue in (SKINNY_F32, SKINNY_RESIDUAL) else torch.bfloat16
     if out.shape != (m, cols) or out.dtype != want or out.stride(1) != 1:
         raise KernelError(f"{what}: output must be [{m}, {cols}] {want}")
+    if epilogue == SKINNY_SWIGLU and n % 16:
+        raise KernelError(f"{what}: the SwiGLU epilogue needs groups of 8 gate and 8 up rows, got {n} rows")
 
 
 def gemm_skinny_norm_supports(x: torch.Tensor, w: torch.Tensor) -> bool:
     """Whether ``gemm_skinny_norm`` takes the float32 rows ``x`` (the residual stream) and ``w``."""
     return (x.dtype == torch.float32 and w.dtype == torch.bfloat16 and x.dim() == 2 and x.stride(1) == 1
-            and x.stride(0) % 4 == 0 and x.data_ptr() % 16 == 0 and w.is_contiguous()
-            and bool(_fn("q25_gemm_skinny_resident", [_I, _I])(x.shape[0], w.shape[1])))
+            and 1 <= x.shape[0] <= SKINNY_MAX_ROWS and w.shape[1] % 32 == 0
+            and x.stride(0) % 4 == 0 and x.data_ptr() % 16 == 0 and w.is_contiguous())
 
 
 def gemm_skinny_norm(x: torch.Tensor, norm_weight: torch.Tensor, eps: float, w: torch.Tensor,
                      bias: Optional[torch.Tensor], out: torch.Tensor, epilogue: int) -> None:
     """out = (rmsnorm(x) * norm_weight) . w^T with the normalisation done inside the kernel;
-    x is float32 [M <= 16, K], everything else as for ``gemm_skinny``."""
+    x is float32 [M <= 8, K], everything else as for ``gemm_skinny``."""
     m, k = x.shape
     n = w.shape[0]
     if not gemm_skinny_norm_supports(x, w) or w.shape[1] != k:
         raise KernelError(f"gemm_skinny_norm: unsupported operands {tuple(x.shape)} {x.dtype} x {tuple(w.shape)} {w.dtype}")
     _dev(norm_weight, torch.float32, "gemm_skinny_norm norm weight")
     _skinny_out(out, m, n, epilogue, "gemm_skinny_norm")
-    if _chain is not None and _chain_add(x, norm_weight, eps, w, bias, out, epilogue):
-        return
-    _check(_fn("q25_gemm_skinny_norm_bf16", [_P, _P, _I, _P, _F, _P, _P, _I, _I, _I, _I, _I, _P, _P])(
-        w.data_ptr(), x.data_ptr(), x.stride(0), norm_weight.data_ptr(), float(eps), _ptr(bias), out.data_ptr(),
-        out.stride(0), m, n, k, int(epilogue), error_flag(x.device).data_ptr(), _stream()), "gemm_skinny_norm")
+    _chain_add(x, norm_weight, eps, w, bias, out, epilogue)
 
 
 # ---- chains of weight-streaming products -------------------------------------------------------
-# Between ``chain_begin`` and ``chain_end`` the weight-streaming products are not launched one by
-# one: they wait in a list, and the list runs as ONE persistent kernel (``csrc/gemm_chain.cu``) as
-# soon as any other kernel of this module is asked for, so that the order of all kernels is the
-# order of the calls.  Only kernels of this module may be launched meanwhile; whoever runs a
-# library operator on the stream in between calls ``chain_flush`` first.
+# Every weight-streaming product is an operation of the chain kernel (``csrc/gemm_chain.cu``).  Outside
+# ``chain_begin`` / ``chain_end`` each runs at once as a chain of one.  Between them the products are
+# not launched one by one: they wait in a list, and the list runs as ONE persistent kernel as soon
+# as any other kernel of this module is asked for, so that the order of all kernels is the order of
+# the calls.  Only kernels of this module may be launched meanwhile; whoever runs a library operator
+# on the stream in between calls ``chain_flush`` first.
 
 
 class _ChainOpDesc(ctypes.Structure):
@@ -429,22 +430,26 @@ class _ChainOpDesc(ctypes.Structure):
 CHAIN_MAX_OPS = 8
 _chain_base = 0                           # value of the barrier counter when the next chain kernel begins
 _CHAIN_SAFE = {"q25_gemm_chain_bf16", "q25_gemm_chain_scratch_floats", "q25_gemm_chain_available", "q25_gemm_chain_desc_bytes",
-               "q25_gemm_chain_grid", "q25_sm_count", "q25_gemm_skinny_resident", "q25_gemm_skinny_bf16",
-               "q25_gemm_skinny_norm_bf16"}
-_chain: Optional[list] = None             # the waiting products: (description, tensors kept alive, replay as one kernel)
+               "q25_gemm_chain_grid", "q25_sm_count"}
+_chain: Optional[list] = None             # the waiting products: (description, tensors kept alive)
 _chain_state: Dict[torch.device, tuple] = {}
 _chain_scratch: Dict[torch.device, list] = {}
 
 
+_chain_ok: Optional[bool] = None
+
+
 def chain_available() -> bool:
-    """Whether chains can run here: a CUDA device that holds the kernel's whole grid at once."""
-    if not torch.cuda.is_available():
-        return False
-    if not _fn("q25_gemm_chain_available", [])():
-        return False
-    if _fn("q25_gemm_chain_desc_bytes", [])() != ctypes.sizeof(_ChainOpDesc):
-        raise KernelError("gemm_chain: the operation description here and in the library differ in layout")
-    return True
+    """Whether the chain kernel can run here: a CUDA device that holds its whole grid at once."""
+    global _chain_ok
+    if _chain_ok is None:
+        if not torch.cuda.is_available():
+            return False
+        ok = bool(_fn("q25_gemm_chain_available", [])())
+        if ok and _fn("q25_gemm_chain_desc_bytes", [])() != ctypes.sizeof(_ChainOpDesc):
+            raise KernelError("gemm_chain: the operation description here and in the library differ in layout")
+        _chain_ok = ok
+    return _chain_ok
 
 
 def chain_begin() -> bool:
@@ -473,45 +478,48 @@ def chain_end() -> None:
         _chain = None
 
 
-def _chain_add(x, norm_weight, eps, w, bias, out, epilogue) -> bool:
+def _chain_add(x, norm_weight, eps, w, bias, out, epilogue) -> None:
+    if not chain_available():
+        raise KernelError("the weight-streaming kernel needs a device that holds its whole grid at once (one CTA per SM)")
     desc = _ChainOpDesc(W=w.data_ptr(), X=x.data_ptr(), norm_w=_ptr(norm_weight), bias=_ptr(bias), out=out.data_ptr(),
                         ldx=x.stride(0), ldo=out.stride(0), M=x.shape[0], N=w.shape[0], K=w.shape[1], epi=int(epilogue),
                         norm=0 if norm_weight is None else 1, eps=float(eps))
-    if norm_weight is None:
-        alone = lambda: gemm_skinny(x, w, bias, out, int(epilogue))
-    else:
-        alone = lambda: gemm_skinny_norm(x, norm_weight, float(eps), w, bias, out, int(epilogue))
-    _chain.append((desc, (x, norm_weight, w, bias, out), alone))
+    entry = (desc, (x, norm_weight, w, bias, out))
+    if _chain is None:
+        _chain_launch([entry])                # nobody is gathering: a chain of one
+        return
+    _chain.append(entry)
     if len(_chain) == CHAIN_MAX_OPS:
         chain_flush()
-    return True
+
+
+def _chain_launch(waiting) -> None:
+    global _chain_base
+    device = next(t for t in waiting[0][1] if t is not None).device
+    ops = (_ChainOpDesc * len(waiting))(*[w_[0] for w_ in waiting])
+    need = _fn("q25_gemm_chain_scratch_floats", [_P, _I])
+    need.restype = ctypes.c_longlong
+    floats = need(ctypes.cast(ops, _P), len(waiting))
+    if floats < 0:
+        raise KernelError("gemm_chain: a product of the chain cannot be cut")
+    held = _chain_scratch.setdefault(device, [])       # never freed or moved: captured graphs keep the addresses
+    if not held or held[-1].numel() < max(floats, 1):
+        held.append(torch.empty(max(floats, 1), dtype=torch.float32, device=device))
+    counters, barrier = _chain_buffers(device)
+    _check(_fn("q25_gemm_chain_bf16", [_P, _I, _P, _P, _P, ctypes.c_uint, _P, _P])(
+        ctypes.cast(ops, _P), len(waiting), held[-1].data_ptr(), counters.data_ptr(), barrier.data_ptr(),
+        _chain_base, error_flag(device).data_ptr(), _stream()), "gemm_chain")
+    _chain_base = (_chain_base + (len(waiting) - 1) * chain_grid()) & 0xFFFFFFFF
 
 
 def chain_flush() -> None:
-    """Runs the products that wait, in order, as one kernel (a single one runs as itself)."""
-    global _chain, _chain_base
+    """Runs the products that wait, in order, as one kernel."""
+    global _chain
     if not _chain:
         return
-    waiting, _chain = _chain, None            # the launches below must not gather again
+    waiting, _chain = _chain, None            # the launch below must not gather again
     try:
-        if len(waiting) == 1:
-            waiting[0][2]()                       # the operation's own kernel
-            return
-        device = next(t for t in waiting[0][1] if t is not None).device
-        ops = (_ChainOpDesc * len(waiting))(*[w_[0] for w_ in waiting])
-        need = _fn("q25_gemm_chain_scratch_floats", [_P, _I])
-        need.restype = ctypes.c_longlong
-        floats = need(ctypes.cast(ops, _P), len(waiting))
-        if floats < 0:
-            raise KernelError("gemm_chain: a product of the chain cannot be cut")
-        held = _chain_scratch.setdefault(device, [])       # never freed or moved: captured graphs keep the addresses
-        if not held or held[-1].numel() < max(floats, 1):
-            held.append(torch.empty(max(floats, 1), dtype=torch.float32, device=device))
-        counters, barrier = _chain_buffers(device)
-        _check(_fn("q25_gemm_chain_bf16", [_P, _I, _P, _P, _P, ctypes.c_uint, _P, _P])(
-            ctypes.cast(ops, _P), len(waiting), held[-1].data_ptr(), counters.data_ptr(), barrier.data_ptr(),
-            _chain_base, error_flag(device).data_ptr(), _stream()), "gemm_chain")
-        _chain_base = (_chain_base + (len(waiting) - 1) * chain_grid()) & 0xFFFFFFFF
+        _chain_launch(waiting)
     finally:
         _chain = []
 
@@ -531,7 +539,7 @@ def gemm_tcgen05(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor],
     if not gemm_tcgen05_supports(x, w) or w.shape[1] != k:
         raise KernelError(f"gemm_tcgen05: unsupported operands {tuple(x.shape)} {x.dtype} x {tuple(w.shape)} {w.dtype}")
     _skinny_out(out, m, n, epilogue, "gemm_tcgen05")
-    _check(_fn("q25_gemm_tcgen05_bf16", _UNTYPED["q25_gemm_skinny_bf16"])(
+    _check(_fn("q25_gemm_tcgen05_bf16", _UNTYPED["q25_gemm_tcgen05_bf16"])(
         w.data_ptr(), x.data_ptr(), x.stride(0), _ptr(bias), out.data_ptr(), out.stride(0), m, n, k, int(epilogue),
         error_flag(x.device).data_ptr(), _stream()), "gemm_tcgen05")
 

@@ -2,16 +2,17 @@
 
 * float32: the engine's own FMA kernel (``csrc/gemm_f32.cu``), whose per-element summation
   order is fixed, so results do not depend on the batch.  No library, no TF32.
-* bfloat16, at most 16 rows (decode steps): the engine's weight-streaming kernel
-  (``csrc/gemm_skinny.cu``).  It can normalise its input on the fly (a ``DeferredNorm``)
+* bfloat16, at most 8 rows (decode steps): the engine's weight-streaming kernel
+  (``csrc/gemm_chain.cu``).  It can normalise its input on the fly (a ``DeferredNorm``)
   and add its result into the float32 residual stream, which removes the norm kernels and
-  the separate residual additions from a decode step.
+  the separate residual additions from a decode step, and it runs the products of a step
+  that follow one another as operations of one launch.
 * bfloat16, 128 rows or more (prefill): the engine's tcgen05 product
   (``csrc/gemm_tcgen05.cu``: TMA loads, accumulators in tensor memory) with the same
   epilogues, or the library product (cuBLAS through ``torch.mm`` / ``torch.addmm``), which the
   reference's engine uses for every projection (``nn.Linear``,
   src/qwen25vl_lite/text.py:61-63,80-83; src/qwen25vl_lite/model.py:84); see ``use_tcgen05``.
-  Batches of 17 to 127 rows (but for the largest gate/up products) and operands the tcgen05
+  Batches of 9 to 127 rows (but for the largest gate/up products) and operands the tcgen05
   kernel refuses (K not a multiple of 8, unaligned rows) go to the library.
 """
 
@@ -23,13 +24,13 @@ import torch
 
 from . import kernels
 
-# The tcgen05 kernel works in tiles of 128 rows; with fewer rows (decode batches of 17 to 127
+# The tcgen05 kernel works in tiles of 128 rows; with fewer rows (decode batches of 9 to 127
 # requests) the product is a stream of the weights, and it takes only the large ones (see below).
 TCGEN05_MIN_ROWS = 128
 
 
 def use_tcgen05(x: torch.Tensor, w: torch.Tensor, fused_epilogue: bool = False) -> bool:
-    """Which kernel takes a product of more than 16 rows.  Measured on B200:
+    """Which kernel takes a product of more than 8 rows.  Measured on B200:
 
     * 2,048 rows (prefill, 3B sizes): the engine's tcgen05 kernel (pairs of CTAs from 256 rows on)
       reaches 1.22 PFLOP/s on the wide products where cuBLAS reaches 1.46-1.48 (at the 7B sizes
@@ -37,14 +38,14 @@ def use_tcgen05(x: torch.Tensor, w: torch.Tensor, fused_epilogue: bool = False) 
       SMs) 0.64-0.79 against 1.2.  So it takes the products where its fused epilogue saves a kernel
       and a round trip through memory (gate_up with SwiGLU: about 150 us against 125 + 75 us), and
       the library the others;
-    * 17 to 127 rows (decode steps of that many requests): the products are streams of the weights.
+    * 9 to 127 rows (decode steps of that many requests): the products are streams of the weights.
       One CTA per SM takes one tile of all rows x ``bn`` features, ``bn`` picked so that the tiles
       fill the SMs once; the stream then runs at the copy bandwidth, but launch, the first trip to
       memory and the epilogue (about 8 us together) are not hidden behind anything, where the
       library's smaller tiles overlap one another (3 us).  With the SwiGLU epilogue fused, against
       library product + SiLU-mul kernel: 23 against 19 to 23 us at the 3B sizes (45 M weights),
       53 against 51 / 54 / 58 us at 32 / 64 / 98 rows at 7B (136 M), 94 to 98 against 101 to 111 us
-      at 32B (283 M).  So it takes gate_up from 64 rows at 2**27 weights and from 17 rows at 2**28.
+      at 32B (283 M).  So it takes gate_up from 64 rows at 2**27 weights and from 9 rows at 2**28.
       A stream-K variant (units of (tile, K block) dealt evenly to all SMs, segment sums handed
       between CTAs in float and added in K order) was built and measured too: 12 / 9 / 26 / 18 us
       for qkv / o / gate_up / down at 17 rows of the 3B sizes against cuBLAS's 5 / 5 / 16 / 17 us.
