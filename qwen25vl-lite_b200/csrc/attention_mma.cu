@@ -279,8 +279,9 @@ __global__ void rope_angles_kernel(const int* __restrict__ positions, int n_toke
   out[idx] = make_float2(c, sn);
 }
 
-// The fused decode kernel: 8 warps, a warp's tile is 16 keys = one page look-up, made an iteration
-// ahead, 3 stages of tiles per warp (210 KB of shared memory at head size 128).  A shape without a
+// The fused decode kernel: 8 warps (4 where that lets all CTAs run at once, see launch_decode_fused),
+// a warp's tile is 16 keys = one page look-up, made an iteration ahead, 3 stages of tiles per warp
+// (210 KB of shared memory at head size 128 with 8 warps).  A shape without a
 // loop (a 32-key tile per warp, all asked for at once) was no faster where it applies (at most 256
 // keys per CTA) and is not kept.
 template <int D, int WARPS, int BN, int STAGES>
@@ -304,6 +305,13 @@ static int launch_decode_fused_shape(const AttnArgs& a, const RopeArgs& r, int n
 
 template <int D>
 static int launch_decode_fused(const AttnArgs& a, const RopeArgs& r, int n_items, cudaStream_t s) {
+  // A CTA of 8 warps has its SM to itself.  Between one and two CTAs per SM, CTAs of 4 warps (half
+  // the shared memory, two to an SM) all run at once instead of in two waves: 128 requests on 2 kv
+  // heads, 2,048 keys each: 57 -> 51 us.  With still more CTAs the waves of 8 warps are faster again
+  // (96 requests on 4 kv heads, 2,560 keys: 98 against 104 us).
+  const long long ctas = (long long)n_items * a.nkv * a.n_splits;
+  const int sms = device_sm_count();
+  if (ctas > sms && ctas <= 2 * sms) return launch_decode_fused_shape<D, 4, 16, 3>(a, r, n_items, s);
   return launch_decode_fused_shape<D, 8, 16, 3>(a, r, n_items, s);
 }
 
