@@ -167,10 +167,7 @@ class LLMEngine:
         if len(ids) > self.ecfg.max_model_len:
             raise ValueError(f"prompt of {len(ids)} tokens exceeds max_model_len {self.ecfg.max_model_len}")
         if image_spans is not None and positions is None:
-            encoding = getattr(self.runner, "position", None)
-            if not hasattr(encoding, "prompt_positions"):
-                raise ValueError("image_spans given, but the model's position encoding does not place image runs")
-            positions = encoding.prompt_positions(len(ids), image_spans)
+            positions = self.runner.position.prompt_positions(len(ids), image_spans)
         if positions is not None:
             positions = np.asarray(positions, dtype=np.int64)
             if positions.ndim != 2 or positions.shape[1] != len(ids):

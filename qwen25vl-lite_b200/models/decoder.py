@@ -75,7 +75,7 @@ class DecoderModel:
 
     def planning_parts(self) -> List[parts.Part]:
         """The parts whose kernels read work lists that the step function packs (``plan_step``)."""
-        return [part for _, part in self._named_parts if hasattr(part, "plan_step")]
+        return [part for _, part in self._named_parts if part.plan_key() is not None]
 
     # ---- weights -----------------------------------------------------------------------
     def expected_tensors(self) -> Dict[str, parts.TensorSpec]:
@@ -139,5 +139,5 @@ class DecoderModel:
         # normalise inside its product then gets the norm handed on instead of its result
         rows = None if getattr(ctx, "logits_every_row", False) else ctx.logit_rows
         h = self.final_norm.forward(ctx, x, pending, rows=rows,
-                                    defer=rows is None and getattr(self.head, "accepts_deferred_norm", False))
+                                    defer=rows is None and self.head.accepts_deferred_norm)
         return self.head.forward(ctx, h)

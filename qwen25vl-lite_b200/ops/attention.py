@@ -81,7 +81,7 @@ def attend(ctx, plan, qkv, kv, position, nq: int, nkv: int, head_dim: int, windo
     for empty lists).  Returns [N, nq * D]."""
     window = int(window or 0)
     group = nq // nkv
-    tables = position.rope_tables() if hasattr(position, "rope_tables") else None
+    tables = position.rope_tables()
     decode_items = plan.get("decode_items")
     if (store and tables is not None and decode_items is not None and decode_items.shape[0] == ctx.n_seqs
             and plan.get("tiles64") is None

@@ -50,6 +50,11 @@ class StateNeed:
 
 
 class Part:
+    # What a part may declare about itself (class attributes); the defaults promise nothing.
+    graph_safe = False              # forward is a fixed sequence of this engine's kernels: a step may be captured
+    accepts_residual = False        # forward takes ``residual=`` and may add its result into the float32 stream
+    accepts_deferred_norm = False   # forward takes an ``ops.linear.DeferredNorm`` to normalise inside its first product
+
     def tensor_specs(self) -> Sequence[TensorSpec]:
         return ()
 
@@ -68,6 +73,17 @@ class Part:
 
     def receive(self, tensors: Dict[str, torch.Tensor]) -> None:
         pass
+
+    # Work lists for a part's kernels, built per step on the host and packed into the step's one
+    # transfer by the step function: a part that wants some returns a key from ``plan_key`` (parts
+    # with equal keys share one plan) and int arrays by name from ``plan_step(host)``, ``host``
+    # being the step's shape (``engine.runner.HostStep``); it finds their device copies under
+    # ``ctx.plan(self)``.  The default asks for nothing.
+    def plan_key(self):
+        return None
+
+    def plan_step(self, host) -> Dict[str, object]:
+        return {}
 
 
 class Norm(Part):
@@ -96,10 +112,12 @@ class PositionEncoding(Part):
     ``default_is_linear``: set True when ``default_positions`` is ``start + offset + i`` on every
     axis, which lets the step function fill a whole batch of single tokens at once.
     ``rotate_and_store(ctx, qkv, ...)``: encode q and k in place and write k, v to the pages.
-    Optional ``rope_tables() -> (inv_freq float32 [D/2], axis int32 [D/2])``: a rotary encoding
-    (channel j turns by ``position[axis[j]] * inv_freq[j]``, any number of axes) that lets the
-    fused decode attention kernel do the rotation itself.
-    Optional ``prompt_positions(num_tokens, image_spans)``: positions of a prompt with image runs.
+    ``rope_tables() -> (inv_freq float32 [D/2], axis int32 [D/2])`` or None: a rotary encoding
+    (channel j turns by ``position[axis[j]] * inv_freq[j]``, any number of axes) hands out its
+    tables, which lets the fused decode attention kernel do the rotation itself; None (the default)
+    sends every step through ``rotate_and_store``.
+    ``prompt_positions(num_tokens, image_spans)``: positions of a prompt with image runs; the
+    default refuses (an encoding that does not place images).
     """
 
     axes = 1
@@ -115,6 +133,12 @@ class PositionEncoding(Part):
 
     def rotate_and_store(self, ctx, qkv, nq, nkv, head_dim, kv):
         raise NotImplementedError
+
+    def rope_tables(self):
+        return None
+
+    def prompt_positions(self, num_tokens: int, image_spans):
+        raise ValueError("image_spans given, but the model's position encoding does not place image runs")
 
 
 class Mixer(Part):

@@ -16,12 +16,12 @@ from .base import Block, register_block
 class PreNormResidualBlock(Block):
     def forward(self, ctx, x, pending, stop):
         mixer, ffn = self.mixer, self.feed_forward
-        h = self.norms[0].forward(ctx, x, pending, defer=getattr(mixer, "accepts_deferred_norm", False))
-        if getattr(mixer, "accepts_residual", False):
+        h = self.norms[0].forward(ctx, x, pending, defer=mixer.accepts_deferred_norm)
+        if mixer.accepts_residual:
             mixed = mixer.forward(ctx, h, stop, residual=x)
         else:
             mixed = mixer.forward(ctx, h, stop)
-        h = self.norms[1].forward(ctx, x, mixed, defer=getattr(ffn, "accepts_deferred_norm", False))
-        if getattr(ffn, "accepts_residual", False):
+        h = self.norms[1].forward(ctx, x, mixed, defer=ffn.accepts_deferred_norm)
+        if ffn.accepts_residual:
             return ffn.forward(ctx, h, residual=x)
         return ffn.forward(ctx, h)
