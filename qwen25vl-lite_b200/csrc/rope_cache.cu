@@ -49,7 +49,7 @@ __global__ void rope_store_kernel(T* __restrict__ qkv, const int* __restrict__ p
                                   const float* __restrict__ inv_freq, const int* __restrict__ axis,
                                   T* __restrict__ kpages, T* __restrict__ vpages,
                                   const int* __restrict__ kv_slot, int nq, int nkv, int d, int page_size,
-                                  int rotate, int store) {
+                                  int rotate, int store, const float2* __restrict__ angles) {
   pdl_trigger();
   pdl_wait();
   extern __shared__ float2 cs[];                       // [d / 2] (cos, sin)
@@ -61,6 +61,10 @@ __global__ void rope_store_kernel(T* __restrict__ qkv, const int* __restrict__ p
   const int off = slot >= 0 ? slot % page_size : 0;
   if (rotate) {
     for (int j = threadIdx.x; j < half; j += blockDim.x) {
+      if (angles) {                                    // the step's (cos, sin), computed once for all its layers
+        cs[j] = angles[(size_t)token * half + j];
+        continue;
+      }
       const float p = (float)pos[(size_t)axis[j] * n_tokens + token];
       float s, c;
       sincosf(p * inv_freq[j], &s, &c);
@@ -105,19 +109,22 @@ __global__ void rope_store_kernel(T* __restrict__ qkv, const int* __restrict__ p
 template <typename T>
 static int rope_store(void* qkv, const int* pos, int n, const float* inv_freq, const int* axis, void* kpages,
                       void* vpages, const int* kv_slot, int nq, int nkv, int d, int page_size, int rotate, int store,
-                      void* stream) {
+                      const void* angles, void* stream) {
   if (n <= 0) return 0;
   if (d % 16 || (((uintptr_t)qkv | (uintptr_t)kpages | (uintptr_t)vpages) & 15)) return (int)cudaErrorInvalidValue;
   launch(rope_store_kernel<T>, dim3(n), dim3(128), (size_t)(d / 2) * sizeof(float2), (cudaStream_t)stream, (T*)qkv, pos, n, inv_freq, axis, (T*)kpages, (T*)vpages,
-                                                            kv_slot, nq, nkv, d, page_size, rotate, store);
+                                                            kv_slot, nq, nkv, d, page_size, rotate, store, (const float2*)angles);
   return launch_status();
 }
 
+// angles: float2 [n, d / 2] (cos, sin) of every token's rotary angles, or null to compute them here.
 Q25_EXPORT int q25_rope_store_f32(void* qkv, const int* pos, int n, const float* inv, const int* axis, void* kp, void* vp,
-                                  const int* slot, int nq, int nkv, int d, int ps, int rotate, int store, void* s) {
-  return rope_store<float>(qkv, pos, n, inv, axis, kp, vp, slot, nq, nkv, d, ps, rotate, store, s);
+                                  const int* slot, int nq, int nkv, int d, int ps, int rotate, int store, const void* angles,
+                                  void* s) {
+  return rope_store<float>(qkv, pos, n, inv, axis, kp, vp, slot, nq, nkv, d, ps, rotate, store, angles, s);
 }
 Q25_EXPORT int q25_rope_store_bf16(void* qkv, const int* pos, int n, const float* inv, const int* axis, void* kp, void* vp,
-                                   const int* slot, int nq, int nkv, int d, int ps, int rotate, int store, void* s) {
-  return rope_store<bf16>(qkv, pos, n, inv, axis, kp, vp, slot, nq, nkv, d, ps, rotate, store, s);
+                                   const int* slot, int nq, int nkv, int d, int ps, int rotate, int store, const void* angles,
+                                   void* s) {
+  return rope_store<bf16>(qkv, pos, n, inv, axis, kp, vp, slot, nq, nkv, d, ps, rotate, store, angles, s);
 }

@@ -24,7 +24,7 @@ _SIGNATURES = {
     "q25_embed_gather": [_P, _P, _P, _I, _I, _I, _P],
     "q25_add_rmsnorm": [_P, _P, _P, _F, _P, _P, _I, _I, _P],
     "q25_silu_mul": [_P, _P, _I, _I, _I, _P],
-    "q25_rope_store": [_P, _P, _I, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P],
+    "q25_rope_store": [_P, _P, _I, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P, _P],
     "q25_paged_attention_generic": [_P, _I, _P, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _P],
 }
 _UNTYPED = {
@@ -181,15 +181,21 @@ def silu_mul(gate_up: torch.Tensor, out: torch.Tensor, paired: bool = False) -> 
 
 def rope_store(qkv: torch.Tensor, positions: Optional[torch.Tensor], inv_freq: Optional[torch.Tensor],
                axis: Optional[torch.Tensor], k_pages: Optional[torch.Tensor], v_pages: Optional[torch.Tensor],
-               kv_slot: Optional[torch.Tensor], nq: int, nkv: int, head_dim: int, page_size: int) -> None:
+               kv_slot: Optional[torch.Tensor], nq: int, nkv: int, head_dim: int, page_size: int,
+               angles: Optional[torch.Tensor] = None) -> None:
     """Rotates q (in place) and k by the position encoding and writes k, v into the pages at
-    ``kv_slot``.  positions None: no rotation; pages None: nothing stored."""
+    ``kv_slot``.  positions None: no rotation; pages None: nothing stored.  ``angles``: what
+    ``rope_angles`` made of these positions (float32 [N, D/2, 2]); given, the kernel reads the
+    cosines and sines there instead of computing them again in every layer."""
     n = qkv.shape[0]
     rotate = positions is not None
     store = k_pages is not None
+    if angles is not None and (angles.dtype != torch.float32 or tuple(angles.shape) != (n, head_dim // 2, 2)
+                               or not angles.is_contiguous()):
+        raise KernelError(f"rope_store: angles must be float32 [{n}, {head_dim // 2}, 2]")
     _check(_typed("q25_rope_store", qkv.dtype)(
         qkv.data_ptr(), _ptr(positions), n, _ptr(inv_freq), _ptr(axis), _ptr(k_pages), _ptr(v_pages), _ptr(kv_slot),
-        nq, nkv, head_dim, page_size, int(rotate), int(store), _stream()), "rope_store")
+        nq, nkv, head_dim, page_size, int(rotate), int(store), _ptr(angles), _stream()), "rope_store")
 
 
 def paged_attention_generic(qkv: torch.Tensor, out: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor,

@@ -91,8 +91,16 @@ class MRope(PositionEncoding):
         """kv: the pages and slots of the stop's cache group, or None to store nothing."""
         if head_dim != self.head_dim:
             raise ValueError(f"mrope built for head size {self.head_dim}, mixer has {head_dim}")
+        angles = None
+        if ctx.dtype == torch.bfloat16:
+            # the angles are the same for every layer of the step that shares the tables: the first
+            # one to ask computes them (the 32-bit path computes them in place, in every layer)
+            key = ("rope_angles", self.inv_freq.data_ptr(), self.axis.data_ptr())
+            angles = ctx.shared.get(key)
+            if angles is None:
+                angles = ctx.shared[key] = kernels.rope_angles(ctx.positions, self.inv_freq, self.axis)
         if kv is None:
-            kernels.rope_store(qkv, ctx.positions, self.inv_freq, self.axis, None, None, None, nq, nkv, head_dim, 1)
+            kernels.rope_store(qkv, ctx.positions, self.inv_freq, self.axis, None, None, None, nq, nkv, head_dim, 1, angles)
         else:
             kernels.rope_store(qkv, ctx.positions, self.inv_freq, self.axis, kv.k_pages, kv.v_pages, kv.kv_slot,
-                               nq, nkv, head_dim, kv.page_size)
+                               nq, nkv, head_dim, kv.page_size, angles)

@@ -102,6 +102,16 @@ def test_rope_store(dtype, nq, nkv, d, section):
     for i, s in enumerate(slots):
         assert np.abs(kp[s // page_size, :, s % page_size] - k_ref[i]).max() < t
         assert np.array_equal(vp[s // page_size, :, s % page_size], x[i, nq + nkv:])
+    if dtype == torch.bfloat16:
+        # the same with the step's angles handed in (what every layer after the first does): bit for bit
+        angles = kernels.rope_angles(dev(pos.astype(np.int32)), rope.inv_freq, rope.axis)
+        qkv_b, k_b, v_b = qkv0.clone(), torch.zeros_like(k_pages), torch.zeros_like(k_pages)
+        kernels.rope_store(qkv_b, dev(pos.astype(np.int32)), rope.inv_freq, rope.axis, k_b, v_b, dev(slots),
+                           nq, nkv, d, page_size, angles)
+        assert torch.equal(qkv_b, qkv) and torch.equal(k_b, k_pages) and torch.equal(v_b, v_pages)
+        with pytest.raises(kernels.KernelError):
+            kernels.rope_store(qkv_b, dev(pos.astype(np.int32)), rope.inv_freq, rope.axis, k_b, v_b, dev(slots),
+                               nq, nkv, d, page_size, angles[:, :-1])
     # slot -1 stores nothing; no positions = no rotation
     k2 = torch.zeros_like(k_pages)
     qkv = qkv0.clone()
