@@ -442,7 +442,8 @@ def test_decode_splits_heuristic():
 
 
 @pytest.mark.parametrize("m", [1, 3, 5, 8])
-@pytest.mark.parametrize("n,k", [(100, 64), (2560, 2048), (4752, 256), (2048, 11008), (48, 8192), (600, 3584)])
+@pytest.mark.parametrize("n,k", [(100, 64), (2560, 2048), (4752, 256), (2048, 11008), (48, 8192), (600, 3584), (2560, 4096),
+                                 (5000, 6400)])
 def test_gemm_skinny(m, n, k):
     """The weight-streaming product (a chain of one) against float64 on the same bfloat16 operands,
     all epilogues, K that fits one slice and K cut into many (slices to different CTAs, slices one
@@ -524,10 +525,14 @@ def test_sample_rows_large_vocabulary():
 
 
 @pytest.mark.parametrize("m", [1, 4, 7, 8])
-@pytest.mark.parametrize("n,k", [(2560, 2048), (96, 64), (4752, 256), (1024, 2560), (320, 5120), (64, 11008)])
+@pytest.mark.parametrize("n,k", [(2560, 2048), (96, 64), (4752, 256), (1024, 2560), (320, 5120), (64, 11008), (2560, 4096),
+                                 (96, 6400)])
 def test_gemm_skinny_with_norm_inside_and_residual_epilogue(m, n, k):
     """The product that normalises its float32 input inside the kernel, and the epilogue that
-    adds into the float32 residual stream."""
+    adds into the float32 residual stream.  The shapes take every way of cutting K: one slice; x
+    whole and the CTA walking two or four slices (2560, 5120); slices to different CTAs, two of
+    them (4096 wide, 160 groups: too few for every CTA to walk), four (6400: x whole would not
+    fit) and six (11008), whose shares the owners' warps add."""
     from qwen25vl_lite.ops import kernels
     rng = np.random.default_rng(m * 77 + k)
     x = dev(rng.standard_normal((m, k)) * 3, torch.float32)
