@@ -628,6 +628,61 @@ def test_gemm_chain_runs_dependent_products_as_one_kernel(m, sizes):
     assert np.abs(f64(chained[3]) - logits).max() / np.abs(logits).max() < 3e-2
 
 
+@pytest.mark.parametrize("hidden,inter", [(2304, 1152), (4096, 3072)])
+@pytest.mark.parametrize("m", [2, 8])
+def test_gemm_chain_with_x_whole_in_shared_memory(m, hidden, inter):
+    """A layer's chain in the order a decode step runs it (o-projection, gate/up, down, the next qkv)
+    at widths between 2048 and about 6000, where the host keeps x whole in shared memory and every
+    CTA walks the K slices of its groups (at 2304: o and gate/up; at 4096: all four, the down
+    projection over its 3072 too): against the products one by one, against float64, and twice."""
+    from qwen25vl_lite.ops import kernels
+    rng = np.random.default_rng(m + hidden)
+    qkv_n = hidden + 512
+    x0 = rng.standard_normal((m, hidden)) * 2
+    attn = dev(rng.standard_normal((m, hidden)), torch.bfloat16)
+    nw = [dev(1 + 0.1 * rng.standard_normal(hidden), torch.float32) for _ in range(2)]
+    w_o = dev(rng.standard_normal((hidden, hidden)) * 0.02, torch.bfloat16)
+    w_gu = dev(rng.standard_normal((2 * inter, hidden)) * 0.03, torch.bfloat16)
+    w_down = dev(rng.standard_normal((hidden, inter)) * 0.03, torch.bfloat16)
+    w_qkv = dev(rng.standard_normal((qkv_n, hidden)) * 0.03, torch.bfloat16)
+    b_qkv = dev(rng.standard_normal(qkv_n), torch.float32)
+
+    def layer():
+        x = dev(x0, torch.float32)
+        act = torch.empty((m, inter), dtype=torch.bfloat16, device="cuda")
+        qkv = torch.empty((m, qkv_n), dtype=torch.bfloat16, device="cuda")
+        kernels.gemm_skinny(attn, w_o, None, x, kernels.SKINNY_RESIDUAL)
+        kernels.gemm_skinny_norm(x, nw[0], 1e-6, w_gu, None, act, kernels.SKINNY_SWIGLU)
+        kernels.gemm_skinny(act, w_down, None, x, kernels.SKINNY_RESIDUAL)
+        kernels.gemm_skinny_norm(x, nw[1], 1e-6, w_qkv, b_qkv, qkv, kernels.SKINNY_BIAS)
+        return x, act, qkv
+
+    one_by_one = layer()
+    runs = []
+    for _ in range(2):
+        assert kernels.chain_begin()
+        try:
+            runs.append(layer())
+        finally:
+            kernels.chain_end()
+        torch.cuda.synchronize()
+    for a, b, c in zip(one_by_one, runs[0], runs[1]):
+        assert torch.equal(b, c)
+        assert (a.float() - b.float()).abs().max().item() <= 2e-2 * a.float().abs().max().item()
+    assert int(kernels.error_flag("cuda:0")[0]) == 0
+    bf = lambda a: f64(dev(a, torch.bfloat16))
+    x1 = x0 + f64(attn) @ f64(w_o).T
+    gu = bf(plain.rms_norm(x1, f64(nw[0]), 1e-6)) @ f64(w_gu).T
+    pairs = gu.reshape(m, -1, 2, 8)
+    act = bf((plain.silu(pairs[:, :, 0]) * pairs[:, :, 1]).reshape(m, inter))
+    x2 = x1 + act @ f64(w_down).T
+    qkv = bf(plain.rms_norm(x2, f64(nw[1]), 1e-6)) @ f64(w_qkv).T + f64(b_qkv)
+    x_got, act_got, qkv_got = runs[1]
+    assert np.abs(f64(x_got) - x2).max() / np.abs(x2).max() < 2e-2
+    assert np.abs(f64(act_got) - act).max() / max(1.0, np.abs(act).max()) < 2e-2
+    assert np.abs(f64(qkv_got) - qkv).max() / np.abs(qkv).max() < 3e-2
+
+
 def test_gemm_skinny_norm_refuses_more_rows_than_it_has_columns():
     from qwen25vl_lite.ops import kernels
     x = torch.zeros((9, 2048), dtype=torch.float32, device="cuda")
