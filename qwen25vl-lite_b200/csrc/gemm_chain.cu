@@ -728,8 +728,7 @@ enum { CUT_ONLY = 0, CUT_OR_SEQ = 1, CUT_SEQ_OR_WALK = 2 };
 // Cuts one operation: K into slices of at most `limit` elements, the slices either to different
 // CTAs (their shares meet in scratch memory) or, where `ways` allows and it pays, one after the
 // other to the same CTA.  Leaves the pitch of x for the caller where x is a slice (op.xp = 0).
-static bool chain_cut(const ChainOpDesc& d, ChainOp& op, int limit, int ways) {
-  const int sms = device_sm_count();
+static bool chain_cut(const ChainOpDesc& d, ChainOp& op, int sms, int limit, int ways) {
   if (sms <= 0) return false;
   if (d.M <= 0 || d.M > GC_MAX_M || d.N <= 0 || d.K <= 0 || d.K % 32) return false;
   if (((unsigned long long)d.W & 15) || ((unsigned long long)d.X & 15)) return false;
@@ -799,10 +798,10 @@ static int chain_smem(int rows, int pitch, int x_bytes, int stash, int& n_stages
 
 // One way of cutting a whole chain: the operations into A.op, the pitch of the stages, and what x
 // needs (the most of: a slice's rows, two buffers of them, or the rows whole).
-static bool chain_cut_all(const ChainOpDesc* ops, int n_ops, int rows, int limit, int ways, ChainArgs& A, int& x_bytes, int& stash) {
+static bool chain_cut_all(const ChainOpDesc* ops, int n_ops, int sms, int rows, int limit, int ways, ChainArgs& A, int& x_bytes, int& stash) {
   int kmax = 0;
   for (int i = 0; i < n_ops; ++i) {
-    if (!chain_cut(ops[i], A.op[i], limit, ways) || A.op[i].groups > 65536) return false;
+    if (!chain_cut(ops[i], A.op[i], sms, limit, ways) || A.op[i].groups > 65536) return false;
     if (A.op[i].slice_k > kmax) kmax = A.op[i].slice_k;
   }
   A.pitch = chain_pitch(kmax);
@@ -829,7 +828,7 @@ static bool chain_cut_all(const ChainOpDesc* ops, int n_ops, int rows, int limit
 // operations' weights.  The best mark wins, except that x whole is taken from three quarters of
 // the best mark on: it has nothing to finish afterwards.  Returns the kernel's shared memory in
 // bytes, 0 if the chain cannot run.
-static int chain_plan(const ChainOpDesc* ops, int n_ops, ChainArgs& A) {
+static int chain_plan(const ChainOpDesc* ops, int n_ops, int sms, ChainArgs& A) {
   if (n_ops <= 0 || n_ops > GC_MAX_OPS) return 0;
   int whole = 0;
   for (int i = 0; i < n_ops; ++i)
@@ -837,27 +836,30 @@ static int chain_plan(const ChainOpDesc* ops, int n_ops, ChainArgs& A) {
   const int rows = GC_MAX_M;                     // shared memory is laid out for a full tile of rows
   double mark[3] = {-1.0, -1.0, -1.0};
   int limit_of[3] = {0, 0, 0}, x_bytes, stash, x_off;
-  for (int ways = CUT_ONLY; ways <= CUT_SEQ_OR_WALK; ++ways)
-    for (int limit = GC_SLICE_K; limit >= 1152 && limit >= whole; limit -= 32) {
-      if (!chain_cut_all(ops, n_ops, rows, limit, ways, A, x_bytes, stash)) continue;
-      chain_smem(rows, A.pitch, x_bytes, 0, A.n_stages, x_off, A.stash_off);
-      if (A.n_stages < 2) continue;
-      bool short_rows = false;
-      for (int i = 0; i < n_ops; ++i) short_rows |= A.op[i].slices > 1 && A.op[i].slice_k < 1152;
-      if (short_rows) continue;
-      double sum = 0.0, weights = 0.0;
-      for (int i = 0; i < n_ops; ++i) {
-        const double w = (double)ops[i].N * ops[i].K;
-        sum += w * (A.n_stages - 0.5) * A.op[i].slice_k;
-        weights += w;
+  // slices shorter than 1152 only when nothing else can be had (a K just above 2048 has to be cut
+  // in two of little more than 1024)
+  for (int shortest = 1152; shortest >= 1024 && mark[0] < 0.0 && mark[1] < 0.0 && mark[2] < 0.0; shortest -= 128)
+    for (int ways = CUT_ONLY; ways <= CUT_SEQ_OR_WALK; ++ways)
+      for (int limit = GC_SLICE_K; limit >= 1152 && limit >= whole; limit -= 32) {
+        if (!chain_cut_all(ops, n_ops, sms, rows, limit, ways, A, x_bytes, stash)) continue;
+        chain_smem(rows, A.pitch, x_bytes, 0, A.n_stages, x_off, A.stash_off);
+        if (A.n_stages < 2) continue;
+        bool short_rows = false;
+        for (int i = 0; i < n_ops; ++i) short_rows |= A.op[i].slices > 1 && A.op[i].slice_k < shortest;
+        if (short_rows) continue;
+        double sum = 0.0, weights = 0.0;
+        for (int i = 0; i < n_ops; ++i) {
+          const double w = (double)ops[i].N * ops[i].K;
+          sum += w * (A.n_stages - 0.5) * A.op[i].slice_k;
+          weights += w;
+        }
+        if (sum / weights > mark[ways] * 1.0001) { mark[ways] = sum / weights; limit_of[ways] = limit; }
       }
-      if (sum / weights > mark[ways] * 1.0001) { mark[ways] = sum / weights; limit_of[ways] = limit; }
-    }
   int ways = mark[CUT_OR_SEQ] >= mark[CUT_ONLY] ? CUT_OR_SEQ : CUT_ONLY;
   if (mark[CUT_SEQ_OR_WALK] >= 0.75 * mark[ways]) ways = CUT_SEQ_OR_WALK;
   if (mark[ways] < 0.0) return 0;
   A.n_ops = n_ops;
-  if (!chain_cut_all(ops, n_ops, rows, limit_of[ways], ways, A, x_bytes, stash)) return 0;
+  if (!chain_cut_all(ops, n_ops, sms, rows, limit_of[ways], ways, A, x_bytes, stash)) return 0;
   A.stash_bytes = stash;
   return chain_smem(rows, A.pitch, x_bytes, stash, A.n_stages, A.x_off, A.stash_off);
 }
@@ -865,7 +867,7 @@ static int chain_plan(const ChainOpDesc* ops, int n_ops, ChainArgs& A) {
 // Floats of scratch that a chain needs (0: no operation's slices meet there; -1: it cannot run).
 Q25_EXPORT long long q25_gemm_chain_scratch_floats(const ChainOpDesc* ops, int n_ops) {
   ChainArgs A;
-  if (!chain_plan(ops, n_ops, A)) return -1;
+  if (!chain_plan(ops, n_ops, device_sm_count(), A)) return -1;
   long long most = 0;
   for (int i = 0; i < n_ops; ++i) {
     const ChainOp& op = A.op[i];
@@ -875,6 +877,25 @@ Q25_EXPORT long long q25_gemm_chain_scratch_floats(const ChainOpDesc* ops, int n
     }
   }
   return most;
+}
+
+// How a chain would be cut on a device of `sms` SMs, without touching a device: for tests of the
+// planner and for whoever wants to see it.  out[i]: slices, slice_k, ctas, groups, seq, x pitch of
+// operation i; returns the kernel's shared memory in bytes (0: the chain cannot run).
+struct ChainPlanOp { int slices, slice_k, ctas, groups, seq, xp; };
+Q25_EXPORT int q25_gemm_chain_plan(const ChainOpDesc* ops, int n_ops, int sms, int* n_stages, int* pitch, int* x_off,
+                                   ChainPlanOp* out) {
+  ChainArgs A;
+  const int total = chain_plan(ops, n_ops, sms, A);
+  if (!total) return 0;
+  if (n_stages) *n_stages = A.n_stages;
+  if (pitch) *pitch = A.pitch;
+  if (x_off) *x_off = A.x_off;
+  for (int i = 0; out && i < n_ops; ++i) {
+    out[i].slices = A.op[i].slices; out[i].slice_k = A.op[i].slice_k; out[i].ctas = A.op[i].ctas;
+    out[i].groups = A.op[i].groups; out[i].seq = A.op[i].seq; out[i].xp = A.op[i].xp;
+  }
+  return total;
 }
 
 // Whether the device can hold the whole grid at once (one CTA per SM), which the barrier needs.
@@ -906,7 +927,7 @@ Q25_EXPORT int q25_gemm_chain_bf16(const ChainOpDesc* ops, int n_ops, float* scr
   if (n_ops <= 0) return 0;
   if (n_ops > GC_MAX_OPS || !counters || !barrier || !err || !q25_gemm_chain_available()) return (int)cudaErrorInvalidValue;
   ChainArgs A;
-  const int total = chain_plan(ops, n_ops, A);
+  const int total = chain_plan(ops, n_ops, device_sm_count(), A);
   if (!total || A.n_stages < 2) return (int)cudaErrorInvalidValue;
   A.scratch = scratch; A.counters = counters; A.barrier = barrier; A.barrier_base = barrier_base; A.err = err;
   for (int i = 0; i < n_ops; ++i)

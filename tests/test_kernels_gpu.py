@@ -443,7 +443,7 @@ def test_decode_splits_heuristic():
 
 @pytest.mark.parametrize("m", [1, 3, 5, 8])
 @pytest.mark.parametrize("n,k", [(100, 64), (2560, 2048), (4752, 256), (2048, 11008), (48, 8192), (600, 3584), (2560, 4096),
-                                 (5000, 6400)])
+                                 (5000, 6400), (512, 2208)])
 def test_gemm_skinny(m, n, k):
     """The weight-streaming product (a chain of one) against float64 on the same bfloat16 operands,
     all epilogues, K that fits one slice and K cut into many (slices to different CTAs, slices one
