@@ -110,20 +110,9 @@ __device__ __forceinline__ void bulk_copy_once(void* dst, const void* src, unsig
 // finished and their writes are visible, so the results are those of plain stream order; what is
 // gained is the launch latency and whatever a kernel does before its wait (the weight-streaming
 // GEMM starts fetching weights).  Before pdl_wait() a kernel may read only what no kernel ever
-// writes: weights and constant tables.  Q25VL_PDL=0 in the environment turns the attribute off.
+// writes: weights and constant tables.
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
-
-#include <stdlib.h>
-
-static inline bool pdl_enabled() {
-  static int on = -1;
-  if (on < 0) {
-    const char* v = getenv("Q25VL_PDL");
-    on = (v && v[0] == '0') ? 0 : 1;
-  }
-  return on == 1;
-}
 
 static thread_local cudaError_t q25_launch_error = cudaSuccess;
 
@@ -136,7 +125,7 @@ static inline void launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_
   cfg.stream = stream;
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  attr[0].val.programmaticStreamSerializationAllowed = pdl_enabled() ? 1 : 0;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
   const cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);

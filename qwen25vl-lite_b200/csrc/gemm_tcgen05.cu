@@ -537,7 +537,7 @@ static int launch_pair(const CUtensorMap& mx, const CUtensorMap& mw, const CUten
   attr[0].val.clusterDim.y = 1;
   attr[0].val.clusterDim.z = 1;
   attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  attr[1].val.programmaticStreamSerializationAllowed = pdl_enabled() ? 1 : 0;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 2;
   e = cudaLaunchKernelEx(&cfg, gemm_tcgen05_pair_kernel<EPI>, mx, mw, mw64, bias, out, ldo, M, N, K, err);
