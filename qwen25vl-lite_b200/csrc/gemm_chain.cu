@@ -45,10 +45,11 @@
 //     scratch memory and nothing to finish afterwards (the owners' round of a wide gate/up product,
 //     sixteen groups a CTA, cost 13 to 23 us of a layer's 130).
 //   * A stage of the ring is as long as the longest slice of the chain, and the host picks the cut
-//     (chain_plan below) that leaves the most bytes in flight: what a CTA can have on its way from
-//     memory, about two stages of 64 KB at a width of 2048, is what bounds its share of the
-//     bandwidth when few CTAs stream (a short operation, the tail of an uneven one).  At a width of
-//     3584 three stages of 60 KB fit if no operation keeps two buffers of x.
+//     (chain_plan below): x whole where it fits, else the cut that leaves the most bytes in the ring.
+//     At a width of 2048 that is two stages of 65 KB, at 3584 and 5120 four of 39 and 45 KB.  (How
+//     deep the ring is matters little once it holds two stages: at the 7B and 32B sizes two, three
+//     and four stages gave 99 / 105 / 101 and 186 / 181 / 178 us a layer.  What costs is what stands
+//     between the operations.)
 //
 // Every wait (mbarrier or grid barrier) is bounded: when it gives up, the kernel records a code in
 // *err, stops waiting anywhere and runs to its end (its output is then invalid).
