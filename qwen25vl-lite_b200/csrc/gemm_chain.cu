@@ -42,7 +42,7 @@
 //     have counted themselves in, adds them in slice order and runs the epilogue.  Either way the
 //     result does not depend on timing.  Up to 8 rows of a width that is cut but not long (3584,
 //     5120) stay in shared memory whole, and a CTA walks the slices of its groups over them: no
-//     scratch memory and nothing to finish afterwards (the owners' round of a wide gate/up product,
+//     scratch memory and nothing to finish afterwards (the owners' pass of a wide gate/up product,
 //     sixteen groups a CTA, cost 13 to 23 us of a layer's 130).
 //   * A stage of the ring is as long as the longest slice of the chain, and the host picks the cut
 //     (chain_plan below): x whole where it fits, else the cut that leaves the most bytes in the ring.
@@ -191,7 +191,7 @@ __device__ __forceinline__ void gc_store_group(const float (&acc)[MT][4], int gr
   }
 }
 
-// One copy of the store code for the owners' round, which runs once per operation: inlined there
+// One copy of the store code for the owners' pass, which runs once per operation: inlined there
 // for every group of a batch, it is a third of the kernel's code, fetched cold every time.
 template <int MT>
 __device__ __noinline__ void gc_store_group_once(float4 a, float4 b, int grp, const ChainOp& op, bool has_old) {
@@ -201,7 +201,7 @@ __device__ __noinline__ void gc_store_group_once(float4 a, float4 b, int grp, co
   gc_store_group<MT>(acc, grp, op, has_old);
 }
 
-// The owners' round of an operation whose slices were other CTAs'.  The i-th group of list r (the
+// The owners' pass of an operation whose slices were other CTAs'.  The i-th group of list r (the
 // groups r, r + ctas, ...) is finished by the CTA of slice (i + r) mod slices, and there by MMA warp
 // (i / slices) mod 8: the warp waits (bounded) until every slice has counted the group in, adds
 // the slices' shares in slice order and runs the epilogue.  G groups at a time and J slices of each
@@ -756,7 +756,7 @@ static bool chain_cut(const ChainOpDesc& d, ChainOp& op, int sms, int limit, int
   const double busy_seq = (double)op.groups / ((double)((op.groups + seq_ctas - 1) / seq_ctas) * sms);
   // A K that is cut but not long: x whole in shared memory and every CTA walks the
   // slices of its groups, unless the groups divide so badly among the CTAs that way that the cut
-  // across CTAs, with its round of finishing, keeps a fifth more of them busy.
+  // across CTAs, with its pass of finishing, keeps a fifth more of them busy.
   if (ways >= CUT_SEQ_OR_WALK && GC_MAX_M * chain_pitch(d.K) <= GC_WALK_X_BYTES && busy_cut <= 1.2 * busy_seq) {
     op.seq = 2; op.ctas = seq_ctas; op.xp = chain_pitch(d.K);
     return true;
