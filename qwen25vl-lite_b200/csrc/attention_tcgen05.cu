@@ -22,6 +22,10 @@
 // V(t) when tile t begins and waits for them when its softmax of tile t is done, so in the steady
 // state it waits for no product and no copy.  The output accumulates in tensor memory over all
 // tiles; the exponentials use a lazy maximum (see below), so it is rescaled only rarely.
+// A step takes as long as its longest walk, so the host cuts the keys of long row tiles into parts
+// (ops/attention.py: split_keys): a CTA then walks one part and leaves its unnormalised output rows
+// with their maxima and sums in scratch memory, and attention_prefill_merge_kernel adds the parts of
+// a tile up, in the order of the parts.
 // Two CTAs fit an SM (99 KB of shared memory, 256 of the 512 tensor-memory columns each).  (Two row
 // tiles to a CTA, which halve the key and value traffic per row, were slower at every length tried:
 // 8,192 tokens 375 against 298 us.)
@@ -135,7 +139,8 @@ __global__ void __launch_bounds__(A5_THREADS, 2) attention_prefill_tcgen05_kerne
   const int work = (n_work > n_sms && n_work <= 2 * n_sms && (int)blockIdx.x >= n_sms)
                        ? n_work - 1 - ((int)blockIdx.x - n_sms) : (int)blockIdx.x;
   const int item = work / a.nkv, kvh = work - item * a.nkv;
-  const int seq = a.items[2 * item], row_tile = a.items[2 * item + 1];
+  const int seq = a.items[3 * item], row_tile = a.items[3 * item + 1], code = a.items[3 * item + 2];
+  const int n_parts = code & 15, part = (code >> 4) & 15, first_part = code >> 8;   // 1 part: the whole tile
   const int G = a.nq / a.nkv;
   const int q0 = a.cu_q[seq], q_len = a.cu_q[seq + 1] - q0, start = a.q_start_pos[seq];
   const int n_rows = q_len * G;
@@ -143,10 +148,17 @@ __global__ void __launch_bounds__(A5_THREADS, 2) attention_prefill_tcgen05_kerne
   const int* table = a.block_table + (size_t)seq * a.table_width;
   // key range of the CTA
   const int c_first = R0 / G, c_last = min(R0 + ROWS - 1, n_rows - 1) / G;
-  const int c_hi = start + c_last;
+  int c_hi = start + c_last;                               // the last key anybody of the CTA sees: nothing is loaded past it
   const int c_lo = a.window > 0 ? max(0, start + c_first - a.window + 1) : 0;
-  const int key_begin = c_lo & ~(A5_BN - 1);
-  const int n_tiles = (c_hi - key_begin) / A5_BN + 1;
+  int key_begin = c_lo & ~(A5_BN - 1);
+  int n_tiles = (c_hi - key_begin) / A5_BN + 1;
+  if (n_parts > 1) {                                       // this CTA's part of the key tiles
+    const int per = (n_tiles + n_parts - 1) / n_parts;
+    const int t0 = part * per, t1 = min(n_tiles, t0 + per);
+    if (t1 < n_tiles) c_hi = key_begin + t1 * A5_BN - 1;
+    key_begin += t0 * A5_BN;
+    n_tiles = t1 - t0;
+  }
 
   if (tid == 0) {
     mbar_init(bars->s_full, 1);
@@ -393,6 +405,22 @@ __global__ void __launch_bounds__(A5_THREADS, 2) attention_prefill_tcgen05_kerne
     }
     tc5_fence_after();
 
+    if (n_parts > 1) {
+      // a part of the keys: the sums as they are, with the maximum they were taken against and the
+      // sum of the weights, for the merge kernel
+      const size_t slot = ((size_t)(first_part + part) * a.nkv + kvh) * ROWS + tid;
+      float* po = a.part_o + slot * A5_D;
+#pragma unroll
+      for (int c = 0; c < A5_D / 32; ++c) {
+        float vals[32];
+        tc5_ld32(t_o + c * 32, vals);
+        if (!live) continue;
+#pragma unroll
+        for (int q = 0; q < 8; ++q)
+          *reinterpret_cast<float4*>(po + c * 32 + q * 4) = make_float4(vals[q * 4], vals[q * 4 + 1], vals[q * 4 + 2], vals[q * 4 + 3]);
+      }
+      if (live) *reinterpret_cast<float2*>(a.part_ml + slot * 2) = make_float2(m_used, l);
+    } else {
     const float inv = live && l > 0.f ? 1.0f / l : 0.f;
     bf16* dst = a.out + (size_t)(q0 + tok) * a.nq * A5_D + (size_t)(kvh * G + head) * A5_D;
 #pragma unroll
@@ -410,6 +438,7 @@ __global__ void __launch_bounds__(A5_THREADS, 2) attention_prefill_tcgen05_kerne
         *reinterpret_cast<uint4*>(dst + c * 32 + q * 8) = o;
       }
     }
+    }
   }
   // every thread gets here (all waits are bounded); then the tensor memory goes back
   tc5_fence_before();
@@ -420,22 +449,80 @@ __global__ void __launch_bounds__(A5_THREADS, 2) attention_prefill_tcgen05_kerne
   }
 }
 
-// items: (entry, row tile) pairs with row tiles of 128 rows; otherwise the arguments of
+// Adds up the parts of the row tiles whose keys were cut.  merges: (entry, row tile, first part,
+// parts).  The parts' maxima m_p
+// (in the units of the exponent: scaled scores times log2 e) and sums l_p give the weights
+// 2^(m_p - M), M the largest, and out = sum_p w_p O_p / sum_p w_p l_p, parts in order.  A warp takes
+// one row (a lane four of its 128 values), a block 8 rows.
+constexpr int A5_MERGE_WARPS = 8;
+__global__ void __launch_bounds__(A5_MERGE_WARPS * 32) attention_prefill_merge_kernel(AttnArgs a, const int* __restrict__ merges) {
+  pdl_trigger();
+  pdl_wait();
+  constexpr int BLOCKS_PER_TILE = A5_ROWS / A5_MERGE_WARPS;
+  const int work = blockIdx.x / BLOCKS_PER_TILE;
+  const int item = work / a.nkv, kvh = work - item * a.nkv;
+  const int seq = merges[4 * item], row_tile = merges[4 * item + 1], first_part = merges[4 * item + 2], n_parts = merges[4 * item + 3];
+  const int G = a.nq / a.nkv;
+  const int q0 = a.cu_q[seq], n_rows = (a.cu_q[seq + 1] - q0) * G;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int r = (blockIdx.x - work * BLOCKS_PER_TILE) * A5_MERGE_WARPS + warp;
+  const int R = row_tile * A5_ROWS + r;
+  if (R >= n_rows) return;
+  const int tok = R / G, head = R - tok * G;
+  const size_t slot0 = ((size_t)first_part * a.nkv + kvh) * A5_ROWS + r, slot_step = (size_t)a.nkv * A5_ROWS;
+  // lane p holds part p's (maximum, sum); every lane asks for its four values of every part at once
+  float2 ml = make_float2(-INFINITY, 0.f);
+  if (lane < n_parts) ml = __ldcg(reinterpret_cast<const float2*>(a.part_ml) + slot0 + lane * slot_step);
+  float4 o[15];
+#pragma unroll
+  for (int p = 0; p < 15; ++p)
+    if (p < n_parts) o[p] = __ldcg(reinterpret_cast<const float4*>(a.part_o + (slot0 + p * slot_step) * A5_D) + lane);
+  float M = ml.x;
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, off));
+  const float w_mine = ml.x == -INFINITY ? 0.f : exp2f(ml.x - M);      // a part whose keys the row does not see brings nothing
+  float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+  float L = 0.f;
+#pragma unroll
+  for (int p = 0; p < 15; ++p) {
+    const float w = __shfl_sync(0xffffffffu, w_mine, p), lp = __shfl_sync(0xffffffffu, ml.y, p);
+    if (p < n_parts && w > 0.f) {
+      L = fmaf(lp, w, L);
+      acc.x = fmaf(o[p].x, w, acc.x); acc.y = fmaf(o[p].y, w, acc.y); acc.z = fmaf(o[p].z, w, acc.z); acc.w = fmaf(o[p].w, w, acc.w);
+    }
+  }
+  const float inv = L > 0.f ? 1.0f / L : 0.f;
+  uint2 packed;
+  packed.x = pack_bf16(acc.x * inv, acc.y * inv);
+  packed.y = pack_bf16(acc.z * inv, acc.w * inv);
+  *reinterpret_cast<uint2*>(a.out + (size_t)(q0 + tok) * a.nq * A5_D + (size_t)(kvh * G + head) * A5_D + lane * 4) = packed;
+}
+
+// tiles: (entry, row tile, code) triples with row tiles of 128 rows (code 1: the whole tile; else
+// first part << 8 | part << 4 | parts: one of up to 15 parts of its keys); merges: (entry, row tile,
+// first part, parts) of the n_merges tiles that were cut, scratch: n_tiles * nkv * 128 * (D + 2)
+// floats when there are any; otherwise the arguments of
 // q25_attention_prefill_bf16.  Head size 128 only.  err: one int that receives a nonzero code if a
 // wait gave up.
 Q25_EXPORT int q25_attention_prefill_tcgen05_bf16(const void* qkv, int qkv_stride, void* out, const void* kp, const void* vp,
                                                   const int* bt, int tw, const int* cu_q, const int* q_start,
                                                   const int* tiles, int n_tiles, int nq, int nkv, int d, int page_size,
-                                                  int window, float scale, int* err, void* stream) {
+                                                  int window, float scale, const int* merges, int n_merges, float* scratch,
+                                                  int* err, void* stream) {
   if (n_tiles <= 0) return 0;
-  if (d != A5_D || !err) return (int)cudaErrorInvalidValue;
+  if (d != A5_D || !err || (n_merges > 0 && (!merges || !scratch || window > 0))) return (int)cudaErrorInvalidValue;
   AttnArgs a;
   int e = fill_args(a, qkv, qkv_stride, out, kp, vp, bt, tw, cu_q, q_start, tiles, nq, nkv, page_size, window, scale);
   if (e) return e;
   if (((uintptr_t)qkv & 15) || (qkv_stride % 8) || ((uintptr_t)out & 15)) return (int)cudaErrorInvalidValue;
   cudaError_t ce = cudaFuncSetAttribute(attention_prefill_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, A5_SMEM);
   if (ce != cudaSuccess) return (int)ce;
+  a.part_o = scratch;                                    // [part, kv head, row, D], then [part, kv head, row, (m, l)]
+  a.part_ml = scratch ? scratch + (size_t)n_tiles * nkv * A5_ROWS * A5_D : nullptr;
   launch(attention_prefill_tcgen05_kernel, dim3(n_tiles * nkv), dim3(A5_THREADS), (size_t)A5_SMEM, (cudaStream_t)stream, a,
          device_sm_count(), err);
+  if (n_merges > 0)
+    launch(attention_prefill_merge_kernel, dim3(n_merges * nkv * (A5_ROWS / A5_MERGE_WARPS)), dim3(A5_MERGE_WARPS * 32), 0,
+           (cudaStream_t)stream, a, merges);
   return launch_status();
 }

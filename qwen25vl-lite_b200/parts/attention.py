@@ -67,11 +67,12 @@ class GQAAttention(Mixer):
 
     def plan_key(self):
         """Mixers with equal keys read the same work lists, which are then built once a step."""
-        return ("gqa_attention", self.rows_per_token)
+        return ("gqa_attention", self.rows_per_token, self.num_kv_heads, bool(self.window))
 
     def plan_step(self, host):
         """The attention kernels' work lists for a step of this shape (int32 arrays by name)."""
-        return attention_ops.plan_step(host, self.rows_per_token)
+        places = 2 * attention_ops.kernels.sm_count() // self.num_kv_heads      # two CTAs of the tcgen05 kernel fit an SM
+        return attention_ops.plan_step(host, self.rows_per_token, self.window or 0, places)
 
     def forward(self, ctx, h, stop, residual=None):
         """Returns the update of the residual stream, or None after adding it into ``residual``."""

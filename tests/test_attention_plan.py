@@ -7,7 +7,9 @@ from types import SimpleNamespace
 import numpy as np
 import pytest
 
-from qwen25vl_lite.ops.attention import PREFILL_TILE_ROWS, plan_step
+from qwen25vl_lite.ops.attention import KEY_TILE, MAX_PARTS, plan_step
+
+PLACES = 148    # CTAs of the tcgen05 kernel at a time for one of two kv heads, on the device the engine is written for
 
 
 def host(q_lens, starts):
@@ -21,27 +23,68 @@ def test_every_row_is_in_one_tile_and_single_tokens_are_decode_items(group):
         n = int(rng.integers(1, 12))
         q_lens = [int(rng.choice([1, 1, 2, 3, 17, 64, 65, 300])) for _ in range(n)]
         starts = [int(rng.integers(0, 5000)) for _ in range(n)]
-        plan = plan_step(host(q_lens, starts), group)
+        plan = plan_step(host(q_lens, starts), group, places=PLACES)
         assert plan["decode_items"].dtype == np.int32
         assert list(plan["decode_items"]) == [i for i, q in enumerate(q_lens) if q == 1]
-        for rows in PREFILL_TILE_ROWS:
-            pairs = plan[f"tiles{rows}"].reshape(-1, 2)
-            want = {(i, t) for i, q in enumerate(q_lens) if q > 1 for t in range(-(-q * group // rows))}
-            assert len(pairs) == len(want) and {tuple(p) for p in pairs.tolist()} == want
-            # heaviest first: the keys a tile's last row sees never grow along the list
-            seen = [starts[i] + min((t + 1) * rows // group, q_lens[i]) for i, t in pairs.tolist()]
-            reach = [starts[i] + (t + 1) * rows // group for i, t in pairs.tolist()]
-            assert reach == sorted(reach, reverse=True) and all(s >= 1 for s in seen)
+        pairs = plan["tiles64"].reshape(-1, 2)
+        want = {(i, t) for i, q in enumerate(q_lens) if q > 1 for t in range(-(-q * group // 64))}
+        assert len(pairs) == len(want) and {tuple(p) for p in pairs.tolist()} == want
+        # heaviest first: the keys a tile's last row sees never grow along the list
+        reach = [starts[i] + (t + 1) * 64 // group for i, t in pairs.tolist()]
+        assert reach == sorted(reach, reverse=True)
+        # tiles of 128 rows: whole, or every part of a cut tile once
+        triples = plan["tiles128"].reshape(-1, 3).tolist()
+        want = {(i, t) for i, q in enumerate(q_lens) if q > 1 for t in range(-(-q * group // 128))}
+        assert {(i, t) for i, t, _ in triples} == want
+        whole = [(i, t) for i, t, code in triples if code == 1]
+        cut = {}
+        for i, t, code in triples:
+            if code != 1:
+                cut.setdefault((i, t), []).append(code)
+        assert len(whole) == len(set(whole)) and not set(whole) & set(cut)
+        merges = plan["merge128"].reshape(-1, 4).tolist()
+        assert {(i, t) for i, t, _, _ in merges} == set(cut)
+        taken = []
+        for i, t, first, parts in merges:
+            assert 2 <= parts <= MAX_PARTS
+            assert sorted(cut[(i, t)]) == [(first << 8) | (p << 4) | parts for p in range(parts)]
+            taken += list(range(first, first + parts))
+        assert sorted(taken) == list(range(len(taken))) and len(taken) <= len(triples)      # the scratch has a place for each
+
+
+def walks_of(plan, q_lens, starts, group):
+    """Key tiles each piece of work of the tcgen05 kernel walks, as the kernel derives them."""
+    walks = []
+    for i, t, code in plan["tiles128"].reshape(-1, 3).tolist():
+        n = (starts[i] + min((t * 128 + 127) // group, q_lens[i] - 1)) // KEY_TILE + 1
+        parts, part = code & 15, (code >> 4) & 15
+        per = -(-n // parts)
+        walks.append(min(n, (part + 1) * per) - part * per)
+    return walks
+
+
+def test_few_long_tiles_are_cut_to_fill_the_places_once():
+    q_lens, starts = [512], [3000]
+    whole = sum((3000 + min(t * 16 + 15, 511)) // KEY_TILE + 1 for t in range(32))
+    plan = plan_step(host(q_lens, starts), 8, places=PLACES)
+    walks = walks_of(plan, q_lens, starts, 8)
+    assert len(walks) > 2 * 32 and len(walks) <= PLACES                  # more pieces, one round of CTAs
+    assert min(walks) >= 1 and sum(walks) == whole and walks == sorted(walks, reverse=True)
+    assert max(walks) <= -(-55 // (len(walks) // 32)) + 1
+    # places for nothing more than the tiles, short walks, a window (a part could hold no key a row sees): whole tiles
+    for q, s, kw in (([2048], [0], {}), ([1024], [0], {}), ([512], [3000], dict(window=300)), ([512], [3000], dict(places=0))):
+        plan = plan_step(host(q, s), 8, **{**dict(places=PLACES), **kw})
+        assert plan["merge128"].size == 0 and all(code == 1 for code in plan["tiles128"].reshape(-1, 3)[:, 2])
 
 
 def test_a_group_wider_than_the_decode_kernels_rows_goes_with_the_runs():
-    plan = plan_step(host([1, 1, 5], [10, 700, 0]), 24)                 # 24 query heads per kv head: more than 16 rows
+    plan = plan_step(host([1, 1, 5], [10, 700, 0]), 24, places=PLACES)                 # 24 query heads per kv head: more than 16 rows
     assert plan["decode_items"].size == 0
     pairs = plan["tiles64"].reshape(-1, 2).tolist()
     assert sorted(pairs) == [[0, 0], [1, 0], [2, 0], [2, 1]]            # 24 rows each, 120 rows for the run of five
 
 
 def test_a_step_of_single_tokens_has_no_tiles():
-    plan = plan_step(host([1] * 9, range(9)), 8)
+    plan = plan_step(host([1] * 9, range(9)), 8, places=PLACES)
     assert list(plan["decode_items"]) == list(range(9))
     assert plan["tiles64"].size == 0 and plan["tiles128"].size == 0

@@ -307,11 +307,40 @@ def test_attention_tensor_core_kernels(nq, nkv, d, page_size, window, splits):
     assert np.abs(f64(out) - ref).max() < 3e-2
 
 
+def run_tcgen05_prefill(c, lens, q_lens, nq, nkv, d, page_size, window, shortest=None, fill=0.0):
+    """The tcgen05 prefill kernel over every run of the case: whole row tiles, or (``shortest``: key
+    tiles per part at least) with the keys of the long tiles cut into parts and merged, as the
+    engine's plan cuts them."""
+    from qwen25vl_lite.ops import kernels
+    from qwen25vl_lite.ops.attention import split_keys
+    G = nq // nkv
+    tiles = []
+    for i, n in enumerate(q_lens):
+        for t in range(-(-n * G // 128)):
+            last = min((t * 128 + 127) // G, n - 1)
+            tiles.append((i, t, (lens[i] - n + last) // 64 + 1))
+    if shortest is None:
+        work, merges = sorted(tiles, key=lambda w: -w[2]), []
+        work = [(i, t, 1) for i, t, _ in work]
+    else:
+        work, merges = split_keys(tiles, bool(window), 1 << 20, shortest=shortest, min_walk=0)
+        assert window or merges
+    out = torch.full((c["qkv"].shape[0], nq * d), fill, dtype=torch.bfloat16, device="cuda")
+    scratch = torch.full((len(work) * nkv * 128 * (d + 2),), float("nan"), device="cuda") if merges else None
+    kernels.attention_prefill_tcgen05(c["qkv"], out, c["k_pages"], c["v_pages"], c["table"], c["cu"], c["start"],
+                                      dev(np.asarray(work, np.int32)), nq, nkv, d, page_size, window or 0, d ** -0.5,
+                                      dev(np.asarray(merges, np.int32)) if merges else None, scratch)
+    return out
+
+
+@pytest.mark.parametrize("shortest", [None, 1, 3])
 @pytest.mark.parametrize("nq,nkv,page_size,window", [(16, 2, 16, None), (8, 8, 4, None), (28, 4, 16, 150), (5, 1, 32, None), (40, 8, 8, 64)])
-def test_attention_prefill_tcgen05(nq, nkv, page_size, window):
+def test_attention_prefill_tcgen05(nq, nkv, page_size, window, shortest):
     """The tcgen05 prefill attention (scores, P and outputs in tensor memory, head size 128) against
     the oracle: runs that start inside a cached prefix, runs shorter and longer than a row tile,
-    groups of 8, 1, 7 and 5 query heads, small and large pages, windows that cut the keys."""
+    groups of 8, 1, 7 and 5 query heads, small and large pages, windows that cut the keys; with
+    whole row tiles and with their keys cut into parts of one and of three key tiles at least (a
+    part of one tile lies wholly behind some rows of its row tile, which then bring nothing)."""
     from qwen25vl_lite.ops import kernels
     d = 128
     rng = np.random.default_rng(21)
@@ -325,12 +354,8 @@ def test_attention_prefill_tcgen05(nq, nkv, page_size, window):
             passed = max(0, L - ql + 1 - window) // page_size
             table[i, :passed] = table[(i + 1) % len(lens), 0]
         c["table"] = dev(table)
-    G = nq // nkv
-    tiles = [(i, t) for i, n in enumerate(q_lens) for t in range(-(-n * G // 128))]
-    out = torch.zeros((c["qkv"].shape[0], nq * d), dtype=torch.bfloat16, device="cuda")
     assert kernels.attention_tcgen05_supports(torch.bfloat16, d, page_size, c["qkv"])
-    kernels.attention_prefill_tcgen05(c["qkv"], out, c["k_pages"], c["v_pages"], c["table"], c["cu"], c["start"],
-                                      dev(np.asarray(tiles, np.int32)), nq, nkv, d, page_size, window or 0, d ** -0.5)
+    out = run_tcgen05_prefill(c, lens, q_lens, nq, nkv, d, page_size, window, shortest)
     torch.cuda.synchronize()
     assert int(kernels.error_flag("cuda:0")[0]) == 0
     ref = attention_oracle(c["dense"], window)
@@ -338,11 +363,13 @@ def test_attention_prefill_tcgen05(nq, nkv, page_size, window):
     assert not kernels.attention_tcgen05_supports(torch.bfloat16, 64, page_size)
 
 
-def test_attention_prefill_tcgen05_long_runs_repeat_exactly():
+@pytest.mark.parametrize("shortest", [None, 4])
+def test_attention_prefill_tcgen05_long_runs_repeat_exactly(shortest):
     """Many key tiles per CTA, more CTAs than the GPU holds at once, and scores that keep growing
     along the keys, so that the rows in tensor memory are rescaled again and again: against the
     oracle, and eight launches give the same bits (the rows of a CTA, the thread that issues the
-    products and the copies meet only at barriers; a missed one shows as a difference between runs)."""
+    products and the copies meet only at barriers; a missed one shows as a difference between runs).
+    The same with the keys cut into parts of four key tiles at least, up to eight parts a tile."""
     from qwen25vl_lite.ops import kernels
     nq, nkv, d, page_size = 16, 2, 128, 16
     rng = np.random.default_rng(22)
@@ -351,16 +378,7 @@ def test_attention_prefill_tcgen05_long_runs_repeat_exactly():
     # than the lazy threshold over its keys
     c = paged_case(rng, lens, q_lens, nq, nkv, d, page_size, torch.bfloat16, key_gain=lambda L: 1.0 + 5.0 * np.arange(L) / L)
     dense = c["dense"]
-    G = nq // nkv
-    tiles = [(i, t) for i, n in enumerate(q_lens) for t in range(-(-n * G // 128))]
-    tiles.sort(key=lambda it: -(lens[it[0]] - q_lens[it[0]] + (it[1] + 1) * 128 // G))
-    items = dev(np.asarray(tiles, np.int32))
-    outs = []
-    for _ in range(8):
-        out = torch.full((c["qkv"].shape[0], nq * d), 3.0, dtype=torch.bfloat16, device="cuda")
-        kernels.attention_prefill_tcgen05(c["qkv"], out, c["k_pages"], c["v_pages"], c["table"], c["cu"], c["start"],
-                                          items, nq, nkv, d, page_size, 0, d ** -0.5)
-        outs.append(out)
+    outs = [run_tcgen05_prefill(c, lens, q_lens, nq, nkv, d, page_size, None, shortest, fill=3.0) for _ in range(8)]
     torch.cuda.synchronize()
     assert int(kernels.error_flag("cuda:0")[0]) == 0
     for o in outs[1:]:
@@ -395,12 +413,14 @@ def test_tcgen05_prefill_attention_finds_a_far_key_and_the_window_edge():
     """The tcgen05 prefill kernel with one dominant key: on the edges of pages and of its 64-key
     tiles, at both ends of the keys, just inside and just outside the window; the matching query
     is the last of a run of 70 (so the key lies many tiles before the diagonal) and, in a second
-    run of the batch, a query in the middle of a row tile."""
+    run of the batch, a query in the middle of a row tile.  Without a window also with the keys cut
+    into parts of two key tiles: the key then lies in the first, a middle or the last part."""
     from qwen25vl_lite.ops import kernels
     nq, nkv, d, ps = 8, 2, 128, 16
     lens, q_lens = [700, 300], [70, 300]
-    for key, window, visible in [(0, None, True), (15, None, True), (16, None, True), (63, None, True), (64, None, True),
-                                 (351, None, True), (629, None, True), (699, None, True), (700 - 60, 60, True), (700 - 61, 60, False)]:
+    cases = [(0, None, True), (15, None, True), (16, None, True), (63, None, True), (64, None, True),
+             (351, None, True), (629, None, True), (699, None, True), (700 - 60, 60, True), (700 - 61, 60, False)]
+    for key, window, visible, shortest in [case + (None,) for case in cases] + [case + (2,) for case in cases if case[1] is None]:
         rng = np.random.default_rng(key)
         c = paged_case(rng, lens, q_lens, nq, nkv, d, ps, torch.bfloat16)
         dense = [list(t) for t in c["dense"]]
@@ -415,16 +435,12 @@ def test_tcgen05_prefill_attention_finds_a_far_key_and_the_window_edge():
         k2[100, 1] = (q2[150, 5] * 3).to(torch.bfloat16)
         c["k_pages"][int(c["table"][1, 100 // ps]), 1, 100 % ps] = k2[100, 1].cuda()
         dense[1][1] = k2
-        G = nq // nkv
-        tiles = [(i, t) for i, n in enumerate(q_lens) for t in range(-(-n * G // 128))]
-        out = torch.zeros((c["qkv"].shape[0], nq * d), dtype=torch.bfloat16, device="cuda")
-        kernels.attention_prefill_tcgen05(c["qkv"], out, c["k_pages"], c["v_pages"], c["table"], c["cu"], c["start"],
-                                          dev(np.asarray(tiles, np.int32)), nq, nkv, d, ps, window or 0, d ** -0.5)
+        out = run_tcgen05_prefill(c, lens, q_lens, nq, nkv, d, ps, window, shortest)
         torch.cuda.synchronize()
         assert int(kernels.error_flag("cuda:0")[0]) == 0
         o = f64(out)
         hit = np.abs(o[69, :d] - f64(v)[key, 0]).max() < 6e-2
-        assert hit == visible, f"key {key} window {window}: found={hit}"
+        assert hit == visible, f"key {key} window {window} parts of {shortest}: found={hit}"
         in_window = window is None or 150 - 100 < window
         hit2 = np.abs(o[70 + 150, 5 * d:6 * d] - f64(v2)[100, 1]).max() < 6e-2
         assert hit2 == in_window
