@@ -135,12 +135,22 @@ __global__ void __launch_bounds__(A5_THREADS, 2) attention_prefill_tcgen05_kerne
   // the same order: with 149 to 296 CTAs in all, CTA 148 + s therefore takes the s-th lightest piece
   // of work, so that every SM gets a heavy and a light one (2,048 tokens in 256 pieces: the busiest
   // SM has 34 key tiles instead of 61).  Larger grids are taken in order: CTAs start as others end.
-  const int n_work = gridDim.x;
-  const int work = (n_work > n_sms && n_work <= 2 * n_sms && (int)blockIdx.x >= n_sms)
-                       ? n_work - 1 - ((int)blockIdx.x - n_sms) : (int)blockIdx.x;
+  // Launched as clusters of two CTAs, a cluster takes a piece of work (in the list's order): a tile
+  // of code 2 half of its keys each, the second CTA leaving its rows in its shared memory for the
+  // first to add up; a whole tile (code 1) the first CTA alone.
+  unsigned n_rank, rank;
+  asm volatile("mov.u32 %0, %%cluster_nctarank;\n" : "=r"(n_rank));
+  asm volatile("mov.u32 %0, %%cluster_ctarank;\n" : "=r"(rank));
+  const bool pair = n_rank == 2;
+  const int n_work = pair ? (int)(gridDim.x >> 1) : (int)gridDim.x;
+  const int work = pair ? (int)(blockIdx.x >> 1)
+                        : ((n_work > n_sms && n_work <= 2 * n_sms && (int)blockIdx.x >= n_sms)
+                               ? n_work - 1 - ((int)blockIdx.x - n_sms) : (int)blockIdx.x);
   const int item = work / a.nkv, kvh = work - item * a.nkv;
   const int seq = a.items[3 * item], row_tile = a.items[3 * item + 1], code = a.items[3 * item + 2];
-  const int n_parts = code & 15, part = (code >> 4) & 15, first_part = code >> 8;   // 1 part: the whole tile
+  const int n_parts = code & 15, first_part = code >> 8;                            // 1 part: the whole tile
+  const int part = pair ? (int)rank : (code >> 4) & 15;
+  if (pair && n_parts == 1 && rank == 1) return;                                    // nothing for the second CTA
   const int G = a.nq / a.nkv;
   const int q0 = a.cu_q[seq], q_len = a.cu_q[seq + 1] - q0, start = a.q_start_pos[seq];
   const int n_rows = q_len * G;
@@ -243,6 +253,13 @@ __global__ void __launch_bounds__(A5_THREADS, 2) attention_prefill_tcgen05_kerne
   const unsigned tmem_base = bars->tmem;
   const unsigned idesc_s = tc5_idesc(A5_BN, false), idesc_pv = tc5_idesc(A5_D, true);
   bool ok = true;
+  // Running softmax with a lazy maximum: the exponentials use m_used, which follows the true maximum
+  // only when that has grown by more than 8 (a factor 256, far inside the range of bfloat16 and of
+  // the float sums), so the output rows in tensor memory are read, scaled and written back only
+  // on those rare occasions, not once per tile.
+  float m_used = -INFINITY, l = 0.f;
+  const unsigned t_lane = tmem_base + ((unsigned)((warp & 3) * 32) << 16);      // this warp's lanes: the score buffers
+  const unsigned t_o = t_lane + O_COL;                                         // and the outputs
 
   if (tid == NROW) {
     // ---- the thread that issues the products ----
@@ -287,13 +304,6 @@ __global__ void __launch_bounds__(A5_THREADS, 2) attention_prefill_tcgen05_kerne
     // ---- the rows ----
     mbar_arrive(bars->k_full);                         // K(0) and K(1), after the fence above
     if (n_tiles > 1) mbar_arrive(bars->k_full + 1);
-    const unsigned t_lane = tmem_base + ((unsigned)(warp * 32) << 16);          // this warp's lanes: the score buffers
-    const unsigned t_o = t_lane + O_COL;                                         // and the outputs
-    // Running softmax with a lazy maximum: the exponentials use m_used, which follows the true maximum
-    // only when that has grown by more than 8 (a factor 256, far inside the range of bfloat16 and of
-    // the float sums), so the output rows in tensor memory are read, scaled and written back only
-    // on those rare occasions, not once per tile.
-    float m_used = -INFINITY, l = 0.f;
     const int min_hi = start + c_first;                                       // the least any live row of the CTA sees
     const int max_lo = a.window > 0 ? max(0, start + c_last - a.window + 1) : 0;
     const bool all_live = R0 + ROWS <= n_rows;
@@ -404,7 +414,62 @@ __global__ void __launch_bounds__(A5_THREADS, 2) attention_prefill_tcgen05_kerne
       atomicExch(err, 27);
     }
     tc5_fence_after();
+  }
 
+  // ---- the results ----
+  if (pair && n_parts > 1) {
+    // Two CTAs of a cluster with half of the keys each.  The second leaves its rows as they are, with
+    // their maxima and sums, in its own shared memory (the K and V tiles are done with: 64 KB, value
+    // quads of all rows side by side; maxima and sums where Q was); the first adds them to its own:
+    // out = (w0 O0 + w1 O1) / (w0 l0 + w1 l1), w_p = 2^(m_p - max(m0, m1)).  The second CTA stays until
+    // the first has read.
+    if (rank == 1 && tid < NROW) {
+#pragma unroll
+      for (int c = 0; c < A5_D / 32; ++c) {
+        float vals[32];
+        tc5_ld32(t_o + c * 32, vals);
+#pragma unroll
+        for (int q = 0; q < 8; ++q)
+          *reinterpret_cast<float4*>(k_s + (size_t)((c * 8 + q) * NROW + tid) * 16) = make_float4(vals[q * 4], vals[q * 4 + 1], vals[q * 4 + 2], vals[q * 4 + 3]);
+      }
+      *reinterpret_cast<float2*>(q_s + tid * 8) = make_float2(m_used, l);
+    }
+    cluster_sync();
+    if (rank == 0 && tid < NROW) {
+      const unsigned peer_o = cluster_map(smem_u32(k_s), 1), peer_ml = cluster_map(smem_u32(q_s), 1);
+      float m1, l1;
+      asm volatile("ld.shared::cluster.v2.f32 {%0, %1}, [%2];\n" : "=f"(m1), "=f"(l1) : "r"(peer_ml + tid * 8) : "memory");
+      const float M = fmaxf(m_used, m1);
+      const float w0 = m_used == -INFINITY ? 0.f : a5_ex2(m_used - M), w1 = m1 == -INFINITY ? 0.f : a5_ex2(m1 - M);
+      const float L = l * w0 + l1 * w1;
+      const float inv = live && L > 0.f ? 1.0f / L : 0.f;
+      const float s0 = w0 * inv, s1 = w1 * inv;
+      bf16* dst = a.out + (size_t)(q0 + tok) * a.nq * A5_D + (size_t)(kvh * G + head) * A5_D;
+#pragma unroll
+      for (int c = 0; c < A5_D / 32; ++c) {
+        float mine[32], theirs[32];
+        tc5_ld32(t_o + c * 32, mine);
+#pragma unroll
+        for (int q = 0; q < 8; ++q)
+          asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];\n"
+                       : "=f"(theirs[q * 4]), "=f"(theirs[q * 4 + 1]), "=f"(theirs[q * 4 + 2]), "=f"(theirs[q * 4 + 3])
+                       : "r"(peer_o + (unsigned)((c * 8 + q) * NROW + tid) * 16) : "memory");
+        if (!live) continue;
+#pragma unroll
+        for (int j = 0; j < 32; ++j) mine[j] = mine[j] * s0 + theirs[j] * s1;
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          uint4 o;
+          o.x = pack_bf16(mine[q * 8], mine[q * 8 + 1]);
+          o.y = pack_bf16(mine[q * 8 + 2], mine[q * 8 + 3]);
+          o.z = pack_bf16(mine[q * 8 + 4], mine[q * 8 + 5]);
+          o.w = pack_bf16(mine[q * 8 + 6], mine[q * 8 + 7]);
+          *reinterpret_cast<uint4*>(dst + c * 32 + q * 8) = o;
+        }
+      }
+    }
+    cluster_sync();
+  } else if (tid < NROW) {
     if (n_parts > 1) {
       // a part of the keys: the sums as they are, with the maximum they were taken against and the
       // sum of the weights, for the merge kernel
@@ -501,16 +566,18 @@ __global__ void __launch_bounds__(A5_MERGE_WARPS * 32) attention_prefill_merge_k
 // tiles: (entry, row tile, code) triples with row tiles of 128 rows (code 1: the whole tile; else
 // first part << 8 | part << 4 | parts: one of up to 15 parts of its keys); merges: (entry, row tile,
 // first part, parts) of the n_merges tiles that were cut, scratch: n_tiles * nkv * 128 * (D + 2)
-// floats when there are any; otherwise the arguments of
+// floats when there are any.  pairs != 0: every piece of work goes to a cluster of two CTAs, and the
+// codes are 1 (the whole tile, one CTA) or 2 (half of the keys each).  Otherwise the arguments of
 // q25_attention_prefill_bf16.  Head size 128 only.  err: one int that receives a nonzero code if a
 // wait gave up.
 Q25_EXPORT int q25_attention_prefill_tcgen05_bf16(const void* qkv, int qkv_stride, void* out, const void* kp, const void* vp,
                                                   const int* bt, int tw, const int* cu_q, const int* q_start,
                                                   const int* tiles, int n_tiles, int nq, int nkv, int d, int page_size,
                                                   int window, float scale, const int* merges, int n_merges, float* scratch,
-                                                  int* err, void* stream) {
+                                                  int pairs, int* err, void* stream) {
   if (n_tiles <= 0) return 0;
-  if (d != A5_D || !err || (n_merges > 0 && (!merges || !scratch || window > 0))) return (int)cudaErrorInvalidValue;
+  if (d != A5_D || !err || (n_merges > 0 && (!merges || !scratch || window > 0 || pairs)) || (pairs && window > 0))
+    return (int)cudaErrorInvalidValue;
   AttnArgs a;
   int e = fill_args(a, qkv, qkv_stride, out, kp, vp, bt, tw, cu_q, q_start, tiles, nq, nkv, page_size, window, scale);
   if (e) return e;
@@ -519,8 +586,8 @@ Q25_EXPORT int q25_attention_prefill_tcgen05_bf16(const void* qkv, int qkv_strid
   if (ce != cudaSuccess) return (int)ce;
   a.part_o = scratch;                                    // [part, kv head, row, D], then [part, kv head, row, (m, l)]
   a.part_ml = scratch ? scratch + (size_t)n_tiles * nkv * A5_ROWS * A5_D : nullptr;
-  launch(attention_prefill_tcgen05_kernel, dim3(n_tiles * nkv), dim3(A5_THREADS), (size_t)A5_SMEM, (cudaStream_t)stream, a,
-         device_sm_count(), err);
+  launch_clusters(pairs ? 2 : 1, attention_prefill_tcgen05_kernel, dim3(n_tiles * nkv * (pairs ? 2 : 1)), dim3(A5_THREADS),
+                  (size_t)A5_SMEM, (cudaStream_t)stream, a, device_sm_count(), err);
   if (n_merges > 0)
     launch(attention_prefill_merge_kernel, dim3(n_merges * nkv * (A5_ROWS / A5_MERGE_WARPS)), dim3(A5_MERGE_WARPS * 32), 0,
            (cudaStream_t)stream, a, merges);

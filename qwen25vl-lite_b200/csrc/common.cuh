@@ -116,20 +116,44 @@ __device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.lau
 
 static thread_local cudaError_t q25_launch_error = cudaSuccess;
 
+// cluster: CTAs per thread-block cluster along x (1: none); the grid is then a multiple of it.
 template <typename... KArgs, typename... Args>
-static inline void launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args... args) {
+static inline void launch_clusters(int cluster, void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                   Args... args) {
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = grid;
   cfg.blockDim = block;
   cfg.dynamicSmemBytes = smem;
   cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[0].val.programmaticStreamSerializationAllowed = 1;
+  attr[1].id = cudaLaunchAttributeClusterDimension;
+  attr[1].val.clusterDim.x = (unsigned)cluster;
+  attr[1].val.clusterDim.y = 1;
+  attr[1].val.clusterDim.z = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = 1;
+  cfg.numAttrs = cluster > 1 ? 2 : 1;
   const cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
   if (e != cudaSuccess && q25_launch_error == cudaSuccess) q25_launch_error = e;
+}
+template <typename... KArgs, typename... Args>
+static inline void launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args... args) {
+  launch_clusters(1, kernel, grid, block, smem, stream, args...);
+}
+
+// ---- thread-block clusters --------------------------------------------------------------------------
+// All threads of all CTAs of the cluster meet; what they wrote to shared memory before is visible to
+// the others' ld.shared::cluster after.  A hardware barrier like __syncthreads: every thread must
+// come, so it stands only where all waits before it are bounded.
+__device__ __forceinline__ void cluster_sync() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n barrier.cluster.wait.acquire.aligned;\n" ::: "memory");
+}
+// The address, in the cluster's shared window, of this CTA's shared address in the CTA of that rank.
+__device__ __forceinline__ unsigned cluster_map(unsigned smem_addr, unsigned rank) {
+  unsigned r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;\n" : "=r"(r) : "r"(smem_addr), "r"(rank));
+  return r;
 }
 
 // Streaming multiprocessors of the current device (asked once per device): persistent grids and

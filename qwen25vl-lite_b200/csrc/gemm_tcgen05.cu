@@ -272,9 +272,6 @@ __device__ __forceinline__ unsigned p2_cta_rank() {
   asm volatile("mov.u32 %0, %%cluster_ctarank;\n" : "=r"(r));
   return r;
 }
-__device__ __forceinline__ void p2_cluster_sync() {
-  asm volatile("barrier.cluster.arrive.release.aligned;\n barrier.cluster.wait.acquire.aligned;\n" ::: "memory");
-}
 __device__ __forceinline__ void p2_tma_load(void* dst, const CUtensorMap* map, int x, int y, unsigned long long* bar) {
   asm volatile(
       "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];\n"
@@ -357,7 +354,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
   // x was written by the kernel before this one, the output may still be read by it, and tensor
   // memory is asked for only when that kernel has gone (see the one-CTA kernel)
   pdl_wait();
-  p2_cluster_sync();                                    // the other CTA's barriers exist before anything signals them
+  cluster_sync();                                    // the other CTA's barriers exist before anything signals them
   if (warp == 1) {   // tensor memory: two accumulators of 256 columns, in both CTAs (the same warp of each asks)
     asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_u32(&sh->tmem_base)), "n"(512) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;\n" ::: "memory");
@@ -462,7 +459,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
   // all threads of both CTAs get here (all waits are bounded): neither CTA leaves, or gives its
   // tensor memory back, while the other may still signal it or compute into it
   tc5_fence_before();
-  p2_cluster_sync();
+  cluster_sync();
   if (warp == 1) {
     tc5_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "n"(512) : "memory");

@@ -30,7 +30,9 @@ from . import kernels
 PREFILL_TILE_ROWS = (64, 128)   # row tiles of the two prefill attention kernels (mma.sync, tcgen05)
 KEY_TILE = 64                   # keys per iteration of the tcgen05 prefill kernel
 MIN_PART_TILES = 4              # a row tile's keys are cut into parts of at least this many key tiles
-MIN_CUT_WALK = 24               # and only when the longest walk of the step has this many key tiles
+MIN_CUT_WALK = 24               # in steps whose longest walk has this many key tiles
+MIN_PAIR_WALK = 6               # a cluster of two CTAs halves a tile's walk of this many key tiles or more,
+MIN_PAIRS_WALK = 12             # in steps whose longest walk has this many
 MAX_PARTS = 15
 _scratch = {}
 
@@ -44,8 +46,9 @@ def plan_step(host, group: int, window: int = 0, places: int = 0) -> Dict[str, n
     other entries, a tile being 64 consecutive rows of the entry's (token, head of the group) pairs;
     the tiles of a run's last tokens see the most keys, so they go first and the short ones fill in
     behind them.  ``tiles128``: the same in tiles of 128 rows for the tcgen05 kernel, as triples
-    (entry, tile, code), with the keys of the long tiles cut into parts (``split_keys``), and
-    ``merge128``: the tiles whose parts a second kernel adds up, as (entry, tile, first part, parts).
+    (entry, tile, code), where a step of few tiles has the keys of its long tiles cut (``cut_keys``);
+    ``merge128``: the tiles whose parts a second kernel adds up, as (entry, tile, first part, parts);
+    ``pairs128`` is not empty when ``tiles128`` is meant for clusters of two CTAs (``pair_split``).
     ``places``: CTAs of the tcgen05 kernel that run at a time for one kv head (0: nothing is cut)."""
     q_lens, starts = host.q_lens, host.starts
     runs = [i for i, n in enumerate(q_lens) if n > 1 or group > 16]
@@ -60,51 +63,79 @@ def plan_step(host, group: int, window: int = 0, places: int = 0) -> Dict[str, n
         for t in range(-(-q_lens[i] * group // 128)):
             last_token = min((t * 128 + 127) // group, q_lens[i] - 1)
             tiles.append((i, t, (starts[i] + last_token) // KEY_TILE + 1))
-    triples, merges = split_keys(tiles, bool(window), places)
+    triples, merges, clusters = cut_keys(tiles, bool(window), places)
+    out["pairs128"] = np.ones(1 if clusters else 0, dtype=np.int32)        # its presence says how tiles128 is to be read
     out["tiles128"] = np.asarray(triples, dtype=np.int32).reshape(-1)
     out["merge128"] = np.asarray(merges, dtype=np.int32).reshape(-1)
     return out
 
 
-def split_keys(tiles, windowed: bool, places: int, shortest: int = MIN_PART_TILES, min_walk: int = MIN_CUT_WALK):
-    """Cuts the keys of long row tiles into parts when a step has few row tiles.  A CTA of the tcgen05
-    prefill kernel walks a tile's keys one key tile after the other (about 1.1 us each), so a step
-    takes as long as its longest walk however many SMs are idle: 128 tokens after 8,000 are 16 CTAs
-    of 126 key tiles each.  The tiles are then cut into parts of at most ``length`` key tiles, each a
-    piece of work of its own that leaves unnormalised sums, and a merge kernel adds the parts up.
-    ``places``: CTAs that run at a time, for one kv head.  Measured on B200 (16 query and 2 kv heads,
-    so 296 places in all; whole -> cut):
+def cut_keys(tiles, windowed: bool, places: int):
+    """How the tcgen05 prefill kernel takes a step's row tiles.  A CTA walks a tile's keys one key tile
+    after the other (about 1.1 us each, after 8 us of start and end), two CTAs to an SM, so a step
+    with few row tiles takes as long as its longest walk however many SMs are idle.  There are two
+    ways to cut walks, and three outcomes; ``tiles`` is (entry, tile, key tiles), ``places`` the CTAs
+    that run at a time for one kv head (0: nothing is cut), and the result (work list, merges,
+    pairs) as ``plan_step`` describes them:
 
-    * the pieces must fit the places: a second round of CTAs costs more than shorter walks save
-      (2,048 tokens: 256 CTAs 45 us, cut into 384 CTAs 57 us; 512 tokens after 3,000: 64 CTAs 64 us,
-      280 CTAs 36 us, 440 CTAs 48 us), so ``length`` is the smallest, from ``shortest`` on, with
-      which they do;
-    * where the whole tiles fill more than half the places, the cut saves what the merge kernel and
-      the fuller SMs cost (2,048 tokens with the 20 longest tiles halved: 45 -> 47 us; 1,500 tokens
-      after 500: 51 -> 47 us), and with short walks it loses (1,024 tokens, 16 key tiles at most:
-      25 -> 28 us), so those steps stay whole;
-    * the others: 128 tokens after 8,000: 134 -> 29 us; 64 after 2,000: 41 -> 16 us; four runs of
-      256 after 100 to 5,000: 92 -> 45 us; 300 and 200 after 4,000: 94 -> 30 us.
+    * parts through scratch memory (``split_keys``): up to ``MAX_PARTS`` parts a tile, as many pieces as
+      there are places, a merge kernel behind; costs about 6 key tiles' time;
+    * clusters of two CTAs (``pair_split``) that halve a tile's keys and add up through the cluster's
+      shared memory: costs about 5 key tiles' time, and twice the places;
+    * whole tiles, when the tiles fill more than three quarters of the places or the walks are short.
 
-    A tile has at most ``MAX_PARTS`` parts.  Windowed attention is not cut (a part may hold no key
-    that a row sees).  ``tiles``: (entry, tile, key tiles).  Returns the work list, longest first, as
+    Measured on B200, 16 query and 2 kv heads (296 places in all), whole / parts / pairs in us:
+    128 tokens after 8,000: 134 / 29 / 75; 512 after 3,000: 64 / 37 / 41; four runs of 256 after 100
+    to 5,000: 92 / 45 / 57; 1,024 after 1,024: 42 / 42 / 32; 1,024: 26 / 28 / 22; 1,200: 29 / - / 26;
+    1,500 after 500: 51 / 47 (296 CTAs) / 46; 2,048: 45 / 47 (296 CTAs), 57 (384 CTAs) / 48; 4,096:
+    89 / - / 124; 8,192: 291 / - / 354.  Windowed attention is not cut (a part may hold no key that a
+    row sees)."""
+    whole = lambda: ([(i, t, 1) for i, t, _ in sorted(tiles, key=lambda w: -w[2])], [], False)
+    if windowed or not places or not tiles:
+        return whole()
+    longest = max(n for _, _, n in tiles)
+    if 2 * len(tiles) <= places:
+        length = part_length(tiles, places) if longest >= MIN_CUT_WALK else 0
+        if length and -(-longest // 2) > length + 6:
+            return split_keys(tiles, length) + (False,)
+    if 4 * len(tiles) <= 3 * places and longest >= MIN_PAIRS_WALK:
+        return pair_split(tiles), [], True
+    return whole()
+
+
+def pair_split(tiles):
+    """The work list for clusters of two CTAs, longest walk first: (entry, tile, 2) for a tile whose
+    keys the two halve (the second leaves its rows in its shared memory and the first adds them up),
+    (entry, tile, 1) for a short one that the first CTA takes alone."""
+    work = [(-(-n // 2) if n >= MIN_PAIR_WALK else n, i, t, 2 if n >= MIN_PAIR_WALK else 1) for i, t, n in tiles]
+    work.sort(key=lambda w: -w[0])
+    return [(i, t, code) for _, i, t, code in work]
+
+
+def part_length(tiles, places: int, shortest: int = MIN_PART_TILES) -> int:
+    """The least number of key tiles per part, from ``shortest`` on, with which the parts of all
+    tiles still fit the places: a second round of CTAs costs more than shorter walks save."""
+    counts = np.asarray([n for _, _, n in tiles], dtype=np.int64)
+    pieces = lambda length: int(np.minimum(MAX_PARTS, -(-counts // length)).sum())
+    lo, hi = shortest, max(shortest, int(counts.max()))            # pieces(longest walk) = len(tiles) fits
+    while lo < hi:
+        mid = (lo + hi) // 2
+        if pieces(mid) <= places:
+            hi = mid
+        else:
+            lo = mid + 1
+    return lo
+
+
+def split_keys(tiles, length: int):
+    """Cuts the keys of the tiles that walk more than ``length`` key tiles into parts of at most that
+    many (``MAX_PARTS`` parts at most), each a piece of work of its own that leaves unnormalised sums
+    in scratch memory; a merge kernel adds the parts up.  Returns the work list, longest first, as
     (entry, tile, code) with code = first part << 8 | part << 4 | parts (1 for a whole tile), and the
     list of cut tiles as (entry, tile, first part, parts); parts are numbered through the whole step."""
-    counts = np.asarray([n for _, _, n in tiles], dtype=np.int64)
-    length = 0
-    if not windowed and len(tiles) and 2 * len(tiles) <= places and counts.max() >= max(min_walk, shortest + 1):
-        pieces = lambda length: int(np.minimum(MAX_PARTS, -(-counts // length)).sum())
-        lo, hi = shortest, int(counts.max())            # pieces(hi) = len(tiles) fits
-        while lo < hi:
-            mid = (lo + hi) // 2
-            if pieces(mid) <= places:
-                hi = mid
-            else:
-                lo = mid + 1
-        length = lo
     work, merges, next_part = [], [], 0
     for i, t, n in tiles:
-        parts = min(MAX_PARTS, -(-n // length)) if length else 1
+        parts = min(MAX_PARTS, -(-n // length))
         if parts == 1:
             work.append((n, i, t, 1))
             continue
@@ -191,6 +222,7 @@ def paged_attention(ctx, plan, qkv, kv, nq: int, nkv: int, head_dim: int, window
         scratch = _scratch_floats(n_items * nq * splits * (head_dim + 2), qkv.device) if splits > 1 else None
         kernels.attention_decode(qkv, out, kv.k_pages, kv.v_pages, kv.block_table, ctx.cu_q, ctx.q_start_pos,
                                  decode_items, nq, nkv, head_dim, kv.page_size, window, scale, splits, scratch)
+    pairs = plan.get("pairs128") is not None
     tiles64, tiles128 = _pairs(plan.get("tiles64")), _pairs(plan.get("tiles128"), 3)
     if tiles64 is not None:
         if tiles128 is not None and group <= 128 and kernels.attention_tcgen05_supports(qkv.dtype, head_dim, kv.page_size, qkv):
@@ -199,7 +231,8 @@ def paged_attention(ctx, plan, qkv, kv, nq: int, nkv: int, head_dim: int, window
             scratch = None if merge128 is None else _scratch_floats(
                 tiles128.shape[0] * nkv * 128 * (head_dim + 2), qkv.device)
             kernels.attention_prefill_tcgen05(qkv, out, kv.k_pages, kv.v_pages, kv.block_table, ctx.cu_q, ctx.q_start_pos,
-                                              tiles128, nq, nkv, head_dim, kv.page_size, window, scale, merge128, scratch)
+                                              tiles128, nq, nkv, head_dim, kv.page_size, window, scale, merge128, scratch,
+                                              pairs=pairs)
         else:
             kernels.attention_prefill(qkv, out, kv.k_pages, kv.v_pages, kv.block_table, ctx.cu_q, ctx.q_start_pos, tiles64,
                                       nq, nkv, head_dim, kv.page_size, window, scale)

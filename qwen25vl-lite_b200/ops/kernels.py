@@ -326,26 +326,30 @@ def attention_prefill_tcgen05(qkv: torch.Tensor, out: torch.Tensor, k_pages: tor
                               block_table: torch.Tensor, cu_q: torch.Tensor, q_start_pos: torch.Tensor,
                               tiles: torch.Tensor, nq: int, nkv: int, head_dim: int, page_size: int, window: int,
                               scale: float, merges: Optional[torch.Tensor] = None,
-                              scratch: Optional[torch.Tensor] = None) -> None:
+                              scratch: Optional[torch.Tensor] = None, pairs: bool = False) -> None:
     """``attention_prefill`` on the tcgen05 tensor cores (scores, P and the outputs in tensor memory).
     ``tiles`` is int32 [n, 3]: (entry, row tile, code) with row tiles of 128 rows; code 1 is a whole
     tile, else first part << 8 | part << 4 | parts: one of the parts its keys are cut into, which
     leaves unnormalised sums in ``scratch`` (float32, room for n * nkv * 128 * (head_dim + 2)).
     ``merges`` is int32 [m, 4]: (entry, row tile, first part, parts) of the cut tiles, which a second
-    kernel adds up."""
+    kernel adds up.  ``pairs``: every piece of work goes to a cluster of two CTAs instead; code 2 then
+    means half of the keys for each, added up through the cluster's shared memory, code 1 the whole
+    tile for one of them."""
     if not attention_tcgen05_supports(qkv.dtype, head_dim, page_size, qkv):
         raise KernelError(f"attention_prefill_tcgen05: unsupported head size {head_dim}, page size {page_size} or layout")
     if tiles.dim() != 2 or tiles.shape[1] != 3:
         raise KernelError("attention_prefill_tcgen05: the work list is (entry, row tile, code) triples")
     n_merge = 0 if merges is None else merges.shape[0]
-    if n_merge and (scratch is None or scratch.dtype != torch.float32
+    if n_merge and (pairs or scratch is None or scratch.dtype != torch.float32
                     or scratch.numel() < tiles.shape[0] * nkv * 128 * (head_dim + 2)):
-        raise KernelError("attention_prefill_tcgen05: cut tiles need float32 scratch for every piece of work")
+        raise KernelError("attention_prefill_tcgen05: cut tiles need float32 scratch for every piece of work, and no pairs")
+    if pairs and window:
+        raise KernelError("attention_prefill_tcgen05: keys behind a window are not cut")
     _check(_fn("q25_attention_prefill_tcgen05_bf16",
-               [_P, _I, _P, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _P, _I, _P, _P, _P])(
+               [_P, _I, _P, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _P, _I, _P, _I, _P, _P])(
         qkv.data_ptr(), qkv.stride(0), out.data_ptr(), k_pages.data_ptr(), v_pages.data_ptr(), block_table.data_ptr(),
         block_table.shape[1], cu_q.data_ptr(), q_start_pos.data_ptr(), tiles.data_ptr(), tiles.shape[0], nq, nkv,
-        head_dim, page_size, int(window or 0), float(scale), _ptr(merges), n_merge, _ptr(scratch),
+        head_dim, page_size, int(window or 0), float(scale), _ptr(merges), n_merge, _ptr(scratch), int(bool(pairs)),
         error_flag(qkv.device).data_ptr(), _stream()), "attention_prefill_tcgen05")
     if n_merge:
         count_replayed(1)                      # the merge kernel, launched by the same call

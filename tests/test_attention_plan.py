@@ -32,9 +32,14 @@ def test_every_row_is_in_one_tile_and_single_tokens_are_decode_items(group):
         # heaviest first: the keys a tile's last row sees never grow along the list
         reach = [starts[i] + (t + 1) * 64 // group for i, t in pairs.tolist()]
         assert reach == sorted(reach, reverse=True)
-        # tiles of 128 rows: whole, or every part of a cut tile once
-        triples = plan["tiles128"].reshape(-1, 3).tolist()
+        # tiles of 128 rows: whole, every part of a cut tile once, or (for clusters of two CTAs) codes 1 and 2
         want = {(i, t) for i, q in enumerate(q_lens) if q > 1 for t in range(-(-q * group // 128))}
+        if plan["pairs128"].size:
+            triples = plan["tiles128"].reshape(-1, 3).tolist()
+            assert plan["merge128"].size == 0 and len(triples) == len(want) and {(i, t) for i, t, _ in triples} == want
+            assert {code for _, _, code in triples} <= {1, 2}
+            continue
+        triples = plan["tiles128"].reshape(-1, 3).tolist()
         assert {(i, t) for i, t, _ in triples} == want
         whole = [(i, t) for i, t, code in triples if code == 1]
         cut = {}
@@ -68,13 +73,30 @@ def test_few_long_tiles_are_cut_to_fill_the_places_once():
     whole = sum((3000 + min(t * 16 + 15, 511)) // KEY_TILE + 1 for t in range(32))
     plan = plan_step(host(q_lens, starts), 8, places=PLACES)
     walks = walks_of(plan, q_lens, starts, 8)
+    assert plan["pairs128"].size == 0
     assert len(walks) > 2 * 32 and len(walks) <= PLACES                  # more pieces, one round of CTAs
     assert min(walks) >= 1 and sum(walks) == whole and walks == sorted(walks, reverse=True)
     assert max(walks) <= -(-55 // (len(walks) // 32)) + 1
-    # places for nothing more than the tiles, short walks, a window (a part could hold no key a row sees): whole tiles
-    for q, s, kw in (([2048], [0], {}), ([1024], [0], {}), ([512], [3000], dict(window=300)), ([512], [3000], dict(places=0))):
+    # more tiles than three quarters of the places, short walks, a window (a part could hold no key a row sees),
+    # no places given: whole tiles
+    for q, s, kw in (([2048], [0], {}), ([4096], [0], {}), ([128], [0], {}), ([512], [3000], dict(window=300)), ([512], [3000], dict(places=0))):
         plan = plan_step(host(q, s), 8, **{**dict(places=PLACES), **kw})
-        assert plan["merge128"].size == 0 and all(code == 1 for code in plan["tiles128"].reshape(-1, 3)[:, 2])
+        assert plan["merge128"].size == 0 and plan["pairs128"].size == 0
+        assert all(code == 1 for code in plan["tiles128"].reshape(-1, 3)[:, 2])
+
+
+def test_steps_that_fill_up_to_three_quarters_of_the_places_go_to_pairs_of_ctas():
+    """1,024 tokens after 1,024 are 64 row tiles of 17 to 32 key tiles: parts that fit the places
+    would be as long as half a tile, so clusters of two CTAs halve every tile; 1,500 tokens are 94
+    tiles, too many for parts."""
+    for q, s in (([1024], [1024]), ([1500], [0]), ([1024], [0])):
+        plan = plan_step(host(q, s), 8, places=PLACES)
+        assert plan["pairs128"].size == 1 and plan["merge128"].size == 0
+        triples = plan["tiles128"].reshape(-1, 3).tolist()
+        walk = lambda t: (s[0] + min(t * 16 + 15, q[0] - 1)) // KEY_TILE + 1
+        assert all(code == (2 if walk(t) >= 6 else 1) for _, t, code in triples)
+        halves = [-(-walk(t) // 2) if code == 2 else walk(t) for _, t, code in triples]
+        assert halves == sorted(halves, reverse=True)
 
 
 def test_a_group_wider_than_the_decode_kernels_rows_goes_with_the_runs():

@@ -310,30 +310,37 @@ def test_attention_tensor_core_kernels(nq, nkv, d, page_size, window, splits):
 def run_tcgen05_prefill(c, lens, q_lens, nq, nkv, d, page_size, window, shortest=None, fill=0.0):
     """The tcgen05 prefill kernel over every run of the case: whole row tiles, or (``shortest``: key
     tiles per part at least) with the keys of the long tiles cut into parts and merged, as the
-    engine's plan cuts them."""
+    engine's plan cuts them, or (``shortest`` = "pairs") by clusters of two CTAs that halve the keys of
+    the longer tiles."""
     from qwen25vl_lite.ops import kernels
-    from qwen25vl_lite.ops.attention import split_keys
+    from qwen25vl_lite.ops.attention import pair_split, split_keys
     G = nq // nkv
     tiles = []
     for i, n in enumerate(q_lens):
         for t in range(-(-n * G // 128)):
             last = min((t * 128 + 127) // G, n - 1)
             tiles.append((i, t, (lens[i] - n + last) // 64 + 1))
-    if shortest is None:
+    pairs = shortest == "pairs"
+    if pairs:
+        work, merges = pair_split(tiles), []
+        assert window is None and any(code == 2 for _, _, code in work) and any(code == 1 for _, _, code in work)
+    elif shortest is None:
         work, merges = sorted(tiles, key=lambda w: -w[2]), []
         work = [(i, t, 1) for i, t, _ in work]
+    elif window:
+        work, merges = [(i, t, 1) for i, t, _ in tiles], []          # keys behind a window are not cut
     else:
-        work, merges = split_keys(tiles, bool(window), 1 << 20, shortest=shortest, min_walk=0)
-        assert window or merges
+        work, merges = split_keys(tiles, shortest)
+        assert merges
     out = torch.full((c["qkv"].shape[0], nq * d), fill, dtype=torch.bfloat16, device="cuda")
     scratch = torch.full((len(work) * nkv * 128 * (d + 2),), float("nan"), device="cuda") if merges else None
     kernels.attention_prefill_tcgen05(c["qkv"], out, c["k_pages"], c["v_pages"], c["table"], c["cu"], c["start"],
                                       dev(np.asarray(work, np.int32)), nq, nkv, d, page_size, window or 0, d ** -0.5,
-                                      dev(np.asarray(merges, np.int32)) if merges else None, scratch)
+                                      dev(np.asarray(merges, np.int32)) if merges else None, scratch, pairs)
     return out
 
 
-@pytest.mark.parametrize("shortest", [None, 1, 3])
+@pytest.mark.parametrize("shortest", [None, 1, 3, "pairs"])
 @pytest.mark.parametrize("nq,nkv,page_size,window", [(16, 2, 16, None), (8, 8, 4, None), (28, 4, 16, 150), (5, 1, 32, None), (40, 8, 8, 64)])
 def test_attention_prefill_tcgen05(nq, nkv, page_size, window, shortest):
     """The tcgen05 prefill attention (scores, P and outputs in tensor memory, head size 128) against
@@ -342,6 +349,8 @@ def test_attention_prefill_tcgen05(nq, nkv, page_size, window, shortest):
     whole row tiles and with their keys cut into parts of one and of three key tiles at least (a
     part of one tile lies wholly behind some rows of its row tile, which then bring nothing)."""
     from qwen25vl_lite.ops import kernels
+    if shortest == "pairs" and window:
+        pytest.skip("keys behind a window are not cut")
     d = 128
     rng = np.random.default_rng(21)
     lens, q_lens = [300, 37, 130, 64, 517, 333, 9], [300, 37, 2, 17, 200, 70, 9]
@@ -363,7 +372,7 @@ def test_attention_prefill_tcgen05(nq, nkv, page_size, window, shortest):
     assert not kernels.attention_tcgen05_supports(torch.bfloat16, 64, page_size)
 
 
-@pytest.mark.parametrize("shortest", [None, 4])
+@pytest.mark.parametrize("shortest", [None, 4, "pairs"])
 def test_attention_prefill_tcgen05_long_runs_repeat_exactly(shortest):
     """Many key tiles per CTA, more CTAs than the GPU holds at once, and scores that keep growing
     along the keys, so that the rows in tensor memory are rescaled again and again: against the
@@ -420,7 +429,7 @@ def test_tcgen05_prefill_attention_finds_a_far_key_and_the_window_edge():
     lens, q_lens = [700, 300], [70, 300]
     cases = [(0, None, True), (15, None, True), (16, None, True), (63, None, True), (64, None, True),
              (351, None, True), (629, None, True), (699, None, True), (700 - 60, 60, True), (700 - 61, 60, False)]
-    for key, window, visible, shortest in [case + (None,) for case in cases] + [case + (2,) for case in cases if case[1] is None]:
+    for key, window, visible, shortest in [case + (None,) for case in cases] + [case + (p,) for case in cases if case[1] is None for p in (2, "pairs")]:
         rng = np.random.default_rng(key)
         c = paged_case(rng, lens, q_lens, nq, nkv, d, ps, torch.bfloat16)
         dense = [list(t) for t in c["dense"]]
