@@ -120,7 +120,6 @@ __global__ void __launch_bounds__(A5_THREADS, 2) attention_prefill_tcgen05_kerne
   constexpr int NROW = A5_NROW, ROWS = A5_ROWS;         // one thread per row; the warp after them issues the products
   constexpr int TMEM_COLS = 256, O_COL = 128;           // two score buffers of 64 columns, then the outputs
   pdl_trigger();
-  pdl_wait();
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   unsigned char* q_s = smem;
@@ -224,6 +223,10 @@ __global__ void __launch_bounds__(A5_THREADS, 2) attention_prefill_tcgen05_kerne
       if (j < n_tiles) key_rows[j * A5_BN + my_key] = a5_key_row(a, table, kvh, key_begin + j * A5_BN + my_key, c_hi);
   }
   __syncwarp();
+  // Up to here the kernel has read the step's work list, lengths and block tables only, which came
+  // with the step's copy from the host before any of its kernels; q, and the keys and values of the
+  // step's own tokens, are what the kernels before this one wrote.
+  pdl_wait();
   // The first two K tiles, the first V tile and Q.  After that a row asks for K(t + 2) and V(t) when
   // tile t begins and waits for them when its part of tile t is done, a softmax later: at its fence
   // nothing of its own is in flight.

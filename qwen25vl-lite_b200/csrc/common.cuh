@@ -110,7 +110,8 @@ __device__ __forceinline__ void bulk_copy_once(void* dst, const void* src, unsig
 // finished and their writes are visible, so the results are those of plain stream order; what is
 // gained is the launch latency and whatever a kernel does before its wait (the weight-streaming
 // GEMM starts fetching weights).  Before pdl_wait() a kernel may read only what no kernel ever
-// writes: weights and constant tables.
+// writes: weights, constant tables, and the step's own lists, lengths and block tables, which come
+// with the step's copy from the host, ahead of its first kernel.
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 

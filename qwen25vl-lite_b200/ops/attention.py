@@ -35,6 +35,7 @@ MIN_PAIR_WALK = 6               # a cluster of two CTAs halves a tile's walk of 
 MIN_PAIRS_WALK = 12             # in steps whose longest walk has this many
 MAX_PARTS = 15
 _scratch = {}
+_retired = []
 
 
 def plan_step(host, group: int, window: int = 0, places: int = 0) -> Dict[str, np.ndarray]:
@@ -159,12 +160,16 @@ def decode_splits(n_items: int, nkv: int, max_kv_len: int, most: int = 64) -> in
     return int(min(by_work, by_sms, most))
 
 
-def _scratch_floats(n: int, device) -> torch.Tensor:
-    """Scratch memory for split partials, grown on demand and kept (stream-ordered reuse)."""
-    buf = _scratch.get(device)
+def _scratch_floats(n: int, device, use: str = "decode") -> torch.Tensor:
+    """Scratch memory for partial results, grown on demand and kept (stream-ordered reuse).  One
+    buffer per use: captured decode steps hold the address of theirs, so the far larger needs of a
+    prompt's parts must not make it move."""
+    buf = _scratch.get((device, use))
     if buf is None or buf.numel() < n:
+        if buf is not None and use == "decode":
+            _retired.append(buf)                    # a captured step may still point at it
         buf = torch.empty(max(n, 1 << 20), dtype=torch.float32, device=device)
-        _scratch[device] = buf
+        _scratch[(device, use)] = buf
     return buf
 
 
@@ -229,7 +234,7 @@ def paged_attention(ctx, plan, qkv, kv, nq: int, nkv: int, head_dim: int, window
             merge128 = _pairs(plan.get("merge128"), 4)
             # every piece of work may be a part: room for that many partial results
             scratch = None if merge128 is None else _scratch_floats(
-                tiles128.shape[0] * nkv * 128 * (head_dim + 2), qkv.device)
+                tiles128.shape[0] * nkv * 128 * (head_dim + 2), qkv.device, "parts")
             kernels.attention_prefill_tcgen05(qkv, out, kv.k_pages, kv.v_pages, kv.block_table, ctx.cu_q, ctx.q_start_pos,
                                               tiles128, nq, nkv, head_dim, kv.page_size, window, scale, merge128, scratch,
                                               pairs=pairs)
