@@ -127,9 +127,36 @@ class StepContext:
                       group.page_size)
 
 
-GRAPH_WIDTH_STEP = 16      # block-table widths of captured steps are rounded up to this many pages
-MAX_GRAPHS = 32
+GRAPH_WIDTH_STEP = 16      # block-table widths of captured steps are rounded up to 1, 1.5, 2, 3, 4, 6, 8, ... times this many pages
+MAX_GRAPHS = 128           # captured steps kept; the one unused for longest goes first
 CAPTURE_ON_USE = 3         # a (batch size, table width) is captured when it comes for the third time
+
+
+def graph_width(pages: int) -> int:
+    """The block-table width a captured step is given for requests of up to ``pages`` pages: the
+    next of 16, 24, 32, 48, 64, 96, 128, ... (steps of a factor 1.5 or 1.33).  A captured step serves
+    one (batch size, width); with widths in equal steps of 256 tokens a batch that decodes on crossed
+    into a new width, two uncaptured steps and a capture, every 256 tokens."""
+    unit = GRAPH_WIDTH_STEP
+    while True:
+        if pages <= unit:
+            return unit
+        if pages <= unit + unit // 2:
+            return unit + unit // 2
+        unit *= 2
+
+
+def graph_batch(entries: int) -> int:
+    """The batch size a captured step is given for ``entries`` one-token entries: itself up to 8 (the
+    chained products take up to 8 rows), then the next multiple of 8, of 16 beyond 64.  The rows
+    that are added read and write a page of their own and their logits are dropped.  While the
+    requests of a batch end one after the other every batch size lives a few steps only, too few
+    to pay for its capture (11 ms at the 7B sizes: 81 captures were 0.9 s of a 6.8 s trace of 128
+    requests)."""
+    if entries <= 8:
+        return entries
+    unit = 8 if entries <= 64 else 16
+    return -(-entries // unit) * unit
 
 
 class ModelRunner:
@@ -169,6 +196,7 @@ class ModelRunner:
         self.cuda_graphs = bool(cuda_graphs and self.device.type == "cuda" and blocks
                                 and all(getattr(p, "graph_safe", False) for p in parts))
         self._graphs: Dict[tuple, tuple] = {}
+        self._padding = None                    # the request of the rows that fill a captured step's batch, while a step is packed
         self._graph_seen: Dict[tuple, int] = {}
         self._capture_stream = None
         self._graph_pool = None
@@ -208,9 +236,11 @@ class ModelRunner:
         time, and while requests of a batch end one after the other most keys come only once or
         twice.  ``make_ctx`` builds the step's context; a replay does not need it (a dozen tensor
         views that would stand between the sampled ids and the launch)."""
-        hit = self._graphs.get(key)
+        hit = self._graphs.pop(key, None)
         if hit is not None and hit[2] != layout:
             hit = None                                  # the staging buffer was re-allocated since
+        if hit is not None:
+            self._graphs[key] = hit                     # used last: kept longest
         if hit is None:
             seen = self._graph_seen[key] = self._graph_seen.get(key, 0) + 1
             if seen < CAPTURE_ON_USE:
@@ -291,6 +321,18 @@ class ModelRunner:
     def _pack(self, entries: Sequence[StepEntry]):
         """Builds the step's arrays in the staging buffer; returns the function that runs the step
         (optionally with other token ids than the entries brought, for ``prepare_decode``)."""
+        try:
+            return self._pack_arrays(entries)
+        except BaseException:
+            self._close_padding()
+            raise
+
+    def _close_padding(self) -> None:
+        if self._padding is not None:
+            self.cache.close(self._padding)
+            self._padding = None
+
+    def _pack_arrays(self, entries: Sequence[StepEntry]):
         self.check_kernel_errors()
         ps = self.cache.page_size
         groups = self.cache.groups
@@ -305,10 +347,20 @@ class ModelRunner:
             self.cache.ensure(e.request.cache, s + n)       # no-op when the caller already did
         widths = [max(max(len(e.request.cache.tables[g.index]) for e in entries), 1) for g in groups]
         graph_key = None
+        pad, pad_cache = 0, None
         if self.cuda_graphs and max(q_lens) == 1 and all(list(e.want) == [0] for e in entries):
-            widths = [-(-w // GRAPH_WIDTH_STEP) * GRAPH_WIDTH_STEP for w in widths]
-            graph_key = (len(entries), tuple(widths))
+            widths = [graph_width(w) for w in widths]
+            if (graph_batch(S) > S and all(e.positions is None for e in entries)
+                    and getattr(self.position, "default_is_linear", False)):
+                pad_cache = self._padding = self._open_padding()
+                if pad_cache is not None:
+                    pad = graph_batch(S) - S
+            graph_key = (S + pad, tuple(widths))
         M = sum(len(e.want) for e in entries)
+        real = S
+        if pad:                      # rows of one token at position 0 in a page of their own, all alike
+            q_lens, starts = q_lens + [1] * pad, starts + [0] * pad
+            S, N, M = S + pad, N + pad, M + pad
 
         # ---- pack ----
         host = HostStep(q_lens, starts, N, S)
@@ -357,18 +409,20 @@ class ModelRunner:
             # A step of single tokens at their default positions (the usual decode step): the
             # arrays are filled for all entries at once, and a request's block table is converted
             # only when it has grown.
-            ids = np.fromiter((e.tokens[0] for e in entries), dtype=np.int64, count=S)
+            ids = np.fromiter((e.tokens[0] for e in entries), dtype=np.int64, count=real)
             if ids.min() < 0 or ids.max() >= self.vocab_size:
                 raise ValueError(f"token id outside [0, {self.vocab_size}) in a decode step")
             st = np.asarray(starts, dtype=np.int64)
-            place = st + np.fromiter((e.request.cache.position_offset for e in entries), dtype=np.int64, count=S)
-            tok[:] = ids
+            place = st.copy()
+            place[:real] += np.fromiter((e.request.cache.position_offset for e in entries), dtype=np.int64, count=real)
+            tok[:real] = ids
+            tok[real:] = 0
             pos[:, :] = place
-            last_position = place.tolist()
+            last_position = place[:real].tolist()
             tseq[:] = np.arange(S)
             cu[1:] = np.arange(1, S + 1)
             qs[:] = st
-            sl[:] = [e.request.cache.slot for e in entries]
+            sl[:real] = [e.request.cache.slot for e in entries]
             r = 0
             for i, e in enumerate(entries):
                 for w_ in e.want:
@@ -376,12 +430,19 @@ class ModelRunner:
                         raise ValueError(f"wanted place {w_} is outside the 1 token of the entry")
                     rows[r] = i
                     r += 1
+            if pad:
+                sl[real:] = pad_cache.slot
+                rows[real:] = np.arange(real, S)
             for g, gs, gt in zip(groups, g_slot, g_tab):
                 for i, (e, s0) in enumerate(zip(entries, starts)):
                     table = e.request.block_table(g.index)
                     gs[i] = e.request.cache.tables[g.index][s0 // ps] * ps + s0 % ps
                     gt[i, :len(table)] = table
                     gt[i, len(table):] = 0
+                if pad:
+                    gs[real:] = pad_cache.tables[g.index][0] * ps
+                    gt[real:, :] = 0
+                    gt[real:, 0] = pad_cache.tables[g.index][0]
         else:
             at = 0
             r = 0
@@ -422,15 +483,30 @@ class ModelRunner:
 
         return lambda tokens=None: self._run_packed(
             tokens, entries, q_lens, starts, widths, graph_key, off, N, S, M, ps, tok, tok_s, pos_s, tseq_s, cu_s, qs_s, sl_s,
-            rows_s, g_slot_s, g_tab_s, plan_s, last_position)
+            rows_s, g_slot_s, g_tab_s, plan_s, last_position, pad_cache)
+
+    def _open_padding(self):
+        """A request of one token for the rows that fill a captured step's batch, or None when no
+        slot or page is free for it.  It is closed again when the step has been launched."""
+        try:
+            cache = self.cache.open()
+        except Exception:
+            return None
+        try:
+            self.cache.ensure(cache, 1)
+        except Exception:
+            self.cache.close(cache)
+            return None
+        return cache
 
     def _run_packed(self, tokens, entries, q_lens, starts, widths, graph_key, off, N, S, M, ps, tok, tok_s, pos_s, tseq_s,
-                    cu_s, qs_s, sl_s, rows_s, g_slot_s, g_tab_s, plan_s, last_position):
+                    cu_s, qs_s, sl_s, rows_s, g_slot_s, g_tab_s, plan_s, last_position, pad_cache=None):
+        real = len(entries)
         if tokens is not None:
             ids = np.asarray(tokens, dtype=np.int64)
-            if ids.shape != (N,) or ids.min() < 0 or ids.max() >= self.vocab_size:
-                raise ValueError(f"a prepared step needs {N} token ids in [0, {self.vocab_size})")
-            tok[:] = ids
+            if ids.shape != (real,) or S != N or ids.min() < 0 or ids.max() >= self.vocab_size:
+                raise ValueError(f"a prepared step needs {real} token ids in [0, {self.vocab_size})")
+            tok[:real] = ids
         dev = self._device_ints
         dev[:off].copy_(self._staging[:off], non_blocking=True)
         if self._staging_free is not None:
@@ -452,12 +528,19 @@ class ModelRunner:
             cache=self.cache,
             plans=self._plan_views(plan_s, d),
             host_q_lens=q_lens, host_q_start=starts,
-            host_slots=[e.request.cache.slot for e in entries],
+            host_slots=[e.request.cache.slot for e in entries] + ([pad_cache.slot] * (S - real) if S > real else []),
         )
-        if graph_key is None:
-            logits = self.model.forward(make_ctx())
-        else:
-            logits = self._replay(graph_key, make_ctx, (dev.data_ptr(), off))
+        try:
+            if graph_key is None:
+                logits = self.model.forward(make_ctx())
+            else:
+                logits = self._replay(graph_key, make_ctx, (dev.data_ptr(), off))
+        finally:
+            # the rows that filled the batch: their page goes back (whoever gets it next writes it
+            # behind this step on the stream); their logits are dropped
+            self._close_padding()
+        if S > real:
+            logits = logits[:real]
 
         if self.device.type == "cuda":
             self._error_host.copy_(kernels.error_flag(self.device), non_blocking=True)
