@@ -524,7 +524,7 @@ __global__ void __launch_bounds__(A5_THREADS, 2) attention_prefill_tcgen05_kerne
 // 2^(m_p - M), M the largest, and out = sum_p w_p O_p / sum_p w_p l_p, parts in order.  A warp takes
 // one row (a lane four of its 128 values), a block 8 rows.
 constexpr int A5_MERGE_WARPS = 8;
-__global__ void __launch_bounds__(A5_MERGE_WARPS * 32) attention_prefill_merge_kernel(AttnArgs a, const int* __restrict__ merges) {
+__global__ void __launch_bounds__(A5_MERGE_WARPS * 32, 4) attention_prefill_merge_kernel(AttnArgs a, const int* __restrict__ merges) {
   pdl_trigger();
   pdl_wait();
   constexpr int BLOCKS_PER_TILE = A5_ROWS / A5_MERGE_WARPS;
@@ -539,25 +539,28 @@ __global__ void __launch_bounds__(A5_MERGE_WARPS * 32) attention_prefill_merge_k
   if (R >= n_rows) return;
   const int tok = R / G, head = R - tok * G;
   const size_t slot0 = ((size_t)first_part * a.nkv + kvh) * A5_ROWS + r, slot_step = (size_t)a.nkv * A5_ROWS;
-  // lane p holds part p's (maximum, sum); every lane asks for its four values of every part at once
+  // lane p holds part p's (maximum, sum); then every lane takes its four values of five parts at a
+  // time (a tile has five parts or fewer unless its step had very few tiles)
   float2 ml = make_float2(-INFINITY, 0.f);
   if (lane < n_parts) ml = __ldcg(reinterpret_cast<const float2*>(a.part_ml) + slot0 + lane * slot_step);
-  float4 o[15];
-#pragma unroll
-  for (int p = 0; p < 15; ++p)
-    if (p < n_parts) o[p] = __ldcg(reinterpret_cast<const float4*>(a.part_o + (slot0 + p * slot_step) * A5_D) + lane);
   float M = ml.x;
 #pragma unroll
   for (int off = 16; off > 0; off >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, off));
   const float w_mine = ml.x == -INFINITY ? 0.f : exp2f(ml.x - M);      // a part whose keys the row does not see brings nothing
   float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
   float L = 0.f;
+  for (int p0 = 0; p0 < n_parts; p0 += 5) {
+    float4 o[5];
 #pragma unroll
-  for (int p = 0; p < 15; ++p) {
-    const float w = __shfl_sync(0xffffffffu, w_mine, p), lp = __shfl_sync(0xffffffffu, ml.y, p);
-    if (p < n_parts && w > 0.f) {
-      L = fmaf(lp, w, L);
-      acc.x = fmaf(o[p].x, w, acc.x); acc.y = fmaf(o[p].y, w, acc.y); acc.z = fmaf(o[p].z, w, acc.z); acc.w = fmaf(o[p].w, w, acc.w);
+    for (int k = 0; k < 5; ++k)
+      if (p0 + k < n_parts) o[k] = __ldcg(reinterpret_cast<const float4*>(a.part_o + (slot0 + (p0 + k) * slot_step) * A5_D) + lane);
+#pragma unroll
+    for (int k = 0; k < 5; ++k) {
+      const float w = __shfl_sync(0xffffffffu, w_mine, (p0 + k) & 31), lp = __shfl_sync(0xffffffffu, ml.y, (p0 + k) & 31);
+      if (p0 + k < n_parts && w > 0.f) {
+        L = fmaf(lp, w, L);
+        acc.x = fmaf(o[k].x, w, acc.x); acc.y = fmaf(o[k].y, w, acc.y); acc.z = fmaf(o[k].z, w, acc.z); acc.w = fmaf(o[k].w, w, acc.w);
+      }
     }
   }
   const float inv = L > 0.f ? 1.0f / L : 0.f;
