@@ -444,42 +444,69 @@ class ModelRunner:
                     gt[real:, :] = 0
                     gt[real:, 0] = pad_cache.tables[g.index][0]
         else:
-            at = 0
+            # Any mix of runs and single tokens.  What is the same for every entry is filled for all
+            # at once; the single tokens at their default positions (the decoding requests beside a
+            # few prompt portions) too; only the runs, and tokens that bring positions, go one by one.
+            q = np.asarray(q_lens, dtype=np.int64)
+            ends = np.cumsum(q)
+            first = ends - q                               # where each entry's tokens begin
+            st = np.asarray(starts, dtype=np.int64)
+            cu[1:] = ends
+            tseq[:] = np.repeat(np.arange(S), q)
+            qs[:] = st
+            sl[:] = [e.request.cache.slot for e in entries]
+            linear = getattr(self.position, "default_is_linear", False)
+            single = np.fromiter((n == 1 and e.positions is None and linear for e, n in zip(entries, q_lens)),
+                                 dtype=bool, count=S)
+            last = np.zeros(S, dtype=np.int64)
+            if single.any():
+                which = np.nonzero(single)[0]
+                ids = np.fromiter((entries[i].tokens[0] for i in which), dtype=np.int64, count=len(which))
+                if ids.min() < 0 or ids.max() >= self.vocab_size:
+                    raise ValueError(f"token id outside [0, {self.vocab_size}) in a step")
+                place = st[which] + np.fromiter((entries[i].request.cache.position_offset for i in which), dtype=np.int64,
+                                                count=len(which))
+                tok[first[which]] = ids
+                pos[:, first[which]] = place
+                last[which] = place
             r = 0
             for i, (e, n, s) in enumerate(zip(entries, q_lens, starts)):
-                ids = np.asarray(e.tokens, dtype=np.int64)
-                if ids.min() < 0 or ids.max() >= self.vocab_size:
-                    raise ValueError(f"request {e.request.request_id!r}: token id outside [0, {self.vocab_size})")
-                tok[at:at + n] = ids
-                cache = e.request.cache
-                if e.positions is None:
-                    pos[:, at:at + n] = self.position.default_positions(s, n, cache.position_offset)
-                else:
-                    p = np.asarray(e.positions)
-                    k = p.shape[1] if p.ndim == 2 else -1
-                    if p.ndim != 2 or p.shape[0] != self.axes or not 0 < k <= n:
-                        raise ValueError(f"positions must be [{self.axes}, 1..{n}], got {p.shape}")
-                    pos[:, at:at + k] = p
-                    if k < n:     # plain text after tokens that brought their positions
-                        offset = self.position.offset_after(max(cache.max_position, int(p.max())), s + k)
-                        pos[:, at + k:at + n] = self.position.default_positions(s + k, n - k, offset)
-                last_position.append(int(pos[:, at:at + n].max()))
-                tseq[at:at + n] = i
-                cu[i + 1] = at + n
-                qs[i] = s
-                sl[i] = e.request.cache.slot
+                at = int(first[i])
+                if not single[i]:
+                    ids = np.asarray(e.tokens, dtype=np.int64)
+                    if ids.min() < 0 or ids.max() >= self.vocab_size:
+                        raise ValueError(f"request {e.request.request_id!r}: token id outside [0, {self.vocab_size})")
+                    tok[at:at + n] = ids
+                    cache = e.request.cache
+                    if e.positions is None:
+                        pos[:, at:at + n] = self.position.default_positions(s, n, cache.position_offset)
+                    else:
+                        p = np.asarray(e.positions)
+                        k = p.shape[1] if p.ndim == 2 else -1
+                        if p.ndim != 2 or p.shape[0] != self.axes or not 0 < k <= n:
+                            raise ValueError(f"positions must be [{self.axes}, 1..{n}], got {p.shape}")
+                        pos[:, at:at + k] = p
+                        if k < n:     # plain text after tokens that brought their positions
+                            offset = self.position.offset_after(max(cache.max_position, int(p.max())), s + k)
+                            pos[:, at + k:at + n] = self.position.default_positions(s + k, n - k, offset)
+                    last[i] = int(pos[:, at:at + n].max())
                 for w_ in e.want:
                     if not 0 <= int(w_) < n:
                         raise ValueError(f"wanted place {w_} is outside the {n} tokens of the entry")
                     rows[r] = at + int(w_)
                     r += 1
-                logical = np.arange(s, s + n)
-                for g, gs, gt in zip(groups, g_slot, g_tab):
-                    table = np.asarray(e.request.cache.tables[g.index], dtype=np.int64)
-                    gs[at:at + n] = table[logical // ps] * ps + logical % ps
-                    gt[i, :len(table)] = np.maximum(table, 0)
+            last_position = last.tolist()
+            for g, gs, gt in zip(groups, g_slot, g_tab):
+                for i, (e, n, s) in enumerate(zip(entries, q_lens, starts)):
+                    table = e.request.block_table(g.index)
+                    at = int(first[i])
+                    if n == 1:
+                        gs[at] = table[s // ps] * ps + s % ps
+                    else:
+                        logical = np.arange(s, s + n)
+                        gs[at:at + n] = table[logical // ps] * ps + logical % ps
+                    gt[i, :len(table)] = table
                     gt[i, len(table):] = 0
-                at += n
 
         return lambda tokens=None: self._run_packed(
             tokens, entries, q_lens, starts, widths, graph_key, off, N, S, M, ps, tok, tok_s, pos_s, tseq_s, cu_s, qs_s, sl_s,
