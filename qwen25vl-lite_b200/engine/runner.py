@@ -318,9 +318,15 @@ class ModelRunner:
     def launch_prepared(self, prepared, tokens: Sequence[int]) -> torch.Tensor:
         return prepared(tokens)
 
+    def drop_prepared(self, prepared) -> None:
+        """A prepared step that will not be launched: the page and slot of the rows that filled its
+        batch go back."""
+        self._close_padding()
+
     def _pack(self, entries: Sequence[StepEntry]):
         """Builds the step's arrays in the staging buffer; returns the function that runs the step
         (optionally with other token ids than the entries brought, for ``prepare_decode``)."""
+        self._close_padding()                               # of a prepared step that was never launched
         try:
             return self._pack_arrays(entries)
         except BaseException:

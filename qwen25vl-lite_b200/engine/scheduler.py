@@ -294,6 +294,8 @@ class LLMEngine:
             self.stats_.decode_tokens += decoded
             logits = self.runner.launch_prepared(prepared[0], [s.output_token_ids[-1] for s in samplers])
         else:
+            if prepared is not None:
+                self._drop(prepared)                       # the batch changed: what was packed ahead is void
             scheduled = self.schedule()
             by_id = {s.seq_id: s for s in self.running}
             for seq_id, n in scheduled.items():
@@ -329,7 +331,8 @@ class LLMEngine:
             for seq, token in zip(samplers, tokens):
                 if seq.status == "running":                # a request aborted while its step ran draws nothing
                     self._accept(seq, int(token), done)
-            if done:
+            if done and self._prepared is not None:
+                self._drop(self._prepared)
                 self._prepared = None
         self.stats_.steps += 1
         self.stats_.record_step(time.perf_counter() - t0, decoded)
@@ -358,6 +361,12 @@ class LLMEngine:
         except OutOfPages:
             return None
         return runner.prepare_decode([seq.request for seq in self.running]), [s.seq_id for s in self.running]
+
+    def _drop(self, prepared) -> None:
+        """A step that was packed ahead and will not run: the runner takes back what it held for it."""
+        drop = getattr(self.runner, "drop_prepared", None)
+        if drop is not None:
+            drop(prepared[0])
 
     def _ends(self, seq: Sequence, token: int) -> bool:
         """Whether this token, drawn now, ends the request by what it is (ends by length are known

@@ -254,3 +254,30 @@ def test_generate_with_random_weights_from_the_command_line(model_dirs):
     cmd[cmd.index("7")] = "8"
     other = subprocess.run(cmd, cwd=ROOT, capture_output=True, text=True, timeout=300)
     assert other.returncode == 0 and len(eval(other.stdout.strip().splitlines()[-1])) == 4
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_padded_batches_and_requests_that_end_by_their_token(model_dirs, tmp_path, dtype):
+    """11 requests decode together: captured steps run them as 16 rows, the five added rows on a
+    page and slot of their own.  One token in 16 ends a request, so requests end by their
+    token while the next step is packed ahead, and that step (with its page) is dropped; the batch
+    shrinks through 10 and 9 rows (still 16) into the chained products' 8.  Every page and slot
+    comes back; in 32-bit, whose sums do not depend on the batch, every request's tokens are those
+    of the same request generated alone."""
+    from qwen25vl_lite import LLM, SamplingParams
+    from tiny_models import make_model_dir
+    folder = model_dirs["B"] if dtype == "float32" else make_model_dir(tmp_path, "B", "bfloat16")
+    prompts = _prompts("B", (9, 23, 5, 40, 17, 3, 31, 12, 26, 7, 19), 31)
+    stops = tuple(range(0, 512, 16))
+    params = SamplingParams(max_tokens=40, temperature=0.9, seed=5, stop_token_ids=stops)
+    llm = LLM(folder, dtype=dtype, num_blocks=96, block_size=8, max_num_seqs=12)
+    outs = llm.generate(prompts, params)
+    assert llm.runner.graph_replays > 0
+    assert "stop" in [o.finish_reason for o in outs]
+    assert llm.runner.cache.pages_in_use() == [0] and llm.runner.cache.free_slots == 12
+    llm.runner.cache.check([])
+    if dtype == "float32":
+        alone = LLM(folder, dtype=dtype, num_blocks=96, block_size=8, max_num_seqs=12, cuda_graph=False)
+        for p, o in zip(prompts, outs):
+            ref = alone.generate([p], params)[0]
+            assert ref.output_token_ids == o.output_token_ids and ref.finish_reason == o.finish_reason
