@@ -233,21 +233,45 @@ def test_abort_and_stats():
 
 # ---- the next decode step packed while this one runs ------------------------------------------------
 class PreparingRunner(FakeRunner):
-    """A step function that also offers ``prepare_decode`` / ``launch_prepared`` and counts them."""
+    """A step function that also offers ``prepare_decode`` / ``launch_prepared`` and counts them.  Like
+    the engine's own it holds something for a prepared step (a request of one page, when a slot and
+    a page are free) until that step is launched or the engine says it is dropped."""
 
-    prepared = launched = 0
+    prepared = launched = dropped = 0
+    held = None
+
+    def _release(self):
+        if self.held is not None:
+            self.cache.close(self.held)
+            self.held = None
+
+    def step(self, entries):
+        assert self.held is None, "a prepared step was neither launched nor dropped before the next step"
+        return super().step(entries)
 
     def prepare_decode(self, requests):
         self.prepared += 1
+        assert self.held is None, "a prepared step was neither launched nor dropped before the next was prepared"
         for r in requests:
             assert self.cache.pages_missing(r.cache, r.cache.num_tokens + 1) == [0]      # the engine took the pages first
+        if self.cache.free_slots:
+            self.held = self.cache.open()
+            if self.cache.can_hold(self.held, 1):
+                self.cache.ensure(self.held, 1)
+            else:
+                self._release()
         return list(requests)
 
     def launch_prepared(self, prepared, tokens):
         from qwen25vl_lite.engine.runner import StepEntry
         self.launched += 1
+        self._release()
         assert len(tokens) == len(prepared)
         return self.step([StepEntry(r, [t], [0]) for r, t in zip(prepared, tokens)])
+
+    def drop_prepared(self, prepared):
+        self.dropped += 1
+        self._release()
 
 
 class AsyncSampler(FakeSampler):
@@ -267,7 +291,7 @@ def test_prepared_decode_steps_change_nothing():
     lengths = [9, 14, 5, 11]
     eos = next_token([5, 6, 7] + expected([5, 6, 7], 4))                    # request 0 ends by its 5th token
     ecfg = EngineConfig(num_blocks=64, block_size=4, max_num_seqs=3)
-    runner = PreparingRunner(64, 4, ecfg.max_num_seqs)
+    runner = PreparingRunner(64, 4, ecfg.max_num_seqs + 1)
     engine = LLMEngine(runner, AsyncSampler(), ecfg, eos_token_id=eos)
     runner._requests = _LiveView(engine)
     ids = [engine.add_request(p, SamplingParams(max_tokens=n, ignore_eos=i != 0)) for i, (p, n) in enumerate(zip(prompts[:3], lengths))]
@@ -280,7 +304,8 @@ def test_prepared_decode_steps_change_nothing():
             outs[o.seq_id] = o
         if not engine.has_work():
             break
-    assert runner.launched > 5 and runner.prepared >= runner.launched          # some preparations were dropped
+    assert runner.launched > 5 and runner.prepared >= runner.launched         # preparations may be dropped,
+    assert runner.dropped == runner.prepared - runner.launched                # and the step function was told of each
     want0 = expected(prompts[0], lengths[0])
     assert outs[ids[0]].output_token_ids == want0[:want0.index(eos) + 1] and outs[ids[0]].finish_reason == "stop"
     for i in (1, 2):
@@ -295,7 +320,7 @@ def test_next_step_is_launched_before_the_bookkeeping_and_survives_an_abort():
     such a step runs draws nothing from it; the others go on as if nothing had happened."""
     prompts = [[5, 6, 7], list(range(20, 31)), [9] * 6]
     ecfg = EngineConfig(num_blocks=64, block_size=4, max_num_seqs=3)
-    runner = PreparingRunner(64, 4, ecfg.max_num_seqs)
+    runner = PreparingRunner(64, 4, ecfg.max_num_seqs + 1)
     engine = LLMEngine(runner, AsyncSampler(), ecfg, eos_token_id=None)
     runner._requests = _LiveView(engine)
     ids = [engine.add_request(p, SamplingParams(max_tokens=12, ignore_eos=True)) for p in prompts]
@@ -328,7 +353,7 @@ def test_random_arrivals_stops_and_aborts_with_steps_packed_and_launched_ahead(s
     import random
     rng = random.Random(seed)
     ecfg = EngineConfig(num_blocks=40, block_size=4, max_num_seqs=4, max_num_batched_tokens=16)
-    runner = PreparingRunner(40, 4, ecfg.max_num_seqs)
+    runner = PreparingRunner(40, 4, ecfg.max_num_seqs + 1)
     engine = LLMEngine(runner, AsyncSampler(), ecfg, eos_token_id=None)
     runner._requests = _LiveView(engine)
     plans, outs, aborted = {}, {}, set()
@@ -360,5 +385,5 @@ def test_random_arrivals_stops_and_aborts_with_steps_packed_and_launched_ahead(s
         want = full[:full.index(stop) + 1] if stop is not None else full
         assert outs[sid].output_token_ids == want, (sid, prompt, n, stop)
         assert outs[sid].finish_reason == ("stop" if stop is not None else "length")
-    assert runner.launched > 0
+    assert runner.launched > 0 and runner.dropped == runner.prepared - runner.launched and runner.held is None
     runner.cache.check([])
