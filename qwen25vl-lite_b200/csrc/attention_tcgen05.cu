@@ -22,10 +22,12 @@
 // V(t) when tile t begins and waits for them when its softmax of tile t is done, so in the steady
 // state it waits for no product and no copy.  The output accumulates in tensor memory over all
 // tiles; the exponentials use a lazy maximum (see below), so it is rescaled only rarely.
-// A step takes as long as its longest walk, so the host cuts the keys of long row tiles into parts
-// (ops/attention.py: split_keys): a CTA then walks one part and leaves its unnormalised output rows
-// with their maxima and sums in scratch memory, and attention_prefill_merge_kernel adds the parts of
-// a tile up, in the order of the parts.
+// A step takes as long as its longest walk, so where a step has few row tiles the host cuts their keys
+// (ops/attention.py: cut_keys).  Either into parts: a CTA then walks one part and leaves its
+// unnormalised output rows with their maxima and sums in scratch memory, and
+// attention_prefill_merge_kernel adds the parts of a tile up, in the order of the parts.  Or between
+// the two CTAs of a cluster, which take half of a tile's keys each and add up through the cluster's
+// shared memory.
 // Two CTAs fit an SM (99 KB of shared memory, 256 of the 512 tensor-memory columns each).  (Two row
 // tiles to a CTA, which halve the key and value traffic per row, were slower at every length tried:
 // 8,192 tokens 375 against 298 us.  So were two threads to a row, 32 keys of a tile each, their maxima

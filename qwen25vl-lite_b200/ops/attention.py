@@ -27,7 +27,6 @@ import torch
 
 from . import kernels
 
-PREFILL_TILE_ROWS = (64, 128)   # row tiles of the two prefill attention kernels (mma.sync, tcgen05)
 KEY_TILE = 64                   # keys per iteration of the tcgen05 prefill kernel
 MIN_PART_TILES = 4              # a row tile's keys are cut into parts of at least this many key tiles
 MIN_CUT_WALK = 24               # in steps whose longest walk has this many key tiles
