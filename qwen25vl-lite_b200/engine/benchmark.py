@@ -140,6 +140,7 @@ def run_trace(engine, prompts: Sequence[Sequence[int]], output_lengths: Sequence
     for p, n in zip(prompts, output_lengths):
         engine.add_request(p, SamplingParams(max_tokens=int(n), ignore_eos=True))
     before = len(engine.finished)
+    stats0 = engine.stats()
     engine.run_until_complete()
     torch.cuda.synchronize()
     wall = time.perf_counter() - t0
@@ -150,8 +151,8 @@ def run_trace(engine, prompts: Sequence[Sequence[int]], output_lengths: Sequence
     stats = engine.stats()
     return {"requests": len(outs), "wall_s": wall, "prompt_tokens": prompt_tokens, "generated_tokens": generated,
             "generated_tokens_per_s": generated / wall, "total_tokens_per_s": (generated + prompt_tokens) / wall,
-            "ttft_s_median": ttft[len(ttft) // 2], "ttft_s_max": ttft[-1], "steps": stats["steps"],
-            "preemptions": stats["preemptions"],
+            "ttft_s_median": ttft[len(ttft) // 2], "ttft_s_max": ttft[-1], "steps": stats["steps"] - stats0["steps"],
+            "preemptions": stats["preemptions"] - stats0["preemptions"],
             # the reference's figure: generated tokens over the wall time after the last first token
             "decode_tokens_per_s_after_ttft": generated / max(wall - ttft[-1], 1e-9)}
 
