@@ -20,7 +20,7 @@ the device copies back through ``ctx.plan(part)``.
 
 from __future__ import annotations
 
-from typing import Dict
+from typing import Dict, Optional
 
 import numpy as np
 import torch
@@ -185,9 +185,11 @@ def attend(ctx, plan, qkv, kv, position, nq: int, nkv: int, head_dim: int, windo
     group = nq // nkv
     tables = position.rope_tables()
     decode_items = plan.get("decode_items")
-    if (store and tables is not None and decode_items is not None and decode_items.shape[0] == ctx.n_seqs
-            and plan.get("tiles64") is None
+    out = None
+    if (store and tables is not None and decode_items is not None
             and kernels.attention_fused_supports(qkv.dtype, head_dim, kv.page_size, group)):
+        # The entries of one token go through the fused kernel, which rotates q and k, stores k and
+        # v and attends by itself, from qkv as projected.
         inv_freq, axis = tables
         # the angles are the same for every layer of the step that shares the tables: the first
         # one to ask computes them
@@ -196,22 +198,32 @@ def attend(ctx, plan, qkv, kv, position, nq: int, nkv: int, head_dim: int, windo
         if angles is None:
             angles = ctx.shared[key] = kernels.rope_angles(ctx.positions, inv_freq, axis)
         out = torch.empty((qkv.shape[0], nq * head_dim), dtype=qkv.dtype, device=qkv.device)
+        n_items = decode_items.shape[0]
+        alone = n_items == ctx.n_seqs and plan.get("tiles64") is None
         visible = min(ctx.max_kv_len, window) if window else ctx.max_kv_len
-        splits = decode_splits(ctx.n_seqs, nkv, visible)
-        scratch = _scratch_floats(ctx.n_seqs * nq * splits * (head_dim + 2), qkv.device) if splits > 1 else None
+        splits = decode_splits(n_items, nkv, visible)
+        scratch = _scratch_floats(n_items * nq * splits * (head_dim + 2), qkv.device) if splits > 1 else None
         kernels.attention_decode_fused(qkv, out, kv.k_pages, kv.v_pages, kv.block_table, ctx.cu_q, ctx.q_start_pos,
                                        decode_items, nq, nkv, head_dim, kv.page_size, window, scale, splits,
                                        ctx.positions, inv_freq, axis, kv.kv_slot, scratch, angles,
-                                       dense=True)          # every entry of the step is one token, in order
-        return out
+                                       dense=alone)          # every entry of the step is one token, in order
+        if alone:
+            return out
+        # The runs beside them: q and k of all tokens are rotated now (the single tokens' too, whose
+        # rows of the output are written already, and their keys and values are stored a second
+        # time with the same values), then the runs' kernels fill their rows.
     position.rotate_and_store(ctx, qkv, nq, nkv, head_dim, kv if store else None)
-    return paged_attention(ctx, plan, qkv, kv, nq, nkv, head_dim, window, scale)
+    return paged_attention(ctx, plan, qkv, kv, nq, nkv, head_dim, window, scale, out)
 
 
-def paged_attention(ctx, plan, qkv, kv, nq: int, nkv: int, head_dim: int, window, scale: float) -> torch.Tensor:
+def paged_attention(ctx, plan, qkv, kv, nq: int, nkv: int, head_dim: int, window, scale: float,
+                    out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """qkv: [N, (nq + 2 nkv) * D] with q already position-encoded and this step's keys and
-    values already in the pages.  Returns [N, nq * D]."""
-    out = torch.empty((qkv.shape[0], nq * head_dim), dtype=qkv.dtype, device=qkv.device)
+    values already in the pages.  Returns [N, nq * D].  ``out``: the result with the rows of the
+    one-token entries already written (only the runs are left to do)."""
+    single_done = out is not None
+    if out is None:
+        out = torch.empty((qkv.shape[0], nq * head_dim), dtype=qkv.dtype, device=qkv.device)
     window = int(window or 0)
     group = nq // nkv
     if not kernels.attention_mma_supports(qkv.dtype, head_dim, kv.page_size):
@@ -219,7 +231,7 @@ def paged_attention(ctx, plan, qkv, kv, nq: int, nkv: int, head_dim: int, window
                                         ctx.q_start_pos, nq, nkv, head_dim, kv.page_size, window, scale)
         return out
     decode_items = plan.get("decode_items")
-    if decode_items is not None:
+    if decode_items is not None and not single_done:
         n_items = decode_items.shape[0]
         visible = min(ctx.max_kv_len, window) if window else ctx.max_kv_len
         splits = decode_splits(n_items, nkv, visible)
