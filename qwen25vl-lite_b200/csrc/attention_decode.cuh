@@ -1,6 +1,6 @@
-// Device code shared by the attention kernels (attention_mma.cu) and the chain kernel
-// (gemm_chain.cu): the argument structs, the tensor-core helpers, one tile of FlashAttention-style
-// attention, and the fused decode attention unit.
+// Device code shared by the attention kernels (attention_mma.cu, attention_tcgen05.cu): the argument
+// structs, the tensor-core helpers, one tile of FlashAttention-style attention, and the fused decode
+// attention unit.
 #pragma once
 
 #include "common.cuh"
@@ -303,9 +303,8 @@ __device__ __forceinline__ unsigned rotate_pair_hi(unsigned x1, unsigned x2, flo
 // ------------------------------------------------------------------------------------------------
 // One (entry, kv head, key range) unit of the fused decode attention, run by WARPS warps whose
 // threads are numbered tid = 0 .. WARPS*32-1 and meet at sync().  It is the body of
-// attention_decode_fused_kernel (WARPS = 4, 32-key tiles, two stages per warp) and an operation of
-// the chain kernel (gemm_chain.cu: WARPS = 8, 16-key tiles, one stage per warp, so that it fits
-// beside the ring of weights).  Position encoding of q and the new k, the write of the new key and
+// attention_decode_fused_kernel (8 warps, or 4 where that lets all CTAs run at once; 16-key tiles,
+// three stages per warp).  Position encoding of q and the new k, the write of the new key and
 // value into the pages, attention over the unit's key range, the merge of the warps, and the merge
 // of the ranges by the unit that counts itself in last (nobody waits).  Rotation as in
 // rope_cache.cu (reference src/qwen25vl_lite/rope.py:48-96).
