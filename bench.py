@@ -52,6 +52,11 @@ FULL_LAYERS = 36
 PROMPT_LEN = 2048
 CONTEXT_LEN = 4096
 PAGE = 16
+# Seconds of rest between a timed decode loop's prompts and its warm-up steps: the prompts' products run
+# at the power cap and leave the SM clock lowered for some tens of milliseconds, which 20 timed
+# steps of 2 ms would spend at 1.6 to 1.9 GHz instead of the 1.965 GHz decode steps run at by
+# themselves (2.18 to 2.45 ms a step without the rest, 2.05 ms with it or over 256 steps).
+SETTLE_S = 0.25
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 
 
@@ -71,16 +76,82 @@ def load_peaks():
 
 
 class ClockSampler:
-    """Samples SM clocks and throttle reasons with nvidia-smi while a region is timed."""
+    """Samples SM clocks and throttle reasons while a region is timed: through NVML in a thread of this
+    process (what ``nvidia-smi --query-gpu=clocks.sm,clocks.max.sm,clocks_event_reasons...`` reads,
+    without the tool).  ``nvidia-smi -lms`` beside the run held the GPU for 2 to 4 ms at each of its
+    polls: over 20 timed steps of 2 ms that was 4 to 10 % of the figure; a poll through NVML takes
+    tens of microseconds.  Falls back to ``nvidia-smi`` where the NVML binding is missing."""
 
     QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    NAMES = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+    INTERVAL_S = 0.05
 
     def __init__(self):
         self.proc = None
         self.lines = []
+        self.samples = []          # (sm MHz, max MHz, reason bits) from NVML
+        self._stop = threading.Event()
+        self._thread = None
+        self._nvml = None
+
+    # ---- NVML ----
+    def _nvml_handle(self):
+        import pynvml
+        pynvml.nvmlInit()
+        try:
+            import torch
+            uuid = str(torch.cuda.get_device_properties(torch.cuda.current_device()).uuid)
+            return pynvml, pynvml.nvmlDeviceGetHandleByUUID(("GPU-" + uuid).encode())
+        except Exception:
+            return pynvml, pynvml.nvmlDeviceGetHandleByIndex(0)
+
+    def _sample(self):
+        nv, h = self._nvml
+        reasons = nv.nvmlDeviceGetCurrentClocksEventReasons(h)
+        self.samples.append((nv.nvmlDeviceGetClockInfo(h, nv.NVML_CLOCK_SM), nv.nvmlDeviceGetMaxClockInfo(h, nv.NVML_CLOCK_SM),
+                             int(reasons)))
+
+    def _poll(self):
+        while not self._stop.wait(self.INTERVAL_S):
+            try:
+                self._sample()
+            except Exception:
+                return
 
     def start(self):
+        """Returns when the sampler runs (NVML loaded and a first sample taken, which is dropped)."""
+        try:
+            self._nvml = self._nvml_handle()
+            self._sample()
+            del self.samples[:]
+            self._thread = threading.Thread(target=self._poll, daemon=True)
+            self._thread.start()
+            return
+        except Exception:
+            self._nvml = None
+        self._start_tool()
+
+    def stop(self):
+        if self._nvml is not None:
+            try:
+                self._sample()                        # at least one sample, taken under load: the region has just ended
+            except Exception:
+                pass
+            self._stop.set()
+            if self._thread is not None:
+                self._thread.join(timeout=2.0)
+            nv = self._nvml[0]
+            bits = {"hw_slowdown": nv.nvmlClocksEventReasonHwSlowdown, "hw_thermal_slowdown": nv.nvmlClocksEventReasonHwThermalSlowdown,
+                    "sw_thermal_slowdown": nv.nvmlClocksEventReasonSwThermalSlowdown, "sw_power_cap": nv.nvmlClocksEventReasonSwPowerCap}
+            mhz = [m for m, _, _ in self.samples]
+            reasons = sorted(n for n, bit in bits.items() if any(r & bit for _, _, r in self.samples))
+            return {"sm_mhz": statistics.median(mhz) if mhz else None, "sm_max_mhz": self.samples[0][1] if self.samples else None,
+                    "reasons": reasons, "samples": len(mhz), "source": "nvml"}
+        return self._stop_tool()
+
+    # ---- nvidia-smi, where there is no NVML binding ----
+    def _start_tool(self):
         """Returns when the first sample has come (or after five seconds): nvidia-smi's own start
         can hold the driver for up to a second, which must not fall into what is timed."""
         try:
@@ -99,23 +170,22 @@ class ClockSampler:
         for line in self.proc.stdout:
             self.lines.append(line.strip())
 
-    def stop(self):
+    def _stop_tool(self):
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
         self.proc.terminate()
         mhz, mx, reasons = [], None, set()
-        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
         for line in self.lines:
             parts = [p.strip() for p in line.split(",")]
             if len(parts) < 6 or not parts[0].isdigit():
                 continue
             mhz.append(int(parts[0]))
             mx = int(parts[1]) if parts[1].isdigit() else mx
-            for n, v in zip(names, parts[2:6]):
+            for n, v in zip(self.NAMES, parts[2:6]):
                 if v.lower().startswith("active"):
                     reasons.add(n)
         return {"sm_mhz": statistics.median(mhz) if mhz else None, "sm_max_mhz": mx, "reasons": sorted(reasons),
-                "samples": len(mhz)}
+                "samples": len(mhz), "source": "nvidia-smi"}
 
 
 def run_reference(args):
@@ -167,6 +237,8 @@ def run_reference(args):
         with torch.no_grad():
             while engine.waiting or any(s.num_computed_tokens < len(s.prompt_token_ids) for s in engine.running):
                 engine.step()
+            torch.cuda.synchronize()
+            time.sleep(SETTLE_S)                           # the same rest as our own arm gets
             for _ in range(args.warmup):
                 engine.step()
             clocks = ClockSampler()
@@ -191,7 +263,8 @@ def run_reference(args):
                        "hidden": t["hidden_size"], "q_heads": t["num_attention_heads"], "kv_heads": t["num_key_value_heads"],
                        "head_dim": d, "intermediate": t["intermediate_size"], "vocab": t["vocab_size"], "global_batch": 8,
                        "seq_len": CONTEXT_LEN, "prompt_len": PROMPT_LEN, "kv_page": PAGE, "parallelism": "single GPU",
-                       "l2": "weights read per step exceed L2 (126 MB)", "peaks": load_peaks()["source"]},
+                       "l2": "weights read per step exceed L2 (126 MB)", "peaks": load_peaks()["source"],
+                       "settle_ms": int(SETTLE_S * 1e3)},
             "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": None, "d2h_bytes_per_step": None},
             "clocks": clock_record}))
     except Exception as exc:  # the reference could not run here: say why, in one line
@@ -206,7 +279,7 @@ def _base_line(metric, value, args, ms_per_step, cfg, layers, batch, seq_len, pr
               "kv_heads": t["num_key_value_heads"], "head_dim": t["hidden_size"] // t["num_attention_heads"],
               "intermediate": t["intermediate_size"], "vocab": t["vocab_size"], "global_batch": batch, "seq_len": seq_len,
               "prompt_len": prompt_len, "kv_page": PAGE, "parallelism": "single GPU",
-              "l2": "weights read per step exceed L2 (126 MB)", "peaks": peaks["source"]}
+              "l2": "weights read per step exceed L2 (126 MB)", "peaks": peaks["source"], "settle_ms": int(SETTLE_S * 1e3)}
     config.update(extra_config or {})
     return {"metric": metric, "value": value, "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
@@ -240,21 +313,21 @@ def run_ours(args):
                "frac": B.prefill_flops(t, layers, PROMPT_LEN) / (prefill_ms / 1e3) / (peaks["bf16_tflops"] * 1e12)}
 
     if args.only_batch:             # for profiler runs at another batch size: that decode loop alone, a short line
-        r = B.time_decode_steps(runner, args.only_batch, PROMPT_LEN, args.steps, args.warmup, vocab, rng)
+        r = B.time_decode_steps(runner, args.only_batch, PROMPT_LEN, args.steps, args.warmup, vocab, rng, settle_s=SETTLE_S)
         print(json.dumps({"decode_batch": args.only_batch, "tokens_per_s": r["tokens_per_s"], "ms_per_step": r["ms_per_step"],
                           "layers": layers, "context": r["context"], "gpu_launches": r["launches"]}))
         return 0
     clocks = ClockSampler()
     clocks.start()
-    head = B.time_decode_steps(runner, 8, PROMPT_LEN, args.steps, args.warmup, vocab, rng)
+    head = B.time_decode_steps(runner, 8, PROMPT_LEN, args.steps, args.warmup, vocab, rng, settle_s=SETTLE_S)
     clock_record = clocks.stop()
     points = {}
     if args.headline_only:          # for profiler runs: the headline loop and the prefill alone
         e2e_value = None
     else:
-        e2e_value = B.time_decode_e2e(engine, 8, PROMPT_LEN, args.steps, args.warmup, vocab, rng)
+        e2e_value = B.time_decode_e2e(engine, 8, PROMPT_LEN, args.steps, args.warmup, vocab, rng, settle_s=SETTLE_S)
         for b in (1, 16, 17, 32, 64):      # every point over as many steps as the headline
-            points[f"decode_b{b}"] = B.time_decode_steps(runner, b, PROMPT_LEN, args.steps, args.warmup, vocab, rng)["tokens_per_s"]
+            points[f"decode_b{b}"] = B.time_decode_steps(runner, b, PROMPT_LEN, args.steps, args.warmup, vocab, rng, settle_s=SETTLE_S)["tokens_per_s"]
 
     ctx = head["context"]
     step_bytes = B.weight_bytes(t, layers, element) + 8 * ctx * B.kv_bytes_per_token(t, layers, element)
@@ -307,7 +380,7 @@ def run_32b(args):
     clocks.start()
     points, roofs, launches = {}, {}, 0
     for b in (8, 1, 32):
-        r = B.time_decode_steps(llm.runner, b, prompt_len, args.steps, args.warmup, vocab, rng, prefill_group=1)
+        r = B.time_decode_steps(llm.runner, b, prompt_len, args.steps, args.warmup, vocab, rng, prefill_group=1, settle_s=SETTLE_S)
         points[f"decode_b{b}"] = r["tokens_per_s"]
         step_bytes = B.weight_bytes(t, layers) + b * r["context"] * B.kv_bytes_per_token(t, layers)
         roofs[f"decode_b{b}"] = step_bytes / (r["ms_per_step"] / 1e3) / 1e9 / peaks["hbm_gbs"]

@@ -77,7 +77,7 @@ def time_prefill(runner, n_tokens: int, vocab: int, rng, warmup: int = 3, repeat
 
 
 def time_decode_steps(runner, batch: int, prompt_len: int, steps: int, warmup: int, vocab: int, rng,
-                      prefill_group: int = 4) -> Dict[str, float]:
+                      prefill_group: int = 4, settle_s: float = 0.0) -> Dict[str, float]:
     """``steps`` decode steps of ``batch`` requests (after prompts of ``prompt_len``), fed
     back-to-back with given tokens and each followed by the greedy draw, timed on the device."""
     reqs = [runner.open_request(f"d{i}") for i in range(batch)]
@@ -86,6 +86,11 @@ def time_decode_steps(runner, batch: int, prompt_len: int, steps: int, warmup: i
         runner.step([StepEntry(r, p, []) for r, p in zip(reqs[i:i + prefill_group], prompts[i:i + prefill_group])])
     feed = rng.integers(0, vocab, size=(steps + warmup, batch))
     out = torch.empty(batch, dtype=torch.int32, device=runner.device)
+    if settle_s > 0:
+        # The prompts' products run at the power cap and leave the SM clock lowered for some tens of
+        # milliseconds; decode steps are what is measured, at the clock they run at by themselves.
+        torch.cuda.synchronize()
+        time.sleep(settle_s)
 
     def one(k):
         logits = runner.step([StepEntry(r, [int(feed[k, i])], [0]) for i, r in enumerate(reqs)])
@@ -110,7 +115,7 @@ def time_decode_steps(runner, batch: int, prompt_len: int, steps: int, warmup: i
             "context": prompt_len + warmup + steps // 2}
 
 
-def time_decode_e2e(engine, batch: int, prompt_len: int, steps: int, warmup: int, vocab: int, rng) -> float:
+def time_decode_e2e(engine, batch: int, prompt_len: int, steps: int, warmup: int, vocab: int, rng, settle_s: float = 0.0) -> float:
     """Decoded tokens a second through the scheduler: host token ids in, sampled ids out, every
     step; timed with the wall clock around ``steps`` calls of ``engine.step()``."""
     params = SamplingParams(max_tokens=warmup + steps + 8, ignore_eos=True)
@@ -118,6 +123,9 @@ def time_decode_e2e(engine, batch: int, prompt_len: int, steps: int, warmup: int
         engine.add_request(p, params)
     while engine.waiting or any(s.pending > 1 for s in engine.running):
         engine.step()
+    if settle_s > 0:                     # as in time_decode_steps: the clock the prompts left lowered comes back
+        torch.cuda.synchronize()
+        time.sleep(settle_s)
     for _ in range(warmup):
         engine.step()
     torch.cuda.synchronize()
