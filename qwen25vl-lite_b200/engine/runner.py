@@ -315,8 +315,11 @@ class ModelRunner:
         ``launch_prepared`` only has to add the token ids.  Nothing else may be stepped between."""
         return self._pack([StepEntry(r, (0,), (0,)) for r in requests])
 
-    def launch_prepared(self, prepared, tokens: Sequence[int]) -> torch.Tensor:
-        return prepared(tokens)
+    def launch_prepared(self, prepared, tokens: Optional[Sequence[int]], device_ids: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """Runs a prepared step with its token ids: from the host (``tokens``), or from the device
+        (``device_ids`` int32, one per request in order: the ids the sampler has just drawn, which
+        the step then reads without their trip to the host and back)."""
+        return prepared(tokens, device_ids)
 
     def drop_prepared(self, prepared) -> None:
         """A prepared step that will not be launched: the page and slot of the rows that filled its
@@ -514,9 +517,9 @@ class ModelRunner:
                     gt[i, :len(table)] = table
                     gt[i, len(table):] = 0
 
-        return lambda tokens=None: self._run_packed(
+        return lambda tokens=None, device_ids=None: self._run_packed(
             tokens, entries, q_lens, starts, widths, graph_key, off, N, S, M, ps, tok, tok_s, pos_s, tseq_s, cu_s, qs_s, sl_s,
-            rows_s, g_slot_s, g_tab_s, plan_s, last_position, pad_cache)
+            rows_s, g_slot_s, g_tab_s, plan_s, last_position, pad_cache, device_ids)
 
     def _open_padding(self):
         """A request of one token for the rows that fill a captured step's batch, or None when no
@@ -533,8 +536,11 @@ class ModelRunner:
         return cache
 
     def _run_packed(self, tokens, entries, q_lens, starts, widths, graph_key, off, N, S, M, ps, tok, tok_s, pos_s, tseq_s,
-                    cu_s, qs_s, sl_s, rows_s, g_slot_s, g_tab_s, plan_s, last_position, pad_cache=None):
+                    cu_s, qs_s, sl_s, rows_s, g_slot_s, g_tab_s, plan_s, last_position, pad_cache=None, device_ids=None):
         real = len(entries)
+        if device_ids is not None and (tokens is not None or S != N or device_ids.dtype != torch.int32
+                                       or device_ids.numel() < real or device_ids.device != self.device):
+            raise ValueError(f"a prepared step takes {real} int32 token ids on {self.device}, or ids from the host")
         if tokens is not None:
             ids = np.asarray(tokens, dtype=np.int64)
             if ids.shape != (real,) or S != N or ids.min() < 0 or ids.max() >= self.vocab_size:
@@ -542,6 +548,8 @@ class ModelRunner:
             tok[:real] = ids
         dev = self._device_ints
         dev[:off].copy_(self._staging[:off], non_blocking=True)
+        if device_ids is not None:
+            dev[tok_s[0]:tok_s[0] + real].copy_(device_ids[:real], non_blocking=True)
         if self._staging_free is not None:
             self._staging_free.record()
 

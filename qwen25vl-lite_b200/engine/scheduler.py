@@ -275,9 +275,12 @@ class LLMEngine:
 
         While the device runs a step whose requests will all decode one more token, the host
         already packs the next step (pages, block tables, positions: everything but the token
-        ids), so that between two decode steps only the sampled ids have to travel.  When those ids
-        end no request, that next step is even launched before this call does its bookkeeping and
-        returns (``_launched``): the next call starts at its sampling."""
+        ids), so that between two decode steps only the sampled ids have to travel.  With a sampler
+        that says where the drawn ids lie on the device, that next step is launched at once and reads
+        them there, before the host has them; a request that its id then ends draws nothing from the
+        step that is already running.  Otherwise, when the ids (on the host) end no request, the next
+        step is launched before this call does its bookkeeping and returns.  Either way the next call
+        starts at that step's sampling (``_launched``)."""
         t0 = time.perf_counter()
         prepared, self._prepared = self._prepared, None
         launched, self._launched = self._launched, None
@@ -319,6 +322,15 @@ class LLMEngine:
             if hasattr(self.sampler, "sample_async"):
                 pending = self.sampler.sample_async(*args)
                 self._prepared = self._prepare_next(samplers)          # host work under the device's step
+                ids = getattr(self.sampler, "device_ids", lambda p: None)(pending)
+                if self._prepared is not None and ids is not None:
+                    # The drawn ids are on the device and the next step is packed: it goes to the
+                    # device now and reads them there, before they have reached the host.  A
+                    # request that its id then turns out to end draws nothing from that step (as
+                    # one that is aborted while its step runs); nobody ends by length here, or
+                    # nothing would have been prepared.
+                    next_logits = self.runner.launch_prepared(self._prepared[0], None, device_ids=ids)
+                    self._launched, self._prepared = (next_logits, samplers), None
                 tokens = self.sampler.collect(pending)
                 self._check_step()                         # the step's results are on the host: was it whole?
                 if self._prepared is not None and not any(self._ends(seq, int(tok)) for seq, tok in zip(samplers, tokens)):

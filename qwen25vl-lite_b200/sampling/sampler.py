@@ -73,16 +73,22 @@ class Sampler:
         """Waits for the draw that ``sample_async`` started and returns its token ids."""
         if pending is None:
             return []
-        host, event, rows = pending
+        host, event, rows = pending[:3]
         if event is None:
             return host
         event.synchronize()
         return host[:rows].tolist()
 
+    @staticmethod
+    def device_ids(pending):
+        """The ids a pending draw leaves on the device (int32 [rows]), for a next step that is fed
+        from there before the ids have reached the host; None when there are none."""
+        return pending[3] if isinstance(pending, tuple) and len(pending) > 3 else None
+
     def sample_async(self, logits: torch.Tensor, params: Sequence[SamplingParams], seeds: Sequence[int],
                      token_indices: Sequence[int], previous: Optional[Sequence[Sequence[int]]] = None):
         """Starts the draw and the copy of its result to pinned host memory; the host is free until
-        ``collect``."""
+        ``collect``.  Returns (pinned ids, event of the copy, rows, ids on the device)."""
         rows = logits.shape[0]
         if rows == 0:
             return None
@@ -120,10 +126,10 @@ class Sampler:
                                 torch.from_numpy(seed_arr).to(self.device, non_blocking=True),
                                 self._upload([int(t) for t in token_indices], torch.int32), out)
         if self.device.type != "cuda":
-            return out.tolist(), None, rows
+            return out.tolist(), None, rows, out
         if self._host is None or self._host.numel() < rows:
             self._host = torch.empty(max(rows, 64), dtype=torch.int32, pin_memory=True)
         self._host[:rows].copy_(out, non_blocking=True)
         event = torch.cuda.Event()
         event.record()
-        return self._host, event, rows
+        return self._host, event, rows, out

@@ -262,10 +262,15 @@ class PreparingRunner(FakeRunner):
                 self._release()
         return list(requests)
 
-    def launch_prepared(self, prepared, tokens):
+    fed_from_device = 0
+
+    def launch_prepared(self, prepared, tokens, device_ids=None):
         from qwen25vl_lite.engine.runner import StepEntry
         self.launched += 1
         self._release()
+        if tokens is None:                       # the ids the sampler left "on the device"
+            tokens = list(device_ids)
+            self.fed_from_device += 1
         assert len(tokens) == len(prepared)
         return self.step([StepEntry(r, [t], [0]) for r, t in zip(prepared, tokens)])
 
@@ -280,6 +285,22 @@ class AsyncSampler(FakeSampler):
 
     def collect(self, pending):
         return pending
+
+
+class DeviceFeedSampler(FakeSampler):
+    """Like the engine's sampler it says where the drawn ids lie before the host has them, so the
+    engine can launch the next step from there without waiting for them."""
+
+    def sample_async(self, rows, params, seeds, token_indices, previous):
+        ids = [next_token(h) for h in rows]
+        return ids, None, len(ids), list(ids)
+
+    def collect(self, pending):
+        return pending[0]
+
+    @staticmethod
+    def device_ids(pending):
+        return pending[3]
 
 
 def test_prepared_decode_steps_change_nothing():
@@ -344,17 +365,20 @@ def test_next_step_is_launched_before_the_bookkeeping_and_survives_an_abort():
     runner.cache.check([])
 
 
+@pytest.mark.parametrize("sampler", [AsyncSampler, DeviceFeedSampler])
 @pytest.mark.parametrize("seed", range(8))
-def test_random_arrivals_stops_and_aborts_with_steps_packed_and_launched_ahead(seed):
+def test_random_arrivals_stops_and_aborts_with_steps_packed_and_launched_ahead(seed, sampler):
     """Requests of random lengths arrive at random steps, some end by a stop token, some are
     aborted, the pool is small enough for preemptions: every finished request has exactly the
     tokens of its own history (the fake step function derives each token from all before it), no
-    page is lost, and the steps that are packed or launched ahead are really used."""
+    page is lost, and the steps that are packed or launched ahead are really used.  With a sampler
+    that leaves its ids "on the device" the next step is launched before the host knows whether a
+    request has just ended by its token: such a request draws nothing from that step."""
     import random
     rng = random.Random(seed)
     ecfg = EngineConfig(num_blocks=40, block_size=4, max_num_seqs=4, max_num_batched_tokens=16)
     runner = PreparingRunner(40, 4, ecfg.max_num_seqs + 1)
-    engine = LLMEngine(runner, AsyncSampler(), ecfg, eos_token_id=None)
+    engine = LLMEngine(runner, sampler(), ecfg, eos_token_id=None)
     runner._requests = _LiveView(engine)
     plans, outs, aborted = {}, {}, set()
     to_add = 10
@@ -386,4 +410,5 @@ def test_random_arrivals_stops_and_aborts_with_steps_packed_and_launched_ahead(s
         assert outs[sid].output_token_ids == want, (sid, prompt, n, stop)
         assert outs[sid].finish_reason == ("stop" if stop is not None else "length")
     assert runner.launched > 0 and runner.dropped == runner.prepared - runner.launched and runner.held is None
+    assert (runner.fed_from_device > 0) == (sampler is DeviceFeedSampler)
     runner.cache.check([])
