@@ -290,7 +290,7 @@ class LLMEngine:
             logits, samplers = launched                    # the step is running already
             decoded = len(samplers)
             self.stats_.decode_tokens += decoded
-        elif prepared is not None and not self.waiting and [s.seq_id for s in self.running] == prepared[1] \
+        elif prepared is not None and not self._could_admit() and [s.seq_id for s in self.running] == prepared[1] \
                 and all(s.pending == 1 for s in self.running):
             samplers = list(self.running)
             decoded = len(samplers)
@@ -359,7 +359,7 @@ class LLMEngine:
         token, or anything else that changes the batch, makes ``step`` drop the preparation; the
         pages it took stay with their requests."""
         runner = self.runner
-        if self.waiting or not hasattr(runner, "prepare_decode") or len(samplers) != len(self.running) \
+        if not hasattr(runner, "prepare_decode") or len(samplers) != len(self.running) \
                 or len(self.running) > self.ecfg.max_num_batched_tokens:
             return None
         for seq in self.running:
@@ -372,7 +372,26 @@ class LLMEngine:
                 runner.cache.ensure(seq.request.cache, seq.num_computed + 1)
         except OutOfPages:
             return None
+        if self._could_admit():            # a request that waits would join the next step: that step is not known yet
+            return None
         return runner.prepare_decode([seq.request for seq in self.running]), [s.seq_id for s in self.running]
+
+    def _could_admit(self) -> bool:
+        """Whether ``schedule`` would take the first waiting request into the next step, given that
+        every running request decodes one token in it: a seat, a slot, budget, and pages for its
+        first portion (as ``schedule`` asks for them).  While the pool is full the requests that wait
+        cannot join, and the next decode step is known all the same."""
+        if not self.waiting:
+            return False
+        cache = self.runner.cache
+        if len(self.running) >= self.ecfg.max_num_seqs or cache.free_slots <= 0:
+            return False
+        budget = self.ecfg.max_num_batched_tokens - len(self.running)
+        n = self._portion(self.waiting[0], budget) if budget > 0 else 0
+        if n <= 0:
+            return False
+        pages = -(-n // cache.page_size)                   # what a request that holds nothing yet needs in every group
+        return all(g.pool.num_free >= pages for g in cache.groups)
 
     def _drop(self, prepared) -> None:
         """A step that was packed ahead and will not run: the runner takes back what it held for it."""

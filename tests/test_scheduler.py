@@ -412,3 +412,34 @@ def test_random_arrivals_stops_and_aborts_with_steps_packed_and_launched_ahead(s
     assert runner.launched > 0 and runner.dropped == runner.prepared - runner.launched and runner.held is None
     assert (runner.fed_from_device > 0) == (sampler is DeviceFeedSampler)
     runner.cache.check([])
+
+
+def test_steps_are_packed_ahead_while_a_request_waits_that_cannot_join():
+    """Two seats, three requests: while the third waits for a seat the two that run decode in steps
+    that are packed and launched ahead (the next step is known: nobody can join it); when one of
+    them ends, the one that waits joins the very next step, and every request has its own tokens."""
+    prompts = [[5, 6, 7], [9] * 6, [1, 2, 3, 4]]
+    lengths = [6, 14, 5]
+    ecfg = EngineConfig(num_blocks=64, block_size=4, max_num_seqs=2)
+    runner = PreparingRunner(64, 4, ecfg.max_num_seqs + 1)
+    engine = LLMEngine(runner, DeviceFeedSampler(), ecfg, eos_token_id=None)
+    runner._requests = _LiveView(engine)
+    ids = [engine.add_request(p, SamplingParams(max_tokens=n, ignore_eos=True)) for p, n in zip(prompts, lengths)]
+    outs, ahead_while_waiting, joined_at, ended_at = {}, 0, None, None
+    for step in range(200):
+        before = runner.launched
+        for o in engine.step():
+            outs[o.seq_id] = o
+            if o.seq_id == ids[0] and ended_at is None:
+                ended_at = step
+        if engine.waiting and runner.launched > before:
+            ahead_while_waiting += 1
+        if joined_at is None and any(s.seq_id == ids[2] for s in engine.running):
+            joined_at = step
+        if not engine.has_work():
+            break
+    assert ahead_while_waiting >= 3
+    assert ended_at is not None and joined_at is not None and joined_at <= ended_at + 1
+    for i in range(3):
+        assert outs[ids[i]].output_token_ids == expected(prompts[i], lengths[i])
+    runner.cache.check([])
